@@ -1,0 +1,168 @@
+/* liblithos_b200 — C ABI of the B200-native batch-1 decode hot path.
+ *
+ * Plain C: integer status codes, opaque context, device addresses as
+ * uint64_t (CUdeviceptr), host buffers as plain pointers.  Each entry point
+ * names the reference interface it replaces (paths relative to the reference
+ * project root).  Every call returns LB_OK (0) or an error code; the text of
+ * the last error is available from lb_last_error().  Nothing is ever skipped
+ * silently: a missing kernel image, driver or GPU is an error, there is no CPU
+ * fallback.
+ *
+ * Threading: one host thread per context, kernels are issued in program order
+ * on the context's own stream (the reference launcher is single-threaded with
+ * one main stream, src/launcher.s:455-492).
+ */
+#ifndef LITHOS_B200_H
+#define LITHOS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct lb_ctx lb_ctx;
+typedef struct lb_model lb_model;
+
+enum {
+    LB_OK = 0,
+    LB_ERR_INVALID = 1,     /* bad argument (shape, alignment, NULL) */
+    LB_ERR_NO_DRIVER = 2,   /* libcuda.so.1 could not be loaded / no device */
+    LB_ERR_CUDA = 3,        /* a CUDA driver call failed (see lb_last_error) */
+    LB_ERR_NO_KERNEL = 4,   /* kernel image or entry point missing */
+    LB_ERR_DEVICE_WAIT = 5, /* a bounded device-side wait gave up; status word in the message */
+    LB_ERR_IO = 6,          /* file could not be read / bad weight index */
+    LB_ERR_NOMEM = 7,
+    LB_ERR_STATE = 8        /* call not valid in the current state (e.g. replay before capture) */
+};
+
+const char* lb_status_string(int status);
+const char* lb_version(void);
+
+/* ---- context ---------------------------------------------------------------
+ * Replaces _start's cuInit / cuDeviceGet / cuCtxCreate / cuStreamCreate and
+ * load_cubins (src/launcher.s:397-520, :3708-3965).  kernel_dir holds the
+ * sm_100a cubins; NULL = the directory "kernels" beside the shared library.
+ * Unlike the reference, a cubin or entry point that cannot be found is an
+ * error here (the launcher stores NULL and skips every launch of it). */
+int lb_init(int device, const char* kernel_dir, lb_ctx** out);
+void lb_destroy(lb_ctx* ctx);
+const char* lb_last_error(const lb_ctx* ctx);
+int lb_device_sm_count(const lb_ctx* ctx);
+/* status word written by bounded device-side waits (0 = none gave up); reading it synchronises the stream */
+int lb_device_status(lb_ctx* ctx, uint32_t* status_out);
+/* number of kernels this library has launched on the context (graph replays count their kernel nodes) */
+uint64_t lb_launch_count(const lb_ctx* ctx);
+void lb_launch_count_reset(lb_ctx* ctx);
+/* enable (1, default) / disable (0) programmatic dependent launch between consecutive kernels */
+void lb_set_pdl(lb_ctx* ctx, int on);
+
+/* ---- generic module load + launch ----------------------------------------------
+ * The reference's own mechanism, kept as is: load_one_cubin = file read +
+ * cuModuleLoadData + cuModuleGetFunction (src/launcher.s:3861-3965) and
+ * cuLaunchKernel with a void** parameter array (src/launcher.s:744-762).  Any cubin
+ * that keeps the reference's entry names and parameter blocks (the ones under
+ * lithos_b200/kernels/compat do) can be driven through these three calls. */
+int lb_module_load(lb_ctx* ctx, const char* cubin_path, int* module_out);
+int lb_module_get_kernel(lb_ctx* ctx, int module, const char* entry, uint64_t* kernel_out);
+int lb_launch_kernel(lb_ctx* ctx, uint64_t kernel, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by,
+                     unsigned bz, unsigned smem_bytes, void** params);
+
+/* ---- device memory: replaces alloc_buffers (src/launcher.s:2981-3136) ------ */
+int lb_malloc(lb_ctx* ctx, size_t bytes, uint64_t* dptr_out);
+int lb_free(lb_ctx* ctx, uint64_t dptr);
+int lb_malloc_host(lb_ctx* ctx, size_t bytes, void** host_out); /* pinned */
+int lb_free_host(lb_ctx* ctx, void* host);
+int lb_memcpy_h2d(lb_ctx* ctx, uint64_t dst, const void* src, size_t bytes); /* async on the context stream */
+int lb_memcpy_d2h(lb_ctx* ctx, void* dst, uint64_t src, size_t bytes);       /* async on the context stream */
+int lb_memcpy_d2d(lb_ctx* ctx, uint64_t dst, uint64_t src, size_t bytes);
+int lb_memset(lb_ctx* ctx, uint64_t dst, int byte_value, size_t bytes);
+int lb_sync(lb_ctx* ctx); /* replaces cuCtxSynchronize (src/launcher.s:931) */
+
+/* ---- timing on the context's stream (CUDA events) -------------------------- */
+int lb_timer_start(lb_ctx* ctx);
+int lb_timer_stop(lb_ctx* ctx, float* ms_out); /* synchronises */
+/* overwrite a > L2-sized buffer so that the next kernel starts with a cold L2 */
+int lb_flush_l2(lb_ctx* ctx);
+
+/* ---- seeded synthetic tensors (host) ---------------------------------------
+ * Element i of stream s is a pure function of (seed, s, i). */
+void lb_fill_u32(uint32_t* dst, size_t n, uint64_t seed, uint64_t stream); /* 8 nibbles U{0..15} per word */
+void lb_fill_normal_f32(float* dst, size_t n, uint64_t seed, uint64_t stream, float mean, float std);
+void lb_fill_normal_f16(uint16_t* dst, size_t n, uint64_t seed, uint64_t stream, float mean, float std);
+void lb_fill_normal_bf16(uint16_t* dst, size_t n, uint64_t seed, uint64_t stream, float mean, float std);
+void lb_fill_uniform_f32(float* dst, size_t n, uint64_t seed, uint64_t stream, float lo, float hi);
+void lb_fill_scales_f16(uint16_t* dst, size_t n, uint64_t seed, uint64_t stream); /* |N(0,1)|*0.01+1e-3 */
+void lb_convert_f32_to_f16(const float* src, uint16_t* dst, size_t n);
+void lb_convert_f32_to_bf16(const float* src, uint16_t* dst, size_t n);
+void lb_convert_f16_to_f32(const uint16_t* src, float* dst, size_t n);
+void lb_convert_bf16_to_f32(const uint16_t* src, float* dst, size_t n);
+
+/* ---- GPTQ int4 GEMV ----------------------------------------------------------
+ * Replaces launch_proj + gptq_gemv_safe (src/launcher.s:1231-1535,
+ * minds/gptq_gemv_safe.ptx:46-55; spec inference/gemv.ls:22-186).
+ *   qweight int32 [K/8,N], scales fp16 [K/128,N], qzeros int32 [K/128,N/8]
+ *   (0 = zero-point 8 as in every reference kernel).  K % 128 == 0, N % 32 == 0.
+ * flags select the activation / result types (primary contract: fp16 x, fp16 y).
+ * The result OVERWRITES y unless LB_GEMV_Y_ACCUM is set (the reference kernel
+ * always accumulates into a caller-zeroed y). */
+enum {
+    LB_GEMV_X_F32 = 1 << 0,   /* x is fp32 (rounded to fp16 inside) instead of fp16 */
+    LB_GEMV_Y_F32 = 1 << 1,   /* y is fp32 instead of fp16 */
+    LB_GEMV_Y_ACCUM = 1 << 2, /* y (fp32) += result */
+    LB_GEMV_Y_SWIGLU = 1 << 3 /* N columns are interleaved 64-wide (gate, up) blocks;
+                                 y fp16 [N/2] = silu(gate)*up  (kernels.ls:61-66) */
+};
+int lb_gemv_int4(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y, int K, int N,
+                 int flags);
+/* Same call with HOST buffers: copies the operands in, runs, copies y out, synchronises.
+ * weights_resident != 0 reuses the device copy of the weights made by the previous call
+ * with the same host pointers (only x goes in and y comes out). */
+int lb_gemv_int4_host(lb_ctx* ctx, const uint32_t* qweight, const uint16_t* scales, const uint32_t* qzeros,
+                      const void* x, void* y, int K, int N, int flags, int weights_resident);
+/* fused variants used by the decode step (norm prologues): see lithos_b200/csrc/kernels/params.h */
+int lb_gemv_int4_fused(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y, int K,
+                       int N, int x_mode, int y_mode, uint64_t aux0, uint64_t aux1, uint64_t x_out, float eps);
+/* bit-exact targets: W(k,n) = fma(float(q), s, -z*s) as fp32 [K,N]; q as u8 [K,N] */
+int lb_gptq_dequant(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t w_out_f32, int K, int N);
+int lb_gptq_unpack(lb_ctx* ctx, uint64_t qweight, uint64_t q_out_u8, int K, int N);
+
+/* ---- dense bf16 [N,K] x vector: replaces launch_lm_head (src/launcher.s:2903-2970) */
+int lb_dense_bf16_gemv(lb_ctx* ctx, uint64_t w_bf16, uint64_t x, uint64_t y_f32, int N, int K, int x_is_f32);
+
+/* ---- gated DeltaNet ------------------------------------------------------------
+ * Replaces launch_recurrence / deltanet_fused (src/launcher.s:1960-2064,
+ * inference/deltanet_fused.ls:37-151) and decay_gate + gate_sigmoid
+ * (inference/decay_gate.ls:28-57, inference/recur.ls:45-55).
+ * state fp32 [HV,128,128] in place; q,k [n_steps,HK,128]; v, z, out [n_steps,HV,128];
+ * g, beta fp32 [n_steps,HV]; z == 0 skips the silu(z) gate.  in_is_f32 selects fp32
+ * (else bf16) q/k/v.  n_steps > 1 runs consecutive tokens with the state held on chip. */
+int lb_deltanet_step(lb_ctx* ctx, uint64_t state, uint64_t q, uint64_t k, uint64_t v, uint64_t z, uint64_t g,
+                     uint64_t beta, uint64_t out, int HV, int HK, int n_steps, int in_is_f32);
+int lb_decay_gate(lb_ctx* ctx, uint64_t a, uint64_t a_log, uint64_t dt_bias, uint64_t b, uint64_t g_out,
+                  uint64_t beta_out, int n);
+
+/* ---- GQA decode attention -----------------------------------------------------------
+ * Replaces launch_rope + launch_kv_cache_write + launch_attention
+ * (src/launcher.s:2260-2355, :2150-2247, :1846-1950; inference/attend.ls:21-191).
+ * q [HQ,256], k_new/v_new [HKV,256], gate [HQ,256] (0 = none) in bf16 (or fp32 when
+ * in_is_f32); q_norm_w/k_norm_w bf16 [256] (0 = no per-head RMSNorm); caches bf16
+ * [ctx,HKV,256]; the new row is written at `pos`, rows [0,pos] are attended; out fp32. */
+int lb_attention_decode(lb_ctx* ctx, uint64_t q, uint64_t k_new, uint64_t v_new, uint64_t gate, uint64_t q_norm_w,
+                        uint64_t k_norm_w, uint64_t k_cache, uint64_t v_cache, uint64_t out, int pos, int HQ, int HKV,
+                        int in_is_f32, int rot_dims, float rope_theta, float eps);
+
+/* ---- small kernels ---------------------------------------------------------------------
+ * rmsnorm: replaces launch_norm (src/launcher.s:1101-1219, inference/reduce.ls:21-147);
+ * argmax: replaces the CPU argmax loop (src/launcher.s:962-1073, inference/reduce.ls:214-313);
+ * embed: replaces the embed launch (src/launcher.s:713-762, inference/embed.ls:16-24). */
+int lb_rmsnorm(lb_ctx* ctx, uint64_t x, uint64_t res, uint64_t w_bf16, uint64_t y, uint64_t sum_out, int rows, int D,
+               float eps, int one_plus_w);
+int lb_argmax(lb_ctx* ctx, uint64_t x_f32, int n, uint64_t out_idx_i32);
+int lb_embed(lb_ctx* ctx, uint64_t table_bf16, uint64_t token_i32, uint64_t out_f32, int D);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

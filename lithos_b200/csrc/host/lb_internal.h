@@ -1,0 +1,152 @@
+/* Internal declarations shared by the host-side C files of liblithos_b200. */
+#ifndef LB_INTERNAL_H
+#define LB_INTERNAL_H
+
+#include <stddef.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <cuda.h> /* types and enums only: the driver itself is bound at run time */
+
+#include "lithos_b200.h"
+
+#define LB_API __attribute__((visibility("default")))
+
+/* ---- run-time binding of the CUDA driver (libcuda.so.1) ---------------- */
+/* The library must load (and export its symbols) on a machine without a GPU
+ * driver, so nothing links against libcuda: entry points are fetched through
+ * cuGetProcAddress on first lb_init. */
+#define LB_DRIVER_FUNCS(X)                                                                                      \
+    X(Init, cuInit, (unsigned int))                                                                             \
+    X(DriverGetVersion, cuDriverGetVersion, (int*))                                                             \
+    X(DeviceGet, cuDeviceGet, (CUdevice*, int))                                                                 \
+    X(DeviceGetCount, cuDeviceGetCount, (int*))                                                                 \
+    X(DeviceGetAttribute, cuDeviceGetAttribute, (int*, CUdevice_attribute, CUdevice))                           \
+    X(DevicePrimaryCtxRetain, cuDevicePrimaryCtxRetain, (CUcontext*, CUdevice))                                 \
+    X(DevicePrimaryCtxRelease, cuDevicePrimaryCtxRelease, (CUdevice))                                           \
+    X(CtxSetCurrent, cuCtxSetCurrent, (CUcontext))                                                              \
+    X(CtxSynchronize, cuCtxSynchronize, (void))                                                                 \
+    X(MemAlloc, cuMemAlloc, (CUdeviceptr*, size_t))                                                             \
+    X(MemFree, cuMemFree, (CUdeviceptr))                                                                        \
+    X(MemHostAlloc, cuMemHostAlloc, (void**, size_t, unsigned int))                                             \
+    X(MemFreeHost, cuMemFreeHost, (void*))                                                                      \
+    X(MemcpyHtoDAsync, cuMemcpyHtoDAsync, (CUdeviceptr, const void*, size_t, CUstream))                         \
+    X(MemcpyDtoHAsync, cuMemcpyDtoHAsync, (void*, CUdeviceptr, size_t, CUstream))                               \
+    X(MemcpyDtoDAsync, cuMemcpyDtoDAsync, (CUdeviceptr, CUdeviceptr, size_t, CUstream))                         \
+    X(MemsetD8Async, cuMemsetD8Async, (CUdeviceptr, unsigned char, size_t, CUstream))                           \
+    X(ModuleLoadData, cuModuleLoadData, (CUmodule*, const void*))                                               \
+    X(ModuleUnload, cuModuleUnload, (CUmodule))                                                                 \
+    X(ModuleGetFunction, cuModuleGetFunction, (CUfunction*, CUmodule, const char*))                             \
+    X(FuncSetAttribute, cuFuncSetAttribute, (CUfunction, CUfunction_attribute, int))                            \
+    X(LaunchKernel, cuLaunchKernel,                                                                             \
+      (CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**)) \
+    X(LaunchKernelEx, cuLaunchKernelEx, (const CUlaunchConfig*, CUfunction, void**, void**))                    \
+    X(StreamCreate, cuStreamCreate, (CUstream*, unsigned int))                                                  \
+    X(StreamDestroy, cuStreamDestroy, (CUstream))                                                               \
+    X(StreamSynchronize, cuStreamSynchronize, (CUstream))                                                       \
+    X(EventCreate, cuEventCreate, (CUevent*, unsigned int))                                                     \
+    X(EventDestroy, cuEventDestroy, (CUevent))                                                                  \
+    X(EventRecord, cuEventRecord, (CUevent, CUstream))                                                          \
+    X(EventSynchronize, cuEventSynchronize, (CUevent))                                                          \
+    X(EventElapsedTime, cuEventElapsedTime, (float*, CUevent, CUevent))                                         \
+    X(StreamBeginCapture, cuStreamBeginCapture, (CUstream, CUstreamCaptureMode))                                \
+    X(StreamEndCapture, cuStreamEndCapture, (CUstream, CUgraph*))                                               \
+    X(GraphInstantiate, cuGraphInstantiate, (CUgraphExec*, CUgraph, unsigned long long))                        \
+    X(GraphLaunch, cuGraphLaunch, (CUgraphExec, CUstream))                                                      \
+    X(GraphDestroy, cuGraphDestroy, (CUgraph))                                                                  \
+    X(GraphExecDestroy, cuGraphExecDestroy, (CUgraphExec))                                                      \
+    X(GraphGetNodes, cuGraphGetNodes, (CUgraph, CUgraphNode*, size_t*))                                         \
+    X(IpcGetMemHandle, cuIpcGetMemHandle, (CUipcMemHandle*, CUdeviceptr))                                       \
+    X(IpcOpenMemHandle, cuIpcOpenMemHandle, (CUdeviceptr*, CUipcMemHandle, unsigned int))                       \
+    X(IpcCloseMemHandle, cuIpcCloseMemHandle, (CUdeviceptr))                                                    \
+    X(GetErrorString, cuGetErrorString, (CUresult, const char**))                                               \
+    X(GetErrorName, cuGetErrorName, (CUresult, const char**))
+
+typedef struct {
+#define X(field, sym, args) CUresult(CUDAAPI* field) args;
+    LB_DRIVER_FUNCS(X)
+#undef X
+    int loaded;
+} lb_driver;
+
+extern lb_driver lb_drv;
+int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
+
+/* ---- kernels (entry points inside the cubins) -------------------------- */
+#define LB_KERNELS(X)                 \
+    X(gemv_int4_w128)                 \
+    X(gptq_dequant_f32)               \
+    X(gptq_unpack_u8)                 \
+    X(dense_bf16_gemv)                \
+    X(decay_gate_beta)                \
+    X(deltanet_step_bf16)             \
+    X(deltanet_step_f32)              \
+    X(attn_decode_split)              \
+    X(embed_bf16)                     \
+    X(argmax_f32)                     \
+    X(rmsnorm_f32)                    \
+    X(l2_flush)
+
+enum {
+#define X(name) LBK_##name,
+    LB_KERNELS(X)
+#undef X
+    LBK_COUNT
+};
+
+#define LB_MAX_MODULES 16
+#define LB_MAX_PEERS 8
+
+struct lb_ctx {
+    int device;
+    CUdevice cu_dev;
+    CUcontext cu_ctx;
+    CUstream stream;
+    CUevent ev[2];
+    int sm_count;
+    int max_smem_optin;
+    CUmodule modules[LB_MAX_MODULES];
+    int n_modules;
+    CUfunction fn[LBK_COUNT];
+    /* split-K scratch shared by every GEMV launched on this context's stream */
+    CUdeviceptr gemv_partial; /* fp32 [LB_GEMV_MAX_SPLITS][LB_GEMV_SCRATCH_N] */
+    CUdeviceptr gemv_counters; /* u32 per column tile, self-resetting */
+    CUdeviceptr attn_scratch;  /* split-KV partials */
+    size_t attn_scratch_bytes;
+    CUdeviceptr dev_status; /* u32 words written by bounded device-side waits */
+    CUdeviceptr flush_buf;  /* L2 flush target */
+    size_t flush_bytes;
+    uint64_t launches; /* kernels launched (or graph nodes replayed) since reset */
+    int pdl;           /* use programmatic dependent launch between kernels */
+    char err[512];
+};
+
+#define LB_GEMV_SCRATCH_N (1 << 18) /* widest N a split-K GEMV may have */
+#define LB_GEMV_MAX_SPLITS 16
+
+int lb_fail(lb_ctx* c, int status, const char* fmt, ...);
+int lb_cu(lb_ctx* c, CUresult r, const char* what);
+#define LB_CU(c, call)                                  \
+    do {                                                \
+        int _s = lb_cu((c), (call), #call);             \
+        if (_s != LB_OK) return _s;                     \
+    } while (0)
+#define LB_TRY(expr)                  \
+    do {                              \
+        int _s = (expr);              \
+        if (_s != LB_OK) return _s;   \
+    } while (0)
+
+int lb_launch(lb_ctx* c, int kernel, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned smem, void** params,
+              int pdl);
+
+/* rng helpers used by the synthetic model builder */
+uint64_t lb_rng_u64(uint64_t seed, uint64_t stream, uint64_t i);
+uint16_t lb_f32_to_f16(float f);
+float lb_f16_to_f32(uint16_t u);
+uint16_t lb_f32_to_bf16(float f);
+float lb_bf16_to_f32(uint16_t b);
+
+#endif

@@ -1,0 +1,260 @@
+/* Per-kernel launch wrappers: argument checks, launch geometry, parameter
+ * blocks.  These are the C counterparts of the reference's launch_* helpers
+ * (src/launcher.s:1101-2975), one per kernel family. */
+#include "lb_internal.h"
+#include "../kernels/params.h"
+#include <math.h>
+
+#define GEMV_THREADS ((LB_GEMV_WARPS + 1) * 32)
+
+/* Geometry of one int4 GEMV launch.  All CTAs of a launch must be co-resident
+ * (two per SM) and carry equal work, so that the HBM pipe — not a tail of late
+ * CTAs — ends the kernel: the K range is cut into `ksplit` group-aligned slices
+ * such that tiles*ksplit is close to (and not above) 2 CTAs per SM. */
+typedef struct { int tiles, ksplit, gps, stages; unsigned smem; } gemv_geom;
+
+static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
+    if (K <= 0 || N <= 0 || K % LB_GEMV_GROUP != 0 || N % 32 != 0)
+        return lb_fail(c, LB_ERR_INVALID, "int4 GEMV needs K %% 128 == 0 and N %% 32 == 0 (K=%d, N=%d)", K, N);
+    if (N > LB_GEMV_SCRATCH_N) return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: N=%d above the %d limit", N, LB_GEMV_SCRATCH_N);
+    int groups = K / LB_GEMV_GROUP;
+    g->tiles = (N + LB_GEMV_TILE_N - 1) / LB_GEMV_TILE_N;
+    int slots = 2 * c->sm_count;
+    int ks = slots / g->tiles;
+    if (ks < 1) ks = 1;
+    if (ks > LB_GEMV_MAX_SPLITS) ks = LB_GEMV_MAX_SPLITS;
+    if (ks > groups) ks = groups;
+    g->gps = (groups + ks - 1) / ks;
+    g->ksplit = (groups + g->gps - 1) / g->gps;
+    /* ring depth: as deep as fits when two CTAs share an SM, at most 12 */
+    size_t fixed = (size_t)g->gps * LB_GEMV_ROWS * 16 + (size_t)((g->gps + 3) & ~3) * 4 +
+                   (LB_GEMV_WARPS * LB_GEMV_TILE_N + 40) * 4;
+    size_t per_stage = LB_GEMV_STAGE_BYTES + 16; /* stage + its two mbarriers */
+    size_t budget = (size_t)(c->max_smem_optin - 2048) / 2;
+    int st = budget > fixed ? (int)((budget - fixed) / per_stage) : 0;
+    if (st < 2) { /* very long K slice: give the CTA the SM to itself */
+        budget = (size_t)(c->max_smem_optin - 2048);
+        st = budget > fixed ? (int)((budget - fixed) / per_stage) : 0;
+        if (st < 1) return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: K slice of %d groups does not fit shared memory", g->gps);
+    }
+    if (st > 12) st = 12;
+    if (st > g->gps) st = g->gps;
+    g->stages = st;
+    g->smem = (unsigned)((fixed + (size_t)st * per_stage + 127) & ~(size_t)127);
+    return LB_OK;
+}
+
+LB_API int lb_gemv_int4_fused(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y,
+                              int K, int N, int x_mode, int y_mode, uint64_t aux0, uint64_t aux1, uint64_t x_out,
+                              float eps) {
+    if (!c) return LB_ERR_INVALID;
+    if (!qweight || !scales || !x || !y) return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: NULL operand");
+    if (x_mode < LB_X_F16 || x_mode > LB_X_F32_HEADNORM_SILU || y_mode < LB_Y_F16 || y_mode > LB_Y_SWIGLU_F16)
+        return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: unknown x_mode/y_mode %d/%d", x_mode, y_mode);
+    if ((x_mode == LB_X_F32_RMSNORM && !aux0) || (x_mode == LB_X_F32_HEADNORM_SILU && (!aux0 || !aux1)))
+        return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: norm prologue without its weight/gate operand");
+    if (y_mode == LB_Y_SWIGLU_F16 && N % 128 != 0)
+        return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: SwiGLU epilogue needs N %% 128 == 0 (N=%d)", N);
+    if (((qweight | scales | qzeros | x | y | aux0 | aux1 | x_out) & 15ull) != 0)
+        return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: operands must be 16-byte aligned");
+    gemv_geom g;
+    LB_TRY(gemv_plan(c, K, N, &g));
+    lb_gemv_params p;
+    memset(&p, 0, sizeof p);
+    p.qweight = (const uint32_t*)qweight;
+    p.scales = (const uint16_t*)scales;
+    p.qzeros = (const uint32_t*)qzeros;
+    p.x = (const void*)x;
+    p.y = (void*)y;
+    p.aux0 = (const void*)aux0;
+    p.aux1 = (const void*)aux1;
+    p.x_out = (uint16_t*)x_out;
+    p.partial = (float*)c->gemv_partial;
+    p.counters = (uint32_t*)c->gemv_counters;
+    p.status = (uint32_t*)c->dev_status;
+    p.K = K; p.N = N;
+    p.ksplit = g.ksplit;
+    p.groups_per_split = g.gps;
+    p.stages = g.stages;
+    p.x_mode = x_mode; p.y_mode = y_mode;
+    p.eps = eps;
+    void* params[] = {&p};
+    return lb_launch(c, LBK_gemv_int4_w128, (unsigned)g.tiles, (unsigned)g.ksplit, 1, GEMV_THREADS, g.smem, params, 1);
+}
+
+LB_API int lb_gemv_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y, int K,
+                        int N, int flags) {
+    if (!c) return LB_ERR_INVALID;
+    int x_mode = (flags & LB_GEMV_X_F32) ? LB_X_F32 : LB_X_F16;
+    int y_mode = (flags & LB_GEMV_Y_SWIGLU) ? LB_Y_SWIGLU_F16
+                 : (flags & LB_GEMV_Y_ACCUM) ? LB_Y_F32_ACCUM
+                 : (flags & LB_GEMV_Y_F32)   ? LB_Y_F32
+                                             : LB_Y_F16;
+    return lb_gemv_int4_fused(c, qweight, scales, qzeros, x, y, K, N, x_mode, y_mode, 0, 0, 0, 1e-6f);
+}
+
+/* Host-buffer entry: the reference-facing call a launcher without device
+ * buffers of its own would make.  Device copies of the weights are cached on
+ * the context between calls. */
+static struct {
+    lb_ctx* owner;
+    const void *hq, *hs, *hz;
+    int K, N;
+    CUdeviceptr dq, ds, dz, dx, dy;
+} g_host_cache;
+
+static void host_cache_drop(lb_ctx* c) {
+    if (g_host_cache.owner != c) return;
+    if (g_host_cache.dq) lb_drv.MemFree(g_host_cache.dq);
+    if (g_host_cache.ds) lb_drv.MemFree(g_host_cache.ds);
+    if (g_host_cache.dz) lb_drv.MemFree(g_host_cache.dz);
+    if (g_host_cache.dx) lb_drv.MemFree(g_host_cache.dx);
+    if (g_host_cache.dy) lb_drv.MemFree(g_host_cache.dy);
+    memset(&g_host_cache, 0, sizeof g_host_cache);
+}
+
+void lb_ops_release(lb_ctx* c) { host_cache_drop(c); }
+
+LB_API int lb_gemv_int4_host(lb_ctx* c, const uint32_t* qweight, const uint16_t* scales, const uint32_t* qzeros,
+                             const void* x, void* y, int K, int N, int flags, int weights_resident) {
+    if (!c || !qweight || !scales || !x || !y) return lb_fail(c, LB_ERR_INVALID, "lb_gemv_int4_host: NULL operand");
+    gemv_geom g;
+    LB_TRY(gemv_plan(c, K, N, &g));
+    LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
+    size_t qb = (size_t)K / 8 * N * 4, sb = (size_t)K / 128 * N * 2, zb = (size_t)K / 128 * N / 2;
+    size_t xb = (size_t)K * ((flags & LB_GEMV_X_F32) ? 4 : 2);
+    size_t yb = (size_t)((flags & LB_GEMV_Y_SWIGLU) ? N / 2 : N) *
+                ((flags & (LB_GEMV_Y_F32 | LB_GEMV_Y_ACCUM)) && !(flags & LB_GEMV_Y_SWIGLU) ? 4 : 2);
+    int hit = weights_resident && g_host_cache.owner == c && g_host_cache.hq == qweight && g_host_cache.hs == scales &&
+              g_host_cache.hz == qzeros && g_host_cache.K == K && g_host_cache.N == N;
+    if (!hit) {
+        host_cache_drop(g_host_cache.owner);
+        g_host_cache.owner = c;
+        LB_CU(c, lb_drv.MemAlloc(&g_host_cache.dq, qb));
+        LB_CU(c, lb_drv.MemAlloc(&g_host_cache.ds, sb));
+        if (qzeros) LB_CU(c, lb_drv.MemAlloc(&g_host_cache.dz, zb));
+        LB_CU(c, lb_drv.MemAlloc(&g_host_cache.dx, (size_t)K * 4));
+        LB_CU(c, lb_drv.MemAlloc(&g_host_cache.dy, (size_t)N * 4));
+        LB_CU(c, lb_drv.MemcpyHtoDAsync(g_host_cache.dq, qweight, qb, c->stream));
+        LB_CU(c, lb_drv.MemcpyHtoDAsync(g_host_cache.ds, scales, sb, c->stream));
+        if (qzeros) LB_CU(c, lb_drv.MemcpyHtoDAsync(g_host_cache.dz, qzeros, zb, c->stream));
+        g_host_cache.hq = qweight; g_host_cache.hs = scales; g_host_cache.hz = qzeros;
+        g_host_cache.K = K; g_host_cache.N = N;
+    }
+    LB_CU(c, lb_drv.MemcpyHtoDAsync(g_host_cache.dx, x, xb, c->stream));
+    if (flags & LB_GEMV_Y_ACCUM) LB_CU(c, lb_drv.MemcpyHtoDAsync(g_host_cache.dy, y, yb, c->stream));
+    LB_TRY(lb_gemv_int4(c, g_host_cache.dq, g_host_cache.ds, g_host_cache.dz, g_host_cache.dx, g_host_cache.dy, K, N,
+                        flags));
+    LB_CU(c, lb_drv.MemcpyDtoHAsync(y, g_host_cache.dy, yb, c->stream));
+    LB_CU(c, lb_drv.StreamSynchronize(c->stream));
+    return LB_OK;
+}
+
+LB_API int lb_gptq_dequant(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t w_out, int K, int N) {
+    if (!c || !qweight || !scales || !w_out || K % 128 || N % 8) return lb_fail(c, LB_ERR_INVALID, "lb_gptq_dequant: bad argument");
+    void* params[] = {&qweight, &scales, &qzeros, &w_out, &K, &N};
+    return lb_launch(c, LBK_gptq_dequant_f32, (unsigned)((N + 255) / 256), (unsigned)(K / 8), 1, 256, 0, params, 0);
+}
+
+LB_API int lb_gptq_unpack(lb_ctx* c, uint64_t qweight, uint64_t q_out, int K, int N) {
+    if (!c || !qweight || !q_out || K % 8) return lb_fail(c, LB_ERR_INVALID, "lb_gptq_unpack: bad argument");
+    void* params[] = {&qweight, &q_out, &K, &N};
+    return lb_launch(c, LBK_gptq_unpack_u8, (unsigned)((N + 255) / 256), (unsigned)(K / 8), 1, 256, 0, params, 0);
+}
+
+int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps) {
+    if (!c || !w || !x || !y || K % 8 || N <= 0) return lb_fail(c, LB_ERR_INVALID, "dense bf16 GEMV: bad argument");
+    lb_dense_params p;
+    memset(&p, 0, sizeof p);
+    p.w = (const uint16_t*)w; p.x = (const void*)x; p.y = (float*)y; p.norm_w = (const void*)norm_w;
+    p.N = N; p.K = K; p.x_mode = x_mode; p.eps = eps;
+    int rows_per_cta = 8;
+    int ctas = (N + rows_per_cta - 1) / rows_per_cta;
+    int cap = c->sm_count * 8; /* persistent-ish: each CTA strides over rows */
+    if (ctas > cap) ctas = cap;
+    void* params[] = {&p};
+    return lb_launch(c, LBK_dense_bf16_gemv, (unsigned)ctas, 1, 1, 256, (unsigned)(K * 4 + 256), params, 1);
+}
+
+LB_API int lb_dense_bf16_gemv(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_is_f32) {
+    return lb_dense_launch(c, w, x, y, N, K, x_is_f32 ? LB_X_F32 : LB_X_F16, 0, 1e-6f);
+}
+
+LB_API int lb_deltanet_step(lb_ctx* c, uint64_t state, uint64_t q, uint64_t k, uint64_t v, uint64_t z, uint64_t g,
+                            uint64_t beta, uint64_t out, int HV, int HK, int n_steps, int in_is_f32) {
+    if (!c || !state || !q || !k || !v || !g || !beta || !out || HV <= 0 || HK <= 0 || HV % HK || n_steps < 1)
+        return lb_fail(c, LB_ERR_INVALID, "lb_deltanet_step: bad argument");
+    lb_deltanet_params p;
+    memset(&p, 0, sizeof p);
+    p.state = (float*)state; p.q = (const void*)q; p.k = (const void*)k; p.v = (const void*)v;
+    p.z = (const float*)z; p.g = (const float*)g; p.beta = (const float*)beta; p.out = (float*)out;
+    p.HV = HV; p.HK = HK;
+    void* params[] = {&p, &n_steps};
+    return lb_launch(c, in_is_f32 ? LBK_deltanet_step_f32 : LBK_deltanet_step_bf16, (unsigned)HV, 4, 1, 128, 0, params, 1);
+}
+
+LB_API int lb_decay_gate(lb_ctx* c, uint64_t a, uint64_t a_log, uint64_t dt_bias, uint64_t b, uint64_t g_out,
+                         uint64_t beta_out, int n) {
+    if (!c || !a || !a_log || !dt_bias || !g_out || n <= 0) return lb_fail(c, LB_ERR_INVALID, "lb_decay_gate: bad argument");
+    lb_decay_params p = {(const float*)a, (const float*)a_log, (const float*)dt_bias, (const float*)b,
+                         (float*)g_out, (float*)beta_out, n};
+    void* params[] = {&p};
+    return lb_launch(c, LBK_decay_gate_beta, (unsigned)((n + 127) / 128), 1, 1, 128, 0, params, 1);
+}
+
+/* number of position slices: enough CTAs to fill the GPU, at least 256 rows each */
+int lb_attn_splits(lb_ctx* c, int pos, int HKV) {
+    int want = (2 * c->sm_count + HKV - 1) / HKV;
+    int by_len = pos / 256;
+    int s = want < by_len ? want : by_len;
+    if (s < 1) s = 1;
+    if (s > 64) s = 64;
+    return s;
+}
+
+unsigned lb_attn_smem(int G) { return (unsigned)((G * 256 + 256 + 256 + 40 + 2 * 8 * 8 + 8 * G * 256) * 4 + 64); }
+
+LB_API int lb_attention_decode(lb_ctx* c, uint64_t q, uint64_t k_new, uint64_t v_new, uint64_t gate, uint64_t q_norm_w,
+                               uint64_t k_norm_w, uint64_t k_cache, uint64_t v_cache, uint64_t out, int pos, int HQ,
+                               int HKV, int in_is_f32, int rot_dims, float rope_theta, float eps) {
+    if (!c || !q || !k_new || !v_new || !k_cache || !v_cache || !out || pos < 0 || HKV <= 0 || HQ % HKV)
+        return lb_fail(c, LB_ERR_INVALID, "lb_attention_decode: bad argument");
+    int G = HQ / HKV;
+    if (!(G == 1 || G == 2 || G == 3 || G == 4 || G == 6 || G == 8) || HKV > 8)
+        return lb_fail(c, LB_ERR_INVALID, "lb_attention_decode: unsupported head ratio %d/%d", HQ, HKV);
+    if ((q_norm_w == 0) != (k_norm_w == 0)) return lb_fail(c, LB_ERR_INVALID, "lb_attention_decode: q/k norm weights must come together");
+    if (rot_dims < 0 || rot_dims > 256 || rot_dims % 2) return lb_fail(c, LB_ERR_INVALID, "lb_attention_decode: bad rot_dims");
+    lb_attn_params p;
+    memset(&p, 0, sizeof p);
+    p.q = (const void*)q; p.k_new = (const void*)k_new; p.v_new = (const void*)v_new; p.gate = (const void*)gate;
+    p.q_norm_w = (const uint16_t*)q_norm_w; p.k_norm_w = (const uint16_t*)k_norm_w;
+    p.k_cache = (uint16_t*)k_cache; p.v_cache = (uint16_t*)v_cache; p.out = (float*)out;
+    p.scratch = (float*)c->attn_scratch; p.counters = (uint32_t*)(c->gemv_counters + 2048 * 4);
+    p.pos = pos; p.HQ = HQ; p.HKV = HKV;
+    p.splits = lb_attn_splits(c, pos, HKV);
+    p.in_dtype = in_is_f32 ? 1 : 0;
+    p.gate_stride = 256; p.q_stride = 256;
+    p.rot_dims = rot_dims; p.log2_theta = log2f(rope_theta); p.eps = eps;
+    void* params[] = {&p};
+    return lb_launch(c, LBK_attn_decode_split, (unsigned)HKV, (unsigned)p.splits, 1, 256, lb_attn_smem(G), params, 1);
+}
+
+LB_API int lb_rmsnorm(lb_ctx* c, uint64_t x, uint64_t res, uint64_t w, uint64_t y, uint64_t sum_out, int rows, int D,
+                      float eps, int one_plus_w) {
+    if (!c || !x || !w || !y || rows <= 0 || D <= 0) return lb_fail(c, LB_ERR_INVALID, "lb_rmsnorm: bad argument");
+    void* params[] = {&x, &res, &w, &y, &sum_out, &D, &eps, &one_plus_w};
+    return lb_launch(c, LBK_rmsnorm_f32, (unsigned)rows, 1, 1, 256, 0, params, 1);
+}
+
+LB_API int lb_argmax(lb_ctx* c, uint64_t x, int n, uint64_t out_idx) {
+    if (!c || !x || !out_idx || n <= 0) return lb_fail(c, LB_ERR_INVALID, "lb_argmax: bad argument");
+    uint64_t zero = 0;
+    void* params[] = {&x, &n, &out_idx, &zero, &zero};
+    return lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1);
+}
+
+LB_API int lb_embed(lb_ctx* c, uint64_t table, uint64_t token, uint64_t out, int D) {
+    if (!c || !table || !token || !out || D <= 0) return lb_fail(c, LB_ERR_INVALID, "lb_embed: bad argument");
+    void* params[] = {&table, &token, &out, &D};
+    return lb_launch(c, LBK_embed_bf16, (unsigned)((D + 1023) / 1024), 1, 1, 256, 0, params, 1);
+}

@@ -1,0 +1,254 @@
+// GQA decode attention (split-KV flash-decode) for sm_100a.
+//
+// Restates inference/attend.ls:85-191 (online-softmax loop over the KV cache,
+// GQA map kv = h*n_kv/n_q, cache layout [seq, n_kv, d]) with the natural-exp
+// soft-max and true -inf start of inference/attend_full.ls:186-196, and fuses
+// what the reference runs as separate launches around it: per-head RMSNorm of
+// q and of the new k (models/.../attention/kernels.ls:7-8), partial RoPE on
+// interleaved pairs (inference/attend.ls:21-71), the KV append
+// (src/launcher.s:2150-2247) and the sigmoid output gate
+// (inference/attend_full.ls:236-248).
+//
+// The reference runs one CTA per query head and walks the positions serially
+// with two barriers each.  Here a CTA owns one KV head and one slice of the
+// positions, serves all G = HQ/HKV query heads of that KV head from a single
+// pass over the bf16 K/V rows (KV bytes are the roofline), keeps a per-warp
+// online soft-max, and the slices are merged in a fixed order by the last CTA
+// to arrive (ordered, so run-to-run identical).
+#include "common.cuh"
+#include "params.h"
+
+#define AT_D 256
+#define AT_THREADS 256
+#define AT_WARPS 8
+#define AT_GMAX 8
+#define AT_REC 260 // floats per (kv, split, g) record: 256 acc + m + l + pad
+
+__device__ __forceinline__ float ld_in(const void* p, size_t i, int is_f32) {
+    return is_f32 ? reinterpret_cast<const float*>(p)[i]
+                  : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// RMS-normalise (plain weight) then rotate the first rot_dims dims in
+// interleaved pairs at position pos; one value per thread, dst in shared.
+__device__ __forceinline__ void norm_rope_256(float v, const uint16_t* w, float* dst, float* red, int pos, int rot_dims,
+                                              float log2_theta, float eps, float post_scale) {
+    const int t = threadIdx.x;
+    if (w) {
+        float ss = block_sum(v * v, red);
+        v = v * rsqrtf(ss * (1.0f / AT_D) + eps) * bf16_bits_to_f32(w[t]);
+    }
+    dst[t] = v;
+    __syncthreads();
+    if (t < rot_dims / 2) {
+        // angle in double: pos * freq reaches 1e5 rad, far beyond fp32 resolution
+        double freq = exp2(-(double)log2_theta * (double)t / (double)(rot_dims / 2));
+        double sn, cs;
+        sincos((double)pos * freq, &sn, &cs);
+        float a = dst[2 * t], b = dst[2 * t + 1];
+        dst[2 * t] = a * (float)cs - b * (float)sn;
+        dst[2 * t + 1] = a * (float)sn + b * (float)cs;
+    }
+    __syncthreads();
+    dst[t] *= post_scale;
+    __syncthreads();
+}
+
+template <int G>
+__device__ __forceinline__ void attn_body(const lb_attn_params& p, float* sm) {
+    const int kv = blockIdx.x, split = blockIdx.y;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    float* q_s = sm;                      // [G][256]
+    float* kn_s = q_s + G * AT_D;         // [256] new key (bf16-rounded)
+    float* vn_s = kn_s + AT_D;            // [256] new value (bf16-rounded)
+    float* red = vn_s + AT_D;             // [40]
+    float* wm = red + 40;                 // [8][G] per-warp max
+    float* wl = wm + AT_WARPS * AT_GMAX;  // [8][G] per-warp sum
+    float* wacc = wl + AT_WARPS * AT_GMAX; // [8][G][256]
+    __shared__ uint32_t s_ticket;
+
+    pdl_wait();
+    const bool last = split == p.splits - 1;
+    const float LOG2E = 1.4426950408889634f;
+    const float qscale = rsqrtf((float)AT_D) * LOG2E; // scores kept in log2 units
+    for (int g = 0; g < G; ++g) {
+        const int hq = kv * G + g;
+        float v = ld_in(p.q, (size_t)hq * p.q_stride + t, p.in_dtype);
+        norm_rope_256(v, p.q_norm_w, q_s + g * AT_D, red, p.pos, p.rot_dims, p.log2_theta, p.eps, qscale);
+    }
+    if (last) {
+        float kr = ld_in(p.k_new, (size_t)kv * AT_D + t, p.in_dtype);
+        norm_rope_256(kr, p.k_norm_w, kn_s, red, p.pos, p.rot_dims, p.log2_theta, p.eps, 1.0f);
+        __nv_bfloat16 kb = __float2bfloat16_rn(kn_s[t]);
+        __nv_bfloat16 vb = __float2bfloat16_rn(ld_in(p.v_new, (size_t)kv * AT_D + t, p.in_dtype));
+        const size_t row = ((size_t)p.pos * p.HKV + kv) * AT_D + t;
+        reinterpret_cast<__nv_bfloat16*>(p.k_cache)[row] = kb; // KV append
+        reinterpret_cast<__nv_bfloat16*>(p.v_cache)[row] = vb;
+        kn_s[t] = __bfloat162float(kb);
+        vn_s[t] = __bfloat162float(vb);
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    // this lane's 8 dims of every query head
+    float qr[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qr[g][j] = q_s[g * AT_D + lane * 8 + j];
+
+    float m[G], l[G], acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
+    }
+
+    const int chunk = (p.pos + p.splits - 1) / p.splits;
+    const int t0 = split * chunk, t1 = min(p.pos, t0 + chunk);
+    const size_t row_stride = (size_t)p.HKV * AT_D;
+    const uint4* kbase = reinterpret_cast<const uint4*>(p.k_cache + (size_t)kv * AT_D) + lane;
+    const uint4* vbase = reinterpret_cast<const uint4*>(p.v_cache + (size_t)kv * AT_D) + lane;
+
+    auto step = [&](const float (&kf)[8], const float (&vf)[8]) {
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float d = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d = fmaf(qr[g][j], kf[j], d);
+            s[g] = d;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int g = 0; g < G; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float mn = fmaxf(m[g], s[g]);
+            const float corr = exp2f(m[g] - mn); // exp2f(-inf) = 0 on the first row
+            const float pr = exp2f(s[g] - mn);
+            m[g] = mn;
+            l[g] = fmaf(l[g], corr, pr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(acc[g][j], corr, pr * vf[j]);
+        }
+    };
+    auto unpack = [](const uint4& raw, float (&f)[8]) {
+        f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
+        f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
+        f[4] = __uint_as_float(raw.z << 16); f[5] = __uint_as_float(raw.z & 0xffff0000u);
+        f[6] = __uint_as_float(raw.w << 16); f[7] = __uint_as_float(raw.w & 0xffff0000u);
+    };
+
+    int r = t0 + warp;
+    // two rows in flight per warp
+    for (; r + AT_WARPS < t1; r += 2 * AT_WARPS) {
+        uint4 k0 = __ldg(kbase + (size_t)r * (row_stride / 8));
+        uint4 v0 = __ldg(vbase + (size_t)r * (row_stride / 8));
+        uint4 k1 = __ldg(kbase + (size_t)(r + AT_WARPS) * (row_stride / 8));
+        uint4 v1 = __ldg(vbase + (size_t)(r + AT_WARPS) * (row_stride / 8));
+        float kf[8], vf[8];
+        unpack(k0, kf); unpack(v0, vf); step(kf, vf);
+        unpack(k1, kf); unpack(v1, vf); step(kf, vf);
+    }
+    for (; r < t1; r += AT_WARPS) {
+        uint4 k0 = __ldg(kbase + (size_t)r * (row_stride / 8));
+        uint4 v0 = __ldg(vbase + (size_t)r * (row_stride / 8));
+        float kf[8], vf[8];
+        unpack(k0, kf); unpack(v0, vf); step(kf, vf);
+    }
+    if (last && warp == 0) { // the token being decoded, straight from shared memory
+        float kf[8], vf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            kf[j] = kn_s[lane * 8 + j];
+            vf[j] = vn_s[lane * 8 + j];
+        }
+        step(kf, vf);
+    }
+
+    // ---- merge the 8 warps (fixed order) ----
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (lane == 0) {
+            wm[warp * AT_GMAX + g] = m[g];
+            wl[warp * AT_GMAX + g] = l[g];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wacc[((size_t)warp * G + g) * AT_D + lane * 8 + j] = acc[g][j];
+    }
+    __syncthreads();
+    float Mg[G], Lg[G], Ag[G]; // thread t owns dim t
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float M = -INFINITY;
+        for (int w = 0; w < AT_WARPS; ++w) M = fmaxf(M, wm[w * AT_GMAX + g]);
+        float L = 0.f, A = 0.f;
+        for (int w = 0; w < AT_WARPS; ++w) {
+            const float mw = wm[w * AT_GMAX + g];
+            const float sc = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            L = fmaf(wl[w * AT_GMAX + g], sc, L);
+            A = fmaf(wacc[((size_t)w * G + g) * AT_D + t], sc, A);
+        }
+        Mg[g] = M; Lg[g] = L; Ag[g] = A;
+    }
+
+    // ---- merge the position slices across CTAs (fixed order, last arriver) ----
+    if (p.splits > 1) {
+        float* rec = p.scratch + ((size_t)(kv * p.splits + split) * G) * AT_REC;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            __stcg(rec + g * AT_REC + t, Ag[g]);
+            if (t == 0) {
+                __stcg(rec + g * AT_REC + 256, Mg[g]);
+                __stcg(rec + g * AT_REC + 257, Lg[g]);
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        if (t == 0) s_ticket = atomicAdd(p.counters + kv, 1u);
+        __syncthreads();
+        if (s_ticket != (uint32_t)(p.splits - 1)) return;
+        __threadfence();
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float M = -INFINITY;
+            for (int s2 = 0; s2 < p.splits; ++s2)
+                M = fmaxf(M, __ldcg(p.scratch + ((size_t)(kv * p.splits + s2) * G + g) * AT_REC + 256));
+            float L = 0.f, A = 0.f;
+            for (int s2 = 0; s2 < p.splits; ++s2) {
+                const float* r2 = p.scratch + ((size_t)(kv * p.splits + s2) * G + g) * AT_REC;
+                const float ms = __ldcg(r2 + 256);
+                const float sc = ms == -INFINITY ? 0.f : exp2f(ms - M);
+                L = fmaf(__ldcg(r2 + 257), sc, L);
+                A = fmaf(__ldcg(r2 + t), sc, A);
+            }
+            Lg[g] = L; Ag[g] = A;
+        }
+        if (t == 0) p.counters[kv] = 0u;
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int hq = kv * G + g;
+        float o = Ag[g] / Lg[g];
+        if (p.gate) o *= sigmoidf_dev(ld_in(p.gate, (size_t)hq * p.gate_stride + t, p.in_dtype));
+        p.out[(size_t)hq * AT_D + t] = o;
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(AT_THREADS) attn_decode_split(const __grid_constant__ lb_attn_params p) {
+    extern __shared__ __align__(16) float at_sm[];
+    const int G = p.HQ / p.HKV;
+    switch (G) {
+        case 1: attn_body<1>(p, at_sm); break;
+        case 2: attn_body<2>(p, at_sm); break;
+        case 3: attn_body<3>(p, at_sm); break;
+        case 4: attn_body<4>(p, at_sm); break;
+        case 6: attn_body<6>(p, at_sm); break;
+        case 8: attn_body<8>(p, at_sm); break;
+        default: break; // host rejects other ratios
+    }
+}

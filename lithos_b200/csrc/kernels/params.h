@@ -1,0 +1,112 @@
+/* Kernel parameter blocks shared by the host layer (C) and the kernels (CUDA).
+ * Every struct is passed by value as the single kernel parameter, so the
+ * layout here IS the launch ABI of the primary entry points.  (The entry
+ * points that keep the reference's own positional parameter blocks live in
+ * compat.cu and do not use these structs.) */
+#ifndef LB_KERNEL_PARAMS_H
+#define LB_KERNEL_PARAMS_H
+#include <stdint.h>
+
+/* ---- int4 GEMV ---------------------------------------------------------- */
+#define LB_GEMV_TILE_N 128   /* columns per CTA tile (512 B of packed words per row) */
+#define LB_GEMV_GROUP 128    /* GPTQ group size along K */
+#define LB_GEMV_ROWS 16      /* packed rows per group */
+#define LB_GEMV_WARPS 8      /* consumer warps per CTA (one more warp issues copies) */
+#define LB_GEMV_STAGE_BYTES (LB_GEMV_ROWS * LB_GEMV_TILE_N * 4 + LB_GEMV_TILE_N * 2 + LB_GEMV_TILE_N / 2 + 64)
+
+/* how the activation vector is produced from p.x */
+enum {
+    LB_X_F16 = 0,          /* x fp16 [K] */
+    LB_X_F32 = 1,          /* x fp32 [K], rounded to fp16 */
+    LB_X_F32_RMSNORM = 2,  /* x fp32 [K]; h = x*rsqrt(mean x^2+eps)*(1+w), w = aux0 bf16 [K] */
+    LB_X_F32_HEADNORM_SILU = 3 /* x fp32 [K] in heads of 128; h = x*rsqrt(mean_head x^2+eps)*w[i]*silu(z),
+                                  w = aux0 fp32 [128], z = aux1 fp32 [K] */
+};
+/* what is done with the N results */
+enum {
+    LB_Y_F16 = 0,       /* y fp16 [N] = result */
+    LB_Y_F32 = 1,       /* y fp32 [N] = result */
+    LB_Y_F32_ACCUM = 2, /* y fp32 [N] += result (residual add) */
+    LB_Y_SWIGLU_F16 = 3 /* columns come in interleaved 64-wide blocks (gate block, up block);
+                           y fp16 [N/2] = silu(gate)*up */
+};
+
+typedef struct {
+    const uint32_t* qweight; /* [K/8, N] */
+    const uint16_t* scales;  /* fp16 [K/128, N] */
+    const uint32_t* qzeros;  /* [K/128, N/8] or NULL: zero-point 8 */
+    const void* x;
+    void* y;
+    const void* aux0;
+    const void* aux1;
+    uint16_t* x_out;    /* optional fp16 [K]: the activation vector as the kernel used it */
+    float* partial;     /* split-K scratch, fp32 [ksplit][N] */
+    uint32_t* counters; /* split-K arrival counters, one per column tile, zero between launches */
+    uint32_t* status;   /* device status word (bounded waits) */
+    int32_t K, N;
+    int32_t ksplit;           /* gridDim.y */
+    int32_t groups_per_split; /* ceil(K/128 / ksplit) */
+    int32_t stages;           /* bulk-copy ring depth */
+    int32_t x_mode, y_mode;
+    float eps;
+} lb_gemv_params;
+
+/* ---- dense bf16 [N,K] x vector ------------------------------------------ */
+typedef struct {
+    const uint16_t* w; /* bf16 [N,K] row-major */
+    const void* x;     /* fp16 or fp32 [K] */
+    float* y;          /* fp32 [N] */
+    const void* norm_w; /* bf16 [K] when x_mode == LB_X_F32_RMSNORM */
+    int32_t N, K;
+    int32_t x_mode; /* LB_X_F16 | LB_X_F32 | LB_X_F32_RMSNORM */
+    float eps;
+} lb_dense_params;
+
+/* ---- gated DeltaNet step -------------------------------------------------- */
+typedef struct {
+    float* state;      /* fp32 [HV,128,128] updated in place */
+    const void* q;     /* [HK,128] bf16 or fp32 */
+    const void* k;     /* [HK,128] */
+    const void* v;     /* [HV,128] */
+    const float* z;    /* fp32 [HV,128] or NULL: no silu(z) output gate */
+    const float* g;    /* fp32 [HV] decay */
+    const float* beta; /* fp32 [HV] */
+    float* out;        /* fp32 [HV,128] */
+    int32_t HV, HK;
+} lb_deltanet_params;
+
+typedef struct {
+    const float* a;        /* [n] in_proj_a output */
+    const float* a_log;    /* [n] */
+    const float* dt_bias;  /* [n] */
+    const float* b;        /* [n] in_proj_b output */
+    float* g;              /* [n] decay out */
+    float* beta;           /* [n] beta out */
+    int32_t n;
+} lb_decay_params;
+
+/* ---- GQA decode attention ------------------------------------------------- */
+typedef struct {
+    const void* q;        /* [HQ,256] bf16 or fp32 (raw, before norm) */
+    const void* k_new;    /* [HKV,256] raw new key */
+    const void* v_new;    /* [HKV,256] new value */
+    const void* gate;     /* [HQ,256] or NULL */
+    const uint16_t* q_norm_w; /* bf16 [256] or NULL: skip q/k norm */
+    const uint16_t* k_norm_w; /* bf16 [256] */
+    uint16_t* k_cache;    /* bf16 [ctx,HKV,256] */
+    uint16_t* v_cache;
+    float* out;           /* fp32 [HQ,256] */
+    float* scratch;       /* split partials: [HKV][splits][G][(256 acc) + m + l] */
+    uint32_t* counters;   /* one per kv head, zero between launches */
+    int32_t pos;          /* position of the new token; rows [0,pos] are attended */
+    int32_t HQ, HKV;
+    int32_t splits;
+    int32_t in_dtype;     /* 0 = bf16 inputs, 1 = fp32 inputs */
+    int32_t gate_stride;  /* elements between consecutive heads of gate (256, or 512 when interleaved with q) */
+    int32_t q_stride;     /* elements between consecutive heads of q */
+    int32_t rot_dims;
+    float log2_theta;
+    float eps;
+} lb_attn_params;
+
+#endif

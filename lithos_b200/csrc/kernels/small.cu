@@ -1,0 +1,92 @@
+// Small kernels of the decode step: embedding gather, greedy argmax,
+// stand-alone RMSNorm, and the L2 flush used by the timing harness.
+#include "common.cuh"
+#include "params.h"
+
+// x = float(E[token]) : inference/embed.ls:16-24 with a bf16 table.  The token
+// id is read from device memory so a captured graph can be replayed with a new
+// token each step.
+extern "C" __global__ void embed_bf16(const uint16_t* __restrict__ table, const int* __restrict__ token,
+                                      float* __restrict__ out, int D) {
+    pdl_wait();
+    const size_t base = (size_t)token[0] * D;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < D; i += gridDim.x * blockDim.x)
+        out[i] = bf16_bits_to_f32(table[base + i]);
+}
+
+// Greedy sampling: index of the maximum, FIRST maximum on ties (strict > in
+// inference/reduce.ls:225-227 and src/launcher.s:1060-1063).  One CTA; the
+// (value, index) pairs are combined with "greater value, else smaller index",
+// which is order-independent, so the answer does not depend on the schedule.
+// Also writes the winner into next_token (the next step's embed input) and
+// advances *pos when given.
+extern "C" __global__ void __launch_bounds__(1024) argmax_f32(const float* __restrict__ x, int n, int* __restrict__ out_idx,
+                                                              int* __restrict__ next_token, int* __restrict__ pos) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    pdl_wait();
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = x[i];
+        if (v > bv) { bv = v; bi = i; } // ascending i per thread: first maximum kept
+    }
+    auto better = [](float v, int i, float bv2, int bi2) { return v > bv2 || (v == bv2 && i < bi2); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) { sv[w] = bv; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+        const int nw = blockDim.x >> 5;
+        bv = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            if (bi == 0x7fffffff) bi = 0; // all -inf / NaN: the reference's loop would keep index 0
+            out_idx[0] = bi;
+            if (next_token) next_token[0] = bi;
+            if (pos) pos[0] += 1;
+        }
+    }
+}
+
+// y = (x [+ r]) * w' * rsqrt(mean((x+r)^2) + eps), w' = 1+w or w (bf16 weight);
+// inference/reduce.ls:21-147.  One CTA per row of D values.  sum_out (may be
+// NULL) receives x+r.
+extern "C" __global__ void __launch_bounds__(256) rmsnorm_f32(const float* __restrict__ x, const float* __restrict__ res,
+                                                              const uint16_t* __restrict__ w, float* __restrict__ y,
+                                                              float* __restrict__ sum_out, int D, float eps,
+                                                              int one_plus_w) {
+    __shared__ float red[40];
+    pdl_wait();
+    const size_t row = (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = x[row + i] + (res ? res[row + i] : 0.f);
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rinv = rsqrtf(ss / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = x[row + i] + (res ? res[row + i] : 0.f);
+        if (sum_out) sum_out[row + i] = v;
+        const float ww = bf16_bits_to_f32(w[i]);
+        y[row + i] = v * rinv * (one_plus_w ? 1.0f + ww : ww);
+    }
+}
+
+// Overwrites a buffer larger than L2 so the next timed kernel starts cold.
+extern "C" __global__ void l2_flush(uint4* __restrict__ buf, size_t n16, uint32_t tag) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+        buf[i] = make_uint4(tag, tag, tag, tag);
+}

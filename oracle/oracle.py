@@ -1,0 +1,257 @@
+"""ctypes wrapper of the CPU oracle (oracle/oracle.c) — TEST INFRASTRUCTURE.
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may
+import this module.  The product package never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_LIB = _HERE / "liboracle.so"
+REF_DIR = _HERE / "_ref"  # reference PTX assembled for sm_100a (built by the Makefile)
+
+
+def build() -> None:
+    targets = ["liboracle.so"]
+    if Path("/root/reference/minds").is_dir():
+        targets.append("ref")
+    r = subprocess.run(["make", "-C", str(_HERE)] + targets, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("oracle build failed:\n" + r.stdout[-2000:] + r.stderr[-2000:])
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not _LIB.exists():
+            build()
+        _lib = C.CDLL(str(_LIB))
+        _lib.orc_num_threads.restype = C.c_int
+        _lib.orc_argmax.restype = C.c_int
+        _lib.orc_model_create.restype = C.c_void_p
+        _lib.orc_model_decode.restype = C.c_int
+        for n in ("orc_model_dn_state", "orc_model_conv_hist", "orc_model_k_cache", "orc_model_v_cache",
+                  "orc_model_logits", "orc_model_residual"):
+            getattr(_lib, n).restype = C.c_void_p
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def num_threads() -> int:
+    return lib().orc_num_threads()
+
+
+def bf16_to_f32(a: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(a, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(a: np.ndarray) -> np.ndarray:
+    u = _f32(a).view(np.uint32).astype(np.uint64)
+    r = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return r.astype(np.uint16)
+
+
+# ---- GPTQ -------------------------------------------------------------------
+def gptq_unpack(qweight: np.ndarray, K: int, N: int) -> np.ndarray:
+    out = np.empty((K, N), dtype=np.uint8)
+    lib().orc_gptq_unpack(_p(qweight), K, N, _p(out))
+    return out
+
+
+def gptq_unpack_zeros(qzeros: np.ndarray, K: int, N: int, group: int = 128) -> np.ndarray:
+    out = np.empty((K // group, N), dtype=np.uint8)
+    lib().orc_gptq_unpack_zeros(_p(qzeros), K, N, group, _p(out))
+    return out
+
+
+def gptq_dequant(qweight, scales, qzeros, K: int, N: int, group: int = 128) -> np.ndarray:
+    out = np.empty((K, N), dtype=np.float32)
+    lib().orc_gptq_dequant(_p(qweight), _p(scales), _p(qzeros), K, N, group, _p(out))
+    return out
+
+
+def gptq_gemv(qweight, scales, qzeros, x_f16, K: int, N: int, group: int = 128):
+    """returns (y_f32, y_f16)"""
+    y32 = np.empty(N, dtype=np.float32)
+    y16 = np.empty(N, dtype=np.float16)
+    x = np.ascontiguousarray(x_f16, dtype=np.float16)
+    lib().orc_gptq_gemv(_p(qweight), _p(scales), _p(qzeros), _p(x), _p(y32), _p(y16), K, N, group)
+    return y32, y16
+
+
+def gptq_gemv_f32_accum(qweight, scales, x_f32, y_f32, K: int, N: int) -> np.ndarray:
+    y = _f32(y_f32).copy()
+    lib().orc_gptq_gemv_f32_accum(_p(qweight), _p(scales), _p(_f32(x_f32)), _p(y), K, N)
+    return y
+
+
+def dense_bf16_gemv(w_bf16, x_f32, N: int, K: int) -> np.ndarray:
+    y = np.empty(N, dtype=np.float32)
+    lib().orc_dense_bf16_gemv(_p(w_bf16), _p(_f32(x_f32)), _p(y), N, K)
+    return y
+
+
+# ---- norms / elementwise -------------------------------------------------------
+def rmsnorm(x, w, res=None, eps=1e-6, one_plus_w=True):
+    x = _f32(x)
+    y = np.empty_like(x)
+    s = np.empty_like(x)
+    lib().orc_rmsnorm(_p(x), _p(_f32(res)) if res is not None else None, _p(_f32(w)), _p(y), _p(s), x.size,
+                      C.c_float(eps), 1 if one_plus_w else 0)
+    return y, s
+
+
+def l2norm(x):
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().orc_l2norm(_p(x), _p(y), x.size)
+    return y
+
+
+def swiglu(gate, up, swap_operands=False):
+    g, u = _f32(gate), _f32(up)
+    y = np.empty_like(g)
+    lib().orc_swiglu(_p(g), _p(u), _p(y), g.size, 1 if swap_operands else 0)
+    return y
+
+
+def conv1d_step(x, w, hist):
+    """returns (y, new_hist); w [4,C], hist [3,C]"""
+    x, w, h = _f32(x), _f32(w), _f32(hist).copy()
+    y = np.empty_like(x)
+    lib().orc_conv1d_step(_p(x), _p(w), _p(h), _p(y), x.size)
+    return y, h
+
+
+# ---- DeltaNet ------------------------------------------------------------------
+def decay_gate(a, a_log, dt_bias, b):
+    a, a_log, dt_bias, b = _f32(a), _f32(a_log), _f32(dt_bias), _f32(b)
+    g, beta = np.empty_like(a), np.empty_like(a)
+    lib().orc_decay_gate(_p(a), _p(a_log), _p(dt_bias), _p(b), _p(g), _p(beta), a.size)
+    return g, beta
+
+
+def deltanet_step(state, q, k, v, z, g, beta, HV: int, HK: int, d: int = 128):
+    """state is updated IN PLACE (must be a contiguous float32 array); returns out [HV,d]"""
+    assert state.dtype == np.float32 and state.flags["C_CONTIGUOUS"]
+    out = np.empty((HV, d), dtype=np.float32)
+    lib().orc_deltanet_step(_p(state), _p(_f32(q)), _p(_f32(k)), _p(_f32(v)), _p(_f32(z)) if z is not None else None,
+                            _p(_f32(g)), _p(_f32(beta)), _p(out), HV, HK, d)
+    return out
+
+
+# ---- attention ------------------------------------------------------------------
+def rope(x, heads: int, d: int, rot_dims: int, pos: int, theta: float):
+    x = _f32(x).copy()
+    lib().orc_rope(_p(x), heads, d, rot_dims, pos, C.c_double(theta))
+    return x
+
+
+def attention_decode(q, kc, vc, gate, L: int, HQ: int, HKV: int, d: int = 256):
+    out = np.empty((HQ, d), dtype=np.float32)
+    lib().orc_attention_decode(_p(_f32(q)), _p(kc), _p(vc), _p(_f32(gate)) if gate is not None else None, _p(out), L, HQ,
+                               HKV, d)
+    return out
+
+
+def attention_step(q_raw, k_raw, v_new, gate, q_norm_w, k_norm_w, kc, vc, pos: int, HQ: int, HKV: int, d: int = 256,
+                   rot_dims: int = 64, theta: float = 1e7, eps: float = 1e-6):
+    """kc, vc (uint16 bf16 bits, [ctx,HKV,d]) get the new row appended IN PLACE; returns out [HQ,d]"""
+    out = np.empty((HQ, d), dtype=np.float32)
+    lib().orc_attention_step(_p(_f32(q_raw)), _p(_f32(k_raw)), _p(_f32(v_new)),
+                             _p(_f32(gate)) if gate is not None else None, _p(_f32(q_norm_w)), _p(_f32(k_norm_w)),
+                             _p(kc), _p(vc), _p(out), pos, HQ, HKV, d, rot_dims, C.c_double(theta), C.c_float(eps))
+    return out
+
+
+def embed_bf16(table, token: int, D: int):
+    out = np.empty(D, dtype=np.float32)
+    lib().orc_embed_bf16(_p(table), token, D, _p(out))
+    return out
+
+
+def argmax(x) -> int:
+    x = _f32(x)
+    return lib().orc_argmax(_p(x), x.size)
+
+
+# ---- whole model ------------------------------------------------------------------
+class ModelCfg(C.Structure):
+    _fields_ = [(n, C.c_int) for n in (
+        "n_layers", "hidden", "inter", "vocab", "dn_k_heads", "dn_v_heads", "dn_dim", "conv_taps",
+        "fa_q_heads", "fa_kv_heads", "fa_dim", "rot_dims", "group", "fa_period", "max_ctx", "reserved")] + [
+        ("eps", C.c_float), ("rope_theta", C.c_float)]
+
+
+WS_SLOTS, WG_SLOTS = 26, 3
+
+
+class Model:
+    """CPU model over a host weight table: layer_slots[l][slot] and globals[3] are numpy arrays."""
+
+    def __init__(self, cfg: ModelCfg, layer_slots, globals_):
+        self.cfg = cfg
+        self._keep = (layer_slots, globals_)
+        n = cfg.n_layers * WS_SLOTS
+        self._slots = (C.c_void_p * n)()
+        for l in range(cfg.n_layers):
+            for s in range(WS_SLOTS):
+                a = layer_slots[l][s]
+                self._slots[l * WS_SLOTS + s] = a.ctypes.data if a is not None else None
+        self._globals = (C.c_void_p * WG_SLOTS)(*[g.ctypes.data for g in globals_])
+        self.h = C.c_void_p(lib().orc_model_create(C.byref(cfg), self._slots, self._globals))
+
+    def _view(self, fn, layer, shape, dtype):
+        p = getattr(lib(), fn)(self.h, layer)
+        if not p:
+            return None
+        n = int(np.prod(shape))
+        ct = {np.float32: C.c_float, np.uint16: C.c_uint16}[dtype]
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(ct)), shape=(n,)).reshape(shape)
+
+    def dn_state(self, layer):
+        c = self.cfg
+        return self._view("orc_model_dn_state", layer, (c.dn_v_heads, c.dn_dim, c.dn_dim), np.float32)
+
+    def conv_hist(self, layer):
+        c = self.cfg
+        return self._view("orc_model_conv_hist", layer, (3, (2 * c.dn_k_heads + c.dn_v_heads) * c.dn_dim), np.float32)
+
+    def k_cache(self, layer):
+        c = self.cfg
+        return self._view("orc_model_k_cache", layer, (c.max_ctx, c.fa_kv_heads, c.fa_dim), np.uint16)
+
+    def v_cache(self, layer):
+        c = self.cfg
+        return self._view("orc_model_v_cache", layer, (c.max_ctx, c.fa_kv_heads, c.fa_dim), np.uint16)
+
+    def logits(self):
+        p = lib().orc_model_logits(self.h)
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(self.cfg.vocab,))
+
+    def residual(self):
+        p = lib().orc_model_residual(self.h)
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(self.cfg.hidden,))
+
+    def decode(self, token: int, pos: int, n_layers_run: int = 0) -> int:
+        return lib().orc_model_decode(self.h, token, pos, n_layers_run)
+
+    def close(self):
+        if self.h:
+            lib().orc_model_destroy(self.h)
+            self.h = None

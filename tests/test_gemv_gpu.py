@@ -1,0 +1,220 @@
+"""GPU: int4 GEMV, dequant and unpack through the C ABI against the CPU oracle, the
+committed known-answer fixture, and the reference's own PTX kernel (assembled for
+sm_100a) on the same buffers.
+
+Tolerances (written where they are used):
+  * unpack / dequant: bit-exact;
+  * GEMV: max|y - y_ref| / max|y_ref| <= 1e-3 (fp16 products, fp32 accumulation);
+  * compat entry vs the reference PTX with K_SPLITS = 1: bit-exact.
+"""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from helpers import gptq_case, rel_err_max
+
+pytestmark = pytest.mark.gpu
+G = np.load(Path(__file__).parent / "golden" / "kat_small.npz")
+ROOT = Path(__file__).resolve().parent.parent
+TOL = 1e-3
+
+
+def run_gemv(ctx, lb, qw, sc, qz, x, K, N, flags=0, y_init=None):
+    d_qw, d_sc = ctx.to_device(qw), ctx.to_device(sc)
+    d_qz = ctx.to_device(qz) if qz is not None else None
+    d_x = ctx.to_device(x)
+    f32 = bool(flags & (lb.GEMV_Y_F32 | lb.GEMV_Y_ACCUM)) and not (flags & lb.GEMV_Y_SWIGLU)
+    n_out = N // 2 if flags & lb.GEMV_Y_SWIGLU else N
+    d_y = ctx.alloc(n_out * 4)
+    if y_init is not None:
+        d_y.upload(y_init)
+    ctx.gemv_int4(d_qw, d_sc, d_qz, d_x, d_y, K, N, flags)
+    y = d_y.download(np.float32 if f32 else np.float16, n_out)
+    assert ctx.device_status() == 0
+    for b in (d_qw, d_sc, d_qz, d_x, d_y):
+        if b:
+            b.free()
+    return y
+
+
+def test_unpack_and_dequant_bit_exact_fixture(ctx, lb):
+    K, N = G["gptq_q"].shape
+    d_qw, d_sc, d_qz = ctx.to_device(G["gptq_qweight"]), ctx.to_device(G["gptq_scales"]), ctx.to_device(G["gptq_qzeros"])
+    d_q, d_w = ctx.alloc(K * N), ctx.alloc(K * N * 4)
+    ctx.gptq_unpack(d_qw, d_q, K, N)
+    assert np.array_equal(d_q.download(np.uint8, K * N).reshape(K, N), G["gptq_q"])
+    ctx.gptq_dequant(d_qw, d_sc, d_qz, d_w, K, N)
+    assert np.array_equal(d_w.download(np.float32, K * N).reshape(K, N), G["gptq_w"])
+    ctx.gptq_dequant(d_qw, d_sc, None, d_w, K, N)
+    assert np.array_equal(d_w.download(np.float32, K * N).reshape(K, N), G["gptq_w_sym"])
+
+
+def test_gemv_fixture(ctx, lb):
+    K, N = G["gptq_q"].shape
+    y = run_gemv(ctx, lb, G["gptq_qweight"], G["gptq_scales"], G["gptq_qzeros"], G["gptq_x"], K, N, lb.GEMV_Y_F32)
+    assert rel_err_max(y, G["gptq_y"]) <= TOL
+    y = run_gemv(ctx, lb, G["gptq_qweight"], G["gptq_scales"], None, G["gptq_x"], K, N, lb.GEMV_Y_F32)
+    assert rel_err_max(y, G["gptq_y_sym"]) <= TOL
+
+
+@pytest.mark.parametrize("K,N", [(128, 32), (128, 96), (256, 128), (384, 160), (1024, 1024), (5120, 1024), (2048, 4096),
+                                 (17408, 640), (6144, 5120)])
+@pytest.mark.parametrize("zeros", [True, False])
+def test_gemv_vs_oracle_shapes(ctx, lb, oracle, K, N, zeros):
+    """ragged column tiles (N % 128 != 0), single-group K, deep split-K, both zero-point modes"""
+    qw, sc, qz, x = gptq_case(K, N, seed=K * 7 + N, zeros=zeros)
+    y32, y16 = oracle.gptq_gemv(qw, sc, qz, x, K, N)
+    y = run_gemv(ctx, lb, qw, sc, qz, x, K, N, lb.GEMV_Y_F32)
+    assert rel_err_max(y, y32) <= TOL
+    yh = run_gemv(ctx, lb, qw, sc, qz, x, K, N, 0)
+    assert rel_err_max(yh.astype(np.float32), y32) <= TOL + 1e-3  # + fp16 rounding of the output itself
+
+
+def test_gemv_config0_full_shape(ctx, lb, oracle):
+    """BASELINE config 0: 17408 x 5120, group 128, asymmetric, fp16 x, fp32 accumulate, fp16 y"""
+    K, N = 5120, 17408
+    qw, sc, qz, x = gptq_case(K, N, seed=0)
+    y32, y16 = oracle.gptq_gemv(qw, sc, qz, x, K, N)
+    y = run_gemv(ctx, lb, qw, sc, qz, x, K, N, lb.GEMV_Y_F32)
+    assert rel_err_max(y, y32) <= TOL
+    yh = run_gemv(ctx, lb, qw, sc, qz, x, K, N, 0)
+    # fp16 outputs: equal to the oracle's fp16 rounding except where the fp32 values straddle a rounding boundary
+    ulp_diff = np.abs(yh.view(np.int16).astype(np.int32) - y16.view(np.int16).astype(np.int32))
+    assert rel_err_max(yh.astype(np.float32), y32) <= 2e-3
+    assert np.mean(ulp_diff <= 1) > 0.97
+    # dequantised weights, full shape: bit-exact
+    d_qw, d_sc, d_qz = ctx.to_device(qw), ctx.to_device(sc), ctx.to_device(qz)
+    d_w = ctx.alloc(K * N * 4)
+    ctx.gptq_dequant(d_qw, d_sc, d_qz, d_w, K, N)
+    w = d_w.download(np.float32, K * N).reshape(K, N)
+    assert np.array_equal(w, oracle.gptq_dequant(qw, sc, qz, K, N))
+    for b in (d_qw, d_sc, d_qz, d_w):
+        b.free()
+
+
+def test_gemv_properties_full_size(ctx, lb):
+    """size-independent properties on the largest projection shapes: run-to-run identical bits
+    (ordered reductions), exact scaling by a power of two, accumulate mode = overwrite + y0."""
+    for K, N in [(5120, 17408), (17408, 5120), (5120, 22528)]:
+        qw, sc, qz, x = gptq_case(K, N, seed=3)
+        y1 = run_gemv(ctx, lb, qw, sc, qz, x, K, N, lb.GEMV_Y_F32)
+        y2 = run_gemv(ctx, lb, qw, sc, qz, x, K, N, lb.GEMV_Y_F32)
+        assert np.array_equal(y1, y2)
+        y4 = run_gemv(ctx, lb, qw, sc, qz, (x.astype(np.float32) * 4).astype(np.float16), K, N, lb.GEMV_Y_F32)
+        assert np.array_equal(y4, y1 * 4)
+        y0 = np.linspace(-1, 1, N, dtype=np.float32)
+        ya = run_gemv(ctx, lb, qw, sc, qz, x, K, N, lb.GEMV_Y_ACCUM, y_init=y0)
+        assert np.array_equal(ya, y0 + y1)
+
+
+def test_gemv_f32_input_and_swiglu(ctx, lb, oracle):
+    K, N = 1024, 512
+    qw, sc, qz, x = gptq_case(K, N, seed=5)
+    y32, _ = oracle.gptq_gemv(qw, sc, qz, x, K, N)
+    y = run_gemv(ctx, lb, qw, sc, qz, x.astype(np.float32), K, N, lb.GEMV_X_F32 | lb.GEMV_Y_F32)
+    assert rel_err_max(y, y32) <= TOL
+    # interleaved 64-wide (gate, up) column blocks -> silu(gate)*up, fp16
+    blocks = y32.reshape(N // 128, 2, 64)
+    want = oracle.swiglu(blocks[:, 0, :].ravel(), blocks[:, 1, :].ravel())
+    m = run_gemv(ctx, lb, qw, sc, qz, x, K, N, lb.GEMV_Y_SWIGLU)
+    assert m.shape == (N // 2,)
+    assert rel_err_max(m.astype(np.float32), want) <= 2e-3
+
+
+def test_gemv_norm_prologues(ctx, lb, oracle):
+    K, N = 5120, 1024
+    qw, sc, qz, _ = gptq_case(K, N, seed=6)
+    X = lb.fill_normal(K, 6, 30, std=3.0)
+    w = lb.fill_normal(K, 6, 31, std=0.02, dtype="bf16")
+    h, _ = oracle.rmsnorm(X, oracle.bf16_to_f32(w), one_plus_w=True)
+    y32, _ = oracle.gptq_gemv(qw, sc, qz, h.astype(np.float16), K, N)
+    d = [ctx.to_device(a) for a in (qw, sc, qz, X, w)]
+    d_y, d_xo = ctx.alloc(N * 4), ctx.alloc(K * 2)
+    ctx.gemv_int4_fused(d[0], d[1], d[2], d[3], d_y, K, N, lb.X_F32_RMSNORM, lb.Y_F32, aux0=d[4], x_out=d_xo)
+    assert rel_err_max(d_y.download(np.float32, N), y32) <= TOL
+    xo = d_xo.download(np.float16, K).astype(np.float32)
+    assert np.max(np.abs(xo - h.astype(np.float16).astype(np.float32))) <= 2e-3 * np.max(np.abs(h))
+    # per-head RMSNorm (heads of 128) times silu(z): the DeltaNet out-projection prologue
+    K2 = 6144
+    qw, sc, qz, _ = gptq_case(K2, N, seed=7)
+    o = lb.fill_normal(K2, 7, 32, std=2.0)
+    z = lb.fill_normal(K2, 7, 33)
+    hw = lb.fill_normal(128, 7, 34, mean=1.0, std=0.1)
+    hn = np.concatenate([oracle.rmsnorm(o[i:i + 128], hw, one_plus_w=False)[0] for i in range(0, K2, 128)])
+    hn = hn * (z / (1 + np.exp(-z)))
+    y32, _ = oracle.gptq_gemv(qw, sc, qz, hn.astype(np.float16), K2, N)
+    d2 = [ctx.to_device(a) for a in (qw, sc, qz, o, hw, z)]
+    ctx.gemv_int4_fused(d2[0], d2[1], d2[2], d2[3], d_y, K2, N, lb.X_F32_HEADNORM_SILU, lb.Y_F32, aux0=d2[4], aux1=d2[5])
+    assert rel_err_max(d_y.download(np.float32, N), y32) <= TOL
+    assert ctx.device_status() == 0
+    for b in d + d2 + [d_y, d_xo]:
+        b.free()
+
+
+def test_gemv_host_entry(ctx, lb, oracle):
+    K, N = 1024, 2048
+    qw, sc, qz, x = gptq_case(K, N, seed=8)
+    y32, _ = oracle.gptq_gemv(qw, sc, qz, x, K, N)
+    y = np.empty(N, dtype=np.float32)
+    ctx.gemv_int4_host(qw, sc, qz, x, y, K, N, lb.GEMV_Y_F32)
+    assert rel_err_max(y, y32) <= TOL
+    x2 = lb.fill_normal(K, 9, 4, dtype="f16")
+    ctx.gemv_int4_host(qw, sc, qz, x2, y, K, N, lb.GEMV_Y_F32, weights_resident=True)
+    assert rel_err_max(y, oracle.gptq_gemv(qw, sc, qz, x2, K, N)[0]) <= TOL
+
+
+def test_invalid_arguments_are_rejected(ctx, lb):
+    d = ctx.alloc(1 << 16)
+    with pytest.raises(lb.LithosError) as e:
+        ctx.gemv_int4(d, d, None, d, d, 100, 128)       # K not a multiple of the group size
+    assert e.value.status == lb.LB_ERR_INVALID
+    with pytest.raises(lb.LithosError):
+        ctx.gemv_int4(d, d, None, d, d, 128, 100)       # N not a multiple of 32
+    d.free()
+
+
+def _launch_ref_abi(ctx, lb, cubin, entry, qw, sc, x32, K, N, k_splits=1):
+    """drive a gptq_gemv_safe-ABI cubin exactly as the reference launcher does
+    (grid (ceil(N/256), K_SPLITS), block 64, dynamic smem 4*K, y zeroed by the caller)"""
+    L = lb.lib()
+    L.lb_module_load.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int)]
+    L.lb_module_get_kernel.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.POINTER(C.c_uint64)]
+    L.lb_launch_kernel.argtypes = [C.c_void_p, C.c_uint64] + [C.c_uint] * 7 + [C.POINTER(C.c_void_p)]
+    mod, fn = C.c_int(), C.c_uint64()
+    ctx._check(L.lb_module_load(ctx.h, str(cubin).encode(), C.byref(mod)))
+    ctx._check(L.lb_module_get_kernel(ctx.h, mod, entry.encode(), C.byref(fn)))
+    d_qw, d_sc, d_x = ctx.to_device(qw), ctx.to_device(sc), ctx.to_device(x32)
+    d_y = ctx.alloc(N * 4).zero()
+    kpps = (K // 8 + k_splits - 1) // k_splits
+    vals = [C.c_uint64(d_qw.ptr), C.c_uint64(d_sc.ptr), C.c_uint64(d_x.ptr), C.c_uint64(d_y.ptr), C.c_uint32(N),
+            C.c_uint32(K), C.c_uint32(k_splits), C.c_uint32(kpps)]
+    params = (C.c_void_p * len(vals))(*[C.cast(C.pointer(v), C.c_void_p) for v in vals])
+    ctx._check(L.lb_launch_kernel(ctx.h, fn, (N + 255) // 256, k_splits, 1, 64, 1, 1, 4 * K, params))
+    y = d_y.download(np.float32, N)
+    for b in (d_qw, d_sc, d_x, d_y):
+        b.free()
+    return y
+
+
+def test_compat_entry_vs_reference_ptx(ctx, lb, oracle):
+    """The reference's own kernel (minds/gptq_gemv_safe.ptx assembled unmodified for sm_100a) and
+    the drop-in with the same entry name / parameter block, on the same buffers: bit-exact with
+    K_SPLITS = 1; both within 1e-3 of the oracle, which this pins."""
+    ref_cubin = ROOT / "oracle" / "_ref" / "gptq_gemv_safe.cubin"
+    if not ref_cubin.exists():
+        pytest.skip("oracle/_ref not built (reference tree absent at build time)")
+    ours = ROOT / "lithos_b200" / "kernels" / "compat" / "gptq_gemv_safe.cubin"
+    for K, N in [(1024, 512), (5120, 17408)]:
+        qw, sc, _, x = gptq_case(K, N, seed=11, zeros=False)
+        x32 = x.astype(np.float32)
+        y_ref = _launch_ref_abi(ctx, lb, ref_cubin, "gptq_gemv_safe", qw, sc, x32, K, N)
+        y_our = _launch_ref_abi(ctx, lb, ours, "gptq_gemv_safe", qw, sc, x32, K, N)
+        y_orc = oracle.gptq_gemv_f32_accum(qw, sc, x32, np.zeros(N, np.float32), K, N)
+        assert np.array_equal(y_our, y_ref)
+        assert np.array_equal(y_ref, y_orc)  # same fma order as the oracle: the oracle is pinned by the reference here
+        y_prim = run_gemv(ctx, lb, qw, sc, None, x, K, N, lb.GEMV_Y_F32)
+        assert rel_err_max(y_prim, y_ref) <= TOL
+        y_split = _launch_ref_abi(ctx, lb, ours, "gptq_gemv_safe", qw, sc, x32, K, N, k_splits=4)
+        assert rel_err_max(y_split, y_ref) <= 1e-5
