@@ -143,12 +143,19 @@ def bench_gemv(args, rank, local, world, dist):
             w = dev[(i * per_step + j) % SETS]
             ctx.gemv_int4(w[0], w[1], w[2], d_x, d_y, K, N, 0)
 
-    for i in range(args.warmup):
-        step(i)
-    ctx.sync()
+    # bring the SM clocks up from idle before anything is timed (not one of the W warm-up steps)
+    t_ramp = time.perf_counter()
+    while time.perf_counter() - t_ramp < args.ramp_s:
+        for i in range(8):
+            step(i)
+        ctx.sync()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+        time.sleep(0.3)
+    for i in range(args.warmup):
+        step(i)
+    ctx.sync()
     barrier(dist)
     ctx.reset_launches()
     ctx.timer_start()
@@ -231,10 +238,11 @@ def reference_gemv(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="gemv", choices=["gemv"])
+    ap.add_argument("--ramp-s", type=float, default=1.5, help="seconds of untimed work before warm-up (clock ramp)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, local, world = dist_env()

@@ -61,6 +61,9 @@
     X(IpcGetMemHandle, cuIpcGetMemHandle, (CUipcMemHandle*, CUdeviceptr))                                       \
     X(IpcOpenMemHandle, cuIpcOpenMemHandle, (CUdeviceptr*, CUipcMemHandle, unsigned int))                       \
     X(IpcCloseMemHandle, cuIpcCloseMemHandle, (CUdeviceptr))                                                    \
+    X(TensorMapEncodeTiled, cuTensorMapEncodeTiled,                                                             \
+      (CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, \
+       const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill)) \
     X(GetErrorString, cuGetErrorString, (CUresult, const char**))                                               \
     X(GetErrorName, cuGetErrorName, (CUresult, const char**))
 

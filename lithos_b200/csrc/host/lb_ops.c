@@ -26,19 +26,20 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
     if (ks > groups) ks = groups;
     g->gps = (groups + ks - 1) / ks;
     g->ksplit = (groups + g->gps - 1) / g->gps;
-    /* ring depth: as deep as fits when two CTAs share an SM, at most 12 */
-    size_t fixed = (size_t)g->gps * LB_GEMV_ROWS * 16 + (size_t)((g->gps + 3) & ~3) * 4 +
+    /* ring depth: as deep as fits when two CTAs share an SM, at most 24 boxes of 4 KB */
+    int units = g->gps * (LB_GEMV_ROWS / LB_GEMV_UNIT_ROWS);
+    size_t fixed = (size_t)g->gps * LB_GEMV_ROWS * 16 + (size_t)((units + 3) & ~3) * 4 +
                    (LB_GEMV_WARPS * LB_GEMV_TILE_N + 40) * 4;
     size_t per_stage = LB_GEMV_STAGE_BYTES + 16; /* stage + its two mbarriers */
     size_t budget = (size_t)(c->max_smem_optin - 2048) / 2;
     int st = budget > fixed ? (int)((budget - fixed) / per_stage) : 0;
-    if (st < 2) { /* very long K slice: give the CTA the SM to itself */
+    if (st < 4) { /* very long K slice: give the CTA the SM to itself */
         budget = (size_t)(c->max_smem_optin - 2048);
         st = budget > fixed ? (int)((budget - fixed) / per_stage) : 0;
         if (st < 1) return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: K slice of %d groups does not fit shared memory", g->gps);
     }
-    if (st > 12) st = 12;
-    if (st > g->gps) st = g->gps;
+    if (st > 24) st = 24;
+    if (st > units) st = units;
     g->stages = st;
     g->smem = (unsigned)((fixed + (size_t)st * per_stage + 127) & ~(size_t)127);
     return LB_OK;
@@ -78,6 +79,19 @@ LB_API int lb_gemv_int4_fused(lb_ctx* c, uint64_t qweight, uint64_t scales, uint
     p.stages = g.stages;
     p.x_mode = x_mode; p.y_mode = y_mode;
     p.eps = eps;
+    /* qweight as a [K/8, N] uint32 matrix; one TMA box = 8 packed rows x 128 columns.
+     * Columns past N (ragged last tile) are zero-filled and never stored. */
+    {
+        CUtensorMap tm;
+        cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 8)};
+        cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+        cuuint32_t box[2] = {LB_GEMV_TILE_N, LB_GEMV_UNIT_ROWS};
+        cuuint32_t estr[2] = {1, 1};
+        LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)qweight, dims, strides, box,
+                                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+        memcpy(p.tmap, &tm, sizeof tm);
+    }
     void* params[] = {&p};
     return lb_launch(c, LBK_gemv_int4_w128, (unsigned)g.tiles, (unsigned)g.ksplit, 1, GEMV_THREADS, g.smem, params, 1);
 }
@@ -234,7 +248,7 @@ LB_API int lb_attention_decode(lb_ctx* c, uint64_t q, uint64_t k_new, uint64_t v
     p.splits = lb_attn_splits(c, pos, HKV);
     p.in_dtype = in_is_f32 ? 1 : 0;
     p.gate_stride = 256; p.q_stride = 256;
-    p.rot_dims = rot_dims; p.log2_theta = log2f(rope_theta); p.eps = eps;
+    p.rot_dims = rot_dims; p.rope_theta = rope_theta; p.eps = eps;
     void* params[] = {&p};
     return lb_launch(c, LBK_attn_decode_split, (unsigned)HKV, (unsigned)p.splits, 1, 256, lb_attn_smem(G), params, 1);
 }

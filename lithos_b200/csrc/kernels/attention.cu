@@ -32,7 +32,7 @@ __device__ __forceinline__ float ld_in(const void* p, size_t i, int is_f32) {
 // RMS-normalise (plain weight) then rotate the first rot_dims dims in
 // interleaved pairs at position pos; one value per thread, dst in shared.
 __device__ __forceinline__ void norm_rope_256(float v, const uint16_t* w, float* dst, float* red, int pos, int rot_dims,
-                                              float log2_theta, float eps, float post_scale) {
+                                              float theta, float eps, float post_scale) {
     const int t = threadIdx.x;
     if (w) {
         float ss = block_sum(v * v, red);
@@ -42,7 +42,7 @@ __device__ __forceinline__ void norm_rope_256(float v, const uint16_t* w, float*
     __syncthreads();
     if (t < rot_dims / 2) {
         // angle in double: pos * freq reaches 1e5 rad, far beyond fp32 resolution
-        double freq = exp2(-(double)log2_theta * (double)t / (double)(rot_dims / 2));
+        double freq = exp2(-log2((double)theta) * (double)t / (double)(rot_dims / 2));
         double sn, cs;
         sincos((double)pos * freq, &sn, &cs);
         float a = dst[2 * t], b = dst[2 * t + 1];
@@ -74,11 +74,11 @@ __device__ __forceinline__ void attn_body(const lb_attn_params& p, float* sm) {
     for (int g = 0; g < G; ++g) {
         const int hq = kv * G + g;
         float v = ld_in(p.q, (size_t)hq * p.q_stride + t, p.in_dtype);
-        norm_rope_256(v, p.q_norm_w, q_s + g * AT_D, red, p.pos, p.rot_dims, p.log2_theta, p.eps, qscale);
+        norm_rope_256(v, p.q_norm_w, q_s + g * AT_D, red, p.pos, p.rot_dims, p.rope_theta, p.eps, qscale);
     }
     if (last) {
         float kr = ld_in(p.k_new, (size_t)kv * AT_D + t, p.in_dtype);
-        norm_rope_256(kr, p.k_norm_w, kn_s, red, p.pos, p.rot_dims, p.log2_theta, p.eps, 1.0f);
+        norm_rope_256(kr, p.k_norm_w, kn_s, red, p.pos, p.rot_dims, p.rope_theta, p.eps, 1.0f);
         __nv_bfloat16 kb = __float2bfloat16_rn(kn_s[t]);
         __nv_bfloat16 vb = __float2bfloat16_rn(ld_in(p.v_new, (size_t)kv * AT_D + t, p.in_dtype));
         const size_t row = ((size_t)p.pos * p.HKV + kv) * AT_D + t;

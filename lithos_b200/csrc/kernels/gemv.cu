@@ -8,12 +8,13 @@
 //
 // Shape of the kernel (HBM-bound, ~0.5 B/weight):
 //   * CTA (tile, split) owns 128 output columns and a contiguous range of
-//     K-groups.  One producer warp streams "units" (one group = 16 packed rows
-//     x 512 B, plus that group's 128 scales and 16 zero words) into a ring of
-//     shared-memory stages with 1-D bulk copies (TMA engine) that complete on
-//     mbarriers; weights carry an L2 evict-first hint since they are read once.
+//     K-groups.  One elected producer lane streams "units" (half a group: a box
+//     of 8 packed rows x 512 B) into a ring of shared-memory stages with one
+//     tiled TMA load each (cp.async.bulk.tensor.2d, completion on an mbarrier,
+//     L2 evict-first hint since weights are read once).
 //   * 8 consumer warps each take whole units round-robin; a lane owns 4
-//     adjacent columns (one 128-bit shared load per packed row).
+//     adjacent columns (one 128-bit shared load per packed row) and fetches its
+//     4 scales / zero-points of the unit's group straight from global memory.
 //   * Dequant in registers: (word & 0x000f000f) | 0x6400 6400 is the fp16x2
 //     pair (1024+q_j, 1024+q_{j+4}); one HSUB2/HFMA2 turns it into exact
 //     integers (q-8); four HFMA2 against the matching x pairs give the
@@ -31,9 +32,7 @@
 #include "params.h"
 
 #define CONSUMERS (LB_GEMV_WARPS * 32)
-#define QW_BYTES (LB_GEMV_ROWS * LB_GEMV_TILE_N * 4)
-#define SC_OFF QW_BYTES
-#define ZR_OFF (QW_BYTES + LB_GEMV_TILE_N * 2)
+#define UROWS LB_GEMV_UNIT_ROWS
 
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
 
@@ -41,6 +40,16 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint3
     uint32_t r;
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(magic)); // (a & mask) | magic
     return r;
+}
+
+// One tiled TMA load: box (UROWS rows x 128 columns of packed words) at
+// (column x, packed row y) of the qweight matrix into one shared-memory stage.
+__device__ __forceinline__ void tma_load_box(void* dst_smem, const void* tmap, int x, int y, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(dst_smem)),
+        "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
 }
 
 // partial dot product of one packed word (8 weights of one column, zero-point
@@ -67,7 +76,7 @@ __device__ __forceinline__ float dot8(uint32_t w, const __half2 (&xp)[4]) {
     return f.x + f.y;
 }
 
-extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 1) gemv_int4_w128(const __grid_constant__ lb_gemv_params p) {
+extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 2) gemv_int4_w128(const __grid_constant__ lb_gemv_params p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x, split = blockIdx.y;
@@ -76,14 +85,14 @@ extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 1) gemv_int4_w128(c
     const int groups = p.K / LB_GEMV_GROUP;
     const int g0 = split * p.groups_per_split;
     const int g1 = min(groups, g0 + p.groups_per_split);
-    const int n_units = max(0, g1 - g0);
+    const int n_units = max(0, g1 - g0) * (LB_GEMV_ROWS / UROWS); // half-group units
     const int S = p.stages;
 
     // shared-memory carve-up
     unsigned char* stage_base = smem;
     uint4* xs = reinterpret_cast<uint4*>(smem + (size_t)S * LB_GEMV_STAGE_BYTES);           // [rows] permuted fp16 x
     float* xsum = reinterpret_cast<float*>(xs + (size_t)p.groups_per_split * LB_GEMV_ROWS); // [units]
-    float* red = xsum + ((p.groups_per_split + 3) & ~3);                                    // [8][128] + 40
+    float* red = xsum + ((2 * p.groups_per_split + 3) & ~3);                                // [8][128] + 40
     uint64_t* full = reinterpret_cast<uint64_t*>(red + LB_GEMV_WARPS * LB_GEMV_TILE_N + 40);
     uint64_t* empty = full + S;
     __shared__ uint32_t s_ticket;
@@ -100,44 +109,30 @@ extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 1) gemv_int4_w128(c
     __syncthreads();
 
     if (warp == LB_GEMV_WARPS) {
-        // ---------------- producer warp: stream units into the ring ----------------
-        const uint64_t pol = l2_policy_evict_first();
-        const unsigned char* qw = reinterpret_cast<const unsigned char*>(p.qweight) + (size_t)n0 * 4;
-        const unsigned char* sc = reinterpret_cast<const unsigned char*>(p.scales) + (size_t)n0 * 2;
-        const unsigned char* qz = p.qzeros ? reinterpret_cast<const unsigned char*>(p.qzeros) + (size_t)n0 / 2 : nullptr;
-        const uint32_t row_bytes = ncols * 4, sc_bytes = ncols * 2, z_bytes = ncols / 2;
-        const uint32_t tx = LB_GEMV_ROWS * row_bytes + sc_bytes + (qz ? z_bytes : 0);
-        for (int u = 0; u < n_units; ++u) {
-            const int s = u % S;
-            if (u >= S) {
-                if (!mbar_wait(&empty[s], ((u / S) - 1) & 1)) {
-                    if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_EMPTY); s_bad = 1; }
+        // ---------------- producer: one elected lane streams boxes into the ring ----------------
+        // Weights never change, so this starts before griddepcontrol.wait: under programmatic
+        // dependent launch the ring is already full when the activations become visible.
+        if (lane == 0) {
+            const uint64_t pol = l2_policy_evict_first();
+            const int row0 = g0 * LB_GEMV_ROWS;
+            for (int u = 0; u < n_units; ++u) {
+                const int s = u % S;
+                if (u >= S && !mbar_wait(&empty[s], ((u / S) - 1) & 1)) {
+                    atomicExch(p.status, LB_DEV_TIMEOUT_EMPTY);
+                    s_bad = 1;
                     break;
                 }
-            }
-            unsigned char* st = stage_base + (size_t)s * LB_GEMV_STAGE_BYTES;
-            const int g = g0 + u;
-            if (lane == 0) mbar_arrive_expect_tx(&full[s], tx);
-            __syncwarp();
-            if (lane < LB_GEMV_ROWS) {
-                bulk_g2s(st + lane * (LB_GEMV_TILE_N * 4), qw + ((size_t)g * LB_GEMV_ROWS + lane) * p.N * 4, row_bytes,
-                         &full[s], pol);
-            } else if (lane == LB_GEMV_ROWS) {
-                bulk_g2s(st + SC_OFF, sc + (size_t)g * p.N * 2, sc_bytes, &full[s], pol);
-            } else if (lane == LB_GEMV_ROWS + 1 && qz) {
-                bulk_g2s(st + ZR_OFF, qz + (size_t)g * (p.N / 2), z_bytes, &full[s], pol);
+                mbar_arrive_expect_tx(&full[s], LB_GEMV_STAGE_BYTES);
+                tma_load_box(stage_base + (size_t)s * LB_GEMV_STAGE_BYTES, p.tmap, n0, row0 + u * UROWS, &full[s], pol);
             }
         }
-        // Never leave with copies in flight: wait (bounded) for every stage this
-        // warp filled and that no consumer will wait for if an error was raised.
-        // In the normal path consumers have already observed every full phase.
-        return;
+        return; // consumers wait for every box, so no copy is in flight when the CTA ends
     }
 
     // ---------------- consumer warps ----------------
     pdl_wait(); // x (and y for accumulate mode) come from the previous kernel
 
-    const int rows = n_units * LB_GEMV_ROWS;
+    const int rows = n_units * UROWS;
     const int row0 = g0 * LB_GEMV_ROWS; // first packed row of this split
 
     // --- prologue: build the fp16 activation slice in shared memory ---
@@ -159,7 +154,7 @@ extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 1) gemv_int4_w128(c
         consumer_bar();
     }
     for (int rb = 0; rb < rows; rb += CONSUMERS) {
-        const int r = rb + tid;         // row within the split (always a full 16-row unit per 16 lanes)
+        const int r = rb + tid;         // row within the split (16-lane segments never straddle a group)
         const bool live = r < rows;
         const int k = (row0 + r) * 8;   // first k of this packed row
         float v[8];
@@ -214,14 +209,14 @@ extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 1) gemv_int4_w128(c
             h[j] = __float2half_rn(v[j]);
             rs += __half2float(h[j]);
         }
-        // sum over the 16 rows of the unit (16-lane segment)
+        // sum over the 8 rows of the unit (8-lane segment)
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
+        for (int o = 4; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
         if (live) {
             __half2 pr[4] = {__halves2half2(h[0], h[4]), __halves2half2(h[1], h[5]), __halves2half2(h[2], h[6]),
                              __halves2half2(h[3], h[7])};
             xs[r] = *reinterpret_cast<uint4*>(pr);
-            if ((lane & 15) == 0) xsum[r >> 4] = rs;
+            if ((lane & 7) == 0) xsum[r >> 3] = rs;
             if (p.x_out && tile == 0) {
                 __half2 pl[4] = {__halves2half2(h[0], h[1]), __halves2half2(h[2], h[3]), __halves2half2(h[4], h[5]),
                                  __halves2half2(h[6], h[7])};
@@ -232,21 +227,28 @@ extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 1) gemv_int4_w128(c
     consumer_bar();
     pdl_launch_dependents();
 
-    // --- main loop: each warp consumes whole units ---
+    // --- main loop: each warp consumes whole units; a lane owns 4 adjacent columns ---
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    bool ok = true;
+    const bool col_ok = lane * 4 < ncols;
     for (int u = warp; u < n_units; u += LB_GEMV_WARPS) {
         const int s = u % S;
+        const int g = g0 + (u >> 1);
+        // this unit's scales / zero-points for the lane's columns: issued first, used last
+        uint2 sraw = make_uint2(0u, 0u);
+        uint32_t zw = 0x88888888u;
+        if (col_ok) {
+            sraw = __ldg(reinterpret_cast<const uint2*>(p.scales + (size_t)g * p.N + n0 + lane * 4));
+            if (p.qzeros) zw = __ldg(p.qzeros + (size_t)g * (p.N >> 3) + (n0 >> 3) + (lane >> 1));
+        }
         if (!mbar_wait(&full[s], (u / S) & 1)) {
             if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); s_bad = 1; }
-            ok = false;
             break;
         }
         const unsigned char* st = stage_base + (size_t)s * LB_GEMV_STAGE_BYTES;
         float ga[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint4* xrow = xs + u * LB_GEMV_ROWS;
-#pragma unroll 4
-        for (int r = 0; r < LB_GEMV_ROWS; ++r) {
+        const uint4* xrow = xs + u * UROWS;
+#pragma unroll
+        for (int r = 0; r < UROWS; ++r) {
             uint4 w = *reinterpret_cast<const uint4*>(st + r * (LB_GEMV_TILE_N * 4) + lane * 16);
             uint4 xr = xrow[r];
             const __half2(&xp)[4] = *reinterpret_cast<const __half2(*)[4]>(&xr);
@@ -255,25 +257,17 @@ extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 1) gemv_int4_w128(c
             ga[2] += dot8(w.z, xp);
             ga[3] += dot8(w.w, xp);
         }
-        // scales and zero-points of this group for the lane's 4 columns
-        uint2 sraw = *reinterpret_cast<const uint2*>(st + SC_OFF + lane * 8);
-        float2 s01 = __half22float2(*reinterpret_cast<__half2*>(&sraw.x));
-        float2 s23 = __half22float2(*reinterpret_cast<__half2*>(&sraw.y));
-        float zc[4] = {0.f, 0.f, 0.f, 0.f};
-        if (p.qzeros) {
-            uint32_t zw = *reinterpret_cast<const uint32_t*>(st + ZR_OFF + (lane >> 1) * 4) >> ((lane & 1) * 16);
-            float xsu = xsum[u];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) zc[c] = (8.0f - (float)((zw >> (4 * c)) & 0xFu)) * xsu;
-        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]); // stage may be refilled
-        acc[0] = fmaf(s01.x, ga[0] + zc[0], acc[0]);
-        acc[1] = fmaf(s01.y, ga[1] + zc[1], acc[1]);
-        acc[2] = fmaf(s23.x, ga[2] + zc[2], acc[2]);
-        acc[3] = fmaf(s23.y, ga[3] + zc[3], acc[3]);
+        float2 s01 = __half22float2(*reinterpret_cast<__half2*>(&sraw.x));
+        float2 s23 = __half22float2(*reinterpret_cast<__half2*>(&sraw.y));
+        zw >>= (lane & 1) * 16;
+        const float xsu = xsum[u];
+        acc[0] = fmaf(s01.x, fmaf(8.0f - (float)(zw & 0xFu), xsu, ga[0]), acc[0]);
+        acc[1] = fmaf(s01.y, fmaf(8.0f - (float)((zw >> 4) & 0xFu), xsu, ga[1]), acc[1]);
+        acc[2] = fmaf(s23.x, fmaf(8.0f - (float)((zw >> 8) & 0xFu), xsu, ga[2]), acc[2]);
+        acc[3] = fmaf(s23.y, fmaf(8.0f - (float)((zw >> 12) & 0xFu), xsu, ga[3]), acc[3]);
     }
-    (void)ok;
 
     // --- ordered reduction across the 8 warps ---
     *reinterpret_cast<float4*>(red + warp * LB_GEMV_TILE_N + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);

@@ -11,8 +11,9 @@
 #define LB_GEMV_TILE_N 128   /* columns per CTA tile (512 B of packed words per row) */
 #define LB_GEMV_GROUP 128    /* GPTQ group size along K */
 #define LB_GEMV_ROWS 16      /* packed rows per group */
+#define LB_GEMV_UNIT_ROWS 8  /* packed rows per pipeline unit (half a group): one TMA box */
 #define LB_GEMV_WARPS 8      /* consumer warps per CTA (one more warp issues copies) */
-#define LB_GEMV_STAGE_BYTES (LB_GEMV_ROWS * LB_GEMV_TILE_N * 4 + LB_GEMV_TILE_N * 2 + LB_GEMV_TILE_N / 2 + 64)
+#define LB_GEMV_STAGE_BYTES (LB_GEMV_UNIT_ROWS * LB_GEMV_TILE_N * 4)
 
 /* how the activation vector is produced from p.x */
 enum {
@@ -32,6 +33,8 @@ enum {
 };
 
 typedef struct {
+    /* CUtensorMap over qweight as a [K/8, N] uint32 matrix, box = 8 rows x 128 columns */
+    unsigned char tmap[128] __attribute__((aligned(64)));
     const uint32_t* qweight; /* [K/8, N] */
     const uint16_t* scales;  /* fp16 [K/128, N] */
     const uint32_t* qzeros;  /* [K/128, N/8] or NULL: zero-point 8 */
@@ -105,7 +108,7 @@ typedef struct {
     int32_t gate_stride;  /* elements between consecutive heads of gate (256, or 512 when interleaved with q) */
     int32_t q_stride;     /* elements between consecutive heads of q */
     int32_t rot_dims;
-    float log2_theta;
+    float rope_theta;
     float eps;
 } lb_attn_params;
 
