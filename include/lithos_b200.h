@@ -69,6 +69,17 @@ int lb_module_get_kernel(lb_ctx* ctx, int module, const char* entry, uint64_t* k
 int lb_launch_kernel(lb_ctx* ctx, uint64_t kernel, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by,
                      unsigned bz, unsigned smem_bytes, void** params);
 
+/* ---- CUDA graphs: whole sequences of launches as one submission ------------------
+ * The reference issues ~1000 cuLaunchKernel calls per token (src/launcher.s:776-920) and
+ * plans one submission per token (src/launcher.ls:16-106).  Everything launched through
+ * this library between begin and end is captured (not run) and can then be replayed. */
+typedef struct lb_graph lb_graph;
+int lb_graph_begin_capture(lb_ctx* ctx);
+int lb_graph_end_capture(lb_ctx* ctx, lb_graph** out);
+int lb_graph_launch(lb_ctx* ctx, lb_graph* graph);
+int lb_graph_kernel_count(const lb_graph* graph);
+void lb_graph_destroy(lb_ctx* ctx, lb_graph* graph);
+
 /* ---- device memory: replaces alloc_buffers (src/launcher.s:2981-3136) ------ */
 int lb_malloc(lb_ctx* ctx, size_t bytes, uint64_t* dptr_out);
 int lb_free(lb_ctx* ctx, uint64_t dptr);

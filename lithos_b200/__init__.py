@@ -73,6 +73,11 @@ def lib() -> C.CDLL:
     sig("lb_launch_count", u64, vp)
     sig("lb_launch_count_reset", None, vp)
     sig("lb_set_pdl", None, vp, i32)
+    sig("lb_graph_begin_capture", i32, vp)
+    sig("lb_graph_end_capture", i32, vp, P(vp))
+    sig("lb_graph_launch", i32, vp, vp)
+    sig("lb_graph_kernel_count", i32, vp)
+    sig("lb_graph_destroy", None, vp, vp)
     sig("lb_malloc", i32, vp, sz, P(u64))
     sig("lb_free", i32, vp, u64)
     sig("lb_malloc_host", i32, vp, sz, P(vp))
@@ -193,6 +198,25 @@ class DeviceBuffer:
             self.ptr = 0
 
 
+class Graph:
+    """A captured sequence of launches, replayed with one submission."""
+
+    def __init__(self, ctx: "Context", h):
+        self.ctx, self.h = ctx, h
+
+    @property
+    def kernels(self) -> int:
+        return lib().lb_graph_kernel_count(self.h)
+
+    def launch(self):
+        self.ctx._check(lib().lb_graph_launch(self.ctx.h, self.h))
+
+    def destroy(self):
+        if self.h:
+            lib().lb_graph_destroy(self.ctx.h, self.h)
+            self.h = None
+
+
 class Context:
     """One GPU, one stream: the host-side owner of every buffer and launch."""
 
@@ -251,6 +275,15 @@ class Context:
 
     def set_pdl(self, on: bool):
         lib().lb_set_pdl(self.h, 1 if on else 0)
+
+    # -- graphs --
+    def begin_capture(self):
+        self._check(lib().lb_graph_begin_capture(self.h))
+
+    def end_capture(self) -> "Graph":
+        g = C.c_void_p(None)
+        self._check(lib().lb_graph_end_capture(self.h, C.byref(g)))
+        return Graph(self, g)
 
     # -- timing --
     def timer_start(self):

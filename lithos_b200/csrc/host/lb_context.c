@@ -309,6 +309,12 @@ LB_API int lb_flush_l2(lb_ctx* c) {
 /* ---- launch: replaces the cuLaunchKernel call sites (src/launcher.s:744-762) ---- */
 int lb_launch(lb_ctx* c, int kernel, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned smem, void** params,
               int pdl) {
+    return lb_launch_cluster(c, kernel, gx, gy, gz, bx, smem, params, pdl, 1);
+}
+
+/* cluster_y > 1: the gy CTAs of a column are launched as one thread-block cluster (gy % cluster_y == 0) */
+int lb_launch_cluster(lb_ctx* c, int kernel, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned smem,
+                      void** params, int pdl, unsigned cluster_y) {
     if (!c->fn[kernel]) return lb_fail(c, LB_ERR_NO_KERNEL, "kernel %s not loaded", k_kernel_names[kernel]);
     if (gx == 0 || gy == 0 || gz == 0) return lb_fail(c, LB_ERR_INVALID, "empty grid for %s", k_kernel_names[kernel]);
     if ((int)smem > c->max_smem_optin - 1024)
@@ -320,13 +326,25 @@ int lb_launch(lb_ctx* c, int kernel, unsigned gx, unsigned gy, unsigned gz, unsi
     cfg.blockDimX = bx; cfg.blockDimY = 1; cfg.blockDimZ = 1;
     cfg.sharedMemBytes = smem;
     cfg.hStream = c->stream;
-    CUlaunchAttribute attr[1];
+    CUlaunchAttribute attr[2];
     memset(attr, 0, sizeof attr);
+    unsigned na = 0;
     if (pdl && c->pdl) {
-        attr[0].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
-        attr[0].value.programmaticStreamSerializationAllowed = 1;
+        attr[na].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attr[na].value.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    if (cluster_y > 1) {
+        if (gy % cluster_y) return lb_fail(c, LB_ERR_INVALID, "grid.y %u not a multiple of the cluster size %u", gy, cluster_y);
+        attr[na].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+        attr[na].value.clusterDim.x = 1;
+        attr[na].value.clusterDim.y = cluster_y;
+        attr[na].value.clusterDim.z = 1;
+        na++;
+    }
+    if (na) {
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = na;
     }
     CUresult r = lb_drv.LaunchKernelEx(&cfg, c->fn[kernel], params, NULL);
     if (r != CUDA_SUCCESS) return lb_cu(c, r, k_kernel_names[kernel]);
@@ -374,4 +392,61 @@ LB_API int lb_launch_kernel(lb_ctx* c, uint64_t kernel, unsigned gx, unsigned gy
     LB_CU(c, lb_drv.LaunchKernel((CUfunction)(uintptr_t)kernel, gx, gy, gz, bx, by, bz, smem_bytes, c->stream, params, NULL));
     c->launches++;
     return LB_OK;
+}
+
+/* ---- CUDA graphs -----------------------------------------------------------------
+ * The reference submits ~1000 launches per token one by one and synchronises after each
+ * (debug_sync_tag, src/launcher.s:4044-4096); its design notes aim at one submission per
+ * token (src/launcher.ls:16-106).  Here any sequence of this library's launches on the
+ * context stream can be captured once and replayed as a single graph launch;
+ * programmatic-dependent-launch edges between consecutive kernels are kept. */
+struct lb_graph {
+    CUgraph graph;
+    CUgraphExec exec;
+    size_t kernel_nodes;
+};
+
+LB_API int lb_graph_begin_capture(lb_ctx* c) {
+    if (!c) return LB_ERR_INVALID;
+    if (c->capturing) return lb_fail(c, LB_ERR_STATE, "capture already in progress");
+    LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
+    LB_CU(c, lb_drv.StreamBeginCapture(c->stream, CU_STREAM_CAPTURE_MODE_THREAD_LOCAL));
+    c->capturing = 1;
+    c->capture_launches0 = c->launches;
+    return LB_OK;
+}
+
+LB_API int lb_graph_end_capture(lb_ctx* c, lb_graph** out) {
+    if (!c || !out) return LB_ERR_INVALID;
+    if (!c->capturing) return lb_fail(c, LB_ERR_STATE, "no capture in progress");
+    c->capturing = 0;
+    lb_graph* g = (lb_graph*)calloc(1, sizeof *g);
+    if (!g) return LB_ERR_NOMEM;
+    CUresult r = lb_drv.StreamEndCapture(c->stream, &g->graph);
+    if (r != CUDA_SUCCESS) { free(g); return lb_cu(c, r, "cuStreamEndCapture"); }
+    g->kernel_nodes = (size_t)(c->launches - c->capture_launches0);
+    c->launches = c->capture_launches0; /* captured launches have not run */
+    r = lb_drv.GraphInstantiate(&g->exec, g->graph, 0);
+    if (r != CUDA_SUCCESS) { lb_drv.GraphDestroy(g->graph); free(g); return lb_cu(c, r, "cuGraphInstantiate"); }
+    *out = g;
+    return LB_OK;
+}
+
+LB_API int lb_graph_launch(lb_ctx* c, lb_graph* g) {
+    if (!c || !g) return LB_ERR_INVALID;
+    if (c->capturing) return lb_fail(c, LB_ERR_STATE, "graph launch during capture");
+    LB_CU(c, lb_drv.GraphLaunch(g->exec, c->stream));
+    c->launches += g->kernel_nodes;
+    return LB_OK;
+}
+
+LB_API int lb_graph_kernel_count(const lb_graph* g) { return g ? (int)g->kernel_nodes : 0; }
+
+LB_API void lb_graph_destroy(lb_ctx* c, lb_graph* g) {
+    if (!g) return;
+    if (lb_drv.loaded) {
+        if (g->exec) lb_drv.GraphExecDestroy(g->exec);
+        if (g->graph) lb_drv.GraphDestroy(g->graph);
+    }
+    free(g);
 }

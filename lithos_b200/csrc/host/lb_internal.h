@@ -53,7 +53,7 @@
     X(EventElapsedTime, cuEventElapsedTime, (float*, CUevent, CUevent))                                         \
     X(StreamBeginCapture, cuStreamBeginCapture, (CUstream, CUstreamCaptureMode))                                \
     X(StreamEndCapture, cuStreamEndCapture, (CUstream, CUgraph*))                                               \
-    X(GraphInstantiate, cuGraphInstantiate, (CUgraphExec*, CUgraph, unsigned long long))                        \
+    X(GraphInstantiate, cuGraphInstantiateWithFlags, (CUgraphExec*, CUgraph, unsigned long long))                        \
     X(GraphLaunch, cuGraphLaunch, (CUgraphExec, CUstream))                                                      \
     X(GraphDestroy, cuGraphDestroy, (CUgraph))                                                                  \
     X(GraphExecDestroy, cuGraphExecDestroy, (CUgraphExec))                                                      \
@@ -79,7 +79,7 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
 
 /* ---- kernels (entry points inside the cubins) -------------------------- */
 #define LB_KERNELS(X)                 \
-    X(gemv_int4_w128)                 \
+    X(gemv_int4_w256)                 \
     X(gptq_dequant_f32)               \
     X(gptq_unpack_u8)                 \
     X(dense_bf16_gemv)                \
@@ -123,11 +123,13 @@ struct lb_ctx {
     size_t flush_bytes;
     uint64_t launches; /* kernels launched (or graph nodes replayed) since reset */
     int pdl;           /* use programmatic dependent launch between kernels */
+    int capturing;     /* stream capture in progress */
+    uint64_t capture_launches0;
     char err[512];
 };
 
 #define LB_GEMV_SCRATCH_N (1 << 18) /* widest N a split-K GEMV may have */
-#define LB_GEMV_MAX_SPLITS 16
+#define LB_GEMV_MAX_SPLITS 8 /* = the portable thread-block-cluster size */
 
 int lb_fail(lb_ctx* c, int status, const char* fmt, ...);
 int lb_cu(lb_ctx* c, CUresult r, const char* what);
@@ -144,6 +146,8 @@ int lb_cu(lb_ctx* c, CUresult r, const char* what);
 
 int lb_launch(lb_ctx* c, int kernel, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned smem, void** params,
               int pdl);
+int lb_launch_cluster(lb_ctx* c, int kernel, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned smem,
+                      void** params, int pdl, unsigned cluster_y);
 
 /* rng helpers used by the synthetic model builder */
 uint64_t lb_rng_u64(uint64_t seed, uint64_t stream, uint64_t i);

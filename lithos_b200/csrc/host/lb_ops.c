@@ -5,18 +5,22 @@
 #include "../kernels/params.h"
 #include <math.h>
 
-#define GEMV_THREADS ((LB_GEMV_WARPS + 1) * 32)
+#define GEMV_THREADS LB_GEMV_THREADS
 
-/* Geometry of one int4 GEMV launch.  All CTAs of a launch must be co-resident
- * (two per SM) and carry equal work, so that the HBM pipe — not a tail of late
- * CTAs — ends the kernel: the K range is cut into `ksplit` group-aligned slices
- * such that tiles*ksplit is close to (and not above) 2 CTAs per SM. */
+/* Geometry of one int4 GEMV launch.
+ *  - grid = (column tiles of 128, ksplit); the ksplit CTAs of a tile form one cluster and add
+ *    their partial sums on chip, so ksplit <= 8.
+ *  - All CTAs of a launch should be co-resident and carry equal work, so that the HBM pipe and
+ *    not a tail of late CTAs ends the kernel: ksplit is chosen so that tiles*ksplit comes close
+ *    to (and not above) two CTAs per SM.
+ *  - A CTA's shared memory (ring of 16 KB stages + its activation slice) is kept under a quarter
+ *    of an SM where possible, so that the CTAs of the NEXT kernel fit beside it and prefetch
+ *    their weights while this one computes (programmatic dependent launch). */
 typedef struct { int tiles, ksplit, gps, stages; unsigned smem; } gemv_geom;
 
 static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
     if (K <= 0 || N <= 0 || K % LB_GEMV_GROUP != 0 || N % 32 != 0)
         return lb_fail(c, LB_ERR_INVALID, "int4 GEMV needs K %% 128 == 0 and N %% 32 == 0 (K=%d, N=%d)", K, N);
-    if (N > LB_GEMV_SCRATCH_N) return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: N=%d above the %d limit", N, LB_GEMV_SCRATCH_N);
     int groups = K / LB_GEMV_GROUP;
     g->tiles = (N + LB_GEMV_TILE_N - 1) / LB_GEMV_TILE_N;
     int slots = 2 * c->sm_count;
@@ -26,20 +30,22 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
     if (ks > groups) ks = groups;
     g->gps = (groups + ks - 1) / ks;
     g->ksplit = (groups + g->gps - 1) / g->gps;
-    /* ring depth: as deep as fits when two CTAs share an SM, at most 24 boxes of 4 KB */
-    int units = g->gps * (LB_GEMV_ROWS / LB_GEMV_UNIT_ROWS);
-    size_t fixed = (size_t)g->gps * LB_GEMV_ROWS * 16 + (size_t)((units + 3) & ~3) * 4 +
-                   (LB_GEMV_WARPS * LB_GEMV_TILE_N + 40) * 4;
+    /* shared memory: 1 KB alignment slack, ring of 16 KB stages (one group each), the digit
+     * table of the K slice (26 bytes per packed row), per-group sums, result buffer, mbarriers */
+    int rows = g->gps * LB_GEMV_ROWS;
+    size_t dig_words = (size_t)((6 * rows + 2 * (rows >> 2) + 3) & ~3);
+    size_t fixed = 1024 + dig_words * 4 + (size_t)((g->gps + 3) & ~3) * 4 + (LB_GEMV_TILE_N + 40) * 4;
     size_t per_stage = LB_GEMV_STAGE_BYTES + 16; /* stage + its two mbarriers */
-    size_t budget = (size_t)(c->max_smem_optin - 2048) / 2;
-    int st = budget > fixed ? (int)((budget - fixed) / per_stage) : 0;
-    if (st < 4) { /* very long K slice: give the CTA the SM to itself */
-        budget = (size_t)(c->max_smem_optin - 2048);
+    size_t sm_total = (size_t)c->max_smem_optin + 1024; /* shared memory of one SM */
+    int st = 0;
+    for (int per_sm = 4; per_sm >= 1 && st < 2; per_sm >>= 1) {
+        size_t budget = sm_total / per_sm - 1024;
+        if (budget > (size_t)c->max_smem_optin) budget = (size_t)c->max_smem_optin;
         st = budget > fixed ? (int)((budget - fixed) / per_stage) : 0;
-        if (st < 1) return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: K slice of %d groups does not fit shared memory", g->gps);
     }
-    if (st > 24) st = 24;
-    if (st > units) st = units;
+    if (st < 1) return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: K slice of %d groups does not fit shared memory", g->gps);
+    if (st > 6) st = 6;
+    if (st > g->gps) st = g->gps;
     g->stages = st;
     g->smem = (unsigned)((fixed + (size_t)st * per_stage + 127) & ~(size_t)127);
     return LB_OK;
@@ -70,30 +76,31 @@ LB_API int lb_gemv_int4_fused(lb_ctx* c, uint64_t qweight, uint64_t scales, uint
     p.aux0 = (const void*)aux0;
     p.aux1 = (const void*)aux1;
     p.x_out = (uint16_t*)x_out;
-    p.partial = (float*)c->gemv_partial;
-    p.counters = (uint32_t*)c->gemv_counters;
     p.status = (uint32_t*)c->dev_status;
     p.K = K; p.N = N;
     p.ksplit = g.ksplit;
     p.groups_per_split = g.gps;
-    p.stages = g.stages;
     p.x_mode = x_mode; p.y_mode = y_mode;
     p.eps = eps;
-    /* qweight as a [K/8, N] uint32 matrix; one TMA box = 8 packed rows x 128 columns.
-     * Columns past N (ragged last tile) are zero-filled and never stored. */
+    p.stages = g.stages;
+    /* qweight viewed as [N/32 column blocks][K/8 packed rows][32 columns] so that ONE tiled load
+     * brings a whole stage: box = 8 column blocks x 16 rows x 32 columns, laid down as eight
+     * consecutive 2 KB boxes with the 128-byte swizzle.  Parts of the box past the matrix
+     * (ragged last tile, last group) are zero-filled and never used. */
     {
         CUtensorMap tm;
-        cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 8)};
-        cuuint64_t strides[1] = {(cuuint64_t)N * 4};
-        cuuint32_t box[2] = {LB_GEMV_TILE_N, LB_GEMV_UNIT_ROWS};
-        cuuint32_t estr[2] = {1, 1};
-        LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)qweight, dims, strides, box,
-                                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+        cuuint64_t dims[3] = {32, (cuuint64_t)(K / 8), (cuuint64_t)(N / 32)};
+        cuuint64_t strides[2] = {(cuuint64_t)N * 4, 128};
+        cuuint32_t box[3] = {32, LB_GEMV_ROWS, LB_GEMV_TILE_N / 32};
+        cuuint32_t estr[3] = {1, 1, 1};
+        LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void*)qweight, dims, strides, box,
+                                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
         memcpy(p.tmap, &tm, sizeof tm);
     }
     void* params[] = {&p};
-    return lb_launch(c, LBK_gemv_int4_w128, (unsigned)g.tiles, (unsigned)g.ksplit, 1, GEMV_THREADS, g.smem, params, 1);
+    return lb_launch_cluster(c, LBK_gemv_int4_w256, (unsigned)g.tiles, (unsigned)g.ksplit, 1, GEMV_THREADS, g.smem, params, 1,
+                             (unsigned)g.ksplit);
 }
 
 LB_API int lb_gemv_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y, int K,

@@ -6,78 +6,148 @@
 // [K/128,N/8] (NULL = zero-point 8, the reference's constant), x fp16, fp32
 // accumulation over groups, y fp16/fp32.
 //
-// Shape of the kernel (HBM-bound, ~0.5 B/weight):
-//   * CTA (tile, split) owns 128 output columns and a contiguous range of
-//     K-groups.  One elected producer lane streams "units" (half a group: a box
-//     of 8 packed rows x 512 B) into a ring of shared-memory stages with one
-//     tiled TMA load each (cp.async.bulk.tensor.2d, completion on an mbarrier,
-//     L2 evict-first hint since weights are read once).
-//   * 8 consumer warps each take whole units round-robin; a lane owns 4
-//     adjacent columns (one 128-bit shared load per packed row) and fetches its
-//     4 scales / zero-points of the unit's group straight from global memory.
-//   * Dequant in registers: (word & 0x000f000f) | 0x6400 6400 is the fp16x2
-//     pair (1024+q_j, 1024+q_{j+4}); one HSUB2/HFMA2 turns it into exact
-//     integers (q-8); four HFMA2 against the matching x pairs give the
-//     8-weight partial dot product, widened to fp32 once per packed word.
-//     The per-group scale and the zero-point correction (8-z)*sum(x) are
-//     applied once per unit in fp32.
-//   * Reduction is ordered everywhere (warp order inside the CTA, split order
-//     across CTAs through a scratch buffer and a self-resetting arrival
-//     counter), so results are bit-identical run to run; the reference's
-//     atom.global.add.f32 split-K is not reproduced.
-//   * The producer starts prefetching weights before griddepcontrol.wait, so
-//     under programmatic dependent launch the copy pipeline is already full
-//     when the previous kernel's output (x) becomes visible.
+// Shape of the kernel.  At B200 bandwidth (6.5 TB/s measured) a weight must cost well
+// under one instruction or the SMs, not HBM, bound the GEMV: scalar dequant (4 ops/weight
+// in the reference), fp16x2 FMA (2.4 ops/weight measured here) and even fp16 mma.sync
+// (8 cycles per 256 weights per SM sub-partition) all measured slower than the memory
+// stream.  Per-thread loads are too slow as well (about 2.7 TB/s measured for read-only
+// ld.global on this part).  So:
+//   * Weights are streamed by the TMA engine: CTA (tile, split) owns 256 output columns
+//     and a contiguous range of K-groups; one elected producer lane feeds a ring of
+//     16 KB stages (one group x 256 columns) with ONE tiled cp.async.bulk.tensor.3d each
+//     (eight 32-column boxes, 128-byte swizzle, completion on an mbarrier, L2 evict-first).
+//   * The dot products are exact integer arithmetic on the tensor cores:
+//     mma.sync.m16n8k32.u8.s8.  A fragment = packed words as they are: w & 0x0f0f0f0f
+//     and (w >> 4) & 0x0f0f0f0f (3 instructions per 8 weights); B fragment = the fp16
+//     activations scaled by a power of two to integers |X| < 2^22 and split into three
+//     signed base-256 digits, one B column per digit plane.  sum q*X is exact in int32;
+//     the zero-point term z * sum X, the digit weights, the fp16 group scale and 2^-shift
+//     are applied per group in fp32.  X is exact for every activation within 2^-11 of the
+//     slice maximum (and off by at most max|x| 2^-23 below), so the result is closer to
+//     the real-number dot product than an fp32 FMA loop.
+//     (mma.sync rather than tcgen05: M is 1 here; tcgen05's 64/128-row tiles belong to the
+//     batched path.  The int4 mma shape is emulated on this part: 152 cycles measured.)
+//   * A CTA needs about 55 KB of shared memory, so the CTAs of TWO consecutive kernels
+//     fit on an SM: griddepcontrol.launch_dependents is issued at once and the next kernel
+//     streams its first stages while this one computes; its consumers wait in
+//     griddepcontrol.wait for the activations.
+//   * Split-K is ordered and stays on chip: the CTAs that split one column tile form a
+//     thread-block cluster and rank 0 adds their partial sums in rank order out of
+//     distributed shared memory, so results are bit-identical run to run; the reference's
+//     atom.global.add.f32 split-K is not reproduced.  Every mbarrier wait is bounded and
+//     reports through a status word instead of hanging.
 #include "common.cuh"
 #include "params.h"
 
-#define CONSUMERS (LB_GEMV_WARPS * 32)
-#define UROWS LB_GEMV_UNIT_ROWS
+#define GEMV_CONSUMER_WARPS 4
+#define GEMV_CONSUMERS (GEMV_CONSUMER_WARPS * 32)
+#define GEMV_BOX_BYTES (LB_GEMV_ROWS * 128)  // one swizzled box: 16 packed rows x 32 columns
+#define GEMV_STAGE_BYTES LB_GEMV_STAGE_BYTES // eight boxes side by side = one group x 256 columns
 
-__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS) : "memory"); }
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_CONSUMERS) : "memory"); }
 
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t magic) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(magic)); // (a & mask) | magic
-    return r;
-}
-
-// One tiled TMA load: box (UROWS rows x 128 columns of packed words) at
-// (column x, packed row y) of the qweight matrix into one shared-memory stage.
-__device__ __forceinline__ void tma_load_box(void* dst_smem, const void* tmap, int x, int y, uint64_t* bar, uint64_t policy) {
+// One tiled TMA load (no multicast) of a whole stage: the tensor map views qweight as
+// [column block of 32][packed row][32 columns]; the box is 8 column blocks x 16 rows x 32
+// columns, written as eight consecutive 2 KB boxes with the 128-byte swizzle.
+__device__ __forceinline__ void tma_load_stage(uint32_t dst_smem, const void* tmap, int colblock, int row, uint64_t* bar,
+                                               uint64_t policy) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
-        " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(dst_smem)),
-        "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(dst_smem),
+        "l"(tmap), "r"(0), "r"(row), "r"(colblock), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
 
-// partial dot product of one packed word (8 weights of one column, zero-point
-// 8 removed) with the 8 matching activations; returns fp32
-__device__ __forceinline__ float dot8(uint32_t w, const __half2 (&xp)[4]) {
-    const uint32_t MAGIC = 0x64006400u;                        // fp16x2 (1024, 1024)
-    const __half2 BIAS_LO = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408)); // 1032
-    const __half2 SIXTEENTH = __halves2half2(__ushort_as_half(0x2C00), __ushort_as_half(0x2C00)); // 1/16
-    const __half2 BIAS_HI = __halves2half2(__ushort_as_half(0xD480), __ushort_as_half(0xD480));   // -72
-    uint32_t w8 = w >> 8;
-    uint32_t a = lop3_and_or(w, 0x000f000fu, MAGIC);   // 1024 + (q0, q4)
-    uint32_t b = lop3_and_or(w, 0x00f000f0u, MAGIC);   // 1024 + 16*(q1, q5)
-    uint32_t c = lop3_and_or(w8, 0x000f000fu, MAGIC);  // 1024 + (q2, q6)
-    uint32_t d = lop3_and_or(w8, 0x00f000f0u, MAGIC);  // 1024 + 16*(q3, q7)
-    __half2 qa = __hsub2(*reinterpret_cast<__half2*>(&a), BIAS_LO);
-    __half2 qb = __hfma2(*reinterpret_cast<__half2*>(&b), SIXTEENTH, BIAS_HI);
-    __half2 qc = __hsub2(*reinterpret_cast<__half2*>(&c), BIAS_LO);
-    __half2 qd = __hfma2(*reinterpret_cast<__half2*>(&d), SIXTEENTH, BIAS_HI);
-    __half2 p = __hmul2(qa, xp[0]);
-    p = __hfma2(qb, xp[1], p);
-    p = __hfma2(qc, xp[2], p);
-    p = __hfma2(qd, xp[3], p);
-    float2 f = __half22float2(p);
-    return f.x + f.y;
+// D(16x8, s32) += A(16x32, u8) * B(32x8, s8)
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 2) gemv_int4_w128(const __grid_constant__ lb_gemv_params p) {
-    extern __shared__ __align__(128) unsigned char smem[];
+// Two packed words of one packed row (column cA -> fragment row g, cB -> row g+8) against the
+// activation digits of that row.  w & 0x0f0f0f0f are the even nibbles (k = 0,2,4,6) as four
+// u8, (w >> 4) & 0x0f0f0f0f the odd ones: the whole int4 -> operand conversion is 3
+// instructions per 8 weights, and the products are exact integers.
+__device__ __forceinline__ void imma_words(int (&d)[4], uint32_t cA, uint32_t cB, uint2 xb) {
+    const uint32_t M = 0x0f0f0f0fu;
+    imma16832(d, cA & M, cB & M, (cA >> 4) & M, (cB >> 4) & M, xb.x, xb.y);
+}
+
+// cluster helpers: the CTAs that split one column tile along K form a thread-block cluster and
+// combine their partial sums through distributed shared memory
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local_ptr, uint32_t rank) {
+    uint32_t remote; float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_ptr)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// word offset of packed row R in the digit table: 6 words (3 planes x 8 bytes) per row plus a
+// 2-word pad every 4 rows, which makes the per-step fragment loads bank-conflict free
+__device__ __forceinline__ int digit_row_word(int R) { return 6 * R + 2 * (R >> 2); }
+
+// The activation of one packed row (8 consecutive k) as the kernel uses it: fp32 values already
+// rounded to fp16 (the activation contract), after the optional norm prologue.
+__device__ __forceinline__ void load_x_row(const lb_gemv_params& p, int k, bool live, float rinv, float (&v)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    if (live) {
+        if (p.x_mode == LB_X_F16) {
+            uint4 raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + k));
+            const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 f = __half22float2(h[j]);
+                v[2 * j] = f.x;
+                v[2 * j + 1] = f.y;
+            }
+        } else {
+            const float4* xv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + k);
+            float4 a = __ldg(xv), b = __ldg(xv + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        }
+    }
+    if (p.x_mode == LB_X_F32_RMSNORM) {
+        if (live) {
+            uint4 wr = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.aux0) + k));
+            const uint16_t* wb = reinterpret_cast<const uint16_t*>(&wr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = v[j] * rinv * (1.0f + bf16_bits_to_f32(wb[j]));
+        }
+    } else if (p.x_mode == LB_X_F32_HEADNORM_SILU) {
+        // one head = 128 values = the 16 rows held by a 16-lane segment (called by full warps)
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        float hr = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+        if (live) {
+            const float4* zv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.aux1) + k);
+            const float4* wv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.aux0) + (k & 127));
+            float4 za = __ldg(zv), zb = __ldg(zv + 1), wa = __ldg(wv), wb = __ldg(wv + 1);
+            float z[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
+            float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = v[j] * hr * w[j] * siluf_dev(z[j]);
+        }
+    }
+    if (p.x_mode != LB_X_F16) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __half2float(__float2half_rn(v[j]));
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w256(const __grid_constant__ lb_gemv_params p) {
+    extern __shared__ unsigned char smem_raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tile = blockIdx.x, split = blockIdx.y;
     const int n0 = tile * LB_GEMV_TILE_N;
@@ -85,231 +155,266 @@ extern "C" __global__ void __launch_bounds__(CONSUMERS + 32, 2) gemv_int4_w128(c
     const int groups = p.K / LB_GEMV_GROUP;
     const int g0 = split * p.groups_per_split;
     const int g1 = min(groups, g0 + p.groups_per_split);
-    const int n_units = max(0, g1 - g0) * (LB_GEMV_ROWS / UROWS); // half-group units
+    const int n_groups = max(0, g1 - g0); // one pipeline stage per group
     const int S = p.stages;
 
-    // shared-memory carve-up
-    unsigned char* stage_base = smem;
-    uint4* xs = reinterpret_cast<uint4*>(smem + (size_t)S * LB_GEMV_STAGE_BYTES);           // [rows] permuted fp16 x
-    float* xsum = reinterpret_cast<float*>(xs + (size_t)p.groups_per_split * LB_GEMV_ROWS); // [units]
-    float* red = xsum + ((2 * p.groups_per_split + 3) & ~3);                                // [8][128] + 40
-    uint64_t* full = reinterpret_cast<uint64_t*>(red + LB_GEMV_WARPS * LB_GEMV_TILE_N + 40);
+    // shared-memory carve-up; the swizzled boxes need 1024-byte alignment
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint32_t* xdig = reinterpret_cast<uint32_t*>(smem + (size_t)S * GEMV_STAGE_BYTES); // digit table of this K slice
+    const int dig_words = (digit_row_word(p.groups_per_split * LB_GEMV_ROWS) + 3) & ~3;
+    int* xsum = reinterpret_cast<int*>(xdig + dig_words);                 // [groups] integer sum of the group's x
+    float* red = reinterpret_cast<float*>(xsum + ((p.groups_per_split + 3) & ~3)); // [256] + 40
+    uint64_t* full = reinterpret_cast<uint64_t*>(red + LB_GEMV_TILE_N + 40);
     uint64_t* empty = full + S;
-    __shared__ uint32_t s_ticket;
     __shared__ uint32_t s_bad;
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
+            mbar_init(&empty[s], GEMV_CONSUMER_WARPS);
         }
         s_bad = 0;
         mbar_fence_init();
     }
     __syncthreads();
+    // Let the next kernel in the stream become resident now: it only prefetches its own weights
+    // until this grid has completed (its consumers sit in griddepcontrol.wait), which keeps the
+    // HBM pipe busy across the kernel boundary.
+    pdl_launch_dependents();
 
-    if (warp == LB_GEMV_WARPS) {
-        // ---------------- producer: one elected lane streams boxes into the ring ----------------
-        // Weights never change, so this starts before griddepcontrol.wait: under programmatic
-        // dependent launch the ring is already full when the activations become visible.
+    if (warp == GEMV_CONSUMER_WARPS) {
+        // ---------------- producer: one elected lane streams stages into the ring ----------------
+        // Weights never change, so this starts before griddepcontrol.wait.
         if (lane == 0) {
             const uint64_t pol = l2_policy_evict_first();
-            const int row0 = g0 * LB_GEMV_ROWS;
-            for (int u = 0; u < n_units; ++u) {
+            for (int u = 0; u < n_groups; ++u) {
                 const int s = u % S;
                 if (u >= S && !mbar_wait(&empty[s], ((u / S) - 1) & 1)) {
                     atomicExch(p.status, LB_DEV_TIMEOUT_EMPTY);
                     s_bad = 1;
                     break;
                 }
-                mbar_arrive_expect_tx(&full[s], LB_GEMV_STAGE_BYTES);
-                tma_load_box(stage_base + (size_t)s * LB_GEMV_STAGE_BYTES, p.tmap, n0, row0 + u * UROWS, &full[s], pol);
+                mbar_arrive_expect_tx(&full[s], GEMV_STAGE_BYTES); // out-of-range parts of the box are zero-filled
+                tma_load_stage(smem_base + (uint32_t)s * GEMV_STAGE_BYTES, p.tmap, n0 >> 5, (g0 + u) * LB_GEMV_ROWS, &full[s], pol);
             }
         }
-        return; // consumers wait for every box, so no copy is in flight when the CTA ends
+        // consumers wait for every stage, so no copy is in flight past their loop; the warp
+        // stays for the cluster barriers below
     }
 
-    // ---------------- consumer warps ----------------
-    pdl_wait(); // x (and y for accumulate mode) come from the previous kernel
+    const int fg = lane >> 2, ft = lane & 3; // fragment row group / k-slot group of this lane
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float unit = 1.0f; // value of one integer step of the quantised activations (2^-shift)
+    if (warp < GEMV_CONSUMER_WARPS) {
+        pdl_wait(); // x (and y for accumulate mode) come from the previous kernel
+        const int rows = n_groups * LB_GEMV_ROWS;
+        const int row0 = g0 * LB_GEMV_ROWS; // first packed row of this split
 
-    const int rows = n_units * UROWS;
-    const int row0 = g0 * LB_GEMV_ROWS; // first packed row of this split
-
-    // --- prologue: build the fp16 activation slice in shared memory ---
-    float rinv = 1.0f;
-    if (p.x_mode == LB_X_F32_RMSNORM) {
-        const float4* xv = reinterpret_cast<const float4*>(p.x);
-        float ss = 0.f;
-        for (int i = tid; i < p.K / 4; i += CONSUMERS) {
-            float4 v = __ldg(xv + i);
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) red[warp] = ss;
-        consumer_bar();
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < LB_GEMV_WARPS; ++w) tot += red[w];
-        rinv = rsqrtf(tot / (float)p.K + p.eps);
-        consumer_bar();
-    }
-    for (int rb = 0; rb < rows; rb += CONSUMERS) {
-        const int r = rb + tid;         // row within the split (16-lane segments never straddle a group)
-        const bool live = r < rows;
-        const int k = (row0 + r) * 8;   // first k of this packed row
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = 0.f;
-        if (live) {
-            if (p.x_mode == LB_X_F16) {
-                uint4 raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + k));
-                const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float2 f = __half22float2(h[j]);
-                    v[2 * j] = f.x;
-                    v[2 * j + 1] = f.y;
-                }
-            } else {
-                const float4* xv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x) + k);
-                float4 a = __ldg(xv), b = __ldg(xv + 1);
-                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-                v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-            }
-        }
+        // --- prologue: the activation slice as exact integers -------------------------------
+        // X_k = rint(x_k * 2^shift) with |X| < 2^22, split into three signed base-256 digits; the
+        // digits are the B operand of the integer MMA (one B column per digit plane).  x_k is
+        // fp16, so X_k is EXACT for every element within 2^-11 of the slice maximum and off by at
+        // most max|x| * 2^-23 below that.
+        float rinv = 1.0f;
         if (p.x_mode == LB_X_F32_RMSNORM) {
-            if (live) {
-                uint4 wr = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.aux0) + k));
-                const uint16_t* wb = reinterpret_cast<const uint16_t*>(&wr);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = v[j] * rinv * (1.0f + bf16_bits_to_f32(wb[j]));
-            }
-        } else if (p.x_mode == LB_X_F32_HEADNORM_SILU) {
-            // one head = 128 values = the 16 rows held by a 16-lane segment
+            const float4* xv = reinterpret_cast<const float4*>(p.x);
             float ss = 0.f;
+            for (int i = tid; i < p.K / 4; i += GEMV_CONSUMERS) {
+                float4 v = __ldg(xv + i);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) red[warp] = ss;
+            consumer_bar();
+            float tot = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+            for (int w = 0; w < GEMV_CONSUMER_WARPS; ++w) tot += red[w];
+            rinv = rsqrtf(tot / (float)p.K + p.eps);
+            consumer_bar();
+        }
+        float vmax = 0.f;
+        for (int rb = 0; rb < rows; rb += GEMV_CONSUMERS) {
+            float v[8];
+            load_x_row(p, (row0 + rb + tid) * 8, rb + tid < rows, rinv, v);
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            float hr = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+            for (int j = 0; j < 8; ++j) vmax = fmaxf(vmax, fabsf(v[j]));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+        if (lane == 0) red[8 + warp] = vmax;
+        consumer_bar();
+        vmax = fmaxf(fmaxf(red[8], red[9]), fmaxf(red[10], red[11]));
+        // shift so that max|x| * 2^shift lies in [2^21, 2^22); all-zero or non-finite slices use shift 0
+        int shift = 0;
+        if (vmax > 0.f && vmax < 3.0e38f) shift = 21 - (int)((__float_as_uint(vmax) >> 23) & 0xffu) + 127;
+        const float qscale = __uint_as_float((uint32_t)(127 + shift) << 23); // 2^shift (|shift| < 60 for fp16 data)
+        unit = __uint_as_float((uint32_t)(127 - shift) << 23);
+        for (int rb = 0; rb < rows; rb += GEMV_CONSUMERS) {
+            const int r = rb + tid;
+            const bool live = r < rows;
+            float v[8];
+            load_x_row(p, (row0 + r) * 8, live, rinv, v);
+            int X[8], rs = 0;
+            uint32_t ev[3] = {0u, 0u, 0u}, od[3] = {0u, 0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                X[j] = __float2int_rn(v[j] * qscale);
+                rs += X[j];
+                int t = X[j];
+#pragma unroll
+                for (int d = 0; d < 3; ++d) {
+                    const int dg = d < 2 ? ((t + 128) & 255) - 128 : t; // signed digit in [-128,127]
+                    t = (t - dg) >> 8;
+                    const uint32_t byte = (uint32_t)dg & 0xffu;
+                    if (j & 1) od[d] |= byte << (8 * (j >> 1));
+                    else ev[d] |= byte << (8 * (j >> 1));
+                }
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o); // the group's 16 rows
             if (live) {
-                const float4* zv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.aux1) + k);
-                const float4* wv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.aux0) + (k & 127));
-                float4 za = __ldg(zv), zb = __ldg(zv + 1), wa = __ldg(wv), wb = __ldg(wv + 1);
-                float z[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
-                float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+                uint32_t* dst = xdig + digit_row_word(r);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = v[j] * hr * w[j] * siluf_dev(z[j]);
+                for (int d = 0; d < 3; ++d) *reinterpret_cast<uint2*>(dst + 2 * d) = make_uint2(ev[d], od[d]);
+                if ((lane & 15) == 0) xsum[r >> 4] = rs;
+                if (p.x_out && tile == 0) {
+                    __half2 pl[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
+                                     __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
+                    *reinterpret_cast<uint4*>(p.x_out + (row0 + r) * 8) = *reinterpret_cast<uint4*>(pl);
+                }
             }
         }
-        __half h[8];
-        float rs = 0.f;
+        consumer_bar();
+
+        // --- main loop: one group (16 packed rows x 256 columns) per stage; a warp takes two
+        //     adjacent 32-column boxes.  Box rows are 128 B; the 16-byte chunk c of row r sits at
+        //     chunk c ^ (r & 7) (128-byte swizzle).  In step e a lane reads packed row
+        //     8*(e>>1) + 2*ft + (e&1), chunk fg: the 8 lanes of a quarter-warp then hit 8 different
+        //     chunks (no bank conflict), and all lanes with the same ft share one packed row, as
+        //     the MMA k-slots need.  Lanes fg = 0,1,2 supply the three digit planes as B columns.
+        const int cbase = warp * 64;                  // this warp's first column inside the tile
+        const bool live0 = cbase < ncols, live1 = cbase + 32 < ncols; // N % 32 == 0: a box is all valid or all past N
+        const int col0 = n0 + cbase + fg * 4;         // lane's 4 columns in box 0; box 1 is 32 further
+        const __half* sc_ptr = reinterpret_cast<const __half*>(p.scales) + col0;
+        const uint32_t* qz_ptr = p.qzeros ? p.qzeros + (col0 >> 3) : nullptr;
+        // lane ft holds B columns 2ft, 2ft+1 of the result: ft=0 digits 0 and 1, ft=1 digit 2
+        const float lane_mul = ft == 0 ? 1.0f : (ft == 1 ? 65536.0f : 0.0f);
+        const bool has_digits = fg < 3;
+        for (int u = 0; u < n_groups; ++u) {
+            const int s = u % S;
+            uint2 sraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
+            uint32_t zw[2] = {0x88888888u, 0x88888888u};
+            // issued before the wait, used after the MMAs
+            if (live0) sraw[0] = __ldg(reinterpret_cast<const uint2*>(sc_ptr + (size_t)(g0 + u) * p.N));
+            if (live1) sraw[1] = __ldg(reinterpret_cast<const uint2*>(sc_ptr + (size_t)(g0 + u) * p.N + 32));
+            if (qz_ptr) {
+                if (live0) zw[0] = __ldg(qz_ptr + (size_t)(g0 + u) * (p.N >> 3));
+                if (live1) zw[1] = __ldg(qz_ptr + (size_t)(g0 + u) * (p.N >> 3) + 4);
+            }
+            if (!mbar_wait(&full[s], (u / S) & 1)) {
+                if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); s_bad = 1; }
+                break;
+            }
+            int d[2][2][4]; // [box][column pair][fragment]
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            h[j] = __float2half_rn(v[j]);
-            rs += __half2float(h[j]);
-        }
-        // sum over the 8 rows of the unit (8-lane segment)
+            for (int i = 0; i < 16; ++i) (&d[0][0][0])[i] = 0;
+            if (live0) {
+                const unsigned char* box = smem + (size_t)s * GEMV_STAGE_BYTES + (warp * 2) * GEMV_BOX_BYTES;
 #pragma unroll
-        for (int o = 4; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
-        if (live) {
-            __half2 pr[4] = {__halves2half2(h[0], h[4]), __halves2half2(h[1], h[5]), __halves2half2(h[2], h[6]),
-                             __halves2half2(h[3], h[7])};
-            xs[r] = *reinterpret_cast<uint4*>(pr);
-            if ((lane & 7) == 0) xsum[r >> 3] = rs;
-            if (p.x_out && tile == 0) {
-                __half2 pl[4] = {__halves2half2(h[0], h[1]), __halves2half2(h[2], h[3]), __halves2half2(h[4], h[5]),
-                                 __halves2half2(h[6], h[7])};
-                *reinterpret_cast<uint4*>(p.x_out + k) = *reinterpret_cast<uint4*>(pl);
+                for (int e = 0; e < 4; ++e) {
+                    const int r = 8 * (e >> 1) + 2 * ft + (e & 1);
+                    uint2 xb = make_uint2(0u, 0u);
+                    if (has_digits) xb = *reinterpret_cast<const uint2*>(xdig + digit_row_word(u * LB_GEMV_ROWS + r) + 2 * fg);
+                    const uint32_t off = r * 128 + ((fg ^ (r & 7)) << 4);
+                    const uint4 w0 = *reinterpret_cast<const uint4*>(box + off);
+                    imma_words(d[0][0], w0.x, w0.y, xb);
+                    imma_words(d[0][1], w0.z, w0.w, xb);
+                    if (live1) {
+                        const uint4 w1 = *reinterpret_cast<const uint4*>(box + GEMV_BOX_BYTES + off);
+                        imma_words(d[1][0], w1.x, w1.y, xb);
+                        imma_words(d[1][1], w1.z, w1.w, xb);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]); // this warp is done with the stage
+            // per column: (sum q X) - z * (sum X), times the fp16 group scale.  Fragment element 0/2
+            // is B column 2ft (row g / g+8), element 1/3 is B column 2ft+1: digit d and d+1.
+            const float xs_f = ft == 0 ? (float)xsum[u] : 0.f;
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[b].x));
+                const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[b].y));
+                const uint32_t z = zw[b] >> ((fg & 1) * 16);
+                const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int* f = d[b][c >> 1];
+                    const int comb = f[(c & 1) * 2] + (f[(c & 1) * 2 + 1] << 8);
+                    const float zf = __uint_as_float(0x4B000000u | ((z >> (4 * c)) & 0xFu)) - 8388608.0f;
+                    acc[b * 4 + c] = fmaf(sc[c], fmaf(-zf, xs_f, (float)comb * lane_mul), acc[b * 4 + c]);
+                }
             }
         }
-    }
-    consumer_bar();
-    pdl_launch_dependents();
-
-    // --- main loop: each warp consumes whole units; a lane owns 4 adjacent columns ---
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool col_ok = lane * 4 < ncols;
-    for (int u = warp; u < n_units; u += LB_GEMV_WARPS) {
-        const int s = u % S;
-        const int g = g0 + (u >> 1);
-        // this unit's scales / zero-points for the lane's columns: issued first, used last
-        uint2 sraw = make_uint2(0u, 0u);
-        uint32_t zw = 0x88888888u;
-        if (col_ok) {
-            sraw = __ldg(reinterpret_cast<const uint2*>(p.scales + (size_t)g * p.N + n0 + lane * 4));
-            if (p.qzeros) zw = __ldg(p.qzeros + (size_t)g * (p.N >> 3) + (n0 >> 3) + (lane >> 1));
-        }
-        if (!mbar_wait(&full[s], (u / S) & 1)) {
-            if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); s_bad = 1; }
-            break;
-        }
-        const unsigned char* st = stage_base + (size_t)s * LB_GEMV_STAGE_BYTES;
-        float ga[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint4* xrow = xs + u * UROWS;
+        // add the digit planes held by the four ft lanes (fixed order), scale back to x units
 #pragma unroll
-        for (int r = 0; r < UROWS; ++r) {
-            uint4 w = *reinterpret_cast<const uint4*>(st + r * (LB_GEMV_TILE_N * 4) + lane * 16);
-            uint4 xr = xrow[r];
-            const __half2(&xp)[4] = *reinterpret_cast<const __half2(*)[4]>(&xr);
-            ga[0] += dot8(w.x, xp);
-            ga[1] += dot8(w.y, xp);
-            ga[2] += dot8(w.z, xp);
-            ga[3] += dot8(w.w, xp);
+        for (int i = 0; i < 8; ++i) {
+            float a = acc[i];
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            acc[i] = a * unit;
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]); // stage may be refilled
-        float2 s01 = __half22float2(*reinterpret_cast<__half2*>(&sraw.x));
-        float2 s23 = __half22float2(*reinterpret_cast<__half2*>(&sraw.y));
-        zw >>= (lane & 1) * 16;
-        const float xsu = xsum[u];
-        acc[0] = fmaf(s01.x, fmaf(8.0f - (float)(zw & 0xFu), xsu, ga[0]), acc[0]);
-        acc[1] = fmaf(s01.y, fmaf(8.0f - (float)((zw >> 4) & 0xFu), xsu, ga[1]), acc[1]);
-        acc[2] = fmaf(s23.x, fmaf(8.0f - (float)((zw >> 8) & 0xFu), xsu, ga[2]), acc[2]);
-        acc[3] = fmaf(s23.y, fmaf(8.0f - (float)((zw >> 12) & 0xFu), xsu, ga[3]), acc[3]);
-    }
+        if (ft == 0) {
+            *reinterpret_cast<float4*>(red + cbase + fg * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            *reinterpret_cast<float4*>(red + cbase + 32 + fg * 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        }
+    } // consumer warps
 
-    // --- ordered reduction across the 8 warps ---
-    *reinterpret_cast<float4*>(red + warp * LB_GEMV_TILE_N + lane * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    consumer_bar();
-    float v = 0.f;
-    if (tid < LB_GEMV_TILE_N) {
-#pragma unroll
-        for (int w = 0; w < LB_GEMV_WARPS; ++w) v += red[w * LB_GEMV_TILE_N + tid];
-    }
-
-    // --- ordered split-K across CTAs: last arriver sums the partials ---
+    // --- ordered split-K: the ksplit CTAs of a tile are one cluster; rank 0 adds the partial sums
+    //     of ranks 0,1,2,... in that order out of their shared memory ---
+    float v0 = 0.f, v1 = 0.f; // columns tid and tid + 128 (the block has 160 threads, the tile 256 columns)
+    const bool owner = tid < 128;
     if (p.ksplit > 1) {
-        if (tid < ncols) __stcg(p.partial + (size_t)split * p.N + n0 + tid, v);
-        __threadfence();
-        consumer_bar();
-        if (tid == 0) s_ticket = atomicAdd(p.counters + tile, 1u);
-        consumer_bar();
-        if (s_ticket != (uint32_t)(p.ksplit - 1)) return;
-        __threadfence();
-        v = 0.f;
-        if (tid < ncols)
-            for (int sp = 0; sp < p.ksplit; ++sp) v += __ldcg(p.partial + (size_t)sp * p.N + n0 + tid);
-        if (tid == 0) p.counters[tile] = 0u; // ready for the next launch on this stream
+        cluster_sync_all();
+        if (cluster_ctarank() == 0 && owner)
+            for (uint32_t r = 0; r < (uint32_t)p.ksplit; ++r) {
+                v0 += ld_cluster_f32(red + tid, r);
+                v1 += ld_cluster_f32(red + 128 + tid, r);
+            }
+        cluster_sync_all(); // nobody leaves while rank 0 is still reading its shared memory
+        if (cluster_ctarank() != 0) return;
+    } else {
+        __syncthreads();
+        if (owner) { v0 = red[tid]; v1 = red[128 + tid]; }
     }
 
     // --- epilogue ---
     if (s_bad) return;
     if (p.y_mode == LB_Y_SWIGLU_F16) {
-        consumer_bar(); // red is reused below; every warp has finished reading it
-        if (tid < LB_GEMV_TILE_N) red[tid] = v;
-        consumer_bar();
-        if (tid < ncols / 2) {
-            float gate = red[tid], up = red[tid + 64];
+        // columns come in interleaved 64-wide (gate, up) blocks: [0,64) gate, [64,128) up, ...
+        __syncthreads();
+        if (owner) { red[tid] = v0; red[128 + tid] = v1; }
+        __syncthreads();
+        if (owner && tid < ncols / 2) {
+            const int blk = tid >> 6, i = tid & 63;
+            const float gate = red[blk * 128 + i], up = red[blk * 128 + 64 + i];
             reinterpret_cast<__half*>(p.y)[n0 / 2 + tid] = __float2half_rn(siluf_dev(gate) * up);
         }
         return;
     }
-    if (tid < ncols) {
-        const int n = n0 + tid;
-        if (p.y_mode == LB_Y_F16) reinterpret_cast<__half*>(p.y)[n] = __float2half_rn(v);
-        else if (p.y_mode == LB_Y_F32) reinterpret_cast<float*>(p.y)[n] = v;
-        else reinterpret_cast<float*>(p.y)[n] += v;
+    if (owner) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int c = tid + 128 * h;
+            const float v = h ? v1 : v0;
+            if (c < ncols) {
+                const int n = n0 + c;
+                if (p.y_mode == LB_Y_F16) reinterpret_cast<__half*>(p.y)[n] = __float2half_rn(v);
+                else if (p.y_mode == LB_Y_F32) reinterpret_cast<float*>(p.y)[n] = v;
+                else reinterpret_cast<float*>(p.y)[n] += v;
+            }
+        }
     }
 }
 

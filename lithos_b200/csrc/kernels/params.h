@@ -8,12 +8,11 @@
 #include <stdint.h>
 
 /* ---- int4 GEMV ---------------------------------------------------------- */
-#define LB_GEMV_TILE_N 128   /* columns per CTA tile (512 B of packed words per row) */
+#define LB_GEMV_TILE_N 256   /* columns per CTA tile: eight 32-column TMA boxes */
 #define LB_GEMV_GROUP 128    /* GPTQ group size along K */
 #define LB_GEMV_ROWS 16      /* packed rows per group */
-#define LB_GEMV_UNIT_ROWS 8  /* packed rows per pipeline unit (half a group): one TMA box */
-#define LB_GEMV_WARPS 8      /* consumer warps per CTA (one more warp issues copies) */
-#define LB_GEMV_STAGE_BYTES (LB_GEMV_UNIT_ROWS * LB_GEMV_TILE_N * 4)
+#define LB_GEMV_THREADS 160  /* 4 consumer warps (one 32-column box each) + 1 producer warp */
+#define LB_GEMV_STAGE_BYTES 16384 /* one pipeline stage: 16 packed rows (one group) x 256 columns */
 
 /* how the activation vector is produced from p.x */
 enum {
@@ -28,12 +27,12 @@ enum {
     LB_Y_F16 = 0,       /* y fp16 [N] = result */
     LB_Y_F32 = 1,       /* y fp32 [N] = result */
     LB_Y_F32_ACCUM = 2, /* y fp32 [N] += result (residual add) */
-    LB_Y_SWIGLU_F16 = 3 /* columns come in interleaved 64-wide blocks (gate block, up block);
+    LB_Y_SWIGLU_F16 = 3 /* columns come in interleaved 64-wide blocks (gate block, up block, gate block, ...);
                            y fp16 [N/2] = silu(gate)*up */
 };
 
 typedef struct {
-    /* CUtensorMap over qweight as a [K/8, N] uint32 matrix, box = 8 rows x 128 columns */
+    /* CUtensorMap over qweight viewed as [N/32][K/8][32] uint32: box 8 x 16 x 32, 128-byte swizzle */
     unsigned char tmap[128] __attribute__((aligned(64)));
     const uint32_t* qweight; /* [K/8, N] */
     const uint16_t* scales;  /* fp16 [K/128, N] */
@@ -43,13 +42,11 @@ typedef struct {
     const void* aux0;
     const void* aux1;
     uint16_t* x_out;    /* optional fp16 [K]: the activation vector as the kernel used it */
-    float* partial;     /* split-K scratch, fp32 [ksplit][N] */
-    uint32_t* counters; /* split-K arrival counters, one per column tile, zero between launches */
     uint32_t* status;   /* device status word (bounded waits) */
     int32_t K, N;
-    int32_t ksplit;           /* gridDim.y */
+    int32_t ksplit;           /* gridDim.y = cluster size along y */
     int32_t groups_per_split; /* ceil(K/128 / ksplit) */
-    int32_t stages;           /* bulk-copy ring depth */
+    int32_t stages;           /* TMA ring depth */
     int32_t x_mode, y_mode;
     float eps;
 } lb_gemv_params;
