@@ -173,6 +173,49 @@ int lb_rmsnorm(lb_ctx* ctx, uint64_t x, uint64_t res, uint64_t w_bf16, uint64_t 
 int lb_argmax(lb_ctx* ctx, uint64_t x_f32, int n, uint64_t out_idx_i32);
 int lb_embed(lb_ctx* ctx, uint64_t table_bf16, uint64_t token_i32, uint64_t out_f32, int D);
 
+/* ---- the whole decode step ------------------------------------------------------------
+ * Replaces decode_one_token and its launch_* helpers (src/launcher.s:685-1092), the per-layer
+ * weight-slot table (src/launcher.s:92-141, 298-311) and the buffer plan (src/launcher.s:143-169).
+ * Layer l is a full-attention layer when l % fa_period == fa_period-1, otherwise a Gated
+ * DeltaNet layer (compiler/megakernel-link.ls:204-211); both are followed by the SwiGLU MLP. */
+typedef struct {
+    int32_t n_layers, hidden, inter, vocab;
+    int32_t dn_k_heads, dn_v_heads, dn_dim, conv_taps; /* dn_dim must be 128, conv_taps 4 */
+    int32_t fa_q_heads, fa_kv_heads, fa_dim, rot_dims; /* fa_dim must be 256 */
+    int32_t group, fa_period, max_ctx, reserved;       /* group must be 128 */
+    float eps, rope_theta;
+} lb_model_cfg;
+
+enum { LB_WS_SLOTS = 26, LB_WG_SLOTS = 3 }; /* slot indices as in src/launcher.s:92-141 and :306-311 */
+
+/* tp_rank / tp_size: tensor-parallel shard held by this context (1 GPU: 0 / 1). */
+int lb_model_create(lb_ctx* ctx, const lb_model_cfg* cfg, int tp_rank, int tp_size, lb_model** out);
+void lb_model_destroy(lb_model* m);
+/* Host tensors of one layer in the reference's slot order (26 pointers, unused slots NULL) in
+ * the reference's packed formats; they are re-laid (projections that share an input fused along
+ * N, gate/up interleaved, tensor-parallel shard cut out) and uploaded.  Replaces load_weights
+ * (src/launcher.s:3284-3683). */
+int lb_model_load_layer(lb_model* m, int layer, const void* const* slots);
+int lb_model_load_globals(lb_model* m, const void* const* globals); /* embed, lm_head, final_norm */
+/* Seeded synthetic weights with the shapes/distributions of the benchmark definition; tensor
+ * (layer, slot) is stream (layer+1)*100+slot of the generator, globals are streams 1..3. */
+int lb_model_fill_synthetic(lb_model* m, uint64_t seed);
+int lb_model_reset_state(lb_model* m); /* zero DeltaNet states, conv history and KV caches */
+/* device address of a layer's recurrent buffers: which = 0 DeltaNet state / K cache,
+ * 1 conv ring [4][C] (slot = position & 3) / V cache */
+int lb_model_state_ptr(lb_model* m, int layer, int which, uint64_t* dptr_out, size_t* bytes_out);
+int lb_model_logits_ptr(lb_model* m, uint64_t* dptr_out);
+uint64_t lb_model_weight_bytes(const lb_model* m); /* bytes of weights one decode step streams on this shard */
+/* One token, launch by launch: token and position go in, the greedy next token comes out. */
+int lb_model_decode(lb_model* m, int token, int pos, int* next_out);
+/* Capture the whole step once; then each replay consumes the token/position left on the device
+ * by the previous step (set them with lb_model_set_input) and leaves the next token there. */
+int lb_model_capture(lb_model* m);
+int lb_model_set_input(lb_model* m, int token, int pos);
+int lb_model_replay(lb_model* m, int n_steps);        /* n graph launches, no host round trip */
+int lb_model_read_next(lb_model* m, int* next_out);   /* synchronises */
+int lb_model_step_kernels(const lb_model* m);         /* kernels per decode step */
+
 #ifdef __cplusplus
 }
 #endif

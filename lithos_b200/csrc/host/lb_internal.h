@@ -86,6 +86,7 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
     X(decay_gate_beta)                \
     X(deltanet_step_bf16)             \
     X(deltanet_step_f32)              \
+    X(deltanet_layer_fused)           \
     X(attn_decode_split)              \
     X(embed_bf16)                     \
     X(argmax_f32)                     \

@@ -1,0 +1,542 @@
+/* The decode step of the Qwen3.5-27B-shaped hybrid model: weight table, buffer plan, launch
+ * sequence, graph capture.  C re-expression of the reference's host loop
+ * (src/launcher.s:685-1092 decode_one_token, :92-141 weight slots, :2981-3136 alloc_buffers,
+ * :3284-3683 load_weights) with the layer recipe of compiler/megakernel-link.ls:281-525 and
+ * models/families/qwen/qwen3.5/27b/layers/{deltanet,attention}/kernels.ls.
+ *
+ * Per layer the reference issues 15-17 launches; here it is 5:
+ *   DeltaNet layer : [RMSNorm + qkv|z projection]  [a/b proj + conv + SiLU + L2 norms + gates +
+ *                    recurrence]  [per-head RMSNorm + silu(z) gate + out projection + residual]
+ *   attention layer: [RMSNorm + q|gate|k|v projection]  [q/k norm + RoPE + KV append + split-KV
+ *                    attention + sigmoid gate]  [o projection + residual]
+ *   MLP            : [RMSNorm + gate|up projection + SwiGLU]  [down projection + residual]
+ */
+#include "lb_internal.h"
+#include "../kernels/params.h"
+#include <math.h>
+
+enum { /* src/launcher.s:92-141 */
+    WS_DN_QKV = 0, WS_DN_Z = 3, WS_DN_OUT = 6, WS_DN_PROJ_A = 9, WS_DN_PROJ_B = 10, WS_DN_A_LOG = 11, WS_DN_DT_BIAS = 12,
+    WS_DN_CONV1D = 13, WS_DN_NORM = 14,
+    WS_FA_Q = 0, WS_FA_K = 3, WS_FA_V = 6, WS_FA_O = 9, WS_FA_Q_NORM = 12, WS_FA_K_NORM = 13,
+    WS_GATE = 15, WS_UP = 18, WS_DOWN = 21, WS_INPUT_NORM = 24, WS_POST_NORM = 25,
+    WG_EMBED = 0, WG_LM_HEAD = 1, WG_FINAL_NORM = 2
+};
+
+typedef struct { CUdeviceptr qweight, scales, qzeros; int K, N; } q4_mat;
+
+typedef struct {
+    int is_fa;
+    q4_mat w_in, w_out, w_gateup, w_down;
+    CUdeviceptr input_norm, post_norm;
+    /* DeltaNet */
+    CUdeviceptr proj_a, proj_b, a_log, dt_bias, conv_w, dn_norm, dn_state, conv_ring;
+    /* attention */
+    CUdeviceptr q_norm, k_norm, k_cache, v_cache;
+    int loaded;
+} layer_t;
+
+struct lb_model {
+    lb_ctx* c;
+    lb_model_cfg cfg;
+    int tp_rank, tp_size;
+    /* per-shard sizes */
+    int HV, HK, HQ, HKV, inter_s; /* heads / intermediate columns on this shard */
+    int C_s;                      /* conv channels on this shard: 2*HK*128 + HV*128 */
+    layer_t* L;
+    CUdeviceptr embed, lm_head, final_norm;
+    int globals_loaded;
+    /* activations */
+    CUdeviceptr X, xn, in_out, mix_out, mlp_m, logits, d_token, d_pos, d_next;
+    int* h_next; /* pinned */
+    uint64_t weight_bytes;
+    lb_graph* graph;
+    int step_kernels;
+};
+
+extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps);
+extern int lb_attn_splits(lb_ctx* c, int pos, int HKV);
+extern unsigned lb_attn_smem(int G);
+
+static int is_fa(const lb_model_cfg* c, int l) { return (l % c->fa_period) == c->fa_period - 1; }
+
+static int dalloc(lb_model* m, CUdeviceptr* p, size_t bytes) {
+    uint64_t d = 0;
+    LB_TRY(lb_malloc(m->c, bytes < 16 ? 16 : bytes, &d));
+    *p = (CUdeviceptr)d;
+    return LB_OK;
+}
+static int upload(lb_model* m, CUdeviceptr* p, const void* src, size_t bytes) {
+    LB_TRY(dalloc(m, p, bytes));
+    LB_CU(m->c, lb_drv.MemcpyHtoDAsync(*p, src, bytes, m->c->stream));
+    LB_CU(m->c, lb_drv.StreamSynchronize(m->c->stream)); /* src may be a temporary */
+    return LB_OK;
+}
+
+LB_API int lb_model_create(lb_ctx* c, const lb_model_cfg* cfg, int tp_rank, int tp_size, lb_model** out) {
+    if (!c || !cfg || !out) return LB_ERR_INVALID;
+    *out = NULL;
+    if (cfg->dn_dim != 128 || cfg->fa_dim != 256 || cfg->group != 128 || cfg->conv_taps != 4)
+        return lb_fail(c, LB_ERR_INVALID, "model: kernels are built for dn_dim 128, fa_dim 256, group 128, 4 conv taps");
+    if (cfg->hidden % 128 || cfg->inter % 64 || cfg->n_layers < 1 || cfg->fa_period < 1 || cfg->max_ctx < 1 ||
+        cfg->dn_v_heads % cfg->dn_k_heads || cfg->fa_q_heads % cfg->fa_kv_heads)
+        return lb_fail(c, LB_ERR_INVALID, "model: unsupported shape");
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return lb_fail(c, LB_ERR_INVALID, "model: bad tensor-parallel rank");
+    if (tp_size != 1) return lb_fail(c, LB_ERR_INVALID, "model: tensor parallelism is set up through lb_model_create_tp");
+    lb_model* m = (lb_model*)calloc(1, sizeof *m);
+    if (!m) return LB_ERR_NOMEM;
+    m->c = c; m->cfg = *cfg; m->tp_rank = tp_rank; m->tp_size = tp_size;
+    m->HV = cfg->dn_v_heads; m->HK = cfg->dn_k_heads; m->HQ = cfg->fa_q_heads; m->HKV = cfg->fa_kv_heads;
+    m->inter_s = cfg->inter;
+    m->C_s = (2 * m->HK + m->HV) * 128;
+    m->L = (layer_t*)calloc((size_t)cfg->n_layers, sizeof(layer_t));
+    if (!m->L) { free(m); return LB_ERR_NOMEM; }
+    *out = m;
+    LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
+    const int H = cfg->hidden;
+    int n_in_dn = m->C_s + m->HV * 128, n_in_fa = (2 * m->HQ + 2 * m->HKV) * 256;
+    int n_in = n_in_dn > n_in_fa ? n_in_dn : n_in_fa;
+    int n_mix = m->HV * 128 > m->HQ * 256 ? m->HV * 128 : m->HQ * 256;
+    LB_TRY(dalloc(m, &m->X, (size_t)H * 4));
+    LB_TRY(dalloc(m, &m->xn, (size_t)H * 2));
+    LB_TRY(dalloc(m, &m->in_out, (size_t)n_in * 4));
+    LB_TRY(dalloc(m, &m->mix_out, (size_t)n_mix * 4));
+    LB_TRY(dalloc(m, &m->mlp_m, (size_t)m->inter_s * 2));
+    LB_TRY(dalloc(m, &m->logits, (size_t)cfg->vocab * 4));
+    LB_TRY(dalloc(m, &m->d_token, 16));
+    LB_TRY(dalloc(m, &m->d_pos, 16));
+    LB_TRY(dalloc(m, &m->d_next, 16));
+    LB_CU(c, lb_drv.MemHostAlloc((void**)&m->h_next, 64, 0));
+    for (int l = 0; l < cfg->n_layers; l++) {
+        layer_t* L = &m->L[l];
+        L->is_fa = is_fa(cfg, l);
+        if (L->is_fa) {
+            size_t n = (size_t)cfg->max_ctx * m->HKV * 256 * 2;
+            LB_TRY(dalloc(m, &L->k_cache, n));
+            LB_TRY(dalloc(m, &L->v_cache, n));
+        } else {
+            LB_TRY(dalloc(m, &L->dn_state, (size_t)m->HV * 128 * 128 * 4));
+            LB_TRY(dalloc(m, &L->conv_ring, (size_t)4 * m->C_s * 4));
+        }
+    }
+    return lb_model_reset_state(m);
+}
+
+LB_API int lb_model_reset_state(lb_model* m) {
+    if (!m) return LB_ERR_INVALID;
+    lb_ctx* c = m->c;
+    for (int l = 0; l < m->cfg.n_layers; l++) {
+        layer_t* L = &m->L[l];
+        if (L->is_fa) {
+            size_t n = (size_t)m->cfg.max_ctx * m->HKV * 256 * 2;
+            LB_CU(c, lb_drv.MemsetD8Async(L->k_cache, 0, n, c->stream));
+            LB_CU(c, lb_drv.MemsetD8Async(L->v_cache, 0, n, c->stream));
+        } else {
+            LB_CU(c, lb_drv.MemsetD8Async(L->dn_state, 0, (size_t)m->HV * 128 * 128 * 4, c->stream));
+            LB_CU(c, lb_drv.MemsetD8Async(L->conv_ring, 0, (size_t)4 * m->C_s * 4, c->stream));
+        }
+    }
+    LB_CU(c, lb_drv.StreamSynchronize(c->stream));
+    return LB_OK;
+}
+
+LB_API int lb_model_state_ptr(lb_model* m, int layer, int which, uint64_t* dptr, size_t* bytes) {
+    if (!m || layer < 0 || layer >= m->cfg.n_layers || !dptr || !bytes || which < 0 || which > 1) return LB_ERR_INVALID;
+    layer_t* L = &m->L[layer];
+    if (L->is_fa) {
+        *dptr = which ? L->v_cache : L->k_cache;
+        *bytes = (size_t)m->cfg.max_ctx * m->HKV * 256 * 2;
+    } else {
+        *dptr = which ? L->conv_ring : L->dn_state;
+        *bytes = which ? (size_t)4 * m->C_s * 4 : (size_t)m->HV * 128 * 128 * 4;
+    }
+    return LB_OK;
+}
+LB_API int lb_model_logits_ptr(lb_model* m, uint64_t* dptr) {
+    if (!m || !dptr) return LB_ERR_INVALID;
+    *dptr = m->logits;
+    return LB_OK;
+}
+LB_API uint64_t lb_model_weight_bytes(const lb_model* m) { return m ? m->weight_bytes : 0; }
+LB_API int lb_model_step_kernels(const lb_model* m) { return m ? m->step_kernels : 0; }
+
+/* ---- weight re-layout (host) --------------------------------------------------------
+ * A "column map" lists, for every output column of the device matrix, the column of which
+ * source matrix it comes from.  qweight / scales are gathered column by column; qzeros is
+ * re-packed nibble by nibble (8 columns per word). */
+typedef struct { const uint32_t* qw; const uint16_t* sc; const uint32_t* qz; int N; } q4_src;
+
+static int build_q4(lb_model* m, q4_mat* dst, const q4_src* src, int n_src, const int* col_src, const int* col_idx,
+                    int N_out, int K, int k0, int k1 /* packed-row range [k0,k1) in units of groups */) {
+    int groups = k1 - k0, Kd = groups * 128;
+    size_t qb = (size_t)Kd / 8 * N_out * 4, sb = (size_t)groups * N_out * 2, zb = (size_t)groups * (N_out / 8) * 4;
+    uint32_t* qw = (uint32_t*)malloc(qb);
+    uint16_t* sc = (uint16_t*)malloc(sb);
+    uint32_t* qz = (uint32_t*)calloc(1, zb);
+    if (!qw || !sc || !qz) { free(qw); free(sc); free(qz); return lb_fail(m->c, LB_ERR_NOMEM, "model: host staging"); }
+    (void)n_src; (void)K;
+#pragma omp parallel for schedule(static)
+    for (int kp = 0; kp < Kd / 8; kp++) {
+        uint32_t* o = qw + (size_t)kp * N_out;
+        for (int n = 0; n < N_out; n++) {
+            const q4_src* s = &src[col_src[n]];
+            o[n] = s->qw[(size_t)(k0 * 16 + kp) * s->N + col_idx[n]];
+        }
+    }
+#pragma omp parallel for schedule(static)
+    for (int g = 0; g < groups; g++) {
+        for (int n = 0; n < N_out; n++) {
+            const q4_src* s = &src[col_src[n]];
+            int ci = col_idx[n];
+            sc[(size_t)g * N_out + n] = s->sc[(size_t)(k0 + g) * s->N + ci];
+            uint32_t z = (s->qz[(size_t)(k0 + g) * (s->N / 8) + (ci >> 3)] >> (4 * (ci & 7))) & 0xFu;
+            qz[(size_t)g * (N_out / 8) + (n >> 3)] |= z << (4 * (n & 7));
+        }
+    }
+    dst->K = Kd; dst->N = N_out;
+    int st = upload(m, &dst->qweight, qw, qb);
+    if (st == LB_OK) st = upload(m, &dst->scales, sc, sb);
+    if (st == LB_OK) st = upload(m, &dst->qzeros, qz, zb);
+    free(qw); free(sc); free(qz);
+    m->weight_bytes += qb + sb + zb;
+    return st;
+}
+
+static q4_src slot_src(const void* const* slots, int base, int N) {
+    q4_src s = {(const uint32_t*)slots[base], (const uint16_t*)slots[base + 1], (const uint32_t*)slots[base + 2], N};
+    return s;
+}
+static int slots_present(lb_model* m, const void* const* slots, const int* idx, int n, int layer) {
+    for (int i = 0; i < n; i++)
+        if (!slots[idx[i]]) return lb_fail(m->c, LB_ERR_INVALID, "model: layer %d weight slot %d is NULL", layer, idx[i]);
+    return LB_OK;
+}
+
+LB_API int lb_model_load_layer(lb_model* m, int layer, const void* const* slots) {
+    if (!m || !slots || layer < 0 || layer >= m->cfg.n_layers) return LB_ERR_INVALID;
+    const lb_model_cfg* c = &m->cfg;
+    layer_t* L = &m->L[layer];
+    if (L->loaded) return lb_fail(m->c, LB_ERR_STATE, "model: layer %d already loaded", layer);
+    LB_CU(m->c, lb_drv.CtxSetCurrent(m->c->cu_ctx));
+    const int H = c->hidden, I = c->inter;
+    int* cs = NULL; int* ci = NULL;
+    int st = LB_OK;
+    if (!L->is_fa) {
+        static const int need[] = {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22, 23, 24, 25};
+        LB_TRY(slots_present(m, slots, need, 26, layer));
+        const int C = m->C_s, V = m->HV * 128, N = C + V;
+        q4_src src[2] = {slot_src(slots, WS_DN_QKV, C), slot_src(slots, WS_DN_Z, V)};
+        cs = (int*)malloc(sizeof(int) * N); ci = (int*)malloc(sizeof(int) * N);
+        for (int n = 0; n < N; n++) { cs[n] = n < C ? 0 : 1; ci[n] = n < C ? n : n - C; }
+        st = build_q4(m, &L->w_in, src, 2, cs, ci, N, H, 0, H / 128);
+        free(cs); free(ci);
+        if (st != LB_OK) return st;
+        q4_src so = slot_src(slots, WS_DN_OUT, H);
+        cs = (int*)calloc((size_t)H, sizeof(int)); ci = (int*)malloc(sizeof(int) * H);
+        for (int n = 0; n < H; n++) ci[n] = n;
+        st = build_q4(m, &L->w_out, &so, 1, cs, ci, H, V, 0, V / 128);
+        free(cs); free(ci);
+        if (st != LB_OK) return st;
+        LB_TRY(upload(m, &L->proj_a, slots[WS_DN_PROJ_A], (size_t)m->HV * H * 2));
+        LB_TRY(upload(m, &L->proj_b, slots[WS_DN_PROJ_B], (size_t)m->HV * H * 2));
+        LB_TRY(upload(m, &L->a_log, slots[WS_DN_A_LOG], (size_t)m->HV * 4));
+        LB_TRY(upload(m, &L->dt_bias, slots[WS_DN_DT_BIAS], (size_t)m->HV * 2));
+        LB_TRY(upload(m, &L->conv_w, slots[WS_DN_CONV1D], (size_t)4 * C * 2));
+        LB_TRY(upload(m, &L->dn_norm, slots[WS_DN_NORM], 128 * 4));
+        m->weight_bytes += (uint64_t)2 * m->HV * H * 2 + (uint64_t)4 * C * 2;
+    } else {
+        static const int need[] = {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 15, 16, 17, 18, 19, 20, 21, 22, 23, 24, 25};
+        LB_TRY(slots_present(m, slots, need, 25, layer));
+        const int NQ = 2 * m->HQ * 256, NKV = m->HKV * 256, N = NQ + 2 * NKV;
+        q4_src src[3] = {slot_src(slots, WS_FA_Q, NQ), slot_src(slots, WS_FA_K, NKV), slot_src(slots, WS_FA_V, NKV)};
+        cs = (int*)malloc(sizeof(int) * N); ci = (int*)malloc(sizeof(int) * N);
+        for (int n = 0; n < N; n++) {
+            cs[n] = n < NQ ? 0 : (n < NQ + NKV ? 1 : 2);
+            ci[n] = n < NQ ? n : (n < NQ + NKV ? n - NQ : n - NQ - NKV);
+        }
+        st = build_q4(m, &L->w_in, src, 3, cs, ci, N, H, 0, H / 128);
+        free(cs); free(ci);
+        if (st != LB_OK) return st;
+        q4_src so = slot_src(slots, WS_FA_O, H);
+        cs = (int*)calloc((size_t)H, sizeof(int)); ci = (int*)malloc(sizeof(int) * H);
+        for (int n = 0; n < H; n++) ci[n] = n;
+        st = build_q4(m, &L->w_out, &so, 1, cs, ci, H, m->HQ * 256, 0, m->HQ * 256 / 128);
+        free(cs); free(ci);
+        if (st != LB_OK) return st;
+        LB_TRY(upload(m, &L->q_norm, slots[WS_FA_Q_NORM], 256 * 2));
+        LB_TRY(upload(m, &L->k_norm, slots[WS_FA_K_NORM], 256 * 2));
+    }
+    /* MLP: gate and up interleaved in 64-column blocks so that one CTA holds both halves of SwiGLU */
+    {
+        const int N = 2 * I;
+        q4_src src[2] = {slot_src(slots, WS_GATE, I), slot_src(slots, WS_UP, I)};
+        cs = (int*)malloc(sizeof(int) * N); ci = (int*)malloc(sizeof(int) * N);
+        for (int n = 0; n < N; n++) { int blk = n / 64; cs[n] = blk & 1; ci[n] = (blk >> 1) * 64 + n % 64; }
+        st = build_q4(m, &L->w_gateup, src, 2, cs, ci, N, H, 0, H / 128);
+        free(cs); free(ci);
+        if (st != LB_OK) return st;
+        q4_src sd = slot_src(slots, WS_DOWN, H);
+        cs = (int*)calloc((size_t)H, sizeof(int)); ci = (int*)malloc(sizeof(int) * H);
+        for (int n = 0; n < H; n++) ci[n] = n;
+        st = build_q4(m, &L->w_down, &sd, 1, cs, ci, H, I, 0, I / 128);
+        free(cs); free(ci);
+        if (st != LB_OK) return st;
+    }
+    LB_TRY(upload(m, &L->input_norm, slots[WS_INPUT_NORM], (size_t)H * 2));
+    LB_TRY(upload(m, &L->post_norm, slots[WS_POST_NORM], (size_t)H * 2));
+    L->loaded = 1;
+    return LB_OK;
+}
+
+LB_API int lb_model_load_globals(lb_model* m, const void* const* g) {
+    if (!m || !g || !g[0] || !g[1] || !g[2]) return LB_ERR_INVALID;
+    if (m->globals_loaded) return lb_fail(m->c, LB_ERR_STATE, "model: globals already loaded");
+    LB_CU(m->c, lb_drv.CtxSetCurrent(m->c->cu_ctx));
+    size_t tb = (size_t)m->cfg.vocab * m->cfg.hidden * 2;
+    LB_TRY(upload(m, &m->embed, g[WG_EMBED], tb));
+    LB_TRY(upload(m, &m->lm_head, g[WG_LM_HEAD], tb));
+    LB_TRY(upload(m, &m->final_norm, g[WG_FINAL_NORM], (size_t)m->cfg.hidden * 2));
+    m->weight_bytes += tb; /* the LM head is streamed every step; the embedding contributes one row */
+    m->globals_loaded = 1;
+    return LB_OK;
+}
+
+/* ---- seeded synthetic weights ------------------------------------------------------------ */
+static void* gen_q4_slot(int which, size_t K, size_t N, uint64_t seed, uint64_t stream) {
+    if (which == 0) { uint32_t* p = (uint32_t*)malloc(K / 8 * N * 4); if (p) lb_fill_u32(p, K / 8 * N, seed, stream); return p; }
+    if (which == 1) { uint16_t* p = (uint16_t*)malloc(K / 128 * N * 2); if (p) lb_fill_scales_f16(p, K / 128 * N, seed, stream); return p; }
+    uint32_t* p = (uint32_t*)malloc(K / 128 * (N / 8) * 4);
+    if (p) lb_fill_u32(p, K / 128 * (N / 8), seed, stream);
+    return p;
+}
+
+LB_API int lb_model_fill_synthetic(lb_model* m, uint64_t seed) {
+    if (!m) return LB_ERR_INVALID;
+    const lb_model_cfg* c = &m->cfg;
+    const size_t H = c->hidden, I = c->inter;
+    for (int l = 0; l < c->n_layers; l++) {
+        void* s[LB_WS_SLOTS];
+        memset(s, 0, sizeof s);
+        const uint64_t base = (uint64_t)(l + 1) * 100;
+        const int fa = is_fa(c, l);
+        struct { int slot; size_t K, N; } q4[7];
+        int nq = 0;
+        if (!fa) {
+            q4[nq].slot = WS_DN_QKV; q4[nq].K = H; q4[nq++].N = (size_t)(2 * c->dn_k_heads + c->dn_v_heads) * 128;
+            q4[nq].slot = WS_DN_Z; q4[nq].K = H; q4[nq++].N = (size_t)c->dn_v_heads * 128;
+            q4[nq].slot = WS_DN_OUT; q4[nq].K = (size_t)c->dn_v_heads * 128; q4[nq++].N = H;
+        } else {
+            q4[nq].slot = WS_FA_Q; q4[nq].K = H; q4[nq++].N = (size_t)2 * c->fa_q_heads * 256;
+            q4[nq].slot = WS_FA_K; q4[nq].K = H; q4[nq++].N = (size_t)c->fa_kv_heads * 256;
+            q4[nq].slot = WS_FA_V; q4[nq].K = H; q4[nq++].N = (size_t)c->fa_kv_heads * 256;
+            q4[nq].slot = WS_FA_O; q4[nq].K = (size_t)c->fa_q_heads * 256; q4[nq++].N = H;
+        }
+        q4[nq].slot = WS_GATE; q4[nq].K = H; q4[nq++].N = I;
+        q4[nq].slot = WS_UP; q4[nq].K = H; q4[nq++].N = I;
+        q4[nq].slot = WS_DOWN; q4[nq].K = I; q4[nq++].N = H;
+        int ok = 1;
+        for (int i = 0; i < nq; i++)
+            for (int w = 0; w < 3; w++) {
+                s[q4[i].slot + w] = gen_q4_slot(w, q4[i].K, q4[i].N, seed, base + q4[i].slot + w);
+                ok &= s[q4[i].slot + w] != NULL;
+            }
+        uint16_t* in_norm = (uint16_t*)malloc(H * 2); uint16_t* post_norm = (uint16_t*)malloc(H * 2);
+        ok &= in_norm && post_norm;
+        if (ok) {
+            lb_fill_normal_bf16(in_norm, H, seed, base + WS_INPUT_NORM, 0.f, 0.02f);
+            lb_fill_normal_bf16(post_norm, H, seed, base + WS_POST_NORM, 0.f, 0.02f);
+        }
+        s[WS_INPUT_NORM] = in_norm; s[WS_POST_NORM] = post_norm;
+        if (ok && !fa) {
+            const size_t HV = c->dn_v_heads, C = (size_t)(2 * c->dn_k_heads + c->dn_v_heads) * 128;
+            uint16_t* pa = (uint16_t*)malloc(HV * H * 2); uint16_t* pb = (uint16_t*)malloc(HV * H * 2);
+            float* alog = (float*)malloc(HV * 4); uint16_t* dtb = (uint16_t*)malloc(HV * 2);
+            uint16_t* cw = (uint16_t*)malloc(4 * C * 2); float* hn = (float*)malloc(128 * 4);
+            ok &= pa && pb && alog && dtb && cw && hn;
+            if (ok) {
+                lb_fill_normal_bf16(pa, HV * H, seed, base + WS_DN_PROJ_A, 0.f, 0.02f);
+                lb_fill_normal_bf16(pb, HV * H, seed, base + WS_DN_PROJ_B, 0.f, 0.02f);
+                lb_fill_uniform_f32(alog, HV, seed, base + WS_DN_A_LOG, 0.f, 2.7f);
+                lb_fill_normal_bf16(dtb, HV, seed, base + WS_DN_DT_BIAS, 0.f, 0.1f);
+                lb_fill_normal_bf16(cw, 4 * C, seed, base + WS_DN_CONV1D, 0.f, 0.3f);
+                lb_fill_normal_f32(hn, 128, seed, base + WS_DN_NORM, 1.f, 0.02f);
+            }
+            s[WS_DN_PROJ_A] = pa; s[WS_DN_PROJ_B] = pb; s[WS_DN_A_LOG] = alog; s[WS_DN_DT_BIAS] = dtb;
+            s[WS_DN_CONV1D] = cw; s[WS_DN_NORM] = hn;
+        } else if (ok) {
+            uint16_t* qn = (uint16_t*)malloc(256 * 2); uint16_t* kn = (uint16_t*)malloc(256 * 2);
+            ok &= qn && kn;
+            if (ok) {
+                lb_fill_normal_bf16(qn, 256, seed, base + WS_FA_Q_NORM, 1.f, 0.02f);
+                lb_fill_normal_bf16(kn, 256, seed, base + WS_FA_K_NORM, 1.f, 0.02f);
+            }
+            s[WS_FA_Q_NORM] = qn; s[WS_FA_K_NORM] = kn;
+        }
+        int st = ok ? lb_model_load_layer(m, l, (const void* const*)s) : lb_fail(m->c, LB_ERR_NOMEM, "model: host staging");
+        for (int i = 0; i < LB_WS_SLOTS; i++) free(s[i]);
+        if (st != LB_OK) return st;
+    }
+    {
+        size_t n = (size_t)c->vocab * H;
+        uint16_t* e = (uint16_t*)malloc(n * 2); uint16_t* h = (uint16_t*)malloc(n * 2); uint16_t* fn = (uint16_t*)malloc(H * 2);
+        int st = LB_ERR_NOMEM;
+        if (e && h && fn) {
+            lb_fill_normal_bf16(e, n, seed, 1, 0.f, 0.02f);
+            lb_fill_normal_bf16(h, n, seed, 2, 0.f, 0.02f);
+            lb_fill_normal_bf16(fn, H, seed, 3, 0.f, 0.02f);
+            const void* g[3] = {e, h, fn};
+            st = lb_model_load_globals(m, g);
+        }
+        free(e); free(h); free(fn);
+        if (st != LB_OK) return st;
+    }
+    return LB_OK;
+}
+
+/* ---- the step ------------------------------------------------------------------------------ */
+static int q4_gemv(lb_model* m, const q4_mat* w, CUdeviceptr x, CUdeviceptr y, int x_mode, int y_mode, CUdeviceptr aux0,
+                   CUdeviceptr aux1, CUdeviceptr x_out) {
+    return lb_gemv_int4_fused(m->c, w->qweight, w->scales, w->qzeros, x, y, w->K, w->N, x_mode, y_mode, aux0, aux1, x_out,
+                              m->cfg.eps);
+}
+
+static int issue_step(lb_model* m) {
+    lb_ctx* c = m->c;
+    const lb_model_cfg* cfg = &m->cfg;
+    const int H = cfg->hidden;
+    uint64_t launches0 = c->launches;
+    {
+        void* params[] = {&m->embed, &m->d_token, &m->X, (void*)&H};
+        LB_TRY(lb_launch(c, LBK_embed_bf16, (unsigned)((H + 1023) / 1024), 1, 1, 256, 0, params, 1));
+    }
+    for (int l = 0; l < cfg->n_layers; l++) {
+        layer_t* L = &m->L[l];
+        if (!L->loaded) return lb_fail(c, LB_ERR_STATE, "model: layer %d has no weights", l);
+        if (!L->is_fa) {
+            const int C = m->C_s;
+            LB_TRY(q4_gemv(m, &L->w_in, m->X, m->in_out, LB_X_F32_RMSNORM, LB_Y_F32, L->input_norm, 0, m->xn));
+            lb_dn_layer_params p;
+            memset(&p, 0, sizeof p);
+            p.qkvz = (const float*)m->in_out; p.xn = (const uint16_t*)m->xn;
+            p.proj_a = (const uint16_t*)L->proj_a; p.proj_b = (const uint16_t*)L->proj_b;
+            p.a_log = (const float*)L->a_log; p.dt_bias = (const uint16_t*)L->dt_bias;
+            p.conv_w = (const uint16_t*)L->conv_w; p.conv_ring = (float*)L->conv_ring;
+            p.state = (float*)L->dn_state; p.out = (float*)m->mix_out; p.pos = (const int*)m->d_pos;
+            p.HV = m->HV; p.HK = m->HK; p.hidden = H;
+            void* params[] = {&p};
+            LB_TRY(lb_launch(c, LBK_deltanet_layer_fused, (unsigned)m->HV, 4, 1, 128, 0, params, 1));
+            LB_TRY(q4_gemv(m, &L->w_out, m->mix_out, m->X, LB_X_F32_HEADNORM_SILU, LB_Y_F32_ACCUM, L->dn_norm,
+                           m->in_out + (size_t)C * 4, 0));
+        } else {
+            LB_TRY(q4_gemv(m, &L->w_in, m->X, m->in_out, LB_X_F32_RMSNORM, LB_Y_F32, L->input_norm, 0, 0));
+            lb_attn_params p;
+            memset(&p, 0, sizeof p);
+            const size_t nq = (size_t)2 * m->HQ * 256, nkv = (size_t)m->HKV * 256;
+            p.q = (const void*)m->in_out;                      /* per head: 256 query then 256 gate columns */
+            p.gate = (const void*)(m->in_out + 256 * 4);
+            p.k_new = (const void*)(m->in_out + nq * 4);
+            p.v_new = (const void*)(m->in_out + (nq + nkv) * 4);
+            p.q_norm_w = (const uint16_t*)L->q_norm; p.k_norm_w = (const uint16_t*)L->k_norm;
+            p.k_cache = (uint16_t*)L->k_cache; p.v_cache = (uint16_t*)L->v_cache;
+            p.out = (float*)m->mix_out; p.scratch = (float*)c->attn_scratch;
+            p.counters = (uint32_t*)(c->gemv_counters + 2048 * 4);
+            p.pos_ptr = (const int*)m->d_pos; p.pos = 0;
+            p.HQ = m->HQ; p.HKV = m->HKV;
+            p.splits = lb_attn_splits(c, cfg->max_ctx, m->HKV);
+            p.in_dtype = 1; p.gate_stride = 512; p.q_stride = 512;
+            p.rot_dims = cfg->rot_dims; p.rope_theta = cfg->rope_theta; p.eps = cfg->eps;
+            void* params[] = {&p};
+            LB_TRY(lb_launch(c, LBK_attn_decode_split, (unsigned)m->HKV, (unsigned)p.splits, 1, 256,
+                             lb_attn_smem(m->HQ / m->HKV), params, 1));
+            LB_TRY(q4_gemv(m, &L->w_out, m->mix_out, m->X, LB_X_F32, LB_Y_F32_ACCUM, 0, 0, 0));
+        }
+        LB_TRY(q4_gemv(m, &L->w_gateup, m->X, m->mlp_m, LB_X_F32_RMSNORM, LB_Y_SWIGLU_F16, L->post_norm, 0, 0));
+        LB_TRY(q4_gemv(m, &L->w_down, m->mlp_m, m->X, LB_X_F16, LB_Y_F32_ACCUM, 0, 0, 0));
+    }
+    if (!m->globals_loaded) return lb_fail(c, LB_ERR_STATE, "model: globals have no weights");
+    LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, cfg->vocab, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps));
+    {
+        int n = cfg->vocab;
+        void* params[] = {&m->logits, &n, &m->d_next, &m->d_token, &m->d_pos};
+        LB_TRY(lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1));
+    }
+    m->step_kernels = (int)(c->launches - launches0);
+    return LB_OK;
+}
+
+LB_API int lb_model_set_input(lb_model* m, int token, int pos) {
+    if (!m) return LB_ERR_INVALID;
+    if (token < 0 || token >= m->cfg.vocab || pos < 0 || pos >= m->cfg.max_ctx)
+        return lb_fail(m->c, LB_ERR_INVALID, "model: token %d / position %d out of range", token, pos);
+    m->h_next[1] = token; m->h_next[2] = pos;
+    LB_CU(m->c, lb_drv.MemcpyHtoDAsync(m->d_token, &m->h_next[1], 4, m->c->stream));
+    LB_CU(m->c, lb_drv.MemcpyHtoDAsync(m->d_pos, &m->h_next[2], 4, m->c->stream));
+    return LB_OK;
+}
+
+LB_API int lb_model_read_next(lb_model* m, int* next_out) {
+    if (!m || !next_out) return LB_ERR_INVALID;
+    LB_CU(m->c, lb_drv.MemcpyDtoHAsync(&m->h_next[0], m->d_next, 4, m->c->stream));
+    LB_CU(m->c, lb_drv.StreamSynchronize(m->c->stream));
+    *next_out = m->h_next[0];
+    uint32_t st = 0;
+    return lb_device_status(m->c, &st);
+}
+
+LB_API int lb_model_decode(lb_model* m, int token, int pos, int* next_out) {
+    if (!m || !next_out) return LB_ERR_INVALID;
+    LB_CU(m->c, lb_drv.CtxSetCurrent(m->c->cu_ctx));
+    LB_TRY(lb_model_set_input(m, token, pos));
+    LB_TRY(issue_step(m));
+    return lb_model_read_next(m, next_out);
+}
+
+LB_API int lb_model_capture(lb_model* m) {
+    if (!m) return LB_ERR_INVALID;
+    if (m->graph) { lb_graph_destroy(m->c, m->graph); m->graph = NULL; }
+    LB_CU(m->c, lb_drv.CtxSetCurrent(m->c->cu_ctx));
+    LB_TRY(lb_graph_begin_capture(m->c));
+    int st = issue_step(m);
+    lb_graph* g = NULL;
+    int st2 = lb_graph_end_capture(m->c, &g);
+    if (st != LB_OK) { if (g) lb_graph_destroy(m->c, g); return st; }
+    if (st2 != LB_OK) return st2;
+    m->graph = g;
+    m->step_kernels = lb_graph_kernel_count(g);
+    return LB_OK;
+}
+
+LB_API int lb_model_replay(lb_model* m, int n_steps) {
+    if (!m || n_steps < 0) return LB_ERR_INVALID;
+    if (!m->graph) return lb_fail(m->c, LB_ERR_STATE, "model: replay before capture");
+    for (int i = 0; i < n_steps; i++) LB_TRY(lb_graph_launch(m->c, m->graph));
+    return LB_OK;
+}
+
+LB_API void lb_model_destroy(lb_model* m) {
+    if (!m) return;
+    lb_ctx* c = m->c;
+    if (lb_drv.loaded && c && c->cu_ctx) {
+        lb_drv.CtxSetCurrent(c->cu_ctx);
+        lb_drv.StreamSynchronize(c->stream);
+        if (m->graph) lb_graph_destroy(c, m->graph);
+        CUdeviceptr g[] = {m->embed, m->lm_head, m->final_norm, m->X, m->xn, m->in_out, m->mix_out, m->mlp_m, m->logits,
+                           m->d_token, m->d_pos, m->d_next};
+        for (size_t i = 0; i < sizeof g / sizeof g[0]; i++) if (g[i]) lb_drv.MemFree(g[i]);
+        for (int l = 0; m->L && l < m->cfg.n_layers; l++) {
+            layer_t* L = &m->L[l];
+            q4_mat* q[] = {&L->w_in, &L->w_out, &L->w_gateup, &L->w_down};
+            for (int i = 0; i < 4; i++) {
+                if (q[i]->qweight) lb_drv.MemFree(q[i]->qweight);
+                if (q[i]->scales) lb_drv.MemFree(q[i]->scales);
+                if (q[i]->qzeros) lb_drv.MemFree(q[i]->qzeros);
+            }
+            CUdeviceptr p[] = {L->input_norm, L->post_norm, L->proj_a, L->proj_b, L->a_log, L->dt_bias, L->conv_w, L->dn_norm,
+                               L->dn_state, L->conv_ring, L->q_norm, L->k_norm, L->k_cache, L->v_cache};
+            for (size_t i = 0; i < sizeof p / sizeof p[0]; i++) if (p[i]) lb_drv.MemFree(p[i]);
+        }
+        if (m->h_next) lb_drv.MemFreeHost(m->h_next);
+    }
+    free(m->L);
+    free(m);
+}

@@ -27,6 +27,7 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
     int ks = slots / g->tiles;
     if (ks < 1) ks = 1;
     if (ks > LB_GEMV_MAX_SPLITS) ks = LB_GEMV_MAX_SPLITS;
+    { const char* e = getenv("LB_GEMV_KSPLIT"); if (e) ks = atoi(e); }
     if (ks > groups) ks = groups;
     g->gps = (groups + ks - 1) / ks;
     g->ksplit = (groups + g->gps - 1) / g->gps;
@@ -34,11 +35,14 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
      * table of the K slice (26 bytes per packed row), per-group sums, result buffer, mbarriers */
     int rows = g->gps * LB_GEMV_ROWS;
     size_t dig_words = (size_t)((6 * rows + 2 * (rows >> 2) + 3) & ~3);
-    size_t fixed = 1024 + dig_words * 4 + (size_t)((g->gps + 3) & ~3) * 4 + (LB_GEMV_TILE_N + 40) * 4;
+    size_t fixed = 1024 + dig_words * 4 + (size_t)((g->gps + 3) & ~3) * 4 + (LB_GEMV_TILE_N + 40) * 4 +
+                   (size_t)g->gps * (LB_GEMV_TILE_N * 2 + LB_GEMV_TILE_N / 2); /* + group scales and zero-points */
     size_t per_stage = LB_GEMV_STAGE_BYTES + 16; /* stage + its two mbarriers */
     size_t sm_total = (size_t)c->max_smem_optin + 1024; /* shared memory of one SM */
     int st = 0;
-    for (int per_sm = 4; per_sm >= 1 && st < 2; per_sm >>= 1) {
+    int per_sm0 = 4;
+    { const char* e = getenv("LB_GEMV_PERSM"); if (e) per_sm0 = atoi(e); }
+    for (int per_sm = per_sm0; per_sm >= 1 && st < 2; per_sm >>= 1) {
         size_t budget = sm_total / per_sm - 1024;
         if (budget > (size_t)c->max_smem_optin) budget = (size_t)c->max_smem_optin;
         st = budget > fixed ? (int)((budget - fixed) / per_stage) : 0;
@@ -46,6 +50,7 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
     if (st < 1) return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: K slice of %d groups does not fit shared memory", g->gps);
     if (st > 6) st = 6;
     if (st > g->gps) st = g->gps;
+    { const char* e = getenv("LB_GEMV_STAGES"); if (e && atoi(e) < st) st = atoi(e); }
     g->stages = st;
     g->smem = (unsigned)((fixed + (size_t)st * per_stage + 127) & ~(size_t)127);
     return LB_OK;
@@ -83,6 +88,7 @@ LB_API int lb_gemv_int4_fused(lb_ctx* c, uint64_t qweight, uint64_t scales, uint
     p.x_mode = x_mode; p.y_mode = y_mode;
     p.eps = eps;
     p.stages = g.stages;
+    { const char* e = getenv("LB_GEMV_DBG"); p.dbg = e ? atoi(e) : 0; }
     /* qweight viewed as [N/32 column blocks][K/8 packed rows][32 columns] so that ONE tiled load
      * brings a whole stage: box = 8 column blocks x 16 rows x 32 columns, laid down as eight
      * consecutive 2 KB boxes with the 128-byte swizzle.  Parts of the box past the matrix
@@ -99,8 +105,8 @@ LB_API int lb_gemv_int4_fused(lb_ctx* c, uint64_t qweight, uint64_t scales, uint
         memcpy(p.tmap, &tm, sizeof tm);
     }
     void* params[] = {&p};
-    return lb_launch_cluster(c, LBK_gemv_int4_w256, (unsigned)g.tiles, (unsigned)g.ksplit, 1, GEMV_THREADS, g.smem, params, 1,
-                             (unsigned)g.ksplit);
+    return lb_launch_cluster(c, LBK_gemv_int4_w256, (unsigned)g.tiles, (unsigned)g.ksplit, 1, GEMV_THREADS, g.smem, params, !(p.dbg & 32),
+                             (p.dbg & 16) ? 1u : (unsigned)g.ksplit);
 }
 
 LB_API int lb_gemv_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y, int K,

@@ -55,7 +55,8 @@ __device__ __forceinline__ void norm_rope_256(float v, const uint16_t* w, float*
 }
 
 template <int G>
-__device__ __forceinline__ void attn_body(const lb_attn_params& p, float* sm) {
+__device__ __forceinline__ void attn_body(const lb_attn_params& p0, float* sm) {
+    lb_attn_params p = p0;
     const int kv = blockIdx.x, split = blockIdx.y;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     float* q_s = sm;                      // [G][256]
@@ -68,6 +69,7 @@ __device__ __forceinline__ void attn_body(const lb_attn_params& p, float* sm) {
     __shared__ uint32_t s_ticket;
 
     pdl_wait();
+    if (p.pos_ptr) p.pos = p.pos_ptr[0];
     const bool last = split == p.splits - 1;
     const float LOG2E = 1.4426950408889634f;
     const float qscale = rsqrtf((float)AT_D) * LOG2E; // scores kept in log2 units

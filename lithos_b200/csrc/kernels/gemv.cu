@@ -165,10 +165,14 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
     const int dig_words = (digit_row_word(p.groups_per_split * LB_GEMV_ROWS) + 3) & ~3;
     int* xsum = reinterpret_cast<int*>(xdig + dig_words);                 // [groups] integer sum of the group's x
     float* red = reinterpret_cast<float*>(xsum + ((p.groups_per_split + 3) & ~3)); // [256] + 40
-    uint64_t* full = reinterpret_cast<uint64_t*>(red + LB_GEMV_TILE_N + 40);
+    __half* sc_s = reinterpret_cast<__half*>(red + LB_GEMV_TILE_N + 40);           // [groups][256] group scales
+    uint32_t* zr_s = reinterpret_cast<uint32_t*>(sc_s + (size_t)p.groups_per_split * LB_GEMV_TILE_N); // [groups][32]
+    uint64_t* full = reinterpret_cast<uint64_t*>(zr_s + (size_t)p.groups_per_split * (LB_GEMV_TILE_N / 8));
     uint64_t* empty = full + S;
     __shared__ uint32_t s_bad;
 
+    unsigned long long* tl = (p.dbg & 256) ? reinterpret_cast<unsigned long long*>(p.x_out) + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
+    if (tl && tid == 0) tl[0] = globaltimer_ns();
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&full[s], 1);
@@ -178,14 +182,14 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
         mbar_fence_init();
     }
     __syncthreads();
-    // Let the next kernel in the stream become resident now: it only prefetches its own weights
-    // until this grid has completed (its consumers sit in griddepcontrol.wait), which keeps the
-    // HBM pipe busy across the kernel boundary.
-    pdl_launch_dependents();
 
     if (warp == GEMV_CONSUMER_WARPS) {
         // ---------------- producer: one elected lane streams stages into the ring ----------------
         // Weights never change, so this starts before griddepcontrol.wait.
+        // Small requests first: once the bulk stream is queued, any other load waits behind
+        // megabytes of weight traffic, so the consumers queue their scale / zero-point lines
+        // before this warp issues the first bulk copy.
+        asm volatile("bar.sync 2, %0;" ::"n"(GEMV_CONSUMERS + 32) : "memory");
         if (lane == 0) {
             const uint64_t pol = l2_policy_evict_first();
             for (int u = 0; u < n_groups; ++u) {
@@ -207,7 +211,30 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float unit = 1.0f; // value of one integer step of the quantised activations (2^-shift)
     if (warp < GEMV_CONSUMER_WARPS) {
-        pdl_wait(); // x (and y for accumulate mode) come from the previous kernel
+        // scales and zero-points of the whole K slice into shared memory; they are weights, so
+        // this too runs ahead of griddepcontrol.wait
+        for (int i = tid; i < n_groups * 5; i += GEMV_CONSUMERS) { // per group: 4 lines of scales, 1 of zero-points
+            const int g = i / 5, l = i % 5;
+            const void* a = l < 4 ? static_cast<const void*>(p.scales + (size_t)(g0 + g) * p.N + n0 + l * 64)
+                                  : static_cast<const void*>(p.qzeros ? p.qzeros + (size_t)(g0 + g) * (p.N >> 3) + (n0 >> 3) : nullptr);
+            if (a && l * 64 < ncols) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+        }
+        asm volatile("bar.arrive 2, %0;" ::"n"(GEMV_CONSUMERS + 32) : "memory");
+        for (int i = tid; i < n_groups * (LB_GEMV_TILE_N / 2); i += GEMV_CONSUMERS) {
+            const int g = i / (LB_GEMV_TILE_N / 2), c2 = i % (LB_GEMV_TILE_N / 2); // pair of columns
+            uint32_t v = 0u;
+            if (2 * c2 < ncols) v = __ldg(reinterpret_cast<const uint32_t*>(p.scales + (size_t)(g0 + g) * p.N + n0) + c2);
+            reinterpret_cast<uint32_t*>(sc_s)[i] = v;
+        }
+        for (int i = tid; i < n_groups * (LB_GEMV_TILE_N / 8); i += GEMV_CONSUMERS) {
+            const int g = i / (LB_GEMV_TILE_N / 8), w = i % (LB_GEMV_TILE_N / 8);
+            uint32_t v = 0x88888888u;
+            if (p.qzeros && 8 * w < ncols) v = __ldg(p.qzeros + (size_t)(g0 + g) * (p.N >> 3) + (n0 >> 3) + w);
+            zr_s[i] = v;
+        }
+        if (tl && tid == 0) tl[1] = globaltimer_ns();
+        if (!(p.dbg & 8)) pdl_wait(); // x (and y for accumulate mode) come from the previous kernel
+        if (tl && tid == 0) tl[2] = globaltimer_ns();
         const int rows = n_groups * LB_GEMV_ROWS;
         const int row0 = g0 * LB_GEMV_ROWS; // first packed row of this split
 
@@ -234,11 +261,20 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
             consumer_bar();
         }
         float vmax = 0.f;
-        for (int rb = 0; rb < rows; rb += GEMV_CONSUMERS) {
+        for (int rb = 0; rb < ((p.dbg & 2) ? 0 : rows); rb += GEMV_CONSUMERS) {
             float v[8];
-            load_x_row(p, (row0 + rb + tid) * 8, rb + tid < rows, rinv, v);
+            const int r = rb + tid;
+            load_x_row(p, (row0 + r) * 8, r < rows, rinv, v);
 #pragma unroll
             for (int j = 0; j < 8; ++j) vmax = fmaxf(vmax, fabsf(v[j]));
+            if (r < rows) { // parked as fp16 in the row's own digit slot until the scale is known
+                __half2 pk[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
+                                 __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
+                uint32_t* dst = xdig + digit_row_word(r);
+                const uint32_t* pw = reinterpret_cast<const uint32_t*>(pk);
+                *reinterpret_cast<uint2*>(dst) = make_uint2(pw[0], pw[1]);
+                *reinterpret_cast<uint2*>(dst + 2) = make_uint2(pw[2], pw[3]);
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
@@ -250,11 +286,23 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
         if (vmax > 0.f && vmax < 3.0e38f) shift = 21 - (int)((__float_as_uint(vmax) >> 23) & 0xffu) + 127;
         const float qscale = __uint_as_float((uint32_t)(127 + shift) << 23); // 2^shift (|shift| < 60 for fp16 data)
         unit = __uint_as_float((uint32_t)(127 - shift) << 23);
-        for (int rb = 0; rb < rows; rb += GEMV_CONSUMERS) {
+        for (int rb = 0; rb < ((p.dbg & 2) ? 0 : rows); rb += GEMV_CONSUMERS) {
             const int r = rb + tid;
             const bool live = r < rows;
             float v[8];
-            load_x_row(p, (row0 + r) * 8, live, rinv, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
+            if (live) { // the same thread parked this row above
+                const uint32_t* src = xdig + digit_row_word(r);
+                const uint2 p0 = *reinterpret_cast<const uint2*>(src), p1 = *reinterpret_cast<const uint2*>(src + 2);
+                const uint32_t pw[4] = {p0.x, p0.y, p1.x, p1.y};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pw[j]));
+                    v[2 * j] = f.x;
+                    v[2 * j + 1] = f.y;
+                }
+            }
             int X[8], rs = 0;
             uint32_t ev[3] = {0u, 0u, 0u}, od[3] = {0u, 0u, 0u};
 #pragma unroll
@@ -278,7 +326,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
 #pragma unroll
                 for (int d = 0; d < 3; ++d) *reinterpret_cast<uint2*>(dst + 2 * d) = make_uint2(ev[d], od[d]);
                 if ((lane & 15) == 0) xsum[r >> 4] = rs;
-                if (p.x_out && tile == 0) {
+                if (p.x_out && tile == 0 && !(p.dbg & 256)) {
                     __half2 pl[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
                                      __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
                     *reinterpret_cast<uint4*>(p.x_out + (row0 + r) * 8) = *reinterpret_cast<uint4*>(pl);
@@ -293,33 +341,29 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
         //     8*(e>>1) + 2*ft + (e&1), chunk fg: the 8 lanes of a quarter-warp then hit 8 different
         //     chunks (no bank conflict), and all lanes with the same ft share one packed row, as
         //     the MMA k-slots need.  Lanes fg = 0,1,2 supply the three digit planes as B columns.
+        if (tl && tid == 0) tl[3] = globaltimer_ns();
         const int cbase = warp * 64;                  // this warp's first column inside the tile
         const bool live0 = cbase < ncols, live1 = cbase + 32 < ncols; // N % 32 == 0: a box is all valid or all past N
-        const int col0 = n0 + cbase + fg * 4;         // lane's 4 columns in box 0; box 1 is 32 further
-        const __half* sc_ptr = reinterpret_cast<const __half*>(p.scales) + col0;
-        const uint32_t* qz_ptr = p.qzeros ? p.qzeros + (col0 >> 3) : nullptr;
         // lane ft holds B columns 2ft, 2ft+1 of the result: ft=0 digits 0 and 1, ft=1 digit 2
         const float lane_mul = ft == 0 ? 1.0f : (ft == 1 ? 65536.0f : 0.0f);
         const bool has_digits = fg < 3;
         for (int u = 0; u < n_groups; ++u) {
             const int s = u % S;
-            uint2 sraw[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};
-            uint32_t zw[2] = {0x88888888u, 0x88888888u};
-            // issued before the wait, used after the MMAs
-            if (live0) sraw[0] = __ldg(reinterpret_cast<const uint2*>(sc_ptr + (size_t)(g0 + u) * p.N));
-            if (live1) sraw[1] = __ldg(reinterpret_cast<const uint2*>(sc_ptr + (size_t)(g0 + u) * p.N + 32));
-            if (qz_ptr) {
-                if (live0) zw[0] = __ldg(qz_ptr + (size_t)(g0 + u) * (p.N >> 3));
-                if (live1) zw[1] = __ldg(qz_ptr + (size_t)(g0 + u) * (p.N >> 3) + 4);
-            }
+            uint2 sraw[2];
+            uint32_t zw[2];
+            sraw[0] = *reinterpret_cast<const uint2*>(sc_s + u * LB_GEMV_TILE_N + cbase + fg * 4);
+            sraw[1] = *reinterpret_cast<const uint2*>(sc_s + u * LB_GEMV_TILE_N + cbase + 32 + fg * 4);
+            zw[0] = zr_s[u * (LB_GEMV_TILE_N / 8) + ((cbase + fg * 4) >> 3)];
+            zw[1] = zr_s[u * (LB_GEMV_TILE_N / 8) + ((cbase + 32 + fg * 4) >> 3)];
             if (!mbar_wait(&full[s], (u / S) & 1)) {
                 if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); s_bad = 1; }
                 break;
             }
+            if (tl && tid == 0 && u == 0) tl[4] = globaltimer_ns();
             int d[2][2][4]; // [box][column pair][fragment]
 #pragma unroll
             for (int i = 0; i < 16; ++i) (&d[0][0][0])[i] = 0;
-            if (live0) {
+            if (live0 && !(p.dbg & 1)) {
                 const unsigned char* box = smem + (size_t)s * GEMV_STAGE_BYTES + (warp * 2) * GEMV_BOX_BYTES;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -343,7 +387,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
             // is B column 2ft (row g / g+8), element 1/3 is B column 2ft+1: digit d and d+1.
             const float xs_f = ft == 0 ? (float)xsum[u] : 0.f;
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
+            for (int b = 0; b < ((p.dbg & 128) ? 0 : 2); ++b) {
                 const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[b].x));
                 const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[b].y));
                 const uint32_t z = zw[b] >> ((fg & 1) * 16);
@@ -357,6 +401,8 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
                 }
             }
         }
+        if (tl && tid == 0) tl[5] = globaltimer_ns();
+        if (!(p.dbg & 64)) pdl_launch_dependents(); // the next kernel may become resident while this one reduces
         // add the digit planes held by the four ft lanes (fixed order), scale back to x units
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -375,7 +421,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
     //     of ranks 0,1,2,... in that order out of their shared memory ---
     float v0 = 0.f, v1 = 0.f; // columns tid and tid + 128 (the block has 160 threads, the tile 256 columns)
     const bool owner = tid < 128;
-    if (p.ksplit > 1) {
+    if (p.ksplit > 1 && !(p.dbg & 4)) {
         cluster_sync_all();
         if (cluster_ctarank() == 0 && owner)
             for (uint32_t r = 0; r < (uint32_t)p.ksplit; ++r) {
@@ -390,6 +436,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
     }
 
     // --- epilogue ---
+    if (tl && tid == 0) tl[6] = globaltimer_ns();
     if (s_bad) return;
     if (p.y_mode == LB_Y_SWIGLU_F16) {
         // columns come in interleaved 64-wide (gate, up) blocks: [0,64) gate, [64,128) up, ...

@@ -47,6 +47,7 @@ typedef struct {
     int32_t ksplit;           /* gridDim.y = cluster size along y */
     int32_t groups_per_split; /* ceil(K/128 / ksplit) */
     int32_t stages;           /* TMA ring depth */
+    int32_t dbg;              /* TEMP ablation flags */
     int32_t x_mode, y_mode;
     float eps;
 } lb_gemv_params;
@@ -85,6 +86,23 @@ typedef struct {
     int32_t n;
 } lb_decay_params;
 
+/* ---- whole DeltaNet mixer of one layer (between the qkvz projection and the out projection) */
+typedef struct {
+    const float* qkvz;       /* fp32 [2*HK*128 + 2*HV*128]: q | k | v | z from the fused projection */
+    const uint16_t* xn;      /* fp16 [hidden]: the normalised layer input (as the projection used it) */
+    const uint16_t* proj_a;  /* bf16 [HV, hidden] in_proj_a */
+    const uint16_t* proj_b;  /* bf16 [HV, hidden] in_proj_b */
+    const float* a_log;      /* fp32 [HV] */
+    const uint16_t* dt_bias; /* bf16 [HV] */
+    const uint16_t* conv_w;  /* bf16 [4, C] planar, tap 0 = current token; C = 2*HK*128 + HV*128 */
+    float* conv_ring;        /* fp32 [4, C]: slot (pos & 3) receives the current token's pre-conv values */
+    float* state;            /* fp32 [HV,128,128] */
+    float* out;              /* fp32 [HV,128] read-out (before the per-head norm and z gate) */
+    const int* pos;          /* device int: position of the token being decoded */
+    int32_t HV, HK, hidden;
+    int32_t h0;              /* first global value head of this shard (tensor parallel), for nothing but clarity */
+} lb_dn_layer_params;
+
 /* ---- GQA decode attention ------------------------------------------------- */
 typedef struct {
     const void* q;        /* [HQ,256] bf16 or fp32 (raw, before norm) */
@@ -98,6 +116,7 @@ typedef struct {
     float* out;           /* fp32 [HQ,256] */
     float* scratch;       /* split partials: [HKV][splits][G][(256 acc) + m + l] */
     uint32_t* counters;   /* one per kv head, zero between launches */
+    const int* pos_ptr;   /* when non-NULL the position is read from device memory (graph replay) */
     int32_t pos;          /* position of the new token; rows [0,pos] are attended */
     int32_t HQ, HKV;
     int32_t splits;
