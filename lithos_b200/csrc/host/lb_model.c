@@ -47,14 +47,16 @@ struct lb_model {
     CUdeviceptr embed, lm_head, final_norm;
     int globals_loaded;
     /* activations */
-    CUdeviceptr X, xn, in_out, mix_out, mlp_m, logits, d_token, d_pos, d_next;
+    CUdeviceptr X, xn, in_out, mix_out, mlp_m, logits, d_token, d_pos, d_next, cand_val, cand_idx;
     int* h_next; /* pinned */
     uint64_t weight_bytes;
     lb_graph* graph;
     int step_kernels;
 };
 
-extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps);
+extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps,
+                           uint64_t part_val, uint64_t part_idx);
+extern int lb_dense_ctas(lb_ctx* c, int N);
 extern int lb_attn_splits(lb_ctx* c, int pos, int HKV);
 extern unsigned lb_attn_smem(int G);
 
@@ -106,6 +108,8 @@ LB_API int lb_model_create(lb_ctx* c, const lb_model_cfg* cfg, int tp_rank, int 
     LB_TRY(dalloc(m, &m->d_token, 16));
     LB_TRY(dalloc(m, &m->d_pos, 16));
     LB_TRY(dalloc(m, &m->d_next, 16));
+    LB_TRY(dalloc(m, &m->cand_val, (size_t)lb_dense_ctas(c, cfg->vocab) * 4));
+    LB_TRY(dalloc(m, &m->cand_idx, (size_t)lb_dense_ctas(c, cfg->vocab) * 4));
     LB_CU(c, lb_drv.MemHostAlloc((void**)&m->h_next, 64, 0));
     for (int l = 0; l < cfg->n_layers; l++) {
         layer_t* L = &m->L[l];
@@ -454,10 +458,11 @@ static int issue_step(lb_model* m) {
         LB_TRY(q4_gemv(m, &L->w_down, m->mlp_m, m->X, LB_X_F16, LB_Y_F32_ACCUM, 0, 0, 0));
     }
     if (!m->globals_loaded) return lb_fail(c, LB_ERR_STATE, "model: globals have no weights");
-    LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, cfg->vocab, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps));
+    LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, cfg->vocab, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps,
+                           m->cand_val, m->cand_idx));
     {
-        int n = cfg->vocab;
-        void* params[] = {&m->logits, &n, &m->d_next, &m->d_token, &m->d_pos};
+        int n = lb_dense_ctas(c, cfg->vocab); /* one (value, row) candidate per LM-head CTA */
+        void* params[] = {&m->cand_val, &n, &m->d_next, &m->d_token, &m->d_pos, &m->cand_idx};
         LB_TRY(lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1));
     }
     m->step_kernels = (int)(c->launches - launches0);
@@ -521,7 +526,7 @@ LB_API void lb_model_destroy(lb_model* m) {
         lb_drv.StreamSynchronize(c->stream);
         if (m->graph) lb_graph_destroy(c, m->graph);
         CUdeviceptr g[] = {m->embed, m->lm_head, m->final_norm, m->X, m->xn, m->in_out, m->mix_out, m->mlp_m, m->logits,
-                           m->d_token, m->d_pos, m->d_next};
+                           m->d_token, m->d_pos, m->d_next, m->cand_val, m->cand_idx};
         for (size_t i = 0; i < sizeof g / sizeof g[0]; i++) if (g[i]) lb_drv.MemFree(g[i]);
         for (int l = 0; m->L && l < m->cfg.n_layers; l++) {
             layer_t* L = &m->L[l];

@@ -27,7 +27,6 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
     int ks = slots / g->tiles;
     if (ks < 1) ks = 1;
     if (ks > LB_GEMV_MAX_SPLITS) ks = LB_GEMV_MAX_SPLITS;
-    { const char* e = getenv("LB_GEMV_KSPLIT"); if (e) ks = atoi(e); }
     if (ks > groups) ks = groups;
     g->gps = (groups + ks - 1) / ks;
     g->ksplit = (groups + g->gps - 1) / g->gps;
@@ -37,12 +36,11 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
     size_t dig_words = (size_t)((6 * rows + 2 * (rows >> 2) + 3) & ~3);
     size_t fixed = 1024 + dig_words * 4 + (size_t)((g->gps + 3) & ~3) * 4 + (LB_GEMV_TILE_N + 40) * 4 +
                    (size_t)g->gps * (LB_GEMV_TILE_N * 2 + LB_GEMV_TILE_N / 2); /* + group scales and zero-points */
+    fixed += 16; /* the scale-box mbarrier */
     size_t per_stage = LB_GEMV_STAGE_BYTES + 16; /* stage + its two mbarriers */
     size_t sm_total = (size_t)c->max_smem_optin + 1024; /* shared memory of one SM */
     int st = 0;
-    int per_sm0 = 4;
-    { const char* e = getenv("LB_GEMV_PERSM"); if (e) per_sm0 = atoi(e); }
-    for (int per_sm = per_sm0; per_sm >= 1 && st < 2; per_sm >>= 1) {
+    for (int per_sm = 4; per_sm >= 1 && st < 2; per_sm >>= 1) {
         size_t budget = sm_total / per_sm - 1024;
         if (budget > (size_t)c->max_smem_optin) budget = (size_t)c->max_smem_optin;
         st = budget > fixed ? (int)((budget - fixed) / per_stage) : 0;
@@ -50,7 +48,6 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
     if (st < 1) return lb_fail(c, LB_ERR_INVALID, "int4 GEMV: K slice of %d groups does not fit shared memory", g->gps);
     if (st > 6) st = 6;
     if (st > g->gps) st = g->gps;
-    { const char* e = getenv("LB_GEMV_STAGES"); if (e && atoi(e) < st) st = atoi(e); }
     g->stages = st;
     g->smem = (unsigned)((fixed + (size_t)st * per_stage + 127) & ~(size_t)127);
     return LB_OK;
@@ -88,7 +85,6 @@ LB_API int lb_gemv_int4_fused(lb_ctx* c, uint64_t qweight, uint64_t scales, uint
     p.x_mode = x_mode; p.y_mode = y_mode;
     p.eps = eps;
     p.stages = g.stages;
-    { const char* e = getenv("LB_GEMV_DBG"); p.dbg = e ? atoi(e) : 0; }
     /* qweight viewed as [N/32 column blocks][K/8 packed rows][32 columns] so that ONE tiled load
      * brings a whole stage: box = 8 column blocks x 16 rows x 32 columns, laid down as eight
      * consecutive 2 KB boxes with the 128-byte swizzle.  Parts of the box past the matrix
@@ -103,10 +99,26 @@ LB_API int lb_gemv_int4_fused(lb_ctx* c, uint64_t qweight, uint64_t scales, uint
                                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
         memcpy(p.tmap, &tm, sizeof tm);
+        cuuint64_t sdims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 128)};
+        cuuint64_t sstr[1] = {(cuuint64_t)N * 2};
+        cuuint32_t sbox[2] = {LB_GEMV_TILE_N, (cuuint32_t)g.gps};
+        LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)scales, sdims, sstr, sbox, estr,
+                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+        memcpy(p.tmap_sc, &tm, sizeof tm);
+        if (qzeros) {
+            cuuint64_t zdims[2] = {(cuuint64_t)(N / 8), (cuuint64_t)(K / 128)};
+            cuuint64_t zstr[1] = {(cuuint64_t)(N / 8) * 4};
+            cuuint32_t zbox[2] = {LB_GEMV_TILE_N / 8, (cuuint32_t)g.gps};
+            LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)qzeros, zdims, zstr, zbox,
+                                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+            memcpy(p.tmap_zr, &tm, sizeof tm);
+        }
     }
     void* params[] = {&p};
-    return lb_launch_cluster(c, LBK_gemv_int4_w256, (unsigned)g.tiles, (unsigned)g.ksplit, 1, GEMV_THREADS, g.smem, params, !(p.dbg & 32),
-                             (p.dbg & 16) ? 1u : (unsigned)g.ksplit);
+    return lb_launch_cluster(c, LBK_gemv_int4_w256, (unsigned)g.tiles, (unsigned)g.ksplit, 1, GEMV_THREADS, g.smem, params, 1,
+                             (unsigned)g.ksplit);
 }
 
 LB_API int lb_gemv_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y, int K,
@@ -189,22 +201,26 @@ LB_API int lb_gptq_unpack(lb_ctx* c, uint64_t qweight, uint64_t q_out, int K, in
     return lb_launch(c, LBK_gptq_unpack_u8, (unsigned)((N + 255) / 256), (unsigned)(K / 8), 1, 256, 0, params, 0);
 }
 
-int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps) {
+int lb_dense_ctas(lb_ctx* c, int N) {
+    int ctas = (N + 7) / 8, cap = c->sm_count * 8; /* each CTA strides over rows, 8 warps = 8 rows at a time */
+    return ctas > cap ? cap : ctas;
+}
+
+int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps,
+                    uint64_t part_val, uint64_t part_idx) {
     if (!c || !w || !x || !y || K % 8 || N <= 0) return lb_fail(c, LB_ERR_INVALID, "dense bf16 GEMV: bad argument");
     lb_dense_params p;
     memset(&p, 0, sizeof p);
     p.w = (const uint16_t*)w; p.x = (const void*)x; p.y = (float*)y; p.norm_w = (const void*)norm_w;
     p.N = N; p.K = K; p.x_mode = x_mode; p.eps = eps;
-    int rows_per_cta = 8;
-    int ctas = (N + rows_per_cta - 1) / rows_per_cta;
-    int cap = c->sm_count * 8; /* persistent-ish: each CTA strides over rows */
-    if (ctas > cap) ctas = cap;
+    p.part_val = (float*)part_val; p.part_idx = (int32_t*)part_idx;
+    int ctas = lb_dense_ctas(c, N);
     void* params[] = {&p};
     return lb_launch(c, LBK_dense_bf16_gemv, (unsigned)ctas, 1, 1, 256, (unsigned)(K * 4 + 256), params, 1);
 }
 
 LB_API int lb_dense_bf16_gemv(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_is_f32) {
-    return lb_dense_launch(c, w, x, y, N, K, x_is_f32 ? LB_X_F32 : LB_X_F16, 0, 1e-6f);
+    return lb_dense_launch(c, w, x, y, N, K, x_is_f32 ? LB_X_F32 : LB_X_F16, 0, 1e-6f, 0, 0);
 }
 
 LB_API int lb_deltanet_step(lb_ctx* c, uint64_t state, uint64_t q, uint64_t k, uint64_t v, uint64_t z, uint64_t g,
@@ -229,10 +245,10 @@ LB_API int lb_decay_gate(lb_ctx* c, uint64_t a, uint64_t a_log, uint64_t dt_bias
     return lb_launch(c, LBK_decay_gate_beta, (unsigned)((n + 127) / 128), 1, 1, 128, 0, params, 1);
 }
 
-/* number of position slices: enough CTAs to fill the GPU, at least 256 rows each */
+/* number of position slices: enough CTAs to fill the GPU twice, at least 64 rows each */
 int lb_attn_splits(lb_ctx* c, int pos, int HKV) {
     int want = (2 * c->sm_count + HKV - 1) / HKV;
-    int by_len = pos / 256;
+    int by_len = pos / 64;
     int s = want < by_len ? want : by_len;
     if (s < 1) s = 1;
     if (s > 64) s = 64;
@@ -276,7 +292,7 @@ LB_API int lb_rmsnorm(lb_ctx* c, uint64_t x, uint64_t res, uint64_t w, uint64_t 
 LB_API int lb_argmax(lb_ctx* c, uint64_t x, int n, uint64_t out_idx) {
     if (!c || !x || !out_idx || n <= 0) return lb_fail(c, LB_ERR_INVALID, "lb_argmax: bad argument");
     uint64_t zero = 0;
-    void* params[] = {&x, &n, &out_idx, &zero, &zero};
+    void* params[] = {&x, &n, &out_idx, &zero, &zero, &zero};
     return lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1);
 }
 

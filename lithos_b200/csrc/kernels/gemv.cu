@@ -58,6 +58,14 @@ __device__ __forceinline__ void tma_load_stage(uint32_t dst_smem, const void* tm
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap, int x, int y, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst_smem),
+        "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+
 // D(16x8, s32) += A(16x32, u8) * B(32x8, s8)
 __device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1) {
@@ -161,23 +169,23 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
     // shared-memory carve-up; the swizzled boxes need 1024-byte alignment
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint32_t* xdig = reinterpret_cast<uint32_t*>(smem + (size_t)S * GEMV_STAGE_BYTES); // digit table of this K slice
+    __half* sc_s = reinterpret_cast<__half*>(smem + (size_t)S * GEMV_STAGE_BYTES);                     // [groups][256] group scales
+    uint32_t* zr_s = reinterpret_cast<uint32_t*>(sc_s + (size_t)p.groups_per_split * LB_GEMV_TILE_N); // [groups][32] zero-point words
+    uint32_t* xdig = zr_s + (size_t)p.groups_per_split * (LB_GEMV_TILE_N / 8);                         // digit table of this K slice
     const int dig_words = (digit_row_word(p.groups_per_split * LB_GEMV_ROWS) + 3) & ~3;
     int* xsum = reinterpret_cast<int*>(xdig + dig_words);                 // [groups] integer sum of the group's x
     float* red = reinterpret_cast<float*>(xsum + ((p.groups_per_split + 3) & ~3)); // [256] + 40
-    __half* sc_s = reinterpret_cast<__half*>(red + LB_GEMV_TILE_N + 40);           // [groups][256] group scales
-    uint32_t* zr_s = reinterpret_cast<uint32_t*>(sc_s + (size_t)p.groups_per_split * LB_GEMV_TILE_N); // [groups][32]
-    uint64_t* full = reinterpret_cast<uint64_t*>(zr_s + (size_t)p.groups_per_split * (LB_GEMV_TILE_N / 8));
+    uint64_t* full = reinterpret_cast<uint64_t*>(red + LB_GEMV_TILE_N + 40);
     uint64_t* empty = full + S;
+    uint64_t* aux = empty + S; // completion of the scale / zero-point boxes
     __shared__ uint32_t s_bad;
 
-    unsigned long long* tl = (p.dbg & 256) ? reinterpret_cast<unsigned long long*>(p.x_out) + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
-    if (tl && tid == 0) tl[0] = globaltimer_ns();
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], GEMV_CONSUMER_WARPS);
         }
+        mbar_init(aux, 1);
         s_bad = 0;
         mbar_fence_init();
     }
@@ -186,12 +194,14 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
     if (warp == GEMV_CONSUMER_WARPS) {
         // ---------------- producer: one elected lane streams stages into the ring ----------------
         // Weights never change, so this starts before griddepcontrol.wait.
-        // Small requests first: once the bulk stream is queued, any other load waits behind
-        // megabytes of weight traffic, so the consumers queue their scale / zero-point lines
-        // before this warp issues the first bulk copy.
-        asm volatile("bar.sync 2, %0;" ::"n"(GEMV_CONSUMERS + 32) : "memory");
         if (lane == 0) {
             const uint64_t pol = l2_policy_evict_first();
+            // Small requests first: once the bulk stream is queued, any other load waits behind
+            // megabytes of weight traffic.  The slice's scales and zero-points are two boxes.
+            const uint32_t sc_bytes = (uint32_t)p.groups_per_split * LB_GEMV_TILE_N * 2, zr_bytes = sc_bytes / 4;
+            mbar_arrive_expect_tx(aux, sc_bytes + (p.qzeros ? zr_bytes : 0u));
+            tma_load_2d(smem_u32(sc_s), p.tmap_sc, n0, g0, aux, pol);
+            if (p.qzeros) tma_load_2d(smem_u32(zr_s), p.tmap_zr, n0 >> 3, g0, aux, pol);
             for (int u = 0; u < n_groups; ++u) {
                 const int s = u % S;
                 if (u >= S && !mbar_wait(&empty[s], ((u / S) - 1) & 1)) {
@@ -211,30 +221,9 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float unit = 1.0f; // value of one integer step of the quantised activations (2^-shift)
     if (warp < GEMV_CONSUMER_WARPS) {
-        // scales and zero-points of the whole K slice into shared memory; they are weights, so
-        // this too runs ahead of griddepcontrol.wait
-        for (int i = tid; i < n_groups * 5; i += GEMV_CONSUMERS) { // per group: 4 lines of scales, 1 of zero-points
-            const int g = i / 5, l = i % 5;
-            const void* a = l < 4 ? static_cast<const void*>(p.scales + (size_t)(g0 + g) * p.N + n0 + l * 64)
-                                  : static_cast<const void*>(p.qzeros ? p.qzeros + (size_t)(g0 + g) * (p.N >> 3) + (n0 >> 3) : nullptr);
-            if (a && l * 64 < ncols) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-        }
-        asm volatile("bar.arrive 2, %0;" ::"n"(GEMV_CONSUMERS + 32) : "memory");
-        for (int i = tid; i < n_groups * (LB_GEMV_TILE_N / 2); i += GEMV_CONSUMERS) {
-            const int g = i / (LB_GEMV_TILE_N / 2), c2 = i % (LB_GEMV_TILE_N / 2); // pair of columns
-            uint32_t v = 0u;
-            if (2 * c2 < ncols) v = __ldg(reinterpret_cast<const uint32_t*>(p.scales + (size_t)(g0 + g) * p.N + n0) + c2);
-            reinterpret_cast<uint32_t*>(sc_s)[i] = v;
-        }
-        for (int i = tid; i < n_groups * (LB_GEMV_TILE_N / 8); i += GEMV_CONSUMERS) {
-            const int g = i / (LB_GEMV_TILE_N / 8), w = i % (LB_GEMV_TILE_N / 8);
-            uint32_t v = 0x88888888u;
-            if (p.qzeros && 8 * w < ncols) v = __ldg(p.qzeros + (size_t)(g0 + g) * (p.N >> 3) + (n0 >> 3) + w);
-            zr_s[i] = v;
-        }
-        if (tl && tid == 0) tl[1] = globaltimer_ns();
-        if (!(p.dbg & 8)) pdl_wait(); // x (and y for accumulate mode) come from the previous kernel
-        if (tl && tid == 0) tl[2] = globaltimer_ns();
+        if (!p.qzeros) // zero-point 8 everywhere
+            for (int i = tid; i < n_groups * (LB_GEMV_TILE_N / 8); i += GEMV_CONSUMERS) zr_s[i] = 0x88888888u;
+        pdl_wait(); // x (and y for accumulate mode) come from the previous kernel
         const int rows = n_groups * LB_GEMV_ROWS;
         const int row0 = g0 * LB_GEMV_ROWS; // first packed row of this split
 
@@ -261,7 +250,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
             consumer_bar();
         }
         float vmax = 0.f;
-        for (int rb = 0; rb < ((p.dbg & 2) ? 0 : rows); rb += GEMV_CONSUMERS) {
+        for (int rb = 0; rb < rows; rb += GEMV_CONSUMERS) {
             float v[8];
             const int r = rb + tid;
             load_x_row(p, (row0 + r) * 8, r < rows, rinv, v);
@@ -286,7 +275,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
         if (vmax > 0.f && vmax < 3.0e38f) shift = 21 - (int)((__float_as_uint(vmax) >> 23) & 0xffu) + 127;
         const float qscale = __uint_as_float((uint32_t)(127 + shift) << 23); // 2^shift (|shift| < 60 for fp16 data)
         unit = __uint_as_float((uint32_t)(127 - shift) << 23);
-        for (int rb = 0; rb < ((p.dbg & 2) ? 0 : rows); rb += GEMV_CONSUMERS) {
+        for (int rb = 0; rb < rows; rb += GEMV_CONSUMERS) {
             const int r = rb + tid;
             const bool live = r < rows;
             float v[8];
@@ -326,7 +315,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
 #pragma unroll
                 for (int d = 0; d < 3; ++d) *reinterpret_cast<uint2*>(dst + 2 * d) = make_uint2(ev[d], od[d]);
                 if ((lane & 15) == 0) xsum[r >> 4] = rs;
-                if (p.x_out && tile == 0 && !(p.dbg & 256)) {
+                if (p.x_out && tile == 0) {
                     __half2 pl[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
                                      __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
                     *reinterpret_cast<uint4*>(p.x_out + (row0 + r) * 8) = *reinterpret_cast<uint4*>(pl);
@@ -341,7 +330,9 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
         //     8*(e>>1) + 2*ft + (e&1), chunk fg: the 8 lanes of a quarter-warp then hit 8 different
         //     chunks (no bank conflict), and all lanes with the same ft share one packed row, as
         //     the MMA k-slots need.  Lanes fg = 0,1,2 supply the three digit planes as B columns.
-        if (tl && tid == 0) tl[3] = globaltimer_ns();
+        if (!mbar_wait(aux, 0)) {
+            if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); s_bad = 1; }
+        }
         const int cbase = warp * 64;                  // this warp's first column inside the tile
         const bool live0 = cbase < ncols, live1 = cbase + 32 < ncols; // N % 32 == 0: a box is all valid or all past N
         // lane ft holds B columns 2ft, 2ft+1 of the result: ft=0 digits 0 and 1, ft=1 digit 2
@@ -359,11 +350,10 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
                 if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); s_bad = 1; }
                 break;
             }
-            if (tl && tid == 0 && u == 0) tl[4] = globaltimer_ns();
             int d[2][2][4]; // [box][column pair][fragment]
 #pragma unroll
             for (int i = 0; i < 16; ++i) (&d[0][0][0])[i] = 0;
-            if (live0 && !(p.dbg & 1)) {
+            if (live0) {
                 const unsigned char* box = smem + (size_t)s * GEMV_STAGE_BYTES + (warp * 2) * GEMV_BOX_BYTES;
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -387,7 +377,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
             // is B column 2ft (row g / g+8), element 1/3 is B column 2ft+1: digit d and d+1.
             const float xs_f = ft == 0 ? (float)xsum[u] : 0.f;
 #pragma unroll
-            for (int b = 0; b < ((p.dbg & 128) ? 0 : 2); ++b) {
+            for (int b = 0; b < 2; ++b) {
                 const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[b].x));
                 const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[b].y));
                 const uint32_t z = zw[b] >> ((fg & 1) * 16);
@@ -401,8 +391,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
                 }
             }
         }
-        if (tl && tid == 0) tl[5] = globaltimer_ns();
-        if (!(p.dbg & 64)) pdl_launch_dependents(); // the next kernel may become resident while this one reduces
+        pdl_launch_dependents(); // the next kernel may become resident while this one reduces
         // add the digit planes held by the four ft lanes (fixed order), scale back to x units
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -421,7 +410,7 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
     //     of ranks 0,1,2,... in that order out of their shared memory ---
     float v0 = 0.f, v1 = 0.f; // columns tid and tid + 128 (the block has 160 threads, the tile 256 columns)
     const bool owner = tid < 128;
-    if (p.ksplit > 1 && !(p.dbg & 4)) {
+    if (p.ksplit > 1) {
         cluster_sync_all();
         if (cluster_ctarank() == 0 && owner)
             for (uint32_t r = 0; r < (uint32_t)p.ksplit; ++r) {
@@ -436,7 +425,6 @@ extern "C" __global__ void __launch_bounds__(GEMV_CONSUMERS + 32, 4) gemv_int4_w
     }
 
     // --- epilogue ---
-    if (tl && tid == 0) tl[6] = globaltimer_ns();
     if (s_bad) return;
     if (p.y_mode == LB_Y_SWIGLU_F16) {
         // columns come in interleaved 64-wide (gate, up) blocks: [0,64) gate, [64,128) up, ...
@@ -527,6 +515,8 @@ extern "C" __global__ void __launch_bounds__(256) dense_bf16_gemv(const __grid_c
     __syncthreads();
     pdl_launch_dependents();
     const int nwarps = blockDim.x >> 5;
+    float best_v = -INFINITY;
+    int best_i = 0x7fffffff;
     for (int n = blockIdx.x * nwarps + warp; n < p.N; n += gridDim.x * nwarps) {
         const uint4* wr = reinterpret_cast<const uint4*>(p.w + (size_t)n * p.K);
         float a0 = 0.f, a1 = 0.f;
@@ -545,5 +535,18 @@ extern "C" __global__ void __launch_bounds__(256) dense_bf16_gemv(const __grid_c
         }
         float t = warp_sum(a0 + a1);
         if (lane == 0) p.y[n] = t;
+        if (t > best_v || (t == best_v && n < best_i)) { best_v = t; best_i = n; }
+    }
+    if (p.part_val) { // this CTA's candidate for the arg-max: greater value, smaller row on ties
+        __syncthreads();
+        int* ri = reinterpret_cast<int*>(red + 16);
+        if (lane == 0) { red[warp] = best_v; ri[warp] = best_i; }
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < nwarps; ++w)
+                if (red[w] > best_v || (red[w] == best_v && ri[w] < best_i)) { best_v = red[w]; best_i = ri[w]; }
+            p.part_val[blockIdx.x] = best_v;
+            p.part_idx[blockIdx.x] = best_i;
+        }
     }
 }

@@ -34,6 +34,9 @@ enum {
 typedef struct {
     /* CUtensorMap over qweight viewed as [N/32][K/8][32] uint32: box 8 x 16 x 32, 128-byte swizzle */
     unsigned char tmap[128] __attribute__((aligned(64)));
+    /* scales as fp16 [K/128, N], box = groups_per_split x 256; qzeros as u32 [K/128, N/8], box = groups_per_split x 32 */
+    unsigned char tmap_sc[128] __attribute__((aligned(64)));
+    unsigned char tmap_zr[128] __attribute__((aligned(64)));
     const uint32_t* qweight; /* [K/8, N] */
     const uint16_t* scales;  /* fp16 [K/128, N] */
     const uint32_t* qzeros;  /* [K/128, N/8] or NULL: zero-point 8 */
@@ -47,7 +50,6 @@ typedef struct {
     int32_t ksplit;           /* gridDim.y = cluster size along y */
     int32_t groups_per_split; /* ceil(K/128 / ksplit) */
     int32_t stages;           /* TMA ring depth */
-    int32_t dbg;              /* TEMP ablation flags */
     int32_t x_mode, y_mode;
     float eps;
 } lb_gemv_params;
@@ -61,6 +63,8 @@ typedef struct {
     int32_t N, K;
     int32_t x_mode; /* LB_X_F16 | LB_X_F32 | LB_X_F32_RMSNORM */
     float eps;
+    float* part_val;  /* optional [gridDim.x]: largest y of the rows this CTA produced ... */
+    int32_t* part_idx; /* ... and its row (smallest row on ties), for the greedy-sampling reduction */
 } lb_dense_params;
 
 /* ---- gated DeltaNet step -------------------------------------------------- */

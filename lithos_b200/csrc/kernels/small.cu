@@ -20,8 +20,11 @@ extern "C" __global__ void embed_bf16(const uint16_t* __restrict__ table, const 
 // which is order-independent, so the answer does not depend on the schedule.
 // Also writes the winner into next_token (the next step's embed input) and
 // advances *pos when given.
+// cand_idx == NULL: x is the full vector and the index is the position; otherwise x[i] / cand_idx[i]
+// are per-CTA candidates (value, row) left by the LM-head kernel.
 extern "C" __global__ void __launch_bounds__(1024) argmax_f32(const float* __restrict__ x, int n, int* __restrict__ out_idx,
-                                                              int* __restrict__ next_token, int* __restrict__ pos) {
+                                                              int* __restrict__ next_token, int* __restrict__ pos,
+                                                              const int* __restrict__ cand_idx) {
     __shared__ float sv[32];
     __shared__ int si[32];
     pdl_wait();
@@ -29,7 +32,8 @@ extern "C" __global__ void __launch_bounds__(1024) argmax_f32(const float* __res
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float v = x[i];
-        if (v > bv) { bv = v; bi = i; } // ascending i per thread: first maximum kept
+        const int id = cand_idx ? cand_idx[i] : i;
+        if (v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
     }
     auto better = [](float v, int i, float bv2, int bi2) { return v > bv2 || (v == bv2 && i < bi2); };
 #pragma unroll
