@@ -260,22 +260,26 @@ def decode_algorithmic_bytes(cfg, model_weight_bytes, ctx_len):
 
 
 def prefill_state(model, cfg, lb, ctx_len, seed=4242):
+    """direct seeded fill of this shard's recurrent state, conv history and the first ctx_len KV rows"""
     for l in range(cfg.n_layers):
+        _, nbytes = model.state_ptr(l, 0)
+        stream = 1000 * model.tp_rank + l
         if cfg.is_fa(l):
-            n = ctx_len * cfg.fa_kv_heads * 256
-            model.set_state(l, 0, lb.fill_normal(n, seed, 10000 + l, dtype="bf16"))
-            model.set_state(l, 1, lb.fill_normal(n, seed, 20000 + l, dtype="bf16"))
+            n = nbytes // 2 // cfg.max_ctx * ctx_len
+            model.set_state(l, 0, lb.fill_normal(n, seed, 100000 + stream, dtype="bf16"))
+            model.set_state(l, 1, lb.fill_normal(n, seed, 200000 + stream, dtype="bf16"))
         else:
-            model.set_state(l, 0, lb.fill_normal(cfg.dn_v_heads * 128 * 128, seed, 30000 + l, std=0.02))
-            model.set_state(l, 1, lb.fill_normal(4 * cfg.conv_channels, seed, 40000 + l))
+            model.set_state(l, 0, lb.fill_normal(nbytes // 4, seed, 300000 + stream, std=0.02))
+            _, rbytes = model.state_ptr(l, 1)
+            model.set_state(l, 1, lb.fill_normal(rbytes // 4, seed, 400000 + stream))
 
 
-def time_gemv_mix(ctx, lb, cfg, args):
+def time_gemv_mix(ctx, lb, cfg, args, tp_size=1):
     """The step's own int4 GEMV launch mix (5 per layer, real shapes, norm prologues and fused
     epilogues, weights rotating over > L2 worth of distinct matrices), captured as one graph and
     timed alone with CUDA events: average duration and algorithmic bytes per launch."""
     H, I = cfg.hidden, cfg.inter
-    C_, V = cfg.conv_channels, cfg.dn_v_heads * 128
+    C_, V, I = cfg.conv_channels // tp_size, cfg.dn_v_heads * 128 // tp_size, I // tp_size   # this shard's slices
     shapes = [(H, C_ + V, "in"), (V, H, "out"), (H, 2 * I, "gateup"), (I, H, "down")]
     sets = 3   # 3 x ~196 MB of distinct weights per shape group: > 126 MB L2 between reuses
     mats = []
@@ -347,12 +351,20 @@ def cpu_decode_sample(cfg, lb, seed, ctx_len):
 def bench_decode(args, rank, local, world, dist):
     import lithos_b200 as lb
     from lithos_b200 import model as M
-    if world != 1:
-        raise SystemExit("tensor-parallel decode bench: see --workload decode with torchrun (not yet wired)")
+    from lithos_b200 import tp
     cfg = M.qwen35_27b(max_ctx=CTX_PREFILL + args.warmup + args.steps + 64, n_layers=args.layers)
     ctx = lb.Context(local)
     t0 = time.perf_counter()
-    model = M.Model(ctx, cfg)
+    comm = None
+    if world > 1:   # tensor parallel: exchange buffers mapped into every peer (CUDA IPC), handles passed over the process group
+        def all_gather(b):
+            out_ = [None] * world
+            dist.all_gather_object(out_, b)
+            return out_
+        comm = tp.make_comm(ctx, rank, world, cfg.hidden, all_gather)
+    model = M.Model(ctx, cfg, rank, world)
+    if comm is not None:
+        tp.attach(model, comm)
     model.fill_synthetic(args.seed)
     prefill_state(model, cfg, lb, CTX_PREFILL)
     build_s = time.perf_counter() - t0
@@ -397,9 +409,14 @@ def bench_decode(args, rank, local, world, dist):
     e2e_s = max_over_ranks(dist, e2e_s)
 
     step_s = ms * 1e-3 / args.steps
-    algo_step = decode_algorithmic_bytes(cfg, model.weight_bytes, CTX_PREFILL)
+    algo_step = decode_algorithmic_bytes(cfg, model.weight_bytes, CTX_PREFILL) if world == 1 else None
+    if world > 1:   # whole-job bytes: every rank streams its shard
+        import torch
+        t_ = torch.tensor([float(model.weight_bytes)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t_)
+        algo_step = decode_algorithmic_bytes(cfg, int(t_.item()), CTX_PREFILL)
     peak, which = measured_hbm_peak()
-    gemv_s, gemv_algo, _ = time_gemv_mix(ctx, lb, cfg, args)
+    gemv_s, gemv_algo, _ = time_gemv_mix(ctx, lb, cfg, args, world)
     out = {
         "metric": "batch-1 decode tok/s (Qwen3.5-27B-shaped hybrid, GPTQ int4, 4096-token state)", "value": 1.0 / step_s,
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
@@ -408,7 +425,7 @@ def bench_decode(args, rank, local, world, dist):
         "config": {"workload": f"config3: {cfg.n_layers}-layer Qwen3.5-27B-shaped decode step, hidden 5120, 3 DeltaNet + 1 attention "
                                f"per 4 layers, SwiGLU 17408, vocab 248320, int4 g128 linears, bf16 LM head, state pre-filled to {CTX_PREFILL} "
                                "tokens by seeded fill, greedy, one CUDA graph per step",
-                   "parallelism": "tp1", "l2": f"every step streams {algo_step / 1e9:.2f} GB of weights/state (>> 126 MB L2)",
+                   "parallelism": f"tp{world}", "l2": f"every step streams {algo_step / 1e9:.2f} GB of weights/state (>> 126 MB L2)",
                    "kernels_per_step": kernels_per_step, "build_seconds": round(build_s, 1), "last_token": int(last_token)},
         "e2e": {"value": 1.0 / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
         "gpu_launches": int(launches),
@@ -417,11 +434,14 @@ def bench_decode(args, rank, local, world, dist):
         "roofline": {"bound": "hbm", "achieved": gemv_algo / gemv_s / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": gemv_algo / gemv_s / 1e9 / peak, "traffic": None, "peak_source": which, "kernel": "gemv_int4_w256",
                      "us_per_launch": gemv_s * 1e6, "algorithmic_bytes": gemv_algo,
-                     "how": "the step's int4 GEMV launch mix (4 shapes x 12 layers, fused prologues/epilogues) replayed alone as a graph"},
+                     "how": "this GPU's int4 GEMV launch mix of the step (4 shapes x 12 layers, fused prologues/epilogues) replayed alone as a graph"},
         "clocks": clocks,
     }
     model.close()
-    if rank == 0 and not args.no_cpu:
+    if comm is not None:
+        barrier(dist)
+        comm.close()
+    if rank == 0 and not args.no_cpu and world == 1:
         v, cores, sample = cpu_decode_sample(cfg, lb, args.seed, CTX_PREFILL)
         out["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
     ctx.close()

@@ -173,6 +173,18 @@ int lb_rmsnorm(lb_ctx* ctx, uint64_t x, uint64_t res, uint64_t w_bf16, uint64_t 
 int lb_argmax(lb_ctx* ctx, uint64_t x_f32, int n, uint64_t out_idx_i32);
 int lb_embed(lb_ctx* ctx, uint64_t table_bf16, uint64_t token_i32, uint64_t out_f32, int D);
 
+/* ---- tensor-parallel exchange buffers (no counterpart in the reference: it is single-GPU) ---
+ * One process per GPU.  Each rank creates its buffer, the launcher passes the 64-byte IPC
+ * handles around (any transport), every rank opens its peers.  The exchange kernels use plain
+ * peer loads/stores over NVLink with bounded waits. */
+typedef struct lb_comm lb_comm;
+int lb_comm_create(lb_ctx* ctx, int rank, int size, int n_max, lb_comm** out); /* n_max >= hidden size */
+int lb_comm_rank(const lb_comm* comm);
+int lb_comm_size(const lb_comm* comm);
+int lb_comm_handle(lb_comm* comm, void* handle_out64);
+int lb_comm_open(lb_comm* comm, const void* handles_size_x_64);
+void lb_comm_destroy(lb_comm* comm);
+
 /* ---- the whole decode step ------------------------------------------------------------
  * Replaces decode_one_token and its launch_* helpers (src/launcher.s:685-1092), the per-layer
  * weight-slot table (src/launcher.s:92-141, 298-311) and the buffer plan (src/launcher.s:143-169).
@@ -190,6 +202,8 @@ enum { LB_WS_SLOTS = 26, LB_WG_SLOTS = 3 }; /* slot indices as in src/launcher.s
 
 /* tp_rank / tp_size: tensor-parallel shard held by this context (1 GPU: 0 / 1). */
 int lb_model_create(lb_ctx* ctx, const lb_model_cfg* cfg, int tp_rank, int tp_size, lb_model** out);
+/* tensor parallel: the exchange buffers (all peers opened) this model's all-reduces go through */
+int lb_model_set_comm(lb_model* m, lb_comm* comm);
 void lb_model_destroy(lb_model* m);
 /* Host tensors of one layer in the reference's slot order (26 pointers, unused slots NULL) in
  * the reference's packed formats; they are re-laid (projections that share an input fused along
@@ -197,6 +211,12 @@ void lb_model_destroy(lb_model* m);
  * (src/launcher.s:3284-3683). */
 int lb_model_load_layer(lb_model* m, int layer, const void* const* slots);
 int lb_model_load_globals(lb_model* m, const void* const* globals); /* embed, lm_head, final_norm */
+/* Host-only view of the same re-layout (no GPU needed): device matrix `which` (0 fused input
+ * projections, 1 out/o projection, 2 gate|up interleaved, 3 down) of tensor-parallel shard
+ * tp_rank/tp_size for `layer`.  Call with NULL outputs for the sizes, then with buffers of
+ * K/8*N, K/128*N and K/128*N/8 elements. */
+int lb_model_shard_host(const lb_model_cfg* cfg, int tp_rank, int tp_size, int layer, int which, const void* const* slots,
+                        uint32_t* qweight_out, uint16_t* scales_out, uint32_t* qzeros_out, int* K_out, int* N_out);
 /* Seeded synthetic weights with the shapes/distributions of the benchmark definition; tensor
  * (layer, slot) is stream (layer+1)*100+slot of the generator, globals are streams 1..3. */
 int lb_model_fill_synthetic(lb_model* m, uint64_t seed);

@@ -91,6 +91,8 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
     X(embed_bf16)                     \
     X(argmax_f32)                     \
     X(rmsnorm_f32)                    \
+    X(tp_allreduce_add)               \
+    X(tp_argmax_exchange)             \
     X(l2_flush)
 
 enum {

@@ -52,7 +52,13 @@ struct lb_model {
     uint64_t weight_bytes;
     lb_graph* graph;
     int step_kernels;
+    lb_comm* comm;   /* tensor parallel: exchange buffers */
+    int vocab_s;     /* vocabulary rows on this shard */
+    int ar_count;    /* all-reduces issued so far in the step being built (slot parity) */
 };
+
+extern int lb_comm_fill(const lb_comm* m, lb_tp_params* p, int slot, int n);
+extern uint64_t lb_comm_slot_ptr(const lb_comm* m, int slot);
 
 extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps,
                            uint64_t part_val, uint64_t part_idx);
@@ -84,12 +90,16 @@ LB_API int lb_model_create(lb_ctx* c, const lb_model_cfg* cfg, int tp_rank, int 
         cfg->dn_v_heads % cfg->dn_k_heads || cfg->fa_q_heads % cfg->fa_kv_heads)
         return lb_fail(c, LB_ERR_INVALID, "model: unsupported shape");
     if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return lb_fail(c, LB_ERR_INVALID, "model: bad tensor-parallel rank");
-    if (tp_size != 1) return lb_fail(c, LB_ERR_INVALID, "model: tensor parallelism is set up through lb_model_create_tp");
+    if (cfg->dn_k_heads % tp_size || cfg->dn_v_heads % tp_size || cfg->fa_q_heads % tp_size || cfg->vocab % tp_size ||
+        (cfg->inter / 128) % tp_size || (cfg->fa_kv_heads % tp_size && tp_size % cfg->fa_kv_heads))
+        return lb_fail(c, LB_ERR_INVALID, "model: heads / intermediate size / vocabulary do not split %d ways", tp_size);
     lb_model* m = (lb_model*)calloc(1, sizeof *m);
     if (!m) return LB_ERR_NOMEM;
     m->c = c; m->cfg = *cfg; m->tp_rank = tp_rank; m->tp_size = tp_size;
-    m->HV = cfg->dn_v_heads; m->HK = cfg->dn_k_heads; m->HQ = cfg->fa_q_heads; m->HKV = cfg->fa_kv_heads;
-    m->inter_s = cfg->inter;
+    m->HV = cfg->dn_v_heads / tp_size; m->HK = cfg->dn_k_heads / tp_size; m->HQ = cfg->fa_q_heads / tp_size;
+    m->HKV = cfg->fa_kv_heads >= tp_size ? cfg->fa_kv_heads / tp_size : 1; /* fewer KV heads than GPUs: replicated */
+    m->inter_s = cfg->inter / tp_size;
+    m->vocab_s = cfg->vocab / tp_size;
     m->C_s = (2 * m->HK + m->HV) * 128;
     m->L = (layer_t*)calloc((size_t)cfg->n_layers, sizeof(layer_t));
     if (!m->L) { free(m); return LB_ERR_NOMEM; }
@@ -104,12 +114,12 @@ LB_API int lb_model_create(lb_ctx* c, const lb_model_cfg* cfg, int tp_rank, int 
     LB_TRY(dalloc(m, &m->in_out, (size_t)n_in * 4));
     LB_TRY(dalloc(m, &m->mix_out, (size_t)n_mix * 4));
     LB_TRY(dalloc(m, &m->mlp_m, (size_t)m->inter_s * 2));
-    LB_TRY(dalloc(m, &m->logits, (size_t)cfg->vocab * 4));
+    LB_TRY(dalloc(m, &m->logits, (size_t)m->vocab_s * 4));
     LB_TRY(dalloc(m, &m->d_token, 16));
     LB_TRY(dalloc(m, &m->d_pos, 16));
     LB_TRY(dalloc(m, &m->d_next, 16));
-    LB_TRY(dalloc(m, &m->cand_val, (size_t)lb_dense_ctas(c, cfg->vocab) * 4));
-    LB_TRY(dalloc(m, &m->cand_idx, (size_t)lb_dense_ctas(c, cfg->vocab) * 4));
+    LB_TRY(dalloc(m, &m->cand_val, (size_t)lb_dense_ctas(c, m->vocab_s) * 4));
+    LB_TRY(dalloc(m, &m->cand_idx, (size_t)lb_dense_ctas(c, m->vocab_s) * 4));
     LB_CU(c, lb_drv.MemHostAlloc((void**)&m->h_next, 64, 0));
     for (int l = 0; l < cfg->n_layers; l++) {
         layer_t* L = &m->L[l];
@@ -170,15 +180,11 @@ LB_API int lb_model_step_kernels(const lb_model* m) { return m ? m->step_kernels
  * re-packed nibble by nibble (8 columns per word). */
 typedef struct { const uint32_t* qw; const uint16_t* sc; const uint32_t* qz; int N; } q4_src;
 
-static int build_q4(lb_model* m, q4_mat* dst, const q4_src* src, int n_src, const int* col_src, const int* col_idx,
-                    int N_out, int K, int k0, int k1 /* packed-row range [k0,k1) in units of groups */) {
-    int groups = k1 - k0, Kd = groups * 128;
-    size_t qb = (size_t)Kd / 8 * N_out * 4, sb = (size_t)groups * N_out * 2, zb = (size_t)groups * (N_out / 8) * 4;
-    uint32_t* qw = (uint32_t*)malloc(qb);
-    uint16_t* sc = (uint16_t*)malloc(sb);
-    uint32_t* qz = (uint32_t*)calloc(1, zb);
-    if (!qw || !sc || !qz) { free(qw); free(sc); free(qz); return lb_fail(m->c, LB_ERR_NOMEM, "model: host staging"); }
-    (void)n_src; (void)K;
+/* gather one device matrix on the host: columns by map, packed rows of groups [k0,k1) */
+static void gather_q4(const q4_src* src, const int* col_src, const int* col_idx, int N_out, int k0, int k1, uint32_t* qw,
+                      uint16_t* sc, uint32_t* qz) {
+    const int groups = k1 - k0, Kd = groups * 128;
+    memset(qz, 0, (size_t)groups * (N_out / 8) * 4);
 #pragma omp parallel for schedule(static)
     for (int kp = 0; kp < Kd / 8; kp++) {
         uint32_t* o = qw + (size_t)kp * N_out;
@@ -197,6 +203,17 @@ static int build_q4(lb_model* m, q4_mat* dst, const q4_src* src, int n_src, cons
             qz[(size_t)g * (N_out / 8) + (n >> 3)] |= z << (4 * (n & 7));
         }
     }
+}
+
+static int build_q4(lb_model* m, q4_mat* dst, const q4_src* src, const int* col_src, const int* col_idx, int N_out, int k0,
+                    int k1) {
+    int groups = k1 - k0, Kd = groups * 128;
+    size_t qb = (size_t)Kd / 8 * N_out * 4, sb = (size_t)groups * N_out * 2, zb = (size_t)groups * (N_out / 8) * 4;
+    uint32_t* qw = (uint32_t*)malloc(qb);
+    uint16_t* sc = (uint16_t*)malloc(sb);
+    uint32_t* qz = (uint32_t*)malloc(zb);
+    if (!qw || !sc || !qz) { free(qw); free(sc); free(qz); return lb_fail(m->c, LB_ERR_NOMEM, "model: host staging"); }
+    gather_q4(src, col_src, col_idx, N_out, k0, k1, qw, sc, qz);
     dst->K = Kd; dst->N = N_out;
     int st = upload(m, &dst->qweight, qw, qb);
     if (st == LB_OK) st = upload(m, &dst->scales, sc, sb);
@@ -216,75 +233,134 @@ static int slots_present(lb_model* m, const void* const* slots, const int* idx, 
     return LB_OK;
 }
 
+/* copy rows [r0, r0+rows) of a row-major host matrix with `row_bytes` per row */
+static int upload_rows(lb_model* m, CUdeviceptr* p, const void* src, size_t r0, size_t rows, size_t row_bytes) {
+    return upload(m, p, (const unsigned char*)src + r0 * row_bytes, rows * row_bytes);
+}
+
+/* Which columns / packed-row groups of the reference's per-projection tensors make up device
+ * matrix `which` (0 input projections fused, 1 output projection, 2 gate|up, 3 down) of shard
+ * R of T.  Column-parallel matrices keep all of K and take the shard's heads / intermediate
+ * columns; row-parallel ones keep all N and take the K groups of the shard's heads. */
+typedef struct { q4_src src[3]; int* cs; int* ci; int N, k0, k1; } shard_plan;
+
+static void plan_free(shard_plan* p) { free(p->cs); free(p->ci); p->cs = p->ci = NULL; }
+
+static int plan_make(const lb_model_cfg* c, int R, int T, int fa, int which, const void* const* slots, shard_plan* p) {
+    memset(p, 0, sizeof *p);
+    const int H = c->hidden, I = c->inter;
+    const int HV = c->dn_v_heads / T, HK = c->dn_k_heads / T, HQ = c->fa_q_heads / T;
+    const int HKV = c->fa_kv_heads >= T ? c->fa_kv_heads / T : 1;
+    const int Is = I / T;
+    int N = 0;
+    if (which == 0 && !fa) {
+        const int QKf = c->dn_k_heads * 128, Cf = (2 * c->dn_k_heads + c->dn_v_heads) * 128, Vf = c->dn_v_heads * 128;
+        const int QK = HK * 128, V = HV * 128, C = 2 * QK + V;
+        N = C + V;
+        p->src[0] = slot_src(slots, WS_DN_QKV, Cf); p->src[1] = slot_src(slots, WS_DN_Z, Vf);
+        p->cs = (int*)malloc(sizeof(int) * N); p->ci = (int*)malloc(sizeof(int) * N);
+        if (!p->cs || !p->ci) return LB_ERR_NOMEM;
+        for (int n = 0; n < N; n++) { /* device columns: q | k | v | z of this shard's heads */
+            if (n < QK) { p->cs[n] = 0; p->ci[n] = R * QK + n; }
+            else if (n < 2 * QK) { p->cs[n] = 0; p->ci[n] = QKf + R * QK + (n - QK); }
+            else if (n < C) { p->cs[n] = 0; p->ci[n] = 2 * QKf + R * V + (n - 2 * QK); }
+            else { p->cs[n] = 1; p->ci[n] = R * V + (n - C); }
+        }
+        p->k0 = 0; p->k1 = H / 128;
+    } else if (which == 0) {
+        const int NQf = 2 * c->fa_q_heads * 256, NKVf = c->fa_kv_heads * 256;
+        const int NQ = 2 * HQ * 256, NKV = HKV * 256;
+        const int kv0 = c->fa_kv_heads >= T ? R * HKV : (R * c->fa_kv_heads) / T; /* first KV head of this shard */
+        N = NQ + 2 * NKV;
+        p->src[0] = slot_src(slots, WS_FA_Q, NQf); p->src[1] = slot_src(slots, WS_FA_K, NKVf); p->src[2] = slot_src(slots, WS_FA_V, NKVf);
+        p->cs = (int*)malloc(sizeof(int) * N); p->ci = (int*)malloc(sizeof(int) * N);
+        if (!p->cs || !p->ci) return LB_ERR_NOMEM;
+        for (int n = 0; n < N; n++) { /* per query head 512 columns (query, gate), then the KV head(s) */
+            if (n < NQ) { p->cs[n] = 0; p->ci[n] = R * NQ + n; }
+            else if (n < NQ + NKV) { p->cs[n] = 1; p->ci[n] = kv0 * 256 + (n - NQ); }
+            else { p->cs[n] = 2; p->ci[n] = kv0 * 256 + (n - NQ - NKV); }
+        }
+        p->k0 = 0; p->k1 = H / 128;
+    } else if (which == 2) {
+        N = 2 * Is;
+        p->src[0] = slot_src(slots, WS_GATE, I); p->src[1] = slot_src(slots, WS_UP, I);
+        p->cs = (int*)malloc(sizeof(int) * N); p->ci = (int*)malloc(sizeof(int) * N);
+        if (!p->cs || !p->ci) return LB_ERR_NOMEM;
+        for (int n = 0; n < N; n++) { int blk = n / 64; p->cs[n] = blk & 1; p->ci[n] = R * Is + (blk >> 1) * 64 + n % 64; }
+        p->k0 = 0; p->k1 = H / 128;
+    } else { /* row-parallel: out / o projection (which 1), down projection (which 3) */
+        N = H;
+        p->src[0] = slot_src(slots, which == 3 ? WS_DOWN : (fa ? WS_FA_O : WS_DN_OUT), H);
+        p->cs = (int*)calloc((size_t)N, sizeof(int)); p->ci = (int*)malloc(sizeof(int) * N);
+        if (!p->cs || !p->ci) return LB_ERR_NOMEM;
+        for (int n = 0; n < N; n++) p->ci[n] = n;
+        if (which == 3) { p->k0 = R * Is / 128; p->k1 = (R + 1) * Is / 128; }
+        else if (fa) { p->k0 = R * HQ * 2; p->k1 = (R + 1) * HQ * 2; }   /* two groups of 128 per 256-wide head */
+        else { p->k0 = R * HV; p->k1 = (R + 1) * HV; }                    /* one group per value head */
+    }
+    p->N = N;
+    return LB_OK;
+}
+
+/* Host-only view of the sharder (no GPU): sizes first (outputs NULL), then the data. */
+LB_API int lb_model_shard_host(const lb_model_cfg* cfg, int tp_rank, int tp_size, int layer, int which,
+                               const void* const* slots, uint32_t* qweight_out, uint16_t* scales_out, uint32_t* qzeros_out,
+                               int* K_out, int* N_out) {
+    if (!cfg || !slots || which < 0 || which > 3 || tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return LB_ERR_INVALID;
+    shard_plan p;
+    int st = plan_make(cfg, tp_rank, tp_size, is_fa(cfg, layer), which, slots, &p);
+    if (st == LB_OK) {
+        if (K_out) *K_out = (p.k1 - p.k0) * 128;
+        if (N_out) *N_out = p.N;
+        if (qweight_out && scales_out && qzeros_out) gather_q4(p.src, p.cs, p.ci, p.N, p.k0, p.k1, qweight_out, scales_out, qzeros_out);
+    }
+    plan_free(&p);
+    return st;
+}
+
 LB_API int lb_model_load_layer(lb_model* m, int layer, const void* const* slots) {
     if (!m || !slots || layer < 0 || layer >= m->cfg.n_layers) return LB_ERR_INVALID;
     const lb_model_cfg* c = &m->cfg;
     layer_t* L = &m->L[layer];
     if (L->loaded) return lb_fail(m->c, LB_ERR_STATE, "model: layer %d already loaded", layer);
     LB_CU(m->c, lb_drv.CtxSetCurrent(m->c->cu_ctx));
-    const int H = c->hidden, I = c->inter;
-    int* cs = NULL; int* ci = NULL;
-    int st = LB_OK;
+    const int H = c->hidden, R = m->tp_rank, T = m->tp_size;
     if (!L->is_fa) {
         static const int need[] = {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22, 23, 24, 25};
         LB_TRY(slots_present(m, slots, need, 26, layer));
-        const int C = m->C_s, V = m->HV * 128, N = C + V;
-        q4_src src[2] = {slot_src(slots, WS_DN_QKV, C), slot_src(slots, WS_DN_Z, V)};
-        cs = (int*)malloc(sizeof(int) * N); ci = (int*)malloc(sizeof(int) * N);
-        for (int n = 0; n < N; n++) { cs[n] = n < C ? 0 : 1; ci[n] = n < C ? n : n - C; }
-        st = build_q4(m, &L->w_in, src, 2, cs, ci, N, H, 0, H / 128);
-        free(cs); free(ci);
-        if (st != LB_OK) return st;
-        q4_src so = slot_src(slots, WS_DN_OUT, H);
-        cs = (int*)calloc((size_t)H, sizeof(int)); ci = (int*)malloc(sizeof(int) * H);
-        for (int n = 0; n < H; n++) ci[n] = n;
-        st = build_q4(m, &L->w_out, &so, 1, cs, ci, H, V, 0, V / 128);
-        free(cs); free(ci);
-        if (st != LB_OK) return st;
-        LB_TRY(upload(m, &L->proj_a, slots[WS_DN_PROJ_A], (size_t)m->HV * H * 2));
-        LB_TRY(upload(m, &L->proj_b, slots[WS_DN_PROJ_B], (size_t)m->HV * H * 2));
-        LB_TRY(upload(m, &L->a_log, slots[WS_DN_A_LOG], (size_t)m->HV * 4));
-        LB_TRY(upload(m, &L->dt_bias, slots[WS_DN_DT_BIAS], (size_t)m->HV * 2));
-        LB_TRY(upload(m, &L->conv_w, slots[WS_DN_CONV1D], (size_t)4 * C * 2));
-        LB_TRY(upload(m, &L->dn_norm, slots[WS_DN_NORM], 128 * 4));
-        m->weight_bytes += (uint64_t)2 * m->HV * H * 2 + (uint64_t)4 * C * 2;
     } else {
         static const int need[] = {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 15, 16, 17, 18, 19, 20, 21, 22, 23, 24, 25};
         LB_TRY(slots_present(m, slots, need, 25, layer));
-        const int NQ = 2 * m->HQ * 256, NKV = m->HKV * 256, N = NQ + 2 * NKV;
-        q4_src src[3] = {slot_src(slots, WS_FA_Q, NQ), slot_src(slots, WS_FA_K, NKV), slot_src(slots, WS_FA_V, NKV)};
-        cs = (int*)malloc(sizeof(int) * N); ci = (int*)malloc(sizeof(int) * N);
-        for (int n = 0; n < N; n++) {
-            cs[n] = n < NQ ? 0 : (n < NQ + NKV ? 1 : 2);
-            ci[n] = n < NQ ? n : (n < NQ + NKV ? n - NQ : n - NQ - NKV);
+    }
+    q4_mat* mats[4] = {&L->w_in, &L->w_out, &L->w_gateup, &L->w_down};
+    for (int which = 0; which < 4; which++) {
+        shard_plan p;
+        int st = plan_make(c, R, T, L->is_fa, which, slots, &p);
+        if (st == LB_OK) st = build_q4(m, mats[which], p.src, p.cs, p.ci, p.N, p.k0, p.k1);
+        if (st == LB_OK && which == 0 && !L->is_fa) { /* conv taps of the shard's channels: the first C device columns */
+            const int C = m->C_s, Cf = (2 * c->dn_k_heads + c->dn_v_heads) * 128;
+            uint16_t* cw = (uint16_t*)malloc((size_t)4 * C * 2);
+            if (!cw) st = LB_ERR_NOMEM;
+            else {
+                for (int t = 0; t < 4; t++)
+                    for (int n = 0; n < C; n++) cw[(size_t)t * C + n] = ((const uint16_t*)slots[WS_DN_CONV1D])[(size_t)t * Cf + p.ci[n]];
+                st = upload(m, &L->conv_w, cw, (size_t)4 * C * 2);
+                free(cw);
+            }
         }
-        st = build_q4(m, &L->w_in, src, 3, cs, ci, N, H, 0, H / 128);
-        free(cs); free(ci);
-        if (st != LB_OK) return st;
-        q4_src so = slot_src(slots, WS_FA_O, H);
-        cs = (int*)calloc((size_t)H, sizeof(int)); ci = (int*)malloc(sizeof(int) * H);
-        for (int n = 0; n < H; n++) ci[n] = n;
-        st = build_q4(m, &L->w_out, &so, 1, cs, ci, H, m->HQ * 256, 0, m->HQ * 256 / 128);
-        free(cs); free(ci);
-        if (st != LB_OK) return st;
+        plan_free(&p);
+        if (st != LB_OK) return st == LB_ERR_NOMEM ? lb_fail(m->c, st, "model: host staging") : st;
+    }
+    if (!L->is_fa) {
+        LB_TRY(upload_rows(m, &L->proj_a, slots[WS_DN_PROJ_A], (size_t)R * m->HV, (size_t)m->HV, (size_t)H * 2));
+        LB_TRY(upload_rows(m, &L->proj_b, slots[WS_DN_PROJ_B], (size_t)R * m->HV, (size_t)m->HV, (size_t)H * 2));
+        LB_TRY(upload_rows(m, &L->a_log, slots[WS_DN_A_LOG], (size_t)R * m->HV, (size_t)m->HV, 4));
+        LB_TRY(upload_rows(m, &L->dt_bias, slots[WS_DN_DT_BIAS], (size_t)R * m->HV, (size_t)m->HV, 2));
+        LB_TRY(upload(m, &L->dn_norm, slots[WS_DN_NORM], 128 * 4));
+        m->weight_bytes += (uint64_t)2 * m->HV * H * 2 + (uint64_t)4 * m->C_s * 2;
+    } else {
         LB_TRY(upload(m, &L->q_norm, slots[WS_FA_Q_NORM], 256 * 2));
         LB_TRY(upload(m, &L->k_norm, slots[WS_FA_K_NORM], 256 * 2));
-    }
-    /* MLP: gate and up interleaved in 64-column blocks so that one CTA holds both halves of SwiGLU */
-    {
-        const int N = 2 * I;
-        q4_src src[2] = {slot_src(slots, WS_GATE, I), slot_src(slots, WS_UP, I)};
-        cs = (int*)malloc(sizeof(int) * N); ci = (int*)malloc(sizeof(int) * N);
-        for (int n = 0; n < N; n++) { int blk = n / 64; cs[n] = blk & 1; ci[n] = (blk >> 1) * 64 + n % 64; }
-        st = build_q4(m, &L->w_gateup, src, 2, cs, ci, N, H, 0, H / 128);
-        free(cs); free(ci);
-        if (st != LB_OK) return st;
-        q4_src sd = slot_src(slots, WS_DOWN, H);
-        cs = (int*)calloc((size_t)H, sizeof(int)); ci = (int*)malloc(sizeof(int) * H);
-        for (int n = 0; n < H; n++) ci[n] = n;
-        st = build_q4(m, &L->w_down, &sd, 1, cs, ci, H, I, 0, I / 128);
-        free(cs); free(ci);
-        if (st != LB_OK) return st;
     }
     LB_TRY(upload(m, &L->input_norm, slots[WS_INPUT_NORM], (size_t)H * 2));
     LB_TRY(upload(m, &L->post_norm, slots[WS_POST_NORM], (size_t)H * 2));
@@ -298,9 +374,9 @@ LB_API int lb_model_load_globals(lb_model* m, const void* const* g) {
     LB_CU(m->c, lb_drv.CtxSetCurrent(m->c->cu_ctx));
     size_t tb = (size_t)m->cfg.vocab * m->cfg.hidden * 2;
     LB_TRY(upload(m, &m->embed, g[WG_EMBED], tb));
-    LB_TRY(upload(m, &m->lm_head, g[WG_LM_HEAD], tb));
+    LB_TRY(upload_rows(m, &m->lm_head, g[WG_LM_HEAD], (size_t)m->tp_rank * m->vocab_s, (size_t)m->vocab_s, (size_t)m->cfg.hidden * 2));
     LB_TRY(upload(m, &m->final_norm, g[WG_FINAL_NORM], (size_t)m->cfg.hidden * 2));
-    m->weight_bytes += tb; /* the LM head is streamed every step; the embedding contributes one row */
+    m->weight_bytes += tb / m->tp_size; /* the LM head shard is streamed every step; the embedding contributes one row */
     m->globals_loaded = 1;
     return LB_OK;
 }
@@ -404,11 +480,26 @@ static int q4_gemv(lb_model* m, const q4_mat* w, CUdeviceptr x, CUdeviceptr y, i
                               m->cfg.eps);
 }
 
+/* output of a row-parallel projection: straight into the residual stream on one GPU; on several,
+ * this GPU's partial goes to its exchange buffer and tp_allreduce_add folds all partials into X */
+static int row_parallel(lb_model* m, const q4_mat* w, CUdeviceptr x, int x_mode, CUdeviceptr aux0, CUdeviceptr aux1) {
+    if (m->tp_size == 1) return q4_gemv(m, w, x, m->X, x_mode, LB_Y_F32_ACCUM, aux0, aux1, 0);
+    if (!m->comm) return lb_fail(m->c, LB_ERR_STATE, "model: tensor-parallel shard without exchange buffers (lb_model_set_comm)");
+    const int slot = m->ar_count++ & 1;
+    LB_TRY(q4_gemv(m, w, x, (CUdeviceptr)lb_comm_slot_ptr(m->comm, slot), x_mode, LB_Y_F32, aux0, aux1, 0));
+    lb_tp_params p;
+    LB_TRY(lb_comm_fill(m->comm, &p, slot, m->cfg.hidden));
+    p.x = (float*)m->X;
+    void* params[] = {&p};
+    return lb_launch(m->c, LBK_tp_allreduce_add, 1, 1, 1, 1024, 0, params, 1);
+}
+
 static int issue_step(lb_model* m) {
     lb_ctx* c = m->c;
     const lb_model_cfg* cfg = &m->cfg;
     const int H = cfg->hidden;
     uint64_t launches0 = c->launches;
+    m->ar_count = 0;
     {
         void* params[] = {&m->embed, &m->d_token, &m->X, (void*)&H};
         LB_TRY(lb_launch(c, LBK_embed_bf16, (unsigned)((H + 1023) / 1024), 1, 1, 256, 0, params, 1));
@@ -429,8 +520,7 @@ static int issue_step(lb_model* m) {
             p.HV = m->HV; p.HK = m->HK; p.hidden = H;
             void* params[] = {&p};
             LB_TRY(lb_launch(c, LBK_deltanet_layer_fused, (unsigned)m->HV, 4, 1, 128, 0, params, 1));
-            LB_TRY(q4_gemv(m, &L->w_out, m->mix_out, m->X, LB_X_F32_HEADNORM_SILU, LB_Y_F32_ACCUM, L->dn_norm,
-                           m->in_out + (size_t)C * 4, 0));
+            LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32_HEADNORM_SILU, L->dn_norm, m->in_out + (size_t)C * 4));
         } else {
             LB_TRY(q4_gemv(m, &L->w_in, m->X, m->in_out, LB_X_F32_RMSNORM, LB_Y_F32, L->input_norm, 0, 0));
             lb_attn_params p;
@@ -452,20 +542,38 @@ static int issue_step(lb_model* m) {
             void* params[] = {&p};
             LB_TRY(lb_launch(c, LBK_attn_decode_split, (unsigned)m->HKV, (unsigned)p.splits, 1, 256,
                              lb_attn_smem(m->HQ / m->HKV), params, 1));
-            LB_TRY(q4_gemv(m, &L->w_out, m->mix_out, m->X, LB_X_F32, LB_Y_F32_ACCUM, 0, 0, 0));
+            LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32, 0, 0));
         }
         LB_TRY(q4_gemv(m, &L->w_gateup, m->X, m->mlp_m, LB_X_F32_RMSNORM, LB_Y_SWIGLU_F16, L->post_norm, 0, 0));
-        LB_TRY(q4_gemv(m, &L->w_down, m->mlp_m, m->X, LB_X_F16, LB_Y_F32_ACCUM, 0, 0, 0));
+        LB_TRY(row_parallel(m, &L->w_down, m->mlp_m, LB_X_F16, 0, 0));
     }
     if (!m->globals_loaded) return lb_fail(c, LB_ERR_STATE, "model: globals have no weights");
-    LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, cfg->vocab, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps,
+    LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, m->vocab_s, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps,
                            m->cand_val, m->cand_idx));
-    {
-        int n = lb_dense_ctas(c, cfg->vocab); /* one (value, row) candidate per LM-head CTA */
+    if (m->tp_size == 1) {
+        int n = lb_dense_ctas(c, m->vocab_s); /* one (value, row) candidate per LM-head CTA */
         void* params[] = {&m->cand_val, &n, &m->d_next, &m->d_token, &m->d_pos, &m->cand_idx};
         LB_TRY(lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1));
+    } else {
+        lb_tp_argmax_params q;
+        memset(&q, 0, sizeof q);
+        LB_TRY(lb_comm_fill(m->comm, &q.tp, 2, 2));
+        q.cand_val = (const float*)m->cand_val; q.cand_idx = (const int32_t*)m->cand_idx;
+        q.n_cand = lb_dense_ctas(c, m->vocab_s); q.vocab_offset = m->tp_rank * m->vocab_s;
+        q.out_idx = (int32_t*)m->d_next; q.next_token = (int32_t*)m->d_token; q.pos = (int32_t*)m->d_pos;
+        void* params[] = {&q};
+        LB_TRY(lb_launch(c, LBK_tp_argmax_exchange, 1, 1, 1, 1024, 0, params, 1));
     }
     m->step_kernels = (int)(c->launches - launches0);
+    return LB_OK;
+}
+
+LB_API int lb_model_set_comm(lb_model* m, lb_comm* comm) {
+    if (!m || !comm) return LB_ERR_INVALID;
+    if (lb_comm_rank(comm) != m->tp_rank || lb_comm_size(comm) != m->tp_size)
+        return lb_fail(m->c, LB_ERR_INVALID, "model: exchange buffers are for rank %d/%d, the model is shard %d/%d",
+                       lb_comm_rank(comm), lb_comm_size(comm), m->tp_rank, m->tp_size);
+    m->comm = comm;
     return LB_OK;
 }
 

@@ -132,4 +132,26 @@ typedef struct {
     float eps;
 } lb_attn_params;
 
+/* ---- tensor-parallel exchange (comm.cu) ----------------------------------------------- */
+#define LB_TP_MAX 8
+typedef struct {
+    float* x;                          /* residual stream [n] on this GPU */
+    const float* partials[LB_TP_MAX];  /* every rank's exchange buffer: float [3][n_max] (peer pointers) */
+    unsigned* peer_flags[LB_TP_MAX];   /* every rank's flag array: unsigned [LB_TP_MAX] */
+    unsigned* my_flags;                /* this rank's flag array (local) */
+    unsigned* gen;                     /* this rank's generation counter (local, advanced by the kernel) */
+    unsigned* status;
+    int32_t n, n_max, slot, rank, size;
+} lb_tp_params;
+
+typedef struct {
+    lb_tp_params tp;        /* slot = 2: the record (logit, token) lives at the start of that slot */
+    const float* cand_val;  /* this rank's per-CTA candidates from the LM-head kernel */
+    const int32_t* cand_idx; /* rows inside this rank's vocabulary shard */
+    int32_t n_cand, vocab_offset;
+    int32_t* out_idx;
+    int32_t* next_token;
+    int32_t* pos;
+} lb_tp_argmax_params;
+
 #endif

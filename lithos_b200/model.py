@@ -119,7 +119,7 @@ class Model:
 
     def __init__(self, ctx: Context, cfg: ModelCfg, tp_rank: int = 0, tp_size: int = 1):
         _sigs()
-        self.ctx, self.cfg = ctx, cfg
+        self.ctx, self.cfg, self.tp_rank, self.tp_size = ctx, cfg, tp_rank, tp_size
         self.h = C.c_void_p(None)
         st = lib().lb_model_create(ctx.h, C.byref(cfg), tp_rank, tp_size, C.byref(self.h))
         if st != LB_OK:
@@ -176,7 +176,7 @@ class Model:
     def logits(self) -> np.ndarray:
         p = C.c_uint64(0)
         self.ctx._check(lib().lb_model_logits_ptr(self.h, C.byref(p)))
-        out = np.empty(self.cfg.vocab, dtype=np.float32)
+        out = np.empty(self.cfg.vocab // self.tp_size, dtype=np.float32)  # this shard's vocabulary rows
         self._xfer(p.value, out, False)
         return out
 
