@@ -429,8 +429,8 @@ def bench_decode(args, rank, local, world, dist):
                    "kernels_per_step": kernels_per_step, "build_seconds": round(build_s, 1), "last_token": int(last_token)},
         "e2e": {"value": 1.0 / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
         "gpu_launches": int(launches),
-        "step_roofline": {"algorithmic_bytes_per_step": algo_step, "achieved_GBs": algo_step / step_s / 1e9, "peak_GBs": peak,
-                          "frac": algo_step / step_s / 1e9 / peak, "tok_s_at_peak": peak * 1e9 / algo_step},
+        "step_roofline": {"algorithmic_bytes_per_step": algo_step, "achieved_GBs": algo_step / step_s / 1e9, "peak_GBs": peak * world,
+                          "frac": algo_step / step_s / 1e9 / (peak * world), "tok_s_at_peak": peak * world * 1e9 / algo_step},
         "roofline": {"bound": "hbm", "achieved": gemv_algo / gemv_s / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": gemv_algo / gemv_s / 1e9 / peak, "traffic": None, "peak_source": which, "kernel": "gemv_int4_w256",
                      "us_per_launch": gemv_s * 1e6, "algorithmic_bytes": gemv_algo,

@@ -215,18 +215,46 @@ __device__ __forceinline__ void attn_body(const lb_attn_params& p0, float* sm) {
         __syncthreads();
         if (s_ticket != (uint32_t)(p.splits - 1)) return;
         __threadfence();
+        // all (max, sum) pairs of this KV head in one parallel pass, then the slice weights once
+        float* ms_s = wacc;                       // [splits][G] slice maxima, then slice weights
+        float* ls_s = wacc + p.splits * G;        // [splits][G] slice sums
+        float* Mx_s = wacc + 2 * p.splits * G;    // [G]
+        const float* kvrec = p.scratch + (size_t)kv * p.splits * G * AT_REC;
+        for (int i = t; i < p.splits * G; i += AT_THREADS) {
+            ms_s[i] = __ldcg(kvrec + (size_t)i * AT_REC + 256);
+            ls_s[i] = __ldcg(kvrec + (size_t)i * AT_REC + 257);
+        }
+        __syncthreads();
+        if (t < G) {
+            float M = -INFINITY;
+            for (int s2 = 0; s2 < p.splits; ++s2) M = fmaxf(M, ms_s[s2 * G + t]);
+            Mx_s[t] = M;
+        }
+        __syncthreads();
+        for (int i = t; i < p.splits * G; i += AT_THREADS) {
+            const float mi = ms_s[i];
+            ms_s[i] = mi == -INFINITY ? 0.f : exp2f(mi - Mx_s[i % G]);
+        }
+        __syncthreads();
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            float M = -INFINITY;
-            for (int s2 = 0; s2 < p.splits; ++s2)
-                M = fmaxf(M, __ldcg(p.scratch + ((size_t)(kv * p.splits + s2) * G + g) * AT_REC + 256));
             float L = 0.f, A = 0.f;
-            for (int s2 = 0; s2 < p.splits; ++s2) {
-                const float* r2 = p.scratch + ((size_t)(kv * p.splits + s2) * G + g) * AT_REC;
-                const float ms = __ldcg(r2 + 256);
-                const float sc = ms == -INFINITY ? 0.f : exp2f(ms - M);
-                L = fmaf(__ldcg(r2 + 257), sc, L);
-                A = fmaf(__ldcg(r2 + t), sc, A);
+            int s2 = 0;
+            for (; s2 + 8 <= p.splits; s2 += 8) { // 8 independent loads in flight, added in slice order
+                float a8[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a8[j] = __ldcg(kvrec + ((size_t)(s2 + j) * G + g) * AT_REC + t);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float w = ms_s[(s2 + j) * G + g];
+                    L = fmaf(ls_s[(s2 + j) * G + g], w, L);
+                    A = fmaf(a8[j], w, A);
+                }
+            }
+            for (; s2 < p.splits; ++s2) {
+                const float w = ms_s[s2 * G + g];
+                L = fmaf(ls_s[s2 * G + g], w, L);
+                A = fmaf(__ldcg(kvrec + ((size_t)s2 * G + g) * AT_REC + t), w, A);
             }
             Lg[g] = L; Ag[g] = A;
         }

@@ -1,5 +1,6 @@
 """GPU (needs >= 2 GPUs on the box; skipped otherwise): tensor-parallel decode through IPC-mapped
-exchange buffers gives the same greedy tokens as one GPU, and logits within 1e-4."""
+exchange buffers gives the same greedy tokens as one GPU, and logits within 2e-3 of max|logit| (the shards quantise their
+activation slices separately and add partial sums in a different order)."""
 import os
 import subprocess
 import sys

