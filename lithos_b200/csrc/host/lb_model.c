@@ -539,6 +539,8 @@ static int issue_step(lb_model* m) {
             p.splits = lb_attn_splits(c, cfg->max_ctx, m->HKV);
             p.in_dtype = 1; p.gate_stride = 512; p.q_stride = 512;
             p.rot_dims = cfg->rot_dims; p.rope_theta = cfg->rope_theta; p.eps = cfg->eps;
+            for (int i = 0; i < cfg->rot_dims / 2; i++)
+                p.rope_freq[i] = exp2(-log2((double)cfg->rope_theta) * (double)i / (double)(cfg->rot_dims / 2));
             void* params[] = {&p};
             LB_TRY(lb_launch(c, LBK_attn_decode_split, (unsigned)m->HKV, (unsigned)p.splits, 1, 256,
                              lb_attn_smem(m->HQ / m->HKV), params, 1));

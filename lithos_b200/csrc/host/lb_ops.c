@@ -263,10 +263,10 @@ LB_API int lb_attention_decode(lb_ctx* c, uint64_t q, uint64_t k_new, uint64_t v
     if (!c || !q || !k_new || !v_new || !k_cache || !v_cache || !out || pos < 0 || HKV <= 0 || HQ % HKV)
         return lb_fail(c, LB_ERR_INVALID, "lb_attention_decode: bad argument");
     int G = HQ / HKV;
-    if (!(G == 1 || G == 2 || G == 3 || G == 4 || G == 6 || G == 8) || HKV > 8)
+    if (!(G == 1 || G == 2 || G == 3 || G == 4 || G == 6) || HKV > 8)
         return lb_fail(c, LB_ERR_INVALID, "lb_attention_decode: unsupported head ratio %d/%d", HQ, HKV);
     if ((q_norm_w == 0) != (k_norm_w == 0)) return lb_fail(c, LB_ERR_INVALID, "lb_attention_decode: q/k norm weights must come together");
-    if (rot_dims < 0 || rot_dims > 256 || rot_dims % 2) return lb_fail(c, LB_ERR_INVALID, "lb_attention_decode: bad rot_dims");
+    if (rot_dims < 0 || rot_dims > 128 || rot_dims % 8) return lb_fail(c, LB_ERR_INVALID, "lb_attention_decode: bad rot_dims");
     lb_attn_params p;
     memset(&p, 0, sizeof p);
     p.q = (const void*)q; p.k_new = (const void*)k_new; p.v_new = (const void*)v_new; p.gate = (const void*)gate;
@@ -278,6 +278,7 @@ LB_API int lb_attention_decode(lb_ctx* c, uint64_t q, uint64_t k_new, uint64_t v
     p.in_dtype = in_is_f32 ? 1 : 0;
     p.gate_stride = 256; p.q_stride = 256;
     p.rot_dims = rot_dims; p.rope_theta = rope_theta; p.eps = eps;
+    for (int i = 0; i < rot_dims / 2; i++) p.rope_freq[i] = exp2(-log2((double)rope_theta) * (double)i / (double)(rot_dims / 2));
     void* params[] = {&p};
     return lb_launch(c, LBK_attn_decode_split, (unsigned)HKV, (unsigned)p.splits, 1, 256, lb_attn_smem(G), params, 1);
 }

@@ -29,29 +29,39 @@ __device__ __forceinline__ float ld_in(const void* p, size_t i, int is_f32) {
                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
 }
 
-// RMS-normalise (plain weight) then rotate the first rot_dims dims in
-// interleaved pairs at position pos; one value per thread, dst in shared.
-__device__ __forceinline__ void norm_rope_256(float v, const uint16_t* w, float* dst, float* red, int pos, int rot_dims,
-                                              float theta, float eps, float post_scale) {
-    const int t = threadIdx.x;
+// One warp prepares one 256-wide head vector: RMS-normalise (plain weight), rotate the first
+// rot_dims dims in interleaved pairs with the CTA's cos/sin table, scale, store to shared memory.
+// A lane owns 8 consecutive dims, i.e. 4 rotation pairs.
+__device__ __forceinline__ void warp_norm_rope(const void* src, size_t base, int is_f32, const uint16_t* w, float* dst,
+                                               const float* cs_s, const float* sn_s, int rot_dims, float eps,
+                                               float post_scale) {
+    const int lane = threadIdx.x & 31;
+    float v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        v[j] = ld_in(src, base + lane * 8 + j, is_f32);
+        ss += v[j] * v[j];
+    }
     if (w) {
-        float ss = block_sum(v * v, red);
-        v = v * rsqrtf(ss * (1.0f / AT_D) + eps) * bf16_bits_to_f32(w[t]);
+        ss = warp_sum(ss);
+        const float r = rsqrtf(ss * (1.0f / AT_D) + eps);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = v[j] * r * bf16_bits_to_f32(w[lane * 8 + j]);
     }
-    dst[t] = v;
-    __syncthreads();
-    if (t < rot_dims / 2) {
-        // angle in double: pos * freq reaches 1e5 rad, far beyond fp32 resolution
-        double freq = exp2(-log2((double)theta) * (double)t / (double)(rot_dims / 2));
-        double sn, cs;
-        sincos((double)pos * freq, &sn, &cs);
-        float a = dst[2 * t], b = dst[2 * t + 1];
-        dst[2 * t] = a * (float)cs - b * (float)sn;
-        dst[2 * t + 1] = a * (float)sn + b * (float)cs;
+    if (lane * 8 < rot_dims) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = lane * 4 + j;
+            if (2 * i < rot_dims) {
+                const float a = v[2 * j], b = v[2 * j + 1], cs = cs_s[i], sn = sn_s[i];
+                v[2 * j] = a * cs - b * sn;
+                v[2 * j + 1] = a * sn + b * cs;
+            }
+        }
     }
-    __syncthreads();
-    dst[t] *= post_scale;
-    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[lane * 8 + j] = v[j] * post_scale;
 }
 
 template <int G>
@@ -73,14 +83,27 @@ __device__ __forceinline__ void attn_body(const lb_attn_params& p0, float* sm) {
     const bool last = split == p.splits - 1;
     const float LOG2E = 1.4426950408889634f;
     const float qscale = rsqrtf((float)AT_D) * LOG2E; // scores kept in log2 units
-    for (int g = 0; g < G; ++g) {
-        const int hq = kv * G + g;
-        float v = ld_in(p.q, (size_t)hq * p.q_stride + t, p.in_dtype);
-        norm_rope_256(v, p.q_norm_w, q_s + g * AT_D, red, p.pos, p.rot_dims, p.rope_theta, p.eps, qscale);
+    // cos/sin of this position once per CTA.  The angle pos*freq reaches 1e5 rad, far beyond fp32
+    // resolution: it is formed and reduced modulo 2*pi in double (4 double operations), the
+    // trigonometry itself is fp32 on |r| <= pi.  freq comes from the host in double.
+    float* cs_s = wacc;       // the per-warp accumulators are not in use yet
+    float* sn_s = wacc + 128;
+    if (t < p.rot_dims / 2) {
+        const double a = (double)p.pos * p.rope_freq[t];
+        const double k = rint(a * 0.15915494309189535);
+        const float r = (float)fma(-k, 6.283185307179586, a);
+        sincosf(r, &sn_s[t], &cs_s[t]);
     }
+    __syncthreads();
+    for (int row = warp; row < G + (last ? 1 : 0); row += AT_WARPS) {
+        if (row < G)
+            warp_norm_rope(p.q, (size_t)(kv * G + row) * p.q_stride, p.in_dtype, p.q_norm_w, q_s + row * AT_D, cs_s, sn_s,
+                           p.rot_dims, p.eps, qscale);
+        else
+            warp_norm_rope(p.k_new, (size_t)kv * AT_D, p.in_dtype, p.k_norm_w, kn_s, cs_s, sn_s, p.rot_dims, p.eps, 1.0f);
+    }
+    __syncthreads();
     if (last) {
-        float kr = ld_in(p.k_new, (size_t)kv * AT_D + t, p.in_dtype);
-        norm_rope_256(kr, p.k_norm_w, kn_s, red, p.pos, p.rot_dims, p.rope_theta, p.eps, 1.0f);
         __nv_bfloat16 kb = __float2bfloat16_rn(kn_s[t]);
         __nv_bfloat16 vb = __float2bfloat16_rn(ld_in(p.v_new, (size_t)kv * AT_D + t, p.in_dtype));
         const size_t row = ((size_t)p.pos * p.HKV + kv) * AT_D + t;
@@ -92,12 +115,9 @@ __device__ __forceinline__ void attn_body(const lb_attn_params& p0, float* sm) {
     __syncthreads();
     pdl_launch_dependents();
 
-    // this lane's 8 dims of every query head
-    float qr[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) qr[g][j] = q_s[g * AT_D + lane * 8 + j];
+    // the query heads stay in shared memory (two 128-bit loads per head and row): registers hold
+    // the running soft-max state only, so that two CTAs fit on an SM
+    const float4* q4 = reinterpret_cast<const float4*>(q_s) + lane * 2;
 
     float m[G], l[G], acc[G][8];
 #pragma unroll
@@ -118,9 +138,10 @@ __device__ __forceinline__ void attn_body(const lb_attn_params& p0, float* sm) {
         float s[G];
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            float d = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) d = fmaf(qr[g][j], kf[j], d);
+            const float4 qa = q4[g * (AT_D / 4)], qb = q4[g * (AT_D / 4) + 1];
+            float d = qa.x * kf[0];
+            d = fmaf(qa.y, kf[1], d); d = fmaf(qa.z, kf[2], d); d = fmaf(qa.w, kf[3], d);
+            d = fmaf(qb.x, kf[4], d); d = fmaf(qb.y, kf[5], d); d = fmaf(qb.z, kf[6], d); d = fmaf(qb.w, kf[7], d);
             s[g] = d;
         }
 #pragma unroll
@@ -237,27 +258,30 @@ __device__ __forceinline__ void attn_body(const lb_attn_params& p0, float* sm) {
         }
         __syncthreads();
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float L = 0.f, A = 0.f;
-            int s2 = 0;
-            for (; s2 + 8 <= p.splits; s2 += 8) { // 8 independent loads in flight, added in slice order
-                float a8[8];
+        for (int g = 0; g < G; ++g) { Lg[g] = 0.f; Ag[g] = 0.f; }
+        int s2 = 0;
+        for (; s2 + 8 <= p.splits; s2 += 8) { // 8*G independent loads in flight, then added in slice order
+            float a8[G][8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) a8[j] = __ldcg(kvrec + ((size_t)(s2 + j) * G + g) * AT_REC + t);
+            for (int g = 0; g < G; ++g)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a8[g][j] = __ldcg(kvrec + ((size_t)(s2 + j) * G + g) * AT_REC + t);
+#pragma unroll
+            for (int g = 0; g < G; ++g)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float w = ms_s[(s2 + j) * G + g];
-                    L = fmaf(ls_s[(s2 + j) * G + g], w, L);
-                    A = fmaf(a8[j], w, A);
+                    Lg[g] = fmaf(ls_s[(s2 + j) * G + g], w, Lg[g]);
+                    Ag[g] = fmaf(a8[g][j], w, Ag[g]);
                 }
-            }
-            for (; s2 < p.splits; ++s2) {
-                const float w = ms_s[s2 * G + g];
-                L = fmaf(ls_s[s2 * G + g], w, L);
-                A = fmaf(__ldcg(kvrec + ((size_t)s2 * G + g) * AT_REC + t), w, A);
-            }
-            Lg[g] = L; Ag[g] = A;
         }
+        for (; s2 < p.splits; ++s2)
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float w = ms_s[s2 * G + g];
+                Lg[g] = fmaf(ls_s[s2 * G + g], w, Lg[g]);
+                Ag[g] = fmaf(__ldcg(kvrec + ((size_t)s2 * G + g) * AT_REC + t), w, Ag[g]);
+            }
         if (t == 0) p.counters[kv] = 0u;
     }
 #pragma unroll
@@ -269,7 +293,7 @@ __device__ __forceinline__ void attn_body(const lb_attn_params& p0, float* sm) {
     }
 }
 
-extern "C" __global__ void __launch_bounds__(AT_THREADS) attn_decode_split(const __grid_constant__ lb_attn_params p) {
+extern "C" __global__ void __launch_bounds__(AT_THREADS, 2) attn_decode_split(const __grid_constant__ lb_attn_params p) {
     extern __shared__ __align__(16) float at_sm[];
     const int G = p.HQ / p.HKV;
     switch (G) {
@@ -278,7 +302,6 @@ extern "C" __global__ void __launch_bounds__(AT_THREADS) attn_decode_split(const
         case 3: attn_body<3>(p, at_sm); break;
         case 4: attn_body<4>(p, at_sm); break;
         case 6: attn_body<6>(p, at_sm); break;
-        case 8: attn_body<8>(p, at_sm); break;
         default: break; // host rejects other ratios
     }
 }

@@ -130,6 +130,7 @@ typedef struct {
     int32_t rot_dims;
     float rope_theta;
     float eps;
+    double rope_freq[64]; /* theta^(-i/(rot_dims/2)), i < rot_dims/2 <= 64, computed on the host in double */
 } lb_attn_params;
 
 /* ---- tensor-parallel exchange (comm.cu) ----------------------------------------------- */
