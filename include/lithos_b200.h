@@ -164,6 +164,25 @@ int lb_attention_decode(lb_ctx* ctx, uint64_t q, uint64_t k_new, uint64_t v_new,
                         uint64_t k_norm_w, uint64_t k_cache, uint64_t v_cache, uint64_t out, int pos, int HQ, int HKV,
                         int in_is_f32, int rot_dims, float rope_theta, float eps);
 
+/* No counterpart in the reference.  The same decode-attention call for callers that cannot
+ * allocate device memory and have no lb_ctx: code recording its own CUDA graph, a real-time loop
+ * that sized everything at start-up, a plugin inside another runtime's memory pool, a process
+ * held to a fixed memory budget.  The split-KV scratch is an array built into this library's
+ * device image (798 976 bytes, held by every GPU that loads the library until the process exits),
+ * so the call makes no cudaMalloc/cudaFree and uses no allocating library routine.
+ *   - Runs on the CURRENT device, on `stream` (a CUstream / cudaStream_t, NULL = default stream).
+ *   - Limits: at most 8 KV heads and 1, 2, 3, 4 or 6 query heads per KV head; the positions are
+ *     cut into at most 16 slices whatever `pos` is.  Anything else returns LB_ERR_INVALID with
+ *     the reason in `err`.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
+ *     sets the kernel's shared-memory limit; make that first call before any stream capture.
+ *   - All calls on a device share the one array: calls that overlap on the GPU (two streams, two
+ *     threads) race on it.  The call itself zeroes the arrival counters it needs on `stream`.
+ * Arguments as lb_attention_decode; `err` (may be NULL) receives the error text. */
+int lb_attention_decode_noalloc(void* stream, uint64_t q, uint64_t k_new, uint64_t v_new, uint64_t gate, uint64_t q_norm_w,
+                                uint64_t k_norm_w, uint64_t k_cache, uint64_t v_cache, uint64_t out, int pos, int HQ,
+                                int HKV, int in_is_f32, int rot_dims, float rope_theta, float eps, char* err, size_t errlen);
+
 /* ---- small kernels ---------------------------------------------------------------------
  * rmsnorm: replaces launch_norm (src/launcher.s:1101-1219, inference/reduce.ls:21-147);
  * argmax: replaces the CPU argmax loop (src/launcher.s:962-1073, inference/reduce.ls:214-313);
