@@ -372,12 +372,16 @@ def bench_decode(args, rank, local, world, dist):
     kernels_per_step = model.step_kernels
 
     # clock ramp (untimed, not one of the W warm-up steps), then W warm-up steps
+    # (every rank must replay the same number of steps: the ramp is sized from a step time all ranks agree on)
     model.set_input(1, CTX_PREFILL)
     t_ramp = time.perf_counter()
-    while time.perf_counter() - t_ramp < args.ramp_s:
+    model.replay(4)
+    ctx.sync()
+    t4 = max_over_ranks(dist, time.perf_counter() - t_ramp)
+    for _ in range(min(2000, int(args.ramp_s / max(t4 / 4, 1e-4))) // 4):
         model.set_input(1, CTX_PREFILL)
         model.replay(4)
-        ctx.sync()
+    ctx.sync()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()

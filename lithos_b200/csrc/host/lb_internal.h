@@ -102,7 +102,7 @@ enum {
     LBK_COUNT
 };
 
-#define LB_MAX_MODULES 16
+#define LB_MAX_MODULES 64
 #define LB_MAX_PEERS 8
 
 struct lb_ctx {

@@ -34,7 +34,10 @@ __device__ __forceinline__ bool tp_rendezvous(const lb_tp_params& p, unsigned g,
         st_release_sys(p.peer_flags[t] + p.rank, g);
         const uint64_t t0 = globaltimer_ns();
         bool ok = false;
-        for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
+        // a wait that already ran out in this context is not repeated: every later exchange returns at once,
+        // so a lost peer costs one time limit, not one per exchange
+        const bool dead = *reinterpret_cast<volatile unsigned*>(p.status) != 0u;
+        for (unsigned it = 0; it < LB_WAIT_SPINS && !dead; ++it) {
             // generations only grow; (int) difference keeps the test valid across wrap-around
             if ((int)(ld_acquire_sys(p.my_flags + t) - g) >= 0) { ok = true; break; }
             if ((it & 63u) == 63u && globaltimer_ns() - t0 > LB_WAIT_NS) break;
