@@ -57,6 +57,9 @@ uint64_t lb_launch_count(const lb_ctx* ctx);
 void lb_launch_count_reset(lb_ctx* ctx);
 /* enable (1, default) / disable (0) programmatic dependent launch between consecutive kernels */
 void lb_set_pdl(lb_ctx* ctx, int on);
+/* bytes of an SM's shared memory lb_gemv_chain leaves free so that a CTA of the kernel before/after it can be
+ * resident at the same time (default 32 KB; 0 = the deepest weight ring) */
+void lb_set_chain_reserve(lb_ctx* ctx, int bytes);
 
 /* ---- generic module load + launch ----------------------------------------------
  * The reference's own mechanism, kept as is: load_one_cubin = file read +
@@ -135,6 +138,24 @@ int lb_gemv_int4_host(lb_ctx* ctx, const uint32_t* qweight, const uint16_t* scal
 /* fused variants used by the decode step (norm prologues): see lithos_b200/csrc/kernels/params.h */
 int lb_gemv_int4_fused(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y, int K,
                        int N, int x_mode, int y_mode, uint64_t aux0, uint64_t aux1, uint64_t x_out, float eps);
+/* A chain of up to LB_GEMV_CHAIN_MAX fused GEMVs in ONE persistent launch (one CTA per SM, a grid
+ * barrier between consecutive GEMVs): GEMV i+1 may read what GEMV i wrote.  Replaces a run of
+ * consecutive launch_gemv calls of the decode step (src/launcher.s:829-933: out projection,
+ * gate/up projection, down projection, next layer's input projections).  Same operand formats,
+ * x_mode / y_mode values and results (to rounding) as lb_gemv_int4_fused called once per entry.
+ * LB_ERR_INVALID when a GEMV has fewer (tile, K-group) units than the GPU has SMs, or K > 6144
+ * with so few column tiles that one CTA would need more than 6144 activations. */
+#define LB_GEMV_CHAIN_MAX 6
+typedef struct {
+    uint64_t qweight, scales, qzeros; /* device pointers; qzeros 0 = zero-point 8 */
+    uint64_t x, y, aux0, aux1, x_out; /* as in lb_gemv_int4_fused */
+    int32_t K, N, x_mode, y_mode;
+    float eps;
+    int32_t reserved;
+} lb_gemv_op;
+int lb_gemv_chain(lb_ctx* ctx, const lb_gemv_op* ops, int n_ops);
+/* LB_OK when lb_gemv_chain accepts this shape on this GPU (no launch) */
+int lb_gemv_chain_supports(lb_ctx* ctx, int K, int N);
 /* bit-exact targets: W(k,n) = fma(float(q), s, -z*s) as fp32 [K,N]; q as u8 [K,N] */
 int lb_gptq_dequant(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t w_out_f32, int K, int N);
 int lb_gptq_unpack(lb_ctx* ctx, uint64_t qweight, uint64_t q_out_u8, int K, int N);

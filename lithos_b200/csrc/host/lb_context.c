@@ -126,7 +126,7 @@ static int load_cubin(lb_ctx* c, const char* dir, const char* file) {
     return LB_OK;
 }
 
-static const char* const k_cubins[] = {"gemv.cubin", "deltanet.cubin", "attention.cubin", "small.cubin", "comm.cubin"};
+static const char* const k_cubins[] = {"gemv.cubin", "chain.cubin", "deltanet.cubin", "attention.cubin", "small.cubin", "comm.cubin"};
 
 LB_API int lb_init(int device, const char* kernel_dir, lb_ctx** out) {
     if (!out) return LB_ERR_INVALID;
@@ -138,6 +138,7 @@ LB_API int lb_init(int device, const char* kernel_dir, lb_ctx** out) {
     if (st != LB_OK) return st;
     c->device = device;
     c->pdl = 1;
+    c->chain_reserve = 32 * 1024;
     LB_CU(c, lb_drv.DeviceGet(&c->cu_dev, device));
     int major = 0, minor = 0;
     LB_CU(c, lb_drv.DeviceGetAttribute(&major, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MAJOR, c->cu_dev));
@@ -169,8 +170,12 @@ LB_API int lb_init(int device, const char* kernel_dir, lb_ctx** out) {
         if (r != CUDA_SUCCESS)
             return lb_fail(c, LB_ERR_NO_KERNEL, "entry point %s not found in any kernel image under %s",
                            k_kernel_names[k], dir);
-        /* let every kernel use the full opt-in shared memory */
-        lb_drv.FuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, c->max_smem_optin - 1024);
+        /* let every kernel use the full opt-in shared memory (its static part counts against the same limit) */
+        int stat = 0;
+        LB_CU(c, lb_drv.FuncGetAttribute(&stat, CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES, c->fn[k]));
+        c->fn_static_smem[k] = stat;
+        LB_CU(c, lb_drv.FuncSetAttribute(c->fn[k], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                         c->max_smem_optin - ((stat + 1023) & ~1023)));
     }
 
     LB_CU(c, lb_drv.MemAlloc(&c->gemv_partial, (size_t)LB_GEMV_MAX_SPLITS * LB_GEMV_SCRATCH_N * sizeof(float)));
@@ -214,6 +219,7 @@ LB_API int lb_device_sm_count(const lb_ctx* c) { return c ? c->sm_count : 0; }
 LB_API uint64_t lb_launch_count(const lb_ctx* c) { return c ? c->launches : 0; }
 LB_API void lb_launch_count_reset(lb_ctx* c) { if (c) c->launches = 0; }
 LB_API void lb_set_pdl(lb_ctx* c, int on) { if (c) c->pdl = on ? 1 : 0; }
+LB_API void lb_set_chain_reserve(lb_ctx* c, int bytes) { if (c && bytes >= 0 && bytes <= 128 * 1024) c->chain_reserve = bytes; }
 
 LB_API int lb_device_status(lb_ctx* c, uint32_t* out) {
     if (!c || !out) return LB_ERR_INVALID;
@@ -317,9 +323,9 @@ int lb_launch_cluster(lb_ctx* c, int kernel, unsigned gx, unsigned gy, unsigned 
                       void** params, int pdl, unsigned cluster_y) {
     if (!c->fn[kernel]) return lb_fail(c, LB_ERR_NO_KERNEL, "kernel %s not loaded", k_kernel_names[kernel]);
     if (gx == 0 || gy == 0 || gz == 0) return lb_fail(c, LB_ERR_INVALID, "empty grid for %s", k_kernel_names[kernel]);
-    if ((int)smem > c->max_smem_optin - 1024)
-        return lb_fail(c, LB_ERR_INVALID, "%s needs %u B of shared memory (> %d)", k_kernel_names[kernel], smem,
-                       c->max_smem_optin - 1024);
+    if ((int)smem > c->max_smem_optin - ((c->fn_static_smem[kernel] + 1023) & ~1023))
+        return lb_fail(c, LB_ERR_INVALID, "%s needs %u B of dynamic shared memory (> %d)", k_kernel_names[kernel], smem,
+                       c->max_smem_optin - ((c->fn_static_smem[kernel] + 1023) & ~1023));
     CUlaunchConfig cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDimX = gx; cfg.gridDimY = gy; cfg.gridDimZ = gz;

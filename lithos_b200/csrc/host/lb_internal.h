@@ -40,6 +40,7 @@
     X(ModuleUnload, cuModuleUnload, (CUmodule))                                                                 \
     X(ModuleGetFunction, cuModuleGetFunction, (CUfunction*, CUmodule, const char*))                             \
     X(FuncSetAttribute, cuFuncSetAttribute, (CUfunction, CUfunction_attribute, int))                            \
+    X(FuncGetAttribute, cuFuncGetAttribute, (int*, CUfunction_attribute, CUfunction))                           \
     X(LaunchKernel, cuLaunchKernel,                                                                             \
       (CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**)) \
     X(LaunchKernelEx, cuLaunchKernelEx, (const CUlaunchConfig*, CUfunction, void**, void**))                    \
@@ -80,6 +81,7 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
 /* ---- kernels (entry points inside the cubins) -------------------------- */
 #define LB_KERNELS(X)                 \
     X(gemv_int4_w256)                 \
+    X(gemv_chain)                     \
     X(gptq_dequant_f32)               \
     X(gptq_unpack_u8)                 \
     X(dense_bf16_gemv)                \
@@ -116,6 +118,7 @@ struct lb_ctx {
     CUmodule modules[LB_MAX_MODULES];
     int n_modules;
     CUfunction fn[LBK_COUNT];
+    int fn_static_smem[LBK_COUNT]; /* static shared memory of each kernel, bytes */
     /* split-K scratch shared by every GEMV launched on this context's stream */
     CUdeviceptr gemv_partial; /* fp32 [LB_GEMV_MAX_SPLITS][LB_GEMV_SCRATCH_N] */
     CUdeviceptr gemv_counters; /* u32 per column tile, self-resetting */
@@ -126,6 +129,7 @@ struct lb_ctx {
     size_t flush_bytes;
     uint64_t launches; /* kernels launched (or graph nodes replayed) since reset */
     int pdl;           /* use programmatic dependent launch between kernels */
+    int chain_reserve; /* bytes of an SM's shared memory the GEMV chain leaves to a neighbouring kernel's CTA */
     int capturing;     /* stream capture in progress */
     uint64_t capture_launches0;
     char err[512];
@@ -135,6 +139,8 @@ struct lb_ctx {
 #define LB_GEMV_MAX_SPLITS 8 /* = the portable thread-block-cluster size */
 
 int lb_fail(lb_ctx* c, int status, const char* fmt, ...);
+int lb_gemv_tensor_maps(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, int K, int N, int box_groups,
+                        unsigned char* tm_w, unsigned char* tm_sc, unsigned char* tm_zr);
 int lb_cu(lb_ctx* c, CUresult r, const char* what);
 #define LB_CU(c, call)                                  \
     do {                                                \

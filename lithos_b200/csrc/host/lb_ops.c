@@ -53,6 +53,42 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
     return LB_OK;
 }
 
+/* The three tensor maps of one int4 matrix.
+ * qweight is viewed as [N/32 column blocks][K/8 packed rows][32 columns] so that ONE tiled load
+ * brings a whole stage: box = 8 column blocks x 16 rows x 32 columns, laid down as eight
+ * consecutive 2 KB boxes with the 128-byte swizzle.  Parts of the box past the matrix
+ * (ragged last tile, last group) are zero-filled and never used.  Scales fp16 [K/128, N] and
+ * zero-points u32 [K/128, N/8] come as boxes of box_groups rows x one column tile. */
+int lb_gemv_tensor_maps(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, int K, int N, int box_groups,
+                        unsigned char* tm_w, unsigned char* tm_sc, unsigned char* tm_zr) {
+    CUtensorMap tm;
+    cuuint64_t dims[3] = {32, (cuuint64_t)(K / 8), (cuuint64_t)(N / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)N * 4, 128};
+    cuuint32_t box[3] = {32, LB_GEMV_ROWS, LB_GEMV_TILE_N / 32};
+    cuuint32_t estr[3] = {1, 1, 1};
+    LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void*)qweight, dims, strides, box,
+                                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    memcpy(tm_w, &tm, sizeof tm);
+    cuuint64_t sdims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 128)};
+    cuuint64_t sstr[1] = {(cuuint64_t)N * 2};
+    cuuint32_t sbox[2] = {LB_GEMV_TILE_N, (cuuint32_t)box_groups};
+    LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)scales, sdims, sstr, sbox, estr,
+                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    memcpy(tm_sc, &tm, sizeof tm);
+    if (qzeros) {
+        cuuint64_t zdims[2] = {(cuuint64_t)(N / 8), (cuuint64_t)(K / 128)};
+        cuuint64_t zstr[1] = {(cuuint64_t)(N / 8) * 4};
+        cuuint32_t zbox[2] = {LB_GEMV_TILE_N / 8, (cuuint32_t)box_groups};
+        LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)qzeros, zdims, zstr, zbox,
+                                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+        memcpy(tm_zr, &tm, sizeof tm);
+    }
+    return LB_OK;
+}
+
 LB_API int lb_gemv_int4_fused(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y,
                               int K, int N, int x_mode, int y_mode, uint64_t aux0, uint64_t aux1, uint64_t x_out,
                               float eps) {
@@ -85,37 +121,7 @@ LB_API int lb_gemv_int4_fused(lb_ctx* c, uint64_t qweight, uint64_t scales, uint
     p.x_mode = x_mode; p.y_mode = y_mode;
     p.eps = eps;
     p.stages = g.stages;
-    /* qweight viewed as [N/32 column blocks][K/8 packed rows][32 columns] so that ONE tiled load
-     * brings a whole stage: box = 8 column blocks x 16 rows x 32 columns, laid down as eight
-     * consecutive 2 KB boxes with the 128-byte swizzle.  Parts of the box past the matrix
-     * (ragged last tile, last group) are zero-filled and never used. */
-    {
-        CUtensorMap tm;
-        cuuint64_t dims[3] = {32, (cuuint64_t)(K / 8), (cuuint64_t)(N / 32)};
-        cuuint64_t strides[2] = {(cuuint64_t)N * 4, 128};
-        cuuint32_t box[3] = {32, LB_GEMV_ROWS, LB_GEMV_TILE_N / 32};
-        cuuint32_t estr[3] = {1, 1, 1};
-        LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void*)qweight, dims, strides, box,
-                                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
-        memcpy(p.tmap, &tm, sizeof tm);
-        cuuint64_t sdims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 128)};
-        cuuint64_t sstr[1] = {(cuuint64_t)N * 2};
-        cuuint32_t sbox[2] = {LB_GEMV_TILE_N, (cuuint32_t)g.gps};
-        LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)scales, sdims, sstr, sbox, estr,
-                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
-        memcpy(p.tmap_sc, &tm, sizeof tm);
-        if (qzeros) {
-            cuuint64_t zdims[2] = {(cuuint64_t)(N / 8), (cuuint64_t)(K / 128)};
-            cuuint64_t zstr[1] = {(cuuint64_t)(N / 8) * 4};
-            cuuint32_t zbox[2] = {LB_GEMV_TILE_N / 8, (cuuint32_t)g.gps};
-            LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)qzeros, zdims, zstr, zbox,
-                                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
-            memcpy(p.tmap_zr, &tm, sizeof tm);
-        }
-    }
+    LB_TRY(lb_gemv_tensor_maps(c, qweight, scales, qzeros, K, N, g.gps, p.tmap, p.tmap_sc, p.tmap_zr));
     void* params[] = {&p};
     return lb_launch_cluster(c, LBK_gemv_int4_w256, (unsigned)g.tiles, (unsigned)g.ksplit, 1, GEMV_THREADS, g.smem, params, 1,
                              (unsigned)g.ksplit);

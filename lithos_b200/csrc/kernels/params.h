@@ -54,6 +54,50 @@ typedef struct {
     float eps;
 } lb_gemv_params;
 
+/* ---- chain of int4 GEMVs in ONE persistent launch (chain.cu) ------------------------------
+ * One CTA per SM.  The work of GEMV i is cut into units (column tile of 256, K-group of 128) in
+ * tile-major order and CTA c takes units [c*U/G, (c+1)*U/G).  The producer lane runs ahead of the
+ * consumers across GEMV boundaries (weights are constants), so HBM keeps streaming while the
+ * consumers finish a GEMV, meet at the grid barrier and build the next activation table. */
+#define LB_CHAIN_MAX_OPS 6
+#define LB_CHAIN_XCAP 48             /* K-groups of activations one CTA can hold (6144 values) */
+#define LB_CHAIN_GROUPS 2            /* consumer groups of 4 warps; group j takes every LB_CHAIN_GROUPS-th unit */
+#define LB_CHAIN_THREADS (LB_CHAIN_GROUPS * 128 + 32)
+#define LB_CHAIN_SCALE_OFF 16384     /* inside a stage: weights, then 256 fp16 scales, then 32 zero-point words */
+#define LB_CHAIN_ZERO_OFF (16384 + 512)
+#define LB_CHAIN_STAGE_STRIDE 17408  /* 17 KB: keeps every stage 1 KB aligned for the 128-byte swizzle */
+#define LB_CHAIN_MAX_TILES 1024
+
+typedef struct {
+    unsigned char tmap[128] __attribute__((aligned(64)));    /* qweight [N/32][K/8][32], box 8 x 16 x 32, 128-byte swizzle */
+    unsigned char tmap_sc[128] __attribute__((aligned(64))); /* scales fp16 [K/128, N], box 1 x 256 */
+    unsigned char tmap_zr[128] __attribute__((aligned(64))); /* qzeros u32 [K/128, N/8], box 1 x 32 */
+    const void* x;
+    void* y;
+    const void* aux0;
+    const void* aux1;
+    uint16_t* x_out;
+    int32_t K, N;
+    int32_t kg;        /* K / 128 */
+    int32_t units;     /* ceil(N/256) * kg */
+    int32_t x_mode, y_mode;
+    int32_t has_zeros; /* 0: zero-point 8 everywhere */
+    float eps;
+    int32_t pad_[8];
+} lb_chain_op;
+
+typedef struct {
+    lb_chain_op op[LB_CHAIN_MAX_OPS];
+    uint32_t* status;
+    uint32_t* sync;       /* [0] grid-barrier arrivals, [1] CTAs that left; both zero between launches */
+    uint32_t* tile_count; /* [LB_CHAIN_MAX_TILES] contributors that delivered their part of a tile; zero between GEMVs */
+    float* partial;       /* [gridDim.x][2][256] partial sums of tiles shared between CTAs */
+    int32_t n_ops;
+    int32_t stages;       /* ring depth */
+    int32_t trigger_op;   /* griddepcontrol.launch_dependents is issued when this GEMV starts */
+    int32_t pad_;
+} lb_chain_params;
+
 /* ---- dense bf16 [N,K] x vector ------------------------------------------ */
 typedef struct {
     const uint16_t* w; /* bf16 [N,K] row-major */
