@@ -368,6 +368,8 @@ def bench_decode(args, rank, local, world, dist):
     model.fill_synthetic(args.seed)
     prefill_state(model, cfg, lb, CTX_PREFILL)
     build_s = time.perf_counter() - t0
+    if args.no_chain:
+        model.set_chain(False)
     model.capture()
     kernels_per_step = model.step_kernels
 
@@ -477,6 +479,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64, help="decode workload: number of layers (64 = the benchmark definition)")
     ap.add_argument("--seed", type=int, default=20260413)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-chain", action="store_true", help="decode workload: one launch per projection instead of persistent chains")
     ap.add_argument("--ramp-s", type=float, default=1.5, help="seconds of untimed work before warm-up (clock ramp)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

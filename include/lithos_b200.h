@@ -141,21 +141,26 @@ int lb_gemv_int4_fused(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t 
 /* A chain of up to LB_GEMV_CHAIN_MAX fused GEMVs in ONE persistent launch (one CTA per SM, a grid
  * barrier between consecutive GEMVs): GEMV i+1 may read what GEMV i wrote.  Replaces a run of
  * consecutive launch_gemv calls of the decode step (src/launcher.s:829-933: out projection,
- * gate/up projection, down projection, next layer's input projections).  Same operand formats,
+ * gate/up projection, down projection, next layer's input projections).  Same activation formats,
  * x_mode / y_mode values and results (to rounding) as lb_gemv_int4_fused called once per entry.
- * LB_ERR_INVALID when a GEMV has fewer (tile, K-group) units than the GPU has SMs, or K > 6144
- * with so few column tiles that one CTA would need more than 6144 activations. */
-#define LB_GEMV_CHAIN_MAX 6
+ * The weights are read from a strip-packed copy in which every SM's columns are contiguous:
+ * lb_gemv_pack builds it once per matrix from the reference format (device to device;
+ * lb_gemv_packed_bytes gives the size of the buffer the caller allocates; swiglu = 1 for a matrix
+ * that will be used with the SwiGLU epilogue).  x and y of one entry must not overlap.
+ * LB_ERR_INVALID when a shape puts more than 256 columns on one SM. */
+#define LB_GEMV_CHAIN_MAX 8
 typedef struct {
-    uint64_t qweight, scales, qzeros; /* device pointers; qzeros 0 = zero-point 8 */
+    uint64_t packed;                  /* from lb_gemv_pack */
     uint64_t x, y, aux0, aux1, x_out; /* as in lb_gemv_int4_fused */
     int32_t K, N, x_mode, y_mode;
     float eps;
     int32_t reserved;
 } lb_gemv_op;
+size_t lb_gemv_packed_bytes(int K, int N);
+int lb_gemv_pack(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, int K, int N, int swiglu, uint64_t packed_out);
 int lb_gemv_chain(lb_ctx* ctx, const lb_gemv_op* ops, int n_ops);
-/* LB_OK when lb_gemv_chain accepts this shape on this GPU (no launch) */
-int lb_gemv_chain_supports(lb_ctx* ctx, int K, int N);
+/* LB_OK when lb_gemv_pack / lb_gemv_chain accept this shape on this GPU (no launch) */
+int lb_gemv_chain_supports(lb_ctx* ctx, int K, int N, int swiglu);
 /* bit-exact targets: W(k,n) = fma(float(q), s, -z*s) as fp32 [K,N]; q as u8 [K,N] */
 int lb_gptq_dequant(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t w_out_f32, int K, int N);
 int lb_gptq_unpack(lb_ctx* ctx, uint64_t qweight, uint64_t q_out_u8, int K, int N);
@@ -243,6 +248,9 @@ enum { LB_WS_SLOTS = 26, LB_WG_SLOTS = 3 }; /* slot indices as in src/launcher.s
 /* tp_rank / tp_size: tensor-parallel shard held by this context (1 GPU: 0 / 1). */
 int lb_model_create(lb_ctx* ctx, const lb_model_cfg* cfg, int tp_rank, int tp_size, lb_model** out);
 /* tensor parallel: the exchange buffers (all peers opened) this model's all-reduces go through */
+/* on (default): consecutive projections of the step are issued as one persistent launch (lb_gemv_chain);
+ * off: one launch per projection.  Takes effect at the next lb_model_decode / lb_model_capture. */
+int lb_model_set_chain(lb_model* m, int on);
 int lb_model_set_comm(lb_model* m, lb_comm* comm);
 void lb_model_destroy(lb_model* m);
 /* Host tensors of one layer in the reference's slot order (26 pointers, unused slots NULL) in

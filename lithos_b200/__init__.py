@@ -100,7 +100,9 @@ def lib() -> C.CDLL:
     sig("lb_gemv_int4_host", i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32)
     sig("lb_gemv_int4_fused", i32, vp, u64, u64, u64, u64, u64, i32, i32, i32, i32, u64, u64, u64, f32)
     sig("lb_gemv_chain", i32, vp, P(GemvOp), i32)
-    sig("lb_gemv_chain_supports", i32, vp, i32, i32)
+    sig("lb_gemv_chain_supports", i32, vp, i32, i32, i32)
+    sig("lb_gemv_packed_bytes", sz, i32, i32)
+    sig("lb_gemv_pack", i32, vp, u64, u64, u64, i32, i32, i32, u64)
     sig("lb_set_chain_reserve", None, vp, i32)
     sig("lb_gptq_dequant", i32, vp, u64, u64, u64, u64, i32, i32)
     sig("lb_gptq_unpack", i32, vp, u64, u64, i32, i32)
@@ -117,7 +119,7 @@ def lib() -> C.CDLL:
 
 class GemvOp(C.Structure):
     """lb_gemv_op (include/lithos_b200.h): one entry of a GEMV chain"""
-    _fields_ = [(n, C.c_uint64) for n in ("qweight", "scales", "qzeros", "x", "y", "aux0", "aux1", "x_out")] + \
+    _fields_ = [(n, C.c_uint64) for n in ("packed", "x", "y", "aux0", "aux1", "x_out")] + \
                [(n, C.c_int32) for n in ("K", "N", "x_mode", "y_mode")] + [("eps", C.c_float), ("reserved", C.c_int32)]
 
 
@@ -315,18 +317,24 @@ class Context:
                                              x_mode, y_mode, aux0.ptr if aux0 else 0, aux1.ptr if aux1 else 0,
                                              x_out.ptr if x_out else 0, eps))
 
+    def gemv_pack(self, qweight, scales, qzeros, K, N, swiglu=False) -> "DeviceBuffer":
+        """strip-packed copy of a reference-format matrix for gemv_chain (device to device, once per matrix)"""
+        out = self.alloc(lib().lb_gemv_packed_bytes(K, N))
+        self._check(lib().lb_gemv_pack(self.h, qweight.ptr, scales.ptr, qzeros.ptr if qzeros else 0, K, N, 1 if swiglu else 0, out.ptr))
+        return out
+
     def gemv_chain(self, ops):
-        """ops: dicts with the keyword arguments of gemv_int4_fused; all of them run as ONE persistent launch"""
+        """ops: dicts (packed, x, y, K, N, x_mode, y_mode, aux0, aux1, x_out, eps); all of them run as ONE persistent launch"""
         arr = (GemvOp * len(ops))()
         for a, o in zip(arr, ops):
-            for name in ("qweight", "scales", "qzeros", "x", "y", "aux0", "aux1", "x_out"):
+            for name in ("packed", "x", "y", "aux0", "aux1", "x_out"):
                 b = o.get(name)
                 setattr(a, name, b.ptr if b else 0)
             a.K, a.N, a.x_mode, a.y_mode, a.eps = o["K"], o["N"], o["x_mode"], o["y_mode"], o.get("eps", 1e-6)
         self._check(lib().lb_gemv_chain(self.h, arr, len(ops)))
 
-    def gemv_chain_supports(self, K, N) -> bool:
-        return lib().lb_gemv_chain_supports(self.h, K, N) == 0
+    def gemv_chain_supports(self, K, N, swiglu=False) -> bool:
+        return lib().lb_gemv_chain_supports(self.h, K, N, 1 if swiglu else 0) == 0
 
     def gemv_int4_host(self, qweight, scales, qzeros, x, y, K, N, flags=0, weights_resident=False):
         self._check(lib().lb_gemv_int4_host(self.h, _ptr(qweight), _ptr(scales), _ptr(qzeros) if qzeros is not None else None,

@@ -82,6 +82,7 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
 #define LB_KERNELS(X)                 \
     X(gemv_int4_w256)                 \
     X(gemv_chain)                     \
+    X(gemv_pack_strips)               \
     X(gptq_dequant_f32)               \
     X(gptq_unpack_u8)                 \
     X(dense_bf16_gemv)                \
@@ -139,8 +140,7 @@ struct lb_ctx {
 #define LB_GEMV_MAX_SPLITS 8 /* = the portable thread-block-cluster size */
 
 int lb_fail(lb_ctx* c, int status, const char* fmt, ...);
-int lb_gemv_tensor_maps(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, int K, int N, int box_groups,
-                        unsigned char* tm_w, unsigned char* tm_sc, unsigned char* tm_zr);
+
 int lb_cu(lb_ctx* c, CUresult r, const char* what);
 #define LB_CU(c, call)                                  \
     do {                                                \

@@ -23,7 +23,11 @@ enum { /* src/launcher.s:92-141 */
     WG_EMBED = 0, WG_LM_HEAD = 1, WG_FINAL_NORM = 2
 };
 
-typedef struct { CUdeviceptr qweight, scales, qzeros; int K, N; } q4_mat;
+typedef struct {
+    CUdeviceptr qweight, scales, qzeros; /* the reference format */
+    CUdeviceptr packed;                  /* strip-packed copy for the persistent GEMV chain (0 = none) */
+    int K, N;
+} q4_mat;
 
 typedef struct {
     int is_fa;
@@ -55,6 +59,9 @@ struct lb_model {
     lb_comm* comm;   /* tensor parallel: exchange buffers */
     int vocab_s;     /* vocabulary rows on this shard */
     int ar_count;    /* all-reduces issued so far in the step being built (slot parity) */
+    int use_chain;   /* consecutive GEMVs of the step go out as one persistent launch (lb_gemv_chain) */
+    lb_gemv_op pend[LB_GEMV_CHAIN_MAX]; /* GEMVs collected since the last other kernel */
+    int n_pend;
 };
 
 extern int lb_comm_fill(const lb_comm* m, lb_tp_params* p, int slot, int n);
@@ -96,6 +103,7 @@ LB_API int lb_model_create(lb_ctx* c, const lb_model_cfg* cfg, int tp_rank, int 
     lb_model* m = (lb_model*)calloc(1, sizeof *m);
     if (!m) return LB_ERR_NOMEM;
     m->c = c; m->cfg = *cfg; m->tp_rank = tp_rank; m->tp_size = tp_size;
+    m->use_chain = 1;
     m->HV = cfg->dn_v_heads / tp_size; m->HK = cfg->dn_k_heads / tp_size; m->HQ = cfg->fa_q_heads / tp_size;
     m->HKV = cfg->fa_kv_heads >= tp_size ? cfg->fa_kv_heads / tp_size : 1; /* fewer KV heads than GPUs: replicated */
     m->inter_s = cfg->inter / tp_size;
@@ -337,6 +345,12 @@ LB_API int lb_model_load_layer(lb_model* m, int layer, const void* const* slots)
         shard_plan p;
         int st = plan_make(c, R, T, L->is_fa, which, slots, &p);
         if (st == LB_OK) st = build_q4(m, mats[which], p.src, p.cs, p.ci, p.N, p.k0, p.k1);
+        if (st == LB_OK && m->tp_size == 1 && lb_gemv_chain_supports(m->c, mats[which]->K, mats[which]->N, which == 2) == LB_OK) {
+            /* second copy in the chain kernel's layout: every SM's columns contiguous */
+            q4_mat* w = mats[which];
+            st = dalloc(m, &w->packed, lb_gemv_packed_bytes(w->K, w->N));
+            if (st == LB_OK) st = lb_gemv_pack(m->c, w->qweight, w->scales, w->qzeros, w->K, w->N, which == 2, w->packed);
+        }
         if (st == LB_OK && which == 0 && !L->is_fa) { /* conv taps of the shard's channels: the first C device columns */
             const int C = m->C_s, Cf = (2 * c->dn_k_heads + c->dn_v_heads) * 128;
             uint16_t* cw = (uint16_t*)malloc((size_t)4 * C * 2);
@@ -474,8 +488,25 @@ LB_API int lb_model_fill_synthetic(lb_model* m, uint64_t seed) {
 }
 
 /* ---- the step ------------------------------------------------------------------------------ */
+/* launch the GEMVs collected so far as one persistent chain */
+static int flush_gemvs(lb_model* m) {
+    int n = m->n_pend;
+    m->n_pend = 0;
+    return n ? lb_gemv_chain(m->c, m->pend, n) : LB_OK;
+}
+
 static int q4_gemv(lb_model* m, const q4_mat* w, CUdeviceptr x, CUdeviceptr y, int x_mode, int y_mode, CUdeviceptr aux0,
                    CUdeviceptr aux1, CUdeviceptr x_out) {
+    if (m->use_chain && w->packed) {
+        if (m->n_pend == LB_GEMV_CHAIN_MAX) LB_TRY(flush_gemvs(m));
+        lb_gemv_op* o = &m->pend[m->n_pend++];
+        memset(o, 0, sizeof *o);
+        o->packed = w->packed;
+        o->x = x; o->y = y; o->aux0 = aux0; o->aux1 = aux1; o->x_out = x_out;
+        o->K = w->K; o->N = w->N; o->x_mode = x_mode; o->y_mode = y_mode; o->eps = m->cfg.eps;
+        return LB_OK;
+    }
+    LB_TRY(flush_gemvs(m));
     return lb_gemv_int4_fused(m->c, w->qweight, w->scales, w->qzeros, x, y, w->K, w->N, x_mode, y_mode, aux0, aux1, x_out,
                               m->cfg.eps);
 }
@@ -500,6 +531,7 @@ static int issue_step(lb_model* m) {
     const int H = cfg->hidden;
     uint64_t launches0 = c->launches;
     m->ar_count = 0;
+    m->n_pend = 0;
     {
         void* params[] = {&m->embed, &m->d_token, &m->X, (void*)&H};
         LB_TRY(lb_launch(c, LBK_embed_bf16, (unsigned)((H + 1023) / 1024), 1, 1, 256, 0, params, 1));
@@ -519,6 +551,7 @@ static int issue_step(lb_model* m) {
             p.state = (float*)L->dn_state; p.out = (float*)m->mix_out; p.pos = (const int*)m->d_pos;
             p.HV = m->HV; p.HK = m->HK; p.hidden = H;
             void* params[] = {&p};
+            LB_TRY(flush_gemvs(m));
             LB_TRY(lb_launch(c, LBK_deltanet_layer_fused, (unsigned)m->HV, 4, 1, 128, 0, params, 1));
             LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32_HEADNORM_SILU, L->dn_norm, m->in_out + (size_t)C * 4));
         } else {
@@ -542,6 +575,7 @@ static int issue_step(lb_model* m) {
             for (int i = 0; i < cfg->rot_dims / 2; i++)
                 p.rope_freq[i] = exp2(-log2((double)cfg->rope_theta) * (double)i / (double)(cfg->rot_dims / 2));
             void* params[] = {&p};
+            LB_TRY(flush_gemvs(m));
             LB_TRY(lb_launch(c, LBK_attn_decode_split, (unsigned)m->HKV, (unsigned)p.splits, 1, 256,
                              lb_attn_smem(m->HQ / m->HKV), params, 1));
             LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32, 0, 0));
@@ -550,6 +584,7 @@ static int issue_step(lb_model* m) {
         LB_TRY(row_parallel(m, &L->w_down, m->mlp_m, LB_X_F16, 0, 0));
     }
     if (!m->globals_loaded) return lb_fail(c, LB_ERR_STATE, "model: globals have no weights");
+    LB_TRY(flush_gemvs(m));
     LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, m->vocab_s, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps,
                            m->cand_val, m->cand_idx));
     if (m->tp_size == 1) {
@@ -567,6 +602,12 @@ static int issue_step(lb_model* m) {
         LB_TRY(lb_launch(c, LBK_tp_argmax_exchange, 1, 1, 1, 1024, 0, params, 1));
     }
     m->step_kernels = (int)(c->launches - launches0);
+    return LB_OK;
+}
+
+LB_API int lb_model_set_chain(lb_model* m, int on) {
+    if (!m) return LB_ERR_INVALID;
+    m->use_chain = on ? 1 : 0;
     return LB_OK;
 }
 
@@ -645,6 +686,7 @@ LB_API void lb_model_destroy(lb_model* m) {
                 if (q[i]->qweight) lb_drv.MemFree(q[i]->qweight);
                 if (q[i]->scales) lb_drv.MemFree(q[i]->scales);
                 if (q[i]->qzeros) lb_drv.MemFree(q[i]->qzeros);
+                if (q[i]->packed) lb_drv.MemFree(q[i]->packed);
             }
             CUdeviceptr p[] = {L->input_norm, L->post_norm, L->proj_a, L->proj_b, L->a_log, L->dt_bias, L->conv_w, L->dn_norm,
                                L->dn_state, L->conv_ring, L->q_norm, L->k_norm, L->k_cache, L->v_cache};

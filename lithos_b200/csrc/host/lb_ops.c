@@ -59,7 +59,7 @@ static int gemv_plan(lb_ctx* c, int K, int N, gemv_geom* g) {
  * consecutive 2 KB boxes with the 128-byte swizzle.  Parts of the box past the matrix
  * (ragged last tile, last group) are zero-filled and never used.  Scales fp16 [K/128, N] and
  * zero-points u32 [K/128, N/8] come as boxes of box_groups rows x one column tile. */
-int lb_gemv_tensor_maps(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, int K, int N, int box_groups,
+static int lb_gemv_tensor_maps(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, int K, int N, int box_groups,
                         unsigned char* tm_w, unsigned char* tm_sc, unsigned char* tm_zr) {
     CUtensorMap tm;
     cuuint64_t dims[3] = {32, (cuuint64_t)(K / 8), (cuuint64_t)(N / 32)};

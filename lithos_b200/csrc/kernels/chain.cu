@@ -6,390 +6,457 @@
 // of every launch cost as much as the streaming itself.  Here the GEMVs between two token-mixer
 // kernels (out projection, gate/up projection with SwiGLU, down projection, next layer's input
 // projection) are one launch of one CTA per SM:
-//   * Work of GEMV i = units (column tile of 256, K-group of 128), tile-major; CTA c owns the
-//     contiguous unit range [c*U/G, (c+1)*U/G), so every CTA streams the same number of bytes.
-//   * One producer lane per CTA feeds a ring of 17 KB stages (16 KB of packed weights, the
-//     group's 256 scales, its 32 zero-point words) with tiled TMA loads.  Weights are constants:
-//     the producer never waits for a grid barrier, it runs on into the NEXT GEMV's units while
-//     the consumers finish the current one.  The ring of all SMs (about 25 MB) is the prefetch
-//     buffer that keeps HBM busy across GEMV boundaries.
-//   * Consumers (groups of 4 warps, one unit at a time per group) use the same exact integer
-//     tensor-core dot product as gemv_int4_w256 (gemv_core.cuh).
-//   * A tile split between CTAs is summed in a fixed order: every contributor stores its
-//     partial, the last one to arrive (a counter per tile) adds the partials in CTA order and
-//     runs the epilogue.  Results do not depend on arrival order.
-//   * Between GEMVs the consumers meet at a grid barrier (an arrival counter in global memory,
-//     bounded spin).  All CTAs are resident because the grid is one CTA per SM and a CTA takes
-//     more than half of an SM's shared memory.
+//   * CTA c owns whole columns of every GEMV (a strip of octets, all of K), so its results are
+//     final: no partial sums, counters or atomics between CTAs, and the sum order is fixed.
+//   * The weights come from a strip-packed copy (gemv_pack_strips below; layout in params.h) in
+//     which a CTA's strip is one contiguous byte range, cut into stages of 4 K-groups x 16
+//     columns (4352 bytes).  Stage k of the CTA's list (all GEMVs of the chain, in order) belongs
+//     to warp k % 16: that warp requests it with a plain 1-D bulk copy into one of its own ring
+//     slots, waits for it on the slot's mbarrier, consumes it alone and refills the slot with its
+//     next stage.  No producer warp, no block-wide synchronisation inside a GEMV.  Weights are
+//     constants, so a warp's requests run on into the NEXT GEMV of the chain while the block
+//     finishes the current one: the rings of all SMs keep HBM busy across GEMV boundaries.
+//   * A stage item is (K-group, pair of octets): two 128-bit loads per lane give the packed words,
+//     four m16n8k32 u8 x s8 tensor-core steps give the exact integer dot products of 16 columns
+//     against the three activation digit planes (gemv_core.cuh); scale and zero-point are applied
+//     in fp32 per group.  Per-column sums are added in a fixed order (stage order inside a warp,
+//     then warp order).
+//   * Between GEMVs the block meets the other blocks at a grid barrier (an arrival counter in
+//     global memory, bounded spin).  All CTAs are resident: the grid is one CTA per SM and a CTA
+//     takes more than half of an SM's shared memory.
 // Activations written inside the launch are read through L2 only (ld.global.cg).
 #include "gemv_core.cuh"
 
-#define CH_NG LB_CHAIN_GROUPS
-#define CH_CONSUMERS (CH_NG * 128)
+#define CH_W LB_CHAIN_WARPS
+#define CH_GC LB_CHAIN_GC
 
-__device__ __forceinline__ void ch_bar() { asm volatile("bar.sync 1, %0;" ::"n"(CH_CONSUMERS) : "memory"); }
 __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ long long ch_start(int c, int U, int G) { return (long long)c * U / G; }
-// the CTA whose range holds unit u (ranges are non-empty: U >= G is checked by the host)
-__device__ __forceinline__ int ch_owner(long long u, int U, int G) { return (int)(((u + 1) * G - 1) / U); }
+// first octet of CTA c's strip
+__device__ __forceinline__ int ch_start(int c, int units, int upo, int G) { return (int)((long long)c * units / G) * upo; }
 
 struct __align__(16) ch_shared {
-    float red[CH_NG][LB_GEMV_TILE_N]; // first: written with 16-byte stores
-    float scratch[48];
-    int xsum[LB_CHAIN_XCAP];
+    float vals[LB_CHAIN_MAX_OCTETS * 8];
+    float scratch[64];
+    int op_n0[LB_CHAIN_MAX_OPS];     // first octet of this CTA's strip, per GEMV
+    int op_no[LB_CHAIN_MAX_OPS];     // octets in the strip
+    int op_np[LB_CHAIN_MAX_OPS];     // pairs in the strip (a trailing single octet counts as one)
+    int op_nch[LB_CHAIN_MAX_OPS];    // chunks of CH_GC K-groups per pair
     uint32_t bad;  // a bounded wait ran out (set by any thread at any time)
-    uint32_t snap; // copy of bad taken by thread 0 before a consumer barrier: the value all consumers act on together
-    uint32_t last; // this CTA delivered the last part of the current tile
+    uint32_t snap; // copy of bad taken by thread 0 before a block barrier: the value all threads act on together
 };
 
+// position in the CTA's stage list: GEMV o, pair of that GEMV's strip, chunk of CH_GC K-groups of the pair
+struct ch_cursor {
+    int o, pair, chunk;
+    // move `by` stages forward (chunks run fastest, then pairs, then GEMVs)
+    __device__ __forceinline__ void advance(const ch_shared& sh, int n_ops, int by) {
+        chunk += by;
+        while (o < n_ops) {
+            const int nch = sh.op_nch[o];
+            while (chunk >= nch && pair < sh.op_np[o]) { chunk -= nch; ++pair; }
+            if (pair < sh.op_np[o]) return;
+            ++o; // past the last pair of this GEMV: the rest counts from the start of the next one
+            pair = 0;
+        }
+    }
+};
+
+struct ch_stage {
+    const unsigned char* src;
+    uint32_t bytes;
+    int g0, gcount, recb;
+};
+
+__device__ __forceinline__ ch_stage ch_decode(const lb_chain_params& p, const ch_shared& sh, const ch_cursor& k) {
+    const lb_chain_op& op = p.op[k.o];
+    ch_stage s;
+    s.recb = 2 * k.pair + 1 < sh.op_no[k.o] ? 2 * LB_CHAIN_RECORD : LB_CHAIN_RECORD; // a trailing single octet has half records
+    s.g0 = k.chunk * CH_GC;
+    s.gcount = min(CH_GC, op.kg - s.g0);
+    s.src = op.packed + ((size_t)sh.op_n0[k.o] * op.kg + (size_t)k.pair * op.kg * 2) * LB_CHAIN_RECORD + (size_t)s.g0 * s.recb;
+    s.bytes = (uint32_t)(s.gcount * s.recb);
+    return s;
+}
+
+// D(16x8, s32) += A(16x32, u8) * B(32x8, s8); not volatile: a pure function of its operands, free to be scheduled
+__device__ __forceinline__ void imma_nv(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One stage: up to CH_GC items (K-group, pair of octets), 16 columns x 128 k each, as exact integer dot products
+// against the digit planes.  Fragment rows 0-7 are the columns of the first octet, rows 8-15 those of the second.
+// All loads first, then the tensor-core steps of the items interleaved (independent accumulator chains), then the
+// fp32 part: the latencies of one item hide behind the others.  PARTIAL = false: all CH_GC groups are there.
+template <bool PARTIAL>
+__device__ __forceinline__ void ch_stage_items(const unsigned char* stage, int g0, int gcount, bool full_pair, const uint32_t* xdig,
+                                               const float* xsumf, int lane, float lane_mul, float& acc_a, float& acc_b) {
+    const int g = lane >> 2, t = lane & 3;
+    const int recb = full_pair ? 2 * LB_CHAIN_RECORD : LB_CHAIN_RECORD;
+    // digit_row_word(16 G + t + 4 q) = 104 G + 26 q + 6 t
+    const uint32_t* xrow = xdig + 104 * g0 + 6 * t + 2 * g;
+    uint4 wa[CH_GC], wb[CH_GC];
+    uint2 xb[CH_GC][4];
+#pragma unroll
+    for (int j = 0; j < CH_GC; ++j) {
+        const bool on = !PARTIAL || j < gcount;
+        const unsigned char* rec = stage + j * recb;
+        wa[j] = on ? *reinterpret_cast<const uint4*>(rec + lane * 16) : make_uint4(0u, 0u, 0u, 0u);
+        wb[j] = on && full_pair ? *reinterpret_cast<const uint4*>(rec + LB_CHAIN_RECORD + lane * 16) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            xb[j][q] = on && g < 3 ? *reinterpret_cast<const uint2*>(xrow + 104 * j + 26 * q) : make_uint2(0u, 0u);
+    }
+    int d[CH_GC][4];
+#pragma unroll
+    for (int j = 0; j < CH_GC; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0;
+    const uint32_t M = 0x0f0f0f0fu;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < CH_GC; ++j) {
+            const uint32_t a = q == 0 ? wa[j].x : q == 1 ? wa[j].y : q == 2 ? wa[j].z : wa[j].w;
+            const uint32_t b = q == 0 ? wb[j].x : q == 1 ? wb[j].y : q == 2 ? wb[j].z : wb[j].w;
+            imma_nv(d[j], a & M, b & M, (a >> 4) & M, (b >> 4) & M, xb[j][q].x, xb[j][q].y);
+        }
+#pragma unroll
+    for (int j = 0; j < CH_GC; ++j)
+        if (!PARTIAL || j < gcount) {
+            const unsigned char* rec = stage + j * recb;
+            const float xs_f = t == 0 ? xsumf[g0 + j] : 0.f;
+            // (scale, zero-point) of column g; t = 0 holds digit planes 0 and 1, t = 1 plane 2 (and the empty plane 3)
+            const float2 sa = __half22float2(*reinterpret_cast<const __half2*>(rec + 512 + 4 * g));
+            acc_a = fmaf(sa.x, fmaf(-sa.y, xs_f, (float)(d[j][0] + (d[j][1] << 8)) * lane_mul), acc_a);
+            if (full_pair) {
+                const float2 sb = __half22float2(*reinterpret_cast<const __half2*>(rec + LB_CHAIN_RECORD + 512 + 4 * g));
+                acc_b = fmaf(sb.x, fmaf(-sb.y, xs_f, (float)(d[j][2] + (d[j][3] << 8)) * lane_mul), acc_b);
+            }
+        }
+}
+
 extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(const __grid_constant__ lb_chain_params p) {
-    extern __shared__ unsigned char smem_raw[];
+    extern __shared__ __align__(16) unsigned char smem[];
     __shared__ ch_shared sh;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int c = blockIdx.x, G = gridDim.x;
-    const int S = p.stages;
+    const int NS = p.slots; // ring slots of every warp
 
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    unsigned char* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint32_t* xdig = reinterpret_cast<uint32_t*>(smem + (size_t)S * LB_CHAIN_STAGE_STRIDE); // digit table, LB_CHAIN_XCAP groups
-    const int dig_words = (digit_row_word(LB_CHAIN_XCAP * LB_GEMV_ROWS) + 3) & ~3;
-    uint64_t* full = reinterpret_cast<uint64_t*>(xdig + dig_words);
-    uint64_t* empty = full + S;
+    // shared memory: [ring: CH_W * NS stages][digit table][group sums][per (pair, warp) column sums][mbarriers][stage lists]
+    uint32_t* xdig = reinterpret_cast<uint32_t*>(smem + (size_t)CH_W * NS * LB_CHAIN_STAGE_BYTES);
+    const int dig_words = (digit_row_word(p.table_rows) + 3) & ~3;
+    float* xsumf = reinterpret_cast<float*>(xdig + dig_words);             // [table_rows / 16] sum of each K-group's integers
+    float* red = xsumf + ((p.table_rows / LB_GEMV_ROWS + 3) & ~3);        // [max_pairs][CH_W][16]
+    uint64_t* full = reinterpret_cast<uint64_t*>(red + (size_t)p.max_pairs * CH_W * 16); // [CH_W * NS]
+    uint2* stage_tab = reinterpret_cast<uint2*>(full + CH_W * NS);                        // [CH_W][tab_len]
 
+    if (tid < CH_W * NS) mbar_init(&full[tid], 1);
+    if (tid < p.n_ops) {
+        const lb_chain_op& op = p.op[tid];
+        const int n0 = ch_start(c, op.units, op.upo, G), no = ch_start(c + 1, op.units, op.upo, G) - n0;
+        sh.op_n0[tid] = n0;
+        sh.op_no[tid] = no;
+        sh.op_np[tid] = (no + 1) / 2;
+        sh.op_nch[tid] = (op.kg + CH_GC - 1) / CH_GC;
+    }
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 4); // the four warps of the group that consumed the stage
-        }
         sh.bad = 0;
         sh.snap = 0;
-        sh.last = 0;
-        mbar_fence_init();
     }
+    mbar_fence_init();
     __syncthreads();
 
-    uint32_t issued = 0; // producer lane: stages handed to the TMA engine
-    if (warp == CH_NG * 4) {
-        // ---------------- producer: runs through every GEMV of the chain without stopping ----------------
+    // ---- this warp's stream: stages warp, warp + 16, warp + 32, ... of the CTA's list (all GEMVs of the chain).
+    //      The warp writes them down once as (offset, descriptor) words; stage number m of the stream lives in ring
+    //      slot m % NS of the warp. ----
+    uint2* tab = stage_tab + (size_t)warp * p.tab_len;
+    uint32_t n_mine = 0;
+    {
+        ch_cursor k = {0, 0, 0};
+        k.advance(sh, p.n_ops, warp);
+        while (k.o < p.n_ops && n_mine < (uint32_t)p.tab_len) {
+            const ch_stage st = ch_decode(p, sh, k);
+            const uint32_t full_pair = st.recb == 2 * LB_CHAIN_RECORD;
+            if (lane == 0)
+                tab[n_mine] = make_uint2((uint32_t)((st.src - p.op[k.o].packed) >> 4),
+                                         (uint32_t)k.o | ((uint32_t)k.pair << 4) | ((uint32_t)st.g0 << 12) | ((uint32_t)st.gcount << 24) |
+                                             (full_pair << 28));
+            ++n_mine;
+            k.advance(sh, p.n_ops, CH_W);
+        }
+    }
+    __syncwarp();
+    const uint64_t pol = l2_policy_evict_first();
+    uint32_t m_req = 0, m_use = 0;
+    auto request = [&]() { // weights never change: requests may run ahead of everything, the first ones start before griddepcontrol.wait
+        if (m_req >= n_mine) return;
         if (lane == 0) {
-            const uint64_t pol = l2_policy_evict_first();
-            bool ok = true;
-            for (int o = 0; o < p.n_ops && ok; ++o) {
-                const lb_chain_op& op = p.op[o];
-                const long long u0 = ch_start(c, op.units, G), u1 = ch_start(c + 1, op.units, G);
-                const uint32_t bytes = LB_GEMV_STAGE_BYTES + 512u + (op.has_zeros ? 128u : 0u);
-                for (long long u = u0; u < u1; ++u, ++issued) {
-                    const int s = issued % S;
-                    if (issued >= (uint32_t)S && !mbar_wait(&empty[s], ((issued / S) - 1) & 1)) {
-                        atomicExch(p.status, LB_DEV_TIMEOUT_EMPTY);
-                        sh.bad = 1;
-                        ok = false;
-                        break;
-                    }
-                    if (*reinterpret_cast<volatile uint32_t*>(&sh.bad)) { ok = false; break; }
-                    const int tile = (int)(u / op.kg), g = (int)(u - (long long)tile * op.kg);
-                    const uint32_t dst = smem_base + (uint32_t)s * LB_CHAIN_STAGE_STRIDE;
-                    mbar_arrive_expect_tx(&full[s], bytes); // parts of a box past the matrix are zero-filled and counted
-                    tma_load_2d(dst + LB_CHAIN_SCALE_OFF, op.tmap_sc, tile * LB_GEMV_TILE_N, g, &full[s], pol);
-                    if (op.has_zeros) tma_load_2d(dst + LB_CHAIN_ZERO_OFF, op.tmap_zr, tile * (LB_GEMV_TILE_N / 8), g, &full[s], pol);
-                    tma_load_stage(dst, op.tmap, tile * (LB_GEMV_TILE_N / 32), g * LB_GEMV_ROWS, &full[s], pol);
+            const uint2 e = tab[m_req];
+            const uint32_t slot = warp * NS + m_req % NS;
+            const uint32_t bytes = ((e.y >> 24) & 15u) * ((e.y >> 28) & 1u ? 2u * LB_CHAIN_RECORD : (uint32_t)LB_CHAIN_RECORD);
+            mbar_arrive_expect_tx(&full[slot], bytes);
+            bulk_g2s(smem + (size_t)slot * LB_CHAIN_STAGE_BYTES, p.op[e.y & 15u].packed + ((size_t)e.x << 4), bytes, &full[slot], pol);
+        }
+        ++m_req;
+    };
+    for (int i = 0; i < NS; ++i) request();
+
+    const int fg = lane >> 2, ft = lane & 3;
+    const float lane_mul = ft == 0 ? 1.0f : (ft == 1 ? 65536.0f : 0.0f);
+    pdl_wait(); // activations and barrier words belong to the stream order
+    for (int o = 0; o < p.n_ops; ++o) {
+        const lb_chain_op& op = p.op[o];
+        const int n0 = sh.op_n0[o], no = sh.op_no[o];
+        if (o > 0) {
+            // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence();
+                atomicAdd(p.sync, 1u);
+                const unsigned target = (unsigned)o * (unsigned)G;
+                const uint64_t t0 = globaltimer_ns();
+                bool ok = false;
+                const bool dead = sh.bad || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u;
+                for (unsigned it = 0; it < LB_WAIT_SPINS && !dead; ++it) {
+                    if (ld_acquire_gpu(p.sync) >= target) { ok = true; break; }
+                    if ((it & 63u) == 63u && globaltimer_ns() - t0 > LB_WAIT_NS) break;
                 }
+                if (!ok) { atomicExch(p.status, LB_DEV_TIMEOUT_COUNTER); sh.bad = 1; }
+                __threadfence();
+                sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
+            }
+            __syncthreads();
+        }
+        if (o == p.trigger_op) pdl_launch_dependents();
+        if (sh.snap) break; // uniform: written before the barrier above, by one thread
+
+        // ---- the activation vector as exact integers: three signed base-256 digit planes ----
+        const int rows = op.K / 8;
+        for (int i = tid; i < ((no + 1) / 2) * CH_W * 16; i += LB_CHAIN_THREADS) red[i] = 0.f;
+        float rinv = 1.0f;
+        if (op.x_mode == LB_X_F32_RMSNORM) {
+            const float4* xv = reinterpret_cast<const float4*>(op.x);
+            float ss = 0.f;
+            for (int i = tid; i < op.K / 4; i += LB_CHAIN_THREADS) {
+                const float4 v = __ldcg(xv + i);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) sh.scratch[warp] = ss;
+            __syncthreads();
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < CH_W; ++w) tot += sh.scratch[w];
+            rinv = rsqrtf(tot / (float)op.K + op.eps);
+            __syncthreads();
+        }
+        float vmax = 0.f;
+        for (int rb = 0; rb < rows; rb += LB_CHAIN_THREADS) {
+            float v[8];
+            const int r = rb + tid;
+            const bool live = r < rows;
+            load_x_row<true>(op, live ? r * 8 : 0, live, rinv, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vmax = fmaxf(vmax, fabsf(v[j]));
+            if (live) { // parked as fp16 in the row's own digit slot until the scale is known
+                __half2 pk[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
+                                 __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
+                uint32_t* dst = xdig + digit_row_word(r);
+                const uint32_t* pw = reinterpret_cast<const uint32_t*>(pk);
+                *reinterpret_cast<uint2*>(dst) = make_uint2(pw[0], pw[1]);
+                *reinterpret_cast<uint2*>(dst + 2) = make_uint2(pw[2], pw[3]);
             }
         }
-    } else {
-        // ---------------- consumers ----------------
-        const int grp = warp >> 2, w4 = warp & 3;
-        const int fg = lane >> 2, ft = lane & 3;
-        const int cbase = w4 * 64; // this warp's first column inside the tile
-        const float lane_mul = ft == 0 ? 1.0f : (ft == 1 ? 65536.0f : 0.0f);
-        const bool has_digits = fg < 3;
-        pdl_wait(); // activations, barrier words and tile counters belong to the stream order
-        uint32_t it0 = 0; // ring position of this CTA's first unit of the current GEMV
-        for (int o = 0; o < p.n_ops; ++o) {
-            const lb_chain_op& op = p.op[o];
-            const int U = op.units, KG = op.kg;
-            const long long u0 = ch_start(c, U, G), u1 = ch_start(c + 1, U, G);
-            if (o > 0) {
-                // ---- grid barrier: every epilogue of GEMV o-1 is in memory before its results are read ----
-                ch_bar();
-                if (tid == 0) {
-                    __threadfence();
-                    atomicAdd(p.sync, 1u);
-                    const unsigned target = (unsigned)o * (unsigned)G;
-                    const uint64_t t0 = globaltimer_ns();
-                    bool ok = false;
-                    const bool dead = sh.bad || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u;
-                    for (unsigned it = 0; it < LB_WAIT_SPINS && !dead; ++it) {
-                        if (ld_acquire_gpu(p.sync) >= target) { ok = true; break; }
-                        if ((it & 63u) == 63u && globaltimer_ns() - t0 > LB_WAIT_NS) break;
-                    }
-                    if (!ok) { atomicExch(p.status, LB_DEV_TIMEOUT_COUNTER); sh.bad = 1; }
-                    __threadfence();
-                    sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
-                }
-                ch_bar();
-            }
-            if (o == p.trigger_op) pdl_launch_dependents();
-            if (sh.snap) break; // uniform: written before the barrier above, by one thread
-
-            // ---- activation table of the K-groups this CTA meets: exact integers, three signed base-256 digits ----
-            const int cnt = (u1 - u0) >= KG ? KG : (int)(u1 - u0); // groups in the (cyclic) window
-            const int gA = cnt == KG ? 0 : (int)(u0 % KG);
-            const int rows = cnt * LB_GEMV_ROWS;
-            float rinv = 1.0f;
-            if (op.x_mode == LB_X_F32_RMSNORM) {
-                const float4* xv = reinterpret_cast<const float4*>(op.x);
-                float ss = 0.f;
-                for (int i = tid; i < op.K / 4; i += CH_CONSUMERS) {
-                    const float4 v = __ldcg(xv + i);
-                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                }
-                ss = warp_sum(ss);
-                if (lane == 0) sh.scratch[warp] = ss;
-                ch_bar();
-                float tot = 0.f;
 #pragma unroll
-                for (int w = 0; w < CH_NG * 4; ++w) tot += sh.scratch[w];
-                rinv = rsqrtf(tot / (float)op.K + op.eps);
-                ch_bar();
-            }
-            float vmax = 0.f;
-            for (int rb = 0; rb < rows; rb += CH_CONSUMERS) {
-                float v[8];
-                const int r = rb + tid;
-                const bool live = r < rows;
-                int g = gA + (r >> 4);
-                if (g >= KG) g -= KG;
-                load_x_row<true>(op, live ? g * LB_GEMV_GROUP + (r & 15) * 8 : 0, live, rinv, v);
+        for (int o2 = 16; o2 > 0; o2 >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o2));
+        if (lane == 0) sh.scratch[32 + warp] = vmax;
+        __syncthreads();
+        vmax = 0.f;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) vmax = fmaxf(vmax, fabsf(v[j]));
-                if (live) { // parked as fp16 in the row's own digit slot until the scale is known
-                    __half2 pk[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
+        for (int w = 0; w < CH_W; ++w) vmax = fmaxf(vmax, sh.scratch[32 + w]);
+        int shift = 0; // max|x| * 2^shift in [2^21, 2^22); all-zero or non-finite vectors use shift 0
+        if (vmax > 0.f && vmax < 3.0e38f) shift = 21 - (int)((__float_as_uint(vmax) >> 23) & 0xffu) + 127;
+        const float qscale = __uint_as_float((uint32_t)(127 + shift) << 23);
+        const float unit = __uint_as_float((uint32_t)(127 - shift) << 23);
+        for (int rb = 0; rb < rows; rb += LB_CHAIN_THREADS) {
+            const int r = rb + tid;
+            const bool live = r < rows;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
+            if (live) { // the same thread parked this row above
+                const uint32_t* src = xdig + digit_row_word(r);
+                const uint2 p0 = *reinterpret_cast<const uint2*>(src), p1 = *reinterpret_cast<const uint2*>(src + 2);
+                const uint32_t pw[4] = {p0.x, p0.y, p1.x, p1.y};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pw[j]));
+                    v[2 * j] = f.x;
+                    v[2 * j + 1] = f.y;
+                }
+            }
+            int rs = 0;
+            uint32_t ev[3] = {0u, 0u, 0u}, od[3] = {0u, 0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                int t = __float2int_rn(v[j] * qscale);
+                rs += t;
+#pragma unroll
+                for (int d = 0; d < 3; ++d) {
+                    const int dg = d < 2 ? ((t + 128) & 255) - 128 : t; // signed digit in [-128,127]
+                    t = (t - dg) >> 8;
+                    const uint32_t byte = (uint32_t)dg & 0xffu;
+                    if (j & 1) od[d] |= byte << (8 * (j >> 1));
+                    else ev[d] |= byte << (8 * (j >> 1));
+                }
+            }
+#pragma unroll
+            for (int o2 = 8; o2 > 0; o2 >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o2); // the group's 16 rows
+            if (live) {
+                uint32_t* dst = xdig + digit_row_word(r);
+#pragma unroll
+                for (int d = 0; d < 3; ++d) *reinterpret_cast<uint2*>(dst + 2 * d) = make_uint2(ev[d], od[d]);
+                if ((lane & 15) == 0) xsumf[r >> 4] = (float)rs;
+                if (op.x_out && c == 0) { // every CTA holds the whole vector: one of them writes it out
+                    __half2 pl[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
                                      __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
-                    uint32_t* dst = xdig + digit_row_word(r);
-                    const uint32_t* pw = reinterpret_cast<const uint32_t*>(pk);
-                    *reinterpret_cast<uint2*>(dst) = make_uint2(pw[0], pw[1]);
-                    *reinterpret_cast<uint2*>(dst + 2) = make_uint2(pw[2], pw[3]);
+                    *reinterpret_cast<uint4*>(op.x_out + r * 8) = *reinterpret_cast<uint4*>(pl);
                 }
             }
-#pragma unroll
-            for (int o2 = 16; o2 > 0; o2 >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o2));
-            if (lane == 0) sh.scratch[16 + warp] = vmax;
-            ch_bar();
-            vmax = 0.f;
-#pragma unroll
-            for (int w = 0; w < CH_NG * 4; ++w) vmax = fmaxf(vmax, sh.scratch[16 + w]);
-            int shift = 0; // max|x| * 2^shift in [2^21, 2^22); all-zero or non-finite windows use shift 0
-            if (vmax > 0.f && vmax < 3.0e38f) shift = 21 - (int)((__float_as_uint(vmax) >> 23) & 0xffu) + 127;
-            const float qscale = __uint_as_float((uint32_t)(127 + shift) << 23);
-            const float unit = __uint_as_float((uint32_t)(127 - shift) << 23);
-            for (int rb = 0; rb < rows; rb += CH_CONSUMERS) {
-                const int r = rb + tid;
-                const bool live = r < rows;
-                float v[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = 0.f;
-                if (live) { // the same thread parked this row above
-                    const uint32_t* src = xdig + digit_row_word(r);
-                    const uint2 p0 = *reinterpret_cast<const uint2*>(src), p1 = *reinterpret_cast<const uint2*>(src + 2);
-                    const uint32_t pw[4] = {p0.x, p0.y, p1.x, p1.y};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pw[j]));
-                        v[2 * j] = f.x;
-                        v[2 * j + 1] = f.y;
-                    }
-                }
-                int rs = 0;
-                uint32_t ev[3] = {0u, 0u, 0u}, od[3] = {0u, 0u, 0u};
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    int t = __float2int_rn(v[j] * qscale);
-                    rs += t;
-#pragma unroll
-                    for (int d = 0; d < 3; ++d) {
-                        const int dg = d < 2 ? ((t + 128) & 255) - 128 : t; // signed digit in [-128,127]
-                        t = (t - dg) >> 8;
-                        const uint32_t byte = (uint32_t)dg & 0xffu;
-                        if (j & 1) od[d] |= byte << (8 * (j >> 1));
-                        else ev[d] |= byte << (8 * (j >> 1));
-                    }
-                }
-#pragma unroll
-                for (int o2 = 8; o2 > 0; o2 >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o2); // the group's 16 rows
-                if (live) {
-                    uint32_t* dst = xdig + digit_row_word(r);
-#pragma unroll
-                    for (int d = 0; d < 3; ++d) *reinterpret_cast<uint2*>(dst + 2 * d) = make_uint2(ev[d], od[d]);
-                    if ((lane & 15) == 0) sh.xsum[r >> 4] = rs;
-                    int g = gA + (r >> 4);
-                    if (g >= KG) g -= KG;
-                    if (op.x_out && g >= u0 && g < u1) { // the CTAs that own units of tile 0 write the vector out once
-                        __half2 pl[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
-                                         __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
-                        *reinterpret_cast<uint4*>(op.x_out + g * LB_GEMV_GROUP + (r & 15) * 8) = *reinterpret_cast<uint4*>(pl);
-                    }
-                }
-            }
-            ch_bar();
-
-            // ---- this CTA's units, one tile segment at a time ----
-            long long ua = u0;
-            while (ua < u1 && !sh.snap) {
-                const int tile = (int)(ua / KG);
-                const long long tile_u0 = (long long)tile * KG;
-                const long long ub = u1 < tile_u0 + KG ? u1 : tile_u0 + KG;
-                const int n0 = tile * LB_GEMV_TILE_N;
-                const int ncols = min(LB_GEMV_TILE_N, op.N - n0);
-                const bool live0 = cbase < ncols, live1 = cbase + 32 < ncols; // N % 32 == 0
-                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                // group grp takes the units whose ring position is grp modulo the number of groups
-                const uint32_t pos_a = it0 + (uint32_t)(ua - u0);
-                const int off = (grp + CH_NG - (int)(pos_a % CH_NG)) % CH_NG;
-                for (long long u = ua + off; u < ub; u += CH_NG) {
-                    const uint32_t idx = it0 + (uint32_t)(u - u0);
-                    const int s = idx % S;
-                    int slot = (int)(u - tile_u0) - gA; // position of the K-group in the activation table
-                    if (slot < 0) slot += KG;
-                    if (!mbar_wait(&full[s], (idx / S) & 1)) {
-                        if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); sh.bad = 1; }
-                        break;
-                    }
-                    const unsigned char* stage = smem + (size_t)s * LB_CHAIN_STAGE_STRIDE;
-                    uint2 sraw[2];
-                    uint32_t zw[2];
-                    sraw[0] = *reinterpret_cast<const uint2*>(stage + LB_CHAIN_SCALE_OFF + (cbase + fg * 4) * 2);
-                    sraw[1] = *reinterpret_cast<const uint2*>(stage + LB_CHAIN_SCALE_OFF + (cbase + 32 + fg * 4) * 2);
-                    zw[0] = zw[1] = 0x88888888u;
-                    if (op.has_zeros) {
-                        zw[0] = *reinterpret_cast<const uint32_t*>(stage + LB_CHAIN_ZERO_OFF + ((cbase + fg * 4) >> 3) * 4);
-                        zw[1] = *reinterpret_cast<const uint32_t*>(stage + LB_CHAIN_ZERO_OFF + ((cbase + 32 + fg * 4) >> 3) * 4);
-                    }
-                    int d[2][2][4]; // [box][column pair][fragment]
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) (&d[0][0][0])[i] = 0;
-                    if (live0) {
-                        const unsigned char* box = stage + (w4 * 2) * GEMV_BOX_BYTES;
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int r = 8 * (e >> 1) + 2 * ft + (e & 1);
-                            uint2 xb = make_uint2(0u, 0u);
-                            if (has_digits) xb = *reinterpret_cast<const uint2*>(xdig + digit_row_word(slot * LB_GEMV_ROWS + r) + 2 * fg);
-                            const uint32_t boff = r * 128 + ((fg ^ (r & 7)) << 4);
-                            const uint4 w0 = *reinterpret_cast<const uint4*>(box + boff);
-                            imma_words(d[0][0], w0.x, w0.y, xb);
-                            imma_words(d[0][1], w0.z, w0.w, xb);
-                            if (live1) {
-                                const uint4 w1 = *reinterpret_cast<const uint4*>(box + GEMV_BOX_BYTES + boff);
-                                imma_words(d[1][0], w1.x, w1.y, xb);
-                                imma_words(d[1][1], w1.z, w1.w, xb);
-                            }
-                        }
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty[s]); // this warp is done with the stage
-                    const float xs_f = ft == 0 ? (float)sh.xsum[slot] : 0.f;
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[b].x));
-                        const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(&sraw[b].y));
-                        const uint32_t z = zw[b] >> ((fg & 1) * 16);
-                        const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
-#pragma unroll
-                        for (int cc = 0; cc < 4; ++cc) {
-                            const int* f = d[b][cc >> 1];
-                            const int comb = f[(cc & 1) * 2] + (f[(cc & 1) * 2 + 1] << 8);
-                            const float zf = __uint_as_float(0x4B000000u | ((z >> (4 * cc)) & 0xFu)) - 8388608.0f;
-                            acc[b * 4 + cc] = fmaf(sc[cc], fmaf(-zf, xs_f, (float)comb * lane_mul), acc[b * 4 + cc]);
-                        }
-                    }
-                }
-                // ---- segment done: the groups' sums, in group order ----
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float a = acc[i];
-                    a += __shfl_xor_sync(0xffffffffu, a, 1);
-                    a += __shfl_xor_sync(0xffffffffu, a, 2);
-                    acc[i] = a * unit;
-                }
-                if (ft == 0) {
-                    *reinterpret_cast<float4*>(&sh.red[grp][cbase + fg * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                    *reinterpret_cast<float4*>(&sh.red[grp][cbase + 32 + fg * 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
-                }
-                ch_bar();
-                const bool owner = tid < LB_GEMV_TILE_N;
-                float v = 0.f;
-                if (owner) {
-#pragma unroll
-                    for (int gq = 0; gq < CH_NG; ++gq) v += sh.red[gq][tid];
-                }
-                bool run_epilogue = true;
-                if (ub - ua < KG) {
-                    // the tile is shared: deliver this part; the last contributor adds all parts in CTA order
-                    const int first = ch_owner(tile_u0, U, G), lastc = ch_owner(tile_u0 + KG - 1, U, G);
-                    const int myslot = tile == (int)(u0 / KG) ? 0 : 1;
-                    if (owner) __stcg(p.partial + ((size_t)c * 2 + myslot) * LB_GEMV_TILE_N + tid, v);
-                    __threadfence();
-                    ch_bar();
-                    if (tid == 0) {
-                        const unsigned old = atomicAdd(p.tile_count + tile, 1u);
-                        const bool last = old == (unsigned)(lastc - first);
-                        if (last) p.tile_count[tile] = 0u; // everybody has arrived: ready for the next GEMV
-                        sh.last = last ? 1u : 0u;
-                    }
-                    ch_bar();
-                    run_epilogue = sh.last != 0u;
-                    if (run_epilogue && owner) {
-                        __threadfence();
-                        v = 0.f;
-                        for (int cc = first; cc <= lastc; ++cc) {
-                            const int sl = tile == (int)(ch_start(cc, U, G) / KG) ? 0 : 1;
-                            v += __ldcg(p.partial + ((size_t)cc * 2 + sl) * LB_GEMV_TILE_N + tid);
-                        }
-                    }
-                }
-                if (run_epilogue) {
-                    if (op.y_mode == LB_Y_SWIGLU_F16) {
-                        // columns come in interleaved 64-wide (gate, up) blocks: [0,64) gate, [64,128) up, ...
-                        ch_bar();
-                        if (owner) sh.red[0][tid] = v;
-                        ch_bar();
-                        if (tid < ncols / 2) {
-                            const int blk = tid >> 6, i = tid & 63;
-                            const float gate = sh.red[0][blk * 128 + i], up = sh.red[0][blk * 128 + 64 + i];
-                            reinterpret_cast<__half*>(op.y)[n0 / 2 + tid] = __float2half_rn(siluf_dev(gate) * up);
-                        }
-                    } else if (owner && tid < ncols) {
-                        const int n = n0 + tid;
-                        if (op.y_mode == LB_Y_F16) reinterpret_cast<__half*>(op.y)[n] = __float2half_rn(v);
-                        else if (op.y_mode == LB_Y_F32) reinterpret_cast<float*>(op.y)[n] = v;
-                        else reinterpret_cast<float*>(op.y)[n] = __ldcg(reinterpret_cast<float*>(op.y) + n) + v;
-                    }
-                }
-                if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
-                ch_bar(); // sh.red and sh.last are reused by the next segment; sh.snap is the same for everyone
-                ua = ub;
-            }
-            it0 += (uint32_t)(u1 - u0);
         }
-        // ---- leave: the last CTA out zeroes the barrier words for the next launch ----
-        ch_bar();
-        if (tid == 0) {
-            __threadfence();
-            const unsigned old = atomicAdd(p.sync + 1, 1u);
-            if (old == (unsigned)G - 1u) {
-                p.sync[0] = 0u;
-                p.sync[1] = 0u;
+        __syncthreads();
+
+        // ---- this warp's stages of GEMV o.  Column sums stay in registers while consecutive stages belong to
+        //      the same pair, and go to this warp's own row of `red` when the pair changes. ----
+        float acc_a = 0.f, acc_b = 0.f;
+        int cur_pair = -1;
+        auto flush = [&]() {
+            if (cur_pair < 0) return;
+            float a = acc_a, b = acc_b;
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            b += __shfl_xor_sync(0xffffffffu, b, 1);
+            b += __shfl_xor_sync(0xffffffffu, b, 2);
+            if (ft == 0) { // only this warp touches row (cur_pair, warp): plain read-modify-write, fixed order
+                float* row = red + ((size_t)cur_pair * CH_W + warp) * 16;
+                row[fg] += a;
+                row[8 + fg] += b;
             }
+            acc_a = acc_b = 0.f;
+        };
+        while (m_use < n_mine) {
+            const uint2 e = tab[m_use];
+            if ((int)(e.y & 15u) != o) break; // the stream has reached the next GEMV
+            const uint32_t slot = warp * NS + m_use % NS;
+            if (!__all_sync(0xffffffffu, mbar_wait(&full[slot], (m_use / NS) & 1))) { // the same answer in every lane
+                if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); sh.bad = 1; }
+                break;
+            }
+            const int pair = (int)((e.y >> 4) & 255u), g0 = (int)((e.y >> 12) & 4095u), gcount = (int)((e.y >> 24) & 15u);
+            const bool full_pair = (e.y >> 28) & 1u;
+            if (pair != cur_pair) {
+                flush();
+                cur_pair = pair;
+            }
+            const unsigned char* stage = smem + (size_t)slot * LB_CHAIN_STAGE_BYTES;
+            if (gcount == CH_GC) ch_stage_items<false>(stage, g0, gcount, full_pair, xdig, xsumf, lane, lane_mul, acc_a, acc_b);
+            else ch_stage_items<true>(stage, g0, gcount, full_pair, xdig, xsumf, lane, lane_mul, acc_a, acc_b);
+            ++m_use;
+            __syncwarp(); // every lane has consumed its words (the sums above depend on them): the slot can be overwritten
+            request();    // refill this slot with the stream's next stage (maybe of a later GEMV)
+        }
+        flush();
+        __syncthreads();
+
+        // ---- column sums over the warps, in warp order; epilogue ----
+        const int ncol = no * 8;
+        if (tid < ncol) {
+            const int oct = tid >> 3, g = tid & 7;
+            const float* col = red + (size_t)(oct >> 1) * CH_W * 16 + (oct & 1) * 8 + g;
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < CH_W; ++w) v += col[w * 16];
+            v *= unit;
+            if (op.y_mode == LB_Y_SWIGLU_F16) {
+                sh.vals[tid] = v;
+            } else {
+                const int n = n0 * 8 + tid;
+                if (op.y_mode == LB_Y_F16) reinterpret_cast<__half*>(op.y)[n] = __float2half_rn(v);
+                else if (op.y_mode == LB_Y_F32) reinterpret_cast<float*>(op.y)[n] = v;
+                else reinterpret_cast<float*>(op.y)[n] = __ldcg(reinterpret_cast<float*>(op.y) + n) + v;
+            }
+        }
+        if (op.y_mode == LB_Y_SWIGLU_F16) {
+            // the strip is made of (gate octet, up octet) pairs; pair P of the matrix gives y[8P .. 8P+7]
+            __syncthreads();
+            if (tid < ncol / 2) {
+                const int pr = tid >> 3, g = tid & 7;
+                const float gate = sh.vals[pr * 16 + g], up = sh.vals[pr * 16 + 8 + g];
+                reinterpret_cast<__half*>(op.y)[(n0 / 2) * 8 + tid] = __float2half_rn(siluf_dev(gate) * up);
+            }
+        }
+        if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
+        __syncthreads(); // red / vals are reused by the next GEMV; sh.snap is the same for everyone
+        if (sh.snap) break;
+    }
+    // ---- leave: the last CTA out zeroes the barrier words for the next launch ----
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned old = atomicAdd(p.sync + 1, 1u);
+        if (old == (unsigned)G - 1u) {
+            p.sync[0] = 0u;
+            p.sync[1] = 0u;
         }
     }
-    __syncthreads();
-    // after a failed wait: no copy may still be in flight into this CTA's shared memory when it exits
-    if (sh.bad && warp == CH_NG * 4 && lane == 0) {
-        for (uint32_t k = issued > (uint32_t)S ? issued - S : 0u; k < issued; ++k) mbar_wait(&full[k % S], (k / S) & 1);
+    // no copy may still be in flight into this CTA's shared memory when it exits (only after a failed wait can
+    // requested stages be left unconsumed)
+    for (; m_use < m_req; ++m_use) mbar_wait(&full[warp * NS + m_use % NS], (m_use / NS) & 1);
+}
+
+// ---------------------------------------------------------------------------
+// Reference format (qweight [K/8,N], scales [K/128,N], qzeros [K/128,N/8]) -> strip-packed records
+// for G CTAs (layout in params.h).  One thread per 32-bit word of the output; run once per matrix.
+// With swiglu set, the input columns are the interleaved 64-wide (gate, up) blocks of the
+// LB_Y_SWIGLU_F16 contract and unit P of the output is (gate octet, up octet) of y[8P .. 8P+7].
+// ---------------------------------------------------------------------------
+extern "C" __global__ void gemv_pack_strips(const __grid_constant__ lb_pack_params p) {
+    const int KG = p.K / LB_GEMV_GROUP, NO = p.N / 8;
+    const int upo = p.swiglu ? 2 : 1, units = NO / upo;
+    const int RW = LB_CHAIN_RECORD / 4; // words per record
+    const long long total = (long long)NO * KG * RW;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int word = (int)(i % RW);
+        const long long r = i / RW;
+        const int O = (int)(r / KG), q = (int)(r % KG); // global octet, K-group
+        int lo = 0, hi = p.G; // the CTA whose strip holds octet O: largest c with start(c) <= O
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if ((int)((long long)mid * units / p.G) * upo <= O) lo = mid; else hi = mid;
+        }
+        const int n0 = (int)((long long)lo * units / p.G) * upo, no = (int)((long long)(lo + 1) * units / p.G) * upo - n0;
+        const int oi = O - n0, pair = oi >> 1;
+        const int recw = (2 * pair + 1 < no ? 2 : 1) * RW; // words of one K-group of this pair
+        const size_t dst = ((size_t)n0 * KG + (size_t)pair * KG * 2) * RW + (size_t)q * recw + (size_t)(oi & 1) * RW + word;
+        int col0; // source columns of octet O
+        if (p.swiglu) {
+            const int P = O >> 1, blk = P >> 3;
+            col0 = blk * 128 + (O & 1) * 64 + (P & 7) * 8;
+        } else col0 = O * 8;
+        uint32_t out;
+        if (word < 128) {
+            const int lane = word >> 2, j = word & 3, g = lane >> 2, t = lane & 3;
+            out = p.qweight[(size_t)(q * LB_GEMV_ROWS + t + 4 * j) * p.N + col0 + g];
+        } else {
+            const int g = word - 128;
+            const uint32_t sc = p.scales[(size_t)q * p.N + col0 + g];
+            const uint32_t z = p.qzeros ? (p.qzeros[(size_t)q * (p.N / 8) + (col0 >> 3)] >> (4 * g)) & 0xFu : 8u;
+            out = sc | ((uint32_t)__half_as_ushort(__float2half_rn((float)z)) << 16);
+        }
+        p.out[dst] = out;
     }
 }

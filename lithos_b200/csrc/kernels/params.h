@@ -55,48 +55,64 @@ typedef struct {
 } lb_gemv_params;
 
 /* ---- chain of int4 GEMVs in ONE persistent launch (chain.cu) ------------------------------
- * One CTA per SM.  The work of GEMV i is cut into units (column tile of 256, K-group of 128) in
- * tile-major order and CTA c takes units [c*U/G, (c+1)*U/G).  The producer lane runs ahead of the
- * consumers across GEMV boundaries (weights are constants), so HBM keeps streaming while the
- * consumers finish a GEMV, meet at the grid barrier and build the next activation table. */
-#define LB_CHAIN_MAX_OPS 6
-#define LB_CHAIN_XCAP 48             /* K-groups of activations one CTA can hold (6144 values) */
-#define LB_CHAIN_GROUPS 2            /* consumer groups of 4 warps; group j takes every LB_CHAIN_GROUPS-th unit */
-#define LB_CHAIN_THREADS (LB_CHAIN_GROUPS * 128 + 32)
-#define LB_CHAIN_SCALE_OFF 16384     /* inside a stage: weights, then 256 fp16 scales, then 32 zero-point words */
-#define LB_CHAIN_ZERO_OFF (16384 + 512)
-#define LB_CHAIN_STAGE_STRIDE 17408  /* 17 KB: keeps every stage 1 KB aligned for the 128-byte swizzle */
-#define LB_CHAIN_MAX_TILES 1024
+ * One CTA per SM; CTA c owns a strip of whole columns of every GEMV (all of K), so no partial sums
+ * cross CTAs.  The weights are read from a strip-packed copy made once by gemv_pack_strips:
+ *   column unit = an octet of 8 columns (for the SwiGLU epilogue a unit is two octets: gate, up);
+ *   CTA c owns octets [start(c), start(c+1)), start(c) = floor(c * units / G) * octets_per_unit,
+ *   taken two at a time (a pair = the 16 rows of one tensor-core step; a strip with an odd number
+ *   of octets ends with a single);
+ *   per (octet, K-group) one 544-byte record
+ *     [32 lanes x 16 B : lane (g = column in octet, t) holds the packed words of rows t, t+4, t+8, t+12 of the group]
+ *     [8 x (fp16 scale, fp16 zero-point)];
+ *   the strip is contiguous and pair-major: strip base = start(c) * KG * 544, then for every pair all
+ *   K-groups in order, each group as [record of the first octet][record of the second octet].
+ * A pipeline stage is LB_CHAIN_GC consecutive K-groups of one pair (4352 bytes), brought by one 1-D
+ * bulk copy and consumed by ONE warp. */
+#define LB_CHAIN_MAX_OPS 8
+#define LB_CHAIN_WARPS 16            /* consumer warps; every warp streams its own stages */
+#define LB_CHAIN_THREADS (LB_CHAIN_WARPS * 32)
+#define LB_CHAIN_RECORD 544          /* bytes per (octet, K-group) */
+#define LB_CHAIN_GC 4                /* K-groups per stage */
+#define LB_CHAIN_STAGE_BYTES (LB_CHAIN_GC * 2 * LB_CHAIN_RECORD)
+#define LB_CHAIN_MAX_OCTETS 32       /* octets one CTA may own */
 
 typedef struct {
-    unsigned char tmap[128] __attribute__((aligned(64)));    /* qweight [N/32][K/8][32], box 8 x 16 x 32, 128-byte swizzle */
-    unsigned char tmap_sc[128] __attribute__((aligned(64))); /* scales fp16 [K/128, N], box 1 x 256 */
-    unsigned char tmap_zr[128] __attribute__((aligned(64))); /* qzeros u32 [K/128, N/8], box 1 x 32 */
+    const unsigned char* packed; /* strip-packed weights (gemv_pack_strips) */
     const void* x;
     void* y;
     const void* aux0;
     const void* aux1;
     uint16_t* x_out;
     int32_t K, N;
-    int32_t kg;        /* K / 128 */
-    int32_t units;     /* ceil(N/256) * kg */
+    int32_t kg;       /* K / 128 */
+    int32_t units;    /* column units: N/8 octets, or N/16 pairs for the SwiGLU epilogue */
+    int32_t upo;      /* octets per unit: 1 or 2 */
     int32_t x_mode, y_mode;
-    int32_t has_zeros; /* 0: zero-point 8 everywhere */
     float eps;
-    int32_t pad_[8];
 } lb_chain_op;
 
 typedef struct {
     lb_chain_op op[LB_CHAIN_MAX_OPS];
     uint32_t* status;
     uint32_t* sync;       /* [0] grid-barrier arrivals, [1] CTAs that left; both zero between launches */
-    uint32_t* tile_count; /* [LB_CHAIN_MAX_TILES] contributors that delivered their part of a tile; zero between GEMVs */
-    float* partial;       /* [gridDim.x][2][256] partial sums of tiles shared between CTAs */
     int32_t n_ops;
-    int32_t stages;       /* ring depth */
+    int32_t slots;        /* ring slots per warp */
+    int32_t table_rows;   /* packed rows (K/8) the activation table holds: the largest K of the chain */
+    int32_t max_pairs;    /* pairs (incl. a trailing single) of the widest strip of the chain */
     int32_t trigger_op;   /* griddepcontrol.launch_dependents is issued when this GEMV starts */
-    int32_t pad_;
+    int32_t tab_len;      /* entries of a warp's stage list: ceil(stages of the busiest CTA / warps) */
 } lb_chain_params;
+
+/* gemv_pack_strips: reference format -> strip-packed (one thread per 32-bit word of the output) */
+typedef struct {
+    const uint32_t* qweight; /* [K/8, N] */
+    const uint16_t* scales;  /* fp16 [K/128, N] */
+    const uint32_t* qzeros;  /* [K/128, N/8] or NULL: zero-point 8 */
+    uint32_t* out;           /* N/8 * K/128 records of 136 words */
+    int32_t K, N;
+    int32_t swiglu;          /* input columns are interleaved 64-wide (gate, up) blocks; output units are (gate octet, up octet) pairs */
+    int32_t G;               /* CTAs the strips are cut for */
+} lb_pack_params;
 
 /* ---- dense bf16 [N,K] x vector ------------------------------------------ */
 typedef struct {

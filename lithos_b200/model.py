@@ -107,6 +107,7 @@ def _sigs():
     L.lb_model_weight_bytes.restype = u64
     L.lb_model_decode.argtypes = [vp, i32, i32, P(i32)]
     L.lb_model_capture.argtypes = [vp]
+    L.lb_model_set_chain.argtypes = [vp, i32]
     L.lb_model_set_input.argtypes = [vp, i32, i32]
     L.lb_model_replay.argtypes = [vp, i32]
     L.lb_model_read_next.argtypes = [vp, P(i32)]
@@ -195,6 +196,10 @@ class Model:
 
     def capture(self):
         self.ctx._check(lib().lb_model_capture(self.h))
+
+    def set_chain(self, on: bool):
+        """on (default): consecutive projections go out as one persistent launch; off: one launch each"""
+        self.ctx._check(lib().lb_model_set_chain(self.h, 1 if on else 0))
 
     def set_input(self, token: int, pos: int):
         self.ctx._check(lib().lb_model_set_input(self.h, token, pos))

@@ -15,17 +15,25 @@ TOL = 1e-3
 
 
 def _op(d, x, y, K, N, x_mode, y_mode, aux0=None, aux1=None, x_out=None):
-    return dict(qweight=d[0], scales=d[1], qzeros=d[2], x=x, y=y, K=K, N=N, x_mode=x_mode, y_mode=y_mode, aux0=aux0,
+    """d = [qweight, scales, qzeros, packed]"""
+    return dict(qweight=d[0], scales=d[1], qzeros=d[2], packed=d[3], x=x, y=y, K=K, N=N, x_mode=x_mode, y_mode=y_mode, aux0=aux0,
                 aux1=aux1, x_out=x_out, eps=1e-6)
 
 
+def _dev(ctx, qw, sc, qz, K, N, swiglu=False):
+    d = [ctx.to_device(qw), ctx.to_device(sc), ctx.to_device(qz) if qz is not None else None]
+    d.append(ctx.gemv_pack(d[0], d[1], d[2], K, N, swiglu))
+    return d
+
+
 @pytest.mark.parametrize("K,N,zeros", [(5120, 16384, True), (6144, 5120, True), (17408, 5120, False), (5120, 34816, True),
-                                       (1024, 38144, True)])
+                                       (1024, 37888, True), (256, 64, True)])
 def test_single_gemv_vs_oracle(ctx, lb, oracle, K, N, zeros):
-    """the decode step's four shapes (and a ragged last tile: 38144 = 149 * 256) as chains of one"""
+    """the decode step's four shapes, the widest strips (37888 = 148 SMs x 256 columns) and a matrix with
+    fewer octets than SMs, as chains of one"""
     qw, sc, qz, x = gptq_case(K, N, seed=21, zeros=zeros)
     want, _ = oracle.gptq_gemv(qw, sc, qz, x, K, N)
-    d = [ctx.to_device(qw), ctx.to_device(sc), ctx.to_device(qz) if zeros else None]
+    d = _dev(ctx, qw, sc, qz, K, N)
     d_x, d_y = ctx.to_device(x), ctx.alloc(N * 4)
     ctx.gemv_chain([_op(d, d_x, d_y, K, N, lb.X_F16, lb.Y_F32)])
     got = d_y.download(np.float32, N)
@@ -41,7 +49,7 @@ def _layer_case(ctx, lb, seed, H=5120, V=6144, I=17408, NIN=16384):
     gate/up (RMSNorm, SwiGLU), down (residual add), next layer's input projection (RMSNorm, fp16 copy out)"""
     mats = {"out": gptq_case(V, H, seed + 1), "gu": gptq_case(H, 2 * I, seed + 2), "down": gptq_case(I, H, seed + 3, zeros=False),
             "in": gptq_case(H, NIN, seed + 4)}
-    dev = {k: [ctx.to_device(m[0]), ctx.to_device(m[1]), ctx.to_device(m[2]) if m[2] is not None else None] for k, m in mats.items()}
+    dev = {k: _dev(ctx, m[0], m[1], m[2], m[0].shape[0] * 8, m[0].shape[1], swiglu=(k == "gu")) for k, m in mats.items()}
     host = dict(mix=lb.fill_normal(V, seed, 40, std=2.0), z=lb.fill_normal(V, seed, 41), hw=lb.fill_normal(128, seed, 42, mean=1.0, std=0.1),
                 X=lb.fill_normal(H, seed, 43, std=1.5), w_post=lb.fill_normal(H, seed, 44, std=0.02, dtype="bf16"),
                 w_in=lb.fill_normal(H, seed, 45, std=0.02, dtype="bf16"))
@@ -106,7 +114,7 @@ def test_chain_in_a_graph(ctx, lb):
     """captured once, replayed three times: each replay continues from the previous residual stream"""
     K, N = 5120, 5120
     qw, sc, qz, _ = gptq_case(K, N, seed=60)
-    d = [ctx.to_device(qw), ctx.to_device(sc), ctx.to_device(qz)]
+    d = _dev(ctx, qw, sc, qz, K, N)
     x0 = lb.fill_normal(K, 60, 5, std=0.5)
     w = lb.fill_normal(K, 60, 6, std=0.02, dtype="bf16")
     d_w = ctx.to_device(w)
@@ -137,10 +145,12 @@ def test_chain_in_a_graph(ctx, lb):
 
 def test_chain_rejects_what_it_cannot_run(ctx, lb):
     d = ctx.alloc(1 << 16)
-    with pytest.raises(lb.LithosError) as e:      # 4 tiles x 8 groups = 32 units: fewer than the SMs
-        ctx.gemv_chain([dict(qweight=d, scales=d, qzeros=None, x=d, y=d, K=1024, N=1024, x_mode=lb.X_F16, y_mode=lb.Y_F32)])
+    with pytest.raises(lb.LithosError) as e:      # 38144 columns: more than 256 on one SM
+        ctx.gemv_chain([dict(packed=d, x=d, y=d, K=1024, N=38144 + 256 * 148, x_mode=lb.X_F16, y_mode=lb.Y_F32)])
     assert e.value.status == lb.LB_ERR_INVALID
-    with pytest.raises(lb.LithosError):           # 136 groups and one tile per CTA pair: window too wide
-        ctx.gemv_chain([dict(qweight=d, scales=d, qzeros=None, x=d, y=d, K=17408, N=256 * 100, x_mode=lb.X_F16, y_mode=lb.Y_F32)])
-    assert not ctx.gemv_chain_supports(1024, 1024) and ctx.gemv_chain_supports(5120, 16384)
+    with pytest.raises(lb.LithosError):           # K not a multiple of the group size
+        ctx.gemv_chain([dict(packed=d, x=d, y=d, K=1000, N=1024, x_mode=lb.X_F16, y_mode=lb.Y_F32)])
+    with pytest.raises(lb.LithosError):           # no packed weights
+        ctx.gemv_chain([dict(packed=None, x=d, y=d, K=1024, N=1024, x_mode=lb.X_F16, y_mode=lb.Y_F32)])
+    assert ctx.gemv_chain_supports(5120, 34816, swiglu=True) and not ctx.gemv_chain_supports(5120, 2 * 37888 + 128)
     d.free()

@@ -76,7 +76,7 @@ def test_graph_replay_equals_eager(ctx, lb, oracle):
     logits_eager = gm.logits()
     gm.reset_state()
     gm.capture()
-    assert gm.step_kernels == 5 * cfg.n_layers + 3
+    assert gm.step_kernels == 2 * cfg.n_layers + 4   # embed, first input projection, (mixer, GEMV chain) per layer, LM head, arg-max
     gm.set_input(5, 0)
     replayed = []
     for pos in range(24):
@@ -124,4 +124,44 @@ def test_seeded_state_is_used(ctx, lb, oracle):
         assert rel(gm.logits(), om.logits()) <= 2e-3
         assert tok_g == tok_o
     gm.close()
+    om.close()
+
+
+def test_full_width_layers_chain_vs_separate_launches_vs_oracle(ctx, lb, oracle):
+    """Four layers at the benchmark's widths (hidden 5120, SwiGLU 17408, 48/16 DeltaNet heads, 24/4
+    attention heads; small vocabulary): here the projections between token mixers run as one
+    persistent chain launch.  Tokens equal the oracle's and those of the one-launch-per-projection
+    path over 12 steps; logits within 2e-3; the captured graph replays the same tokens."""
+    from lithos_b200 import model as M
+    full = M.qwen35_27b(max_ctx=48, n_layers=4)
+    cfg = M.ModelCfg(**{**{n: getattr(full, n) for n, _ in M.ModelCfg._fields_}, "vocab": 4096})
+    gm, om = build_pair(ctx, lb, oracle, cfg, seed=77)
+    g1 = M.Model(ctx, cfg)
+    g1.fill_synthetic(77)
+    g1.set_chain(False)
+    assert gm.ctx.gemv_chain_supports(cfg.hidden, 2 * cfg.inter, swiglu=True)
+    tok = 5
+    toks, worst = [], 0.0
+    for pos in range(12):
+        n_o = om.decode(tok, pos)
+        n_c = gm.decode(tok, pos)
+        n_1 = g1.decode(tok, pos)
+        worst = max(worst, rel(gm.logits(), om.logits()), rel(g1.logits(), om.logits()))
+        assert n_c == n_o == n_1, f"step {pos}: chain {n_c}, separate launches {n_1}, oracle {n_o} (logit err {worst:.2e})"
+        tok = n_o
+        toks.append(tok)
+    assert worst <= 2e-3
+    assert gm.step_kernels < g1.step_kernels        # 4 layers: 4 mixers + chains, against 5 launches per layer
+    # graph replay from the start on a fresh model: same tokens
+    g2 = M.Model(ctx, cfg)
+    g2.fill_synthetic(77)
+    g2.capture()
+    g2.set_input(5, 0)
+    rep = []
+    for _ in range(12):
+        g2.replay(1)
+        rep.append(g2.read_next())
+    assert rep == toks
+    for m in (gm, g1, g2):
+        m.close()
     om.close()
