@@ -139,6 +139,166 @@ __device__ __forceinline__ void ch_stage_items(const unsigned char* stage, int g
         }
 }
 
+// The activation vector of one GEMV as exact integers, for the whole block: X_k = rint(x_k * 2^shift) with
+// |X| < 2^22, split into three signed base-256 digits that become the B operand of the integer MMA (digit table
+// layout: digit_row_word).  x_k is the fp16 activation (after the optional norm prologue), so X_k is EXACT for every
+// element within 2^-11 of the vector maximum and off by at most max|x| * 2^-23 below that.  Returns 2^-shift.
+// Thread tid owns packed rows tid, tid + 512, ... (NI of them at most); all global loads are issued before the
+// first use, so the prologue costs one trip to L2, not one per row.
+template <int NI>
+__device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& sh, uint32_t* xdig, float* xsumf, int tid, bool write_x) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int rows = op.K / 8;
+    uint32_t hv[NI][4]; // the row as 8 fp16 values
+    if (op.x_mode == LB_X_F16) {
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const int r = tid + i * LB_CHAIN_THREADS;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (r < rows) raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(op.x) + r * 8));
+            hv[i][0] = raw.x; hv[i][1] = raw.y; hv[i][2] = raw.z; hv[i][3] = raw.w;
+        }
+    } else {
+        float v[NI][8];
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const int r = tid + i * LB_CHAIN_THREADS;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+            if (r < rows) {
+                const float4* xv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.x) + r * 8);
+                a = __ldcg(xv);
+                b = __ldcg(xv + 1);
+            }
+            v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
+            v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+        }
+        if (op.x_mode == LB_X_F32_RMSNORM) {
+            // h = x * rsqrt(mean x^2 + eps) * (1 + w): the rows held by the block's threads are the whole vector
+            uint4 wr[NI];
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const int r = tid + i * LB_CHAIN_THREADS;
+                wr[i] = r < rows ? __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op.aux0) + r * 8)) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < NI; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+            ss = warp_sum(ss);
+            if (lane == 0) sh.scratch[warp] = ss;
+            __syncthreads();
+            float tot = 0.f;
+#pragma unroll
+            for (int w = 0; w < CH_W; ++w) tot += sh.scratch[w];
+            const float rinv = rsqrtf(tot / (float)op.K + op.eps);
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const uint32_t ww[4] = {wr[i].x, wr[i].y, wr[i].z, wr[i].w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float wf = __uint_as_float(j & 1 ? ww[j >> 1] & 0xffff0000u : ww[j >> 1] << 16);
+                    v[i][j] = v[i][j] * rinv * (1.0f + wf);
+                }
+            }
+        } else if (op.x_mode == LB_X_F32_HEADNORM_SILU) {
+            // one head = 128 values = the 16 rows held by a 16-lane segment; h = x * rsqrt(mean_head x^2 + eps) * w * silu(z)
+            const float4* wv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.aux0) + (tid & 15) * 8);
+            const float4 wa = __ldg(wv), wb = __ldg(wv + 1);
+            const float hw[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+            float z[NI][8];
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const int r = tid + i * LB_CHAIN_THREADS;
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                if (r < rows) {
+                    const float4* zv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.aux1) + r * 8);
+                    a = __ldcg(zv);
+                    b = __ldcg(zv + 1);
+                }
+                z[i][0] = a.x; z[i][1] = a.y; z[i][2] = a.z; z[i][3] = a.w;
+                z[i][4] = b.x; z[i][5] = b.y; z[i][6] = b.z; z[i][7] = b.w;
+            }
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float hr = rsqrtf(ss * (1.0f / 128.0f) + op.eps);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * hr * hw[j] * siluf_dev(z[i][j]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NI; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 h = __floats2half2_rn(v[i][2 * j], v[i][2 * j + 1]);
+                hv[i][j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+    }
+    // the scale: max|x| * 2^shift in [2^21, 2^22); all-zero or non-finite vectors use shift 0
+    float vmax = 0.f;
+#pragma unroll
+    for (int i = 0; i < NI; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hv[i][j]));
+            vmax = fmaxf(vmax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    if (lane == 0) sh.scratch[32 + warp] = vmax;
+    __syncthreads();
+    vmax = 0.f;
+#pragma unroll
+    for (int w = 0; w < CH_W; ++w) vmax = fmaxf(vmax, sh.scratch[32 + w]);
+    int shift = 0;
+    if (vmax > 0.f && vmax < 3.0e38f) shift = 21 - (int)((__float_as_uint(vmax) >> 23) & 0xffu) + 127;
+    const float qscale = __uint_as_float((uint32_t)(127 + shift) << 23);
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+        const int r = tid + i * LB_CHAIN_THREADS;
+        const bool live = r < rows;
+        // X = d0 + 256 d1 + 65536 d2 with d0, d1 in [-128,127]: d0 is the low byte of X, d1 the low byte of
+        // (X + 128) >> 8, d2 = ((X + 128 >> 8) + 128) >> 8
+        int X[8], rs = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hv[i][j]));
+            X[2 * j] = __float2int_rn(f.x * qscale);
+            X[2 * j + 1] = __float2int_rn(f.y * qscale);
+        }
+        uint32_t ev[3], od[3];
+#pragma unroll
+        for (int d = 0; d < 3; ++d) {
+            // bytes 0 of X[0], X[2], X[4], X[6] -> ev; of X[1], X[3], X[5], X[7] -> od
+            ev[d] = __byte_perm(__byte_perm(X[0], X[2], 0x0040), __byte_perm(X[4], X[6], 0x0040), 0x5410);
+            od[d] = __byte_perm(__byte_perm(X[1], X[3], 0x0040), __byte_perm(X[5], X[7], 0x0040), 0x5410);
+            if (d == 0) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) rs += X[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) X[j] = (X[j] + 128) >> 8;
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o); // the group's 16 rows
+        if (live) {
+            uint32_t* dst = xdig + digit_row_word(r);
+#pragma unroll
+            for (int d = 0; d < 3; ++d) *reinterpret_cast<uint2*>(dst + 2 * d) = make_uint2(ev[d], od[d]);
+            if ((lane & 15) == 0) xsumf[r >> 4] = (float)rs;
+            if (op.x_out && write_x) // every CTA holds the whole vector: one of them writes it out
+                *reinterpret_cast<uint4*>(op.x_out + r * 8) = make_uint4(hv[i][0], hv[i][1], hv[i][2], hv[i][3]);
+        }
+    }
+    __syncthreads();
+    return __uint_as_float((uint32_t)(127 - shift) << 23);
+}
+
 extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(const __grid_constant__ lb_chain_params p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ ch_shared sh;
@@ -235,100 +395,9 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         if (sh.snap) break; // uniform: written before the barrier above, by one thread
 
         // ---- the activation vector as exact integers: three signed base-256 digit planes ----
-        const int rows = op.K / 8;
         for (int i = tid; i < ((no + 1) / 2) * CH_W * 16; i += LB_CHAIN_THREADS) red[i] = 0.f;
-        float rinv = 1.0f;
-        if (op.x_mode == LB_X_F32_RMSNORM) {
-            const float4* xv = reinterpret_cast<const float4*>(op.x);
-            float ss = 0.f;
-            for (int i = tid; i < op.K / 4; i += LB_CHAIN_THREADS) {
-                const float4 v = __ldcg(xv + i);
-                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) sh.scratch[warp] = ss;
-            __syncthreads();
-            float tot = 0.f;
-#pragma unroll
-            for (int w = 0; w < CH_W; ++w) tot += sh.scratch[w];
-            rinv = rsqrtf(tot / (float)op.K + op.eps);
-            __syncthreads();
-        }
-        float vmax = 0.f;
-        for (int rb = 0; rb < rows; rb += LB_CHAIN_THREADS) {
-            float v[8];
-            const int r = rb + tid;
-            const bool live = r < rows;
-            load_x_row<true>(op, live ? r * 8 : 0, live, rinv, v);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) vmax = fmaxf(vmax, fabsf(v[j]));
-            if (live) { // parked as fp16 in the row's own digit slot until the scale is known
-                __half2 pk[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
-                                 __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
-                uint32_t* dst = xdig + digit_row_word(r);
-                const uint32_t* pw = reinterpret_cast<const uint32_t*>(pk);
-                *reinterpret_cast<uint2*>(dst) = make_uint2(pw[0], pw[1]);
-                *reinterpret_cast<uint2*>(dst + 2) = make_uint2(pw[2], pw[3]);
-            }
-        }
-#pragma unroll
-        for (int o2 = 16; o2 > 0; o2 >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o2));
-        if (lane == 0) sh.scratch[32 + warp] = vmax;
-        __syncthreads();
-        vmax = 0.f;
-#pragma unroll
-        for (int w = 0; w < CH_W; ++w) vmax = fmaxf(vmax, sh.scratch[32 + w]);
-        int shift = 0; // max|x| * 2^shift in [2^21, 2^22); all-zero or non-finite vectors use shift 0
-        if (vmax > 0.f && vmax < 3.0e38f) shift = 21 - (int)((__float_as_uint(vmax) >> 23) & 0xffu) + 127;
-        const float qscale = __uint_as_float((uint32_t)(127 + shift) << 23);
-        const float unit = __uint_as_float((uint32_t)(127 - shift) << 23);
-        for (int rb = 0; rb < rows; rb += LB_CHAIN_THREADS) {
-            const int r = rb + tid;
-            const bool live = r < rows;
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = 0.f;
-            if (live) { // the same thread parked this row above
-                const uint32_t* src = xdig + digit_row_word(r);
-                const uint2 p0 = *reinterpret_cast<const uint2*>(src), p1 = *reinterpret_cast<const uint2*>(src + 2);
-                const uint32_t pw[4] = {p0.x, p0.y, p1.x, p1.y};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&pw[j]));
-                    v[2 * j] = f.x;
-                    v[2 * j + 1] = f.y;
-                }
-            }
-            int rs = 0;
-            uint32_t ev[3] = {0u, 0u, 0u}, od[3] = {0u, 0u, 0u};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                int t = __float2int_rn(v[j] * qscale);
-                rs += t;
-#pragma unroll
-                for (int d = 0; d < 3; ++d) {
-                    const int dg = d < 2 ? ((t + 128) & 255) - 128 : t; // signed digit in [-128,127]
-                    t = (t - dg) >> 8;
-                    const uint32_t byte = (uint32_t)dg & 0xffu;
-                    if (j & 1) od[d] |= byte << (8 * (j >> 1));
-                    else ev[d] |= byte << (8 * (j >> 1));
-                }
-            }
-#pragma unroll
-            for (int o2 = 8; o2 > 0; o2 >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o2); // the group's 16 rows
-            if (live) {
-                uint32_t* dst = xdig + digit_row_word(r);
-#pragma unroll
-                for (int d = 0; d < 3; ++d) *reinterpret_cast<uint2*>(dst + 2 * d) = make_uint2(ev[d], od[d]);
-                if ((lane & 15) == 0) xsumf[r >> 4] = (float)rs;
-                if (op.x_out && c == 0) { // every CTA holds the whole vector: one of them writes it out
-                    __half2 pl[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]),
-                                     __floats2half2_rn(v[4], v[5]), __floats2half2_rn(v[6], v[7])};
-                    *reinterpret_cast<uint4*>(op.x_out + r * 8) = *reinterpret_cast<uint4*>(pl);
-                }
-            }
-        }
-        __syncthreads();
+        const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xdig, xsumf, tid, c == 0)
+                                                             : ch_prologue<5>(op, sh, xdig, xsumf, tid, c == 0);
 
         // ---- this warp's stages of GEMV o.  Column sums stay in registers while consecutive stages belong to
         //      the same pair, and go to this warp's own row of `red` when the pair changes. ----
