@@ -60,6 +60,11 @@ void lb_set_pdl(lb_ctx* ctx, int on);
 /* bytes of an SM's shared memory lb_gemv_chain leaves free so that a CTA of the kernel before/after it can be
  * resident at the same time (default 32 KB; 0 = the deepest weight ring) */
 void lb_set_chain_reserve(lb_ctx* ctx, int bytes);
+/* Profiling hook: while buf != 0, every persistent-chain launch made (or captured) afterwards writes, for each SM and
+ * chain entry, four %globaltimer values (ns) of the SM's thread 0 -- reached the grid barrier, left it, activation
+ * table ready / mixer started, entry finished -- into buf as u64 [SMs][LB_GEMV_CHAIN_MAX][4].  Launches overwrite
+ * each other's stamps. */
+void lb_set_chain_timeline(lb_ctx* ctx, uint64_t buf);
 
 /* ---- generic module load + launch ----------------------------------------------
  * The reference's own mechanism, kept as is: load_one_cubin = file read +
@@ -148,7 +153,7 @@ int lb_gemv_int4_fused(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t 
  * lb_gemv_packed_bytes gives the size of the buffer the caller allocates; swiglu = 1 for a matrix
  * that will be used with the SwiGLU epilogue).  x and y of one entry must not overlap.
  * LB_ERR_INVALID when a shape puts more than 256 columns on one SM. */
-#define LB_GEMV_CHAIN_MAX 8
+#define LB_GEMV_CHAIN_MAX 24
 typedef struct {
     uint64_t packed;                  /* from lb_gemv_pack */
     uint64_t x, y, aux0, aux1, x_out; /* as in lb_gemv_int4_fused */

@@ -104,6 +104,7 @@ def lib() -> C.CDLL:
     sig("lb_gemv_packed_bytes", sz, i32, i32)
     sig("lb_gemv_pack", i32, vp, u64, u64, u64, i32, i32, i32, u64)
     sig("lb_set_chain_reserve", None, vp, i32)
+    sig("lb_set_chain_timeline", None, vp, u64)
     sig("lb_gptq_dequant", i32, vp, u64, u64, u64, u64, i32, i32)
     sig("lb_gptq_unpack", i32, vp, u64, u64, i32, i32)
     sig("lb_dense_bf16_gemv", i32, vp, u64, u64, u64, i32, i32, i32)

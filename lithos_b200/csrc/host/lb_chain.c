@@ -38,45 +38,25 @@ LB_API int lb_gemv_pack(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
     return lb_launch(c, LBK_gemv_pack_strips, (unsigned)c->sm_count * 8, 1, 1, 256, 0, params, 0);
 }
 
-LB_API int lb_gemv_chain(lb_ctx* c, const lb_gemv_op* ops, int n_ops) {
-    if (!c || !ops) return LB_ERR_INVALID;
-    if (n_ops < 1 || n_ops > LB_CHAIN_MAX_OPS) return lb_fail(c, LB_ERR_INVALID, "GEMV chain: %d entries (1..%d)", n_ops, LB_CHAIN_MAX_OPS);
-    lb_chain_params p;
-    memset(&p, 0, sizeof p);
-    int max_rows = 0, max_oct = 0;
+/* Shared-memory plan of one chain launch: 0 ring slots = does not fit. */
+typedef struct { int slots, table_rows, max_pairs, tab_len; unsigned smem; } chain_plan;
+
+static void chain_plan_make(const lb_ctx* c, const lb_chain_op* ops, int n_ops, chain_plan* pl) {
+    int max_rows = 16, max_oct = 2, has_dn = 0;
     long long max_stages = 0; /* stages of the busiest CTA, all GEMVs of the chain */
     for (int i = 0; i < n_ops; i++) {
-        const lb_gemv_op* o = &ops[i];
-        if (!o->packed || !o->x || !o->y) return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: NULL operand", i);
-        if (o->x_mode < LB_X_F16 || o->x_mode > LB_X_F32_HEADNORM_SILU || o->y_mode < LB_Y_F16 || o->y_mode > LB_Y_SWIGLU_F16)
-            return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: unknown x_mode/y_mode %d/%d", i, o->x_mode, o->y_mode);
-        if ((o->x_mode == LB_X_F32_RMSNORM && !o->aux0) || (o->x_mode == LB_X_F32_HEADNORM_SILU && (!o->aux0 || !o->aux1)))
-            return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: norm prologue without its weight/gate operand", i);
-        if (((o->packed | o->x | o->y | o->aux0 | o->aux1 | o->x_out) & 15ull) != 0)
-            return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: operands must be 16-byte aligned", i);
-        const int swiglu = o->y_mode == LB_Y_SWIGLU_F16;
-        const char* why = chain_shape_problem(c, o->K, o->N, swiglu);
-        if (why) return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: K=%d N=%d: %s", i, o->K, o->N, why);
-        lb_chain_op* d = &p.op[i];
-        d->packed = (const unsigned char*)o->packed;
-        d->x = (const void*)o->x; d->y = (void*)o->y;
-        d->aux0 = (const void*)o->aux0; d->aux1 = (const void*)o->aux1;
-        d->x_out = (uint16_t*)o->x_out;
-        d->K = o->K; d->N = o->N;
-        d->kg = o->K / LB_GEMV_GROUP;
-        d->upo = swiglu ? 2 : 1;
-        d->units = o->N / 8 / d->upo;
-        d->x_mode = o->x_mode; d->y_mode = o->y_mode;
-        d->eps = o->eps;
-        if (o->K / 8 > max_rows) max_rows = o->K / 8;
+        const lb_chain_op* d = &ops[i];
+        if (d->type != LB_CHAIN_OP_GEMV) { has_dn = 1; continue; }
+        if (d->K / 8 > max_rows) max_rows = d->K / 8;
         const int widest = (int)(((long long)d->units + c->sm_count - 1) / c->sm_count) * d->upo;
         if (widest > max_oct) max_oct = widest;
         max_stages += (long long)((widest + 1) / 2) * ((d->kg + LB_CHAIN_GC - 1) / LB_CHAIN_GC);
     }
-    /* shared memory: the activation table of the longest K, the per-(pair, warp) column sums, then as many ring
-     * slots per warp as fit, minus (when that still leaves two slots) room for a small CTA of the neighbouring
-     * kernel, which programmatic dependent launch lets become resident early */
-    const int max_pairs = (max_oct + 1) / 2;
+    /* the activation table of the longest K, the per-(pair, warp) column sums (the DeltaNet entries use the same
+     * bytes: four units of 3232 B), the warps' stage lists, then as many ring slots per warp as fit, minus (when that
+     * still leaves two slots) room for a small CTA of the neighbouring kernel */
+    int max_pairs = (max_oct + 1) / 2;
+    if (has_dn && max_pairs < 13) max_pairs = 13;
     const size_t dig_words = (size_t)((6 * max_rows + 2 * (max_rows >> 2) + 3) & ~3);
     const int tab_len = (int)((max_stages + LB_CHAIN_WARPS - 1) / LB_CHAIN_WARPS) + 1;
     const size_t fixed = dig_words * 4 + (size_t)((max_rows / LB_GEMV_ROWS + 3) & ~3) * 4 + (size_t)max_pairs * LB_CHAIN_WARPS * 16 * 4 +
@@ -86,16 +66,73 @@ LB_API int lb_gemv_chain(lb_ctx* c, const lb_gemv_op* ops, int n_ops) {
     int slots = limit > fixed + (size_t)c->chain_reserve ? (int)((limit - fixed - (size_t)c->chain_reserve) / per_slot) : 0;
     if (slots < 2) slots = limit > fixed ? (int)((limit - fixed) / per_slot) : 0;
     if (slots > 4) slots = 4;
-    if (slots < 2) return lb_fail(c, LB_ERR_INVALID, "GEMV chain: K=%d leaves room for %d ring slots per warp", max_rows * 8, slots);
-    p.slots = slots;
-    p.table_rows = max_rows;
-    p.max_pairs = max_pairs;
-    p.tab_len = tab_len;
+    if (slots < 2) slots = 0;
+    pl->slots = slots; pl->table_rows = max_rows; pl->max_pairs = max_pairs; pl->tab_len = tab_len;
+    pl->smem = (unsigned)(fixed + (size_t)slots * per_slot);
+}
+
+/* internal: LB_OK when these entries can run as one launch */
+int lb_chain_fits(lb_ctx* c, const lb_chain_op* ops, int n_ops) {
+    if (n_ops < 1 || n_ops > LB_CHAIN_MAX_OPS) return LB_ERR_INVALID;
+    chain_plan pl;
+    chain_plan_make(c, ops, n_ops, &pl);
+    return pl.slots ? LB_OK : LB_ERR_INVALID;
+}
+
+/* internal: launch kernel-level entries (GEMVs over packed weights, DeltaNet mixers) as one persistent kernel */
+int lb_chain_launch(lb_ctx* c, const lb_chain_op* ops, int n_ops) {
+    if (n_ops < 1 || n_ops > LB_CHAIN_MAX_OPS) return lb_fail(c, LB_ERR_INVALID, "chain: %d entries (1..%d)", n_ops, LB_CHAIN_MAX_OPS);
+    lb_chain_params p;
+    memset(&p, 0, sizeof p);
+    memcpy(p.op, ops, sizeof(lb_chain_op) * (size_t)n_ops);
+    chain_plan pl;
+    chain_plan_make(c, ops, n_ops, &pl);
+    if (!pl.slots) return lb_fail(c, LB_ERR_INVALID, "chain: %d entries (longest K %d) do not fit shared memory", n_ops, pl.table_rows * 8);
+    p.slots = pl.slots;
+    p.table_rows = pl.table_rows;
+    p.max_pairs = pl.max_pairs;
+    p.tab_len = pl.tab_len;
     p.n_ops = n_ops;
     p.trigger_op = n_ops - 1;
     p.status = (uint32_t*)c->dev_status;
     p.sync = (uint32_t*)c->gemv_counters; /* two words */
+    p.timeline = (unsigned long long*)c->chain_timeline;
     void* params[] = {&p};
-    return lb_launch(c, LBK_gemv_chain, (unsigned)c->sm_count, 1, 1, LB_CHAIN_THREADS,
-                     (unsigned)(fixed + (size_t)slots * per_slot), params, 1);
+    return lb_launch(c, LBK_gemv_chain, (unsigned)c->sm_count, 1, 1, LB_CHAIN_THREADS, pl.smem, params, 1);
+}
+
+/* internal: fill a kernel-level GEMV entry; LB_ERR_INVALID (with the reason recorded) when the shape cannot run */
+int lb_chain_fill_gemv(lb_ctx* c, lb_chain_op* d, const lb_gemv_op* o, int i) {
+    if (!o->packed || !o->x || !o->y) return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: NULL operand", i);
+    if (o->x_mode < LB_X_F16 || o->x_mode > LB_X_F32_HEADNORM_SILU || o->y_mode < LB_Y_F16 || o->y_mode > LB_Y_SWIGLU_F16)
+        return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: unknown x_mode/y_mode %d/%d", i, o->x_mode, o->y_mode);
+    if ((o->x_mode == LB_X_F32_RMSNORM && !o->aux0) || (o->x_mode == LB_X_F32_HEADNORM_SILU && (!o->aux0 || !o->aux1)))
+        return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: norm prologue without its weight/gate operand", i);
+    if (((o->packed | o->x | o->y | o->aux0 | o->aux1 | o->x_out) & 15ull) != 0)
+        return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: operands must be 16-byte aligned", i);
+    const int swiglu = o->y_mode == LB_Y_SWIGLU_F16;
+    const char* why = chain_shape_problem(c, o->K, o->N, swiglu);
+    if (why) return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: K=%d N=%d: %s", i, o->K, o->N, why);
+    if (o->K > 8 * LB_CHAIN_THREADS * 5) return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: K=%d above %d", i, o->K, 8 * LB_CHAIN_THREADS * 5);
+    memset(d, 0, sizeof *d);
+    d->type = LB_CHAIN_OP_GEMV;
+    d->packed = (const unsigned char*)o->packed;
+    d->x = (const void*)o->x; d->y = (void*)o->y;
+    d->aux0 = (const void*)o->aux0; d->aux1 = (const void*)o->aux1;
+    d->x_out = (uint16_t*)o->x_out;
+    d->K = o->K; d->N = o->N;
+    d->kg = o->K / LB_GEMV_GROUP;
+    d->upo = swiglu ? 2 : 1;
+    d->units = o->N / 8 / d->upo;
+    d->x_mode = o->x_mode; d->y_mode = o->y_mode;
+    d->eps = o->eps;
+    return LB_OK;
+}
+
+LB_API int lb_gemv_chain(lb_ctx* c, const lb_gemv_op* ops, int n_ops) {
+    if (!c || !ops) return LB_ERR_INVALID;
+    if (n_ops < 1 || n_ops > LB_CHAIN_MAX_OPS) return lb_fail(c, LB_ERR_INVALID, "GEMV chain: %d entries (1..%d)", n_ops, LB_CHAIN_MAX_OPS);
+    lb_chain_op k[LB_CHAIN_MAX_OPS];
+    for (int i = 0; i < n_ops; i++) LB_TRY(lb_chain_fill_gemv(c, &k[i], &ops[i], i));
+    return lb_chain_launch(c, k, n_ops);
 }

@@ -219,6 +219,7 @@ LB_API int lb_device_sm_count(const lb_ctx* c) { return c ? c->sm_count : 0; }
 LB_API uint64_t lb_launch_count(const lb_ctx* c) { return c ? c->launches : 0; }
 LB_API void lb_launch_count_reset(lb_ctx* c) { if (c) c->launches = 0; }
 LB_API void lb_set_pdl(lb_ctx* c, int on) { if (c) c->pdl = on ? 1 : 0; }
+LB_API void lb_set_chain_timeline(lb_ctx* c, uint64_t buf) { if (c) c->chain_timeline = (CUdeviceptr)buf; }
 LB_API void lb_set_chain_reserve(lb_ctx* c, int bytes) { if (c && bytes >= 0 && bytes <= 128 * 1024) c->chain_reserve = bytes; }
 
 LB_API int lb_device_status(lb_ctx* c, uint32_t* out) {

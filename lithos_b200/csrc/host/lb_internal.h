@@ -130,6 +130,7 @@ struct lb_ctx {
     size_t flush_bytes;
     uint64_t launches; /* kernels launched (or graph nodes replayed) since reset */
     int pdl;           /* use programmatic dependent launch between kernels */
+    CUdeviceptr chain_timeline; /* optional time-stamp buffer handed to every chain launch (lb_set_chain_timeline) */
     int chain_reserve; /* bytes of an SM's shared memory the GEMV chain leaves to a neighbouring kernel's CTA */
     int capturing;     /* stream capture in progress */
     uint64_t capture_launches0;

@@ -35,6 +35,7 @@ typedef struct {
     CUdeviceptr input_norm, post_norm;
     /* DeltaNet */
     CUdeviceptr proj_a, proj_b, a_log, dt_bias, conv_w, dn_norm, dn_state, conv_ring;
+    CUdeviceptr dn_params; /* lb_dn_layer_params of this layer in device memory, for the persistent chain */
     /* attention */
     CUdeviceptr q_norm, k_norm, k_cache, v_cache;
     int loaded;
@@ -60,13 +61,17 @@ struct lb_model {
     int vocab_s;     /* vocabulary rows on this shard */
     int ar_count;    /* all-reduces issued so far in the step being built (slot parity) */
     int use_chain;   /* consecutive GEMVs of the step go out as one persistent launch (lb_gemv_chain) */
-    lb_gemv_op pend[LB_GEMV_CHAIN_MAX]; /* GEMVs collected since the last other kernel */
+    lb_chain_op pend[LB_CHAIN_MAX_OPS]; /* GEMVs and DeltaNet mixers collected since the last stand-alone kernel */
     int n_pend;
 };
 
+static void dn_fill_params(const lb_model* m, const layer_t* L, lb_dn_layer_params* p);
 extern int lb_comm_fill(const lb_comm* m, lb_tp_params* p, int slot, int n);
 extern uint64_t lb_comm_slot_ptr(const lb_comm* m, int slot);
 
+extern int lb_chain_fits(lb_ctx* c, const lb_chain_op* ops, int n_ops);
+extern int lb_chain_launch(lb_ctx* c, const lb_chain_op* ops, int n_ops);
+extern int lb_chain_fill_gemv(lb_ctx* c, lb_chain_op* d, const lb_gemv_op* o, int i);
 extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps,
                            uint64_t part_val, uint64_t part_idx);
 extern int lb_dense_ctas(lb_ctx* c, int N);
@@ -378,6 +383,11 @@ LB_API int lb_model_load_layer(lb_model* m, int layer, const void* const* slots)
     }
     LB_TRY(upload(m, &L->input_norm, slots[WS_INPUT_NORM], (size_t)H * 2));
     LB_TRY(upload(m, &L->post_norm, slots[WS_POST_NORM], (size_t)H * 2));
+    if (!L->is_fa) { /* the mixer's parameter block, for the persistent chain (read by the kernel from device memory) */
+        lb_dn_layer_params dp;
+        dn_fill_params(m, L, &dp);
+        LB_TRY(upload(m, &L->dn_params, &dp, sizeof dp));
+    }
     L->loaded = 1;
     return LB_OK;
 }
@@ -488,25 +498,51 @@ LB_API int lb_model_fill_synthetic(lb_model* m, uint64_t seed) {
 }
 
 /* ---- the step ------------------------------------------------------------------------------ */
-/* launch the GEMVs collected so far as one persistent chain */
-static int flush_gemvs(lb_model* m) {
+/* parameters of the DeltaNet mixer of one layer (between the qkvz projection and the out projection) */
+static void dn_fill_params(const lb_model* m, const layer_t* L, lb_dn_layer_params* p) {
+    memset(p, 0, sizeof *p);
+    p->qkvz = (const float*)m->in_out; p->xn = (const uint16_t*)m->xn;
+    p->proj_a = (const uint16_t*)L->proj_a; p->proj_b = (const uint16_t*)L->proj_b;
+    p->a_log = (const float*)L->a_log; p->dt_bias = (const uint16_t*)L->dt_bias;
+    p->conv_w = (const uint16_t*)L->conv_w; p->conv_ring = (float*)L->conv_ring;
+    p->state = (float*)L->dn_state; p->out = (float*)m->mix_out; p->pos = (const int*)m->d_pos;
+    p->HV = m->HV; p->HK = m->HK; p->hidden = m->cfg.hidden;
+}
+
+/* launch what has been collected so far as one persistent kernel */
+static int flush_chain(lb_model* m) {
     int n = m->n_pend;
     m->n_pend = 0;
-    return n ? lb_gemv_chain(m->c, m->pend, n) : LB_OK;
+    return n ? lb_chain_launch(m->c, m->pend, n) : LB_OK;
+}
+
+/* add an entry to the pending chain; what is pending goes out first when the new entry no longer fits beside it */
+static int chain_push(lb_model* m, const lb_chain_op* op) {
+    if (m->n_pend > 0) {
+        int fits = m->n_pend < LB_CHAIN_MAX_OPS;
+        if (fits) {
+            m->pend[m->n_pend] = *op;
+            fits = lb_chain_fits(m->c, m->pend, m->n_pend + 1) == LB_OK;
+        }
+        if (!fits) LB_TRY(flush_chain(m));
+    }
+    m->pend[m->n_pend++] = *op;
+    return LB_OK;
 }
 
 static int q4_gemv(lb_model* m, const q4_mat* w, CUdeviceptr x, CUdeviceptr y, int x_mode, int y_mode, CUdeviceptr aux0,
                    CUdeviceptr aux1, CUdeviceptr x_out) {
     if (m->use_chain && w->packed) {
-        if (m->n_pend == LB_GEMV_CHAIN_MAX) LB_TRY(flush_gemvs(m));
-        lb_gemv_op* o = &m->pend[m->n_pend++];
-        memset(o, 0, sizeof *o);
-        o->packed = w->packed;
-        o->x = x; o->y = y; o->aux0 = aux0; o->aux1 = aux1; o->x_out = x_out;
-        o->K = w->K; o->N = w->N; o->x_mode = x_mode; o->y_mode = y_mode; o->eps = m->cfg.eps;
-        return LB_OK;
+        lb_gemv_op o;
+        memset(&o, 0, sizeof o);
+        o.packed = w->packed;
+        o.x = x; o.y = y; o.aux0 = aux0; o.aux1 = aux1; o.x_out = x_out;
+        o.K = w->K; o.N = w->N; o.x_mode = x_mode; o.y_mode = y_mode; o.eps = m->cfg.eps;
+        lb_chain_op k;
+        LB_TRY(lb_chain_fill_gemv(m->c, &k, &o, m->n_pend));
+        return chain_push(m, &k);
     }
-    LB_TRY(flush_gemvs(m));
+    LB_TRY(flush_chain(m));
     return lb_gemv_int4_fused(m->c, w->qweight, w->scales, w->qzeros, x, y, w->K, w->N, x_mode, y_mode, aux0, aux1, x_out,
                               m->cfg.eps);
 }
@@ -543,16 +579,18 @@ static int issue_step(lb_model* m) {
             const int C = m->C_s;
             LB_TRY(q4_gemv(m, &L->w_in, m->X, m->in_out, LB_X_F32_RMSNORM, LB_Y_F32, L->input_norm, 0, m->xn));
             lb_dn_layer_params p;
-            memset(&p, 0, sizeof p);
-            p.qkvz = (const float*)m->in_out; p.xn = (const uint16_t*)m->xn;
-            p.proj_a = (const uint16_t*)L->proj_a; p.proj_b = (const uint16_t*)L->proj_b;
-            p.a_log = (const float*)L->a_log; p.dt_bias = (const uint16_t*)L->dt_bias;
-            p.conv_w = (const uint16_t*)L->conv_w; p.conv_ring = (float*)L->conv_ring;
-            p.state = (float*)L->dn_state; p.out = (float*)m->mix_out; p.pos = (const int*)m->d_pos;
-            p.HV = m->HV; p.HK = m->HK; p.hidden = H;
-            void* params[] = {&p};
-            LB_TRY(flush_gemvs(m));
-            LB_TRY(lb_launch(c, LBK_deltanet_layer_fused, (unsigned)m->HV, 4, 1, 128, 0, params, 1));
+            dn_fill_params(m, L, &p);
+            if (m->use_chain && L->dn_params && L->w_in.packed) { /* the mixer joins the persistent chain */
+                lb_chain_op k;
+                memset(&k, 0, sizeof k);
+                k.type = LB_CHAIN_OP_DELTANET;
+                k.ext = (const void*)L->dn_params;
+                LB_TRY(chain_push(m, &k));
+            } else {
+                void* params[] = {&p};
+                LB_TRY(flush_chain(m));
+                LB_TRY(lb_launch(c, LBK_deltanet_layer_fused, (unsigned)m->HV, 4, 1, 128, 0, params, 1));
+            }
             LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32_HEADNORM_SILU, L->dn_norm, m->in_out + (size_t)C * 4));
         } else {
             LB_TRY(q4_gemv(m, &L->w_in, m->X, m->in_out, LB_X_F32_RMSNORM, LB_Y_F32, L->input_norm, 0, 0));
@@ -575,7 +613,7 @@ static int issue_step(lb_model* m) {
             for (int i = 0; i < cfg->rot_dims / 2; i++)
                 p.rope_freq[i] = exp2(-log2((double)cfg->rope_theta) * (double)i / (double)(cfg->rot_dims / 2));
             void* params[] = {&p};
-            LB_TRY(flush_gemvs(m));
+            LB_TRY(flush_chain(m));
             LB_TRY(lb_launch(c, LBK_attn_decode_split, (unsigned)m->HKV, (unsigned)p.splits, 1, 256,
                              lb_attn_smem(m->HQ / m->HKV), params, 1));
             LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32, 0, 0));
@@ -584,7 +622,7 @@ static int issue_step(lb_model* m) {
         LB_TRY(row_parallel(m, &L->w_down, m->mlp_m, LB_X_F16, 0, 0));
     }
     if (!m->globals_loaded) return lb_fail(c, LB_ERR_STATE, "model: globals have no weights");
-    LB_TRY(flush_gemvs(m));
+    LB_TRY(flush_chain(m));
     LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, m->vocab_s, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps,
                            m->cand_val, m->cand_idx));
     if (m->tp_size == 1) {
@@ -689,7 +727,7 @@ LB_API void lb_model_destroy(lb_model* m) {
                 if (q[i]->packed) lb_drv.MemFree(q[i]->packed);
             }
             CUdeviceptr p[] = {L->input_norm, L->post_norm, L->proj_a, L->proj_b, L->a_log, L->dt_bias, L->conv_w, L->dn_norm,
-                               L->dn_state, L->conv_ring, L->q_norm, L->k_norm, L->k_cache, L->v_cache};
+                               L->dn_state, L->conv_ring, L->q_norm, L->k_norm, L->k_cache, L->v_cache, L->dn_params};
             for (size_t i = 0; i < sizeof p / sizeof p[0]; i++) if (p[i]) lb_drv.MemFree(p[i]);
         }
         if (m->h_next) lb_drv.MemFreeHost(m->h_next);

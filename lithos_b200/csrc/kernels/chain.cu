@@ -26,6 +26,7 @@
 //     takes more than half of an SM's shared memory.
 // Activations written inside the launch are read through L2 only (ld.global.cg).
 #include "gemv_core.cuh"
+#include "deltanet_core.cuh"
 
 #define CH_W LB_CHAIN_WARPS
 #define CH_GC LB_CHAIN_GC
@@ -317,7 +318,8 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     if (tid < CH_W * NS) mbar_init(&full[tid], 1);
     if (tid < p.n_ops) {
         const lb_chain_op& op = p.op[tid];
-        const int n0 = ch_start(c, op.units, op.upo, G), no = ch_start(c + 1, op.units, op.upo, G) - n0;
+        const bool gemv = op.type == LB_CHAIN_OP_GEMV;
+        const int n0 = gemv ? ch_start(c, op.units, op.upo, G) : 0, no = gemv ? ch_start(c + 1, op.units, op.upo, G) - n0 : 0;
         sh.op_n0[tid] = n0;
         sh.op_no[tid] = no;
         sh.op_np[tid] = (no + 1) / 2;
@@ -343,8 +345,8 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             const uint32_t full_pair = st.recb == 2 * LB_CHAIN_RECORD;
             if (lane == 0)
                 tab[n_mine] = make_uint2((uint32_t)((st.src - p.op[k.o].packed) >> 4),
-                                         (uint32_t)k.o | ((uint32_t)k.pair << 4) | ((uint32_t)st.g0 << 12) | ((uint32_t)st.gcount << 24) |
-                                             (full_pair << 28));
+                                         (uint32_t)k.o | ((uint32_t)k.pair << 5) | ((uint32_t)st.g0 << 10) | ((uint32_t)st.gcount << 22) |
+                                             (full_pair << 25));
             ++n_mine;
             k.advance(sh, p.n_ops, CH_W);
         }
@@ -357,9 +359,9 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         if (lane == 0) {
             const uint2 e = tab[m_req];
             const uint32_t slot = warp * NS + m_req % NS;
-            const uint32_t bytes = ((e.y >> 24) & 15u) * ((e.y >> 28) & 1u ? 2u * LB_CHAIN_RECORD : (uint32_t)LB_CHAIN_RECORD);
+            const uint32_t bytes = ((e.y >> 22) & 7u) * ((e.y >> 25) & 1u ? 2u * LB_CHAIN_RECORD : (uint32_t)LB_CHAIN_RECORD);
             mbar_arrive_expect_tx(&full[slot], bytes);
-            bulk_g2s(smem + (size_t)slot * LB_CHAIN_STAGE_BYTES, p.op[e.y & 15u].packed + ((size_t)e.x << 4), bytes, &full[slot], pol);
+            bulk_g2s(smem + (size_t)slot * LB_CHAIN_STAGE_BYTES, p.op[e.y & 31u].packed + ((size_t)e.x << 4), bytes, &full[slot], pol);
         }
         ++m_req;
     };
@@ -371,6 +373,8 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     for (int o = 0; o < p.n_ops; ++o) {
         const lb_chain_op& op = p.op[o];
         const int n0 = sh.op_n0[o], no = sh.op_no[o];
+        unsigned long long* const tl = p.timeline ? p.timeline + ((size_t)c * LB_CHAIN_MAX_OPS + o) * 4 : nullptr;
+        if (tl && tid == 0) tl[0] = globaltimer_ns();
         if (o > 0) {
             // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
             __syncthreads();
@@ -391,14 +395,35 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             }
             __syncthreads();
         }
+        if (tl && tid == 0) tl[1] = globaltimer_ns();
         if (o == p.trigger_op) pdl_launch_dependents();
         if (sh.snap) break; // uniform: written before the barrier above, by one thread
+
+        if (op.type == LB_CHAIN_OP_DELTANET) {
+            // ---- the DeltaNet mixer of a layer: (value head, 32-column slab) units, one per team of 128 threads.
+            //      The warps' weight rings stay full meanwhile (their next stages belong to the following GEMV). ----
+            const lb_dn_layer_params& dn = *reinterpret_cast<const lb_dn_layer_params*>(op.ext);
+            const int team = tid >> 7;
+            dn_unit_smem& sm = reinterpret_cast<dn_unit_smem*>(red)[team];
+            for (int u = c + G * team; u < dn.HV * (DN_D / DN_COLS); u += G * (LB_CHAIN_THREADS / DN_THREADS)) {
+                deltanet_layer_unit<false>(dn, u / (DN_D / DN_COLS), u % (DN_D / DN_COLS), tid & (DN_THREADS - 1), sm, [team] {
+                    asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "n"(DN_THREADS) : "memory");
+                });
+                asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "n"(DN_THREADS) : "memory"); // the unit's shared memory is reused
+            }
+            if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
+            __syncthreads();
+            if (tl && tid == 0) tl[2] = tl[3] = globaltimer_ns();
+            if (sh.snap) break;
+            continue;
+        }
 
         // ---- the activation vector as exact integers: three signed base-256 digit planes ----
         for (int i = tid; i < ((no + 1) / 2) * CH_W * 16; i += LB_CHAIN_THREADS) red[i] = 0.f;
         const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xdig, xsumf, tid, c == 0)
                                                              : ch_prologue<5>(op, sh, xdig, xsumf, tid, c == 0);
 
+        if (tl && tid == 0) tl[2] = globaltimer_ns();
         // ---- this warp's stages of GEMV o.  Column sums stay in registers while consecutive stages belong to
         //      the same pair, and go to this warp's own row of `red` when the pair changes. ----
         float acc_a = 0.f, acc_b = 0.f;
@@ -419,14 +444,14 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         };
         while (m_use < n_mine) {
             const uint2 e = tab[m_use];
-            if ((int)(e.y & 15u) != o) break; // the stream has reached the next GEMV
+            if ((int)(e.y & 31u) != o) break; // the stream has reached the next GEMV
             const uint32_t slot = warp * NS + m_use % NS;
             if (!__all_sync(0xffffffffu, mbar_wait(&full[slot], (m_use / NS) & 1))) { // the same answer in every lane
                 if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); sh.bad = 1; }
                 break;
             }
-            const int pair = (int)((e.y >> 4) & 255u), g0 = (int)((e.y >> 12) & 4095u), gcount = (int)((e.y >> 24) & 15u);
-            const bool full_pair = (e.y >> 28) & 1u;
+            const int pair = (int)((e.y >> 5) & 31u), g0 = (int)((e.y >> 10) & 4095u), gcount = (int)((e.y >> 22) & 7u);
+            const bool full_pair = (e.y >> 25) & 1u;
             if (pair != cur_pair) {
                 flush();
                 cur_pair = pair;
@@ -468,6 +493,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                 reinterpret_cast<__half*>(op.y)[(n0 / 2) * 8 + tid] = __float2half_rn(siluf_dev(gate) * up);
             }
         }
+        if (tl && tid == 0) tl[3] = globaltimer_ns();
         if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
         __syncthreads(); // red / vals are reused by the next GEMV; sh.snap is the same for everyone
         if (sh.snap) break;

@@ -13,12 +13,7 @@
 // a 32-column slab of one head and holds it in REGISTERS (128 threads x 32
 // fp32): the state is read from HBM once and written once per step, and when
 // n_steps > 1 it stays on chip for the whole run of steps.
-#include "common.cuh"
-#include "params.h"
-
-#define DN_D 128
-#define DN_COLS 32      // state columns per CTA
-#define DN_THREADS 128  // 8 column-quads x 16 row phases
+#include "deltanet_core.cuh"
 
 template <typename T> __device__ __forceinline__ float ld_as_f32(const T* p, size_t i);
 template <> __device__ __forceinline__ float ld_as_f32<float>(const float* p, size_t i) { return p[i]; }
@@ -149,110 +144,6 @@ extern "C" __global__ void decay_gate_beta(const __grid_constant__ lb_decay_para
 // previous slots while one of them writes the current one.
 // ---------------------------------------------------------------------------
 extern "C" __global__ void __launch_bounds__(DN_THREADS) deltanet_layer_fused(const __grid_constant__ lb_dn_layer_params p) {
-    __shared__ float ks[DN_D], qs[DN_D], vs[DN_COLS], red[40];
-    __shared__ __align__(16) float part[16][DN_COLS];
-    const int h = blockIdx.x, jb = blockIdx.y;
-    const int gqa = p.HV / p.HK, kh = h / gqa;
-    const int t = threadIdx.x, tj = t & 7, ti = t >> 3;
-    const int j0 = jb * DN_COLS + tj * 4;
-    const int QK = p.HK * DN_D, C = 2 * QK + p.HV * DN_D;
-    float* S = p.state + (size_t)h * DN_D * DN_D;
-
-    // the state slab does not depend on the previous kernel of this step: load it first
-    float4 s[8];
-#pragma unroll
-    for (int rr = 0; rr < 8; ++rr) s[rr] = *reinterpret_cast<const float4*>(S + (size_t)(ti + 16 * rr) * DN_D + j0);
-
-    pdl_wait();
-    const int pos = p.pos[0];
-    // decay / beta projections: two 5120-long dot products per value head
-    float a = 0.f, b = 0.f;
-    {
-        const uint4* ra = reinterpret_cast<const uint4*>(p.proj_a + (size_t)h * p.hidden);
-        const uint4* rb = reinterpret_cast<const uint4*>(p.proj_b + (size_t)h * p.hidden);
-        const uint4* xv = reinterpret_cast<const uint4*>(p.xn);
-        for (int i = t; i < p.hidden / 8; i += DN_THREADS) {
-            const uint4 wa = __ldg(ra + i), wb = __ldg(rb + i), xx = xv[i];
-            const uint32_t aw[4] = {wa.x, wa.y, wa.z, wa.w}, bw[4] = {wb.x, wb.y, wb.z, wb.w}, xw[4] = {xx.x, xx.y, xx.z, xx.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xw[j]));
-                a = fmaf(__uint_as_float(aw[j] << 16), xf.x, a);
-                a = fmaf(__uint_as_float(aw[j] & 0xffff0000u), xf.y, a);
-                b = fmaf(__uint_as_float(bw[j] << 16), xf.x, b);
-                b = fmaf(__uint_as_float(bw[j] & 0xffff0000u), xf.y, b);
-            }
-        }
-        a = block_sum(a, red);
-        b = block_sum(b, red);
-    }
-    const float tt = a + bf16_bits_to_f32(p.dt_bias[h]);
-    const float sp = tt > 20.f ? tt : log1pf(expf(tt));
-    const float g = expf(-expf(p.a_log[h]) * sp);
-    const float beta = 1.0f / (1.0f + expf(-b));
-
-    // causal depthwise conv (ring history) + SiLU on this head's q, k channels and this slab's v channels
-    auto conv = [&](int c) {
-        const float x = p.qkvz[c];
-        float y = bf16_bits_to_f32(p.conv_w[c]) * x;
-        y = fmaf(bf16_bits_to_f32(p.conv_w[C + c]), p.conv_ring[(size_t)((pos + 3) & 3) * C + c], y);
-        y = fmaf(bf16_bits_to_f32(p.conv_w[2 * C + c]), p.conv_ring[(size_t)((pos + 2) & 3) * C + c], y);
-        y = fmaf(bf16_bits_to_f32(p.conv_w[3 * C + c]), p.conv_ring[(size_t)((pos + 1) & 3) * C + c], y);
-        return siluf_dev(y);
-    };
-    const int cq = kh * DN_D + t, ck = QK + kh * DN_D + t, cv = 2 * QK + h * DN_D + jb * DN_COLS + t;
-    float qv = conv(cq), kv = conv(ck);
-    if (t < DN_COLS) vs[t] = conv(cv);
-    // one CTA per key head (and every CTA for its own v channels) records the current token
-    if (h % gqa == 0 && jb == 0) {
-        p.conv_ring[(size_t)(pos & 3) * C + cq] = p.qkvz[cq];
-        p.conv_ring[(size_t)(pos & 3) * C + ck] = p.qkvz[ck];
-    }
-    if (t < DN_COLS) p.conv_ring[(size_t)(pos & 3) * C + cv] = p.qkvz[cv];
-    const float qn = block_sum(qv * qv, red), kn = block_sum(kv * kv, red);
-    qs[t] = qv * rsqrtf(qn) * 0.08838834764831845f; // l2norm then 1/sqrt(128)
-    ks[t] = kv * rsqrtf(kn);
-    __syncthreads();
-    pdl_launch_dependents();
-
-    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int rr = 0; rr < 8; ++rr) {
-        const float kk = ks[ti + 16 * rr];
-        r.x = fmaf(kk, s[rr].x, r.x); r.y = fmaf(kk, s[rr].y, r.y);
-        r.z = fmaf(kk, s[rr].z, r.z); r.w = fmaf(kk, s[rr].w, r.w);
-    }
-    *reinterpret_cast<float4*>(&part[ti][tj * 4]) = r;
-    __syncthreads();
-    r = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float4 q4 = *reinterpret_cast<const float4*>(&part[i][tj * 4]);
-        r.x += q4.x; r.y += q4.y; r.z += q4.z; r.w += q4.w;
-    }
-    float4 d;
-    d.x = beta * (vs[tj * 4 + 0] - r.x); d.y = beta * (vs[tj * 4 + 1] - r.y);
-    d.z = beta * (vs[tj * 4 + 2] - r.z); d.w = beta * (vs[tj * 4 + 3] - r.w);
-    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int rr = 0; rr < 8; ++rr) {
-        const float kk = ks[ti + 16 * rr], qq = qs[ti + 16 * rr];
-        s[rr].x = fmaf(kk, d.x, g * s[rr].x); s[rr].y = fmaf(kk, d.y, g * s[rr].y);
-        s[rr].z = fmaf(kk, d.z, g * s[rr].z); s[rr].w = fmaf(kk, d.w, g * s[rr].w);
-        o.x = fmaf(s[rr].x, qq, o.x); o.y = fmaf(s[rr].y, qq, o.y);
-        o.z = fmaf(s[rr].z, qq, o.z); o.w = fmaf(s[rr].w, qq, o.w);
-        *reinterpret_cast<float4*>(S + (size_t)(ti + 16 * rr) * DN_D + j0) = s[rr];
-    }
-    __syncthreads();
-    *reinterpret_cast<float4*>(&part[ti][tj * 4]) = o;
-    __syncthreads();
-    if (ti == 0) {
-        o = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float4 q4 = *reinterpret_cast<const float4*>(&part[i][tj * 4]);
-            o.x += q4.x; o.y += q4.y; o.z += q4.z; o.w += q4.w;
-        }
-        *reinterpret_cast<float4*>(p.out + (size_t)h * DN_D + j0) = o;
-    }
+    __shared__ dn_unit_smem sm;
+    deltanet_layer_unit<true>(p, blockIdx.x, blockIdx.y, threadIdx.x, sm, [] { __syncthreads(); });
 }

@@ -68,7 +68,9 @@ typedef struct {
  *   K-groups in order, each group as [record of the first octet][record of the second octet].
  * A pipeline stage is LB_CHAIN_GC consecutive K-groups of one pair (4352 bytes), brought by one 1-D
  * bulk copy and consumed by ONE warp. */
-#define LB_CHAIN_MAX_OPS 8
+#define LB_CHAIN_MAX_OPS 24
+#define LB_CHAIN_OP_GEMV 0
+#define LB_CHAIN_OP_DELTANET 1      /* the DeltaNet mixer of one layer (deltanet_core.cuh); ext = lb_dn_layer_params in device memory */
 #define LB_CHAIN_WARPS 16            /* consumer warps; every warp streams its own stages */
 #define LB_CHAIN_THREADS (LB_CHAIN_WARPS * 32)
 #define LB_CHAIN_RECORD 544          /* bytes per (octet, K-group) */
@@ -89,6 +91,8 @@ typedef struct {
     int32_t upo;      /* octets per unit: 1 or 2 */
     int32_t x_mode, y_mode;
     float eps;
+    int32_t type;     /* LB_CHAIN_OP_* */
+    const void* ext;  /* parameters of a non-GEMV entry, in device memory */
 } lb_chain_op;
 
 typedef struct {
@@ -101,6 +105,8 @@ typedef struct {
     int32_t max_pairs;    /* pairs (incl. a trailing single) of the widest strip of the chain */
     int32_t trigger_op;   /* griddepcontrol.launch_dependents is issued when this GEMV starts */
     int32_t tab_len;      /* entries of a warp's stage list: ceil(stages of the busiest CTA / warps) */
+    unsigned long long* timeline; /* optional [gridDim.x][LB_CHAIN_MAX_OPS][4] %globaltimer stamps of thread 0: reached the
+                                     grid barrier, left it, activation table ready (or mixer started), entry finished */
 } lb_chain_params;
 
 /* gemv_pack_strips: reference format -> strip-packed (one thread per 32-bit word of the output) */

@@ -76,7 +76,7 @@ def test_graph_replay_equals_eager(ctx, lb, oracle):
     logits_eager = gm.logits()
     gm.reset_state()
     gm.capture()
-    assert gm.step_kernels == 2 * cfg.n_layers + 4   # embed, first input projection, (mixer, GEMV chain) per layer, LM head, arg-max
+    assert gm.step_kernels <= cfg.n_layers + 4        # embed, persistent chains broken only by the attention kernel, LM head, arg-max
     gm.set_input(5, 0)
     replayed = []
     for pos in range(24):
