@@ -274,10 +274,12 @@ def prefill_state(model, cfg, lb, ctx_len, seed=4242):
             model.set_state(l, 1, lb.fill_normal(rbytes // 4, seed, 400000 + stream))
 
 
-def time_gemv_mix(ctx, lb, cfg, args, tp_size=1):
+def time_gemv_mix(ctx, lb, cfg, args, tp_size=1, chained=False):
     """The step's own int4 GEMV launch mix (5 per layer, real shapes, norm prologues and fused
     epilogues, weights rotating over > L2 worth of distinct matrices), captured as one graph and
-    timed alone with CUDA events: average duration and algorithmic bytes per launch."""
+    timed alone with CUDA events: average duration and algorithmic bytes per launch.
+    chained: the four GEMVs between two token mixers (out, gate/up, down, next input projection) go out as
+    ONE persistent gemv_chain launch, as the single-GPU decode step issues them; a launch is then a whole chain."""
     H, I = cfg.hidden, cfg.inter
     C_, V, I = cfg.conv_channels // tp_size, cfg.dn_v_heads * 128 // tp_size, I // tp_size   # this shard's slices
     shapes = [(H, C_ + V, "in"), (V, H, "out"), (H, 2 * I, "gateup"), (I, H, "down")]
@@ -289,7 +291,8 @@ def time_gemv_mix(ctx, lb, cfg, args, tp_size=1):
             qw = ctx.to_device(lb.fill_u32(K // 8 * N, 7 + s_, 1))
             sc = ctx.to_device(lb.fill_scales_f16(K // 128 * N, 7 + s_, 2))
             qz = ctx.to_device(lb.fill_u32(K // 128 * (N // 8), 7 + s_, 3))
-            row.append((qw, sc, qz, K, N))
+            pk = ctx.gemv_pack(qw, sc, qz, K, N, swiglu=(len(row) == 2)) if chained else None
+            row.append((qw, sc, qz, K, N, pk))
         mats.append(row)
     X = ctx.to_device(lb.fill_normal(H, 7, 4))
     nw = ctx.to_device(lb.fill_normal(H, 7, 5, std=0.02, dtype="bf16"))
@@ -300,6 +303,13 @@ def time_gemv_mix(ctx, lb, cfg, args, tp_size=1):
     n_layers = 12
     for l in range(n_layers):
         m_ = mats[l % sets]
+        if chained:
+            op = lambda w, x, y, xm, ym, **kw: dict(packed=w[5], x=x, y=y, K=w[3], N=w[4], x_mode=xm, y_mode=ym, **kw)
+            ctx.gemv_chain([op(m_[1], y_mix, X, lb.X_F32_HEADNORM_SILU, lb.Y_F32_ACCUM, aux0=hw, aux1=y_in),
+                            op(m_[2], X, y_m, lb.X_F32_RMSNORM, lb.Y_SWIGLU_F16, aux0=nw),
+                            op(m_[3], y_m, X, lb.X_F16, lb.Y_F32_ACCUM),
+                            op(mats[(l + 1) % sets][0], X, y_in, lb.X_F32_RMSNORM, lb.Y_F32, aux0=nw, x_out=xn)])
+            continue
         ctx.gemv_int4_fused(m_[0][0], m_[0][1], m_[0][2], X, y_in, H, C_ + V, lb.X_F32_RMSNORM, lb.Y_F32, aux0=nw, x_out=xn)
         ctx.gemv_int4_fused(m_[1][0], m_[1][1], m_[1][2], y_mix, X, V, H, lb.X_F32_HEADNORM_SILU, lb.Y_F32_ACCUM, aux0=hw, aux1=y_in)
         ctx.gemv_int4_fused(m_[2][0], m_[2][1], m_[2][2], X, y_m, H, 2 * I, lb.X_F32_RMSNORM, lb.Y_SWIGLU_F16, aux0=nw)
@@ -422,7 +432,8 @@ def bench_decode(args, rank, local, world, dist):
         dist.all_reduce(t_)
         algo_step = decode_algorithmic_bytes(cfg, int(t_.item()), CTX_PREFILL)
     peak, which = measured_hbm_peak()
-    gemv_s, gemv_algo, _ = time_gemv_mix(ctx, lb, cfg, args, world)
+    chained = world == 1 and not args.no_chain
+    gemv_s, gemv_algo, _ = time_gemv_mix(ctx, lb, cfg, args, world, chained=chained)
     out = {
         "metric": "batch-1 decode tok/s (Qwen3.5-27B-shaped hybrid, GPTQ int4, 4096-token state)", "value": 1.0 / step_s,
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
@@ -438,9 +449,13 @@ def bench_decode(args, rank, local, world, dist):
         "step_roofline": {"algorithmic_bytes_per_step": algo_step, "achieved_GBs": algo_step / step_s / 1e9, "peak_GBs": peak * world,
                           "frac": algo_step / step_s / 1e9 / (peak * world), "tok_s_at_peak": peak * world * 1e9 / algo_step},
         "roofline": {"bound": "hbm", "achieved": gemv_algo / gemv_s / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": gemv_algo / gemv_s / 1e9 / peak, "traffic": None, "peak_source": which, "kernel": "gemv_int4_w256",
+                     "frac": gemv_algo / gemv_s / 1e9 / peak, "traffic": None, "peak_source": which,
+                     "kernel": "gemv_chain" if chained else "gemv_int4_w256",
                      "us_per_launch": gemv_s * 1e6, "algorithmic_bytes": gemv_algo,
-                     "how": "this GPU's int4 GEMV launch mix of the step (4 shapes x 12 layers, fused prologues/epilogues) replayed alone as a graph"},
+                     "how": ("the step's four int4 GEMVs between two token mixers (out, gate/up + SwiGLU, down, next input projection; fused norm "
+                             "prologues) as ONE persistent gemv_chain launch, 12 launches over rotating weights replayed alone as a graph; bytes = "
+                             "the four matrices in the reference format") if chained else
+                            "this GPU's int4 GEMV launch mix of the step (4 shapes x 12 layers, fused prologues/epilogues) replayed alone as a graph"},
         "clocks": clocks,
     }
     model.close()

@@ -379,18 +379,23 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
             __syncthreads();
             if (tid == 0) {
-                __threadfence();
-                atomicAdd(p.sync, 1u);
+                // arrive with release (this block's results, ordered before by the barrier above, become visible to
+                // whoever observes the count), then poll with acquire; the status word of an earlier failed wait is
+                // looked at only once the wait is already long
+                asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
                 const unsigned target = (unsigned)o * (unsigned)G;
-                const uint64_t t0 = globaltimer_ns();
-                bool ok = false;
-                const bool dead = sh.bad || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u;
-                for (unsigned it = 0; it < LB_WAIT_SPINS && !dead; ++it) {
-                    if (ld_acquire_gpu(p.sync) >= target) { ok = true; break; }
-                    if ((it & 63u) == 63u && globaltimer_ns() - t0 > LB_WAIT_NS) break;
+                bool ok = sh.bad == 0;
+                if (ok && ld_acquire_gpu(p.sync) < target) {
+                    const uint64_t t0 = globaltimer_ns();
+                    ok = false;
+                    for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
+                        if (ld_acquire_gpu(p.sync) >= target) { ok = true; break; }
+                        if ((it & 255u) == 255u &&
+                            (globaltimer_ns() - t0 > LB_WAIT_NS || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u))
+                            break;
+                    }
                 }
                 if (!ok) { atomicExch(p.status, LB_DEV_TIMEOUT_COUNTER); sh.bad = 1; }
-                __threadfence();
                 sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             }
             __syncthreads();
