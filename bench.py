@@ -469,6 +469,22 @@ def bench_decode(args, rank, local, world, dist):
     return out
 
 
+def bench_chain(args, local):
+    """--workload chain: gemv_chain on the decode step's GEMV mix, alone (1.2 GB on the device)"""
+    import lithos_b200 as lb
+    from lithos_b200 import model as M
+    ctx = lb.Context(local)
+    cfg = M.qwen35_27b(max_ctx=64)
+    s_, algo, n = time_gemv_mix(ctx, lb, cfg, args, 1, chained=True)
+    peak, which = measured_hbm_peak()
+    out = {"metric": "gemv_chain launch (4 int4 GEMVs of one layer)", "value": s_ * 1e6, "unit": "us", "n_gpus": 1,
+           "higher_is_better": False, "data": "synthetic", "launches_timed": n,
+           "roofline": {"bound": "hbm", "achieved": algo / s_ / 1e9, "peak": peak, "unit": "GB/s", "frac": algo / s_ / 1e9 / peak,
+                        "peak_source": which, "kernel": "gemv_chain", "algorithmic_bytes": algo}}
+    ctx.close()
+    return out
+
+
 def reference_decode(args, rank):
     """--impl reference: the reference's kernels have no CPU implementation that can run (its interpreters
     evaluate the integer host dialect only), so this arm times the plain-C restatement on the host cores."""
@@ -490,7 +506,9 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "chain"],
+                    help="decode: the benchmark; gemv: config 0 alone; chain: the decode step's four GEMVs between two token "
+                         "mixers as persistent gemv_chain launches alone (the small case used for ncu captures)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: number of layers (64 = the benchmark definition)")
     ap.add_argument("--seed", type=int, default=20260413)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -507,6 +525,11 @@ def main():
             print(json.dumps(ref), flush=True)
         return
     dist = init_dist(world)
+    if args.workload == "chain":
+        out = bench_chain(args, local)
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        return
     out = (bench_decode if args.workload == "decode" else bench_gemv)(args, rank, local, world, dist)
     if rank == 0:
         print(json.dumps(out), flush=True)
