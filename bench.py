@@ -432,7 +432,7 @@ def bench_decode(args, rank, local, world, dist):
         dist.all_reduce(t_)
         algo_step = decode_algorithmic_bytes(cfg, int(t_.item()), CTX_PREFILL)
     peak, which = measured_hbm_peak()
-    chained = world == 1 and not args.no_chain
+    chained = not args.no_chain
     gemv_s, gemv_algo, _ = time_gemv_mix(ctx, lb, cfg, args, world, chained=chained)
     out = {
         "metric": "batch-1 decode tok/s (Qwen3.5-27B-shaped hybrid, GPTQ int4, 4096-token state)", "value": 1.0 / step_s,

@@ -153,7 +153,7 @@ int lb_gemv_int4_fused(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t 
  * lb_gemv_packed_bytes gives the size of the buffer the caller allocates; swiglu = 1 for a matrix
  * that will be used with the SwiGLU epilogue).  x and y of one entry must not overlap.
  * LB_ERR_INVALID when a shape puts more than 256 columns on one SM. */
-#define LB_GEMV_CHAIN_MAX 24
+#define LB_GEMV_CHAIN_MAX 32
 typedef struct {
     uint64_t packed;                  /* from lb_gemv_pack */
     uint64_t x, y, aux0, aux1, x_out; /* as in lb_gemv_int4_fused */

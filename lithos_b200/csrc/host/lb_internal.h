@@ -91,6 +91,7 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
     X(deltanet_step_f32)              \
     X(deltanet_layer_fused)           \
     X(attn_decode_split)              \
+    X(attn_decode_mma)                \
     X(embed_bf16)                     \
     X(argmax_f32)                     \
     X(rmsnorm_f32)                    \

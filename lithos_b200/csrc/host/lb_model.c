@@ -61,6 +61,7 @@ struct lb_model {
     int vocab_s;     /* vocabulary rows on this shard */
     int ar_count;    /* all-reduces issued so far in the step being built (slot parity) */
     int use_chain;   /* consecutive GEMVs of the step go out as one persistent launch (lb_gemv_chain) */
+    CUdeviceptr tp_params[2]; /* tensor parallel: lb_tp_params of the two exchange slots in device memory, for the chain */
     lb_chain_op pend[LB_CHAIN_MAX_OPS]; /* GEMVs and DeltaNet mixers collected since the last stand-alone kernel */
     int n_pend;
 };
@@ -75,8 +76,8 @@ extern int lb_chain_fill_gemv(lb_ctx* c, lb_chain_op* d, const lb_gemv_op* o, in
 extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps,
                            uint64_t part_val, uint64_t part_idx);
 extern int lb_dense_ctas(lb_ctx* c, int N);
-extern int lb_attn_splits(lb_ctx* c, int pos, int HKV);
-extern unsigned lb_attn_smem(int G);
+extern int lb_attn_mma_splits(lb_ctx* c, int pos, int HKV);
+extern unsigned lb_attn_mma_smem(int G);
 
 static int is_fa(const lb_model_cfg* c, int l) { return (l % c->fa_period) == c->fa_period - 1; }
 
@@ -350,7 +351,7 @@ LB_API int lb_model_load_layer(lb_model* m, int layer, const void* const* slots)
         shard_plan p;
         int st = plan_make(c, R, T, L->is_fa, which, slots, &p);
         if (st == LB_OK) st = build_q4(m, mats[which], p.src, p.cs, p.ci, p.N, p.k0, p.k1);
-        if (st == LB_OK && m->tp_size == 1 && lb_gemv_chain_supports(m->c, mats[which]->K, mats[which]->N, which == 2) == LB_OK) {
+        if (st == LB_OK && lb_gemv_chain_supports(m->c, mats[which]->K, mats[which]->N, which == 2) == LB_OK) {
             /* second copy in the chain kernel's layout: every SM's columns contiguous */
             q4_mat* w = mats[which];
             st = dalloc(m, &w->packed, lb_gemv_packed_bytes(w->K, w->N));
@@ -554,6 +555,14 @@ static int row_parallel(lb_model* m, const q4_mat* w, CUdeviceptr x, int x_mode,
     if (!m->comm) return lb_fail(m->c, LB_ERR_STATE, "model: tensor-parallel shard without exchange buffers (lb_model_set_comm)");
     const int slot = m->ar_count++ & 1;
     LB_TRY(q4_gemv(m, w, x, (CUdeviceptr)lb_comm_slot_ptr(m->comm, slot), x_mode, LB_Y_F32, aux0, aux1, 0));
+    if (m->use_chain && w->packed && m->tp_params[slot]) { /* the exchange joins the persistent chain */
+        lb_chain_op k;
+        memset(&k, 0, sizeof k);
+        k.type = LB_CHAIN_OP_ALLREDUCE;
+        k.ext = (const void*)m->tp_params[slot];
+        return chain_push(m, &k);
+    }
+    LB_TRY(flush_chain(m));
     lb_tp_params p;
     LB_TRY(lb_comm_fill(m->comm, &p, slot, m->cfg.hidden));
     p.x = (float*)m->X;
@@ -607,15 +616,16 @@ static int issue_step(lb_model* m) {
             p.counters = (uint32_t*)(c->gemv_counters + 2048 * 4);
             p.pos_ptr = (const int*)m->d_pos; p.pos = 0;
             p.HQ = m->HQ; p.HKV = m->HKV;
-            p.splits = lb_attn_splits(c, cfg->max_ctx, m->HKV);
+            p.splits = lb_attn_mma_splits(c, cfg->max_ctx, m->HKV);
+            p.status = (uint32_t*)c->dev_status;
             p.in_dtype = 1; p.gate_stride = 512; p.q_stride = 512;
             p.rot_dims = cfg->rot_dims; p.rope_theta = cfg->rope_theta; p.eps = cfg->eps;
             for (int i = 0; i < cfg->rot_dims / 2; i++)
                 p.rope_freq[i] = exp2(-log2((double)cfg->rope_theta) * (double)i / (double)(cfg->rot_dims / 2));
             void* params[] = {&p};
             LB_TRY(flush_chain(m));
-            LB_TRY(lb_launch(c, LBK_attn_decode_split, (unsigned)m->HKV, (unsigned)p.splits, 1, 256,
-                             lb_attn_smem(m->HQ / m->HKV), params, 1));
+            LB_TRY(lb_launch(c, LBK_attn_decode_mma, (unsigned)m->HKV, (unsigned)p.splits, 1, 256,
+                             lb_attn_mma_smem(m->HQ / m->HKV), params, 1));
             LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32, 0, 0));
         }
         LB_TRY(q4_gemv(m, &L->w_gateup, m->X, m->mlp_m, LB_X_F32_RMSNORM, LB_Y_SWIGLU_F16, L->post_norm, 0, 0));
@@ -655,6 +665,13 @@ LB_API int lb_model_set_comm(lb_model* m, lb_comm* comm) {
         return lb_fail(m->c, LB_ERR_INVALID, "model: exchange buffers are for rank %d/%d, the model is shard %d/%d",
                        lb_comm_rank(comm), lb_comm_size(comm), m->tp_rank, m->tp_size);
     m->comm = comm;
+    for (int slot = 0; slot < 2; slot++) { /* the exchange parameters of both slots, for all-reduce entries of the chain */
+        lb_tp_params p;
+        LB_TRY(lb_comm_fill(comm, &p, slot, m->cfg.hidden));
+        p.x = (float*)m->X;
+        if (m->tp_params[slot]) { lb_drv.MemFree(m->tp_params[slot]); m->tp_params[slot] = 0; }
+        LB_TRY(upload(m, &m->tp_params[slot], &p, sizeof p));
+    }
     return LB_OK;
 }
 
@@ -715,7 +732,7 @@ LB_API void lb_model_destroy(lb_model* m) {
         lb_drv.StreamSynchronize(c->stream);
         if (m->graph) lb_graph_destroy(c, m->graph);
         CUdeviceptr g[] = {m->embed, m->lm_head, m->final_norm, m->X, m->xn, m->in_out, m->mix_out, m->mlp_m, m->logits,
-                           m->d_token, m->d_pos, m->d_next, m->cand_val, m->cand_idx};
+                           m->d_token, m->d_pos, m->d_next, m->cand_val, m->cand_idx, m->tp_params[0], m->tp_params[1]};
         for (size_t i = 0; i < sizeof g / sizeof g[0]; i++) if (g[i]) lb_drv.MemFree(g[i]);
         for (int l = 0; m->L && l < m->cfg.n_layers; l++) {
             layer_t* L = &m->L[l];

@@ -252,16 +252,18 @@ LB_API int lb_decay_gate(lb_ctx* c, uint64_t a, uint64_t a_log, uint64_t dt_bias
 }
 
 /* number of position slices: enough CTAs to fill the GPU twice, at least 64 rows each */
-int lb_attn_splits(lb_ctx* c, int pos, int HKV) {
-    int want = (2 * c->sm_count + HKV - 1) / HKV;
-    int by_len = pos / 64;
-    int s = want < by_len ? want : by_len;
+/* attn_decode_mma: a CTA of 8 warps takes a slice of 128 rows (one block of 16 per warp) where the context allows */
+int lb_attn_mma_splits(lb_ctx* c, int pos, int HKV) {
+    int s = (pos + 127) / 128;
+    (void)c; (void)HKV;
     if (s < 1) s = 1;
     if (s > 64) s = 64;
     return s;
 }
 
-unsigned lb_attn_smem(int G) { return (unsigned)((G * 256 + 256 + 256 + 40 + 2 * 8 * 8 + 8 * G * 256) * 4 + 64); }
+unsigned lb_attn_mma_smem(int G) {
+    return (unsigned)(8 * 2 * 16 * 528 + G * 256 * 4 + 2 * 8 * 528 + 2 * 256 * 4 + 2 * 128 * 4 + 2 * 8 * 8 * 4 + 8 * 8 + 128);
+}
 
 LB_API int lb_attention_decode(lb_ctx* c, uint64_t q, uint64_t k_new, uint64_t v_new, uint64_t gate, uint64_t q_norm_w,
                                uint64_t k_norm_w, uint64_t k_cache, uint64_t v_cache, uint64_t out, int pos, int HQ,
@@ -280,13 +282,14 @@ LB_API int lb_attention_decode(lb_ctx* c, uint64_t q, uint64_t k_new, uint64_t v
     p.k_cache = (uint16_t*)k_cache; p.v_cache = (uint16_t*)v_cache; p.out = (float*)out;
     p.scratch = (float*)c->attn_scratch; p.counters = (uint32_t*)(c->gemv_counters + 2048 * 4);
     p.pos = pos; p.HQ = HQ; p.HKV = HKV;
-    p.splits = lb_attn_splits(c, pos, HKV);
+    p.splits = lb_attn_mma_splits(c, pos, HKV);
+    p.status = (uint32_t*)c->dev_status;
     p.in_dtype = in_is_f32 ? 1 : 0;
     p.gate_stride = 256; p.q_stride = 256;
     p.rot_dims = rot_dims; p.rope_theta = rope_theta; p.eps = eps;
     for (int i = 0; i < rot_dims / 2; i++) p.rope_freq[i] = exp2(-log2((double)rope_theta) * (double)i / (double)(rot_dims / 2));
     void* params[] = {&p};
-    return lb_launch(c, LBK_attn_decode_split, (unsigned)HKV, (unsigned)p.splits, 1, 256, lb_attn_smem(G), params, 1);
+    return lb_launch(c, LBK_attn_decode_mma, (unsigned)HKV, (unsigned)p.splits, 1, 256, lb_attn_mma_smem(G), params, 1);
 }
 
 LB_API int lb_rmsnorm(lb_ctx* c, uint64_t x, uint64_t res, uint64_t w, uint64_t y, uint64_t sum_out, int rows, int D,

@@ -27,6 +27,7 @@
 // Activations written inside the launch are read through L2 only (ld.global.cg).
 #include "gemv_core.cuh"
 #include "deltanet_core.cuh"
+#include "comm_core.cuh"
 
 #define CH_W LB_CHAIN_WARPS
 #define CH_GC LB_CHAIN_GC
@@ -404,6 +405,31 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         if (o == p.trigger_op) pdl_launch_dependents();
         if (sh.snap) break; // uniform: written before the barrier above, by one thread
 
+        if (op.type == LB_CHAIN_OP_ALLREDUCE) {
+            // ---- tensor parallel: every rank's partial vector (written by the GEMV before this entry into the rank's
+            //      exchange buffer) is added into the residual stream, in rank order, by CTA 0 of every GPU; the other
+            //      CTAs go on to the next grid barrier.  The grid barrier above made this GPU's partial complete. ----
+            if (c == 0) {
+                const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
+                __shared__ bool s_ok;
+                const unsigned gen = tp.gen[0] + 1u;
+                const bool ok = tp_rendezvous(tp, gen, &s_ok);
+                if (ok) {
+                    for (int i = tid; i < tp.n; i += LB_CHAIN_THREADS) {
+                        float sum = 0.f;
+                        for (int r = 0; r < tp.size; ++r) sum += __ldcv(tp.partials[r] + (size_t)tp.slot * tp.n_max + i); // rank order
+                        tp.x[i] = __ldcg(tp.x + i) + sum;
+                    }
+                } else if (tid == 0) sh.bad = 1;
+                __syncthreads();
+                if (tid == 0) tp.gen[0] = gen;
+            }
+            if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
+            __syncthreads();
+            if (tl && tid == 0) tl[2] = tl[3] = globaltimer_ns();
+            if (sh.snap) break;
+            continue;
+        }
         if (op.type == LB_CHAIN_OP_DELTANET) {
             // ---- the DeltaNet mixer of a layer: (value head, 32-column slab) units, one per team of 128 threads.
             //      The warps' weight rings stay full meanwhile (their next stages belong to the following GEMV). ----

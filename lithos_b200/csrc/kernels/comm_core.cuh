@@ -1,0 +1,39 @@
+// The rendezvous of the tensor-parallel exchange, shared by the stand-alone kernels (comm.cu) and the all-reduce
+// entries of the persistent decode chain (chain.cu).  One thread block per GPU runs it.
+#pragma once
+#include "common.cuh"
+#include "params.h"
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// returns false when a peer did not show up in time
+__device__ __forceinline__ bool tp_rendezvous(const lb_tp_params& p, unsigned g, bool* s_ok) {
+    const int t = threadIdx.x;
+    if (t == 0) *s_ok = true;
+    __syncthreads();
+    if (t < p.size) {
+        __threadfence_system(); // the partial written by the previous kernel is visible to peers before the flag
+        st_release_sys(p.peer_flags[t] + p.rank, g);
+        const uint64_t t0 = globaltimer_ns();
+        bool ok = false;
+        // a wait that already ran out in this context is not repeated: every later exchange returns at once,
+        // so a lost peer costs one time limit, not one per exchange
+        const bool dead = *reinterpret_cast<volatile unsigned*>(p.status) != 0u;
+        for (unsigned it = 0; it < LB_WAIT_SPINS && !dead; ++it) {
+            // generations only grow; (int) difference keeps the test valid across wrap-around
+            if ((int)(ld_acquire_sys(p.my_flags + t) - g) >= 0) { ok = true; break; }
+            if ((it & 63u) == 63u && globaltimer_ns() - t0 > LB_WAIT_NS) break;
+        }
+        if (!ok) { atomicExch(p.status, LB_DEV_TIMEOUT_PEER); *s_ok = false; }
+    }
+    __syncthreads();
+    return *s_ok;
+}
+

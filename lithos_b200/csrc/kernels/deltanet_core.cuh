@@ -57,16 +57,31 @@ __device__ __forceinline__ void deltanet_layer_unit(const lb_dn_layer_params& p,
         const uint4* ra = reinterpret_cast<const uint4*>(p.proj_a + (size_t)h * p.hidden);
         const uint4* rb = reinterpret_cast<const uint4*>(p.proj_b + (size_t)h * p.hidden);
         const uint4* xv = reinterpret_cast<const uint4*>(p.xn);
-        for (int i = t; i < p.hidden / 8; i += DN_THREADS) {
-            const uint4 wa = __ldg(ra + i), wb = __ldg(rb + i), xx = __ldcg(xv + i);
-            const uint32_t aw[4] = {wa.x, wa.y, wa.z, wa.w}, bw[4] = {wb.x, wb.y, wb.z, wb.w}, xw[4] = {xx.x, xx.y, xx.z, xx.w};
+        // five 8-element pieces per thread and pass (hidden 5120 = exactly one pass): all fifteen loads are issued
+        // before the first use, so the two dot products cost one trip to L2, not one per piece
+        const int n8 = p.hidden / 8;
+        for (int base = 0; base < n8; base += 5 * DN_THREADS) {
+            uint4 wa[5], wb[5], xx[5];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xw[j]));
-                a = fmaf(__uint_as_float(aw[j] << 16), xf.x, a);
-                a = fmaf(__uint_as_float(aw[j] & 0xffff0000u), xf.y, a);
-                b = fmaf(__uint_as_float(bw[j] << 16), xf.x, b);
-                b = fmaf(__uint_as_float(bw[j] & 0xffff0000u), xf.y, b);
+            for (int j = 0; j < 5; ++j) {
+                const int i = base + j * DN_THREADS + t;
+                const bool on = i < n8;
+                wa[j] = on ? __ldg(ra + i) : make_uint4(0u, 0u, 0u, 0u);
+                wb[j] = on ? __ldg(rb + i) : make_uint4(0u, 0u, 0u, 0u);
+                xx[j] = on ? __ldcg(xv + i) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int j = 0; j < 5; ++j) {
+                const uint32_t aw[4] = {wa[j].x, wa[j].y, wa[j].z, wa[j].w}, bw[4] = {wb[j].x, wb[j].y, wb[j].z, wb[j].w};
+                const uint32_t xw[4] = {xx[j].x, xx[j].y, xx[j].z, xx[j].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xw[q]));
+                    a = fmaf(__uint_as_float(aw[q] << 16), xf.x, a);
+                    a = fmaf(__uint_as_float(aw[q] & 0xffff0000u), xf.y, a);
+                    b = fmaf(__uint_as_float(bw[q] << 16), xf.x, b);
+                    b = fmaf(__uint_as_float(bw[q] & 0xffff0000u), xf.y, b);
+                }
             }
         }
         a = dn_unit_sum(a, red, t, sync);

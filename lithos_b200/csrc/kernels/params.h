@@ -68,9 +68,10 @@ typedef struct {
  *   K-groups in order, each group as [record of the first octet][record of the second octet].
  * A pipeline stage is LB_CHAIN_GC consecutive K-groups of one pair (4352 bytes), brought by one 1-D
  * bulk copy and consumed by ONE warp. */
-#define LB_CHAIN_MAX_OPS 24
+#define LB_CHAIN_MAX_OPS 32
 #define LB_CHAIN_OP_GEMV 0
 #define LB_CHAIN_OP_DELTANET 1      /* the DeltaNet mixer of one layer (deltanet_core.cuh); ext = lb_dn_layer_params in device memory */
+#define LB_CHAIN_OP_ALLREDUCE 2     /* tensor parallel: x += sum over ranks of the partial vectors (comm_core.cuh); ext = lb_tp_params in device memory */
 #define LB_CHAIN_WARPS 16            /* consumer warps; every warp streams its own stages */
 #define LB_CHAIN_THREADS (LB_CHAIN_WARPS * 32)
 #define LB_CHAIN_RECORD 544          /* bytes per (octet, K-group) */
@@ -197,6 +198,7 @@ typedef struct {
     float rope_theta;
     float eps;
     double rope_freq[64]; /* theta^(-i/(rot_dims/2)), i < rot_dims/2 <= 64, computed on the host in double */
+    uint32_t* status;     /* device status word for bounded waits (attn_decode_mma); may be NULL */
 } lb_attn_params;
 
 /* ---- tensor-parallel exchange (comm.cu) ----------------------------------------------- */
