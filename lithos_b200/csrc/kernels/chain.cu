@@ -371,6 +371,13 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     const int fg = lane >> 2, ft = lane & 3;
     const float lane_mul = ft == 0 ? 1.0f : (ft == 1 ? 65536.0f : 0.0f);
     pdl_wait(); // activations and barrier words belong to the stream order
+    // tensor parallel: the exchange generation of this GPU, read once (every all-reduce entry of the launch shares it)
+    unsigned ar_gen0 = 0;
+    int ar_done = 0;
+    const lb_tp_params* ar_tp = nullptr;
+    for (int o = 0; o < p.n_ops; ++o)
+        if (p.op[o].type == LB_CHAIN_OP_ALLREDUCE) { ar_tp = reinterpret_cast<const lb_tp_params*>(p.op[o].ext); break; }
+    if (ar_tp) ar_gen0 = ar_tp->gen[0];
     for (int o = 0; o < p.n_ops; ++o) {
         const lb_chain_op& op = p.op[o];
         const int n0 = sh.op_n0[o], no = sh.op_no[o];
@@ -407,22 +414,40 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
 
         if (op.type == LB_CHAIN_OP_ALLREDUCE) {
             // ---- tensor parallel: every rank's partial vector (written by the GEMV before this entry into the rank's
-            //      exchange buffer) is added into the residual stream, in rank order, by CTA 0 of every GPU; the other
-            //      CTAs go on to the next grid barrier.  The grid barrier above made this GPU's partial complete. ----
-            if (c == 0) {
-                const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
-                __shared__ bool s_ok;
-                const unsigned gen = tp.gen[0] + 1u;
-                const bool ok = tp_rendezvous(tp, gen, &s_ok);
+            //      exchange buffer; the grid barrier above made this GPU's complete) is added into the residual stream in
+            //      rank order.  CTA 0 tells the peers, every CTA waits on this GPU's own flag array and sums its own
+            //      columns with plain peer loads (no multicast). ----
+            const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
+            const unsigned gen = ar_gen0 + (unsigned)(++ar_done);
+            if (c == 0 && tid < tp.size) {
+                __threadfence_system(); // this GPU's partial (observed complete through the grid barrier) before the flag
+                st_release_sys(tp.peer_flags[tid] + tp.rank, gen);
+            }
+            if (tid < tp.size) {
+                const uint64_t t0 = globaltimer_ns();
+                bool ok = sh.bad == 0;
                 if (ok) {
-                    for (int i = tid; i < tp.n; i += LB_CHAIN_THREADS) {
-                        float sum = 0.f;
-                        for (int r = 0; r < tp.size; ++r) sum += __ldcv(tp.partials[r] + (size_t)tp.slot * tp.n_max + i); // rank order
-                        tp.x[i] = __ldcg(tp.x + i) + sum;
+                    ok = false;
+                    for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
+                        // generations only grow; the (int) difference keeps the test valid across wrap-around
+                        if ((int)(ld_acquire_sys(tp.my_flags + tid) - gen) >= 0) { ok = true; break; }
+                        if ((it & 63u) == 63u && (globaltimer_ns() - t0 > LB_WAIT_NS || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) break;
                     }
-                } else if (tid == 0) sh.bad = 1;
-                __syncthreads();
-                if (tid == 0) tp.gen[0] = gen;
+                }
+                if (!ok) { atomicExch(p.status, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
+            }
+            __syncthreads();
+            if (!sh.bad) {
+                const int per = (tp.n + G - 1) / G, i = c * per + tid;
+                if (tid < per && i < tp.n) {
+                    float part[LB_TP_MAX];
+#pragma unroll
+                    for (int r = 0; r < LB_TP_MAX; ++r) part[r] = r < tp.size ? __ldcv(tp.partials[r] + (size_t)tp.slot * tp.n_max + i) : 0.f;
+                    float sum = 0.f;
+#pragma unroll
+                    for (int r = 0; r < LB_TP_MAX; ++r) sum += part[r]; // rank order
+                    tp.x[i] = __ldcg(tp.x + i) + sum;
+                }
             }
             if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             __syncthreads();
@@ -537,6 +562,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         if (old == (unsigned)G - 1u) {
             p.sync[0] = 0u;
             p.sync[1] = 0u;
+            if (ar_tp) const_cast<lb_tp_params*>(ar_tp)->gen[0] = ar_gen0 + (unsigned)ar_done; // every CTA has read the old value
         }
     }
     // no copy may still be in flight into this CTA's shared memory when it exits (only after a failed wait can
