@@ -73,6 +73,50 @@ def gptq_unpack(qweight: np.ndarray, K: int, N: int) -> np.ndarray:
     return out
 
 
+def pack_strips(qweight, scales, qzeros, K: int, N: int, n_sms: int, swiglu: bool = False) -> np.ndarray:
+    """The strip-packed weight layout of the persistent GEMV chain, restated with numpy (test infrastructure: the
+    byte-exact target of lb_gemv_pack).  The reference keeps every matrix as qweight [K/8,N] / scales [K/128,N] /
+    qzeros [K/128,N/8] (inference/gemv.ls:18-26); this layout holds the same numbers, reordered so that SM c owns
+    the octets [start(c), start(c+1)), start(c) = floor(c * units / n_sms) * octets_per_unit, as one contiguous range:
+    pair of octets by pair, K-group by K-group, per (octet, group) a record of 136 words: word 4*lane + j, lane =
+    4*g + t, is the packed word of row 16*group + t + 4*j and column 8*octet + g; then 8 words (fp16 scale | fp16
+    zero-point << 16).  With swiglu the input columns are interleaved 64-wide (gate, up) blocks and unit P is
+    (gate octet, up octet) of output columns 8P..8P+7."""
+    qw = np.asarray(qweight, dtype=np.uint32).reshape(K // 8, N)
+    sc = np.asarray(scales).view(np.uint16).reshape(K // 128, N).astype(np.uint32)
+    kg, no_total = K // 128, N // 8
+    if qzeros is None:
+        z = np.full((kg, N), 8, dtype=np.uint32)
+    else:
+        zw = np.asarray(qzeros, dtype=np.uint32).reshape(kg, N // 8)
+        z = (zw[:, :, None] >> (4 * np.arange(8, dtype=np.uint32))[None, None, :]) & 0xF
+        z = z.reshape(kg, N)
+    zh = np.asarray(z, dtype=np.float16).view(np.uint16).astype(np.uint32)
+    upo = 2 if swiglu else 1
+    units = no_total // upo
+    start = [(c * units // n_sms) * upo for c in range(n_sms + 1)]
+    out = np.zeros(no_total * kg * 136, dtype=np.uint32)
+    lane = np.arange(32)
+    g_of, t_of = lane >> 2, lane & 3
+    for c in range(n_sms):
+        n0, no = start[c], start[c + 1] - start[c]
+        for oi in range(no):
+            O = n0 + oi
+            if swiglu:
+                P = O >> 1
+                col0 = (P >> 3) * 128 + (O & 1) * 64 + (P & 7) * 8
+            else:
+                col0 = O * 8
+            pair = oi >> 1
+            recw = (2 if 2 * pair + 1 < no else 1) * 136
+            for q in range(kg):
+                dst = (n0 * kg + pair * kg * 2) * 136 + q * recw + (oi & 1) * 136
+                rows = (16 * q + t_of[:, None] + 4 * np.arange(4)[None, :])          # [lane][j]
+                out[dst:dst + 128] = qw[rows, (col0 + g_of)[:, None]].reshape(-1)
+                out[dst + 128:dst + 136] = sc[q, col0:col0 + 8] | (zh[q, col0:col0 + 8] << 16)
+    return out
+
+
 def gptq_unpack_zeros(qzeros: np.ndarray, K: int, N: int, group: int = 128) -> np.ndarray:
     out = np.empty((K // group, N), dtype=np.uint8)
     lib().orc_gptq_unpack_zeros(_p(qzeros), K, N, group, _p(out))

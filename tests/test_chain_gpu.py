@@ -27,7 +27,7 @@ def _dev(ctx, qw, sc, qz, K, N, swiglu=False):
 
 
 @pytest.mark.parametrize("K,N,zeros", [(5120, 16384, True), (6144, 5120, True), (17408, 5120, False), (5120, 34816, True),
-                                       (1024, 37888, True), (256, 64, True)])
+                                       (1024, 37888, True), (256, 64, True), (640, 2048, True)])
 def test_single_gemv_vs_oracle(ctx, lb, oracle, K, N, zeros):
     """the decode step's four shapes, the widest strips (37888 = 148 SMs x 256 columns) and a matrix with
     fewer octets than SMs, as chains of one"""
@@ -40,6 +40,20 @@ def test_single_gemv_vs_oracle(ctx, lb, oracle, K, N, zeros):
     assert ctx.device_status() == 0
     assert rel_err_max(got, want) <= TOL
     for b in d + [d_x, d_y]:
+        if b:
+            b.free()
+
+
+@pytest.mark.parametrize("K,N,swiglu,zeros", [(640, 5120, False, True), (256, 4096, True, True), (384, 1184, False, False)])
+def test_pack_is_byte_exact(ctx, lb, oracle, K, N, swiglu, zeros):
+    """lb_gemv_pack against the numpy restatement of the strip layout: strips of 4 and 5 octets with a trailing single
+    (5120 columns over the SMs), SwiGLU pairs, more SMs than octets, no zero-point tensor"""
+    qw, sc, qz, _ = gptq_case(K, N, seed=31, zeros=zeros)
+    d = _dev(ctx, qw, sc, qz, K, N, swiglu)
+    got = d[3].download(np.uint32, N // 8 * (K // 128) * 136)
+    want = oracle.pack_strips(qw, sc, qz, K, N, ctx.sm_count(), swiglu)
+    assert np.array_equal(got, want)
+    for b in d:
         if b:
             b.free()
 

@@ -98,3 +98,23 @@ def test_small_kernels(oracle):
     assert oracle.argmax(G["argmax_x"]) == int(G["argmax_idx"][0])  # first maximum wins
     assert np.array_equal(oracle.rope(G["rope_x"], 2, 256, 64, 0, 1e7), G["rope_x"])
     assert np.allclose(oracle.rope(G["rope_x"], 2, 256, 64, 3, 1e7), G["rope_y_pos3"], rtol=1e-5, atol=1e-6)
+
+
+def test_strip_layout_is_a_permutation(oracle):
+    """The strip-packed layout holds every packed word exactly once, for any SM count and for SwiGLU pairs, and its
+    (scale, zero-point) words match the reference tensors."""
+    from helpers import gptq_case
+    K, N = 384, 256
+    qw, sc, qz, _ = gptq_case(K, N, seed=3)
+    tag = np.arange(K // 8 * N, dtype=np.uint32).reshape(K // 8, N)      # distinct words, so positions can be traced
+    for n_sms, swiglu in ((148, False), (7, False), (5, True), (1, True)):
+        out = oracle.pack_strips(tag, sc, qz, K, N, n_sms, swiglu).reshape(-1, 136)
+        assert out.shape[0] == N // 8 * (K // 128)
+        assert np.array_equal(np.sort(out[:, :128].ravel()), tag.ravel())
+        # lane (g, t), word j of a record: row 16*group + t + 4*j of column 8*octet + g
+        rec = out[0]
+        col0 = int(rec[0]) % N
+        assert int(rec[4 * 5 + 2]) == (0 * 16 + 1 + 4 * 2) * N + col0 + 1   # lane 5 = (g 1, t 1), j = 2, first K-group
+        zeros = oracle.gptq_unpack_zeros(qz, K, N)
+        assert np.array_equal((out[0, 128:] >> 16).astype(np.uint16).view(np.float16).astype(np.int64), zeros[0, col0:col0 + 8])
+        assert np.array_equal((out[0, 128:] & 0xFFFF).astype(np.uint16), sc.view(np.uint16)[0, col0:col0 + 8])
