@@ -51,7 +51,7 @@ def test_pack_is_byte_exact(ctx, lb, oracle, K, N, swiglu, zeros):
     qw, sc, qz, _ = gptq_case(K, N, seed=31, zeros=zeros)
     d = _dev(ctx, qw, sc, qz, K, N, swiglu)
     got = d[3].download(np.uint32, N // 8 * (K // 128) * 136)
-    want = oracle.pack_strips(qw, sc, qz, K, N, ctx.sm_count(), swiglu)
+    want = oracle.pack_strips(qw, sc, qz, K, N, ctx.sm_count, swiglu)
     assert np.array_equal(got, want)
     for b in d:
         if b:
