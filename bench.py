@@ -449,7 +449,10 @@ def bench_decode(args, rank, local, world, dist):
         "step_roofline": {"algorithmic_bytes_per_step": algo_step, "achieved_GBs": algo_step / step_s / 1e9, "peak_GBs": peak * world,
                           "frac": algo_step / step_s / 1e9 / (peak * world), "tok_s_at_peak": peak * world * 1e9 / algo_step},
         "roofline": {"bound": "hbm", "achieved": gemv_algo / gemv_s / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": gemv_algo / gemv_s / 1e9 / peak, "traffic": None, "peak_source": which,
+                     "frac": gemv_algo / gemv_s / 1e9 / peak,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one such launch in the ncu capture summarised in
+                     # profiles/gemv_chain_layer_ncu.md (203 494 656 + 5 823 488); not re-measured by this run
+                     "traffic": 209318144 if chained and world == 1 else None, "peak_source": which,
                      "kernel": "gemv_chain" if chained else "gemv_int4_w256",
                      "us_per_launch": gemv_s * 1e6, "algorithmic_bytes": gemv_algo,
                      "how": ("the step's four int4 GEMVs between two token mixers (out, gate/up + SwiGLU, down, next input projection; fused norm "
