@@ -47,6 +47,7 @@ struct __align__(16) ch_shared {
     int op_no[LB_CHAIN_MAX_OPS];     // octets in the strip
     int op_np[LB_CHAIN_MAX_OPS];     // pairs in the strip (a trailing single octet counts as one)
     int op_nch[LB_CHAIN_MAX_OPS];    // chunks of CH_GC K-groups per pair
+    int op_pre[LB_CHAIN_MAX_OPS + 1]; // stages of this CTA before each GEMV (prefix sums of op_np * op_nch)
     uint32_t bad;  // a bounded wait ran out (set by any thread at any time)
     uint32_t snap; // copy of bad taken by thread 0 before a block barrier: the value all threads act on together
 };
@@ -54,17 +55,6 @@ struct __align__(16) ch_shared {
 // position in the CTA's stage list: GEMV o, pair of that GEMV's strip, chunk of CH_GC K-groups of the pair
 struct ch_cursor {
     int o, pair, chunk;
-    // move `by` stages forward (chunks run fastest, then pairs, then GEMVs)
-    __device__ __forceinline__ void advance(const ch_shared& sh, int n_ops, int by) {
-        chunk += by;
-        while (o < n_ops) {
-            const int nch = sh.op_nch[o];
-            while (chunk >= nch && pair < sh.op_np[o]) { chunk -= nch; ++pair; }
-            if (pair < sh.op_np[o]) return;
-            ++o; // past the last pair of this GEMV: the rest counts from the start of the next one
-            pair = 0;
-        }
-    }
 };
 
 struct ch_stage {
@@ -332,6 +322,15 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     }
     mbar_fence_init();
     __syncthreads();
+    if (tid == 0) {
+        int acc = 0;
+        for (int o = 0; o < p.n_ops; ++o) {
+            sh.op_pre[o] = acc;
+            acc += sh.op_np[o] * sh.op_nch[o];
+        }
+        sh.op_pre[p.n_ops] = acc;
+    }
+    __syncthreads();
 
     // ---- this warp's stream: stages warp, warp + 16, warp + 32, ... of the CTA's list (all GEMVs of the chain).
     //      The warp writes them down once as (offset, descriptor) words; stage number m of the stream lives in ring
@@ -339,17 +338,22 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     uint2* tab = stage_tab + (size_t)warp * p.tab_len;
     uint32_t n_mine = 0;
     {
-        ch_cursor k = {0, 0, 0};
-        k.advance(sh, p.n_ops, warp);
-        while (k.o < p.n_ops && n_mine < (uint32_t)p.tab_len) {
-            const ch_stage st = ch_decode(p, sh, k);
+        // the lanes write the warp's entries in parallel: entry m is stage warp + 16 m of the CTA's list
+        const int total = sh.op_pre[p.n_ops];
+        if (total > warp) n_mine = min((uint32_t)((total - warp + CH_W - 1) / CH_W), (uint32_t)p.tab_len);
+        for (uint32_t m = lane; m < n_mine; m += 32) {
+            const int k = warp + CH_W * (int)m;
+            int o = 0;
+            while (k >= sh.op_pre[o + 1]) ++o; // k < total, so this stops inside the list
+            ch_cursor cur;
+            cur.o = o;
+            const int li = k - sh.op_pre[o];
+            cur.pair = li / sh.op_nch[o];
+            cur.chunk = li - cur.pair * sh.op_nch[o];
+            const ch_stage st = ch_decode(p, sh, cur);
             const uint32_t full_pair = st.recb == 2 * LB_CHAIN_RECORD;
-            if (lane == 0)
-                tab[n_mine] = make_uint2((uint32_t)((st.src - p.op[k.o].packed) >> 4),
-                                         (uint32_t)k.o | ((uint32_t)k.pair << 5) | ((uint32_t)st.g0 << 10) | ((uint32_t)st.gcount << 22) |
-                                             (full_pair << 25));
-            ++n_mine;
-            k.advance(sh, p.n_ops, CH_W);
+            tab[m] = make_uint2((uint32_t)((st.src - p.op[o].packed) >> 4),
+                                (uint32_t)o | ((uint32_t)cur.pair << 5) | ((uint32_t)st.g0 << 10) | ((uint32_t)st.gcount << 22) | (full_pair << 25));
         }
     }
     __syncwarp();
