@@ -299,29 +299,24 @@ __device__ __forceinline__ void attn_mma_body(const lb_attn_params& p0, unsigned
         __syncthreads();
 #pragma unroll
         for (int g = 0; g < G; ++g) { Lg[g] = 0.f; Ag[g] = 0.f; }
-        int s2 = 0;
-        for (; s2 + 8 <= p.splits; s2 += 8) { // 8*G independent loads in flight, then added in slice order
-            float a8[G][8];
+        for (int s2 = 0; s2 < p.splits; s2 += 16) { // 16*G independent loads in flight, then added in slice order
+            float a16[G][16];
 #pragma unroll
             for (int g = 0; g < G; ++g)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) a8[g][j] = __ldcg(kvrec + ((size_t)(s2 + j) * G + g) * AT_REC + t);
+                for (int j = 0; j < 16; ++j)
+                    a16[g][j] = s2 + j < p.splits ? __ldcg(kvrec + ((size_t)(s2 + j) * G + g) * AT_REC + t) : 0.f;
 #pragma unroll
-            for (int g = 0; g < G; ++g)
+            for (int j = 0; j < 16; ++j)
+                if (s2 + j < p.splits) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float w = ms_s[(s2 + j) * G + g];
-                    Lg[g] = fmaf(ls_s[(s2 + j) * G + g], w, Lg[g]);
-                    Ag[g] = fmaf(a8[g][j], w, Ag[g]);
+                    for (int g = 0; g < G; ++g) {
+                        const float w = ms_s[(s2 + j) * G + g];
+                        Lg[g] = fmaf(ls_s[(s2 + j) * G + g], w, Lg[g]);
+                        Ag[g] = fmaf(a16[g][j], w, Ag[g]);
+                    }
                 }
         }
-        for (; s2 < p.splits; ++s2)
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float w = ms_s[s2 * G + g];
-                Lg[g] = fmaf(ls_s[s2 * G + g], w, Lg[g]);
-                Ag[g] = fmaf(__ldcg(kvrec + ((size_t)s2 * G + g) * AT_REC + t), w, Ag[g]);
-            }
         if (t == 0) p.counters[kv] = 0u;
     }
 #pragma unroll

@@ -422,6 +422,7 @@ extern "C" __global__ void __launch_bounds__(256) dense_bf16_gemv(const __grid_c
     for (int n = blockIdx.x * nwarps + warp; n < p.N; n += gridDim.x * nwarps) {
         const uint4* wr = reinterpret_cast<const uint4*>(p.w + (size_t)n * p.K);
         float a0 = 0.f, a1 = 0.f;
+#pragma unroll 5
         for (int i = lane; i < p.K / 8; i += 32) {
             uint4 w = __ldcs(wr + i);
             const float4 xa = *reinterpret_cast<const float4*>(xsm + i * 8);
