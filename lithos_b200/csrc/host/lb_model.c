@@ -52,7 +52,6 @@ struct lb_model {
     CUdeviceptr embed, lm_head, final_norm;
     int globals_loaded;
     /* activations */
-    CUdeviceptr mix_h; /* fp16 [V]: the DeltaNet out projection's input as the chain's mixer entry leaves it */
     CUdeviceptr X, xn, in_out, mix_out, mlp_m, logits, d_token, d_pos, d_next, cand_val, cand_idx;
     int* h_next; /* pinned */
     uint64_t weight_bytes;
@@ -128,7 +127,6 @@ LB_API int lb_model_create(lb_ctx* c, const lb_model_cfg* cfg, int tp_rank, int 
     LB_TRY(dalloc(m, &m->xn, (size_t)H * 2));
     LB_TRY(dalloc(m, &m->in_out, (size_t)n_in * 4));
     LB_TRY(dalloc(m, &m->mix_out, (size_t)n_mix * 4));
-    LB_TRY(dalloc(m, &m->mix_h, (size_t)m->HV * 128 * 2));
     LB_TRY(dalloc(m, &m->mlp_m, (size_t)m->inter_s * 2));
     LB_TRY(dalloc(m, &m->logits, (size_t)m->vocab_s * 4));
     LB_TRY(dalloc(m, &m->d_token, 16));
@@ -510,7 +508,6 @@ static void dn_fill_params(const lb_model* m, const layer_t* L, lb_dn_layer_para
     p->conv_w = (const uint16_t*)L->conv_w; p->conv_ring = (float*)L->conv_ring;
     p->state = (float*)L->dn_state; p->out = (float*)m->mix_out; p->pos = (const int*)m->d_pos;
     p->HV = m->HV; p->HK = m->HK; p->hidden = m->cfg.hidden;
-    p->h_out = (uint16_t*)m->mix_h; p->norm_w = (const float*)L->dn_norm; p->eps = m->cfg.eps;
 }
 
 /* launch what has been collected so far as one persistent kernel */
@@ -598,14 +595,12 @@ static int issue_step(lb_model* m) {
                 k.type = LB_CHAIN_OP_DELTANET;
                 k.ext = (const void*)L->dn_params;
                 LB_TRY(chain_push(m, &k));
-                /* the mixer entry has already applied the per-head norm and the silu(z) gate */
-                LB_TRY(row_parallel(m, &L->w_out, m->mix_h, LB_X_F16, 0, 0));
             } else {
                 void* params[] = {&p};
                 LB_TRY(flush_chain(m));
                 LB_TRY(lb_launch(c, LBK_deltanet_layer_fused, (unsigned)m->HV, 4, 1, 128, 0, params, 1));
-                LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32_HEADNORM_SILU, L->dn_norm, m->in_out + (size_t)C * 4));
             }
+            LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32_HEADNORM_SILU, L->dn_norm, m->in_out + (size_t)C * 4));
         } else {
             LB_TRY(q4_gemv(m, &L->w_in, m->X, m->in_out, LB_X_F32_RMSNORM, LB_Y_F32, L->input_norm, 0, 0));
             lb_attn_params p;
@@ -737,7 +732,7 @@ LB_API void lb_model_destroy(lb_model* m) {
         lb_drv.StreamSynchronize(c->stream);
         if (m->graph) lb_graph_destroy(c, m->graph);
         CUdeviceptr g[] = {m->embed, m->lm_head, m->final_norm, m->X, m->xn, m->in_out, m->mix_out, m->mlp_m, m->logits,
-                           m->d_token, m->d_pos, m->d_next, m->cand_val, m->cand_idx, m->tp_params[0], m->tp_params[1], m->mix_h};
+                           m->d_token, m->d_pos, m->d_next, m->cand_val, m->cand_idx, m->tp_params[0], m->tp_params[1]};
         for (size_t i = 0; i < sizeof g / sizeof g[0]; i++) if (g[i]) lb_drv.MemFree(g[i]);
         for (int l = 0; m->L && l < m->cfg.n_layers; l++) {
             layer_t* L = &m->L[l];

@@ -465,33 +465,11 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             const lb_dn_layer_params& dn = *reinterpret_cast<const lb_dn_layer_params*>(op.ext);
             const int team = tid >> 7;
             dn_unit_smem& sm = reinterpret_cast<dn_unit_smem*>(red)[team];
-            auto team_sync = [team] { asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "n"(DN_THREADS) : "memory"); };
-            if (dn.h_out) {
-                // CTA c takes head c: its four teams are the head's four slabs, so the per-head norm and the silu(z)
-                // gate of the out projection's input can be finished here, on chip
-                if (c < dn.HV) {
-                    deltanet_layer_unit<false>(dn, c, team, tid & (DN_THREADS - 1), sm, team_sync);
-                    __syncthreads(); // the head's 128 outputs are in memory (written by this CTA)
-                    float o = 0.f;
-                    if (tid < DN_D) {
-                        o = __ldcg(dn.out + (size_t)c * DN_D + tid);
-                        const float ss = warp_sum(o * o);
-                        if (lane == 0) sh.scratch[warp] = ss;
-                    }
-                    __syncthreads();
-                    if (tid < DN_D) {
-                        const float tot = (sh.scratch[0] + sh.scratch[1]) + (sh.scratch[2] + sh.scratch[3]);
-                        const float hr = rsqrtf(tot * (1.0f / DN_D) + dn.eps);
-                        const int C = (2 * dn.HK + dn.HV) * DN_D; // z follows the conv channels in the projection output
-                        const float z = __ldcg(dn.qkvz + C + (size_t)c * DN_D + tid);
-                        reinterpret_cast<__half*>(dn.h_out)[(size_t)c * DN_D + tid] = __float2half_rn(o * hr * __ldg(dn.norm_w + tid) * siluf_dev(z));
-                    }
-                }
-            } else {
-                for (int u = c + G * team; u < dn.HV * (DN_D / DN_COLS); u += G * (LB_CHAIN_THREADS / DN_THREADS)) {
-                    deltanet_layer_unit<false>(dn, u / (DN_D / DN_COLS), u % (DN_D / DN_COLS), tid & (DN_THREADS - 1), sm, team_sync);
-                    team_sync(); // the unit's shared memory is reused
-                }
+            for (int u = c + G * team; u < dn.HV * (DN_D / DN_COLS); u += G * (LB_CHAIN_THREADS / DN_THREADS)) {
+                deltanet_layer_unit<false>(dn, u / (DN_D / DN_COLS), u % (DN_D / DN_COLS), tid & (DN_THREADS - 1), sm, [team] {
+                    asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "n"(DN_THREADS) : "memory");
+                });
+                asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "n"(DN_THREADS) : "memory"); // the unit's shared memory is reused
             }
             if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             __syncthreads();

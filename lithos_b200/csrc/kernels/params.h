@@ -172,12 +172,6 @@ typedef struct {
     const int* pos;          /* device int: position of the token being decoded */
     int32_t HV, HK, hidden;
     int32_t h0;              /* first global value head of this shard (tensor parallel), for nothing but clarity */
-    /* persistent chain only: when h_out is set, a CTA runs the four slabs of one head and also writes the
-     * out-projection's input h = out * rsqrt(mean_head out^2 + eps) * norm_w * silu(z) as fp16 */
-    uint16_t* h_out;         /* fp16 [HV,128] or NULL */
-    const float* norm_w;     /* fp32 [128] per-head RMSNorm weight (plain) */
-    float eps;
-    int32_t pad_;
 } lb_dn_layer_params;
 
 /* ---- GQA decode attention ------------------------------------------------- */
