@@ -1,29 +1,32 @@
-// A chain of GPTQ int4 GEMVs in ONE persistent launch on sm_100a.
+// The persistent kernel of the decode step on sm_100a: a chain of GPTQ int4 GEMVs, DeltaNet mixers and (under
+// tensor parallelism) all-reduces in ONE launch of one CTA per SM, with a grid barrier between entries.
 //
 // The decode step of the reference runs its projections as separate launches
-// (src/launcher.s:1226-1535, one launch_gemv per projection); at batch 1 each of them moves
-// 25-90 MB and a B200 drains that in 4-14 us, so launch gaps, pipeline fill and the split-K tail
-// of every launch cost as much as the streaming itself.  Here the GEMVs between two token-mixer
-// kernels (out projection, gate/up projection with SwiGLU, down projection, next layer's input
-// projection) are one launch of one CTA per SM:
+// (src/launcher.s:1226-1535, one launch_gemv per projection; the mixer as ten more, :832-844); at batch 1
+// each projection moves 25-90 MB and a B200 drains that in 4-14 us, so launch gaps, pipeline fill and the
+// split-K tail of every launch cost as much as the streaming itself.  Here everything between two attention
+// kernels is one launch:
 //   * CTA c owns whole columns of every GEMV (a strip of octets, all of K), so its results are
 //     final: no partial sums, counters or atomics between CTAs, and the sum order is fixed.
 //   * The weights come from a strip-packed copy (gemv_pack_strips below; layout in params.h) in
 //     which a CTA's strip is one contiguous byte range, cut into stages of 4 K-groups x 16
-//     columns (4352 bytes).  Stage k of the CTA's list (all GEMVs of the chain, in order) belongs
+//     columns (4352 bytes).  Stage k of the CTA's list (all GEMVs of the launch, in order) belongs
 //     to warp k % 16: that warp requests it with a plain 1-D bulk copy into one of its own ring
 //     slots, waits for it on the slot's mbarrier, consumes it alone and refills the slot with its
 //     next stage.  No producer warp, no block-wide synchronisation inside a GEMV.  Weights are
 //     constants, so a warp's requests run on into the NEXT GEMV of the chain while the block
-//     finishes the current one: the rings of all SMs keep HBM busy across GEMV boundaries.
+//     finishes the current one: the rings of all SMs keep HBM busy across entry boundaries.
 //   * A stage item is (K-group, pair of octets): two 128-bit loads per lane give the packed words,
 //     four m16n8k32 u8 x s8 tensor-core steps give the exact integer dot products of 16 columns
 //     against the three activation digit planes (gemv_core.cuh); scale and zero-point are applied
 //     in fp32 per group.  Per-column sums are added in a fixed order (stage order inside a warp,
 //     then warp order).
-//   * Between GEMVs the block meets the other blocks at a grid barrier (an arrival counter in
-//     global memory, bounded spin).  All CTAs are resident: the grid is one CTA per SM and a CTA
-//     takes more than half of an SM's shared memory.
+//   * A DeltaNet entry runs the mixer of a layer ((value head, 32-column slab) units, four teams of 128
+//     threads per CTA; deltanet_core.cuh); an all-reduce entry adds every rank's partial vector into the
+//     residual stream over plain peer loads (comm_core.cuh).  The weight rings stay full meanwhile.
+//   * Between entries the block meets the other blocks at a grid barrier (an arrival counter in
+//     global memory: release-add, acquire poll, bounded spin).  All CTAs are resident: the grid is one
+//     CTA per SM and a CTA takes more than half of an SM's shared memory.
 // Activations written inside the launch are read through L2 only (ld.global.cg).
 #include "gemv_core.cuh"
 #include "deltanet_core.cuh"
