@@ -47,7 +47,7 @@ def test_single_gemv_vs_oracle(ctx, lb, oracle, K, N, zeros):
 @pytest.mark.parametrize("K,N,swiglu,zeros", [(640, 5120, False, True), (256, 4096, True, True), (384, 1184, False, False)])
 def test_pack_is_byte_exact(ctx, lb, oracle, K, N, swiglu, zeros):
     """lb_gemv_pack against the numpy restatement of the strip layout: strips of 4 and 5 octets with a trailing single
-    (5120 columns over the SMs), SwiGLU pairs, more SMs than octets, no zero-point tensor"""
+    (5120 columns over the SMs), SwiGLU pairs, one octet per SM without a zero-point tensor"""
     qw, sc, qz, _ = gptq_case(K, N, seed=31, zeros=zeros)
     d = _dev(ctx, qw, sc, qz, K, N, swiglu)
     got = d[3].download(np.uint32, N // 8 * (K // 128) * 136)
@@ -168,3 +168,29 @@ def test_chain_rejects_what_it_cannot_run(ctx, lb):
         ctx.gemv_chain([dict(packed=None, x=d, y=d, K=1024, N=1024, x_mode=lb.X_F16, y_mode=lb.Y_F32)])
     assert ctx.gemv_chain_supports(5120, 34816, swiglu=True) and not ctx.gemv_chain_supports(5120, 2 * 37888 + 128)
     d.free()
+
+
+def test_timeline_hook(ctx, lb):
+    """lb_set_chain_timeline: per SM and entry four device time stamps, in order, and nothing written once it is off"""
+    K, N = 1024, 8192
+    qw, sc, qz, x = gptq_case(K, N, seed=70)
+    d = _dev(ctx, qw, sc, qz, K, N)
+    d_x, d_y = ctx.to_device(x), ctx.alloc(N * 4)
+    n_sm = ctx.sm_count
+    tl = ctx.alloc(n_sm * 32 * 4 * 8).zero()
+    lb.lib().lb_set_chain_timeline(ctx.h, tl.ptr)
+    ctx.gemv_chain([_op(d, d_x, d_y, K, N, lb.X_F16, lb.Y_F32)] * 2)
+    ctx.sync()
+    lb.lib().lb_set_chain_timeline(ctx.h, 0)
+    t = tl.download(np.uint64, n_sm * 32 * 4).reshape(n_sm, 32, 4).astype(np.int64)
+    assert (t[:, :2, :] > 0).all() and (t[:, 2:, :] == 0).all()
+    assert (np.diff(t[:, 0, :], axis=1) >= 0).all() and (np.diff(t[:, 1, :], axis=1) >= 0).all()
+    assert (t[:, 1, 0] >= t[:, 0, 3]).all()                 # entry 1 starts after entry 0 ended on the same SM
+    assert t[:, 1, 1].min() >= t[:, 0, 3].max()             # nobody leaves the grid barrier before everybody finished entry 0
+    tl.zero()
+    ctx.gemv_chain([_op(d, d_x, d_y, K, N, lb.X_F16, lb.Y_F32)])
+    ctx.sync()
+    assert not tl.download(np.uint64, n_sm * 32 * 4).any()
+    for b in d + [d_x, d_y, tl]:
+        if b:
+            b.free()
