@@ -86,6 +86,7 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
     X(gptq_dequant_f32)               \
     X(gptq_unpack_u8)                 \
     X(dense_bf16_gemv)                \
+    X(dense_bf16_stream)              \
     X(decay_gate_beta)                \
     X(deltanet_step_bf16)             \
     X(deltanet_step_f32)              \

@@ -75,7 +75,7 @@ extern int lb_chain_launch(lb_ctx* c, const lb_chain_op* ops, int n_ops);
 extern int lb_chain_fill_gemv(lb_ctx* c, lb_chain_op* d, const lb_gemv_op* o, int i);
 extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps,
                            uint64_t part_val, uint64_t part_idx);
-extern int lb_dense_ctas(lb_ctx* c, int N);
+extern int lb_dense_ctas(lb_ctx* c, int N, int K);
 extern int lb_attn_mma_splits(lb_ctx* c, int pos, int HKV);
 extern unsigned lb_attn_mma_smem(int G);
 
@@ -132,8 +132,8 @@ LB_API int lb_model_create(lb_ctx* c, const lb_model_cfg* cfg, int tp_rank, int 
     LB_TRY(dalloc(m, &m->d_token, 16));
     LB_TRY(dalloc(m, &m->d_pos, 16));
     LB_TRY(dalloc(m, &m->d_next, 16));
-    LB_TRY(dalloc(m, &m->cand_val, (size_t)lb_dense_ctas(c, m->vocab_s) * 4));
-    LB_TRY(dalloc(m, &m->cand_idx, (size_t)lb_dense_ctas(c, m->vocab_s) * 4));
+    LB_TRY(dalloc(m, &m->cand_val, (size_t)lb_dense_ctas(c, m->vocab_s, H) * 4));
+    LB_TRY(dalloc(m, &m->cand_idx, (size_t)lb_dense_ctas(c, m->vocab_s, H) * 4));
     LB_CU(c, lb_drv.MemHostAlloc((void**)&m->h_next, 64, 0));
     for (int l = 0; l < cfg->n_layers; l++) {
         layer_t* L = &m->L[l];
@@ -636,7 +636,7 @@ static int issue_step(lb_model* m) {
     LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, m->vocab_s, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps,
                            m->cand_val, m->cand_idx));
     if (m->tp_size == 1) {
-        int n = lb_dense_ctas(c, m->vocab_s); /* one (value, row) candidate per LM-head CTA */
+        int n = lb_dense_ctas(c, m->vocab_s, H); /* one (value, row) candidate per LM-head CTA */
         void* params[] = {&m->cand_val, &n, &m->d_next, &m->d_token, &m->d_pos, &m->cand_idx};
         LB_TRY(lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1));
     } else {
@@ -644,7 +644,7 @@ static int issue_step(lb_model* m) {
         memset(&q, 0, sizeof q);
         LB_TRY(lb_comm_fill(m->comm, &q.tp, 2, 2));
         q.cand_val = (const float*)m->cand_val; q.cand_idx = (const int32_t*)m->cand_idx;
-        q.n_cand = lb_dense_ctas(c, m->vocab_s); q.vocab_offset = m->tp_rank * m->vocab_s;
+        q.n_cand = lb_dense_ctas(c, m->vocab_s, H); q.vocab_offset = m->tp_rank * m->vocab_s;
         q.out_idx = (int32_t*)m->d_next; q.next_token = (int32_t*)m->d_token; q.pos = (int32_t*)m->d_pos;
         void* params[] = {&q};
         LB_TRY(lb_launch(c, LBK_tp_argmax_exchange, 1, 1, 1, 1024, 0, params, 1));

@@ -207,8 +207,17 @@ LB_API int lb_gptq_unpack(lb_ctx* c, uint64_t qweight, uint64_t q_out, int K, in
     return lb_launch(c, LBK_gptq_unpack_u8, (unsigned)((N + 255) / 256), (unsigned)(K / 8), 1, 256, 0, params, 0);
 }
 
-int lb_dense_ctas(lb_ctx* c, int N) {
-    int ctas = (N + 7) / 8, cap = c->sm_count * 8; /* each CTA strides over rows, 8 warps = 8 rows at a time */
+/* shared memory of dense_bf16_stream: 8 warps x 2 ring slots of one row, the fp32 activations, reduction scratch, mbarriers */
+static size_t dense_stream_smem(int K) { return (size_t)8 * 2 * K * 2 + (size_t)K * 4 + 40 * 4 + 16 * 8; }
+static int dense_streams(const lb_ctx* c, int N, int K) {
+    return K % 8 == 0 && N >= 8 * c->sm_count &&
+           dense_stream_smem(K) <= (size_t)c->max_smem_optin - (size_t)((c->fn_static_smem[LBK_dense_bf16_stream] + 1023) & ~1023);
+}
+
+/* CTAs of the dense GEMV = arg-max candidates it leaves */
+int lb_dense_ctas(lb_ctx* c, int N, int K) {
+    if (dense_streams(c, N, K)) return c->sm_count; /* one CTA per SM, rows streamed through shared memory */
+    int ctas = (N + 7) / 8, cap = c->sm_count * 8;  /* each CTA strides over rows, 8 warps = 8 rows at a time */
     return ctas > cap ? cap : ctas;
 }
 
@@ -220,8 +229,10 @@ int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K,
     p.w = (const uint16_t*)w; p.x = (const void*)x; p.y = (float*)y; p.norm_w = (const void*)norm_w;
     p.N = N; p.K = K; p.x_mode = x_mode; p.eps = eps;
     p.part_val = (float*)part_val; p.part_idx = (int32_t*)part_idx;
-    int ctas = lb_dense_ctas(c, N);
+    int ctas = lb_dense_ctas(c, N, K);
     void* params[] = {&p};
+    if (dense_streams(c, N, K))
+        return lb_launch(c, LBK_dense_bf16_stream, (unsigned)ctas, 1, 1, 256, (unsigned)dense_stream_smem(K), params, 1);
     return lb_launch(c, LBK_dense_bf16_gemv, (unsigned)ctas, 1, 1, 256, (unsigned)(K * 4 + 256), params, 1);
 }
 

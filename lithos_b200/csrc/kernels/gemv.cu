@@ -453,3 +453,104 @@ extern "C" __global__ void __launch_bounds__(256) dense_bf16_gemv(const __grid_c
         }
     }
 }
+
+// ---------------------------------------------------------------------------
+// The same dense bf16 [N,K] x vector product, streamed: one CTA per SM, every warp requests whole
+// rows (K * 2 bytes, contiguous) with 1-D bulk copies into its own two ring slots and consumes
+// them from shared memory, so the HBM stream does not depend on per-thread loads in flight.
+// Row n goes to CTA n % gridDim.x, warp (n / gridDim.x) % 8.  Same prologues, results and arg-max
+// candidates as dense_bf16_gemv (one candidate per CTA).  Used for the LM head
+// (src/launcher.s:2903-2970) when a row fits a ring slot.
+// ---------------------------------------------------------------------------
+#define DS_WARPS 8
+#define DS_SLOTS 2
+extern "C" __global__ void __launch_bounds__(DS_WARPS * 32, 1) dense_bf16_stream(const __grid_constant__ lb_dense_params p) {
+    extern __shared__ __align__(16) unsigned char ds_sm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t row_bytes = (uint32_t)p.K * 2u;
+    unsigned char* ring = ds_sm;                                                          // [8 warps][2 slots][row]
+    float* xsm = reinterpret_cast<float*>(ds_sm + (size_t)DS_WARPS * DS_SLOTS * row_bytes); // [K] fp32
+    float* red = xsm + p.K;                                                               // [40]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + 40);                               // [8][2]
+    if (lane == 0)
+        for (int s = 0; s < DS_SLOTS; ++s) mbar_init(&bars[warp * DS_SLOTS + s], 1);
+    mbar_fence_init();
+    __syncwarp();
+    // rows of this warp: n = (warp + 8 m) * G + c; weights are constants: the first requests go out before griddepcontrol.wait
+    const int G = gridDim.x, c = blockIdx.x;
+    const int my_rows = p.N > c ? ((p.N - c + G - 1) / G - warp + DS_WARPS - 1) / DS_WARPS : 0; // rows (p.N - c)/G of the CTA, every 8th
+    const uint64_t pol = l2_policy_evict_first();
+    auto request = [&](int m) {
+        if (lane == 0) {
+            const size_t n = (size_t)(warp + DS_WARPS * m) * G + c;
+            uint64_t* bar = &bars[warp * DS_SLOTS + (m % DS_SLOTS)];
+            mbar_arrive_expect_tx(bar, row_bytes);
+            bulk_g2s(ring + ((size_t)warp * DS_SLOTS + (m % DS_SLOTS)) * row_bytes, p.w + n * p.K, row_bytes, bar, pol);
+        }
+    };
+    for (int m = 0; m < DS_SLOTS && m < my_rows; ++m) request(m);
+
+    pdl_wait();
+    if (p.x_mode == LB_X_F16) {
+        const __half* xh = reinterpret_cast<const __half*>(p.x);
+        for (int i = tid; i < p.K; i += blockDim.x) xsm[i] = __half2float(xh[i]);
+    } else {
+        const float* xf = reinterpret_cast<const float*>(p.x);
+        float rinv = 1.f;
+        if (p.x_mode == LB_X_F32_RMSNORM) {
+            float ss = 0.f;
+            for (int i = tid; i < p.K; i += blockDim.x) ss += xf[i] * xf[i];
+            ss = block_sum(ss, red);
+            rinv = rsqrtf(ss / (float)p.K + p.eps);
+        }
+        const uint16_t* nw = reinterpret_cast<const uint16_t*>(p.norm_w);
+        for (int i = tid; i < p.K; i += blockDim.x) {
+            float v = xf[i];
+            if (p.x_mode == LB_X_F32_RMSNORM) v = v * rinv * (1.0f + bf16_bits_to_f32(nw[i]));
+            xsm[i] = __half2float(__float2half_rn(v)); // activations are fp16 on this path
+        }
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    float best_v = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int m = 0; m < my_rows; ++m) {
+        const int slot = m % DS_SLOTS;
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars[warp * DS_SLOTS + slot], (m / DS_SLOTS) & 1))) break; // bounded: the rows left keep y unset
+        const uint4* wr = reinterpret_cast<const uint4*>(ring + ((size_t)warp * DS_SLOTS + slot) * row_bytes);
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll 4
+        for (int i = lane; i < p.K / 8; i += 32) { // same order of additions as dense_bf16_gemv
+            const uint4 w = wr[i];
+            const float4 xa = *reinterpret_cast<const float4*>(xsm + i * 8);
+            const float4 xb = *reinterpret_cast<const float4*>(xsm + i * 8 + 4);
+            a0 = fmaf(__uint_as_float(w.x << 16), xa.x, a0);
+            a1 = fmaf(__uint_as_float(w.x & 0xffff0000u), xa.y, a1);
+            a0 = fmaf(__uint_as_float(w.y << 16), xa.z, a0);
+            a1 = fmaf(__uint_as_float(w.y & 0xffff0000u), xa.w, a1);
+            a0 = fmaf(__uint_as_float(w.z << 16), xb.x, a0);
+            a1 = fmaf(__uint_as_float(w.z & 0xffff0000u), xb.y, a1);
+            a0 = fmaf(__uint_as_float(w.w << 16), xb.z, a0);
+            a1 = fmaf(__uint_as_float(w.w & 0xffff0000u), xb.w, a1);
+        }
+        __syncwarp(); // every lane has its words in registers (the sums depend on them): the slot can be refilled
+        if (m + DS_SLOTS < my_rows) request(m + DS_SLOTS);
+        const float t = warp_sum(a0 + a1);
+        const int n = (warp + DS_WARPS * m) * G + c;
+        if (lane == 0) p.y[n] = t;
+        if (t > best_v || (t == best_v && n < best_i)) { best_v = t; best_i = n; }
+    }
+    if (p.part_val) { // this CTA's candidate for the arg-max: greater value, smaller row on ties
+        __syncthreads();
+        int* ri = reinterpret_cast<int*>(red + 16);
+        if (lane == 0) { red[warp] = best_v; ri[warp] = best_i; }
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < DS_WARPS; ++w)
+                if (red[w] > best_v || (red[w] == best_v && ri[w] < best_i)) { best_v = red[w]; best_i = ri[w]; }
+            p.part_val[blockIdx.x] = best_v;
+            p.part_idx[blockIdx.x] = best_i;
+        }
+    }
+}
