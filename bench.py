@@ -451,8 +451,8 @@ def bench_decode(args, rank, local, world, dist):
         "roofline": {"bound": "hbm", "achieved": gemv_algo / gemv_s / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": gemv_algo / gemv_s / 1e9 / peak,
                      # dram__bytes_read.sum + dram__bytes_write.sum of one such launch in the ncu capture summarised in
-                     # profiles/gemv_chain_layer_ncu.md (203 494 656 + 5 823 488); not re-measured by this run
-                     "traffic": 209318144 if chained and world == 1 else None, "peak_source": which,
+                     # profiles/gemv_chain_layer_ncu.md (203 520 768 + 3 367 168); not re-measured by this run
+                     "traffic": 206887936 if chained and world == 1 else None, "peak_source": which,
                      "kernel": "gemv_chain" if chained else "gemv_int4_w256",
                      "us_per_launch": gemv_s * 1e6, "algorithmic_bytes": gemv_algo,
                      "how": ("the step's four int4 GEMVs between two token mixers (out, gate/up + SwiGLU, down, next input projection; fused norm "
