@@ -618,6 +618,7 @@ static int issue_step(lb_model* m) {
             p.HQ = m->HQ; p.HKV = m->HKV;
             p.splits = lb_attn_mma_splits(c, cfg->max_ctx, m->HKV);
             p.status = (uint32_t*)c->dev_status;
+            p.coop = m->HKV * p.splits <= c->sm_count;
             p.in_dtype = 1; p.gate_stride = 512; p.q_stride = 512;
             p.rot_dims = cfg->rot_dims; p.rope_theta = cfg->rope_theta; p.eps = cfg->eps;
             for (int i = 0; i < cfg->rot_dims / 2; i++)

@@ -295,6 +295,7 @@ LB_API int lb_attention_decode(lb_ctx* c, uint64_t q, uint64_t k_new, uint64_t v
     p.pos = pos; p.HQ = HQ; p.HKV = HKV;
     p.splits = lb_attn_mma_splits(c, pos, HKV);
     p.status = (uint32_t*)c->dev_status;
+    p.coop = HKV * p.splits <= c->sm_count;
     p.in_dtype = in_is_f32 ? 1 : 0;
     p.gate_stride = 256; p.q_stride = 256;
     p.rot_dims = rot_dims; p.rope_theta = rope_theta; p.eps = eps;

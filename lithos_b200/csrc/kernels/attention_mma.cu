@@ -269,6 +269,82 @@ __device__ __forceinline__ void attn_mma_body(const lb_attn_params& p0, unsigned
                 __stcg(rec + g * AT_REC + 257, Lg[g]);
             }
         }
+        if (p.coop) {
+            // Every CTA of the launch is resident (the host sets coop only when the grid fits the SMs, one CTA each):
+            // all CTAs of this KV head wait for each other and each finishes its own share of the (head, dim)
+            // outputs, instead of one CTA doing all of them.
+            __syncthreads(); // the whole record is written
+            if (t == 0) {
+                asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.counters + kv) : "memory");
+                const uint64_t w0 = globaltimer_ns();
+                bool ok = false;
+                for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
+                    unsigned v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.counters + kv) : "memory");
+                    if (v >= (unsigned)p.splits) { ok = true; break; }
+                    if ((it & 255u) == 255u && globaltimer_ns() - w0 > LB_WAIT_NS) break;
+                }
+                if (!ok && p.status) atomicExch(p.status, LB_DEV_TIMEOUT_COUNTER);
+            }
+            __syncthreads();
+            const float* kvrec = p.scratch + (size_t)kv * p.splits * G * AT_REC;
+            const int per = (G * AT_D + p.splits - 1) / p.splits; // outputs of this CTA: [split * per, (split + 1) * per)
+            float* pm = reinterpret_cast<float*>(tiles);         // [4][64] partial maxima, sums, accumulators of the four slice groups
+            float* pl = pm + 4 * 64;
+            float* pa = pl + 4 * 64;
+            const int sub = t >> 6, ol = t & 63; // slice group (slices sub, sub + 4, ...), output inside a block of 64
+            for (int ob = 0; ob < per; ob += 64) {
+                const int o = split * per + ob + ol;
+                const bool live = ob + ol < per && o < G * AT_D;
+                const int g = live ? o / AT_D : 0, dim = live ? o % AT_D : 0;
+                float mv[16], lv[16], av[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) { // up to 64 slices: 16 per group, all loads in flight at once
+                    const int s2 = sub + 4 * j;
+                    const bool on = live && s2 < p.splits;
+                    const float* r = kvrec + ((size_t)(on ? s2 : 0) * G + g) * AT_REC;
+                    mv[j] = on ? __ldcg(r + 256) : -INFINITY;
+                    lv[j] = on ? __ldcg(r + 257) : 0.f;
+                    av[j] = on ? __ldcg(r + dim) : 0.f;
+                }
+                float M = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) M = fmaxf(M, mv[j]);
+                float L = 0.f, A = 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) { // slice order inside the group
+                    const float w = mv[j] == -INFINITY ? 0.f : exp2f(mv[j] - M);
+                    L = fmaf(lv[j], w, L);
+                    A = fmaf(av[j], w, A);
+                }
+                __syncthreads(); // the previous block of outputs has been combined
+                pm[sub * 64 + ol] = M; pl[sub * 64 + ol] = L; pa[sub * 64 + ol] = A;
+                __syncthreads();
+                if (sub == 0 && live) { // the four groups, in group order
+                    float Mx = fmaxf(fmaxf(pm[ol], pm[64 + ol]), fmaxf(pm[128 + ol], pm[192 + ol]));
+                    float Lx = 0.f, Ax = 0.f;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float w = pm[q * 64 + ol] == -INFINITY ? 0.f : exp2f(pm[q * 64 + ol] - Mx);
+                        Lx = fmaf(pl[q * 64 + ol], w, Lx);
+                        Ax = fmaf(pa[q * 64 + ol], w, Ax);
+                    }
+                    const int hq = kv * G + g;
+                    float out = Ax / Lx;
+                    if (p.gate) out *= sigmoidf_dev(ld_in(p.gate, (size_t)hq * p.gate_stride + dim, p.in_dtype));
+                    p.out[(size_t)hq * AT_D + dim] = out;
+                }
+            }
+            __syncthreads();
+            if (t == 0) { // the last CTA to finish reading puts both counters back to zero
+                const unsigned old = atomicAdd(p.counters + 8 + kv, 1u);
+                if (old == (unsigned)p.splits - 1u) {
+                    p.counters[kv] = 0u;
+                    p.counters[8 + kv] = 0u;
+                }
+            }
+            return;
+        }
         __threadfence();
         __syncthreads();
         if (t == 0) s_ticket = atomicAdd(p.counters + kv, 1u);

@@ -199,6 +199,9 @@ typedef struct {
     float eps;
     double rope_freq[64]; /* theta^(-i/(rot_dims/2)), i < rot_dims/2 <= 64, computed on the host in double */
     uint32_t* status;     /* device status word for bounded waits (attn_decode_mma); may be NULL */
+    int32_t coop;         /* attn_decode_mma: the grid fits the SMs one CTA each, so the CTAs of a KV head may wait for each
+                             other and share the slice merge (counters[kv] arrivals, counters[8 + kv] finished) */
+    int32_t pad_;
 } lb_attn_params;
 
 /* ---- tensor-parallel exchange (comm.cu) ----------------------------------------------- */
