@@ -488,6 +488,56 @@ def bench_chain(args, local):
     return out
 
 
+def bench_batched(args, local):
+    """--workload batched: the batched int4 projection sweep (BASELINE config 4): the four projection shapes of the
+    model at batch 1 / 4 / 16 / 64, fp16 N(0,1) activations, each launch reading a weight set that is not in L2
+    (the sets of a shape rotate and together exceed the 126 MB L2).  One JSON line with one record per
+    (shape, batch): microseconds per launch and algorithmic GB/s (weights + scales + zero-points + X + Y)."""
+    import lithos_b200 as lb
+    ctx = lb.Context(local)
+    peak, which = measured_hbm_peak()
+    shapes = [("gate_up 5120->17408", 5120, 17408, 8), ("down 17408->5120", 17408, 5120, 8),
+              ("qkv 5120->22528", 5120, 22528, 6), ("lm_head 5120->248320", 5120, 248320, 1)]
+    reps = 24
+    sweep = []
+    for name, K, N, sets in shapes:
+        dev = []
+        for s_ in range(sets):
+            dev.append([ctx.to_device(lb.fill_u32(K // 8 * N, 300 + s_, 1)), ctx.to_device(lb.fill_scales_f16(K // 128 * N, 300 + s_, 2)),
+                        ctx.to_device(lb.fill_u32(K // 128 * (N // 8), 300 + s_, 3))])
+        wbytes = K // 8 * N * 4 + K // 128 * N * 2 + K // 128 * (N // 8) * 4
+        d_x = ctx.to_device(lb.fill_normal(64 * K, 300, 4, dtype="f16"))
+        d_y = ctx.alloc(64 * N * 4)
+        for B in (1, 4, 16, 64):
+            ctx.begin_capture()
+            for j in range(reps):
+                w = dev[j % sets]
+                ctx.gemm_int4(w[0], w[1], w[2], d_x, d_y, K, N, B, lb.GEMV_Y_F32)
+            graph = ctx.end_capture()
+            for _ in range(max(args.warmup, 3)):
+                graph.launch()
+            ctx.sync()
+            n = max(2, min(args.steps, 2000) // 50)
+            ctx.timer_start()
+            for _ in range(n):
+                graph.launch()
+            us = ctx.timer_stop() * 1e3 / (n * reps)
+            algo = wbytes + B * K * 2 + B * N * 4
+            sweep.append({"shape": name, "K": K, "N": N, "batch": B, "us": round(us, 2), "GBps": round(algo / us / 1e3, 1),
+                          "frac_of_hbm_peak": round(algo / us / 1e3 / peak, 3), "TFLOPs": round(2.0 * B * K * N / us / 1e6, 1)})
+            graph.destroy()
+            assert ctx.device_status() == 0
+        for w in dev:
+            for b in w:
+                b.free()
+        d_x.free()
+        d_y.free()
+    ctx.close()
+    return {"metric": "batched int4 projection sweep (config 4)", "unit": "us per launch", "n_gpus": 1, "data": "synthetic",
+            "higher_is_better": False, "dtype": "int4 weights, fp16 activations, fp32 accumulation", "peak": peak, "peak_source": which,
+            "kernel": "gemm_int4_mma (mma.sync m16n8k16)", "l2": "weight sets of a shape rotate, together > L2", "sweep": sweep}
+
+
 def reference_decode(args, rank):
     """--impl reference: the reference's kernels have no CPU implementation that can run (its interpreters
     evaluate the integer host dialect only), so this arm times the plain-C restatement on the host cores."""
@@ -509,7 +559,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "chain"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "chain", "batched"],
                     help="decode: the benchmark; gemv: config 0 alone; chain: the decode step's four GEMVs between two token "
                          "mixers as persistent gemv_chain launches alone (the small case used for ncu captures)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: number of layers (64 = the benchmark definition)")
@@ -528,8 +578,8 @@ def main():
             print(json.dumps(ref), flush=True)
         return
     dist = init_dist(world)
-    if args.workload == "chain":
-        out = bench_chain(args, local)
+    if args.workload in ("chain", "batched"):
+        out = (bench_chain if args.workload == "chain" else bench_batched)(args, local)
         if rank == 0:
             print(json.dumps(out), flush=True)
         return

@@ -166,6 +166,17 @@ int lb_gemv_pack(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros
 int lb_gemv_chain(lb_ctx* ctx, const lb_gemv_op* ops, int n_ops);
 /* LB_OK when lb_gemv_pack / lb_gemv_chain accept this shape on this GPU (no launch) */
 int lb_gemv_chain_supports(lb_ctx* ctx, int K, int N, int swiglu);
+/* Batched projection: Y[B,N] = X[B,K] W for B = 1..LB_GEMM_MAX_BATCH tokens, W in the same three GPTQ
+ * buffers as lb_gemv_int4 (read once for the whole batch), x fp16 [B,K] row-major, y fp32 [B,N]
+ * (flags = LB_GEMV_Y_F32) or fp16 [B,N] (flags = 0).  K % 128 == 0, N % 16 == 0.
+ * The reference's batched path is its prefill projection (kernels/projection_gemm.sass:390-631:
+ * int4 -> fp16 dequantisation into shared memory, eight 16x8x16 tensor-core products per k-step);
+ * this entry keeps the integers q - z exact in fp16 and applies the group scale to the group's
+ * fp32 sum, so row b of Y equals lb_gemv_int4 on row b of X to fp32 rounding.
+ * Overwrites y.  x and y must not overlap. */
+#define LB_GEMM_MAX_BATCH 64
+int lb_gemm_int4(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x_f16, uint64_t y, int K,
+                 int N, int B, int flags);
 /* bit-exact targets: W(k,n) = fma(float(q), s, -z*s) as fp32 [K,N]; q as u8 [K,N] */
 int lb_gptq_dequant(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t w_out_f32, int K, int N);
 int lb_gptq_unpack(lb_ctx* ctx, uint64_t qweight, uint64_t q_out_u8, int K, int N);

@@ -106,6 +106,7 @@ def lib() -> C.CDLL:
     sig("lb_set_chain_reserve", None, vp, i32)
     sig("lb_set_chain_timeline", None, vp, u64)
     sig("lb_gptq_dequant", i32, vp, u64, u64, u64, u64, i32, i32)
+    sig("lb_gemm_int4", i32, vp, u64, u64, u64, u64, u64, i32, i32, i32, i32)
     sig("lb_gptq_unpack", i32, vp, u64, u64, i32, i32)
     sig("lb_dense_bf16_gemv", i32, vp, u64, u64, u64, i32, i32, i32)
     sig("lb_deltanet_step", i32, vp, u64, u64, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32)
@@ -340,6 +341,10 @@ class Context:
     def gemv_int4_host(self, qweight, scales, qzeros, x, y, K, N, flags=0, weights_resident=False):
         self._check(lib().lb_gemv_int4_host(self.h, _ptr(qweight), _ptr(scales), _ptr(qzeros) if qzeros is not None else None,
                                             _ptr(x), _ptr(y), K, N, flags, 1 if weights_resident else 0))
+
+    def gemm_int4(self, qweight, scales, qzeros, x, y, K, N, B, flags=0):
+        """Y[B,N] = X[B,K] W for up to 64 tokens; the weights are read once for the whole batch."""
+        self._check(lib().lb_gemm_int4(self.h, qweight.ptr, scales.ptr, qzeros.ptr if qzeros else 0, x.ptr, y.ptr, K, N, B, flags))
 
     def gptq_dequant(self, qweight, scales, qzeros, w_out, K, N):
         self._check(lib().lb_gptq_dequant(self.h, qweight.ptr, scales.ptr, qzeros.ptr if qzeros else 0, w_out.ptr, K, N))

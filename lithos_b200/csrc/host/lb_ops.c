@@ -195,6 +195,32 @@ LB_API int lb_gemv_int4_host(lb_ctx* c, const uint32_t* qweight, const uint16_t*
     return LB_OK;
 }
 
+/* ---- batched int4 projection (gemm_int4_mma) ----------------------------------------
+ * Grid: one CTA per 128 columns x ksplit K-slices, the slices of a column block one cluster.
+ * ksplit grows (powers of two up to the portable cluster size) while the grid would leave SMs
+ * idle and every slice keeps at least four K-groups. */
+LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y, int K, int N,
+                        int B, int flags) {
+    if (!c || !qweight || !scales || !x || !y || K <= 0 || N <= 0 || K % 128 || N % 16 || B < 1 || B > LB_GEMM_MAX_BATCH ||
+        (flags & ~LB_GEMV_Y_F32))
+        return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: bad argument (K %% 128, N %% 16, 1 <= B <= %d, flags 0 or LB_GEMV_Y_F32)",
+                       LB_GEMM_MAX_BATCH);
+    lb_bgemm_params p;
+    memset(&p, 0, sizeof p);
+    p.qweight = (const uint32_t*)qweight; p.scales = (const uint16_t*)scales; p.qzeros = (const uint32_t*)qzeros;
+    p.x = (const uint16_t*)x; p.y = (void*)y;
+    p.K = K; p.N = N; p.B = B; p.y_f32 = (flags & LB_GEMV_Y_F32) != 0;
+    const int wide = B > 32;
+    const int rows = wide ? 64 : B > 16 ? 32 : B > 8 ? 16 : 8; /* token rows the CTA stages */
+    const unsigned smem = (unsigned)(2 * rows * 136 * 2 + rows * 132 * 4);
+    const int blocks = (N + 127) / 128, groups = K / 128;
+    int ksplit = 1;
+    while (ksplit < 8 && blocks * ksplit < c->sm_count * 3 / 2 && groups / (ksplit * 2) >= 4) ksplit *= 2;
+    void* params[] = {&p};
+    return lb_launch_cluster(c, wide ? LBK_gemm_int4_mma_wide : LBK_gemm_int4_mma, (unsigned)blocks, (unsigned)ksplit, 1,
+                             wide ? 512 : 256, smem, params, 1, (unsigned)ksplit);
+}
+
 LB_API int lb_gptq_dequant(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t w_out, int K, int N) {
     if (!c || !qweight || !scales || !w_out || K % 128 || N % 8) return lb_fail(c, LB_ERR_INVALID, "lb_gptq_dequant: bad argument");
     void* params[] = {&qweight, &scales, &qzeros, &w_out, &K, &N};

@@ -121,6 +121,17 @@ typedef struct {
     int32_t G;               /* CTAs the strips are cut for */
 } lb_pack_params;
 
+/* ---- batched int4 projection: Y[B,N] = X[B,K] W ------------------------- */
+typedef struct {
+    const uint32_t* qweight; /* [K/8, N] */
+    const uint16_t* scales;  /* fp16 [K/128, N] */
+    const uint32_t* qzeros;  /* [K/128, N/8] or NULL: zero-point 8 */
+    const uint16_t* x;       /* fp16 [B, K] */
+    void* y;                 /* fp32 or fp16 [B, N] */
+    int32_t K, N, B;
+    int32_t y_f32;
+} lb_bgemm_params;
+
 /* ---- dense bf16 [N,K] x vector ------------------------------------------ */
 typedef struct {
     const uint16_t* w; /* bf16 [N,K] row-major */
