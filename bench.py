@@ -500,7 +500,11 @@ def bench_batched(args, local):
               ("qkv 5120->22528", 5120, 22528, 6), ("lm_head 5120->248320", 5120, 248320, 1)]
     reps = 24
     sweep = []
+    only = [w for w in args.batched_shapes.split(",") if w]
+    batches = [int(b) for b in args.batched_batches.split(",")]
     for name, K, N, sets in shapes:
+        if only and not any(w in name for w in only):
+            continue
         dev = []
         for s_ in range(sets):
             dev.append([ctx.to_device(lb.fill_u32(K // 8 * N, 300 + s_, 1)), ctx.to_device(lb.fill_scales_f16(K // 128 * N, 300 + s_, 2)),
@@ -508,7 +512,7 @@ def bench_batched(args, local):
         wbytes = K // 8 * N * 4 + K // 128 * N * 2 + K // 128 * (N // 8) * 4
         d_x = ctx.to_device(lb.fill_normal(64 * K, 300, 4, dtype="f16"))
         d_y = ctx.alloc(64 * N * 4)
-        for B in (1, 4, 16, 64):
+        for B in batches:
             ctx.begin_capture()
             for j in range(reps):
                 w = dev[j % sets]
@@ -535,7 +539,7 @@ def bench_batched(args, local):
     ctx.close()
     return {"metric": "batched int4 projection sweep (config 4)", "unit": "us per launch", "n_gpus": 1, "data": "synthetic",
             "higher_is_better": False, "dtype": "int4 weights, fp16 activations, fp32 accumulation", "peak": peak, "peak_source": which,
-            "kernel": "gemm_int4_mma (mma.sync m16n8k16)", "l2": "weight sets of a shape rotate, together > L2", "sweep": sweep}
+            "kernel": "gemm_int4_mma_b8/b16/b32/b64 (mma.sync m16n8k16)", "l2": "weight sets of a shape rotate, together > L2", "sweep": sweep}
 
 
 def reference_decode(args, rank):
@@ -563,6 +567,8 @@ def main():
                     help="decode: the benchmark; gemv: config 0 alone; chain: the decode step's four GEMVs between two token "
                          "mixers as persistent gemv_chain launches alone (the small case used for ncu captures)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: number of layers (64 = the benchmark definition)")
+    ap.add_argument("--batched-shapes", default="", help="batched workload: comma-separated substrings of the shape names to run (default all)")
+    ap.add_argument("--batched-batches", default="1,4,16,64", help="batched workload: batch sizes")
     ap.add_argument("--seed", type=int, default=20260413)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-chain", action="store_true", help="decode workload: one launch per projection instead of persistent chains")

@@ -83,8 +83,10 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
     X(gemv_int4_w256)                 \
     X(gemv_chain)                     \
     X(gemv_pack_strips)               \
-    X(gemm_int4_mma)                  \
-    X(gemm_int4_mma_wide)             \
+    X(gemm_int4_mma_b8)               \
+    X(gemm_int4_mma_b16)              \
+    X(gemm_int4_mma_b32)              \
+    X(gemm_int4_mma_b64)              \
     X(gptq_dequant_f32)               \
     X(gptq_unpack_u8)                 \
     X(dense_bf16_gemv)                \

@@ -210,15 +210,14 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
     p.qweight = (const uint32_t*)qweight; p.scales = (const uint16_t*)scales; p.qzeros = (const uint32_t*)qzeros;
     p.x = (const uint16_t*)x; p.y = (void*)y;
     p.K = K; p.N = N; p.B = B; p.y_f32 = (flags & LB_GEMV_Y_F32) != 0;
-    const int wide = B > 32;
-    const int rows = wide ? 64 : B > 16 ? 32 : B > 8 ? 16 : 8; /* token rows the CTA stages */
-    const unsigned smem = (unsigned)(2 * rows * 136 * 2 + rows * 132 * 4);
+    const int rows = B > 32 ? 64 : B > 16 ? 32 : B > 8 ? 16 : 8; /* token rows the CTA stages */
+    const int kernel = B > 32 ? LBK_gemm_int4_mma_b64 : B > 16 ? LBK_gemm_int4_mma_b32 : B > 8 ? LBK_gemm_int4_mma_b16 : LBK_gemm_int4_mma_b8;
+    const unsigned smem = (unsigned)(4 * rows * 256 + rows * 132 * 4); /* four activation stages + the partial tile */
     const int blocks = (N + 127) / 128, groups = K / 128;
     int ksplit = 1;
     while (ksplit < 8 && blocks * ksplit < c->sm_count * 3 / 2 && groups / (ksplit * 2) >= 4) ksplit *= 2;
     void* params[] = {&p};
-    return lb_launch_cluster(c, wide ? LBK_gemm_int4_mma_wide : LBK_gemm_int4_mma, (unsigned)blocks, (unsigned)ksplit, 1,
-                             wide ? 512 : 256, smem, params, 1, (unsigned)ksplit);
+    return lb_launch_cluster(c, kernel, (unsigned)blocks, (unsigned)ksplit, 1, B > 32 ? 512 : 256, smem, params, 1, (unsigned)ksplit);
 }
 
 LB_API int lb_gptq_dequant(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t w_out, int K, int N) {
