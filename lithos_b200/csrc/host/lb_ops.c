@@ -212,12 +212,12 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
     p.K = K; p.N = N; p.B = B; p.y_f32 = (flags & LB_GEMV_Y_F32) != 0;
     const int rows = B > 32 ? 64 : B > 16 ? 32 : B > 8 ? 16 : 8; /* token rows the CTA stages */
     const int kernel = B > 32 ? LBK_gemm_int4_mma_b64 : B > 16 ? LBK_gemm_int4_mma_b32 : B > 8 ? LBK_gemm_int4_mma_b16 : LBK_gemm_int4_mma_b8;
-    const unsigned smem = (unsigned)(4 * rows * 256 + rows * 132 * 4); /* four activation stages + the partial tile */
+    const unsigned smem = (unsigned)((B > 16 ? 3 : 4) * rows * 320); /* activation ring (the partial tile reuses it) */
     const int blocks = (N + 127) / 128, groups = K / 128;
     int ksplit = 1;
     while (ksplit < 8 && blocks * ksplit < c->sm_count * 3 / 2 && groups / (ksplit * 2) >= 4) ksplit *= 2;
     void* params[] = {&p};
-    return lb_launch_cluster(c, kernel, (unsigned)blocks, (unsigned)ksplit, 1, B > 32 ? 512 : 256, smem, params, 1, (unsigned)ksplit);
+    return lb_launch_cluster(c, kernel, (unsigned)blocks, (unsigned)ksplit, 1, 256, smem, params, 1, (unsigned)ksplit);
 }
 
 LB_API int lb_gptq_dequant(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t w_out, int K, int N) {

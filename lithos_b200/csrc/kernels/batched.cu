@@ -12,12 +12,15 @@
 //     0x64006400, is the fp16 pair (1024 + q0, 1024 + 16 q1); one fma with (1, 1/16) and
 //     (-(1024 + z), -(64 + z)) turns it into the exact integers (q0 - z, q1 - z).  The lane's B registers
 //     of two k-steps are one 128-bit read of the 8 activations that packed word multiplies.
-//   * Products of a 5-bit integer and an fp16 value are exact in the fp32 accumulator; the fp16 group scale
-//     multiplies the group's fp32 sum, so no weight is ever rounded.
-//   * The CTA is 8 column sets (128 columns) x 1 or 2 token halves (256 or 512 threads).  Packed words
-//     are prefetched four K-groups ahead in registers; the activations travel K-group by K-group through a
-//     four-stage cp.async ring in shared memory (16-byte chunks, chunk index xor-ed with 4 (row & 1) so
-//     that the 128-bit reads of a quarter-warp cover all banks).
+//   * Up to 32 tokens: products of a 5-bit integer and an fp16 value are exact in the fp32 accumulator; the
+//     fp16 group scale multiplies the group's fp32 sum, so no weight is ever rounded.  33..64 tokens (one
+//     warp keeps all 64 tokens' accumulators, so there is no room for per-group sums): the A registers are
+//     (q - z) * s rounded to fp16, the dequantised weight the reference's own batched kernel multiplies
+//     (kernels/projection_gemm.sass:477-631).
+//   * The CTA is 8 warps = 8 column sets (128 columns).  Packed words
+//     are prefetched three or four K-groups ahead in registers; the activations travel K-group by K-group through a
+//     cp.async ring of as many stages in shared memory (16-byte chunks; rows of 320 bytes, so that the 128-bit
+//     reads of a quarter-warp - two token rows x four chunks - cover all banks).
 //   * Narrow matrices are split along K over the CTAs of a thread-block cluster (grid.y = cluster.y <= 8):
 //     every CTA leaves its partial tile in shared memory and the ranks add them in rank order through
 //     distributed shared memory, each rank the token rows b = rank (mod cluster size): a fixed order, so
@@ -29,9 +32,8 @@
 
 #define BG_CSETS 8      // column sets of 16 columns per CTA
 #define BG_COLS 128     // columns per CTA
-#define BG_STAGES 4     // K-groups of activations in the shared-memory ring
+#define BG_XROW 320     // bytes per staged activation row: 256 + 64, so that odd rows start 16 banks further on
 #define BG_PSTRIDE 132  // floats per row of the partial tile
-#define BG_DEPTH 4      // K-groups of packed words in registers ahead of the products
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -71,30 +73,41 @@ struct bg_group { // lane (g, t): packed rows t, t+4, t+8, t+12 of columns n0 + 
     uint32_t zw; // the zero-point word of the lane's octet (0x88888888 without qzeros)
 };
 
-__device__ __forceinline__ void bg_load_group(bg_group& w, const lb_bgemm_params& p, int grp, int n0, int g, int t) {
-    const uint32_t* q = p.qweight + ((size_t)grp * 16 + t) * p.N + n0 + 2 * g;
+struct bg_cursor { // where the lane's next K-group starts in the three weight buffers
+    const uint32_t* q;
+    const uint16_t* s;
+    const uint32_t* z; // NULL: zero-point 8
+    size_t N;
+};
+
+__device__ __forceinline__ void bg_load_group(bg_group& w, bg_cursor& c) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) w.w[j] = __ldg(reinterpret_cast<const uint2*>(q + (size_t)(4 * j) * p.N));
-    w.s2 = __ldg(reinterpret_cast<const uint32_t*>(p.scales + (size_t)grp * p.N + n0 + 2 * g));
-    w.zw = p.qzeros ? __ldg(p.qzeros + (size_t)grp * (p.N / 8) + (n0 >> 3) + (g >> 2)) : 0x88888888u;
+    for (int j = 0; j < 4; ++j) w.w[j] = __ldg(reinterpret_cast<const uint2*>(c.q + (size_t)(4 * j) * c.N));
+    w.s2 = __ldg(reinterpret_cast<const uint32_t*>(c.s));
+    w.zw = c.z ? __ldg(c.z) : 0x88888888u;
+    c.q += 16 * c.N;
+    c.s += c.N;
+    if (c.z) c.z += c.N / 8;
 }
 
 // byte I of a packed word (q0 | q1 << 4) as the fp16 pair (q0 - z, q1 - z)
 template <int I>
-__device__ __forceinline__ uint32_t bg_pair(uint32_t w, __half2 mul, __half2 add) {
+__device__ __forceinline__ __half2 bg_pair(uint32_t w, __half2 mul, __half2 add) {
     const uint32_t v = __byte_perm(w, 0u, 0x4040u | I | (I << 8));
-    return h2_as_u32(__hfma2(u32_as_h2(lop3_and_or(v, 0x00f0000fu, 0x64006400u)), mul, add));
+    return __hfma2(u32_as_h2(lop3_and_or(v, 0x00f0000fu, 0x64006400u)), mul, add);
 }
+// (-(1024 + z), -(64 + z)) as fp16 bits: 1024 + z = 0x6400 + z, 64 + z = 0x5400 + 16 z
+__device__ __forceinline__ __half2 bg_bias(uint32_t z) { return u32_as_h2((0xE400u + z) | ((0xD400u + (z << 4)) << 16)); }
 
-template <int NB, int TH> // a warp's NB blocks of 8 tokens; TH token halves per CTA
+template <int NB, bool SCALED, int D> // a warp's NB blocks of 8 tokens; SCALED: A = (q - z) * s in fp16, no per-group sums;
+                                      // D K-groups ahead: packed words in registers, activations in shared memory
 __device__ __forceinline__ void gemm_int4_body(const lb_bgemm_params& p, unsigned char* smem) {
-    constexpr int R = NB * 8 * TH, THREADS = BG_CSETS * 32 * TH;
+    constexpr int R = NB * 8, THREADS = BG_CSETS * 32;
     constexpr int CH = (R * 16 + THREADS - 1) / THREADS; // 16-byte activation chunks a thread copies per K-group
-    unsigned char* xs = smem;                                                        // [BG_STAGES][R][256 B]
-    float* pt = reinterpret_cast<float*>(smem + (size_t)BG_STAGES * R * 256);        // [R][BG_PSTRIDE]
+    unsigned char* xs = smem;                 // [D][R][BG_XROW]
+    float* pt = reinterpret_cast<float*>(smem); // [R][BG_PSTRIDE], over the activation ring once the products are done
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int cs = warp % BG_CSETS, tb = (warp / BG_CSETS) * NB * 8; // column set, first token
-    const int n0 = blockIdx.x * BG_COLS + cs * 16;
+    const int n0 = blockIdx.x * BG_COLS + warp * 16;
     const bool live = n0 < p.N; // N % 16 == 0
     const int groups = p.K / 128, KS = (int)gridDim.y;
     const int g_begin = (int)(((long long)blockIdx.y * groups) / KS), g_end = (int)(((long long)(blockIdx.y + 1) * groups) / KS);
@@ -103,68 +116,83 @@ __device__ __forceinline__ void gemm_int4_body(const lb_bgemm_params& p, unsigne
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f;
 
-    // chunk m (k = 8m..8m+7) of token row b of a K-group sits at chunk position m ^ 4 (b & 1) of the row
+    // activations: thread copies chunk m (k = 8m..8m+7) of token rows b0, b0 + 16, ...
+    const int b0 = tid >> 4, m = tid & 15;
+    const uint16_t* xsrc = p.x + (size_t)g_begin * 128 + m * 8; // + b * K per row
+    const uint32_t xdst = (uint32_t)(b0 * BG_XROW + m * 16);
     auto copy_x = [&](int grp, int stage) {
         if (grp < g_end) {
 #pragma unroll
             for (int c = 0; c < CH; ++c) {
-                const int i = tid + c * THREADS, b = i >> 4, m = i & 15;
-                if (i < R * 16) {
+                const int b = b0 + c * 16;
+                if (b < R) {
                     const bool valid = b < p.B;
-                    cp_async16(xs + ((size_t)stage * R + b) * 256 + ((m ^ ((b & 1) << 2)) << 4),
-                               p.x + (size_t)(valid ? b : 0) * p.K + (size_t)grp * 128 + m * 8, valid);
+                    cp_async16(xs + (size_t)stage * R * BG_XROW + xdst + c * 16 * BG_XROW, xsrc + (size_t)(valid ? b : 0) * p.K, valid);
                 }
             }
+            xsrc += 128;
         }
         cp_async_commit(); // one commit per K-group, empty or not: the wait below counts groups
     };
 
-    bg_group ring[BG_DEPTH];
+    bg_cursor cur_ptr;
+    cur_ptr.N = (size_t)p.N;
+    cur_ptr.q = p.qweight + ((size_t)g_begin * 16 + t) * p.N + n0 + 2 * g;
+    cur_ptr.s = p.scales + (size_t)g_begin * p.N + n0 + 2 * g;
+    cur_ptr.z = p.qzeros ? p.qzeros + (size_t)g_begin * (p.N / 8) + (n0 >> 3) + (g >> 2) : nullptr;
+    bg_group ring[D];
 #pragma unroll
-    for (int u = 0; u < BG_DEPTH; ++u)
-        if (live && g_begin + u < g_end) bg_load_group(ring[u], p, g_begin + u, n0, g, t);
+    for (int u = 0; u < D; ++u)
+        if (live && g_begin + u < g_end) bg_load_group(ring[u], cur_ptr);
 #pragma unroll
-    for (int s = 0; s < BG_STAGES - 1; ++s) copy_x(g_begin + s, s);
+    for (int s = 0; s < D - 1; ++s) copy_x(g_begin + s, s);
 
     const __half2 mul = u32_as_h2(0x2C003C00u); // (1, 1/16)
-    for (int base = g_begin; base < g_end; base += BG_DEPTH) {
+    const uint32_t xoff = (uint32_t)(g * BG_XROW + t * 16); // chunk 4j + t of row g: + 64 j
+    for (int base = g_begin; base < g_end; base += D) {
 #pragma unroll
-        for (int u = 0; u < BG_DEPTH; ++u) { // BG_DEPTH == BG_STAGES: stage of K-group base + u is u
+        for (int u = 0; u < D; ++u) { // both rings have D entries: K-group base + u uses entry u of each
             const int grp = base + u;
             if (grp < g_end) { // uniform over the CTA
-                cp_async_wait<BG_STAGES - 2>(); // this thread's chunks of K-group grp have landed
+                cp_async_wait<D - 2>(); // this thread's chunks of K-group grp have landed
                 __syncthreads();                // everybody's have, and everybody is done with K-group grp - 1
-                copy_x(grp + BG_STAGES - 1, (u + BG_STAGES - 1) % BG_STAGES);
+                copy_x(grp + D - 1, (u + D - 1) % D);
                 const bg_group cur = ring[u];
-                if (live && grp + BG_DEPTH < g_end) bg_load_group(ring[u], p, grp + BG_DEPTH, n0, g, t);
+                if (live && grp + D < g_end) bg_load_group(ring[u], cur_ptr);
                 if (live) {
                     const uint32_t za = (cur.zw >> (8 * (g & 3))) & 0xFu, zb = (cur.zw >> (8 * (g & 3) + 4)) & 0xFu;
-                    // q0 - z = (1024 + q0) - (1024 + z),  q1 - z = (1024 + 16 q1) / 16 - (64 + z): exact in fp16
-                    const __half2 addA = __halves2half2(__ushort_as_half((unsigned short)(0xE400u + za)), __int2half_rn(-64 - (int)za));
-                    const __half2 addB = __halves2half2(__ushort_as_half((unsigned short)(0xE400u + zb)), __int2half_rn(-64 - (int)zb));
-                    float ga[NB][4];
+                    const __half2 addA = bg_bias(za), addB = bg_bias(zb);
+                    const __half2 sA = __half2half2(__low2half(u32_as_h2(cur.s2))), sB = __half2half2(__high2half(u32_as_h2(cur.s2)));
+                    float ga[SCALED ? 1 : NB][4];
+                    if (!SCALED) {
 #pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) ga[nb][0] = ga[nb][1] = ga[nb][2] = ga[nb][3] = 0.f;
-                    const unsigned char* xrow = xs + ((size_t)u * R + tb + g) * 256;
+                        for (int nb = 0; nb < NB; ++nb) ga[nb][0] = ga[nb][1] = ga[nb][2] = ga[nb][3] = 0.f;
+                    }
+                    const unsigned char* xrow = xs + (size_t)u * R * BG_XROW + xoff;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) { // packed row 4j + t: k = 8 (4j + t) .. + 7
                         const uint32_t wa = cur.w[j].x, wb = cur.w[j].y;
-                        const uint32_t a0 = bg_pair<0>(wa, mul, addA), a1 = bg_pair<0>(wb, mul, addB);
-                        const uint32_t a2 = bg_pair<1>(wa, mul, addA), a3 = bg_pair<1>(wb, mul, addB);
-                        const uint32_t c0 = bg_pair<2>(wa, mul, addA), c1 = bg_pair<2>(wb, mul, addB);
-                        const uint32_t c2 = bg_pair<3>(wa, mul, addA), c3 = bg_pair<3>(wb, mul, addB);
+                        __half2 h[8] = {bg_pair<0>(wa, mul, addA), bg_pair<0>(wb, mul, addB), bg_pair<1>(wa, mul, addA), bg_pair<1>(wb, mul, addB),
+                                        bg_pair<2>(wa, mul, addA), bg_pair<2>(wb, mul, addB), bg_pair<3>(wa, mul, addA), bg_pair<3>(wb, mul, addB)};
+                        if (SCALED) {
 #pragma unroll
-                        for (int nb = 0; nb < NB; ++nb) { // the 8 activations of token tb + 8 nb + g this packed row multiplies
-                            const uint4 xq = *reinterpret_cast<const uint4*>(xrow + (size_t)nb * 8 * 256 + (((4 * j + t) ^ ((g & 1) << 2)) << 4));
-                            mma_f16(ga[nb], a0, a1, a2, a3, xq.x, xq.y);
-                            mma_f16(ga[nb], c0, c1, c2, c3, xq.z, xq.w);
+                            for (int i = 0; i < 8; ++i) h[i] = __hmul2(h[i], (i & 1) ? sB : sA);
+                        }
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) { // the 8 activations of token 8 nb + g this packed row multiplies
+                            const uint4 xq = *reinterpret_cast<const uint4*>(xrow + nb * 8 * BG_XROW + 64 * j);
+                            float(&d)[4] = SCALED ? acc[nb] : ga[SCALED ? 0 : nb];
+                            mma_f16(d, h2_as_u32(h[0]), h2_as_u32(h[1]), h2_as_u32(h[2]), h2_as_u32(h[3]), xq.x, xq.y);
+                            mma_f16(d, h2_as_u32(h[4]), h2_as_u32(h[5]), h2_as_u32(h[6]), h2_as_u32(h[7]), xq.z, xq.w);
                         }
                     }
-                    const float2 sc = __half22float2(u32_as_h2(cur.s2));
+                    if (!SCALED) {
+                        const float2 sc = __half22float2(u32_as_h2(cur.s2));
 #pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) {
-                        acc[nb][0] = fmaf(sc.x, ga[nb][0], acc[nb][0]); acc[nb][1] = fmaf(sc.x, ga[nb][1], acc[nb][1]);
-                        acc[nb][2] = fmaf(sc.y, ga[nb][2], acc[nb][2]); acc[nb][3] = fmaf(sc.y, ga[nb][3], acc[nb][3]);
+                        for (int nb = 0; nb < NB; ++nb) {
+                            acc[nb][0] = fmaf(sc.x, ga[nb][0], acc[nb][0]); acc[nb][1] = fmaf(sc.x, ga[nb][1], acc[nb][1]);
+                            acc[nb][2] = fmaf(sc.y, ga[nb][2], acc[nb][2]); acc[nb][3] = fmaf(sc.y, ga[nb][3], acc[nb][3]);
+                        }
                     }
                 }
             }
@@ -172,11 +200,12 @@ __device__ __forceinline__ void gemm_int4_body(const lb_bgemm_params& p, unsigne
     }
     cp_async_wait<0>();
     pdl_launch_dependents();
+    __syncthreads(); // the partial tile goes where the activations were
     // partial tile: d0, d1 = column 2g, tokens 2t and 2t + 1; d2, d3 = column 2g + 1
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) pt[(tb + nb * 8 + 2 * t + (i & 1)) * BG_PSTRIDE + cs * 16 + 2 * g + (i >> 1)] = acc[nb][i];
+        for (int i = 0; i < 4; ++i) pt[(nb * 8 + 2 * t + (i & 1)) * BG_PSTRIDE + warp * 16 + 2 * g + (i >> 1)] = acc[nb][i];
     bg_cluster_sync(); // every CTA of the cluster has its tile in place (a plain CTA barrier when there is no cluster)
     const uint32_t rank = KS > 1 ? bg_cluster_rank() : 0u;
     const int cols = min(BG_COLS, p.N - (int)blockIdx.x * BG_COLS);
@@ -194,15 +223,13 @@ __device__ __forceinline__ void gemm_int4_body(const lb_bgemm_params& p, unsigne
     if (KS > 1) bg_cluster_sync(); // nobody leaves while a neighbour still reads its tile
 }
 
-static_assert(BG_DEPTH == BG_STAGES, "the K-group loop indexes both rings with the same unrolled counter");
-
-#define BG_KERNEL(name, NB, TH)                                                                                        \
-    extern "C" __global__ void __launch_bounds__(256 * TH, 2 / TH) name(const __grid_constant__ lb_bgemm_params p) {           \
+#define BG_KERNEL(name, NB, SCALED, D)                                                                                   \
+    extern "C" __global__ void __launch_bounds__(256, 2) name(const __grid_constant__ lb_bgemm_params p) {             \
         extern __shared__ __align__(16) unsigned char bg_smem[];                                                       \
         pdl_wait();                                                                                                    \
-        gemm_int4_body<NB, TH>(p, bg_smem);                                                                            \
+        gemm_int4_body<NB, SCALED, D>(p, bg_smem);                                                                     \
     }
-BG_KERNEL(gemm_int4_mma_b8, 1, 1)  // up to 8 tokens
-BG_KERNEL(gemm_int4_mma_b16, 2, 1) // up to 16
-BG_KERNEL(gemm_int4_mma_b32, 4, 1) // up to 32
-BG_KERNEL(gemm_int4_mma_b64, 4, 2) // up to 64: two warps per column set with 32 tokens each
+BG_KERNEL(gemm_int4_mma_b8, 1, false, 4)  // up to 8 tokens
+BG_KERNEL(gemm_int4_mma_b16, 2, false, 4) // up to 16
+BG_KERNEL(gemm_int4_mma_b32, 4, false, 3) // up to 32
+BG_KERNEL(gemm_int4_mma_b64, 8, true, 3)  // up to 64

@@ -1,10 +1,11 @@
 """GPU: the batched int4 projection (lb_gemm_int4) through the C ABI against the CPU oracle.
 
 Row b of Y must equal the oracle's batch-1 GEMV of row b of X:
-  max|y - y_ref| / max|y_ref| <= 1e-3 per row (the GEMV tolerance; the kernel keeps q - z exact and
-  accumulates in fp32, so the observed error is near 1e-6), and must equal lb_gemv_int4 on the same row
-  to the same tolerance.  Results may not depend on the batch a row travels in (checked bit-exactly between
-  batch sizes that use the same K split).
+  max|y - y_ref| / max|y_ref| <= 1e-3 per row (the GEMV tolerance; up to 32 tokens the kernel keeps q - z
+  exact and accumulates in fp32, so the observed error is near 1e-6; from 33 tokens on it multiplies
+  fp16-rounded weights, error near 2e-4), and must equal lb_gemv_int4 on the same row to the same tolerance.
+  Results may not depend on the batch a row travels in (checked bit-exactly between batch sizes that use
+  the same arithmetic).
 """
 import numpy as np
 import pytest
@@ -65,10 +66,17 @@ def test_rows_do_not_depend_on_the_batch(ctx, lb):
     qw, sc, qz, _ = gptq_case(K, N, seed=77)
     d_qw, d_sc, d_qz = ctx.to_device(qw), ctx.to_device(sc), ctx.to_device(qz)
     X = batch_x(K, 64, seed=5)
-    y64 = run_gemm(ctx, lb, d_qw, d_sc, d_qz, X, K, N)
-    for B in (1, 4, 16, 32):
+    # up to 32 tokens the arithmetic is the same in every kernel variant: bit-exact rows
+    y32 = run_gemm(ctx, lb, d_qw, d_sc, d_qz, X[:32], K, N)
+    for B in (1, 4, 9, 16, 31):
         y = run_gemm(ctx, lb, d_qw, d_sc, d_qz, X[:B], K, N)
-        assert np.array_equal(y, y64[:B]), B
+        assert np.array_equal(y, y32[:B]), B
+    # 33..64 tokens multiply fp16-rounded weights: same rows within the GEMV tolerance, and bit-exact among themselves
+    y64 = run_gemm(ctx, lb, d_qw, d_sc, d_qz, X, K, N)
+    for b in range(32):
+        assert rel_err_max(y64[b], y32[b]) <= TOL
+    y40 = run_gemm(ctx, lb, d_qw, d_sc, d_qz, X[:40], K, N)
+    assert np.array_equal(y40, y64[:40])
     # a permutation of the tokens permutes the rows
     perm = np.random.default_rng(3).permutation(64)
     yp = run_gemm(ctx, lb, d_qw, d_sc, d_qz, X[perm], K, N)

@@ -89,3 +89,25 @@ def test_lm_head(ctx, lb):
     got = d_y.download(np.float32, rows)
     assert np.max(np.abs(got - want)) <= 1e-5 * np.max(np.abs(want)) + 1e-5
     assert int(np.argmax(got)) == int(np.argmax(want))
+
+
+def test_sample(ctx, lb):
+    """entry sample: arg-max of logits / temperature, the first maximum wins; top_k is read and ignored"""
+    rng = np.random.default_rng(8)
+    V = 248320
+    logits = rng.standard_normal(V).astype(np.float32) * 4
+    d_l, d_t = ctx.to_device(logits), ctx.alloc(16)
+    for temp, top_k in ((1.0, 1), (0.7, 40), (2.5, 0)):
+        launch(ctx, lb, "sample.cubin", "sample", [u64(d_l), u64(d_t), C.c_uint32(V), C.c_float(temp), C.c_uint32(top_k)], 1, 256)
+        assert int(d_t.download(np.uint32, 1)[0]) == int(np.argmax(logits))
+    # ties: the smallest index among the maxima, wherever they sit
+    logits[:] = -1.0
+    logits[[200001, 777, 131072, 248319]] = 5.0
+    d_l.upload(logits)
+    for block in (256, 1024, 96):
+        launch(ctx, lb, "sample.cubin", "sample", [u64(d_l), u64(d_t), C.c_uint32(V), C.c_float(1.0), C.c_uint32(1)], 1, block)
+        assert int(d_t.download(np.uint32, 1)[0]) == 777
+    launch(ctx, lb, "sample.cubin", "sample", [u64(d_l), u64(d_t), C.c_uint32(5), C.c_float(1.0), C.c_uint32(1)], 1, 256)
+    assert int(d_t.download(np.uint32, 1)[0]) == 0
+    d_l.free()
+    d_t.free()
