@@ -512,11 +512,11 @@ def bench_batched(args, local):
         wbytes = K // 8 * N * 4 + K // 128 * N * 2 + K // 128 * (N // 8) * 4
         d_x = ctx.to_device(lb.fill_normal(64 * K, 300, 4, dtype="f16"))
         d_y = ctx.alloc(64 * N * 4)
-        for B in batches:
+        for B, flag in [(B, f) for B in batches for f in ((lb.GEMM_TCGEN05, lb.GEMM_MMA_SYNC) if B > 8 else (0,))]:
             ctx.begin_capture()
             for j in range(reps):
                 w = dev[j % sets]
-                ctx.gemm_int4(w[0], w[1], w[2], d_x, d_y, K, N, B, lb.GEMV_Y_F32)
+                ctx.gemm_int4(w[0], w[1], w[2], d_x, d_y, K, N, B, lb.GEMV_Y_F32 | flag)
             graph = ctx.end_capture()
             for _ in range(max(args.warmup, 3)):
                 graph.launch()
@@ -527,7 +527,8 @@ def bench_batched(args, local):
                 graph.launch()
             us = ctx.timer_stop() * 1e3 / (n * reps)
             algo = wbytes + B * K * 2 + B * N * 4
-            sweep.append({"shape": name, "K": K, "N": N, "batch": B, "us": round(us, 2), "GBps": round(algo / us / 1e3, 1),
+            sweep.append({"shape": name, "K": K, "N": N, "batch": B, "path": "tcgen05" if flag == lb.GEMM_TCGEN05 else "mma.sync", "default": (flag == lb.GEMM_TCGEN05) == (B > 32),
+                          "us": round(us, 2), "GBps": round(algo / us / 1e3, 1),
                           "frac_of_hbm_peak": round(algo / us / 1e3 / peak, 3), "TFLOPs": round(2.0 * B * K * N / us / 1e6, 1)})
             graph.destroy()
             assert ctx.device_status() == 0
@@ -539,7 +540,7 @@ def bench_batched(args, local):
     ctx.close()
     return {"metric": "batched int4 projection sweep (config 4)", "unit": "us per launch", "n_gpus": 1, "data": "synthetic",
             "higher_is_better": False, "dtype": "int4 weights, fp16 activations, fp32 accumulation", "peak": peak, "peak_source": which,
-            "kernel": "gemm_int4_mma_b8/b16/b32/b64 (mma.sync m16n8k16)", "l2": "weight sets of a shape rotate, together > L2", "sweep": sweep}
+            "kernels": "gemm_int4_tc (tcgen05.mma 128 x NT x 16, TMEM accumulator), gemm_int4_mma_b8/b16/b32/b64 (mma.sync m16n8k16)", "l2": "weight sets of a shape rotate, together > L2", "sweep": sweep}
 
 
 def reference_decode(args, rank):
@@ -568,7 +569,7 @@ def main():
                          "mixers as persistent gemv_chain launches alone (the small case used for ncu captures)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: number of layers (64 = the benchmark definition)")
     ap.add_argument("--batched-shapes", default="", help="batched workload: comma-separated substrings of the shape names to run (default all)")
-    ap.add_argument("--batched-batches", default="1,4,16,64", help="batched workload: batch sizes")
+    ap.add_argument("--batched-batches", default="1,4,16,32,64", help="batched workload: batch sizes")
     ap.add_argument("--seed", type=int, default=20260413)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-chain", action="store_true", help="decode workload: one launch per projection instead of persistent chains")

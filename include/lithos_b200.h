@@ -171,10 +171,15 @@ int lb_gemv_chain_supports(lb_ctx* ctx, int K, int N, int swiglu);
  * (flags = LB_GEMV_Y_F32) or fp16 [B,N] (flags = 0).  K % 128 == 0, N % 16 == 0.
  * The reference's batched path is its prefill projection (kernels/projection_gemm.sass:390-631:
  * int4 -> fp16 dequantisation into shared memory, eight 16x8x16 tensor-core products per k-step);
- * up to 32 tokens this entry keeps the integers q - z exact in fp16 and applies the group scale to
- * the group's fp32 sum, so row b of Y equals lb_gemv_int4 on row b of X to fp32 rounding; from 33
- * tokens on it multiplies (q - z) * s rounded to fp16, as the reference kernel does.
+ * 33..64 tokens run on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory):
+ * the weights are dequantised to fp16 - (q - z) * s, q - z exact, one fp16 rounding for the scale - into
+ * shared memory, as the reference kernel does.  Up to 32 tokens use mma.sync (faster there, measured):
+ * q - z stays exact and the group scale multiplies the group's fp32 sum, so row b of Y equals
+ * lb_gemv_int4 on row b of X to fp32 rounding.  LB_GEMM_TCGEN05 forces the tensor-memory kernel for
+ * 9 tokens or more, LB_GEMM_MMA_SYNC the mma.sync kernels for every size (cross-checks).
  * Overwrites y.  x and y must not overlap. */
+#define LB_GEMM_MMA_SYNC (1 << 4) /* flags: use the mma.sync kernels for every batch size */
+#define LB_GEMM_TCGEN05 (1 << 5)  /* flags: use the tcgen05 kernel (B >= 9) */
 #define LB_GEMM_MAX_BATCH 64
 int lb_gemm_int4(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x_f16, uint64_t y, int K,
                  int N, int B, int flags);

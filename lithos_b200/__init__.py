@@ -24,6 +24,7 @@ LB_OK, LB_ERR_INVALID, LB_ERR_NO_DRIVER, LB_ERR_CUDA, LB_ERR_NO_KERNEL = 0, 1, 2
 LB_ERR_DEVICE_WAIT, LB_ERR_IO, LB_ERR_NOMEM, LB_ERR_STATE = 5, 6, 7, 8
 
 GEMV_X_F32, GEMV_Y_F32, GEMV_Y_ACCUM, GEMV_Y_SWIGLU = 1, 2, 4, 8
+GEMM_MMA_SYNC, GEMM_TCGEN05 = 16, 32
 X_F16, X_F32, X_F32_RMSNORM, X_F32_HEADNORM_SILU = 0, 1, 2, 3
 Y_F16, Y_F32, Y_F32_ACCUM, Y_SWIGLU_F16 = 0, 1, 2, 3
 

@@ -195,28 +195,41 @@ LB_API int lb_gemv_int4_host(lb_ctx* c, const uint32_t* qweight, const uint16_t*
     return LB_OK;
 }
 
-/* ---- batched int4 projection (gemm_int4_mma) ----------------------------------------
- * Grid: one CTA per 128 columns x ksplit K-slices, the slices of a column block one cluster.
- * ksplit grows (powers of two up to the portable cluster size) while the grid would leave SMs
- * idle and every slice keeps at least four K-groups. */
+/* ---- batched int4 projection ---------------------------------------------------------
+ * 33..64 tokens (9..64 with LB_GEMM_TCGEN05): gemm_int4_tc (tcgen05, one CTA per SM: 128 columns x a K slice);
+ * otherwise, or with LB_GEMM_MMA_SYNC, the mma.sync kernels (two CTAs per SM): the faster one at each size
+ * as measured (bench.py --workload batched).  The K slices of a column block are the CTAs
+ * of one cluster (<= 8); the slice count fills the SMs without starting a second wave and leaves
+ * every slice at least four K-groups. */
 LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x, uint64_t y, int K, int N,
                         int B, int flags) {
     if (!c || !qweight || !scales || !x || !y || K <= 0 || N <= 0 || K % 128 || N % 16 || B < 1 || B > LB_GEMM_MAX_BATCH ||
-        (flags & ~LB_GEMV_Y_F32))
-        return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: bad argument (K %% 128, N %% 16, 1 <= B <= %d, flags 0 or LB_GEMV_Y_F32)",
+        (flags & ~(LB_GEMV_Y_F32 | LB_GEMM_MMA_SYNC | LB_GEMM_TCGEN05)) ||
+        ((flags & LB_GEMM_MMA_SYNC) && (flags & LB_GEMM_TCGEN05)) || ((flags & LB_GEMM_TCGEN05) && B <= 8))
+        return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: bad argument (K %% 128, N %% 16, 1 <= B <= %d, flags LB_GEMV_Y_F32, LB_GEMM_MMA_SYNC or LB_GEMM_TCGEN05 (9 tokens or more))",
                        LB_GEMM_MAX_BATCH);
     lb_bgemm_params p;
     memset(&p, 0, sizeof p);
     p.qweight = (const uint32_t*)qweight; p.scales = (const uint16_t*)scales; p.qzeros = (const uint32_t*)qzeros;
     p.x = (const uint16_t*)x; p.y = (void*)y;
     p.K = K; p.N = N; p.B = B; p.y_f32 = (flags & LB_GEMV_Y_F32) != 0;
+    p.status = (uint32_t*)c->dev_status;
+    const int blocks = (N + 127) / 128, groups = K / 128;
+    void* params[] = {&p};
+    if ((B > 32 && !(flags & LB_GEMM_MMA_SYNC)) || (flags & LB_GEMM_TCGEN05)) {
+        const int nt = B > 32 ? 64 : B > 16 ? 32 : 16;
+        const unsigned smem = (unsigned)(3 * 32768 + 5 * nt * 256); /* three weight stages + five activation stages */
+        int ksplit = c->sm_count / blocks;
+        if (ksplit > 8) ksplit = 8;
+        while (ksplit > 1 && groups / ksplit < 4) ksplit--;
+        if (ksplit < 1) ksplit = 1;
+        return lb_launch_cluster(c, LBK_gemm_int4_tc, (unsigned)blocks, (unsigned)ksplit, 1, 512, smem, params, 1, (unsigned)ksplit);
+    }
     const int rows = B > 32 ? 64 : B > 16 ? 32 : B > 8 ? 16 : 8; /* token rows the CTA stages */
     const int kernel = B > 32 ? LBK_gemm_int4_mma_b64 : B > 16 ? LBK_gemm_int4_mma_b32 : B > 8 ? LBK_gemm_int4_mma_b16 : LBK_gemm_int4_mma_b8;
     const unsigned smem = (unsigned)((B > 16 ? 3 : 4) * rows * 320); /* activation ring (the partial tile reuses it) */
-    const int blocks = (N + 127) / 128, groups = K / 128;
     int ksplit = 1;
     while (ksplit < 8 && blocks * ksplit < c->sm_count * 3 / 2 && groups / (ksplit * 2) >= 4) ksplit *= 2;
-    void* params[] = {&p};
     return lb_launch_cluster(c, kernel, (unsigned)blocks, (unsigned)ksplit, 1, 256, smem, params, 1, (unsigned)ksplit);
 }
 

@@ -1,0 +1,278 @@
+// Batched int4 projection on the 5th-generation tensor cores (tcgen05 + TMEM) for 9..64 tokens on sm_100a:
+// Y[b][n] = sum_k W(k,n) X[b][k], W in the GPTQ buffers of the batch-1 GEMV (qweight [K/8,N], scales fp16
+// [K/128,N], qzeros [K/128,N/8] or NULL = zero-point 8; inference/gemv.ls:44-130), X fp16 [B,K],
+// Y fp32 or fp16 [B,N].  The reference's batched kernel is kernels/projection_gemm.sass:390-631
+// (int4 -> fp16 into shared memory, then 16x8x16 tensor-core products); the product here is one
+// tcgen05.mma of 128 weight columns x NT tokens x 16 k per instruction, accumulated in tensor memory.
+//
+// One CTA = 128 output columns x one K slice, 512 threads.  Per K-group (128 k):
+//   * every thread dequantises 4 packed words of one column (prefetched three groups earlier): a packed
+//     word is the 8 k of one row of a core matrix, so its eight fp16 values (q - z) * s - q - z exact
+//     through the 0x6400 exponent trick, then one fp16 multiply: the weight the reference kernel
+//     multiplies - are one 16-byte shared-memory store into the canonical K-major, unswizzled operand
+//     layout (core matrix = 8 columns x 8 k, 128 contiguous bytes);
+//   * the activations of the group arrive by cp.async (16-byte chunks, three groups ahead) in the same
+//     layout with tokens as rows;
+//   * after a proxy fence and a CTA barrier one thread issues the eight tcgen05.mma (k = 16 each) of the
+//     group and commits them to the stage's mbarrier; the same thread waits for the barrier of the group
+//     two back before it joins the next CTA barrier, after which that group's stages are refilled.
+// Epilogue: warps 0-3 read the accumulator (lane = column, TMEM column = token) with tcgen05.ld into the
+// partial tile in shared memory; K slices (the CTAs of a cluster) are added in rank order through
+// distributed shared memory exactly as in the mma.sync kernel of batched.cu.
+// Every wait is bounded and reports through the status word; TMEM is freed on every path.
+#include "common.cuh"
+#include "params.h"
+
+#define TC_COLS 128    // weight columns per CTA = M of the product
+#define TC_THREADS 512
+#define TC_STAGES 3
+#define TC_PSTRIDE 132                 // floats per row of the partial tile
+#define TC_TMEM_COLS 64
+
+__device__ __forceinline__ uint32_t tc_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void tc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float tc_ld_cluster(const float* local_ptr, uint32_t rank) {
+    uint32_t remote; float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_ptr)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ void tc_cp_async16(void* dst_smem, const void* src, bool valid) { // zero fill when !valid
+    const uint32_t n = valid ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void tc_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tc_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// ---- tcgen05 ---------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) { // one full warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) { // the same warp
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// shared-memory operand descriptor, K-major, no swizzle: start address, leading (k direction) and stride
+// (row-group direction) byte offsets in 16-byte units, descriptor version 1 in bits 46-48
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46);
+}
+// instruction descriptor of kind::f16: fp32 accumulator, fp16 A and B, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+__device__ __forceinline__ uint32_t tc_idesc(uint32_t M, uint32_t N) { return (1u << 4) | ((N >> 3) << 17) | ((M >> 4) << 24); }
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) { // the barrier fires when every tcgen05.mma issued so far by this thread is done
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) { // 32 lanes x 16 consecutive columns
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t tc_lop3_and_or(uint32_t a, uint32_t mask, uint32_t bits) { // (a & mask) | bits
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(bits));
+    return r;
+}
+__device__ __forceinline__ uint32_t tc_h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 tc_bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+// byte I of a packed word (q0 | q1 << 4) as the fp16 pair ((q0 - z) s, (q1 - z) s): (1024 + q0, 1024 + 16 q1) by
+// mask-and-or, (q0 - z, q1 - z) by one fma with (1, 1/16) and (-(1024 + z), -(64 + z)), both exact, then the scale
+template <int I>
+__device__ __forceinline__ uint32_t tc_pair(uint32_t w, __half2 mul, __half2 add, __half2 s) {
+    const uint32_t v = __byte_perm(w, 0u, 0x4040u | I | (I << 8));
+    return tc_h2_bits(__hmul2(__hfma2(tc_bits_h2(tc_lop3_and_or(v, 0x00f0000fu, 0x64006400u)), mul, add), s));
+}
+
+struct tc_group { // a thread's share of one K-group: packed rows 4 rq .. 4 rq + 3 (k = 32 rq .. + 31) of one column
+    uint32_t w[4];
+    uint32_t s;  // its fp16 scale (u16 load)
+    uint32_t zw; // the zero-point word of its octet, as loaded (the nibble is taken out when the group is used)
+};
+
+#define TC_A_SBO 128                   // bytes between column groups (8 columns) of the weight tile: core matrices back to back
+#define TC_A_KSTRIDE (16 * TC_A_SBO)   // bytes between k chunks (8 k)
+#define TC_A_STAGE (16 * TC_A_KSTRIDE) // one K-group of dequantised weights: 32 KB
+#define TC_X_STAGES 5                  // activation ring: a stage is refilled three groups after its products were issued
+#define TC_FAIL_FREE 0x1101u           // status: a stage's products never completed
+#define TC_FAIL_DONE 0x1102u           // status: the last products never completed
+
+extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const __grid_constant__ lb_bgemm_params p) {
+    extern __shared__ __align__(1024) unsigned char tc_smem[];
+    __shared__ __align__(8) uint64_t bar_free[TC_STAGES];
+    __shared__ __align__(8) uint64_t bar_done;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ uint32_t fail_flag;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int NT = p.B > 32 ? 64 : p.B > 16 ? 32 : 16; // tokens the product carries (rows past B are zero)
+    const uint32_t x_stage_bytes = (uint32_t)NT * 256u, x_kstride = (uint32_t)NT * 16u;
+    unsigned char* a_smem = tc_smem;                          // [TC_STAGES][TC_A_STAGE]
+    unsigned char* x_smem = tc_smem + TC_STAGES * TC_A_STAGE; // [TC_X_STAGES][NT * 256]
+    float* pt = reinterpret_cast<float*>(tc_smem);            // [NT][TC_PSTRIDE], over the weight stages once the products are done
+    const int groups = p.K / 128, KS = (int)gridDim.y;
+    const int g_begin = (int)(((long long)blockIdx.y * groups) / KS), g_end = (int)(((long long)(blockIdx.y + 1) * groups) / KS);
+
+    if (tid == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) mbar_init(&bar_free[s], 1);
+        mbar_init(&bar_done, 1);
+        mbar_fence_init();
+        fail_flag = 0u;
+    }
+    if (warp == 0) tmem_alloc(&tmem_base_slot, TC_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = tmem_base_slot;
+    pdl_wait();
+
+    // weights: this thread's column and its four packed rows of every K-group
+    const int nl = tid & (TC_COLS - 1), rq = tid >> 7; // column of the tile, row quad
+    const int n = blockIdx.x * TC_COLS + nl;
+    const bool live = n < p.N;
+    const uint32_t* qptr = p.qweight + ((size_t)g_begin * 16 + 4 * rq) * p.N + n;
+    const uint16_t* sptr = p.scales + (size_t)g_begin * p.N + n;
+    const uint32_t* zptr = p.qzeros ? p.qzeros + (size_t)g_begin * (p.N / 8) + (n >> 3) : nullptr;
+    const size_t row_stride = (size_t)p.N;
+    auto load_group = [&](tc_group& w) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w.w[j] = __ldg(qptr + j * row_stride);
+        w.s = __ldg(sptr);
+        w.zw = zptr ? __ldg(zptr) : 0x88888888u;
+        qptr += 16 * row_stride;
+        sptr += row_stride;
+        if (zptr) zptr += row_stride / 8;
+    };
+    // activations: chunk c (k = 8c..8c+7) of token b goes to (b / 8) * 128 + c * x_kstride + (b % 8) * 16 of its stage;
+    // thread tid < 16 NT copies chunk tid % 16 of token tid / 16, and with 64 tokens also that of token tid / 16 + 32
+    const int xb = tid >> 4;
+    const bool x_copy = xb < NT, x_two = NT > 32;
+    const uint16_t* xsrc0 = p.x + (size_t)g_begin * 128 + (tid & 15) * 8 + (size_t)(xb < p.B ? xb : 0) * p.K;
+    const uint16_t* xsrc1 = p.x + (size_t)g_begin * 128 + (tid & 15) * 8 + (size_t)(xb + 32 < p.B ? xb + 32 : 0) * p.K;
+    const uint32_t xdst = (uint32_t)((xb >> 3) * 128 + (tid & 15) * x_kstride + (xb & 7) * 16);
+    const bool x_valid0 = xb < p.B, x_valid1 = xb + 32 < p.B;
+    auto copy_x = [&](int grp, int stage) {
+        if (grp < g_end && x_copy) {
+            unsigned char* dst = x_smem + (size_t)stage * x_stage_bytes + xdst;
+            tc_cp_async16(dst, xsrc0, x_valid0);
+            if (x_two) tc_cp_async16(dst + 4 * 128, xsrc1, x_valid1);
+            xsrc0 += 128;
+            xsrc1 += 128;
+        }
+        tc_cp_async_commit(); // one commit per K-group, empty or not: the waits count groups
+    };
+
+    tc_group ring[TC_STAGES];
+#pragma unroll
+    for (int u = 0; u < TC_STAGES; ++u) {
+        ring[u].w[0] = ring[u].w[1] = ring[u].w[2] = ring[u].w[3] = 0u;
+        ring[u].s = 0u;
+        ring[u].zw = 0x88888888u;
+        if (live && g_begin + u < g_end) load_group(ring[u]);
+    }
+    copy_x(g_begin, 0);
+    copy_x(g_begin + 1, 1);
+
+    const __half2 mul = tc_bits_h2(0x2C003C00u); // (1, 1/16)
+    const uint32_t idesc = tc_idesc(TC_COLS, (uint32_t)NT);
+    const uint32_t a_dst = (uint32_t)(4 * rq * TC_A_KSTRIDE + (nl >> 3) * TC_A_SBO + (nl & 7) * 16); // + j * TC_A_KSTRIDE
+    const int zshift = 4 * (n & 7);
+    bool failed = false;
+    int it = 0, xstage = 0;
+    for (int base = g_begin; base < g_end && !failed; base += TC_STAGES) {
+#pragma unroll
+        for (int u = 0; u < TC_STAGES; ++u) {
+            const int grp = base + u;
+            if (grp < g_end && !failed) { // uniform over the CTA
+                const tc_group cur = ring[u];
+                if (live && grp + TC_STAGES < g_end) load_group(ring[u]);
+                // weight stage u held K-group grp - 3: thread 0 saw its products complete before the previous barrier
+                unsigned char* a_stage = a_smem + u * TC_A_STAGE + a_dst;
+                const uint32_t z = (cur.zw >> zshift) & 0xFu;
+                const __half2 add = tc_bits_h2((0xE400u + z) | ((0xD400u + (z << 4)) << 16)); // (-(1024 + z), -(64 + z))
+                const __half2 sc = tc_bits_h2((cur.s & 0xFFFFu) * 0x10001u);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) // packed row 4 rq + j = the 8 k of one core-matrix row
+                    *reinterpret_cast<uint4*>(a_stage + j * TC_A_KSTRIDE) =
+                        make_uint4(tc_pair<0>(cur.w[j], mul, add, sc), tc_pair<1>(cur.w[j], mul, add, sc), tc_pair<2>(cur.w[j], mul, add, sc),
+                                   tc_pair<3>(cur.w[j], mul, add, sc));
+                tc_cp_async_wait<1>();    // this thread's activation chunks of K-group grp have landed
+                fence_proxy_async_smem(); // generic-proxy writes (stores, cp.async) before the tensor core reads them
+                if (tid == 0 && it >= 2) { // K-group grp - 2 done: its stages may be refilled after the barrier
+                    if (!mbar_wait(&bar_free[(it - 2) % TC_STAGES], (uint32_t)(((it - 2) / TC_STAGES) & 1))) {
+                        fail_flag = 1u;
+                        if (p.status) atomicExch(p.status, TC_FAIL_FREE);
+                    }
+                }
+                tc_fence_before();
+                __syncthreads();
+                failed = *reinterpret_cast<volatile uint32_t*>(&fail_flag) != 0u;
+                if (!failed) {
+                    if (tid == 0) {
+                        tc_fence_after();
+                        const uint32_t a_addr = smem_u32(a_smem + u * TC_A_STAGE), x_addr = smem_u32(x_smem + (size_t)xstage * x_stage_bytes);
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk) // k = 16 kk .. + 15: two k chunks
+                            tc_mma(tmem_d, tc_smem_desc(a_addr + kk * 2 * TC_A_KSTRIDE, TC_A_KSTRIDE, TC_A_SBO),
+                                   tc_smem_desc(x_addr + kk * 2 * x_kstride, x_kstride, 128), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                        tc_commit(&bar_free[u]);
+                    }
+                    // K-group grp + 2 goes where grp - 3 was
+                    copy_x(grp + 2, xstage + 2 >= TC_X_STAGES ? xstage + 2 - TC_X_STAGES : xstage + 2);
+                    xstage = xstage + 1 == TC_X_STAGES ? 0 : xstage + 1;
+                    ++it;
+                }
+            }
+        }
+    }
+    tc_cp_async_wait<0>();
+    pdl_launch_dependents();
+    // every product issued by thread 0 is done when this barrier fires
+    if (tid == 0) tc_commit(&bar_done);
+    const bool done = mbar_wait(&bar_done, 0);
+    if (!done && tid == 0 && p.status) atomicExch(p.status, TC_FAIL_DONE);
+    tc_fence_after();
+    failed = __syncthreads_or((failed || !done) ? 1 : 0) != 0;
+    // accumulator -> partial tile: TMEM lane = column of the tile, TMEM column = token; warp w may touch lanes 32w..32w+31
+    if (!failed && warp < 4) {
+        for (int c = 0; c < NT / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld16(tmem_d + ((uint32_t)(32 * warp) << 16) + (uint32_t)(c * 16), r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) pt[(c * 16 + j) * TC_PSTRIDE + 32 * warp + lane] = __uint_as_float(r[j]);
+        }
+    }
+    tc_fence_before();
+    tc_cluster_sync(); // every CTA of the cluster has its tile in place (a plain CTA barrier when there is no cluster)
+    const uint32_t rank = KS > 1 ? tc_cluster_rank() : 0u;
+    const int cols = min(TC_COLS, p.N - (int)blockIdx.x * TC_COLS);
+    if (!failed) {
+        for (int i = tid; i < NT * TC_COLS; i += TC_THREADS) {
+            const int b = i / TC_COLS, c = i % TC_COLS;
+            if (b >= p.B || c >= cols || (b % KS) != (int)rank) continue;
+            float v = 0.f;
+            if (KS == 1) v = pt[b * TC_PSTRIDE + c];
+            else
+                for (int q = 0; q < KS; ++q) v += tc_ld_cluster(pt + b * TC_PSTRIDE + c, (uint32_t)q);
+            const size_t o = (size_t)b * p.N + (size_t)blockIdx.x * TC_COLS + c;
+            if (p.y_f32) reinterpret_cast<float*>(p.y)[o] = v;
+            else reinterpret_cast<__half*>(p.y)[o] = __float2half_rn(v);
+        }
+    }
+    if (KS > 1) tc_cluster_sync(); // nobody leaves while a neighbour still reads its tile
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_d, TC_TMEM_COLS);
+}

@@ -130,6 +130,8 @@ typedef struct {
     void* y;                 /* fp32 or fp16 [B, N] */
     int32_t K, N, B;
     int32_t y_f32;
+    uint32_t* status; /* device status word for bounded waits (may be NULL) */
+    int32_t reserved;
 } lb_bgemm_params;
 
 /* ---- dense bf16 [N,K] x vector ------------------------------------------ */
