@@ -5,17 +5,18 @@
 // (int4 -> fp16 into shared memory, then 16x8x16 tensor-core products); the product here is one
 // tcgen05.mma of 128 weight columns x NT tokens x 16 k per instruction, accumulated in tensor memory.
 //
-// One CTA = 128 output columns x one K slice, 512 threads.  Per K-group (128 k):
-//   * every thread dequantises 4 packed words of one column (prefetched three groups earlier): a packed
+// One CTA = 128 output columns x one K slice: 16 dequantising warps and one issuing warp.  Per K-group (128 k):
+//   * every dequantising thread converts 4 packed words of one column (prefetched three groups earlier): a packed
 //     word is the 8 k of one row of a core matrix, so its eight fp16 values (q - z) * s - q - z exact
 //     through the 0x6400 exponent trick, then one fp16 multiply: the weight the reference kernel
 //     multiplies - are one 16-byte shared-memory store into the canonical K-major, unswizzled operand
 //     layout (core matrix = 8 columns x 8 k, 128 contiguous bytes);
 //   * the activations of the group arrive by cp.async (16-byte chunks, three groups ahead) in the same
 //     layout with tokens as rows;
-//   * after a proxy fence and a CTA barrier one thread issues the eight tcgen05.mma (k = 16 each) of the
-//     group and commits them to the stage's mbarrier; the same thread waits for the barrier of the group
-//     two back before it joins the next CTA barrier, after which that group's stages are refilled.
+//   * each warp fences its stores for the async proxy and arrives on the stage's "full" mbarrier; the issuing
+//     thread waits for it, issues the eight tcgen05.mma (k = 16 each) of the group and commits them to the
+//     stage's "free" mbarrier, which the dequantising warps wait for before they refill the stage three
+//     groups later.  No CTA-wide barrier inside the loop: the warps drift apart by up to three stages.
 // Epilogue: warps 0-3 read the accumulator (lane = column, TMEM column = token) with tcgen05.ld into the
 // partial tile in shared memory; K slices (the CTAs of a cluster) are added in rank order through
 // distributed shared memory exactly as in the mma.sync kernel of batched.cu.
@@ -24,8 +25,11 @@
 #include "params.h"
 
 #define TC_COLS 128    // weight columns per CTA = M of the product
-#define TC_THREADS 512
+#define TC_DQ_THREADS 512                // dequantising threads (16 warps)
+#define TC_WORDS (16 * TC_COLS / TC_DQ_THREADS) // packed words (of one column) a thread converts per K-group
+#define TC_THREADS (TC_DQ_THREADS + 32)   // + one warp whose lane 0 issues the products
 #define TC_STAGES 3
+#define TC_RING 3 // K-groups of packed words a thread keeps in registers ahead of its conversion (a multiple of TC_STAGES)
 #define TC_PSTRIDE 132                 // floats per row of the partial tile
 #define TC_TMEM_COLS 64
 
@@ -97,8 +101,8 @@ __device__ __forceinline__ uint32_t tc_pair(uint32_t w, __half2 mul, __half2 add
     return tc_h2_bits(__hmul2(__hfma2(tc_bits_h2(tc_lop3_and_or(v, 0x00f0000fu, 0x64006400u)), mul, add), s));
 }
 
-struct tc_group { // a thread's share of one K-group: packed rows 4 rq .. 4 rq + 3 (k = 32 rq .. + 31) of one column
-    uint32_t w[4];
+struct tc_group { // a thread's share of one K-group: TC_WORDS consecutive packed rows (8 k each) of one column
+    uint32_t w[TC_WORDS];
     uint32_t s;  // its fp16 scale (u16 load)
     uint32_t zw; // the zero-point word of its octet, as loaded (the nibble is taken out when the group is used)
 };
@@ -109,13 +113,14 @@ struct tc_group { // a thread's share of one K-group: packed rows 4 rq .. 4 rq +
 #define TC_X_STAGES 5                  // activation ring: a stage is refilled three groups after its products were issued
 #define TC_FAIL_FREE 0x1101u           // status: a stage's products never completed
 #define TC_FAIL_DONE 0x1102u           // status: the last products never completed
+#define TC_FAIL_FULL 0x1103u           // status: a stage was never filled
 
 extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const __grid_constant__ lb_bgemm_params p) {
     extern __shared__ __align__(1024) unsigned char tc_smem[];
-    __shared__ __align__(8) uint64_t bar_free[TC_STAGES];
+    __shared__ __align__(8) uint64_t bar_free[TC_STAGES]; // a stage's products are done (tcgen05.commit)
+    __shared__ __align__(8) uint64_t bar_full[TC_STAGES]; // a stage's weights and activations are in place (one arrival per dequantising warp)
     __shared__ __align__(8) uint64_t bar_done;
     __shared__ uint32_t tmem_base_slot;
-    __shared__ uint32_t fail_flag;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NT = p.B > 32 ? 64 : p.B > 16 ? 32 : 16; // tokens the product carries (rows past B are zero)
     const uint32_t x_stage_bytes = (uint32_t)NT * 256u, x_kstride = (uint32_t)NT * 16u;
@@ -126,10 +131,12 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
     const int g_begin = (int)(((long long)blockIdx.y * groups) / KS), g_end = (int)(((long long)(blockIdx.y + 1) * groups) / KS);
 
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) mbar_init(&bar_free[s], 1);
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(&bar_free[s], 1);
+            mbar_init(&bar_full[s], TC_DQ_THREADS / 32);
+        }
         mbar_init(&bar_done, 1);
         mbar_fence_init();
-        fail_flag = 0u;
     }
     if (warp == 0) tmem_alloc(&tmem_base_slot, TC_TMEM_COLS);
     tc_fence_before();
@@ -138,109 +145,116 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
     const uint32_t tmem_d = tmem_base_slot;
     pdl_wait();
 
-    // weights: this thread's column and its four packed rows of every K-group
-    const int nl = tid & (TC_COLS - 1), rq = tid >> 7; // column of the tile, row quad
-    const int n = blockIdx.x * TC_COLS + nl;
-    const bool live = n < p.N;
-    const uint32_t* qptr = p.qweight + ((size_t)g_begin * 16 + 4 * rq) * p.N + n;
-    const uint16_t* sptr = p.scales + (size_t)g_begin * p.N + n;
-    const uint32_t* zptr = p.qzeros ? p.qzeros + (size_t)g_begin * (p.N / 8) + (n >> 3) : nullptr;
-    const size_t row_stride = (size_t)p.N;
-    auto load_group = [&](tc_group& w) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) w.w[j] = __ldg(qptr + j * row_stride);
-        w.s = __ldg(sptr);
-        w.zw = zptr ? __ldg(zptr) : 0x88888888u;
-        qptr += 16 * row_stride;
-        sptr += row_stride;
-        if (zptr) zptr += row_stride / 8;
-    };
-    // activations: chunk c (k = 8c..8c+7) of token b goes to (b / 8) * 128 + c * x_kstride + (b % 8) * 16 of its stage;
-    // thread tid < 16 NT copies chunk tid % 16 of token tid / 16, and with 64 tokens also that of token tid / 16 + 32
-    const int xb = tid >> 4;
-    const bool x_copy = xb < NT, x_two = NT > 32;
-    const uint16_t* xsrc0 = p.x + (size_t)g_begin * 128 + (tid & 15) * 8 + (size_t)(xb < p.B ? xb : 0) * p.K;
-    const uint16_t* xsrc1 = p.x + (size_t)g_begin * 128 + (tid & 15) * 8 + (size_t)(xb + 32 < p.B ? xb + 32 : 0) * p.K;
-    const uint32_t xdst = (uint32_t)((xb >> 3) * 128 + (tid & 15) * x_kstride + (xb & 7) * 16);
-    const bool x_valid0 = xb < p.B, x_valid1 = xb + 32 < p.B;
-    auto copy_x = [&](int grp, int stage) {
-        if (grp < g_end && x_copy) {
-            unsigned char* dst = x_smem + (size_t)stage * x_stage_bytes + xdst;
-            tc_cp_async16(dst, xsrc0, x_valid0);
-            if (x_two) tc_cp_async16(dst + 4 * 128, xsrc1, x_valid1);
-            xsrc0 += 128;
-            xsrc1 += 128;
-        }
-        tc_cp_async_commit(); // one commit per K-group, empty or not: the waits count groups
-    };
-
-    tc_group ring[TC_STAGES];
-#pragma unroll
-    for (int u = 0; u < TC_STAGES; ++u) {
-        ring[u].w[0] = ring[u].w[1] = ring[u].w[2] = ring[u].w[3] = 0u;
-        ring[u].s = 0u;
-        ring[u].zw = 0x88888888u;
-        if (live && g_begin + u < g_end) load_group(ring[u]);
-    }
-    copy_x(g_begin, 0);
-    copy_x(g_begin + 1, 1);
-
-    const __half2 mul = tc_bits_h2(0x2C003C00u); // (1, 1/16)
     const uint32_t idesc = tc_idesc(TC_COLS, (uint32_t)NT);
-    const uint32_t a_dst = (uint32_t)(4 * rq * TC_A_KSTRIDE + (nl >> 3) * TC_A_SBO + (nl & 7) * 16); // + j * TC_A_KSTRIDE
-    const int zshift = 4 * (n & 7);
     bool failed = false;
-    int it = 0, xstage = 0;
-    for (int base = g_begin; base < g_end && !failed; base += TC_STAGES) {
+    if (warp < TC_DQ_THREADS / 32) {
+        // ---------------- dequantising warps: fill stage after stage, never waiting for each other ----------------
+        // weights: this thread's column and its four packed rows of every K-group
+        const int nl = tid & (TC_COLS - 1), rq = tid >> 7; // column of the tile, which run of TC_WORDS packed rows (0..3)
+        const int n = blockIdx.x * TC_COLS + nl;
+        const bool live = n < p.N;
+        const uint32_t* qptr = p.qweight + ((size_t)g_begin * 16 + TC_WORDS * rq) * p.N + n;
+        const uint16_t* sptr = p.scales + (size_t)g_begin * p.N + n;
+        const uint32_t* zptr = p.qzeros ? p.qzeros + (size_t)g_begin * (p.N / 8) + (n >> 3) : nullptr;
+        const size_t row_stride = (size_t)p.N;
+        auto load_group = [&](tc_group& w) {
 #pragma unroll
-        for (int u = 0; u < TC_STAGES; ++u) {
-            const int grp = base + u;
-            if (grp < g_end && !failed) { // uniform over the CTA
-                const tc_group cur = ring[u];
-                if (live && grp + TC_STAGES < g_end) load_group(ring[u]);
-                // weight stage u held K-group grp - 3: thread 0 saw its products complete before the previous barrier
-                unsigned char* a_stage = a_smem + u * TC_A_STAGE + a_dst;
-                const uint32_t z = (cur.zw >> zshift) & 0xFu;
-                const __half2 add = tc_bits_h2((0xE400u + z) | ((0xD400u + (z << 4)) << 16)); // (-(1024 + z), -(64 + z))
-                const __half2 sc = tc_bits_h2((cur.s & 0xFFFFu) * 0x10001u);
+            for (int j = 0; j < TC_WORDS; ++j) w.w[j] = __ldg(qptr + j * row_stride);
+            w.s = __ldg(sptr);
+            w.zw = zptr ? __ldg(zptr) : 0x88888888u;
+            qptr += 16 * row_stride;
+            sptr += row_stride;
+            if (zptr) zptr += row_stride / 8;
+        };
+        // activations: chunk c (k = 8c..8c+7) of token b goes to (b / 8) * 128 + c * x_kstride + (b % 8) * 16 of its stage;
+        // thread tid copies chunk tid % 16 of tokens tid / 16, tid / 16 + 32, ... below NT
+        const int xb = tid >> 4;
+        const uint16_t* xsrc = p.x + (size_t)g_begin * 128 + (tid & 15) * 8;
+        const uint32_t xdst = (uint32_t)((xb >> 3) * 128 + (tid & 15) * x_kstride + (xb & 7) * 16);
+        auto copy_x = [&](int grp, int stage) {
+            if (grp < g_end) {
+                unsigned char* dst = x_smem + (size_t)stage * x_stage_bytes + xdst;
+                for (int b = xb, c = 0; b < NT; b += TC_DQ_THREADS / 16, ++c) // token groups of 8 are 128 bytes apart
+                    tc_cp_async16(dst + c * (TC_DQ_THREADS / 128) * 128, xsrc + (size_t)(b < p.B ? b : 0) * p.K, b < p.B);
+                xsrc += 128;
+            }
+            tc_cp_async_commit(); // one commit per K-group, empty or not: the waits count groups
+        };
+
+        tc_group ring[TC_RING]; // packed words of the next TC_RING K-groups
 #pragma unroll
-                for (int j = 0; j < 4; ++j) // packed row 4 rq + j = the 8 k of one core-matrix row
-                    *reinterpret_cast<uint4*>(a_stage + j * TC_A_KSTRIDE) =
-                        make_uint4(tc_pair<0>(cur.w[j], mul, add, sc), tc_pair<1>(cur.w[j], mul, add, sc), tc_pair<2>(cur.w[j], mul, add, sc),
-                                   tc_pair<3>(cur.w[j], mul, add, sc));
-                tc_cp_async_wait<1>();    // this thread's activation chunks of K-group grp have landed
-                fence_proxy_async_smem(); // generic-proxy writes (stores, cp.async) before the tensor core reads them
-                if (tid == 0 && it >= 2) { // K-group grp - 2 done: its stages may be refilled after the barrier
-                    if (!mbar_wait(&bar_free[(it - 2) % TC_STAGES], (uint32_t)(((it - 2) / TC_STAGES) & 1))) {
-                        fail_flag = 1u;
+        for (int u = 0; u < TC_RING; ++u) {
+#pragma unroll
+            for (int j = 0; j < TC_WORDS; ++j) ring[u].w[j] = 0u;
+            ring[u].s = 0u;
+            ring[u].zw = 0x88888888u;
+            if (live && g_begin + u < g_end) load_group(ring[u]);
+        }
+        copy_x(g_begin, 0);
+        copy_x(g_begin + 1, 1);
+
+        const __half2 mul = tc_bits_h2(0x2C003C00u); // (1, 1/16)
+        const uint32_t a_dst = (uint32_t)(TC_WORDS * rq * TC_A_KSTRIDE + (nl >> 3) * TC_A_SBO + (nl & 7) * 16); // + j * TC_A_KSTRIDE
+        const int zshift = 4 * (n & 7);
+        int it = 0, xstage = 0;
+        for (int base = g_begin; base < g_end && !failed; base += TC_RING) {
+#pragma unroll
+            for (int u = 0; u < TC_RING; ++u) {
+                const int grp = base + u, st = u % TC_STAGES; // TC_RING is a multiple of TC_STAGES
+
+                if (grp < g_end && !failed) {
+                    const tc_group cur = ring[u];
+                    if (live && grp + TC_RING < g_end) load_group(ring[u]);
+                    const uint32_t z = (cur.zw >> zshift) & 0xFu;
+                    const __half2 add = tc_bits_h2((0xE400u + z) | ((0xD400u + (z << 4)) << 16)); // (-(1024 + z), -(64 + z))
+                    const __half2 sc = tc_bits_h2((cur.s & 0xFFFFu) * 0x10001u);
+                    uint4 v[TC_WORDS];
+#pragma unroll
+                    for (int j = 0; j < TC_WORDS; ++j) // a packed row = the 8 k of one core-matrix row
+                        v[j] = make_uint4(tc_pair<0>(cur.w[j], mul, add, sc), tc_pair<1>(cur.w[j], mul, add, sc), tc_pair<2>(cur.w[j], mul, add, sc),
+                                          tc_pair<3>(cur.w[j], mul, add, sc));
+                    // stage st held K-group grp - 3: wait until its products are done (its activation stage is then free too)
+                    if (it >= TC_STAGES && !mbar_wait(&bar_free[st], (uint32_t)((it / TC_STAGES - 1) & 1))) {
+                        failed = true;
                         if (p.status) atomicExch(p.status, TC_FAIL_FREE);
                     }
-                }
-                tc_fence_before();
-                __syncthreads();
-                failed = *reinterpret_cast<volatile uint32_t*>(&fail_flag) != 0u;
-                if (!failed) {
-                    if (tid == 0) {
-                        tc_fence_after();
-                        const uint32_t a_addr = smem_u32(a_smem + u * TC_A_STAGE), x_addr = smem_u32(x_smem + (size_t)xstage * x_stage_bytes);
+                    failed = __any_sync(0xffffffffu, failed); // the warp leaves the loop together
+                    unsigned char* a_stage = a_smem + st * TC_A_STAGE + a_dst;
 #pragma unroll
-                        for (int kk = 0; kk < 8; ++kk) // k = 16 kk .. + 15: two k chunks
-                            tc_mma(tmem_d, tc_smem_desc(a_addr + kk * 2 * TC_A_KSTRIDE, TC_A_KSTRIDE, TC_A_SBO),
-                                   tc_smem_desc(x_addr + kk * 2 * x_kstride, x_kstride, 128), idesc, (it > 0 || kk > 0) ? 1u : 0u);
-                        tc_commit(&bar_free[u]);
-                    }
-                    // K-group grp + 2 goes where grp - 3 was
-                    copy_x(grp + 2, xstage + 2 >= TC_X_STAGES ? xstage + 2 - TC_X_STAGES : xstage + 2);
+                    for (int j = 0; j < TC_WORDS; ++j) *reinterpret_cast<uint4*>(a_stage + j * TC_A_KSTRIDE) = v[j];
+                    tc_cp_async_wait<1>();    // this thread's activation chunks of K-group grp have landed
+                    fence_proxy_async_smem(); // generic-proxy writes (stores, cp.async) before the tensor core reads them
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_full[st]);
+                    copy_x(grp + 2, xstage + 2 >= TC_X_STAGES ? xstage + 2 - TC_X_STAGES : xstage + 2); // where grp - 3 was
                     xstage = xstage + 1 == TC_X_STAGES ? 0 : xstage + 1;
                     ++it;
                 }
             }
         }
+    } else if (lane == 0) {
+        // ---------------- issuing thread: eight products per K-group as soon as its stage is full ----------------
+        int it = 0, xstage = 0;
+        for (int grp = g_begin; grp < g_end; ++grp, ++it) {
+            const int u = it % TC_STAGES;
+            if (!mbar_wait(&bar_full[u], (uint32_t)((it / TC_STAGES) & 1))) {
+                failed = true;
+                if (p.status) atomicExch(p.status, TC_FAIL_FULL);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(a_smem + u * TC_A_STAGE), x_addr = smem_u32(x_smem + (size_t)xstage * x_stage_bytes);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) // k = 16 kk .. + 15: two k chunks
+                tc_mma(tmem_d, tc_smem_desc(a_addr + kk * 2 * TC_A_KSTRIDE, TC_A_KSTRIDE, TC_A_SBO),
+                       tc_smem_desc(x_addr + kk * 2 * x_kstride, x_kstride, 128), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+            tc_commit(&bar_free[u]);
+            xstage = xstage + 1 == TC_X_STAGES ? 0 : xstage + 1;
+        }
+        tc_commit(&bar_done); // fires when every product issued above is done
     }
     tc_cp_async_wait<0>();
     pdl_launch_dependents();
-    // every product issued by thread 0 is done when this barrier fires
-    if (tid == 0) tc_commit(&bar_done);
     const bool done = mbar_wait(&bar_done, 0);
     if (!done && tid == 0 && p.status) atomicExch(p.status, TC_FAIL_DONE);
     tc_fence_after();
