@@ -5,14 +5,14 @@
 // (int4 -> fp16 into shared memory, then 16x8x16 tensor-core products); the product here is one
 // tcgen05.mma of 128 weight columns x NT tokens x 16 k per instruction, accumulated in tensor memory.
 //
-// One CTA = 128 output columns x one K slice: 16 dequantising warps and one issuing warp.  Per K-group (128 k):
+// One CTA = 128 output columns x one K slice: 16 dequantising warps, one issuing thread, one activation thread.  Per K-group (128 k):
 //   * every dequantising thread converts 4 packed words of one column (prefetched three groups earlier): a packed
 //     word is the 8 k of one row of a core matrix, so its eight fp16 values (q - z) * s - q - z exact
 //     through the 0x6400 exponent trick, then one fp16 multiply: the weight the reference kernel
 //     multiplies - are one 16-byte shared-memory store into the canonical K-major, unswizzled operand
 //     layout (core matrix = 8 columns x 8 k, 128 contiguous bytes);
-//   * the activations of the group arrive by cp.async (16-byte chunks, three groups ahead) in the same
-//     layout with tokens as rows;
+//   * the activations of the group arrive by one tiled TMA load (three groups ahead; the tensor map walks
+//     X as [chunk of 8 k][token][8 k]) in the same layout with tokens as rows;
 //   * each warp fences its stores for the async proxy and arrives on the stage's "full" mbarrier; the issuing
 //     thread waits for it, issues the eight tcgen05.mma (k = 16 each) of the group and commits them to the
 //     stage's "free" mbarrier, which the dequantising warps wait for before they refill the stage three
@@ -27,7 +27,7 @@
 #define TC_COLS 128    // weight columns per CTA = M of the product
 #define TC_DQ_THREADS 512                // dequantising threads (16 warps)
 #define TC_WORDS (16 * TC_COLS / TC_DQ_THREADS) // packed words (of one column) a thread converts per K-group
-#define TC_THREADS (TC_DQ_THREADS + 32)   // + one warp whose lane 0 issues the products
+#define TC_THREADS (TC_DQ_THREADS + 64)   // + one warp whose lane 0 issues the products + one whose lane 0 brings the activations
 #define TC_STAGES 3
 #define TC_RING 3 // K-groups of packed words a thread keeps in registers ahead of its conversion (a multiple of TC_STAGES)
 #define TC_PSTRIDE 132                 // floats per row of the partial tile
@@ -43,14 +43,6 @@ __device__ __forceinline__ float tc_ld_cluster(const float* local_ptr, uint32_t 
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
     return v;
 }
-__device__ __forceinline__ void tc_cp_async16(void* dst_smem, const void* src, bool valid) { // zero fill when !valid
-    const uint32_t n = valid ? 16u : 0u;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void tc_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void tc_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 // ---- tcgen05 ---------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) { // one full warp
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
@@ -101,6 +93,23 @@ __device__ __forceinline__ uint32_t tc_pair(uint32_t w, __half2 mul, __half2 add
     return tc_h2_bits(__hmul2(__hfma2(tc_bits_h2(tc_lop3_and_or(v, 0x00f0000fu, 0x64006400u)), mul, add), s));
 }
 
+// One tiled TMA load of the activations of a K-group: the tensor map views X as [chunk of 8 k][token][8 k], the box is
+// 16 chunks x NT tokens x 8 k, so the tile lands as [chunk][token][16 bytes]: the K-major core-matrix layout with the
+// tokens as rows.  Tokens past the batch are filled with zeros by the copy engine.
+__device__ __forceinline__ void tc_tma_x(uint32_t dst_smem, const void* tmap, int chunk, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst_smem),
+                 "l"(tmap), "r"(0), "r"(0), "r"(chunk), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Bounded wait of the two single-thread roles on a pipeline mbarrier, without reading the global timer (these waits sit on
+// the critical path of every K-group): try_wait suspends the thread for a while by itself; 4M polls take seconds at most.
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
 struct tc_group { // a thread's share of one K-group: TC_WORDS consecutive packed rows (8 k each) of one column
     uint32_t w[TC_WORDS];
     uint32_t s;  // its fp16 scale (u16 load)
@@ -118,7 +127,9 @@ struct tc_group { // a thread's share of one K-group: TC_WORDS consecutive packe
 extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const __grid_constant__ lb_bgemm_params p) {
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     __shared__ __align__(8) uint64_t bar_free[TC_STAGES]; // a stage's products are done (tcgen05.commit)
-    __shared__ __align__(8) uint64_t bar_full[TC_STAGES]; // a stage's weights and activations are in place (one arrival per dequantising warp)
+    __shared__ __align__(8) uint64_t bar_full[TC_STAGES]; // a stage's weights are in place (one arrival per dequantising warp)
+    __shared__ __align__(8) uint64_t bar_x[TC_X_STAGES];  // an activation stage has landed (TMA transaction bytes)
+    __shared__ __align__(8) uint64_t bar_xfree[TC_X_STAGES]; // the products that read an activation stage are done
     __shared__ __align__(8) uint64_t bar_done;
     __shared__ uint32_t tmem_base_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -134,6 +145,10 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
         for (int s = 0; s < TC_STAGES; ++s) {
             mbar_init(&bar_free[s], 1);
             mbar_init(&bar_full[s], TC_DQ_THREADS / 32);
+        }
+        for (int s = 0; s < TC_X_STAGES; ++s) {
+            mbar_init(&bar_x[s], 1);
+            mbar_init(&bar_xfree[s], 1);
         }
         mbar_init(&bar_done, 1);
         mbar_fence_init();
@@ -166,21 +181,6 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
             sptr += row_stride;
             if (zptr) zptr += row_stride / 8;
         };
-        // activations: chunk c (k = 8c..8c+7) of token b goes to (b / 8) * 128 + c * x_kstride + (b % 8) * 16 of its stage;
-        // thread tid copies chunk tid % 16 of tokens tid / 16, tid / 16 + 32, ... below NT
-        const int xb = tid >> 4;
-        const uint16_t* xsrc = p.x + (size_t)g_begin * 128 + (tid & 15) * 8;
-        const uint32_t xdst = (uint32_t)((xb >> 3) * 128 + (tid & 15) * x_kstride + (xb & 7) * 16);
-        auto copy_x = [&](int grp, int stage) {
-            if (grp < g_end) {
-                unsigned char* dst = x_smem + (size_t)stage * x_stage_bytes + xdst;
-                for (int b = xb, c = 0; b < NT; b += TC_DQ_THREADS / 16, ++c) // token groups of 8 are 128 bytes apart
-                    tc_cp_async16(dst + c * (TC_DQ_THREADS / 128) * 128, xsrc + (size_t)(b < p.B ? b : 0) * p.K, b < p.B);
-                xsrc += 128;
-            }
-            tc_cp_async_commit(); // one commit per K-group, empty or not: the waits count groups
-        };
-
         tc_group ring[TC_RING]; // packed words of the next TC_RING K-groups
 #pragma unroll
         for (int u = 0; u < TC_RING; ++u) {
@@ -190,13 +190,10 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
             ring[u].zw = 0x88888888u;
             if (live && g_begin + u < g_end) load_group(ring[u]);
         }
-        copy_x(g_begin, 0);
-        copy_x(g_begin + 1, 1);
-
         const __half2 mul = tc_bits_h2(0x2C003C00u); // (1, 1/16)
         const uint32_t a_dst = (uint32_t)(TC_WORDS * rq * TC_A_KSTRIDE + (nl >> 3) * TC_A_SBO + (nl & 7) * 16); // + j * TC_A_KSTRIDE
         const int zshift = 4 * (n & 7);
-        int it = 0, xstage = 0;
+        int it = 0;
         for (int base = g_begin; base < g_end && !failed; base += TC_RING) {
 #pragma unroll
             for (int u = 0; u < TC_RING; ++u) {
@@ -213,7 +210,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
                     for (int j = 0; j < TC_WORDS; ++j) // a packed row = the 8 k of one core-matrix row
                         v[j] = make_uint4(tc_pair<0>(cur.w[j], mul, add, sc), tc_pair<1>(cur.w[j], mul, add, sc), tc_pair<2>(cur.w[j], mul, add, sc),
                                           tc_pair<3>(cur.w[j], mul, add, sc));
-                    // stage st held K-group grp - 3: wait until its products are done (its activation stage is then free too)
+                    // stage st held K-group grp - 3: wait until its products are done
                     if (it >= TC_STAGES && !mbar_wait(&bar_free[st], (uint32_t)((it / TC_STAGES - 1) & 1))) {
                         failed = true;
                         if (p.status) atomicExch(p.status, TC_FAIL_FREE);
@@ -222,38 +219,49 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
                     unsigned char* a_stage = a_smem + st * TC_A_STAGE + a_dst;
 #pragma unroll
                     for (int j = 0; j < TC_WORDS; ++j) *reinterpret_cast<uint4*>(a_stage + j * TC_A_KSTRIDE) = v[j];
-                    tc_cp_async_wait<1>();    // this thread's activation chunks of K-group grp have landed
-                    fence_proxy_async_smem(); // generic-proxy writes (stores, cp.async) before the tensor core reads them
+                    fence_proxy_async_smem(); // generic-proxy stores before the tensor core reads them
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bar_full[st]);
-                    copy_x(grp + 2, xstage + 2 >= TC_X_STAGES ? xstage + 2 - TC_X_STAGES : xstage + 2); // where grp - 3 was
-                    xstage = xstage + 1 == TC_X_STAGES ? 0 : xstage + 1;
                     ++it;
                 }
             }
         }
-    } else if (lane == 0) {
-        // ---------------- issuing thread: eight products per K-group as soon as its stage is full ----------------
+    } else if (warp == TC_DQ_THREADS / 32 && lane == 0) {
+        // ---------------- issuing thread: eight products per K-group as soon as its weights and activations are in place ----------------
+        const uint64_t a_desc0 = tc_smem_desc(smem_u32(a_smem), TC_A_KSTRIDE, TC_A_SBO), x_desc0 = tc_smem_desc(smem_u32(x_smem), x_kstride, 128);
         int it = 0, xstage = 0;
         for (int grp = g_begin; grp < g_end; ++grp, ++it) {
             const int u = it % TC_STAGES;
-            if (!mbar_wait(&bar_full[u], (uint32_t)((it / TC_STAGES) & 1))) {
+            if (!tc_wait(&bar_full[u], (uint32_t)((it / TC_STAGES) & 1)) || !tc_wait(&bar_x[xstage], (uint32_t)((it / TC_X_STAGES) & 1))) {
                 failed = true;
                 if (p.status) atomicExch(p.status, TC_FAIL_FULL);
                 break;
             }
             tc_fence_after();
-            const uint32_t a_addr = smem_u32(a_smem + u * TC_A_STAGE), x_addr = smem_u32(x_smem + (size_t)xstage * x_stage_bytes);
+            // descriptors: the start-address field counts 16-byte units
+            const uint64_t a_desc = a_desc0 + (uint64_t)((u * TC_A_STAGE) >> 4), x_desc = x_desc0 + (uint64_t)((xstage * x_stage_bytes) >> 4);
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) // k = 16 kk .. + 15: two k chunks
-                tc_mma(tmem_d, tc_smem_desc(a_addr + kk * 2 * TC_A_KSTRIDE, TC_A_KSTRIDE, TC_A_SBO),
-                       tc_smem_desc(x_addr + kk * 2 * x_kstride, x_kstride, 128), idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                tc_mma(tmem_d, a_desc + (uint64_t)((kk * 2 * TC_A_KSTRIDE) >> 4), x_desc + (uint64_t)((kk * 2 * x_kstride) >> 4), idesc,
+                       (it > 0 || kk > 0) ? 1u : 0u);
             tc_commit(&bar_free[u]);
+            tc_commit(&bar_xfree[xstage]);
             xstage = xstage + 1 == TC_X_STAGES ? 0 : xstage + 1;
         }
         tc_commit(&bar_done); // fires when every product issued above is done
+    } else if (warp == TC_DQ_THREADS / 32 + 1 && lane == 0) {
+        // ---------------- activation thread: one tiled TMA load per K-group, up to five groups ahead ----------------
+        int j = 0, xs = 0;
+        for (int grp = g_begin; grp < g_end; ++grp, ++j) {
+            if (j >= TC_X_STAGES && !tc_wait(&bar_xfree[xs], (uint32_t)((j / TC_X_STAGES - 1) & 1))) {
+                if (p.status) atomicExch(p.status, TC_FAIL_FREE);
+                break; // the issuing thread then gives up on this stage's barrier and reports too
+            }
+            mbar_arrive_expect_tx(&bar_x[xs], x_stage_bytes);
+            tc_tma_x(smem_u32(x_smem + (size_t)xs * x_stage_bytes), p.tmap_x, grp * 16, &bar_x[xs]);
+            xs = xs + 1 == TC_X_STAGES ? 0 : xs + 1;
+        }
     }
-    tc_cp_async_wait<0>();
     pdl_launch_dependents();
     const bool done = mbar_wait(&bar_done, 0);
     if (!done && tid == 0 && p.status) atomicExch(p.status, TC_FAIL_DONE);
