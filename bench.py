@@ -512,7 +512,7 @@ def bench_batched(args, local):
         wbytes = K // 8 * N * 4 + K // 128 * N * 2 + K // 128 * (N // 8) * 4
         d_x = ctx.to_device(lb.fill_normal(64 * K, 300, 4, dtype="f16"))
         d_y = ctx.alloc(64 * N * 4)
-        for B, flag in [(B, f) for B in batches for f in ((lb.GEMM_TCGEN05, lb.GEMM_MMA_SYNC) if B > 8 else (0,))]:
+        for B, flag in [(B, f) for B in batches for f in ((lb.GEMM_TCGEN05, lb.GEMM_MMA_SYNC) if B > 8 else (0, lb.GEMM_MMA_SYNC) if B == 1 else (0,))]:
             ctx.begin_capture()
             for j in range(reps):
                 w = dev[j % sets]
@@ -527,7 +527,7 @@ def bench_batched(args, local):
                 graph.launch()
             us = ctx.timer_stop() * 1e3 / (n * reps)
             algo = wbytes + B * K * 2 + B * N * 4
-            sweep.append({"shape": name, "K": K, "N": N, "batch": B, "path": "tcgen05" if flag == lb.GEMM_TCGEN05 else "mma.sync", "default": (flag == lb.GEMM_TCGEN05) == (B > 32),
+            sweep.append({"shape": name, "K": K, "N": N, "batch": B, "path": "tcgen05" if flag == lb.GEMM_TCGEN05 else "mma.sync" if (B > 1 or flag) else "gemv", "default": (flag == lb.GEMM_TCGEN05) == (B > 32) if B > 8 else flag == 0,
                           "us": round(us, 2), "GBps": round(algo / us / 1e3, 1),
                           "frac_of_hbm_peak": round(algo / us / 1e3 / peak, 3), "TFLOPs": round(2.0 * B * K * N / us / 1e6, 1)})
             graph.destroy()

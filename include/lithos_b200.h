@@ -171,6 +171,7 @@ int lb_gemv_chain_supports(lb_ctx* ctx, int K, int N, int swiglu);
  * (flags = LB_GEMV_Y_F32) or fp16 [B,N] (flags = 0).  K % 128 == 0, N % 16 == 0.
  * The reference's batched path is its prefill projection (kernels/projection_gemm.sass:390-631:
  * int4 -> fp16 dequantisation into shared memory, eight 16x8x16 tensor-core products per k-step);
+ * One token is handed to the GEMV kernel of lb_gemv_int4.
  * 33..64 tokens run on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory):
  * the weights are dequantised to fp16 - (q - z) * s, q - z exact, one fp16 rounding for the scale - into
  * shared memory, as the reference kernel does.  Up to 32 tokens use mma.sync (faster there, measured):

@@ -214,6 +214,9 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
     p.x = (const uint16_t*)x; p.y = (void*)y;
     p.K = K; p.N = N; p.B = B; p.y_f32 = (flags & LB_GEMV_Y_F32) != 0;
     p.status = (uint32_t*)c->dev_status;
+    /* one token: the GEMV kernel (TMA-streamed, integer tensor-core products) is the faster path, with the same result type */
+    if (B == 1 && !(flags & LB_GEMM_MMA_SYNC) && N % 32 == 0 && ((qweight | scales | qzeros | x | y) & 15ull) == 0)
+        if (lb_gemv_int4(c, qweight, scales, qzeros, x, y, K, N, flags & LB_GEMV_Y_F32) == LB_OK) return LB_OK; /* else: the batched kernel */
     const int blocks = (N + 127) / 128, groups = K / 128;
     void* params[] = {&p};
     if ((B > 32 && !(flags & LB_GEMM_MMA_SYNC)) || (flags & LB_GEMM_TCGEN05)) {
