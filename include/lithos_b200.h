@@ -295,6 +295,14 @@ int lb_model_reset_state(lb_model* m); /* zero DeltaNet states, conv history and
 /* device address of a layer's recurrent buffers: which = 0 DeltaNet state / K cache,
  * 1 conv ring [4][C] (slot = position & 3) / V cache */
 int lb_model_state_ptr(lb_model* m, int layer, int which, uint64_t* dptr_out, size_t* bytes_out);
+/* Snapshot / restore of the recurrent state (every DeltaNet layer's state matrix and convolution history), for
+ * speculative decoding: decode ahead, then lb_model_rollback and continue from the checkpointed position.
+ * Replaces the reference's state_rollback copy kernel (inference/recur.ls:82-86, kernels/recurrence_rollback.sass).
+ * Stream-ordered device-to-device copies; the KV caches are not copied (rows past the position are never read).
+ * LB_ERR_STATE from lb_model_rollback when no checkpoint was taken. */
+int lb_model_checkpoint(lb_model* m);
+int lb_model_rollback(lb_model* m);
+
 int lb_model_logits_ptr(lb_model* m, uint64_t* dptr_out);
 uint64_t lb_model_weight_bytes(const lb_model* m); /* bytes of weights one decode step streams on this shard */
 /* One token, launch by launch: token and position go in, the greedy next token comes out. */

@@ -35,6 +35,7 @@ typedef struct {
     CUdeviceptr input_norm, post_norm;
     /* DeltaNet */
     CUdeviceptr proj_a, proj_b, a_log, dt_bias, conv_w, dn_norm, dn_state, conv_ring;
+    CUdeviceptr snap_state, snap_conv; /* lb_model_checkpoint copies of dn_state and conv_ring (allocated on first use) */
     CUdeviceptr dn_params; /* lb_dn_layer_params of this layer in device memory, for the persistent chain */
     /* attention */
     CUdeviceptr q_norm, k_norm, k_cache, v_cache;
@@ -167,6 +168,35 @@ LB_API int lb_model_reset_state(lb_model* m) {
     LB_CU(c, lb_drv.StreamSynchronize(c->stream));
     return LB_OK;
 }
+
+/* Checkpoint / rollback of the recurrent state: the reference's state_rollback kernel is an element-wise copy
+ * state[i] = checkpoint[i] (inference/recur.ls:82-86, kernels/recurrence_rollback.sass).  Here both directions
+ * are device-to-device copies of every DeltaNet layer's state matrix and convolution history on the context
+ * stream (ordered with the decode steps around them).  The KV caches need no copy: a row is rewritten when
+ * its position is decoded again, and rows past the current position are never read. */
+static int model_snapshot(lb_model* m, int restore) {
+    lb_ctx* c = m->c;
+    const size_t sb = (size_t)m->HV * 128 * 128 * 4, cb = (size_t)4 * m->C_s * 4;
+    for (int l = 0; l < m->cfg.n_layers; l++) {
+        layer_t* L = &m->L[l];
+        if (L->is_fa) continue;
+        if (!L->snap_state) {
+            if (restore) return lb_fail(c, LB_ERR_STATE, "lb_model_rollback: no checkpoint taken");
+            LB_CU(c, lb_drv.MemAlloc(&L->snap_state, sb));
+            LB_CU(c, lb_drv.MemAlloc(&L->snap_conv, cb));
+        }
+        if (restore) {
+            LB_CU(c, lb_drv.MemcpyDtoDAsync(L->dn_state, L->snap_state, sb, c->stream));
+            LB_CU(c, lb_drv.MemcpyDtoDAsync(L->conv_ring, L->snap_conv, cb, c->stream));
+        } else {
+            LB_CU(c, lb_drv.MemcpyDtoDAsync(L->snap_state, L->dn_state, sb, c->stream));
+            LB_CU(c, lb_drv.MemcpyDtoDAsync(L->snap_conv, L->conv_ring, cb, c->stream));
+        }
+    }
+    return LB_OK;
+}
+LB_API int lb_model_checkpoint(lb_model* m) { return m ? model_snapshot(m, 0) : LB_ERR_INVALID; }
+LB_API int lb_model_rollback(lb_model* m) { return m ? model_snapshot(m, 1) : LB_ERR_INVALID; }
 
 LB_API int lb_model_state_ptr(lb_model* m, int layer, int which, uint64_t* dptr, size_t* bytes) {
     if (!m || layer < 0 || layer >= m->cfg.n_layers || !dptr || !bytes || which < 0 || which > 1) return LB_ERR_INVALID;
@@ -745,7 +775,8 @@ LB_API void lb_model_destroy(lb_model* m) {
                 if (q[i]->packed) lb_drv.MemFree(q[i]->packed);
             }
             CUdeviceptr p[] = {L->input_norm, L->post_norm, L->proj_a, L->proj_b, L->a_log, L->dt_bias, L->conv_w, L->dn_norm,
-                               L->dn_state, L->conv_ring, L->q_norm, L->k_norm, L->k_cache, L->v_cache, L->dn_params};
+                               L->dn_state, L->conv_ring, L->q_norm, L->k_norm, L->k_cache, L->v_cache, L->dn_params,
+                               L->snap_state, L->snap_conv};
             for (size_t i = 0; i < sizeof p / sizeof p[0]; i++) if (p[i]) lb_drv.MemFree(p[i]);
         }
         if (m->h_next) lb_drv.MemFreeHost(m->h_next);

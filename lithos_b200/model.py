@@ -101,6 +101,8 @@ def _sigs():
     L.lb_model_load_globals.argtypes = [vp, P(vp)]
     L.lb_model_fill_synthetic.argtypes = [vp, u64]
     L.lb_model_reset_state.argtypes = [vp]
+    L.lb_model_checkpoint.argtypes = [vp]
+    L.lb_model_rollback.argtypes = [vp]
     L.lb_model_state_ptr.argtypes = [vp, i32, i32, P(u64), P(C.c_size_t)]
     L.lb_model_logits_ptr.argtypes = [vp, P(u64)]
     L.lb_model_weight_bytes.argtypes = [vp]
@@ -147,6 +149,14 @@ class Model:
 
     def reset_state(self):
         self.ctx._check(lib().lb_model_reset_state(self.h))
+
+    def checkpoint(self):
+        """Snapshot the DeltaNet states and convolution histories (stream-ordered copies)."""
+        self.ctx._check(lib().lb_model_checkpoint(self.h))
+
+    def rollback(self):
+        """Restore the last checkpoint; decoding continues from the checkpointed position."""
+        self.ctx._check(lib().lb_model_rollback(self.h))
 
     def state_ptr(self, layer: int, which: int):
         p, n = C.c_uint64(0), C.c_size_t(0)

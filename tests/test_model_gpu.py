@@ -165,3 +165,44 @@ def test_full_width_layers_chain_vs_separate_launches_vs_oracle(ctx, lb, oracle)
     for m in (gm, g1, g2):
         m.close()
     om.close()
+
+
+def test_checkpoint_and_rollback(ctx, lb, oracle):
+    """decode ahead from a checkpoint, roll back, decode again: the same tokens and bit-identical logits; the rolled-back
+    run also equals a run that never speculated (the KV rows written while speculating are rewritten, never read)"""
+    from lithos_b200 import model as M
+    import lithos_b200 as lb_mod
+    cfg = M.tiny(max_ctx=64)
+    gm = M.Model(ctx, cfg)
+    gm.fill_synthetic(SEED)
+    with pytest.raises(lb_mod.LithosError):
+        gm.rollback()                      # nothing to roll back to yet
+    tok = 7
+    for pos in range(10):
+        tok = gm.decode(tok, pos)
+    gm.checkpoint()
+    t0 = tok
+    first = []
+    for pos in range(10, 18):              # speculate 8 tokens
+        tok = gm.decode(tok, pos)
+        first.append(tok)
+    logits_first = gm.logits()
+    # a different continuation from the same point, to dirty the state and the KV rows 10..17
+    tok = (t0 + 1) % cfg.vocab
+    for pos in range(10, 18):
+        tok = gm.decode(tok, pos)
+    gm.rollback()
+    tok, second = t0, []
+    for pos in range(10, 18):
+        tok = gm.decode(tok, pos)
+        second.append(tok)
+    assert second == first
+    assert np.array_equal(gm.logits(), logits_first)
+    # the checkpoint survives a rollback: roll back once more
+    gm.rollback()
+    tok, third = t0, []
+    for pos in range(10, 18):
+        tok = gm.decode(tok, pos)
+        third.append(tok)
+    assert third == first
+    gm.close()
