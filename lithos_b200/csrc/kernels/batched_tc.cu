@@ -102,11 +102,20 @@ __device__ __forceinline__ void tc_tma_x(uint32_t dst_smem, const void* tmap, in
                  : "memory");
 }
 
-// Bounded wait of the two single-thread roles on a pipeline mbarrier, without reading the global timer (these waits sit on
-// the critical path of every K-group): try_wait suspends the thread for a while by itself; 4M polls take seconds at most.
+// Bounded wait of the single-thread roles and of each converting warp's lane 0 on a pipeline mbarrier: a tight loop of
+// non-blocking test_wait (try_wait parks the thread and wakes it late; these waits sit on the critical path of every
+// K-group), 16M polls at most, no global timer.
+__device__ __forceinline__ bool tc_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 22); ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < (1u << 24); ++i)
+        if (tc_test_wait(bar, parity)) return true;
     return false;
 }
 
@@ -211,11 +220,12 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
                         v[j] = make_uint4(tc_pair<0>(cur.w[j], mul, add, sc), tc_pair<1>(cur.w[j], mul, add, sc), tc_pair<2>(cur.w[j], mul, add, sc),
                                           tc_pair<3>(cur.w[j], mul, add, sc));
                     // stage st held K-group grp - 3: wait until its products are done
-                    if (it >= TC_STAGES && !mbar_wait(&bar_free[st], (uint32_t)((it / TC_STAGES - 1) & 1))) {
+                    // (lane 0 polls for its warp: 16 pollers per barrier instead of 512; the vote orders the others behind it)
+                    if (it >= TC_STAGES && lane == 0 && !tc_wait(&bar_free[st], (uint32_t)((it / TC_STAGES - 1) & 1))) {
                         failed = true;
                         if (p.status) atomicExch(p.status, TC_FAIL_FREE);
                     }
-                    failed = __any_sync(0xffffffffu, failed); // the warp leaves the loop together
+                    failed = __any_sync(0xffffffffu, failed); // the warp goes on, or leaves the loop, together
                     unsigned char* a_stage = a_smem + st * TC_A_STAGE + a_dst;
 #pragma unroll
                     for (int j = 0; j < TC_WORDS; ++j) *reinterpret_cast<uint4*>(a_stage + j * TC_A_KSTRIDE) = v[j];
