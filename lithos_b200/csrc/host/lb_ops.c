@@ -223,13 +223,13 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
         const int nt = B > 32 ? 64 : B > 16 ? 32 : 16;
         const unsigned smem = (unsigned)(3 * 32768 + 5 * nt * 256); /* three weight stages + five activation stages */
         if (x & 15) return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: x must be 16-byte aligned");
-        CUtensorMap tm; /* X as [chunk][token][8 halves]: a box is the K-major core-matrix tile of one K-group */
-        cuuint64_t dims[3] = {8, (cuuint64_t)B, (cuuint64_t)(K / 8)};
-        cuuint64_t strides[2] = {(cuuint64_t)K * 2, 16};
-        cuuint32_t box[3] = {8, (cuuint32_t)nt, 16};
-        cuuint32_t estr[3] = {1, 1, 1};
-        LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, (void*)x, dims, strides, box, estr,
-                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+        CUtensorMap tm; /* X [B, K] fp16, box = 64 k (128 bytes) x NT tokens, laid down with the 128-byte swizzle */
+        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)B};
+        cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)nt};
+        cuuint32_t estr[2] = {1, 1};
+        LB_CU(c, lb_drv.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)x, dims, strides, box, estr,
+                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
         memcpy(p.tmap_x, &tm, sizeof tm);
         int ksplit = c->sm_count / blocks;

@@ -5,18 +5,22 @@
 // (int4 -> fp16 into shared memory, then 16x8x16 tensor-core products); the product here is one
 // tcgen05.mma of 128 weight columns x NT tokens x 16 k per instruction, accumulated in tensor memory.
 //
-// One CTA = 128 output columns x one K slice: 16 dequantising warps, one issuing thread, one activation thread.  Per K-group (128 k):
+// One CTA = 128 output columns x one K slice: 16 dequantising warps, one issuing thread, one activation thread.
+// Per K-group (128 k):
 //   * every dequantising thread converts 4 packed words of one column (prefetched three groups earlier): a packed
-//     word is the 8 k of one row of a core matrix, so its eight fp16 values (q - z) * s - q - z exact
-//     through the 0x6400 exponent trick, then one fp16 multiply: the weight the reference kernel
-//     multiplies - are one 16-byte shared-memory store into the canonical K-major, unswizzled operand
-//     layout (core matrix = 8 columns x 8 k, 128 contiguous bytes);
-//   * the activations of the group arrive by one tiled TMA load (three groups ahead; the tensor map walks
-//     X as [chunk of 8 k][token][8 k]) in the same layout with tokens as rows;
+//     word is 8 consecutive k of one column, so its eight fp16 values (q - z) * s - q - z exact through the 0x6400
+//     exponent trick, then one fp16 multiply: the weight the reference kernel multiplies - are one 16-byte
+//     shared-memory store into the K-major operand tile with the 128-byte swizzle: two halves of 64 k, a row of
+//     128 bytes per column, 16-byte slot (chunk % 8) ^ (column % 8) inside the row;
+//   * the activations of the group arrive by two tiled TMA loads (64 k x NT tokens each, 128-byte swizzle by the
+//     copy engine, tokens past the batch zero-filled), three groups ahead, in the same layout with tokens as rows;
 //   * each warp fences its stores for the async proxy and arrives on the stage's "full" mbarrier; the issuing
-//     thread waits for it, issues the eight tcgen05.mma (k = 16 each) of the group and commits them to the
-//     stage's "free" mbarrier, which the dequantising warps wait for before they refill the stage three
-//     groups later.  No CTA-wide barrier inside the loop: the warps drift apart by up to three stages.
+//     thread waits for it and for the TMA barrier, issues the eight tcgen05.mma (k = 16 each: the descriptor's
+//     start address steps 32 bytes inside the swizzle atom) of the group and commits them to the "free" mbarriers
+//     of the weight stage and of the activation stage, which the dequantising warps and the activation thread wait
+//     for before they refill them.  No CTA-wide barrier inside the loop: the warps drift apart by up to three stages.
+// (With unswizzled core-matrix tiles the same products took ~170 cycles each and bounded the loop together with
+// the conversion; with the swizzled tiles 64 tokens cost what 16 do.)
 // Epilogue: warps 0-3 read the accumulator (lane = column, TMEM column = token) with tcgen05.ld into the
 // partial tile in shared memory; K slices (the CTAs of a cluster) are added in rank order through
 // distributed shared memory exactly as in the mma.sync kernel of batched.cu.
@@ -54,10 +58,11 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) { //
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// shared-memory operand descriptor, K-major, no swizzle: start address, leading (k direction) and stride
-// (row-group direction) byte offsets in 16-byte units, descriptor version 1 in bits 46-48
+// shared-memory operand descriptor, K-major, 128-byte swizzle: start address, leading byte offset (unused by this
+// layout) and stride byte offset (between groups of 8 rows) in 16-byte units, descriptor version 1 in bits 46-48
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46);
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) |
+           (2ull << 61); // layout type 2: 128-byte swizzle
 }
 // instruction descriptor of kind::f16: fp32 accumulator, fp16 A and B, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
 __device__ __forceinline__ uint32_t tc_idesc(uint32_t M, uint32_t N) { return (1u << 4) | ((N >> 3) << 17) | ((M >> 4) << 24); }
@@ -93,12 +98,12 @@ __device__ __forceinline__ uint32_t tc_pair(uint32_t w, __half2 mul, __half2 add
     return tc_h2_bits(__hmul2(__hfma2(tc_bits_h2(tc_lop3_and_or(v, 0x00f0000fu, 0x64006400u)), mul, add), s));
 }
 
-// One tiled TMA load of the activations of a K-group: the tensor map views X as [chunk of 8 k][token][8 k], the box is
-// 16 chunks x NT tokens x 8 k, so the tile lands as [chunk][token][16 bytes]: the K-major core-matrix layout with the
-// tokens as rows.  Tokens past the batch are filled with zeros by the copy engine.
-__device__ __forceinline__ void tc_tma_x(uint32_t dst_smem, const void* tmap, int chunk, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst_smem),
-                 "l"(tmap), "r"(0), "r"(0), "r"(chunk), "r"(smem_u32(bar))
+// One tiled TMA load of 64 k of the activations of a K-group: box 64 k (128 bytes) x NT tokens of X [B, K], written with
+// the 128-byte swizzle: the K-major operand tile with the tokens as rows.  Tokens past the batch are filled with zeros
+// by the copy engine.
+__device__ __forceinline__ void tc_tma_x(uint32_t dst_smem, const void* tmap, int k, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
+                 "l"(tmap), "r"(k), "r"(0), "r"(smem_u32(bar))
                  : "memory");
 }
 
@@ -125,9 +130,9 @@ struct tc_group { // a thread's share of one K-group: TC_WORDS consecutive packe
     uint32_t zw; // the zero-point word of its octet, as loaded (the nibble is taken out when the group is used)
 };
 
-#define TC_A_SBO 128                   // bytes between column groups (8 columns) of the weight tile: core matrices back to back
-#define TC_A_KSTRIDE (16 * TC_A_SBO)   // bytes between k chunks (8 k)
-#define TC_A_STAGE (16 * TC_A_KSTRIDE) // one K-group of dequantised weights: 32 KB
+#define TC_SBO 1024                    // bytes between groups of 8 rows: 8 rows of 128 bytes (one 128-byte swizzle atom)
+#define TC_A_HALF (TC_COLS * 128)      // one 64-k half of the weight tile: 128 rows of 128 bytes
+#define TC_A_STAGE (2 * TC_A_HALF)     // one K-group of dequantised weights: 32 KB
 #define TC_X_STAGES 5                  // activation ring: a stage is refilled three groups after its products were issued
 #define TC_FAIL_FREE 0x1101u           // status: a stage's products never completed
 #define TC_FAIL_DONE 0x1102u           // status: the last products never completed
@@ -143,7 +148,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
     __shared__ uint32_t tmem_base_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NT = p.B > 32 ? 64 : p.B > 16 ? 32 : 16; // tokens the product carries (rows past B are zero)
-    const uint32_t x_stage_bytes = (uint32_t)NT * 256u, x_kstride = (uint32_t)NT * 16u;
+    const uint32_t x_stage_bytes = (uint32_t)NT * 256u, x_half = (uint32_t)NT * 128u; // a 64-k half: NT rows of 128 bytes
     unsigned char* a_smem = tc_smem;                          // [TC_STAGES][TC_A_STAGE]
     unsigned char* x_smem = tc_smem + TC_STAGES * TC_A_STAGE; // [TC_X_STAGES][NT * 256]
     float* pt = reinterpret_cast<float*>(tc_smem);            // [NT][TC_PSTRIDE], over the weight stages once the products are done
@@ -200,7 +205,8 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
             if (live && g_begin + u < g_end) load_group(ring[u]);
         }
         const __half2 mul = tc_bits_h2(0x2C003C00u); // (1, 1/16)
-        const uint32_t a_dst = (uint32_t)(TC_WORDS * rq * TC_A_KSTRIDE + (nl >> 3) * TC_A_SBO + (nl & 7) * 16); // + j * TC_A_KSTRIDE
+        // chunk c (k = 8c..8c+7) of column nl: half c / 8, row nl, 16-byte slot (c % 8) ^ (nl % 8) of the row (128-byte swizzle)
+        const uint32_t a_row = (uint32_t)(nl * 128), a_xor = (uint32_t)(nl & 7);
         const int zshift = 4 * (n & 7);
         int it = 0;
         for (int base = g_begin; base < g_end && !failed; base += TC_RING) {
@@ -226,9 +232,12 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
                         if (p.status) atomicExch(p.status, TC_FAIL_FREE);
                     }
                     failed = __any_sync(0xffffffffu, failed); // the warp goes on, or leaves the loop, together
-                    unsigned char* a_stage = a_smem + st * TC_A_STAGE + a_dst;
+                    unsigned char* a_stage = a_smem + st * TC_A_STAGE + a_row;
 #pragma unroll
-                    for (int j = 0; j < TC_WORDS; ++j) *reinterpret_cast<uint4*>(a_stage + j * TC_A_KSTRIDE) = v[j];
+                    for (int j = 0; j < TC_WORDS; ++j) {
+                        const uint32_t c = (uint32_t)(TC_WORDS * rq + j);
+                        *reinterpret_cast<uint4*>(a_stage + (c >> 3) * TC_A_HALF + (((c & 7) ^ a_xor) << 4)) = v[j];
+                    }
                     fence_proxy_async_smem(); // generic-proxy stores before the tensor core reads them
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bar_full[st]);
@@ -238,7 +247,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
         }
     } else if (warp == TC_DQ_THREADS / 32 && lane == 0) {
         // ---------------- issuing thread: eight products per K-group as soon as its weights and activations are in place ----------------
-        const uint64_t a_desc0 = tc_smem_desc(smem_u32(a_smem), TC_A_KSTRIDE, TC_A_SBO), x_desc0 = tc_smem_desc(smem_u32(x_smem), x_kstride, 128);
+        const uint64_t a_desc0 = tc_smem_desc(smem_u32(a_smem), 16, TC_SBO), x_desc0 = tc_smem_desc(smem_u32(x_smem), 16, TC_SBO);
         int it = 0, xstage = 0;
         for (int grp = g_begin; grp < g_end; ++grp, ++it) {
             const int u = it % TC_STAGES;
@@ -252,7 +261,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
             const uint64_t a_desc = a_desc0 + (uint64_t)((u * TC_A_STAGE) >> 4), x_desc = x_desc0 + (uint64_t)((xstage * x_stage_bytes) >> 4);
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) // k = 16 kk .. + 15: two k chunks
-                tc_mma(tmem_d, a_desc + (uint64_t)((kk * 2 * TC_A_KSTRIDE) >> 4), x_desc + (uint64_t)((kk * 2 * x_kstride) >> 4), idesc,
+                tc_mma(tmem_d, a_desc + (uint64_t)(((kk >> 2) * TC_A_HALF + (kk & 3) * 32) >> 4), x_desc + (uint64_t)(((kk >> 2) * x_half + (kk & 3) * 32) >> 4), idesc,
                        (it > 0 || kk > 0) ? 1u : 0u);
             tc_commit(&bar_free[u]);
             tc_commit(&bar_xfree[xstage]);
@@ -268,7 +277,8 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
                 break; // the issuing thread then gives up on this stage's barrier and reports too
             }
             mbar_arrive_expect_tx(&bar_x[xs], x_stage_bytes);
-            tc_tma_x(smem_u32(x_smem + (size_t)xs * x_stage_bytes), p.tmap_x, grp * 16, &bar_x[xs]);
+            tc_tma_x(smem_u32(x_smem + (size_t)xs * x_stage_bytes), p.tmap_x, grp * 128, &bar_x[xs]);
+            tc_tma_x(smem_u32(x_smem + (size_t)xs * x_stage_bytes + x_half), p.tmap_x, grp * 128 + 64, &bar_x[xs]);
             xs = xs + 1 == TC_X_STAGES ? 0 : xs + 1;
         }
     }

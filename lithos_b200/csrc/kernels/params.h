@@ -123,7 +123,7 @@ typedef struct {
 
 /* ---- batched int4 projection: Y[B,N] = X[B,K] W ------------------------- */
 typedef struct {
-    /* gemm_int4_tc: CUtensorMap over X viewed as [K/8 chunks][B tokens][8] fp16, box 16 x NT x 8 */
+    /* gemm_int4_tc: CUtensorMap over X [B, K] fp16, box 64 k x NT tokens, 128-byte swizzle */
     unsigned char tmap_x[128] __attribute__((aligned(64)));
     const uint32_t* qweight; /* [K/8, N] */
     const uint16_t* scales;  /* fp16 [K/128, N] */
