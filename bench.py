@@ -510,9 +510,9 @@ def bench_batched(args, local):
             dev.append([ctx.to_device(lb.fill_u32(K // 8 * N, 300 + s_, 1)), ctx.to_device(lb.fill_scales_f16(K // 128 * N, 300 + s_, 2)),
                         ctx.to_device(lb.fill_u32(K // 128 * (N // 8), 300 + s_, 3))])
         wbytes = K // 8 * N * 4 + K // 128 * N * 2 + K // 128 * (N // 8) * 4
-        d_x = ctx.to_device(lb.fill_normal(64 * K, 300, 4, dtype="f16"))
-        d_y = ctx.alloc(64 * N * 4)
-        for B, flag in [(B, f) for B in batches for f in ((lb.GEMM_TCGEN05, lb.GEMM_MMA_SYNC) if B > 8 else (0, lb.GEMM_MMA_SYNC) if B == 1 else (0,))]:
+        d_x = ctx.to_device(lb.fill_normal(128 * K, 300, 4, dtype="f16"))
+        d_y = ctx.alloc(128 * N * 4)
+        for B, flag in [(B, f) for B in batches for f in ((lb.GEMM_TCGEN05,) if B > 64 else (lb.GEMM_TCGEN05, lb.GEMM_MMA_SYNC) if B > 8 else (0, lb.GEMM_MMA_SYNC) if B == 1 else (0,))]:
             ctx.begin_capture()
             for j in range(reps):
                 w = dev[j % sets]
@@ -569,7 +569,7 @@ def main():
                          "mixers as persistent gemv_chain launches alone (the small case used for ncu captures)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: number of layers (64 = the benchmark definition)")
     ap.add_argument("--batched-shapes", default="", help="batched workload: comma-separated substrings of the shape names to run (default all)")
-    ap.add_argument("--batched-batches", default="1,4,16,32,64", help="batched workload: batch sizes")
+    ap.add_argument("--batched-batches", default="1,4,16,32,64,128", help="batched workload: batch sizes")
     ap.add_argument("--seed", type=int, default=20260413)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-chain", action="store_true", help="decode workload: one launch per projection instead of persistent chains")

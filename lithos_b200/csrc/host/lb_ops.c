@@ -205,8 +205,9 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
                         int B, int flags) {
     if (!c || !qweight || !scales || !x || !y || K <= 0 || N <= 0 || K % 128 || N % 16 || B < 1 || B > LB_GEMM_MAX_BATCH ||
         (flags & ~(LB_GEMV_Y_F32 | LB_GEMM_MMA_SYNC | LB_GEMM_TCGEN05)) ||
-        ((flags & LB_GEMM_MMA_SYNC) && (flags & LB_GEMM_TCGEN05)) || ((flags & LB_GEMM_TCGEN05) && B <= 8))
-        return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: bad argument (K %% 128, N %% 16, 1 <= B <= %d, flags LB_GEMV_Y_F32, LB_GEMM_MMA_SYNC or LB_GEMM_TCGEN05 (9 tokens or more))",
+        ((flags & LB_GEMM_MMA_SYNC) && (flags & LB_GEMM_TCGEN05)) || ((flags & LB_GEMM_TCGEN05) && B <= 8) ||
+        ((flags & LB_GEMM_MMA_SYNC) && B > 64))
+        return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: bad argument (K %% 128, N %% 16, 1 <= B <= %d, flags LB_GEMV_Y_F32, LB_GEMM_MMA_SYNC (up to 64 tokens) or LB_GEMM_TCGEN05 (9 tokens or more))",
                        LB_GEMM_MAX_BATCH);
     lb_bgemm_params p;
     memset(&p, 0, sizeof p);
@@ -220,8 +221,8 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
     const int blocks = (N + 127) / 128, groups = K / 128;
     void* params[] = {&p};
     if ((B > 32 && !(flags & LB_GEMM_MMA_SYNC)) || (flags & LB_GEMM_TCGEN05)) {
-        const int nt = B > 32 ? 64 : B > 16 ? 32 : 16;
-        const unsigned smem = (unsigned)(3 * 32768 + 5 * nt * 256); /* three weight stages + five activation stages */
+        const int nt = B > 64 ? 128 : B > 32 ? 64 : B > 16 ? 32 : 16;
+        const unsigned smem = (unsigned)(3 * 32768 + (nt > 64 ? 3 : 5) * nt * 256); /* three weight stages + five (three) activation stages */
         if (x & 15) return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: x must be 16-byte aligned");
         CUtensorMap tm; /* X [B, K] fp16, box = 64 k (128 bytes) x NT tokens, laid down with the 128-byte swizzle */
         cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)B};

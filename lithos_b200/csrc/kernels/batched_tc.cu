@@ -1,4 +1,4 @@
-// Batched int4 projection on the 5th-generation tensor cores (tcgen05 + TMEM) for 9..64 tokens on sm_100a:
+// Batched int4 projection on the 5th-generation tensor cores (tcgen05 + TMEM) for 9..128 tokens on sm_100a:
 // Y[b][n] = sum_k W(k,n) X[b][k], W in the GPTQ buffers of the batch-1 GEMV (qweight [K/8,N], scales fp16
 // [K/128,N], qzeros [K/128,N/8] or NULL = zero-point 8; inference/gemv.ls:44-130), X fp16 [B,K],
 // Y fp32 or fp16 [B,N].  The reference's batched kernel is kernels/projection_gemm.sass:390-631
@@ -35,7 +35,7 @@
 #define TC_STAGES 3
 #define TC_RING 3 // K-groups of packed words a thread keeps in registers ahead of its conversion (a multiple of TC_STAGES)
 #define TC_PSTRIDE 132                 // floats per row of the partial tile
-#define TC_TMEM_COLS 64
+#define TC_TMEM_COLS 128
 
 __device__ __forceinline__ uint32_t tc_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ void tc_cluster_sync() {
@@ -147,7 +147,8 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
     __shared__ __align__(8) uint64_t bar_done;
     __shared__ uint32_t tmem_base_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int NT = p.B > 32 ? 64 : p.B > 16 ? 32 : 16; // tokens the product carries (rows past B are zero)
+    const int NT = p.B > 64 ? 128 : p.B > 32 ? 64 : p.B > 16 ? 32 : 16; // tokens the product carries (rows past B are zero)
+    const int xstages = NT > 64 ? 3 : TC_X_STAGES;                       // activation stages that fit beside the weight stages
     const uint32_t x_stage_bytes = (uint32_t)NT * 256u, x_half = (uint32_t)NT * 128u; // a 64-k half: NT rows of 128 bytes
     unsigned char* a_smem = tc_smem;                          // [TC_STAGES][TC_A_STAGE]
     unsigned char* x_smem = tc_smem + TC_STAGES * TC_A_STAGE; // [TC_X_STAGES][NT * 256]
@@ -251,7 +252,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
         int it = 0, xstage = 0;
         for (int grp = g_begin; grp < g_end; ++grp, ++it) {
             const int u = it % TC_STAGES;
-            if (!tc_wait(&bar_full[u], (uint32_t)((it / TC_STAGES) & 1)) || !tc_wait(&bar_x[xstage], (uint32_t)((it / TC_X_STAGES) & 1))) {
+            if (!tc_wait(&bar_full[u], (uint32_t)((it / TC_STAGES) & 1)) || !tc_wait(&bar_x[xstage], (uint32_t)((it / xstages) & 1))) {
                 failed = true;
                 if (p.status) atomicExch(p.status, TC_FAIL_FULL);
                 break;
@@ -265,21 +266,21 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
                        (it > 0 || kk > 0) ? 1u : 0u);
             tc_commit(&bar_free[u]);
             tc_commit(&bar_xfree[xstage]);
-            xstage = xstage + 1 == TC_X_STAGES ? 0 : xstage + 1;
+            xstage = xstage + 1 == xstages ? 0 : xstage + 1;
         }
         tc_commit(&bar_done); // fires when every product issued above is done
     } else if (warp == TC_DQ_THREADS / 32 + 1 && lane == 0) {
         // ---------------- activation thread: one tiled TMA load per K-group, up to five groups ahead ----------------
         int j = 0, xs = 0;
         for (int grp = g_begin; grp < g_end; ++grp, ++j) {
-            if (j >= TC_X_STAGES && !tc_wait(&bar_xfree[xs], (uint32_t)((j / TC_X_STAGES - 1) & 1))) {
+            if (j >= xstages && !tc_wait(&bar_xfree[xs], (uint32_t)((j / xstages - 1) & 1))) {
                 if (p.status) atomicExch(p.status, TC_FAIL_FREE);
                 break; // the issuing thread then gives up on this stage's barrier and reports too
             }
             mbar_arrive_expect_tx(&bar_x[xs], x_stage_bytes);
             tc_tma_x(smem_u32(x_smem + (size_t)xs * x_stage_bytes), p.tmap_x, grp * 128, &bar_x[xs]);
             tc_tma_x(smem_u32(x_smem + (size_t)xs * x_stage_bytes + x_half), p.tmap_x, grp * 128 + 64, &bar_x[xs]);
-            xs = xs + 1 == TC_X_STAGES ? 0 : xs + 1;
+            xs = xs + 1 == xstages ? 0 : xs + 1;
         }
     }
     pdl_launch_dependents();

@@ -48,9 +48,9 @@ def test_rows_match_oracle(ctx, lb, K, N, zeros, path):
     qw, sc, qz, _ = gptq_case(K, N, seed=K + N, zeros=zeros)
     d_qw, d_sc = ctx.to_device(qw), ctx.to_device(sc)
     d_qz = ctx.to_device(qz) if zeros else None
-    X = batch_x(K, 64, seed=N)
+    X = batch_x(K, 128, seed=N)
     ref = np.stack([orc.gptq_gemv(qw, sc, qz, X[b], K, N)[0] for b in range(8)])
-    for B in (1, 3, 4, 8, 16, 17, 33, 64):
+    for B in (1, 3, 4, 8, 16, 17, 33, 64) + ((100, 128) if path == "tcgen05" else ()):  # more than 64 tokens: tcgen05 only
         extra = force if B > 8 else 0  # up to 8 tokens there is only the mma.sync kernel
         y = run_gemm(ctx, lb, d_qw, d_sc, d_qz, X[:B], K, N, extra=extra)
         assert np.isfinite(y).all()
@@ -130,9 +130,11 @@ def test_runs_inside_a_graph(ctx, lb):
 
 def test_bad_arguments_are_rejected(ctx, lb):
     d = ctx.alloc(1 << 16)
-    for K, N, B in ((100, 128, 4), (128, 24, 4), (128, 128, 0), (128, 128, 65)):
+    for K, N, B in ((100, 128, 4), (128, 24, 4), (128, 128, 0), (128, 128, 129)):
         with pytest.raises(lb_mod.LithosError):
             ctx.gemm_int4(d, d, None, d, d, K, N, B, lb.GEMV_Y_F32)
+    with pytest.raises(lb_mod.LithosError):
+        ctx.gemm_int4(d, d, None, d, d, 128, 128, 65, lb.GEMM_MMA_SYNC)   # the mma.sync kernels stop at 64 tokens
     for flags in (lb.GEMV_Y_ACCUM, lb.GEMM_TCGEN05, lb.GEMM_TCGEN05 | lb.GEMM_MMA_SYNC):  # tcgen05 needs 9 tokens or more
         with pytest.raises(lb_mod.LithosError):
             ctx.gemm_int4(d, d, None, d, d, 128, 128, 4, flags)
