@@ -222,7 +222,7 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
     void* params[] = {&p};
     if ((B > 32 && !(flags & LB_GEMM_MMA_SYNC)) || (flags & LB_GEMM_TCGEN05)) {
         const int nt = B > 64 ? 128 : B > 32 ? 64 : B > 16 ? 32 : 16;
-        const unsigned smem = (unsigned)(3 * 32768 + (nt > 64 ? 3 : 5) * nt * 256); /* three weight stages + five (three) activation stages */
+        const unsigned smem = (unsigned)(4 * 32768 + (nt > 64 ? 3 : nt > 32 ? 5 : nt > 16 ? 10 : 16) * nt * 256); /* four weight stages + 3..16 activation stages */
         if (x & 15) return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: x must be 16-byte aligned");
         CUtensorMap tm; /* X [B, K] fp16, box = 64 k (128 bytes) x NT tokens, laid down with the 128-byte swizzle */
         cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)B};

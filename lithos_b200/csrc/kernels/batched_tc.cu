@@ -7,18 +7,19 @@
 //
 // One CTA = 128 output columns x one K slice: 16 dequantising warps, one issuing thread, one activation thread.
 // Per K-group (128 k):
-//   * every dequantising thread converts 4 packed words of one column (prefetched three groups earlier): a packed
+//   * every dequantising thread converts 4 packed words of one column (prefetched four groups earlier): a packed
 //     word is 8 consecutive k of one column, so its eight fp16 values (q - z) * s - q - z exact through the 0x6400
 //     exponent trick, then one fp16 multiply: the weight the reference kernel multiplies - are one 16-byte
 //     shared-memory store into the K-major operand tile with the 128-byte swizzle: two halves of 64 k, a row of
 //     128 bytes per column, 16-byte slot (chunk % 8) ^ (column % 8) inside the row;
 //   * the activations of the group arrive by two tiled TMA loads (64 k x NT tokens each, 128-byte swizzle by the
-//     copy engine, tokens past the batch zero-filled), three groups ahead, in the same layout with tokens as rows;
+//     copy engine, tokens past the batch zero-filled), as many groups ahead as activation stages fit (3..16), in the
+//     same layout with tokens as rows; warp 0 checks their arrival before it signs the stage as full;
 //   * each warp fences its stores for the async proxy and arrives on the stage's "full" mbarrier; the issuing
-//     thread waits for it and for the TMA barrier, issues the eight tcgen05.mma (k = 16 each: the descriptor's
+//     thread waits for it, issues the eight tcgen05.mma (k = 16 each: the descriptor's
 //     start address steps 32 bytes inside the swizzle atom) of the group and commits them to the "free" mbarriers
 //     of the weight stage and of the activation stage, which the dequantising warps and the activation thread wait
-//     for before they refill them.  No CTA-wide barrier inside the loop: the warps drift apart by up to three stages.
+//     for before they refill them.  No CTA-wide barrier inside the loop: the warps drift apart by up to four stages.
 // (With unswizzled core-matrix tiles the same products took ~170 cycles each and bounded the loop together with
 // the conversion; with the swizzled tiles 64 tokens cost what 16 do.)
 // Epilogue: warps 0-3 read the accumulator (lane = column, TMEM column = token) with tcgen05.ld into the
@@ -32,8 +33,8 @@
 #define TC_DQ_THREADS 512                // dequantising threads (16 warps)
 #define TC_WORDS (16 * TC_COLS / TC_DQ_THREADS) // packed words (of one column) a thread converts per K-group
 #define TC_THREADS (TC_DQ_THREADS + 64)   // + one warp whose lane 0 issues the products + one whose lane 0 brings the activations
-#define TC_STAGES 3
-#define TC_RING 3 // K-groups of packed words a thread keeps in registers ahead of its conversion (a multiple of TC_STAGES)
+#define TC_STAGES 4
+#define TC_RING 4 // K-groups of packed words a thread keeps in registers ahead of its conversion (a multiple of TC_STAGES)
 #define TC_PSTRIDE 132                 // floats per row of the partial tile
 #define TC_TMEM_COLS 128
 
@@ -133,7 +134,7 @@ struct tc_group { // a thread's share of one K-group: TC_WORDS consecutive packe
 #define TC_SBO 1024                    // bytes between groups of 8 rows: 8 rows of 128 bytes (one 128-byte swizzle atom)
 #define TC_A_HALF (TC_COLS * 128)      // one 64-k half of the weight tile: 128 rows of 128 bytes
 #define TC_A_STAGE (2 * TC_A_HALF)     // one K-group of dequantised weights: 32 KB
-#define TC_X_STAGES 5                  // activation ring: a stage is refilled three groups after its products were issued
+#define TC_X_STAGES 16                  // most activation stages (16 tokens); fewer for more tokens, see xstages
 #define TC_FAIL_FREE 0x1101u           // status: a stage's products never completed
 #define TC_FAIL_DONE 0x1102u           // status: the last products never completed
 #define TC_FAIL_FULL 0x1103u           // status: a stage was never filled
@@ -148,7 +149,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
     __shared__ uint32_t tmem_base_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NT = p.B > 64 ? 128 : p.B > 32 ? 64 : p.B > 16 ? 32 : 16; // tokens the product carries (rows past B are zero)
-    const int xstages = NT > 64 ? 3 : TC_X_STAGES;                       // activation stages that fit beside the weight stages
+    const int xstages = NT > 64 ? 3 : NT > 32 ? 5 : NT > 16 ? 10 : TC_X_STAGES; // activation stages that fit beside the weight stages
     const uint32_t x_stage_bytes = (uint32_t)NT * 256u, x_half = (uint32_t)NT * 128u; // a 64-k half: NT rows of 128 bytes
     unsigned char* a_smem = tc_smem;                          // [TC_STAGES][TC_A_STAGE]
     unsigned char* x_smem = tc_smem + TC_STAGES * TC_A_STAGE; // [TC_X_STAGES][NT * 256]
@@ -209,7 +210,8 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
         // chunk c (k = 8c..8c+7) of column nl: half c / 8, row nl, 16-byte slot (c % 8) ^ (nl % 8) of the row (128-byte swizzle)
         const uint32_t a_row = (uint32_t)(nl * 128), a_xor = (uint32_t)(nl & 7);
         const int zshift = 4 * (n & 7);
-        int it = 0;
+        int it = 0, xs_c = 0;
+        uint32_t xs_ph = 0u;
         for (int base = g_begin; base < g_end && !failed; base += TC_RING) {
 #pragma unroll
             for (int u = 0; u < TC_RING; ++u) {
@@ -241,7 +243,14 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
                     }
                     fence_proxy_async_smem(); // generic-proxy stores before the tensor core reads them
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_full[st]);
+                    if (lane == 0) {
+                        // warp 0 also vouches for the activations of this K-group, so that the issuing thread polls one barrier only
+                        if (warp == 0 && !tc_wait(&bar_x[xs_c], xs_ph)) {
+                            if (p.status) atomicExch(p.status, TC_FAIL_FULL);
+                        }
+                        mbar_arrive(&bar_full[st]);
+                    }
+                    if (++xs_c == xstages) { xs_c = 0; xs_ph ^= 1u; }
                     ++it;
                 }
             }
@@ -252,7 +261,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
         int it = 0, xstage = 0;
         for (int grp = g_begin; grp < g_end; ++grp, ++it) {
             const int u = it % TC_STAGES;
-            if (!tc_wait(&bar_full[u], (uint32_t)((it / TC_STAGES) & 1)) || !tc_wait(&bar_x[xstage], (uint32_t)((it / xstages) & 1))) {
+            if (!tc_wait(&bar_full[u], (uint32_t)((it / TC_STAGES) & 1))) { // weights stored, activations landed (warp 0 checked)
                 failed = true;
                 if (p.status) atomicExch(p.status, TC_FAIL_FULL);
                 break;
@@ -270,7 +279,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
         }
         tc_commit(&bar_done); // fires when every product issued above is done
     } else if (warp == TC_DQ_THREADS / 32 + 1 && lane == 0) {
-        // ---------------- activation thread: one tiled TMA load per K-group, up to five groups ahead ----------------
+        // ---------------- activation thread: two tiled TMA loads per K-group, up to xstages groups ahead ----------------
         int j = 0, xs = 0;
         for (int grp = g_begin; grp < g_end; ++grp, ++j) {
             if (j >= xstages && !tc_wait(&bar_xfree[xs], (uint32_t)((j / xstages - 1) & 1))) {
