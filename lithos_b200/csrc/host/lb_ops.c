@@ -237,7 +237,7 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
         if (ksplit > 8) ksplit = 8;
         while (ksplit > 1 && groups / ksplit < 4) ksplit--;
         if (ksplit < 1) ksplit = 1;
-        return lb_launch_cluster(c, LBK_gemm_int4_tc, (unsigned)blocks, (unsigned)ksplit, 1, 576, smem, params, 1, (unsigned)ksplit);
+        return lb_launch_cluster(c, nt > 64 ? LBK_gemm_int4_tc_g1 : LBK_gemm_int4_tc, (unsigned)blocks, (unsigned)ksplit, 1, 576, smem, params, 1, (unsigned)ksplit);
     }
     const int rows = B > 32 ? 64 : B > 16 ? 32 : B > 8 ? 16 : 8; /* token rows the CTA stages */
     const int kernel = B > 32 ? LBK_gemm_int4_mma_b64 : B > 16 ? LBK_gemm_int4_mma_b32 : B > 8 ? LBK_gemm_int4_mma_b16 : LBK_gemm_int4_mma_b8;

@@ -139,8 +139,8 @@ struct tc_group { // a thread's share of one K-group: TC_WORDS consecutive packe
 #define TC_FAIL_DONE 0x1102u           // status: the last products never completed
 #define TC_FAIL_FULL 0x1103u           // status: a stage was never filled
 
-extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const __grid_constant__ lb_bgemm_params p) {
-    extern __shared__ __align__(1024) unsigned char tc_smem[];
+template <int G> // K-groups per hand-off between the converting warps and the issuing thread (1 or 2)
+__device__ __forceinline__ void gemm_int4_tc_body(const lb_bgemm_params& p, unsigned char* tc_smem) {
     __shared__ __align__(8) uint64_t bar_free[TC_STAGES]; // a stage's products are done (tcgen05.commit)
     __shared__ __align__(8) uint64_t bar_full[TC_STAGES]; // a stage's weights are in place (one arrival per dequantising warp)
     __shared__ __align__(8) uint64_t bar_x[TC_X_STAGES];  // an activation stage has landed (TMA transaction bytes)
@@ -159,7 +159,7 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
 
     if (tid == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(&bar_free[s], 1);
+            mbar_init(&bar_free[s], 1);                    // (one per stage pair is used)
             mbar_init(&bar_full[s], TC_DQ_THREADS / 32);
         }
         for (int s = 0; s < TC_X_STAGES; ++s) {
@@ -210,72 +210,90 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
         // chunk c (k = 8c..8c+7) of column nl: half c / 8, row nl, 16-byte slot (c % 8) ^ (nl % 8) of the row (128-byte swizzle)
         const uint32_t a_row = (uint32_t)(nl * 128), a_xor = (uint32_t)(nl & 7);
         const int zshift = 4 * (n & 7);
-        int it = 0, xs_c = 0;
+        // K-groups are handed over G at a time (G weight stages share one "full" and one "free" barrier): every hand-off is a
+        // shared-memory round trip behind the stores, so fewer of them is what counts; G = 2 unless only three activation
+        // stages fit (128 tokens), where a hand-off of two would leave the activation thread one stage to work ahead
+        int pit = 0, xs_c = 0;
         uint32_t xs_ph = 0u;
         for (int base = g_begin; base < g_end && !failed; base += TC_RING) {
 #pragma unroll
-            for (int u = 0; u < TC_RING; ++u) {
-                const int grp = base + u, st = u % TC_STAGES; // TC_RING is a multiple of TC_STAGES
-
-                if (grp < g_end && !failed) {
-                    const tc_group cur = ring[u];
-                    if (live && grp + TC_RING < g_end) load_group(ring[u]);
-                    const uint32_t z = (cur.zw >> zshift) & 0xFu;
-                    const __half2 add = tc_bits_h2((0xE400u + z) | ((0xD400u + (z << 4)) << 16)); // (-(1024 + z), -(64 + z))
-                    const __half2 sc = tc_bits_h2((cur.s & 0xFFFFu) * 0x10001u);
-                    uint4 v[TC_WORDS];
+            for (int up = 0; up < TC_RING / G; ++up) { // TC_RING / G == TC_STAGES / G hand-off slots
+                const int g0 = base + G * up;
+                if (g0 < g_end && !failed) {
+                    const int cnt = g_end - g0 < G ? g_end - g0 : G; // K-groups in this hand-off
+                    uint4 v[G][TC_WORDS];
 #pragma unroll
-                    for (int j = 0; j < TC_WORDS; ++j) // a packed row = the 8 k of one core-matrix row
-                        v[j] = make_uint4(tc_pair<0>(cur.w[j], mul, add, sc), tc_pair<1>(cur.w[j], mul, add, sc), tc_pair<2>(cur.w[j], mul, add, sc),
-                                          tc_pair<3>(cur.w[j], mul, add, sc));
-                    // stage st held K-group grp - 3: wait until its products are done
-                    // (lane 0 polls for its warp: 16 pollers per barrier instead of 512; the vote orders the others behind it)
-                    if (it >= TC_STAGES && lane == 0 && !tc_wait(&bar_free[st], (uint32_t)((it / TC_STAGES - 1) & 1))) {
+                    for (int h = 0; h < G; ++h) {
+                        const tc_group cur = ring[G * up + h];
+                        if (live && g0 + h + TC_RING < g_end) load_group(ring[G * up + h]);
+                        const uint32_t z = (cur.zw >> zshift) & 0xFu;
+                        const __half2 add = tc_bits_h2((0xE400u + z) | ((0xD400u + (z << 4)) << 16)); // (-(1024 + z), -(64 + z))
+                        const __half2 sc = tc_bits_h2((cur.s & 0xFFFFu) * 0x10001u);
+#pragma unroll
+                        for (int j = 0; j < TC_WORDS; ++j) // a packed row = the 8 k of one core-matrix row
+                            v[h][j] = make_uint4(tc_pair<0>(cur.w[j], mul, add, sc), tc_pair<1>(cur.w[j], mul, add, sc), tc_pair<2>(cur.w[j], mul, add, sc),
+                                                 tc_pair<3>(cur.w[j], mul, add, sc));
+                    }
+                    // these stages held the K-groups four back: wait until their products are done
+                    // (lane 0 polls for its warp; the vote orders the others behind it)
+                    if (pit >= TC_STAGES / G && lane == 0 && !tc_wait(&bar_free[up], (uint32_t)((pit / (TC_STAGES / G) - 1) & 1))) {
                         failed = true;
                         if (p.status) atomicExch(p.status, TC_FAIL_FREE);
                     }
                     failed = __any_sync(0xffffffffu, failed); // the warp goes on, or leaves the loop, together
-                    unsigned char* a_stage = a_smem + st * TC_A_STAGE + a_row;
 #pragma unroll
-                    for (int j = 0; j < TC_WORDS; ++j) {
-                        const uint32_t c = (uint32_t)(TC_WORDS * rq + j);
-                        *reinterpret_cast<uint4*>(a_stage + (c >> 3) * TC_A_HALF + (((c & 7) ^ a_xor) << 4)) = v[j];
+                    for (int h = 0; h < G; ++h) {
+                        unsigned char* a_stage = a_smem + (G * up + h) * TC_A_STAGE + a_row;
+#pragma unroll
+                        for (int j = 0; j < TC_WORDS; ++j) {
+                            const uint32_t c = (uint32_t)(TC_WORDS * rq + j);
+                            if (h < cnt) *reinterpret_cast<uint4*>(a_stage + (c >> 3) * TC_A_HALF + (((c & 7) ^ a_xor) << 4)) = v[h][j];
+                        }
                     }
                     fence_proxy_async_smem(); // generic-proxy stores before the tensor core reads them
                     __syncwarp();
                     if (lane == 0) {
-                        // warp 0 also vouches for the activations of this K-group, so that the issuing thread polls one barrier only
-                        if (warp == 0 && !tc_wait(&bar_x[xs_c], xs_ph)) {
-                            if (p.status) atomicExch(p.status, TC_FAIL_FULL);
+                        // warp 0 also vouches for the activations of these K-groups, so that the issuing thread polls one barrier only
+                        if (warp == 0) {
+                            bool okx = tc_wait(&bar_x[xs_c], xs_ph);
+                            if (cnt > 1) {
+                                const int xn = xs_c + 1 == xstages ? 0 : xs_c + 1;
+                                okx = okx && tc_wait(&bar_x[xn], xn == 0 ? xs_ph ^ 1u : xs_ph);
+                            }
+                            if (!okx && p.status) atomicExch(p.status, TC_FAIL_FULL);
                         }
-                        mbar_arrive(&bar_full[st]);
+                        mbar_arrive(&bar_full[up]);
                     }
-                    if (++xs_c == xstages) { xs_c = 0; xs_ph ^= 1u; }
-                    ++it;
+                    for (int h = 0; h < cnt; ++h)
+                        if (++xs_c == xstages) { xs_c = 0; xs_ph ^= 1u; }
+                    ++pit;
                 }
             }
         }
     } else if (warp == TC_DQ_THREADS / 32 && lane == 0) {
         // ---------------- issuing thread: eight products per K-group as soon as its weights and activations are in place ----------------
         const uint64_t a_desc0 = tc_smem_desc(smem_u32(a_smem), 16, TC_SBO), x_desc0 = tc_smem_desc(smem_u32(x_smem), 16, TC_SBO);
-        int it = 0, xstage = 0;
-        for (int grp = g_begin; grp < g_end; ++grp, ++it) {
-            const int u = it % TC_STAGES;
-            if (!tc_wait(&bar_full[u], (uint32_t)((it / TC_STAGES) & 1))) { // weights stored, activations landed (warp 0 checked)
+        int pit = 0, xstage = 0;
+        for (int g0 = g_begin; g0 < g_end; g0 += G, ++pit) {
+            const int up = pit % (TC_STAGES / G);
+            const int cnt = g_end - g0 < G ? g_end - g0 : G;
+            if (!tc_wait(&bar_full[up], (uint32_t)((pit / (TC_STAGES / G)) & 1))) { // weights stored, activations landed (warp 0 checked)
                 failed = true;
                 if (p.status) atomicExch(p.status, TC_FAIL_FULL);
                 break;
             }
             tc_fence_after();
-            // descriptors: the start-address field counts 16-byte units
-            const uint64_t a_desc = a_desc0 + (uint64_t)((u * TC_A_STAGE) >> 4), x_desc = x_desc0 + (uint64_t)((xstage * x_stage_bytes) >> 4);
+            for (int h = 0; h < cnt; ++h) {
+                // descriptors: the start-address field counts 16-byte units
+                const uint64_t a_desc = a_desc0 + (uint64_t)(((G * up + h) * TC_A_STAGE) >> 4), x_desc = x_desc0 + (uint64_t)((xstage * x_stage_bytes) >> 4);
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk) // k = 16 kk .. + 15: two k chunks
-                tc_mma(tmem_d, a_desc + (uint64_t)(((kk >> 2) * TC_A_HALF + (kk & 3) * 32) >> 4), x_desc + (uint64_t)(((kk >> 2) * x_half + (kk & 3) * 32) >> 4), idesc,
-                       (it > 0 || kk > 0) ? 1u : 0u);
-            tc_commit(&bar_free[u]);
-            tc_commit(&bar_xfree[xstage]);
-            xstage = xstage + 1 == xstages ? 0 : xstage + 1;
+                for (int kk = 0; kk < 8; ++kk) // k = 16 kk .. + 15: two k chunks
+                    tc_mma(tmem_d, a_desc + (uint64_t)(((kk >> 2) * TC_A_HALF + (kk & 3) * 32) >> 4), x_desc + (uint64_t)(((kk >> 2) * x_half + (kk & 3) * 32) >> 4), idesc,
+                           (pit > 0 || h > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(&bar_xfree[xstage]);
+                xstage = xstage + 1 == xstages ? 0 : xstage + 1;
+            }
+            tc_commit(&bar_free[up]);
         }
         tc_commit(&bar_done); // fires when every product issued above is done
     } else if (warp == TC_DQ_THREADS / 32 + 1 && lane == 0) {
@@ -327,4 +345,13 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const _
     if (KS > 1) tc_cluster_sync(); // nobody leaves while a neighbour still reads its tile
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_d, TC_TMEM_COLS);
+}
+
+extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc(const __grid_constant__ lb_bgemm_params p) { // up to 64 tokens
+    extern __shared__ __align__(1024) unsigned char tc_smem[];
+    gemm_int4_tc_body<2>(p, tc_smem);
+}
+extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc_g1(const __grid_constant__ lb_bgemm_params p) { // 65..128 tokens
+    extern __shared__ __align__(1024) unsigned char tc_smem[];
+    gemm_int4_tc_body<1>(p, tc_smem);
 }
