@@ -184,6 +184,34 @@ class Model:
         self._xfer(p + offset_bytes, out, False)
         return out
 
+    def seed_state(self, ctx_len: int, seed: int):
+        """Stand-in for a prompt of ctx_len tokens (the checkpoint and prompt of the reference's measurement are not
+        distributable): ONE global seeded state, of which this shard takes its heads.  KV rows [0, ctx_len) bf16
+        N(0,1) (streams 100000+l, 200000+l), DeltaNet state fp32 N(0,0.02) (300000+l), the three previous tokens'
+        pre-convolution values fp32 N(0,1) (400000+l; row t = position ctx_len-1-t)."""
+        cfg, R, T = self.cfg, self.tp_rank, self.tp_size
+        HV, HK = cfg.dn_v_heads // T, cfg.dn_k_heads // T
+        HKV = cfg.fa_kv_heads // T if cfg.fa_kv_heads >= T else 1
+        kv0 = R * HKV if cfg.fa_kv_heads >= T else (R * cfg.fa_kv_heads) // T
+        QKf, Cf = cfg.dn_k_heads * 128, cfg.conv_channels
+        QK, V = HK * 128, HV * 128
+        chan = np.concatenate([np.arange(R * QK, (R + 1) * QK), QKf + np.arange(R * QK, (R + 1) * QK),
+                               2 * QKf + np.arange(R * V, (R + 1) * V)])
+        for l in range(cfg.n_layers):
+            if cfg.is_fa(l):
+                n = ctx_len * cfg.fa_kv_heads * 256
+                for which, stream in ((0, 100000 + l), (1, 200000 + l)):
+                    rows = fill_normal(n, seed, stream, dtype="bf16").reshape(ctx_len, cfg.fa_kv_heads, 256)
+                    self.set_state(l, which, np.ascontiguousarray(rows[:, kv0:kv0 + HKV]))
+            else:
+                st = fill_normal(cfg.dn_v_heads * 128 * 128, seed, 300000 + l, std=0.02).reshape(cfg.dn_v_heads, 128, 128)
+                self.set_state(l, 0, np.ascontiguousarray(st[R * HV:(R + 1) * HV]))
+                hist = fill_normal(3 * Cf, seed, 400000 + l).reshape(3, Cf)
+                ring = np.zeros((4, chan.size), np.float32)
+                for t in range(3):
+                    ring[(ctx_len - 1 - t) & 3] = hist[t, chan]
+                self.set_state(l, 1, ring)
+
     def logits(self) -> np.ndarray:
         p = C.c_uint64(0)
         self.ctx._check(lib().lb_model_logits_ptr(self.h, C.byref(p)))

@@ -6,12 +6,19 @@
  *
  * PARITY STATUS: the reference ships no golden vectors, known-answer tests or
  * runnable CPU implementation for these kernels (its interpreters evaluate the
- * integer host dialect only), so this restatement is pinned by
- *   (1) hand-derived known-answer cases in tests/golden/,
- *   (2) for the int4 GEMV only: the reference's own PTX (minds/gptq_gemv_*.ptx,
+ * integer host dialect only).  This restatement is pinned by
+ *   (1) the int4 GEMV: the reference's own PTX (minds/gptq_gemv_*.ptx,
  *       assembled unmodified for sm_100a into oracle/_ref/) run on the same
- *       buffers on the GPU box.
- * For every other kernel: parity unpinned by reference tests.
+ *       buffers on the GPU box, bit for bit;
+ *   (2) decay gate, sigmoid gate, SiLU and the other element-wise kernels, conv1d,
+ *       the fused DeltaNet step, delta_update and RoPE: a fixture computed from the
+ *       reference's own .ls kernel text, parsed by the reference's bootstrap-py
+ *       parser and evaluated statement by statement (tests/golden/make_ls_golden.py
+ *       -> tests/golden/ls_kat.npz, checked by tests/test_oracle_ls_pin.py);
+ *   (3) hand-derived float64 known-answer cases in tests/golden/kat_small.npz.
+ * Still parity unpinned by anything of the reference's: the shuffle-based norms
+ * (reduce.ls), decode attention (this build's contract deliberately differs from
+ * attend.ls: natural exp, -inf start) and the layer recipe of the whole step.
  *
  * Each function cites the reference lines it restates (paths relative to the
  * reference project root).
@@ -61,6 +68,52 @@ ORC_API int orc_num_threads(void) {
 #else
     return 1;
 #endif
+}
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#endif
+}
+
+/* ------------------------------------------------------------------ */
+/* seeded synthetic tensors                                            */
+/* The benchmark's inputs are drawn from one seed by a counter-based   */
+/* generator: element i of stream s is a pure function of (seed, s, i).*/
+/* The product library has the same generator (lb_fill_*); this is its */
+/* twin, so that the CPU arm of the benchmark and the tests can build  */
+/* their inputs without loading the product.  tests/test_oracle_ls_pin */
+/* checks that both give identical bits.                               */
+/* ------------------------------------------------------------------ */
+static inline uint64_t mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+static inline uint64_t rng_u64(uint64_t seed, uint64_t stream, uint64_t i) {
+    uint64_t h = mix64(seed + 0x9E3779B97F4A7C15ull * (mix64(stream ^ 0xD1342543DE82EF95ull) | 1ull));
+    return mix64(h + 0x9E3779B97F4A7C15ull * (i + 1));
+}
+static inline float u01(uint32_t bits) { return ((float)(bits >> 8) + 0.5f) * (1.0f / 16777216.0f); }
+__attribute__((optimize("fp-contract=off"))) static inline float normal_at(uint64_t seed, uint64_t stream, uint64_t i) {
+    uint64_t r = rng_u64(seed, stream, i);
+    float u1 = u01((uint32_t)(r >> 32)), u2 = u01((uint32_t)r);
+    return sqrtf(-2.0f * logf(u1)) * cosf(6.28318530717958647692f * u2);
+}
+/* kind: 0 u32 words (8 nibbles U{0..15}), 1 fp32 N(a,b), 2 fp16 N(a,b), 3 bf16 N(a,b), 4 fp32 U(a,b),
+ * 5 fp16 group scales |N(0,1)|*0.01 + 1e-3 */
+__attribute__((optimize("fp-contract=off"))) /* the product's generator is compiled without fused multiply-add */
+ORC_API void orc_fill(void* dst, size_t n, uint64_t seed, uint64_t stream, int kind, float a, float b) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) {
+        switch (kind) {
+        case 0: ((uint32_t*)dst)[i] = (uint32_t)(rng_u64(seed, stream, i) >> 32); break;
+        case 1: ((float*)dst)[i] = a + b * normal_at(seed, stream, i); break;
+        case 2: ((uint16_t*)dst)[i] = f2h(a + b * normal_at(seed, stream, i)); break;
+        case 3: ((uint16_t*)dst)[i] = f2b(a + b * normal_at(seed, stream, i)); break;
+        case 4: ((float*)dst)[i] = a + (b - a) * u01((uint32_t)(rng_u64(seed, stream, i) >> 32)); break;
+        default: ((uint16_t*)dst)[i] = f2h(fabsf(normal_at(seed, stream, i)) * 0.01f + 1e-3f); break;
+        }
+    }
 }
 
 /* ------------------------------------------------------------------ */
@@ -255,14 +308,20 @@ ORC_API void orc_conv1d_step(const float* x, const float* w, float* hist, float*
  * description models/.../deltanet/unroll.ls "DecayGate ... ln" and the
  * benchmark definition use the natural log, which is what is computed here);
  * beta: inference/recur.ls:45-55 */
-ORC_API void orc_decay_gate(const float* a, const float* a_log, const float* dt_bias, const float* b, float* g,
-                            float* beta, int n) {
+/* text_log2 != 0 evaluates the softplus exactly as the .ls text does (log2(1 + e^t), decay_gate.ls:41-44); that
+ * mode exists so that the fixture computed from the reference's kernel text pins this function. */
+ORC_API void orc_decay_gate_ex(const float* a, const float* a_log, const float* dt_bias, const float* b, float* g,
+                               float* beta, int n, int text_log2) {
     for (int i = 0; i < n; i++) {
         float t = a[i] + dt_bias[i];
-        float sp = t > 20.f ? t : log1pf(expf(t));
+        float sp = text_log2 ? log2f(expf(t) + 1.0f) : (t > 20.f ? t : log1pf(expf(t)));
         g[i] = expf(-expf(a_log[i]) * sp);
         if (b && beta) beta[i] = sigmoidf_(b[i]);
     }
+}
+ORC_API void orc_decay_gate(const float* a, const float* a_log, const float* dt_bias, const float* b, float* g,
+                            float* beta, int n) {
+    orc_decay_gate_ex(a, a_log, dt_bias, b, g, beta, n, 0);
 }
 
 /* One decode step for all value heads (inference/deltanet_fused.ls:97-149).

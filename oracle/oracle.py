@@ -16,11 +16,23 @@ _LIB = _HERE / "liboracle.so"
 REF_DIR = _HERE / "_ref"  # reference PTX assembled for sm_100a (built by the Makefile)
 
 
+def reference_checkout():
+    """The reference tree, when one is mounted: $LITHOS_REF, else a sibling `reference` directory of the repository's
+    parent.  None on machines that only have the prebuilt files."""
+    import os
+    for cand in (os.environ.get("LITHOS_REF"), _HERE.parent.parent / "reference"):
+        if cand and (Path(cand) / "minds").is_dir():
+            return str(cand)
+    return None
+
+
 def build() -> None:
-    targets = ["liboracle.so"]
-    if Path("/root/reference/minds").is_dir():
+    targets, extra = ["liboracle.so"], []
+    ref = reference_checkout()
+    if ref:
         targets.append("ref")
-    r = subprocess.run(["make", "-C", str(_HERE)] + targets, capture_output=True, text=True)
+        extra.append(f"LITHOS_REF={ref}")
+    r = subprocess.run(["make", "-C", str(_HERE)] + targets + extra, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + r.stdout[-2000:] + r.stderr[-2000:])
 
@@ -54,6 +66,35 @@ def _f32(a):
 
 def num_threads() -> int:
     return lib().orc_num_threads()
+
+
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(int(n))
+
+
+# ---- seeded synthetic tensors: the twin of the product's lb_fill_* (same bits) ------------------
+def _fill(n: int, seed: int, stream: int, kind: int, a: float, b: float, dtype) -> np.ndarray:
+    out = np.empty(n, dtype=dtype)
+    lib().orc_fill(_p(out), C.c_size_t(n), C.c_uint64(seed), C.c_uint64(stream), kind, C.c_float(a), C.c_float(b))
+    return out
+
+
+def fill_u32(n, seed, stream):
+    return _fill(n, seed, stream, 0, 0.0, 0.0, np.uint32)
+
+
+def fill_scales_f16(n, seed, stream):
+    return _fill(n, seed, stream, 5, 0.0, 0.0, np.float16)
+
+
+def fill_normal(n, seed, stream, mean=0.0, std=1.0, dtype="f32"):
+    """dtype: 'f32' -> float32, 'f16' -> float16, 'bf16' -> uint16 holding bf16 bits"""
+    kind, dt = {"f32": (1, np.float32), "f16": (2, np.float16), "bf16": (3, np.uint16)}[dtype]
+    return _fill(n, seed, stream, kind, mean, std, dt)
+
+
+def fill_uniform(n, seed, stream, lo, hi):
+    return _fill(n, seed, stream, 4, lo, hi, np.float32)
 
 
 def bf16_to_f32(a: np.ndarray) -> np.ndarray:
@@ -183,11 +224,26 @@ def conv1d_step(x, w, hist):
 
 
 # ---- DeltaNet ------------------------------------------------------------------
-def decay_gate(a, a_log, dt_bias, b):
+def decay_gate(a, a_log, dt_bias, b, text_log2=False):
+    """text_log2: softplus through log2 exactly as inference/decay_gate.ls:41-44 writes it (fixture pin only)"""
     a, a_log, dt_bias, b = _f32(a), _f32(a_log), _f32(dt_bias), _f32(b)
     g, beta = np.empty_like(a), np.empty_like(a)
-    lib().orc_decay_gate(_p(a), _p(a_log), _p(dt_bias), _p(b), _p(g), _p(beta), a.size)
+    lib().orc_decay_gate_ex(_p(a), _p(a_log), _p(dt_bias), _p(b), _p(g), _p(beta), a.size, 1 if text_log2 else 0)
     return g, beta
+
+
+def sigmoid(x):
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().orc_sigmoid(_p(x), _p(y), x.size)
+    return y
+
+
+def silu(x):
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().orc_silu(_p(x), _p(y), x.size)
+    return y
 
 
 def deltanet_step(state, q, k, v, z, g, beta, HV: int, HK: int, d: int = 128):
@@ -299,3 +355,80 @@ class Model:
         if self.h:
             lib().orc_model_destroy(self.h)
             self.h = None
+
+
+# ---- the benchmark's synthetic model, built without the product library -------------------------
+# Twins of lithos_b200.model.qwen35_27b / synthetic_layer_slots / synthetic_globals / Model.seed_state: the same
+# streams of the same generator, so the CPU arm and the GPU arm of the benchmark decode the same model.
+_WS = dict(DN_QKV=0, DN_Z=3, DN_OUT=6, DN_PROJ_A=9, DN_PROJ_B=10, DN_A_LOG=11, DN_DT_BIAS=12, DN_CONV1D=13, DN_NORM=14,
+           FA_Q=0, FA_K=3, FA_V=6, FA_O=9, FA_Q_NORM=12, FA_K_NORM=13, GATE=15, UP=18, DOWN=21, INPUT_NORM=24, POST_NORM=25)
+
+
+def qwen35_27b(max_ctx: int = 4224, n_layers: int = 64) -> ModelCfg:
+    """models/families/qwen/qwen3.5/27b/config.json and src/launcher.s:62-72"""
+    return ModelCfg(n_layers=n_layers, hidden=5120, inter=17408, vocab=248320, dn_k_heads=16, dn_v_heads=48, dn_dim=128,
+                    conv_taps=4, fa_q_heads=24, fa_kv_heads=4, fa_dim=256, rot_dims=64, group=128, fa_period=4,
+                    max_ctx=max_ctx, reserved=0, eps=1e-6, rope_theta=1e7)
+
+
+def cfg_is_fa(cfg, layer: int) -> bool:
+    return layer % cfg.fa_period == cfg.fa_period - 1
+
+
+def synthetic_layer_slots(cfg, seed: int, layer: int):
+    s = [None] * WS_SLOTS
+    base = (layer + 1) * 100
+    H, I = cfg.hidden, cfg.inter
+
+    def q4(slot, K, N):
+        s[slot] = fill_u32(K // 8 * N, seed, base + slot)
+        s[slot + 1] = fill_scales_f16(K // 128 * N, seed, base + slot + 1)
+        s[slot + 2] = fill_u32(K // 128 * (N // 8), seed, base + slot + 2)
+
+    if not cfg_is_fa(cfg, layer):
+        C_, V = (2 * cfg.dn_k_heads + cfg.dn_v_heads) * cfg.dn_dim, cfg.dn_v_heads * 128
+        q4(_WS["DN_QKV"], H, C_)
+        q4(_WS["DN_Z"], H, V)
+        q4(_WS["DN_OUT"], V, H)
+        s[_WS["DN_PROJ_A"]] = fill_normal(cfg.dn_v_heads * H, seed, base + _WS["DN_PROJ_A"], 0.0, 0.02, "bf16")
+        s[_WS["DN_PROJ_B"]] = fill_normal(cfg.dn_v_heads * H, seed, base + _WS["DN_PROJ_B"], 0.0, 0.02, "bf16")
+        s[_WS["DN_A_LOG"]] = fill_uniform(cfg.dn_v_heads, seed, base + _WS["DN_A_LOG"], 0.0, 2.7)
+        s[_WS["DN_DT_BIAS"]] = fill_normal(cfg.dn_v_heads, seed, base + _WS["DN_DT_BIAS"], 0.0, 0.1, "bf16")
+        s[_WS["DN_CONV1D"]] = fill_normal(4 * C_, seed, base + _WS["DN_CONV1D"], 0.0, 0.3, "bf16")
+        s[_WS["DN_NORM"]] = fill_normal(128, seed, base + _WS["DN_NORM"], 1.0, 0.02, "f32")
+    else:
+        q4(_WS["FA_Q"], H, 2 * cfg.fa_q_heads * 256)
+        q4(_WS["FA_K"], H, cfg.fa_kv_heads * 256)
+        q4(_WS["FA_V"], H, cfg.fa_kv_heads * 256)
+        q4(_WS["FA_O"], cfg.fa_q_heads * 256, H)
+        s[_WS["FA_Q_NORM"]] = fill_normal(256, seed, base + _WS["FA_Q_NORM"], 1.0, 0.02, "bf16")
+        s[_WS["FA_K_NORM"]] = fill_normal(256, seed, base + _WS["FA_K_NORM"], 1.0, 0.02, "bf16")
+    q4(_WS["GATE"], H, I)
+    q4(_WS["UP"], H, I)
+    q4(_WS["DOWN"], I, H)
+    s[_WS["INPUT_NORM"]] = fill_normal(H, seed, base + _WS["INPUT_NORM"], 0.0, 0.02, "bf16")
+    s[_WS["POST_NORM"]] = fill_normal(H, seed, base + _WS["POST_NORM"], 0.0, 0.02, "bf16")
+    return s
+
+
+def synthetic_globals(cfg, seed: int):
+    n = cfg.vocab * cfg.hidden
+    return [fill_normal(n, seed, 1, 0.0, 0.02, "bf16"), fill_normal(n, seed, 2, 0.0, 0.02, "bf16"),
+            fill_normal(cfg.hidden, seed, 3, 0.0, 0.02, "bf16")]
+
+
+def seed_state(om: "Model", ctx_len: int, seed: int) -> None:
+    """The benchmark's stand-in for a prompt of ctx_len tokens: KV rows [0, ctx_len) bf16 N(0,1) (streams 100000+l,
+    200000+l), DeltaNet state fp32 N(0,0.02) (300000+l), the three previous tokens' pre-convolution values
+    fp32 N(0,1) (400000+l; row t = position ctx_len-1-t).  Same tensors as lithos_b200.model.Model.seed_state."""
+    cfg = om.cfg
+    for l in range(cfg.n_layers):
+        if cfg_is_fa(cfg, l):
+            n = ctx_len * cfg.fa_kv_heads * cfg.fa_dim
+            om.k_cache(l).ravel()[:n] = fill_normal(n, seed, 100000 + l, dtype="bf16")
+            om.v_cache(l).ravel()[:n] = fill_normal(n, seed, 200000 + l, dtype="bf16")
+        else:
+            st = om.dn_state(l)
+            st[...] = fill_normal(st.size, seed, 300000 + l, std=0.02).reshape(st.shape)
+            h = om.conv_hist(l)
+            h[...] = fill_normal(h.size, seed, 400000 + l).reshape(h.shape)
