@@ -1,5 +1,6 @@
 #!/usr/bin/env python
-"""Benchmark of the batch-1 decode hot path (see DESIGN.md for definitions).
+"""Benchmark of the batch-1 decode hot path: BASELINE config 3 (the 64-layer decode step) is the timed workload; the
+default single-GPU line also carries one measurement each for configs 0, 1 and 2.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemv] [--impl reference]
 
@@ -30,6 +31,44 @@ def measured_hbm_peak():
         return float(json.loads(PEAKS_FILE.read_text())["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def host_threads(world=1):
+    """threads for host-side work.  torchrun exports OMP_NUM_THREADS=1 when the variable is unset; a CPU baseline on one
+    core or a model build on one core per rank is not what anyone wants to time, so that setting (and only that one) is
+    replaced by the cores this process may use, shared between the ranks of the job."""
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    return max(1, cores // max(world, 1))
+
+
+def fix_omp_env(world):
+    if os.environ.get("OMP_NUM_THREADS", "1") == "1" and "TORCHELASTIC_RUN_ID" in os.environ:
+        os.environ["OMP_NUM_THREADS"] = str(host_threads(world))
+    elif "OMP_NUM_THREADS" not in os.environ:
+        os.environ["OMP_NUM_THREADS"] = str(host_threads(world))
+
+
+TRAFFIC_FILE = ROOT / "profiles" / "gemv_chain_traffic.json"
+
+
+def chain_traffic_bytes(lb):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one gemv_chain launch of the roofline workload, from the ncu capture
+    summarised under profiles/; None when no capture is recorded for the packed-weight layout this library uses"""
+    try:
+        rec = json.loads(TRAFFIC_FILE.read_text())
+        if int(rec["pack_version"]) != int(lb.lib().lb_gemv_pack_version()):
+            return None
+        return int(rec["dram_bytes_read"]) + int(rec["dram_bytes_write"])
+    except Exception:
+        return None
+
+
+def logits_hash(a):
+    import hashlib
+    return hashlib.blake2b(np.ascontiguousarray(a, dtype=np.float32).tobytes(), digest_size=8).hexdigest()
 
 
 class ClockSampler:
@@ -211,15 +250,16 @@ def bench_gemv(args, rank, local, world, dist):
 
 
 def reference_gemv(args, rank):
-    """--impl reference: the reference has no CPU implementation of these kernels that can run (its
-    interpreters evaluate the integer host dialect only), so the CPU arm is the plain-C restatement."""
-    import lithos_b200 as lb
-    K, N = 5120, 17408
-    qw = lb.fill_u32(K // 8 * N, 100, 1)
-    sc = lb.fill_scales_f16(K // 128 * N, 100, 2)
-    qz = lb.fill_u32(K // 128 * (N // 8), 100, 3)
-    x = lb.fill_normal(K, 100, 4, dtype="f16")
+    """--impl reference --workload gemv: the plain-C restatement on config 0 (the reference has no CPU implementation of
+    its kernels that can run); inputs from the oracle's own twin of the generator."""
     from oracle import oracle as orc
+    if orc.num_threads() == 1 and host_threads() > 1:
+        orc.set_num_threads(host_threads())
+    K, N = 5120, 17408
+    qw = orc.fill_u32(K // 8 * N, 100, 1)
+    sc = orc.fill_scales_f16(K // 128 * N, 100, 2)
+    qz = orc.fill_u32(K // 128 * (N // 8), 100, 3)
+    x = orc.fill_normal(K, 100, 4, dtype="f16")
     per_step = 16
     for _ in range(min(args.warmup, 2)):
         orc.gptq_gemv(qw, sc, qz, x, K, N)
@@ -257,21 +297,6 @@ def decode_algorithmic_bytes(cfg, model_weight_bytes, ctx_len):
     state = n_dn * 2 * cfg.dn_v_heads * 128 * 128 * 4
     kv = n_fa * ctx_len * cfg.fa_kv_heads * 256 * 2 * 2
     return model_weight_bytes + state + kv
-
-
-def prefill_state(model, cfg, lb, ctx_len, seed=4242):
-    """direct seeded fill of this shard's recurrent state, conv history and the first ctx_len KV rows"""
-    for l in range(cfg.n_layers):
-        _, nbytes = model.state_ptr(l, 0)
-        stream = 1000 * model.tp_rank + l
-        if cfg.is_fa(l):
-            n = nbytes // 2 // cfg.max_ctx * ctx_len
-            model.set_state(l, 0, lb.fill_normal(n, seed, 100000 + stream, dtype="bf16"))
-            model.set_state(l, 1, lb.fill_normal(n, seed, 200000 + stream, dtype="bf16"))
-        else:
-            model.set_state(l, 0, lb.fill_normal(nbytes // 4, seed, 300000 + stream, std=0.02))
-            _, rbytes = model.state_ptr(l, 1)
-            model.set_state(l, 1, lb.fill_normal(rbytes // 4, seed, 400000 + stream))
 
 
 def time_gemv_mix(ctx, lb, cfg, args, tp_size=1, chained=False):
@@ -329,33 +354,144 @@ def time_gemv_mix(ctx, lb, cfg, args, tp_size=1, chained=False):
     return ms * 1e-3 / (reps * launches), algo / launches, launches * reps
 
 
-def cpu_decode_sample(cfg, lb, seed, ctx_len):
-    """CPU baseline: the C oracle (OpenMP) on the first 8 layers (two periods of 3 DeltaNet + 1 attention
-    layer) of the same synthetic model at position ctx_len; the 64-layer step is extrapolated as
-    16 periods + LM head."""
+WORKLOAD = ("config3: 64-layer Qwen3.5-27B-shaped decode step, hidden 5120, 3 DeltaNet + 1 attention per 4 layers, SwiGLU 17408, "
+            "vocab 248320, int4 g128 linears, bf16 LM head, state pre-filled to 4096 tokens by seeded fill, greedy, one CUDA graph per step")
+METRIC = "batch-1 decode tok/s (Qwen3.5-27B-shaped hybrid, GPTQ int4, 4096-token state)"
+
+
+def oracle_decode_run(seed, ctx_len, warm, steps, n_layers=64):
+    """The C oracle (OpenMP over the host cores) decoding the benchmark's model: full steps of all layers + LM head from
+    (token 1, position ctx_len), greedy.  Inputs come from the oracle's own twin of the seeded generator, so nothing
+    of the product library is loaded.  Returns (tokens of all warm + timed steps, seconds per timed step, threads,
+    seconds spent building the model)."""
     from oracle import oracle as orc
-    from lithos_b200 import model as M
-    sub = M.ModelCfg.from_buffer_copy(cfg)
-    sub.n_layers = 8
-    sub.max_ctx = ctx_len + 8
-    ocfg = orc.ModelCfg(**{n: getattr(sub, n) for n, _ in M.ModelCfg._fields_})
-    slots = [M.synthetic_layer_slots(sub, seed, l) for l in range(8)]
-    glob = M.synthetic_globals(sub, seed)
-    om = orc.Model(ocfg, slots, glob)
-    for l in range(8):
-        if sub.is_fa(l):
-            n = ctx_len * sub.fa_kv_heads * 256
-            om.k_cache(l).ravel()[:n] = lb.fill_normal(n, 4242, 10000 + l, dtype="bf16")
-            om.v_cache(l).ravel()[:n] = lb.fill_normal(n, 4242, 20000 + l, dtype="bf16")
-    om.decode(1, ctx_len, 4)          # warm
-    t0 = time.perf_counter(); om.decode(1, ctx_len + 1, 4); t4 = time.perf_counter() - t0
-    t0 = time.perf_counter(); om.decode(1, ctx_len + 2, 8); t8 = time.perf_counter() - t0
-    period = max(t8 - t4, 1e-6)
-    xh = lb.fill_normal(sub.hidden, 1, 1)
-    t0 = time.perf_counter(); orc.dense_bf16_gemv(glob[1], xh, sub.vocab, sub.hidden); head = time.perf_counter() - t0
-    step = 16 * period + head
+    if orc.num_threads() == 1 and host_threads() > 1:
+        orc.set_num_threads(host_threads())
+    t0 = time.perf_counter()
+    cfg = orc.qwen35_27b(max_ctx=ctx_len + warm + steps + 8, n_layers=n_layers)
+    slots = [orc.synthetic_layer_slots(cfg, seed, l) for l in range(cfg.n_layers)]
+    om = orc.Model(cfg, slots, orc.synthetic_globals(cfg, seed))
+    orc.seed_state(om, ctx_len, seed)
+    build_s = time.perf_counter() - t0
+    tok, toks = 1, []
+    for i in range(warm):
+        tok = om.decode(tok, ctx_len + i)
+        toks.append(tok)
+    t0 = time.perf_counter()
+    for i in range(steps):
+        tok = om.decode(tok, ctx_len + warm + i)
+        toks.append(tok)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
     om.close()
-    return 1.0 / step, orc.num_threads(), f"C oracle (OpenMP): 2 decode steps on the first 4 and 8 layers at position {ctx_len}; one period {period * 1e3:.0f} ms, LM head {head * 1e3:.0f} ms; 64-layer step extrapolated as 16 periods + head = {step * 1e3:.0f} ms"
+    return toks, dt, orc.num_threads(), build_s
+
+
+def bench_small_configs(ctx, lb):
+    """One device-timed figure each for BASELINE configs 0, 1 and 2, so that every config has a number in the default
+    line: config 0 (17408 x 5120 int4 GEMV, 8 rotating weight sets > L2), config 1 (one DeltaNet step, 48/16 heads, 64
+    rotating states > L2), config 2 (decode attention at 4096 / 32768 / 131072 rows, rotating caches > L2)."""
+    peak, _ = measured_hbm_peak()
+    out = {}
+    # ---- config 0 ----
+    K, N, SETS = 5120, 17408, 8
+    dev = [[ctx.to_device(lb.fill_u32(K // 8 * N, 100 + s_, 1)), ctx.to_device(lb.fill_scales_f16(K // 128 * N, 100 + s_, 2)),
+            ctx.to_device(lb.fill_u32(K // 128 * (N // 8), 100 + s_, 3))] for s_ in range(SETS)]
+    d_x, d_y = ctx.to_device(lb.fill_normal(K, 100, 4, dtype="f16")), ctx.alloc(N * 2)
+
+    def timed(graph, launches, reps=40):
+        for _ in range(5):
+            graph.launch()
+        ctx.sync()
+        ctx.timer_start()
+        for _ in range(reps):
+            graph.launch()
+        us = ctx.timer_stop() * 1e3 / (reps * launches)
+        graph.destroy()
+        return us
+
+    ctx.begin_capture()
+    for j in range(16):
+        w = dev[j % SETS]
+        ctx.gemv_int4(w[0], w[1], w[2], d_x, d_y, K, N, 0)
+    us = timed(ctx.end_capture(), 16)
+    algo = gemv_bytes(K, N)
+    out["gemv_config0"] = {"workload": "config0: int4 GEMV 17408x5120 g128 asymmetric, fp16 x and y, batch 1; 8 rotating weight sets (371 MB > L2)",
+                           "kernel": "gemv_int4_w256", "us_per_launch": round(us, 2), "algorithmic_bytes": algo, "GBps": round(algo / us / 1e3, 1),
+                           "frac_of_measured_peak": round(algo / us / 1e3 / peak, 3), "frac_of_8TBps": round(algo / us / 1e3 / 8000.0, 3)}
+    # the same matrix as a chain of one (strip-packed weights, one CTA per SM, no split-K)
+    if ctx.gemv_chain_supports(K, N):
+        packed = [ctx.gemv_pack(w[0], w[1], w[2], K, N) for w in dev]
+        ctx.begin_capture()
+        for j in range(16):
+            ctx.gemv_chain([dict(packed=packed[j % SETS], x=d_x, y=d_y, K=K, N=N, x_mode=lb.X_F16, y_mode=lb.Y_F16)])
+        us = timed(ctx.end_capture(), 16)
+        out["gemv_config0"]["strip_packed"] = {"kernel": "gemv_chain (one entry)", "us_per_launch": round(us, 2), "GBps": round(algo / us / 1e3, 1),
+                                               "frac_of_measured_peak": round(algo / us / 1e3 / peak, 3)}
+        for b in packed:
+            b.free()
+    for w in dev:
+        for b in w:
+            b.free()
+    # ---- config 1 ----
+    HV, HK, NS = 48, 16, 64
+    st = ctx.alloc(NS * HV * 128 * 128 * 4)
+    one = lb.fill_normal(HV * 128 * 128, 7, 10, std=0.02)
+    for i in range(NS):
+        lb.lib().lb_memcpy_h2d(ctx.h, st.ptr + i * one.nbytes, one.ctypes.data, one.nbytes)
+    ctx.sync()
+    q = ctx.to_device(lb.fill_normal(HK * 128, 7, 11, std=0.088, dtype="bf16"))
+    k = ctx.to_device(lb.fill_normal(HK * 128, 7, 12, std=0.088, dtype="bf16"))
+    v = ctx.to_device(lb.fill_normal(HV * 128, 7, 13, dtype="bf16"))
+    g = ctx.to_device(np.full(HV, 0.9, np.float32))
+    beta = ctx.to_device(np.full(HV, 0.5, np.float32))
+    o = ctx.alloc(HV * 128 * 4)
+    from lithos_b200 import DeviceBuffer
+
+    def view(buf, off, n):
+        b = DeviceBuffer.__new__(DeviceBuffer)
+        b.ctx, b.ptr, b.nbytes = ctx, buf.ptr + off, n
+        return b
+
+    ctx.begin_capture()
+    for i in range(NS):
+        ctx.deltanet_step(view(st, i * one.nbytes, one.nbytes), q, k, v, None, g, beta, o, HV, HK)
+    us = timed(ctx.end_capture(), NS)
+    algo = 2 * HV * 128 * 128 * 4
+    out["deltanet_step"] = {"workload": "config1: one Gated DeltaNet decode step, 48 value / 16 key heads, fp32 state [48,128,128]; 64 rotating states (201 MB > L2)",
+                            "kernel": "deltanet_step_bf16", "us_per_launch": round(us, 2), "algorithmic_bytes": algo, "GBps": round(algo / us / 1e3, 1),
+                            "frac_of_measured_peak": round(algo / us / 1e3 / peak, 3)}
+    for b in (st, q, k, v, g, beta, o):
+        b.free()
+    # ---- config 2 ----
+    HQ, HKV, POOL = 24, 4, 4 * 131072          # pool of cache rows: 1.07 GB each for K and V
+    row = HKV * 256 * 2
+    chunk = lb.fill_normal(32768 * HKV * 256, 7, 20, dtype="bf16")
+    kc, vc = ctx.alloc(POOL * row), ctx.alloc(POOL * row)
+    for buf in (kc, vc):
+        for i in range(POOL // 32768):
+            lb.lib().lb_memcpy_h2d(ctx.h, buf.ptr + i * chunk.nbytes, chunk.ctypes.data, chunk.nbytes)
+    ctx.sync()
+    ins = {n: ctx.to_device(lb.fill_normal(h * 256, 7, 21 + i, dtype="bf16")) for i, (n, h) in enumerate((("q", HQ), ("k", HKV), ("v", HKV), ("gate", HQ)))}
+    qw = ctx.to_device(lb.fill_normal(256, 7, 26, mean=1.0, std=0.02, dtype="bf16"))
+    kw = ctx.to_device(lb.fill_normal(256, 7, 27, mean=1.0, std=0.02, dtype="bf16"))
+    d_o = ctx.alloc(HQ * 256 * 4)
+    sweep = []
+    for L in (4096, 32768, 131072):
+        sets = min(POOL // L, 32)
+        ctx.begin_capture()
+        for i in range(sets):
+            ctx.attention_decode(ins["q"], ins["k"], ins["v"], ins["gate"], qw, kw, view(kc, i * L * row, L * row), view(vc, i * L * row, L * row),
+                                 d_o, L - 1, HQ, HKV)
+        us = timed(ctx.end_capture(), sets, reps=20 if L < 131072 else 6)
+        algo = L * HKV * 256 * 2 * 2
+        sweep.append({"rows": L, "us_per_launch": round(us, 2), "algorithmic_bytes": algo, "GBps": round(algo / us / 1e3, 1),
+                      "frac_of_measured_peak": round(algo / us / 1e3 / peak, 3), "rotating_caches": sets})
+    out["attention_sweep"] = {"workload": "config2: GQA decode attention, 24 query / 4 KV heads, head_dim 256, bf16 cache, q/k norm + RoPE + append + gate fused",
+                              "kernel": "attn_decode_mma", "sweep": sweep}
+    for b in [kc, vc, qw, kw, d_o] + list(ins.values()):
+        b.free()
+    assert ctx.device_status() == 0
+    return out
 
 
 def bench_decode(args, rank, local, world, dist):
@@ -376,7 +512,8 @@ def bench_decode(args, rank, local, world, dist):
     if comm is not None:
         tp.attach(model, comm)
     model.fill_synthetic(args.seed)
-    prefill_state(model, cfg, lb, CTX_PREFILL)
+    model.seed_state(CTX_PREFILL, args.seed)     # ONE global seeded state; every rank takes its heads of it
+    model.checkpoint()                           # the recurrent state is restored before every measured pass
     build_s = time.perf_counter() - t0
     if args.no_chain:
         model.set_chain(False)
@@ -394,6 +531,20 @@ def bench_decode(args, rank, local, world, dist):
         model.set_input(1, CTX_PREFILL)
         model.replay(4)
     ctx.sync()
+    # parity pass (untimed): the first 16 greedy tokens from (token 1, position 4096) on the restored state.  They do not
+    # depend on N (tensor-parallel shards of ONE model and ONE state) nor on how long the ramp ran.
+    model.rollback()
+    model.set_input(1, CTX_PREFILL)
+    first_tokens = []
+    for _ in range(16):
+        model.replay(1)
+        first_tokens.append(int(model.read_next()))
+    lhash = logits_hash(model.logits())
+    if dist is not None:
+        hs = [None] * world
+        dist.all_gather_object(hs, lhash)
+        lhash = "+".join(hs)
+    model.rollback()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -413,9 +564,11 @@ def bench_decode(args, rank, local, world, dist):
     clocks = sampler.stop() if rank == 0 else None
 
     # end to end through the public call: token id in (H2D), next token out (D2H), every step
-    model.set_input(1, CTX_PREFILL)
+    model.rollback()
     tok, e2e_steps = 1, max(16, min(args.steps, 64))
+    model.set_input(tok, CTX_PREFILL)
     model.replay(2); ctx.sync()
+    tok = model.read_next()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
         model.set_input(tok, CTX_PREFILL + 2 + i)
@@ -435,24 +588,23 @@ def bench_decode(args, rank, local, world, dist):
     chained = not args.no_chain
     gemv_s, gemv_algo, _ = time_gemv_mix(ctx, lb, cfg, args, world, chained=chained)
     out = {
-        "metric": "batch-1 decode tok/s (Qwen3.5-27B-shaped hybrid, GPTQ int4, 4096-token state)", "value": 1.0 / step_s,
+        "metric": METRIC, "value": 1.0 / step_s,
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int4 weights, fp16 activations (exact integer dot products), fp32 state", "data": "synthetic",
-        "config": {"workload": f"config3: {cfg.n_layers}-layer Qwen3.5-27B-shaped decode step, hidden 5120, 3 DeltaNet + 1 attention "
-                               f"per 4 layers, SwiGLU 17408, vocab 248320, int4 g128 linears, bf16 LM head, state pre-filled to {CTX_PREFILL} "
-                               "tokens by seeded fill, greedy, one CUDA graph per step",
+        "config": {"workload": WORKLOAD if cfg.n_layers == 64 else WORKLOAD.replace("64-layer", f"{cfg.n_layers}-layer"),
                    "parallelism": f"tp{world}", "l2": f"every step streams {algo_step / 1e9:.2f} GB of weights/state (>> 126 MB L2)",
                    "kernels_per_step": kernels_per_step, "build_seconds": round(build_s, 1), "last_token": int(last_token)},
+        "parity": {"first_tokens": first_tokens, "logits_hash_after_16": lhash,
+                   "what": "greedy tokens of the first 16 steps from (token 1, position 4096) on the seeded state: the same list at every N "
+                           "is the tensor-parallel parity (TP=n tokens == TP=1 tokens); at N=1 the first of them are also checked against the CPU oracle"},
         "e2e": {"value": 1.0 / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
         "gpu_launches": int(launches),
         "step_roofline": {"algorithmic_bytes_per_step": algo_step, "achieved_GBs": algo_step / step_s / 1e9, "peak_GBs": peak * world,
                           "frac": algo_step / step_s / 1e9 / (peak * world), "tok_s_at_peak": peak * world * 1e9 / algo_step},
         "roofline": {"bound": "hbm", "achieved": gemv_algo / gemv_s / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": gemv_algo / gemv_s / 1e9 / peak,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one such launch in the ncu capture summarised in
-                     # profiles/gemv_chain_layer_ncu.md (203 520 768 + 3 367 168); not re-measured by this run
-                     "traffic": 206887936 if chained and world == 1 else None, "peak_source": which,
+                     "traffic": chain_traffic_bytes(lb) if chained and world == 1 else None, "peak_source": which,
                      "kernel": "gemv_chain" if chained else "gemv_int4_w256",
                      "us_per_launch": gemv_s * 1e6, "algorithmic_bytes": gemv_algo,
                      "how": ("the step's four int4 GEMVs between two token mixers (out, gate/up + SwiGLU, down, next input projection; fused norm "
@@ -465,10 +617,16 @@ def bench_decode(args, rank, local, world, dist):
     if comm is not None:
         barrier(dist)
         comm.close()
-    if rank == 0 and not args.no_cpu and world == 1:
-        v, cores, sample = cpu_decode_sample(cfg, lb, args.seed, CTX_PREFILL)
-        out["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
+    if world == 1 and not args.no_small and cfg.n_layers == 64:
+        out.update(bench_small_configs(ctx, lb))
     ctx.close()
+    if rank == 0 and not args.no_cpu and world == 1 and cfg.n_layers == 64:
+        toks, dt, cores, b_s = oracle_decode_run(args.seed, CTX_PREFILL, 1, 2)
+        out["cpu_baseline"] = {"value": 1.0 / dt, "unit": "tok/s", "cores": cores, "kind": "port",
+                               "sample": f"3 full decode steps (64 layers + LM head) of the same seeded model and state with the C oracle (OpenMP, {cores} "
+                                         f"threads): 1 warm-up + 2 timed, {dt * 1e3:.0f} ms per step; building the model on the host took {b_s:.0f} s"}
+        out["parity"]["oracle_first_tokens"] = [int(t) for t in toks]
+        out["parity"]["matches_oracle"] = first_tokens[:len(toks)] == [int(t) for t in toks]
     return out
 
 
@@ -544,17 +702,16 @@ def bench_batched(args, local):
 
 
 def reference_decode(args, rank):
-    """--impl reference: the reference's kernels have no CPU implementation that can run (its interpreters
-    evaluate the integer host dialect only), so this arm times the plain-C restatement on the host cores."""
-    import lithos_b200 as lb
-    from lithos_b200 import model as M
-    cfg = M.qwen35_27b(max_ctx=CTX_PREFILL + 64)
-    v, cores, sample = cpu_decode_sample(cfg, lb, args.seed, CTX_PREFILL)
-    return {"impl": "reference", "metric": "batch-1 decode tok/s (Qwen3.5-27B-shaped hybrid, GPTQ int4, 4096-token state)",
-            "value": v, "unit": "tok/s", "n_gpus": 0, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / v,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-            "config": {"workload": "config3: 64-layer Qwen3.5-27B-shaped decode step (CPU: bounded sample, extrapolated)"},
-            "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+    """--impl reference: the reference's kernels have no CPU implementation that can run (its interpreters evaluate the
+    integer host dialect only), so this arm times the plain-C restatement (oracle/, OpenMP over the host cores) on the SAME
+    workload: W warm-up + K timed full decode steps, all 64 layers + LM head, same seeded model and state."""
+    toks, dt, cores, b_s = oracle_decode_run(args.seed, CTX_PREFILL, args.warmup, args.steps)
+    v = 1.0 / dt
+    return {"impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": 0, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (int4 weights, fp16 activations)",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "parallelism": f"{cores} host threads", "build_seconds": round(b_s, 1), "last_token": int(toks[-1])},
+            "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port",
+                             "sample": f"{args.warmup} warm-up + {args.steps} timed full decode steps (64 layers + LM head) with the C oracle, OpenMP, {cores} threads"},
             "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
@@ -572,13 +729,15 @@ def main():
     ap.add_argument("--batched-batches", default="1,4,16,32,64,128", help="batched workload: batch sizes")
     ap.add_argument("--seed", type=int, default=20260413)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-small", action="store_true", help="decode workload: skip the one-figure measurements of configs 0, 1 and 2")
     ap.add_argument("--no-chain", action="store_true", help="decode workload: one launch per projection instead of persistent chains")
     ap.add_argument("--ramp-s", type=float, default=1.5, help="seconds of untimed work before warm-up (clock ramp)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.steps is None:
-        args.steps = 256 if args.workload == "decode" else 2000
+        args.steps = (20 if args.impl == "reference" else 256) if args.workload == "decode" else 2000
     rank, local, world = dist_env()
+    fix_omp_env(1 if args.impl == "reference" else world)   # before any OpenMP library is loaded
     if args.impl == "reference":
         if rank == 0:
             ref = reference_decode(args, rank) if args.workload == "decode" else reference_gemv(args, rank)

@@ -50,8 +50,17 @@ int lb_init(int device, const char* kernel_dir, lb_ctx** out);
 void lb_destroy(lb_ctx* ctx);
 const char* lb_last_error(const lb_ctx* ctx);
 int lb_device_sm_count(const lb_ctx* ctx);
-/* status word written by bounded device-side waits (0 = none gave up); reading it synchronises the stream */
+/* status word written by bounded device-side waits (0 = none gave up); reading it synchronises the stream and,
+ * when it is non-zero, returns LB_ERR_DEVICE_WAIT and clears the word.  The reference's own bounded wait traps the
+ * GPU instead (runtime/sync.ls:50-60 sync_wait_flag_timeout); here the kernel returns and the host reads why:
+ * 0x1001 a weight copy never landed, 0x1003 a peer GPU never published its flag, 0x1004 a CTA never reached the grid
+ * barrier, 0x1005 the decode position lies outside the KV cache. */
 int lb_device_status(lb_ctx* ctx, uint32_t* status_out);
+int lb_reset_status(lb_ctx* ctx); /* clear the status word without reading it (stream-ordered) */
+/* Time limit, in nanoseconds, of the kernels' waits on other CTAs and other GPUs (grid barrier, peer flags); 0 = the
+ * built-in 2 s.  Stream-ordered: applies to kernels launched (or replayed) after it.  After a wait has run out, every
+ * later wait returns at once until the status word is cleared, so a lost peer costs one limit, not one per exchange. */
+int lb_set_wait_limit(lb_ctx* ctx, uint64_t ns);
 /* number of kernels this library has launched on the context (graph replays count their kernel nodes) */
 uint64_t lb_launch_count(const lb_ctx* ctx);
 void lb_launch_count_reset(lb_ctx* ctx);
@@ -162,6 +171,7 @@ typedef struct {
     int32_t reserved;
 } lb_gemv_op;
 size_t lb_gemv_packed_bytes(int K, int N);
+int lb_gemv_pack_version(void); /* version of the strip-packed byte layout (recorded beside measured DRAM traffic) */
 int lb_gemv_pack(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, int K, int N, int swiglu, uint64_t packed_out);
 int lb_gemv_chain(lb_ctx* ctx, const lb_gemv_op* ops, int n_ops);
 /* LB_OK when lb_gemv_pack / lb_gemv_chain accept this shape on this GPU (no launch) */
@@ -251,6 +261,16 @@ int lb_comm_rank(const lb_comm* comm);
 int lb_comm_size(const lb_comm* comm);
 int lb_comm_handle(lb_comm* comm, void* handle_out64);
 int lb_comm_open(lb_comm* comm, const void* handles_size_x_64);
+/* A peer whose buffer this process can address directly (a second GPU of the same process with peer access enabled):
+ * its lb_comm_buffer, lb_comm_bytes long, instead of an IPC handle. */
+int lb_comm_set_peer(lb_comm* comm, int rank, uint64_t peer_buffer);
+uint64_t lb_comm_buffer(const lb_comm* comm);      /* this rank's exchange buffer: float [3][n_max] partial slots, then the flags */
+size_t lb_comm_bytes(const lb_comm* comm);
+size_t lb_comm_flags_offset(const lb_comm* comm);  /* byte offset of the flag array u32 [8] (one generation word per rank) */
+/* One exchange outside the decode step: x[0..n) += the sum over ranks, in rank order, of the partial vectors every
+ * rank has left in slot 0 or 1 of its own buffer.  Bounded: a rank that never publishes makes the kernel return with
+ * status 0x1003 after the wait limit. */
+int lb_comm_allreduce(lb_comm* comm, uint64_t x_f32, int n, int slot);
 void lb_comm_destroy(lb_comm* comm);
 
 /* ---- the whole decode step ------------------------------------------------------------
@@ -282,6 +302,31 @@ void lb_model_destroy(lb_model* m);
  * (src/launcher.s:3284-3683). */
 int lb_model_load_layer(lb_model* m, int layer, const void* const* slots);
 int lb_model_load_globals(lb_model* m, const void* const* globals); /* embed, lm_head, final_norm */
+const lb_model_cfg* lb_model_config(const lb_model* m);
+
+/* ---- weight_index.bin: the launcher's weight-table file (src/launcher.s:3267-3282 format, :3284-3683 load_weights) ----
+ * <model_dir>/weight_index.bin names the shard files and gives (shard, offset, size) for 26 slots per layer + 3
+ * globals; load_weights maps the shards and resolves the pointers.  lb_load_weights does the same and hands every
+ * layer to lb_model_load_layer.  Unlike the launcher (which prints a message and goes on with NULL pointers), a bad
+ * magic or version, a truncated index, a shard index out of range, an entry that runs past its shard or does not
+ * have the size the model shape implies are LB_ERR_IO, a missing required slot LB_ERR_INVALID.
+ * The host-only calls (open / entry / check / close, lb_save_weights) need no GPU; `err` receives the reason. */
+typedef struct lb_weight_index lb_weight_index;
+int lb_weight_index_open(const char* model_dir, lb_weight_index** out, char* err, size_t errlen);
+int lb_weight_index_dims(const lb_weight_index* w, int* n_layers, int* n_slots, int* n_globals, int* n_shards);
+/* host pointer into the mapped shard and size of (layer, slot); layer < 0 addresses global `slot`; unused -> NULL, 0 */
+int lb_weight_index_entry(const lb_weight_index* w, int layer, int slot, const void** ptr, size_t* bytes);
+int lb_weight_index_check(const lb_weight_index* w, const lb_model_cfg* cfg, char* err, size_t errlen);
+void lb_weight_index_close(lb_weight_index* w);
+/* bytes of slot `slot` of `layer` / of global `which` for this model shape (0 = unused in that kind of layer):
+ * int4 tensors in the reference's packing, norm / conv / projection-a,b tensors bf16, A_log and the per-head norm fp32 */
+size_t lb_model_slot_bytes(const lb_model_cfg* cfg, int layer, int slot);
+size_t lb_model_global_bytes(const lb_model_cfg* cfg, int which);
+/* Writes <model_dir>/weight_index.bin and one raw shard file holding the given host tensors (layer_slots is
+ * [n_layers * 26], unused slots NULL).  Stands in for the reference's gen_weight_index.py, which is not in its tree. */
+int lb_save_weights(const char* model_dir, const lb_model_cfg* cfg, const void* const* layer_slots, const void* const* globals,
+                    char* err, size_t errlen);
+int lb_load_weights(lb_ctx* ctx, const char* model_dir, lb_model* m);
 /* Host-only view of the same re-layout (no GPU needed): device matrix `which` (0 fused input
  * projections, 1 out/o projection, 2 gate|up interleaved, 3 down) of tensor-parallel shard
  * tp_rank/tp_size for `layer`.  Call with NULL outputs for the sizes, then with buffers of
@@ -310,8 +355,10 @@ int lb_model_decode(lb_model* m, int token, int pos, int* next_out);
 /* Capture the whole step once; then each replay consumes the token/position left on the device
  * by the previous step (set them with lb_model_set_input) and leaves the next token there. */
 int lb_model_capture(lb_model* m);
-int lb_model_set_input(lb_model* m, int token, int pos);
-int lb_model_replay(lb_model* m, int n_steps);        /* n graph launches, no host round trip */
+int lb_model_set_input(lb_model* m, int token, int pos); /* stream-ordered, by value: safe to call back to back */
+/* n graph launches, no host round trip.  LB_ERR_INVALID (nothing launched) when the steps would run past max_ctx:
+ * the host tracks the position from lb_model_set_input / lb_model_decode plus the steps issued since. */
+int lb_model_replay(lb_model* m, int n_steps);
 int lb_model_read_next(lb_model* m, int* next_out);   /* synchronises */
 int lb_model_step_kernels(const lb_model* m);         /* kernels per decode step */
 

@@ -71,6 +71,8 @@ def lib() -> C.CDLL:
     sig("lb_last_error", C.c_char_p, vp)
     sig("lb_device_sm_count", i32, vp)
     sig("lb_device_status", i32, vp, P(C.c_uint32))
+    sig("lb_reset_status", i32, vp)
+    sig("lb_set_wait_limit", i32, vp, u64)
     sig("lb_launch_count", u64, vp)
     sig("lb_launch_count_reset", None, vp)
     sig("lb_set_pdl", None, vp, i32)
@@ -275,6 +277,13 @@ class Context:
         s = C.c_uint32(0)
         self._check(lib().lb_device_status(self.h, C.byref(s)))
         return s.value
+
+    def reset_status(self):
+        self._check(lib().lb_reset_status(self.h))
+
+    def set_wait_limit(self, ns: int):
+        """time limit of the kernels' waits on other CTAs / GPUs, nanoseconds (0 = the built-in 2 s)"""
+        self._check(lib().lb_set_wait_limit(self.h, int(ns)))
 
     @property
     def sm_count(self) -> int:

@@ -22,6 +22,8 @@ LB_API int lb_gemv_chain_supports(lb_ctx* c, int K, int N, int swiglu) {
     return chain_shape_problem(c, K, N, swiglu) ? LB_ERR_INVALID : LB_OK;
 }
 
+LB_API int lb_gemv_pack_version(void) { return LB_CHAIN_PACK_VERSION; }
+
 LB_API size_t lb_gemv_packed_bytes(int K, int N) { return (size_t)(N / 8) * (size_t)(K / LB_GEMV_GROUP) * LB_CHAIN_RECORD; }
 
 LB_API int lb_gemv_pack(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t qzeros, int K, int N, int swiglu, uint64_t packed_out) {

@@ -56,6 +56,19 @@ LB_API int lb_comm_open(lb_comm* m, const void* handles) {
     return LB_OK;
 }
 
+/* a peer's buffer that this process can already address: another GPU of the same process with peer access enabled, or
+ * (tests) a local stand-in for a rank that never answers */
+LB_API int lb_comm_set_peer(lb_comm* m, int rank, uint64_t peer_buffer) {
+    if (!m || rank < 0 || rank >= m->size || rank == m->rank || !peer_buffer || (peer_buffer & 255))
+        return lb_fail(m ? m->c : NULL, LB_ERR_INVALID, "lb_comm_set_peer: bad rank or buffer (256-byte aligned, lb_comm_bytes long)");
+    if (m->opened[rank]) return lb_fail(m->c, LB_ERR_STATE, "lb_comm_set_peer: rank %d is already opened through its IPC handle", rank);
+    m->peer[rank] = (CUdeviceptr)peer_buffer;
+    return LB_OK;
+}
+LB_API size_t lb_comm_bytes(const lb_comm* m) { return m ? m->bytes : 0; }
+LB_API uint64_t lb_comm_buffer(const lb_comm* m) { return m ? (uint64_t)m->buf : 0; }
+LB_API size_t lb_comm_flags_offset(const lb_comm* m) { return m ? m->flags_off : 0; }
+
 LB_API void lb_comm_destroy(lb_comm* m) {
     if (!m) return;
     if (lb_drv.loaded && m->c && m->c->cu_ctx) {
@@ -81,6 +94,17 @@ int lb_comm_fill(const lb_comm* m, lb_tp_params* p, int slot, int n) {
     p->status = (unsigned*)m->c->dev_status;
     p->n = n; p->n_max = m->n_max; p->slot = slot; p->rank = m->rank; p->size = m->size;
     return LB_OK;
+}
+
+/* one exchange outside the decode step: x[0..n) += sum over ranks of their partial vectors in `slot` (0 or 1; every rank
+ * has written its own partial to lb_comm_buffer + slot * n_max * 4 before the call) */
+LB_API int lb_comm_allreduce(lb_comm* m, uint64_t x, int n, int slot) {
+    if (!m || !x || n < 1 || n > m->n_max || slot < 0 || slot > 1) return lb_fail(m ? m->c : NULL, LB_ERR_INVALID, "lb_comm_allreduce: bad argument");
+    lb_tp_params p;
+    LB_TRY(lb_comm_fill(m, &p, slot, n));
+    p.x = (float*)x;
+    void* params[] = {&p};
+    return lb_launch(m->c, LBK_tp_allreduce_add, 1, 1, 1, 1024, 0, params, 1);
 }
 
 uint64_t lb_comm_slot_ptr(const lb_comm* m, int slot) { return (uint64_t)m->buf + (uint64_t)slot * m->n_max * 4; }

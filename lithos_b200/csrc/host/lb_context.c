@@ -235,6 +235,22 @@ LB_API int lb_device_status(lb_ctx* c, uint32_t* out) {
     return LB_OK;
 }
 
+LB_API int lb_reset_status(lb_ctx* c) {
+    if (!c) return LB_ERR_INVALID;
+    LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
+    LB_CU(c, lb_drv.MemsetD32Async(c->dev_status, 0, 1, c->stream));
+    return LB_OK;
+}
+
+/* words 2-3 of the status block: the limit the kernels' waits on other CTAs / GPUs read (common.cuh lb_wait_limit_ns) */
+LB_API int lb_set_wait_limit(lb_ctx* c, uint64_t ns) {
+    if (!c) return LB_ERR_INVALID;
+    LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
+    LB_CU(c, lb_drv.MemsetD32Async(c->dev_status + 8, (unsigned)(ns & 0xffffffffu), 1, c->stream));
+    LB_CU(c, lb_drv.MemsetD32Async(c->dev_status + 12, (unsigned)(ns >> 32), 1, c->stream));
+    return LB_OK;
+}
+
 /* ---- memory ----------------------------------------------------------------- */
 LB_API int lb_malloc(lb_ctx* c, size_t bytes, uint64_t* out) {
     if (!c || !out || bytes == 0) return lb_fail(c, LB_ERR_INVALID, "lb_malloc: bad argument");

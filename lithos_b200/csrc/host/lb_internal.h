@@ -36,6 +36,7 @@
     X(MemcpyDtoHAsync, cuMemcpyDtoHAsync, (void*, CUdeviceptr, size_t, CUstream))                               \
     X(MemcpyDtoDAsync, cuMemcpyDtoDAsync, (CUdeviceptr, CUdeviceptr, size_t, CUstream))                         \
     X(MemsetD8Async, cuMemsetD8Async, (CUdeviceptr, unsigned char, size_t, CUstream))                           \
+    X(MemsetD32Async, cuMemsetD32Async, (CUdeviceptr, unsigned int, size_t, CUstream))                          \
     X(ModuleLoadData, cuModuleLoadData, (CUmodule*, const void*))                                               \
     X(ModuleUnload, cuModuleUnload, (CUmodule))                                                                 \
     X(ModuleGetFunction, cuModuleGetFunction, (CUfunction*, CUmodule, const char*))                             \
@@ -169,6 +170,8 @@ int lb_launch_cluster(lb_ctx* c, int kernel, unsigned gx, unsigned gy, unsigned 
 
 /* rng helpers used by the synthetic model builder */
 uint64_t lb_rng_u64(uint64_t seed, uint64_t stream, uint64_t i);
+uint32_t lb_rng_word(uint64_t seed, uint64_t stream, uint64_t i);
+uint16_t lb_rng_scale_f16(uint64_t seed, uint64_t stream, uint64_t i);
 uint16_t lb_f32_to_f16(float f);
 float lb_f16_to_f32(uint16_t u);
 uint16_t lb_f32_to_bf16(float f);

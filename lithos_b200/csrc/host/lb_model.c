@@ -55,6 +55,7 @@ struct lb_model {
     /* activations */
     CUdeviceptr X, xn, in_out, mix_out, mlp_m, logits, d_token, d_pos, d_next, cand_val, cand_idx;
     int* h_next; /* pinned */
+    int host_pos;  /* position the next step will decode, as the host knows it: set_input's value plus the steps issued since */
     uint64_t weight_bytes;
     lb_graph* graph;
     int step_kernels;
@@ -216,13 +217,23 @@ LB_API int lb_model_logits_ptr(lb_model* m, uint64_t* dptr) {
     return LB_OK;
 }
 LB_API uint64_t lb_model_weight_bytes(const lb_model* m) { return m ? m->weight_bytes : 0; }
+LB_API const lb_model_cfg* lb_model_config(const lb_model* m) { return m ? &m->cfg : NULL; }
 LB_API int lb_model_step_kernels(const lb_model* m) { return m ? m->step_kernels : 0; }
 
 /* ---- weight re-layout (host) --------------------------------------------------------
  * A "column map" lists, for every output column of the device matrix, the column of which
  * source matrix it comes from.  qweight / scales are gathered column by column; qzeros is
  * re-packed nibble by nibble (8 columns per word). */
-typedef struct { const uint32_t* qw; const uint16_t* sc; const uint32_t* qz; int N; } q4_src;
+typedef struct {
+    const uint32_t* qw; const uint16_t* sc; const uint32_t* qz; int N;
+    int synth;             /* the tensors are streams of the seeded generator (qw == sc == qz == NULL): elements are drawn on demand */
+    uint64_t seed, stream; /* qweight = stream, scales = stream + 1, qzeros = stream + 2 */
+} q4_src;
+static inline uint32_t src_qw(const q4_src* s, size_t i) { return s->synth ? lb_rng_word(s->seed, s->stream, i) : s->qw[i]; }
+static inline uint16_t src_sc(const q4_src* s, size_t i) { return s->synth ? lb_rng_scale_f16(s->seed, s->stream + 1, i) : s->sc[i]; }
+static inline uint32_t src_qz(const q4_src* s, size_t i) { return s->synth ? lb_rng_word(s->seed, s->stream + 2, i) : s->qz[i]; }
+/* seeded synthetic weights: tensor (layer, slot) is stream (layer + 1) * 100 + slot */
+typedef struct { uint64_t seed, base; } synth_t;
 
 /* gather one device matrix on the host: columns by map, packed rows of groups [k0,k1) */
 static void gather_q4(const q4_src* src, const int* col_src, const int* col_idx, int N_out, int k0, int k1, uint32_t* qw,
@@ -234,7 +245,7 @@ static void gather_q4(const q4_src* src, const int* col_src, const int* col_idx,
         uint32_t* o = qw + (size_t)kp * N_out;
         for (int n = 0; n < N_out; n++) {
             const q4_src* s = &src[col_src[n]];
-            o[n] = s->qw[(size_t)(k0 * 16 + kp) * s->N + col_idx[n]];
+            o[n] = src_qw(s, (size_t)(k0 * 16 + kp) * s->N + col_idx[n]);
         }
     }
 #pragma omp parallel for schedule(static)
@@ -242,8 +253,8 @@ static void gather_q4(const q4_src* src, const int* col_src, const int* col_idx,
         for (int n = 0; n < N_out; n++) {
             const q4_src* s = &src[col_src[n]];
             int ci = col_idx[n];
-            sc[(size_t)g * N_out + n] = s->sc[(size_t)(k0 + g) * s->N + ci];
-            uint32_t z = (s->qz[(size_t)(k0 + g) * (s->N / 8) + (ci >> 3)] >> (4 * (ci & 7))) & 0xFu;
+            sc[(size_t)g * N_out + n] = src_sc(s, (size_t)(k0 + g) * s->N + ci);
+            uint32_t z = (src_qz(s, (size_t)(k0 + g) * (s->N / 8) + (ci >> 3)) >> (4 * (ci & 7))) & 0xFu;
             qz[(size_t)g * (N_out / 8) + (n >> 3)] |= z << (4 * (n & 7));
         }
     }
@@ -267,8 +278,12 @@ static int build_q4(lb_model* m, q4_mat* dst, const q4_src* src, const int* col_
     return st;
 }
 
-static q4_src slot_src(const void* const* slots, int base, int N) {
-    q4_src s = {(const uint32_t*)slots[base], (const uint16_t*)slots[base + 1], (const uint32_t*)slots[base + 2], N};
+static q4_src slot_src(const void* const* slots, int base, int N, const synth_t* syn) {
+    q4_src s;
+    memset(&s, 0, sizeof s);
+    s.N = N;
+    if (syn) { s.synth = 1; s.seed = syn->seed; s.stream = syn->base + (uint64_t)base; }
+    else { s.qw = (const uint32_t*)slots[base]; s.sc = (const uint16_t*)slots[base + 1]; s.qz = (const uint32_t*)slots[base + 2]; }
     return s;
 }
 static int slots_present(lb_model* m, const void* const* slots, const int* idx, int n, int layer) {
@@ -290,7 +305,7 @@ typedef struct { q4_src src[3]; int* cs; int* ci; int N, k0, k1; } shard_plan;
 
 static void plan_free(shard_plan* p) { free(p->cs); free(p->ci); p->cs = p->ci = NULL; }
 
-static int plan_make(const lb_model_cfg* c, int R, int T, int fa, int which, const void* const* slots, shard_plan* p) {
+static int plan_make(const lb_model_cfg* c, int R, int T, int fa, int which, const void* const* slots, const synth_t* syn, shard_plan* p) {
     memset(p, 0, sizeof *p);
     const int H = c->hidden, I = c->inter;
     const int HV = c->dn_v_heads / T, HK = c->dn_k_heads / T, HQ = c->fa_q_heads / T;
@@ -301,7 +316,7 @@ static int plan_make(const lb_model_cfg* c, int R, int T, int fa, int which, con
         const int QKf = c->dn_k_heads * 128, Cf = (2 * c->dn_k_heads + c->dn_v_heads) * 128, Vf = c->dn_v_heads * 128;
         const int QK = HK * 128, V = HV * 128, C = 2 * QK + V;
         N = C + V;
-        p->src[0] = slot_src(slots, WS_DN_QKV, Cf); p->src[1] = slot_src(slots, WS_DN_Z, Vf);
+        p->src[0] = slot_src(slots, WS_DN_QKV, Cf, syn); p->src[1] = slot_src(slots, WS_DN_Z, Vf, syn);
         p->cs = (int*)malloc(sizeof(int) * N); p->ci = (int*)malloc(sizeof(int) * N);
         if (!p->cs || !p->ci) return LB_ERR_NOMEM;
         for (int n = 0; n < N; n++) { /* device columns: q | k | v | z of this shard's heads */
@@ -316,7 +331,7 @@ static int plan_make(const lb_model_cfg* c, int R, int T, int fa, int which, con
         const int NQ = 2 * HQ * 256, NKV = HKV * 256;
         const int kv0 = c->fa_kv_heads >= T ? R * HKV : (R * c->fa_kv_heads) / T; /* first KV head of this shard */
         N = NQ + 2 * NKV;
-        p->src[0] = slot_src(slots, WS_FA_Q, NQf); p->src[1] = slot_src(slots, WS_FA_K, NKVf); p->src[2] = slot_src(slots, WS_FA_V, NKVf);
+        p->src[0] = slot_src(slots, WS_FA_Q, NQf, syn); p->src[1] = slot_src(slots, WS_FA_K, NKVf, syn); p->src[2] = slot_src(slots, WS_FA_V, NKVf, syn);
         p->cs = (int*)malloc(sizeof(int) * N); p->ci = (int*)malloc(sizeof(int) * N);
         if (!p->cs || !p->ci) return LB_ERR_NOMEM;
         for (int n = 0; n < N; n++) { /* per query head 512 columns (query, gate), then the KV head(s) */
@@ -327,14 +342,14 @@ static int plan_make(const lb_model_cfg* c, int R, int T, int fa, int which, con
         p->k0 = 0; p->k1 = H / 128;
     } else if (which == 2) {
         N = 2 * Is;
-        p->src[0] = slot_src(slots, WS_GATE, I); p->src[1] = slot_src(slots, WS_UP, I);
+        p->src[0] = slot_src(slots, WS_GATE, I, syn); p->src[1] = slot_src(slots, WS_UP, I, syn);
         p->cs = (int*)malloc(sizeof(int) * N); p->ci = (int*)malloc(sizeof(int) * N);
         if (!p->cs || !p->ci) return LB_ERR_NOMEM;
         for (int n = 0; n < N; n++) { int blk = n / 64; p->cs[n] = blk & 1; p->ci[n] = R * Is + (blk >> 1) * 64 + n % 64; }
         p->k0 = 0; p->k1 = H / 128;
     } else { /* row-parallel: out / o projection (which 1), down projection (which 3) */
         N = H;
-        p->src[0] = slot_src(slots, which == 3 ? WS_DOWN : (fa ? WS_FA_O : WS_DN_OUT), H);
+        p->src[0] = slot_src(slots, which == 3 ? WS_DOWN : (fa ? WS_FA_O : WS_DN_OUT), H, syn);
         p->cs = (int*)calloc((size_t)N, sizeof(int)); p->ci = (int*)malloc(sizeof(int) * N);
         if (!p->cs || !p->ci) return LB_ERR_NOMEM;
         for (int n = 0; n < N; n++) p->ci[n] = n;
@@ -352,7 +367,7 @@ LB_API int lb_model_shard_host(const lb_model_cfg* cfg, int tp_rank, int tp_size
                                int* K_out, int* N_out) {
     if (!cfg || !slots || which < 0 || which > 3 || tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return LB_ERR_INVALID;
     shard_plan p;
-    int st = plan_make(cfg, tp_rank, tp_size, is_fa(cfg, layer), which, slots, &p);
+    int st = plan_make(cfg, tp_rank, tp_size, is_fa(cfg, layer), which, slots, NULL, &p);
     if (st == LB_OK) {
         if (K_out) *K_out = (p.k1 - p.k0) * 128;
         if (N_out) *N_out = p.N;
@@ -362,14 +377,18 @@ LB_API int lb_model_shard_host(const lb_model_cfg* cfg, int tp_rank, int tp_size
     return st;
 }
 
-LB_API int lb_model_load_layer(lb_model* m, int layer, const void* const* slots) {
+/* syn != NULL: the int4 tensors (slots 0-8 or 0-11, and 15-23) are not in `slots` but drawn from the generator */
+static int load_layer(lb_model* m, int layer, const void* const* slots, const synth_t* syn) {
     if (!m || !slots || layer < 0 || layer >= m->cfg.n_layers) return LB_ERR_INVALID;
     const lb_model_cfg* c = &m->cfg;
     layer_t* L = &m->L[layer];
     if (L->loaded) return lb_fail(m->c, LB_ERR_STATE, "model: layer %d already loaded", layer);
     LB_CU(m->c, lb_drv.CtxSetCurrent(m->c->cu_ctx));
     const int H = c->hidden, R = m->tp_rank, T = m->tp_size;
-    if (!L->is_fa) {
+    if (syn) {
+        static const int need_dn[] = {9, 10, 11, 12, 13, 14, 24, 25}, need_fa[] = {12, 13, 24, 25};
+        LB_TRY(slots_present(m, slots, L->is_fa ? need_fa : need_dn, L->is_fa ? 4 : 8, layer));
+    } else if (!L->is_fa) {
         static const int need[] = {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22, 23, 24, 25};
         LB_TRY(slots_present(m, slots, need, 26, layer));
     } else {
@@ -379,7 +398,7 @@ LB_API int lb_model_load_layer(lb_model* m, int layer, const void* const* slots)
     q4_mat* mats[4] = {&L->w_in, &L->w_out, &L->w_gateup, &L->w_down};
     for (int which = 0; which < 4; which++) {
         shard_plan p;
-        int st = plan_make(c, R, T, L->is_fa, which, slots, &p);
+        int st = plan_make(c, R, T, L->is_fa, which, slots, syn, &p);
         if (st == LB_OK) st = build_q4(m, mats[which], p.src, p.cs, p.ci, p.N, p.k0, p.k1);
         if (st == LB_OK && lb_gemv_chain_supports(m->c, mats[which]->K, mats[which]->N, which == 2) == LB_OK) {
             /* second copy in the chain kernel's layout: every SM's columns contiguous */
@@ -423,6 +442,8 @@ LB_API int lb_model_load_layer(lb_model* m, int layer, const void* const* slots)
     return LB_OK;
 }
 
+LB_API int lb_model_load_layer(lb_model* m, int layer, const void* const* slots) { return load_layer(m, layer, slots, NULL); }
+
 LB_API int lb_model_load_globals(lb_model* m, const void* const* g) {
     if (!m || !g || !g[0] || !g[1] || !g[2]) return LB_ERR_INVALID;
     if (m->globals_loaded) return lb_fail(m->c, LB_ERR_STATE, "model: globals already loaded");
@@ -437,44 +458,17 @@ LB_API int lb_model_load_globals(lb_model* m, const void* const* g) {
 }
 
 /* ---- seeded synthetic weights ------------------------------------------------------------ */
-static void* gen_q4_slot(int which, size_t K, size_t N, uint64_t seed, uint64_t stream) {
-    if (which == 0) { uint32_t* p = (uint32_t*)malloc(K / 8 * N * 4); if (p) lb_fill_u32(p, K / 8 * N, seed, stream); return p; }
-    if (which == 1) { uint16_t* p = (uint16_t*)malloc(K / 128 * N * 2); if (p) lb_fill_scales_f16(p, K / 128 * N, seed, stream); return p; }
-    uint32_t* p = (uint32_t*)malloc(K / 128 * (N / 8) * 4);
-    if (p) lb_fill_u32(p, K / 128 * (N / 8), seed, stream);
-    return p;
-}
-
 LB_API int lb_model_fill_synthetic(lb_model* m, uint64_t seed) {
     if (!m) return LB_ERR_INVALID;
     const lb_model_cfg* c = &m->cfg;
-    const size_t H = c->hidden, I = c->inter;
+    const size_t H = c->hidden;
     for (int l = 0; l < c->n_layers; l++) {
         void* s[LB_WS_SLOTS];
         memset(s, 0, sizeof s);
         const uint64_t base = (uint64_t)(l + 1) * 100;
         const int fa = is_fa(c, l);
-        struct { int slot; size_t K, N; } q4[7];
-        int nq = 0;
-        if (!fa) {
-            q4[nq].slot = WS_DN_QKV; q4[nq].K = H; q4[nq++].N = (size_t)(2 * c->dn_k_heads + c->dn_v_heads) * 128;
-            q4[nq].slot = WS_DN_Z; q4[nq].K = H; q4[nq++].N = (size_t)c->dn_v_heads * 128;
-            q4[nq].slot = WS_DN_OUT; q4[nq].K = (size_t)c->dn_v_heads * 128; q4[nq++].N = H;
-        } else {
-            q4[nq].slot = WS_FA_Q; q4[nq].K = H; q4[nq++].N = (size_t)2 * c->fa_q_heads * 256;
-            q4[nq].slot = WS_FA_K; q4[nq].K = H; q4[nq++].N = (size_t)c->fa_kv_heads * 256;
-            q4[nq].slot = WS_FA_V; q4[nq].K = H; q4[nq++].N = (size_t)c->fa_kv_heads * 256;
-            q4[nq].slot = WS_FA_O; q4[nq].K = (size_t)c->fa_q_heads * 256; q4[nq++].N = H;
-        }
-        q4[nq].slot = WS_GATE; q4[nq].K = H; q4[nq++].N = I;
-        q4[nq].slot = WS_UP; q4[nq].K = H; q4[nq++].N = I;
-        q4[nq].slot = WS_DOWN; q4[nq].K = I; q4[nq++].N = H;
         int ok = 1;
-        for (int i = 0; i < nq; i++)
-            for (int w = 0; w < 3; w++) {
-                s[q4[i].slot + w] = gen_q4_slot(w, q4[i].K, q4[i].N, seed, base + q4[i].slot + w);
-                ok &= s[q4[i].slot + w] != NULL;
-            }
+        const synth_t syn = {seed, base}; /* the int4 tensors: only this shard's elements are drawn, inside the re-layout */
         uint16_t* in_norm = (uint16_t*)malloc(H * 2); uint16_t* post_norm = (uint16_t*)malloc(H * 2);
         ok &= in_norm && post_norm;
         if (ok) {
@@ -507,7 +501,7 @@ LB_API int lb_model_fill_synthetic(lb_model* m, uint64_t seed) {
             }
             s[WS_FA_Q_NORM] = qn; s[WS_FA_K_NORM] = kn;
         }
-        int st = ok ? lb_model_load_layer(m, l, (const void* const*)s) : lb_fail(m->c, LB_ERR_NOMEM, "model: host staging");
+        int st = ok ? load_layer(m, l, (const void* const*)s, &syn) : lb_fail(m->c, LB_ERR_NOMEM, "model: host staging");
         for (int i = 0; i < LB_WS_SLOTS; i++) free(s[i]);
         if (st != LB_OK) return st;
     }
@@ -649,6 +643,7 @@ static int issue_step(lb_model* m) {
             p.splits = lb_attn_mma_splits(c, cfg->max_ctx, m->HKV);
             p.status = (uint32_t*)c->dev_status;
             p.coop = m->HKV * p.splits <= c->sm_count;
+            p.max_ctx = cfg->max_ctx;
             p.in_dtype = 1; p.gate_stride = 512; p.q_stride = 512;
             p.rot_dims = cfg->rot_dims; p.rope_theta = cfg->rope_theta; p.eps = cfg->eps;
             for (int i = 0; i < cfg->rot_dims / 2; i++)
@@ -710,9 +705,10 @@ LB_API int lb_model_set_input(lb_model* m, int token, int pos) {
     if (!m) return LB_ERR_INVALID;
     if (token < 0 || token >= m->cfg.vocab || pos < 0 || pos >= m->cfg.max_ctx)
         return lb_fail(m->c, LB_ERR_INVALID, "model: token %d / position %d out of range", token, pos);
-    m->h_next[1] = token; m->h_next[2] = pos;
-    LB_CU(m->c, lb_drv.MemcpyHtoDAsync(m->d_token, &m->h_next[1], 4, m->c->stream));
-    LB_CU(m->c, lb_drv.MemcpyHtoDAsync(m->d_pos, &m->h_next[2], 4, m->c->stream));
+    /* by value, in stream order: back-to-back calls cannot overwrite each other's staging */
+    LB_CU(m->c, lb_drv.MemsetD32Async(m->d_token, (unsigned)token, 1, m->c->stream));
+    LB_CU(m->c, lb_drv.MemsetD32Async(m->d_pos, (unsigned)pos, 1, m->c->stream));
+    m->host_pos = pos;
     return LB_OK;
 }
 
@@ -730,6 +726,7 @@ LB_API int lb_model_decode(lb_model* m, int token, int pos, int* next_out) {
     LB_CU(m->c, lb_drv.CtxSetCurrent(m->c->cu_ctx));
     LB_TRY(lb_model_set_input(m, token, pos));
     LB_TRY(issue_step(m));
+    m->host_pos = pos + 1;
     return lb_model_read_next(m, next_out);
 }
 
@@ -751,7 +748,15 @@ LB_API int lb_model_capture(lb_model* m) {
 LB_API int lb_model_replay(lb_model* m, int n_steps) {
     if (!m || n_steps < 0) return LB_ERR_INVALID;
     if (!m->graph) return lb_fail(m->c, LB_ERR_STATE, "model: replay before capture");
-    for (int i = 0; i < n_steps; i++) LB_TRY(lb_graph_launch(m->c, m->graph));
+    /* every step appends one KV row at its position and advances the position on the device: refuse what would run past
+     * the caches before anything is launched */
+    if (m->host_pos + n_steps > m->cfg.max_ctx)
+        return lb_fail(m->c, LB_ERR_INVALID, "model: %d steps from position %d run past the context of %d rows", n_steps, m->host_pos,
+                       m->cfg.max_ctx);
+    for (int i = 0; i < n_steps; i++) {
+        LB_TRY(lb_graph_launch(m->c, m->graph));
+        m->host_pos++;
+    }
     return LB_OK;
 }
 

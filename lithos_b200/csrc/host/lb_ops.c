@@ -281,6 +281,7 @@ int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K,
     p.w = (const uint16_t*)w; p.x = (const void*)x; p.y = (float*)y; p.norm_w = (const void*)norm_w;
     p.N = N; p.K = K; p.x_mode = x_mode; p.eps = eps;
     p.part_val = (float*)part_val; p.part_idx = (int32_t*)part_idx;
+    p.status = (uint32_t*)c->dev_status;
     int ctas = lb_dense_ctas(c, N, K);
     void* params[] = {&p};
     if (dense_streams(c, N, K))

@@ -64,6 +64,13 @@ float lb_bf16_to_f32(uint16_t b) {
     return f;
 }
 
+/* single elements of the streams lb_fill_u32 / lb_fill_scales_f16 produce (the synthetic model builder draws only the
+ * elements of its own tensor-parallel shard) */
+uint32_t lb_rng_word(uint64_t seed, uint64_t stream, uint64_t i) { return (uint32_t)(lb_rng_u64(seed, stream, i) >> 32); }
+uint16_t lb_rng_scale_f16(uint64_t seed, uint64_t stream, uint64_t i) {
+    return lb_f32_to_f16(fabsf(normal_at(seed, stream, i)) * 0.01f + 1e-3f);
+}
+
 LB_API void lb_fill_u32(uint32_t* dst, size_t n, uint64_t seed, uint64_t stream) {
 #pragma omp parallel for schedule(static)
     for (size_t i = 0; i < n; i++) dst[i] = (uint32_t)(lb_rng_u64(seed, stream, i) >> 32);

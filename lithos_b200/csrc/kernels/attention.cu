@@ -33,6 +33,10 @@ __device__ __forceinline__ void attn_body(const lb_attn_params& p0, float* sm) {
 
     pdl_wait();
     if (p.pos_ptr) p.pos = p.pos_ptr[0];
+    if (p.max_ctx > 0 && (p.pos < 0 || p.pos >= p.max_ctx)) { // the position lies outside the caches: report it, touch nothing
+        if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && p.status) atomicExch(p.status, LB_DEV_POS_RANGE);
+        return;
+    }
     const bool last = split == p.splits - 1;
     const float LOG2E = 1.4426950408889634f;
     const float qscale = rsqrtf((float)AT_D) * LOG2E; // scores kept in log2 units

@@ -71,6 +71,10 @@ __device__ __forceinline__ void attn_mma_body(const lb_attn_params& p0, unsigned
     // The position comes from device memory written by the previous STEP (not the previous kernel), and cache rows
     // below it are not written by this step: the first block of every warp can be requested at once.
     if (p.pos_ptr) p.pos = p.pos_ptr[0];
+    if (p.max_ctx > 0 && (p.pos < 0 || p.pos >= p.max_ctx)) { // the position lies outside the caches: report it, touch nothing
+        if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && p.status) atomicExch(p.status, LB_DEV_POS_RANGE);
+        return;
+    }
     const int chunk = (((p.pos + p.splits - 1) / p.splits) + AM_ROWS - 1) & ~(AM_ROWS - 1); // rows per slice, whole blocks
     const int t0 = split * chunk, t1 = min(p.pos, t0 + chunk);
     const int n_blocks = t1 > t0 ? (t1 - t0 + AM_ROWS - 1) / AM_ROWS : 0;

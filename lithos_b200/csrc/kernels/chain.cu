@@ -401,16 +401,16 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                 const unsigned target = (unsigned)o * (unsigned)G;
                 bool ok = sh.bad == 0;
                 if (ok && ld_acquire_gpu(p.sync) < target) {
-                    const uint64_t t0 = globaltimer_ns();
+                    const uint64_t t0 = globaltimer_ns(), limit = lb_wait_limit_ns(p.status);
                     ok = false;
                     for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
                         if (ld_acquire_gpu(p.sync) >= target) { ok = true; break; }
                         if ((it & 255u) == 255u &&
-                            (globaltimer_ns() - t0 > LB_WAIT_NS || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u))
+                            (globaltimer_ns() - t0 > limit || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u))
                             break;
                     }
                 }
-                if (!ok) { atomicExch(p.status, LB_DEV_TIMEOUT_COUNTER); sh.bad = 1; }
+                if (!ok) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_COUNTER); sh.bad = 1; }
                 sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             }
             __syncthreads();
@@ -431,17 +431,17 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                 st_release_sys(tp.peer_flags[tid] + tp.rank, gen);
             }
             if (tid < tp.size) {
-                const uint64_t t0 = globaltimer_ns();
+                const uint64_t t0 = globaltimer_ns(), limit = lb_wait_limit_ns(p.status);
                 bool ok = sh.bad == 0;
                 if (ok) {
                     ok = false;
                     for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
                         // generations only grow; the (int) difference keeps the test valid across wrap-around
                         if ((int)(ld_acquire_sys(tp.my_flags + tid) - gen) >= 0) { ok = true; break; }
-                        if ((it & 63u) == 63u && (globaltimer_ns() - t0 > LB_WAIT_NS || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) break;
+                        if ((it & 63u) == 63u && (globaltimer_ns() - t0 > limit || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) break;
                     }
                 }
-                if (!ok) { atomicExch(p.status, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
+                if (!ok) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
             }
             __syncthreads();
             if (!sh.bad) {
@@ -510,7 +510,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             if ((int)(e.y & 31u) != o) break; // the stream has reached the next GEMV
             const uint32_t slot = warp * NS + m_use % NS;
             if (!__all_sync(0xffffffffu, mbar_wait(&full[slot], (m_use / NS) & 1))) { // the same answer in every lane
-                if (lane == 0) { atomicExch(p.status, LB_DEV_TIMEOUT_FULL); sh.bad = 1; }
+                if (lane == 0) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_FULL); sh.bad = 1; }
                 break;
             }
             const int pair = (int)((e.y >> 5) & 31u), g0 = (int)((e.y >> 10) & 4095u), gcount = (int)((e.y >> 22) & 7u);

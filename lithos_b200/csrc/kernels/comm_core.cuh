@@ -21,7 +21,7 @@ __device__ __forceinline__ bool tp_rendezvous(const lb_tp_params& p, unsigned g,
     if (t < p.size) {
         __threadfence_system(); // the partial written by the previous kernel is visible to peers before the flag
         st_release_sys(p.peer_flags[t] + p.rank, g);
-        const uint64_t t0 = globaltimer_ns();
+        const uint64_t t0 = globaltimer_ns(), limit = lb_wait_limit_ns(p.status);
         bool ok = false;
         // a wait that already ran out in this context is not repeated: every later exchange returns at once,
         // so a lost peer costs one time limit, not one per exchange
@@ -29,9 +29,9 @@ __device__ __forceinline__ bool tp_rendezvous(const lb_tp_params& p, unsigned g,
         for (unsigned it = 0; it < LB_WAIT_SPINS && !dead; ++it) {
             // generations only grow; (int) difference keeps the test valid across wrap-around
             if ((int)(ld_acquire_sys(p.my_flags + t) - g) >= 0) { ok = true; break; }
-            if ((it & 63u) == 63u && globaltimer_ns() - t0 > LB_WAIT_NS) break;
+            if ((it & 63u) == 63u && globaltimer_ns() - t0 > limit) break;
         }
-        if (!ok) { atomicExch(p.status, LB_DEV_TIMEOUT_PEER); *s_ok = false; }
+        if (!ok) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_PEER); *s_ok = false; }
     }
     __syncthreads();
     return *s_ok;

@@ -12,6 +12,7 @@
 #define LB_DEV_TIMEOUT_EMPTY 0x1002u   // producer gave up waiting for a free stage
 #define LB_DEV_TIMEOUT_PEER 0x1003u    // gave up waiting for a peer GPU's flag
 #define LB_DEV_TIMEOUT_COUNTER 0x1004u // gave up waiting on a split counter
+#define LB_DEV_POS_RANGE 0x1005u       // the decode position lies outside the KV cache: nothing was read or written
 
 #define LB_WAIT_SPINS (1u << 22)
 #define LB_WAIT_NS 2000000000ull // 2 s wall-clock cap on any single wait
@@ -22,6 +23,13 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
+}
+
+// Time limit of a wait on another CTA or GPU.  The context's status block is u32 [64]: word 0 is the status word the
+// kernels get a pointer to, words 2-3 hold the limit in nanoseconds as one u64 (0 = the built-in LB_WAIT_NS).
+__device__ __forceinline__ uint64_t lb_wait_limit_ns(const uint32_t* status) {
+    const uint64_t v = *reinterpret_cast<const volatile uint64_t*>(status + 2);
+    return v ? v : LB_WAIT_NS;
 }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

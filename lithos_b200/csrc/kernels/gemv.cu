@@ -517,7 +517,10 @@ extern "C" __global__ void __launch_bounds__(DS_WARPS * 32, 1) dense_bf16_stream
     int best_i = 0x7fffffff;
     for (int m = 0; m < my_rows; ++m) {
         const int slot = m % DS_SLOTS;
-        if (!__all_sync(0xffffffffu, mbar_wait(&bars[warp * DS_SLOTS + slot], (m / DS_SLOTS) & 1))) break; // bounded: the rows left keep y unset
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars[warp * DS_SLOTS + slot], (m / DS_SLOTS) & 1))) { // bounded: the rows left keep y unset
+            if (lane == 0 && p.status) atomicExch(p.status, LB_DEV_TIMEOUT_FULL);
+            break;
+        }
         const uint4* wr = reinterpret_cast<const uint4*>(ring + ((size_t)warp * DS_SLOTS + slot) * row_bytes);
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll 4

@@ -1,8 +1,8 @@
 /* Kernel parameter blocks shared by the host layer (C) and the kernels (CUDA).
  * Every struct is passed by value as the single kernel parameter, so the
  * layout here IS the launch ABI of the primary entry points.  (The entry
- * points that keep the reference's own positional parameter blocks live in
- * compat.cu and do not use these structs.) */
+ * points that keep the reference's own positional parameter blocks live under
+ * csrc/compat/, one source per cubin, and do not use these structs.) */
 #ifndef LB_KERNEL_PARAMS_H
 #define LB_KERNEL_PARAMS_H
 #include <stdint.h>
@@ -69,6 +69,7 @@ typedef struct {
  * A pipeline stage is LB_CHAIN_GC consecutive K-groups of one pair (4352 bytes), brought by one 1-D
  * bulk copy and consumed by ONE warp. */
 #define LB_CHAIN_MAX_OPS 32
+#define LB_CHAIN_PACK_VERSION 1      /* bumped whenever the strip-packed byte layout changes */
 #define LB_CHAIN_OP_GEMV 0
 #define LB_CHAIN_OP_DELTANET 1      /* the DeltaNet mixer of one layer (deltanet_core.cuh); ext = lb_dn_layer_params in device memory */
 #define LB_CHAIN_OP_ALLREDUCE 2     /* tensor parallel: x += sum over ranks of the partial vectors (comm_core.cuh); ext = lb_tp_params in device memory */
@@ -132,7 +133,7 @@ typedef struct {
     void* y;                 /* fp32 or fp16 [B, N] */
     int32_t K, N, B;
     int32_t y_f32;
-    uint32_t* status; /* device status word for bounded waits (may be NULL) */
+    uint32_t* status; /* device status word for bounded waits (the host layer always passes the context's) */
     int32_t reserved;
 } lb_bgemm_params;
 
@@ -147,6 +148,7 @@ typedef struct {
     float eps;
     float* part_val;  /* optional [gridDim.x]: largest y of the rows this CTA produced ... */
     int32_t* part_idx; /* ... and its row (smallest row on ties), for the greedy-sampling reduction */
+    uint32_t* status;  /* device status word: set when a bounded wait for a weight row runs out (the rows left stay unwritten) */
 } lb_dense_params;
 
 /* ---- gated DeltaNet step -------------------------------------------------- */
@@ -216,7 +218,8 @@ typedef struct {
     uint32_t* status;     /* device status word for bounded waits (attn_decode_mma); may be NULL */
     int32_t coop;         /* attn_decode_mma: the grid fits the SMs one CTA each, so the CTAs of a KV head may wait for each
                              other and share the slice merge (counters[kv] arrivals, counters[8 + kv] finished) */
-    int32_t pad_;
+    int32_t max_ctx;      /* rows the caches hold (0 = not checked): a position outside [0, max_ctx) sets status
+                             LB_DEV_POS_RANGE and the kernel returns without reading or writing a cache row */
 } lb_attn_params;
 
 /* ---- tensor-parallel exchange (comm.cu) ----------------------------------------------- */

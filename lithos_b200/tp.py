@@ -19,6 +19,14 @@ def _sigs():
     L.lb_comm_create.argtypes = [vp, i32, i32, i32, C.POINTER(vp)]
     L.lb_comm_handle.argtypes = [vp, vp]
     L.lb_comm_open.argtypes = [vp, vp]
+    L.lb_comm_set_peer.argtypes = [vp, i32, C.c_uint64]
+    L.lb_comm_buffer.argtypes = [vp]
+    L.lb_comm_buffer.restype = C.c_uint64
+    L.lb_comm_bytes.argtypes = [vp]
+    L.lb_comm_bytes.restype = C.c_size_t
+    L.lb_comm_flags_offset.argtypes = [vp]
+    L.lb_comm_flags_offset.restype = C.c_size_t
+    L.lb_comm_allreduce.argtypes = [vp, C.c_uint64, i32, i32]
     L.lb_comm_destroy.argtypes = [vp]
     L.lb_comm_destroy.restype = None
     L.lb_model_set_comm.argtypes = [vp, vp]
@@ -42,6 +50,26 @@ class Comm:
         blob = b"".join(handles)
         assert len(blob) == 64 * self.size
         self.ctx._check(lib().lb_comm_open(self.h, C.c_char_p(blob)))
+
+    def set_peer(self, rank: int, buffer_ptr: int):
+        """a peer whose exchange buffer this process can address directly (no IPC handle)"""
+        self.ctx._check(lib().lb_comm_set_peer(self.h, rank, buffer_ptr))
+
+    @property
+    def buffer(self) -> int:
+        return lib().lb_comm_buffer(self.h)
+
+    @property
+    def nbytes(self) -> int:
+        return lib().lb_comm_bytes(self.h)
+
+    @property
+    def flags_offset(self) -> int:
+        return lib().lb_comm_flags_offset(self.h)
+
+    def allreduce(self, x, n: int, slot: int = 0):
+        """x[0..n) += sum over ranks of the partial vectors in `slot` of every rank's buffer (one stand-alone exchange)"""
+        self.ctx._check(lib().lb_comm_allreduce(self.h, x.ptr, n, slot))
 
     def close(self):
         if self.h:

@@ -132,10 +132,11 @@ def test_attention_fixture(ctx, lb):
     assert np.array_equal(v_row, G["at_v_new"])
 
 
-@pytest.mark.parametrize("L", [1, 2, 77, 4096, 32768])
+@pytest.mark.parametrize("L", [1, 2, 77, 4096, 32768, 131072])
 def test_attention_config2_vs_oracle(ctx, lb, oracle, L):
-    """BASELINE config 2 (24 query / 4 KV heads, head_dim 256, RoPE on 64 dims, theta 1e7) at context
-    lengths the oracle finishes in seconds; L = 1 and 2 are the empty / single-row cache edge cases."""
+    """BASELINE config 2 (24 query / 4 KV heads, head_dim 256, RoPE on 64 dims, theta 1e7) at all three context
+    lengths of the sweep (the oracle needs a few seconds at 131072); L = 1 and 2 are the empty / single-row cache
+    edge cases."""
     HQ, HKV = 24, 4
     c = attention_case(31 + L, L, HQ, HKV)
     f = oracle.bf16_to_f32

@@ -206,3 +206,32 @@ def test_checkpoint_and_rollback(ctx, lb, oracle):
         third.append(tok)
     assert third == first
     gm.close()
+
+
+def test_weights_loaded_from_a_weight_index_file(ctx, lb, oracle, tmp_path):
+    """lb_save_weights -> weight_index.bin + shard -> lb_load_weights: the same tokens and bit-identical logits as the
+    model loaded from the host tensors directly"""
+    from lithos_b200 import model as M, weights as W
+    cfg = M.tiny(max_ctx=32)
+    slots = [M.synthetic_layer_slots(cfg, 11, l) for l in range(cfg.n_layers)]
+    glob = M.synthetic_globals(cfg, 11)
+    W.save_weights(tmp_path, cfg, slots, glob)
+    a, b = M.Model(ctx, cfg), M.Model(ctx, cfg)
+    W.load_weights(a, tmp_path)
+    for l in range(cfg.n_layers):
+        b.load_layer(l, slots[l])
+    b.load_globals(glob)
+    ta = tb = 9
+    for pos in range(10):
+        ta, tb = a.decode(ta, pos), b.decode(tb, pos)
+        assert ta == tb
+    assert np.array_equal(a.logits(), b.logits())
+    with pytest.raises(lb.LithosError) as e:          # a second load into the same model is refused, nothing is overwritten
+        W.load_weights(a, tmp_path)
+    assert e.value.status == lb.LB_ERR_STATE
+    c = M.Model(ctx, cfg)
+    with pytest.raises(lb.LithosError) as e:
+        W.load_weights(c, tmp_path / "nowhere")
+    assert e.value.status == lb.LB_ERR_IO
+    for m in (a, b, c):
+        m.close()

@@ -1,9 +1,9 @@
 """GPU: lb_attention_decode_noalloc, the decode-attention entry point for callers that cannot allocate
 (their own graph capture, pre-sized real-time loops, plugins inside someone else's memory pool).  Its
-scratch is an array inside the library's device image.  Checked through the C ABI against the regular
-lb_attention_decode on the same inputs, two calls in a row (the second reuses whatever the first left
-in the array), within the tolerance the attention tests use (2e-3 of max|out|).  This file sorts last on
-purpose: a run that stops at the first failure has then already run every other test."""
+scratch is an array inside the library's device image.  Checked through the C ABI against the CPU oracle and
+against the regular lb_attention_decode on the same inputs, two calls in a row (the second reuses whatever the
+first left in the array), within the tolerance the attention tests use (2e-3 of max|out|).  This file sorts last
+on purpose: a run that stops at the first failure has then already run every other test."""
 import ctypes as C
 
 import numpy as np
@@ -20,7 +20,7 @@ def _device_sync():
     assert cuda.cuCtxSynchronize() == 0
 
 
-def test_noalloc_attention_matches_regular_entry_twice(ctx, lb):
+def test_noalloc_attention_matches_oracle_and_regular_entry_twice(ctx, lb, oracle):
     L_ = lb.lib()
     u64, i32 = C.c_uint64, C.c_int
     L_.lb_attention_decode_noalloc.restype = i32
@@ -29,6 +29,10 @@ def test_noalloc_attention_matches_regular_entry_twice(ctx, lb):
     err = C.create_string_buffer(256)
     for call, L in enumerate((777, 3000)):          # 12 slices, then the 16-slice cap
         c = attention_case(500 + call, L, HQ, HKV)
+        f = oracle.bf16_to_f32
+        kc_o, vc_o = c["kc"].copy(), c["vc"].copy()
+        want = oracle.attention_step(f(c["q"]), f(c["k_new"]), f(c["v_new"]), f(c["gate"]), f(c["q_norm_w"]),
+                                     f(c["k_norm_w"]), kc_o, vc_o, L - 1, HQ, HKV).ravel()
         outs = []
         for which in ("regular", "noalloc"):
             d = {n: ctx.to_device(c[n]) for n in ("q", "k_new", "v_new", "gate", "q_norm_w", "k_norm_w")}
@@ -51,7 +55,10 @@ def test_noalloc_attention_matches_regular_entry_twice(ctx, lb):
             for b in list(d.values()) + [d_kc, d_vc, d_out]:
                 b.free()
         assert np.isfinite(outs[1][0]).all()
-        assert rel_err_max(outs[1][0], outs[0][0]) <= 2e-3
+        assert rel_err_max(outs[1][0], want) <= 2e-3           # the checker of record: the CPU oracle
+        assert rel_err_max(outs[1][0], outs[0][0]) <= 2e-3     # and the existing entry point
+        kf, kw = f(outs[1][1]), f(kc_o[L - 1].ravel())
+        assert np.max(np.abs(kf - kw)) <= 2.0 ** -7 * np.max(np.abs(kw))
         assert np.array_equal(outs[1][1], outs[0][1])       # the appended key row: same arithmetic, same bits
 
 

@@ -16,10 +16,12 @@ def main():
     from lithos_b200 import model as M, tp
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     dist.init_process_group("gloo")
-    steps, seed = 24, 1234
+    steps, seed, P0 = 24, 1234, 20
     cfg = M.tiny(max_ctx=64)
     if world == 4:      # the tiny model has 2 key heads: use a 4-way splittable variant
         cfg.dn_k_heads, cfg.dn_v_heads, cfg.fa_q_heads, cfg.fa_kv_heads = 4, 12, 12, 2
+    if world == 8:      # 8-way splittable, and like the benchmark's model fewer KV heads (4) than GPUs: each is held by two ranks
+        cfg.dn_k_heads, cfg.dn_v_heads, cfg.fa_q_heads, cfg.fa_kv_heads = 8, 24, 24, 4
 
     def all_gather(b):
         out = [None] * world
@@ -31,9 +33,10 @@ def main():
     m = M.Model(ctx, cfg, rank, world)
     tp.attach(m, comm)
     m.fill_synthetic(seed)
+    m.seed_state(P0, seed)          # every rank takes its heads of ONE seeded state (as bench.py does)
     m.capture()
     dist.barrier()
-    m.set_input(5, 0)
+    m.set_input(5, P0)
     toks = []
     for _ in range(steps):
         m.replay(1)
@@ -46,8 +49,9 @@ def main():
     if rank == 0:
         ref = M.Model(ctx, cfg)
         ref.fill_synthetic(seed)
+        ref.seed_state(P0, seed)
         tok, want = 5, []
-        for pos in range(steps):
+        for pos in range(P0, P0 + steps):
             tok = ref.decode(tok, pos)
             want.append(tok)
         full = ref.logits()
