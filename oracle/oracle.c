@@ -377,6 +377,29 @@ ORC_API void orc_rope(float* x /*[heads,d] in place*/, int heads, int d, int rot
 /* [seq,n_kv,d]); natural-exp softmax with -inf initial maximum as in   */
 /* inference/attend_full.ls:186-196; scale 1/sqrt(d); output *= sigmoid */
 /* (gate) as attend_full.ls:236-248.  K,V bf16, fp32 maths.             */
+/* compat: the launcher's table-driven half-split rotation.  Tables as precompute_rope_tables fills them
+ * (src/launcher.s:3139-3148): t[p * half + i] = cosf / sinf(p * expf(-i * ln(theta) / half)), float32 libm calls;
+ * rotation of pair (i, i + d/2) over the whole head (src/launcher.s:2260-2272, kernels/rotate.sass). */
+ORC_API void orc_rope_tables(float* cos_t, float* sin_t, int n_pos, int half, float theta) {
+    const float step = logf(theta) / (float)half;
+    for (int p = 0; p < n_pos; p++)
+        for (int i = 0; i < half; i++) {
+            float a = (float)p * expf(-(float)i * step);
+            cos_t[(size_t)p * half + i] = cosf(a);
+            sin_t[(size_t)p * half + i] = sinf(a);
+        }
+}
+ORC_API void orc_rotate_half(float* x /*[heads,d] in place*/, int heads, int d, const float* cos_t, const float* sin_t, int pos) {
+    int half = d / 2;
+    for (int h = 0; h < heads; h++)
+        for (int i = 0; i < half; i++) {
+            float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+            float a = x[(size_t)h * d + i], b = x[(size_t)h * d + i + half];
+            x[(size_t)h * d + i] = a * c - b * s;
+            x[(size_t)h * d + i + half] = a * s + b * c;
+        }
+}
+
 /* ------------------------------------------------------------------ */
 ORC_API void orc_attention_decode(const float* q /*[HQ,d]*/, const uint16_t* kc, const uint16_t* vc /*[L,HKV,d]*/,
                                   const float* gate /*[HQ,d] or NULL*/, float* out, int L, int HQ, int HKV, int d) {

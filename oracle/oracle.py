@@ -262,6 +262,20 @@ def rope(x, heads: int, d: int, rot_dims: int, pos: int, theta: float):
     return x
 
 
+def rope_tables(n_pos: int, half: int, theta: float = 1e6):
+    """cos / sin tables [n_pos, half] as the reference launcher precomputes them (src/launcher.s:3139-3148)"""
+    c, s = np.empty((n_pos, half), np.float32), np.empty((n_pos, half), np.float32)
+    lib().orc_rope_tables(_p(c), _p(s), n_pos, half, C.c_float(theta))
+    return c, s
+
+
+def rotate_half(x, heads: int, d: int, cos_t, sin_t, pos: int):
+    """the launcher's half-split rotation of pairs (i, i + d/2) from the tables"""
+    x = _f32(x).copy()
+    lib().orc_rotate_half(_p(x), heads, d, _p(_f32(cos_t)), _p(_f32(sin_t)), pos)
+    return x
+
+
 def attention_decode(q, kc, vc, gate, L: int, HQ: int, HKV: int, d: int = 256):
     out = np.empty((HQ, d), dtype=np.float32)
     lib().orc_attention_decode(_p(_f32(q)), _p(kc), _p(vc), _p(_f32(gate)) if gate is not None else None, _p(out), L, HQ,

@@ -43,7 +43,8 @@ def test_kernel_images_are_built(lb):
     kdir = ROOT / "lithos_b200" / "kernels"
     for f in ("gemv.cubin", "chain.cubin", "batched.cubin", "batched_tc.cubin", "deltanet.cubin", "attention.cubin", "attention_mma.cubin", "small.cubin", "compat/gptq_gemv_safe.cubin", "compat/norm.cubin",
               "compat/activate.cubin", "compat/gate_sigmoid.cubin", "compat/reduce.cubin", "compat/embed_f16.cubin",
-              "compat/lm_head.cubin", "compat/sample.cubin"):
+              "compat/lm_head.cubin", "compat/sample.cubin", "compat/attention_score.cubin", "compat/recur.cubin", "compat/conv1d.cubin",
+              "compat/rotate.cubin"):
         assert (kdir / f).stat().st_size > 1000, f
 
 

@@ -111,3 +111,120 @@ def test_sample(ctx, lb):
     assert int(d_t.download(np.uint32, 1)[0]) == 0
     d_l.free()
     d_t.free()
+
+
+def test_attention_score_three_entries(ctx, lb, oracle):
+    """attention_score.cubin: the .ls parameter block on an fp32 and on a bf16 cache, and the launcher's 7-parameter
+    block; all against the oracle's soft-max attention (natural exp, -inf start), <= 2e-3 of max|out|"""
+    from helpers import attention_case, rel_err_max
+    HQ, HKV, L = 24, 4, 777
+    c = attention_case(901, L, HQ, HKV)
+    f = oracle.bf16_to_f32
+    q = f(c["q"]).astype(np.float32)
+    want = oracle.attention_decode(q, c["kc"], c["vc"], None, L, HQ, HKV)
+    d_q, d_o = ctx.to_device(q), ctx.alloc(HQ * 256 * 4)
+    kc32, vc32 = ctx.to_device(f(c["kc"])), ctx.to_device(f(c["vc"]))
+    kc16, vc16 = ctx.to_device(c["kc"]), ctx.to_device(c["vc"])
+    ls_block = lambda k, v, seq, cur: [u64(d_q), u64(k), u64(v), u64(d_o), C.c_uint32(256), C.c_uint32(seq), C.c_uint32(cur),
+                                       C.c_uint32(HKV), C.c_uint32(HQ)]
+    launch(ctx, lb, "attention_score.cubin", "attention_score", ls_block(kc32, vc32, L, L), HQ, 256)
+    assert rel_err_max(d_o.download(np.float32, HQ * 256), want.ravel()) <= 2e-3
+    d_o.zero()
+    launch(ctx, lb, "attention_score.cubin", "attention_score_bf16", ls_block(kc16, vc16, L + 50, L), HQ, 256)   # current_pos bounds it
+    assert rel_err_max(d_o.download(np.float32, HQ * 256), want.ravel()) <= 2e-3
+    d_o.zero()
+    launch(ctx, lb, "attention_score.cubin", "attention_score_launcher",
+           [u64(d_q), u64(kc32), u64(vc32), u64(d_o), C.c_uint32(L), C.c_uint32(256), C.c_uint32(HQ)], 24, 256)
+    assert rel_err_max(d_o.download(np.float32, HQ * 256), want.ravel()) <= 2e-3
+    # one attended row: the output is that row of V
+    launch(ctx, lb, "attention_score.cubin", "attention_score", ls_block(kc32, vc32, 1, 1), HQ, 256)
+    v0 = np.repeat(f(c["vc"])[0], HQ // HKV, axis=0)
+    np.testing.assert_allclose(d_o.download(np.float32, HQ * 256).reshape(HQ, 256), v0, rtol=1e-6, atol=0)
+
+
+def test_recur_deltanet_fused_and_launcher_alias(ctx, lb, oracle):
+    """recur.cubin: deltanet_fused with the .ls parameter block, 16 key heads x 3, three tokens, against the oracle
+    (which the fixture computed from the reference's kernel text pins); deltanet_step with the launcher's block"""
+    from helpers import rel_err_max
+    HK, G, T = 16, 3, 3
+    HV = HK * G
+    rng = np.random.default_rng(5)
+    state = (rng.standard_normal((HV, 128, 128)) * 0.02).astype(np.float32)
+    d_state = ctx.to_device(state)
+    d_out = ctx.alloc(HV * 128 * 4)
+    ref = state.copy()
+    for t in range(T):
+        q = rng.standard_normal((HK, 128)).astype(np.float32)
+        k = rng.standard_normal((HK, 128)).astype(np.float32)
+        q /= np.linalg.norm(q, axis=1, keepdims=True) * np.sqrt(128.0)
+        k /= np.linalg.norm(k, axis=1, keepdims=True)
+        v, z = rng.standard_normal((HV, 128)).astype(np.float32), rng.standard_normal((HV, 128)).astype(np.float32)
+        g, b = rng.uniform(0.3, 1.0, HV).astype(np.float32), rng.uniform(0.1, 0.9, HV).astype(np.float32)
+        want = oracle.deltanet_step(ref, q, k, v, z, g, b, HV, HK)
+        bufs = [ctx.to_device(a) for a in (q, k, v, z, g, b)]
+        launch(ctx, lb, "recur.cubin", "deltanet_fused", [u64(x) for x in bufs] + [u64(d_state), u64(d_out), C.c_uint32(128), C.c_uint32(G)], HK, 128)
+        assert rel_err_max(d_out.download(np.float32, HV * 128), want.ravel()) <= 1e-4
+    got = d_state.download(np.float32, HV * 128 * 128).reshape(HV, -1).astype(np.float64)
+    fro = np.linalg.norm(got - ref.reshape(HV, -1), axis=1) / np.linalg.norm(ref.reshape(HV, -1), axis=1)
+    assert fro.max() <= 1e-5
+    # the launcher's element-wise placeholder: state += value * key; output = query * state
+    n = 2048
+    s, qq, kk, vv = (rng.standard_normal(n).astype(np.float32) for _ in range(4))
+    d = [ctx.to_device(a) for a in (s, qq, kk, vv)]
+    d_o = ctx.alloc(n * 4)
+    launch(ctx, lb, "recur.cubin", "deltanet_step", [u64(d[0]), u64(d[1]), u64(d[1]), u64(d[2]), u64(d[3]), u64(d_o), C.c_uint32(n)], 8, 256)
+    s2 = (vv.astype(np.float64) * kk + s).astype(np.float32)
+    np.testing.assert_allclose(d[0].download(np.float32, n), s2, rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(d_o.download(np.float32, n), qq * s2, rtol=1e-6, atol=1e-7)
+
+
+def test_conv1d_three_slices_as_launched(ctx, lb, oracle):
+    """conv1d.cubin: Q, K and V slices of a DeltaNet layer's qkv vector, three calls per token as the launcher makes
+    them (in place), four tokens, against the oracle's conv1d_step on every slice"""
+    rng = np.random.default_rng(6)
+    slices = [(16, 128), (16, 128), (48, 128)]
+    for heads, ch in slices[1:]:                      # K-sized and V-sized slices (Q is the same shape as K)
+        N = heads * ch
+        w = (rng.standard_normal((4, N)) * 0.3).astype(np.float32)
+        hist = rng.standard_normal((3, N)).astype(np.float32)
+        d_w, d_h, d_x = ctx.to_device(w), ctx.to_device(hist), ctx.alloc(N * 4)
+        d_wb = ctx.to_device(oracle.f32_to_bf16(w))
+        d_h2, d_x2 = ctx.to_device(hist), ctx.alloc(N * 4)
+        h_ref, h_ref2 = hist.copy(), hist.copy()
+        wb = oracle.bf16_to_f32(oracle.f32_to_bf16(w)).reshape(4, N)
+        for t in range(4):
+            x = rng.standard_normal(N).astype(np.float32)
+            d_x.upload(x)
+            d_x2.upload(x)
+            launch(ctx, lb, "conv1d.cubin", "conv1d", [u64(d_x), u64(d_w), u64(d_h), u64(d_x), C.c_uint32(heads), C.c_uint32(ch)], (N + 255) // 256, 256)
+            y, h_ref = oracle.conv1d_step(x, w, h_ref)
+            np.testing.assert_allclose(d_x.download(np.float32, N), y, rtol=1e-6, atol=1e-6)
+            launch(ctx, lb, "conv1d.cubin", "conv1d_bf16w", [u64(d_x2), u64(d_wb), u64(d_h2), u64(d_x2), C.c_uint32(heads), C.c_uint32(ch)], (N + 255) // 256, 256)
+            y2, h_ref2 = oracle.conv1d_step(x, wb, h_ref2)
+            np.testing.assert_allclose(d_x2.download(np.float32, N), y2, rtol=1e-6, atol=1e-6)
+        assert np.array_equal(d_h.download(np.float32, 3 * N).reshape(3, N), h_ref)
+
+
+def test_rotate_table_driven_and_rope_interleaved(ctx, lb, oracle):
+    """rotate.cubin: `rotate` with the launcher's block and tables (half-split over 256 dims, theta 1e6, 24 query heads and
+    the 4 key heads that follow them); `rope` with the .ls block (interleaved pairs on the first 64 dims, theta 1e7)"""
+    rng = np.random.default_rng(7)
+    HQ, HKV, D, NPOS = 24, 4, 256, 64
+    cos_t, sin_t = oracle.rope_tables(NPOS, D // 2, 1e6)
+    buf = rng.standard_normal((HQ + 2 * HKV, D)).astype(np.float32)      # the launcher's q | k | v slices, back to back
+    d_b, d_c, d_s = ctx.to_device(buf), ctx.to_device(cos_t), ctx.to_device(sin_t)
+    from lithos_b200 import DeviceBuffer
+    k_view = DeviceBuffer.__new__(DeviceBuffer)
+    k_view.ctx, k_view.ptr, k_view.nbytes = ctx, d_b.ptr + HQ * D * 4, HKV * D * 4
+    pos = 37
+    launch(ctx, lb, "rotate.cubin", "rotate", [u64(d_b), u64(k_view), u64(d_c), u64(d_s), C.c_uint32(pos), C.c_uint32(D), C.c_uint32(HQ)], 24, 256)
+    got = d_b.download(np.float32, buf.size).reshape(buf.shape)
+    np.testing.assert_allclose(got[:HQ], oracle.rotate_half(buf[:HQ], HQ, D, cos_t, sin_t, pos).reshape(HQ, D), rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(got[HQ:HQ + HKV], oracle.rotate_half(buf[HQ:HQ + HKV], HKV, D, cos_t, sin_t, pos).reshape(HKV, D), rtol=1e-6, atol=1e-6)
+    assert np.array_equal(got[HQ + HKV:], buf[HQ + HKV:])               # the V slice behind K is untouched
+    for p in (5, 4100):
+        q, k = rng.standard_normal((HKV, D)).astype(np.float32), rng.standard_normal((HKV, D)).astype(np.float32)
+        d_q, d_k, d_qo, d_ko = ctx.to_device(q), ctx.to_device(k), ctx.alloc(q.nbytes), ctx.alloc(k.nbytes)
+        launch(ctx, lb, "rotate.cubin", "rope", [u64(d_q), u64(d_k), u64(d_qo), u64(d_ko), C.c_uint32(D), C.c_uint32(p)], HKV, 128)
+        np.testing.assert_allclose(d_qo.download(np.float32, q.size), oracle.rope(q, HKV, D, 64, p, 1e7).ravel(), rtol=0, atol=2e-6 * np.abs(q).max())
+        np.testing.assert_allclose(d_ko.download(np.float32, k.size), oracle.rope(k, HKV, D, 64, p, 1e7).ravel(), rtol=0, atol=2e-6 * np.abs(k).max())
