@@ -23,7 +23,7 @@ extern "C" __global__ void __launch_bounds__(1024) tp_allreduce_add(const __grid
     if (ok) {
         for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
             float s = 0.f;
-            for (int r = 0; r < p.size; ++r) s += __ldcv(p.partials[r] + (size_t)p.slot * p.n_max + i); // rank order
+            for (int r = 0; r < p.size; ++r) s += __ldcv(p.partials[r] + LB_TP_PARTIAL(p, p.slot, r) + i); // rank order
             p.x[i] += s;
         }
     }
@@ -67,7 +67,7 @@ extern "C" __global__ void __launch_bounds__(1024) tp_argmax_exchange(const __gr
             if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
         }
         if (lane == 0) { // publish (logit, global token) in this rank's exchange buffer
-            float* mine = const_cast<float*>(p.partials[p.rank]) + (size_t)p.slot * p.n_max;
+            float* mine = p.partials[p.rank] + LB_TP_PARTIAL(p, 2, 0) + 2 * p.rank; // every rank its own pair of words
             mine[0] = bv;
             reinterpret_cast<int*>(mine)[1] = bi == 0x7fffffff ? 0x7fffffff : bi + q.vocab_offset;
         }
@@ -80,7 +80,7 @@ extern "C" __global__ void __launch_bounds__(1024) tp_argmax_exchange(const __gr
         int gi = 0x7fffffff;
         if (ok)
             for (int r = 0; r < p.size; ++r) {
-                const float* rec = p.partials[r] + (size_t)p.slot * p.n_max;
+                const float* rec = p.partials[r] + LB_TP_PARTIAL(p, 2, 0) + 2 * r;
                 const float v = __ldcv(rec);
                 const int id = __ldcv(reinterpret_cast<const int*>(rec) + 1);
                 if (better(v, id, gv, gi)) { gv = v; gi = id; }

@@ -27,8 +27,10 @@ enum {
     LB_Y_F16 = 0,       /* y fp16 [N] = result */
     LB_Y_F32 = 1,       /* y fp32 [N] = result */
     LB_Y_F32_ACCUM = 2, /* y fp32 [N] += result (residual add) */
-    LB_Y_SWIGLU_F16 = 3 /* columns come in interleaved 64-wide blocks (gate block, up block, gate block, ...);
+    LB_Y_SWIGLU_F16 = 3, /* columns come in interleaved 64-wide blocks (gate block, up block, gate block, ...);
                            y fp16 [N/2] = silu(gate)*up */
+    LB_Y_TP_PUSH = 4    /* persistent chain under tensor parallelism only: the fp32 results are this rank's partial sums of a
+                           row-parallel projection and are stored straight into every rank's exchange buffer (ext = lb_tp_params) */
 };
 
 typedef struct {
@@ -73,6 +75,9 @@ typedef struct {
 #define LB_CHAIN_OP_GEMV 0
 #define LB_CHAIN_OP_DELTANET 1      /* the DeltaNet mixer of one layer (deltanet_core.cuh); ext = lb_dn_layer_params in device memory */
 #define LB_CHAIN_OP_ALLREDUCE 2     /* tensor parallel: x += sum over ranks of the partial vectors (comm_core.cuh); ext = lb_tp_params in device memory */
+#define LB_CHAIN_OP_ALLREDUCE_PUSHED 3 /* the same sum where the GEMV before it (y_mode LB_Y_TP_PUSH) has already stored its columns into every
+                                          rank's buffer: CTA c waits for the flags of its own columns only, no grid barrier before the entry */
+#define LB_CHAIN_BLOCK (LB_CHAIN_THREADS + 32) /* threads per CTA: the consumer warps and one warp that requests weights into L2 ahead of them */
 #define LB_CHAIN_WARPS 16            /* consumer warps; every warp streams its own stages */
 #define LB_CHAIN_THREADS (LB_CHAIN_WARPS * 32)
 #define LB_CHAIN_RECORD 544          /* bytes per (octet, K-group) */
@@ -107,6 +112,8 @@ typedef struct {
     int32_t max_pairs;    /* pairs (incl. a trailing single) of the widest strip of the chain */
     int32_t trigger_op;   /* griddepcontrol.launch_dependents is issued when this GEMV starts */
     int32_t tab_len;      /* entries of a warp's stage list: ceil(stages of the busiest CTA / warps) */
+    int32_t prefetch_bytes; /* bytes of this CTA's weight stream the extra warp keeps requested into L2 ahead of the consumers (0 = off) */
+    int32_t pad_;
     unsigned long long* timeline; /* optional [gridDim.x][LB_CHAIN_MAX_OPS][4] %globaltimer stamps of thread 0: reached the
                                      grid barrier, left it, activation table ready (or mixer started), entry finished */
 } lb_chain_params;
@@ -224,15 +231,27 @@ typedef struct {
 
 /* ---- tensor-parallel exchange (comm.cu) ----------------------------------------------- */
 #define LB_TP_MAX 8
+#define LB_TP_CTA_MAX 256 /* CTAs of a persistent chain that may own columns (>= SMs of the GPU) */
+/* Exchange buffer of one rank (every rank maps every peer's): float [2][size][n_max] partial vectors (slot = exchange
+ * parity, then the rank that produced the vector), float [n_max] for the sampling record, then the flag words.
+ * "Pull" exchanges (tp_allreduce_add, LB_CHAIN_OP_ALLREDUCE): rank q leaves its partial in ITS OWN buffer at (slot, q),
+ * raises flag [q] in every peer's pull-flag array, readers load the vector from q's buffer.
+ * "Pushed" exchanges (LB_Y_TP_PUSH + LB_CHAIN_OP_ALLREDUCE_PUSHED): CTA c of rank q stores its columns into EVERY rank's
+ * buffer at (slot, q), then raises flag [q][c] in every rank's push-flag array; readers load from their own buffer. */
 typedef struct {
     float* x;                          /* residual stream [n] on this GPU */
-    const float* partials[LB_TP_MAX];  /* every rank's exchange buffer: float [3][n_max] (peer pointers) */
-    unsigned* peer_flags[LB_TP_MAX];   /* every rank's flag array: unsigned [LB_TP_MAX] */
-    unsigned* my_flags;                /* this rank's flag array (local) */
+    float* partials[LB_TP_MAX];        /* every rank's exchange buffer (peer pointers) */
+    unsigned* peer_flags[LB_TP_MAX];   /* every rank's pull-flag array: unsigned [LB_TP_MAX] */
+    unsigned* my_flags;                /* this rank's pull-flag array (local) */
     unsigned* gen;                     /* this rank's generation counter (local, advanced by the kernel) */
     unsigned* status;
+    unsigned* peer_cta_flags[LB_TP_MAX]; /* every rank's push-flag array: unsigned [LB_TP_MAX][LB_TP_CTA_MAX] */
+    unsigned* my_cta_flags;            /* this rank's push-flag array (local) */
     int32_t n, n_max, slot, rank, size;
+    int32_t pad_;
 } lb_tp_params;
+/* float offset of partial vector (slot, rank q) inside an exchange buffer; slot 2 is the sampling record */
+#define LB_TP_PARTIAL(p, slot_, q) ((size_t)((slot_) == 2 ? 2 * (p).size : (slot_) * (p).size + (q)) * (size_t)(p).n_max)
 
 typedef struct {
     lb_tp_params tp;        /* slot = 2: the record (logit, token) lives at the start of that slot */

@@ -160,24 +160,34 @@ ORC_API void orc_gptq_dequant(const uint32_t* qweight, const uint16_t* scales, c
 /* y[n] = sum_k W(k,n) x[k], fp32 fma accumulation in ascending k
  * (minds/gptq_gemv_safe.ptx:248-310 K_LOOP; acc = fma(dq, x, acc)).
  * x is fp32 here; callers holding fp16 activations widen them first (exact). */
+/* Order in which the K products of a column are added: 0 = ascending k (the reference kernel's order within a thread,
+ * minds/gptq_gemv_safe.ptx:150-300), 1 = descending k.  Any order is a valid fp32 evaluation of the same sum; the second
+ * one exists so that a test can measure how far two valid evaluations of the whole decode step drift apart when every
+ * projection's input is rounded to fp16 (the activation contract), which bounds what a logit comparison can ask for. */
+static int g_sum_order = 0;
+ORC_API void orc_set_sum_order(int order) { g_sum_order = order ? 1 : 0; }
+
 static void gemv_core(const uint32_t* qw, const uint16_t* sc, const uint32_t* qz, const float* x, float* y, int K,
                       int N, int group) {
-    const int NB = 256;
+    const int NB = 256, rows = K / 8, rev = g_sum_order;
 #pragma omp parallel for schedule(static)
     for (int n0 = 0; n0 < N; n0 += NB) {
-        int nb = N - n0 < NB ? N - n0 : NB;
+        int nb = N - n0 < NB ? N - n0 : NB, cur_g = -1;
         float acc[256], s[256], bias[256];
         for (int i = 0; i < nb; i++) acc[i] = 0.f;
-        for (int kp = 0; kp < K / 8; kp++) {
-            if ((kp * 8) % group == 0) {
-                int g = kp * 8 / group;
+        for (int t = 0; t < rows; t++) {
+            const int kp = rev ? rows - 1 - t : t;
+            const int g = kp * 8 / group;
+            if (g != cur_g) {
+                cur_g = g;
                 for (int i = 0; i < nb; i++) {
                     s[i] = h2f(sc[(size_t)g * N + n0 + i]);
                     bias[i] = -(float)z_at(qz, N, g, n0 + i) * s[i];
                 }
             }
             const uint32_t* row = qw + (size_t)kp * N + n0;
-            for (int j = 0; j < 8; j++) {
+            for (int jj = 0; jj < 8; jj++) {
+                const int j = rev ? 7 - jj : jj;
                 float xv = x[kp * 8 + j];
                 for (int i = 0; i < nb; i++) {
                     float dq = fmaf((float)((row[i] >> (4 * j)) & 0xFu), s[i], bias[i]);

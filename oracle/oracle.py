@@ -68,6 +68,11 @@ def num_threads() -> int:
     return lib().orc_num_threads()
 
 
+def set_sum_order(order: int) -> None:
+    """0: every projection adds its K products in ascending k, 1: in descending k (both valid fp32 evaluations)"""
+    lib().orc_set_sum_order(int(order))
+
+
 def set_num_threads(n: int) -> None:
     lib().orc_set_num_threads(int(n))
 
