@@ -264,11 +264,12 @@ int lb_comm_open(lb_comm* comm, const void* handles_size_x_64);
 /* A peer whose buffer this process can address directly (a second GPU of the same process with peer access enabled):
  * its lb_comm_buffer, lb_comm_bytes long, instead of an IPC handle. */
 int lb_comm_set_peer(lb_comm* comm, int rank, uint64_t peer_buffer);
-uint64_t lb_comm_buffer(const lb_comm* comm);      /* this rank's exchange buffer: float [3][n_max] partial slots, then the flags */
+uint64_t lb_comm_buffer(const lb_comm* comm);      /* this rank's exchange buffer: float [2][size][n_max] partial vectors, a sampling record, then the flags */
 size_t lb_comm_bytes(const lb_comm* comm);
+size_t lb_comm_partial_offset(const lb_comm* comm, int slot, int rank); /* byte offset of rank's partial vector of slot 0 / 1 */
 size_t lb_comm_flags_offset(const lb_comm* comm);  /* byte offset of the flag array u32 [8] (one generation word per rank) */
 /* One exchange outside the decode step: x[0..n) += the sum over ranks, in rank order, of the partial vectors every
- * rank has left in slot 0 or 1 of its own buffer.  Bounded: a rank that never publishes makes the kernel return with
+ * rank has left at lb_comm_partial_offset(slot, its rank) of its own buffer.  Bounded: a rank that never publishes makes the kernel return with
  * status 0x1003 after the wait limit. */
 int lb_comm_allreduce(lb_comm* comm, uint64_t x_f32, int n, int slot);
 void lb_comm_destroy(lb_comm* comm);

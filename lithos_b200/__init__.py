@@ -108,6 +108,7 @@ def lib() -> C.CDLL:
     sig("lb_gemv_pack", i32, vp, u64, u64, u64, i32, i32, i32, u64)
     sig("lb_set_chain_reserve", None, vp, i32)
     sig("lb_set_chain_timeline", None, vp, u64)
+    sig("lb_gemv_pack_version", i32)
     sig("lb_gptq_dequant", i32, vp, u64, u64, u64, u64, i32, i32)
     sig("lb_gemm_int4", i32, vp, u64, u64, u64, u64, u64, i32, i32, i32, i32)
     sig("lb_gptq_unpack", i32, vp, u64, u64, i32, i32)

@@ -115,6 +115,8 @@ int lb_chain_fill_gemv(lb_ctx* c, lb_chain_op* d, const lb_gemv_op* o, int i) {
     const int swiglu = o->y_mode == LB_Y_SWIGLU_F16;
     const char* why = chain_shape_problem(c, o->K, o->N, swiglu);
     if (why) return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: K=%d N=%d: %s", i, o->K, o->N, why);
+    if (o->x_mode == LB_X_F32_HEADNORM_SILU && o->K > 8 * LB_CHAIN_THREADS * 2)
+        return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: the per-head norm prologue takes K <= %d (K=%d)", i, 8 * LB_CHAIN_THREADS * 2, o->K);
     if (o->K > 8 * LB_CHAIN_THREADS * 5) return lb_fail(c, LB_ERR_INVALID, "GEMV chain[%d]: K=%d above %d", i, o->K, 8 * LB_CHAIN_THREADS * 5);
     memset(d, 0, sizeof *d);
     d->type = LB_CHAIN_OP_GEMV;

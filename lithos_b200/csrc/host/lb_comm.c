@@ -6,8 +6,9 @@
 struct lb_comm {
     lb_ctx* c;
     int rank, size, n_max;
-    size_t flags_off, bytes;
-    CUdeviceptr buf;              /* this rank's buffer: float [3][n_max] | unsigned flags[8] | unsigned gen */
+    size_t flags_off, cta_flags_off, bytes;
+    CUdeviceptr buf;              /* this rank's buffer: float [2][size][n_max] partials | float [n_max] sampling record |
+                                     unsigned pull flags [8] | unsigned gen | unsigned push flags [8][LB_TP_CTA_MAX] (params.h) */
     CUdeviceptr peer[LB_TP_MAX];  /* every rank's buffer as seen from this GPU (peer[rank] == buf) */
     int opened[LB_TP_MAX];
 };
@@ -18,8 +19,9 @@ LB_API int lb_comm_create(lb_ctx* c, int rank, int size, int n_max, lb_comm** ou
     lb_comm* m = (lb_comm*)calloc(1, sizeof *m);
     if (!m) return LB_ERR_NOMEM;
     m->c = c; m->rank = rank; m->size = size; m->n_max = n_max;
-    m->flags_off = ((size_t)3 * n_max * 4 + 255) & ~(size_t)255;
-    m->bytes = m->flags_off + 256;
+    m->flags_off = ((size_t)(2 * size + 1) * n_max * 4 + 255) & ~(size_t)255;
+    m->cta_flags_off = m->flags_off + 256;
+    m->bytes = m->cta_flags_off + (size_t)LB_TP_MAX * LB_TP_CTA_MAX * 4;
     LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
     CUresult r = lb_drv.MemAlloc(&m->buf, m->bytes);
     if (r != CUDA_SUCCESS) { free(m); return lb_cu(c, r, "cuMemAlloc(exchange buffer)"); }
@@ -86,10 +88,12 @@ int lb_comm_fill(const lb_comm* m, lb_tp_params* p, int slot, int n) {
     memset(p, 0, sizeof *p);
     for (int r = 0; r < m->size; r++) {
         if (!m->peer[r]) return lb_fail(m->c, LB_ERR_STATE, "exchange buffer of rank %d not opened", r);
-        p->partials[r] = (const float*)m->peer[r];
+        p->partials[r] = (float*)m->peer[r];
         p->peer_flags[r] = (unsigned*)(m->peer[r] + m->flags_off);
+        p->peer_cta_flags[r] = (unsigned*)(m->peer[r] + m->cta_flags_off);
     }
     p->my_flags = (unsigned*)(m->buf + m->flags_off);
+    p->my_cta_flags = (unsigned*)(m->buf + m->cta_flags_off);
     p->gen = (unsigned*)(m->buf + m->flags_off + 128);
     p->status = (unsigned*)m->c->dev_status;
     p->n = n; p->n_max = m->n_max; p->slot = slot; p->rank = m->rank; p->size = m->size;
@@ -107,4 +111,9 @@ LB_API int lb_comm_allreduce(lb_comm* m, uint64_t x, int n, int slot) {
     return lb_launch(m->c, LBK_tp_allreduce_add, 1, 1, 1, 1024, 0, params, 1);
 }
 
-uint64_t lb_comm_slot_ptr(const lb_comm* m, int slot) { return (uint64_t)m->buf + (uint64_t)slot * m->n_max * 4; }
+/* where rank `rank`'s partial vector of exchange slot `slot` lives inside an exchange buffer (bytes from its start) */
+LB_API size_t lb_comm_partial_offset(const lb_comm* m, int slot, int rank) {
+    if (!m) return 0;
+    return (size_t)(slot == 2 ? 2 * m->size : slot * m->size + rank) * (size_t)m->n_max * 4;
+}
+uint64_t lb_comm_slot_ptr(const lb_comm* m, int slot) { return (uint64_t)m->buf + lb_comm_partial_offset(m, slot, m->rank); }

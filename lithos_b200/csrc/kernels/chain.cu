@@ -34,6 +34,7 @@
 
 #define CH_W LB_CHAIN_WARPS
 #define CH_GC LB_CHAIN_GC
+#define CH_SYNC() __syncthreads()
 
 __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     unsigned v;
@@ -144,6 +145,7 @@ template <int NI>
 __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& sh, uint32_t* xdig, float* xsumf, int tid, bool write_x) {
     const int lane = tid & 31, warp = tid >> 5;
     const int rows = op.K / 8;
+    float pre_max = -1.f; // >= 0: the largest |h| is already known (no second block-wide exchange)
     uint32_t hv[NI][4]; // the row as 8 fp16 values
     if (op.x_mode == LB_X_F16) {
 #pragma unroll
@@ -168,35 +170,43 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
             v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
         }
         if (op.x_mode == LB_X_F32_RMSNORM) {
-            // h = x * rsqrt(mean x^2 + eps) * (1 + w): the rows held by the block's threads are the whole vector
+            // h = (x * (1 + w)) * rsqrt(mean x^2 + eps): the rows held by the block's threads are the whole vector.  The
+            // product with (1 + w) comes first, so that the sum of squares and the largest |x (1 + w)| go through ONE
+            // block-wide exchange: rounding is monotonic, so the largest |h| is the largest |x (1 + w)| times the factor.
             uint4 wr[NI];
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
                 const int r = tid + i * LB_CHAIN_THREADS;
                 wr[i] = r < rows ? __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op.aux0) + r * 8)) : make_uint4(0u, 0u, 0u, 0u);
             }
-            float ss = 0.f;
-#pragma unroll
-            for (int i = 0; i < NI; ++i)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
-            ss = warp_sum(ss);
-            if (lane == 0) sh.scratch[warp] = ss;
-            __syncthreads();
-            float tot = 0.f;
-#pragma unroll
-            for (int w = 0; w < CH_W; ++w) tot += sh.scratch[w];
-            const float rinv = rsqrtf(tot / (float)op.K + op.eps);
+            float ss = 0.f, um = 0.f;
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
                 const uint32_t ww[4] = {wr[i].x, wr[i].y, wr[i].z, wr[i].w};
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float wf = __uint_as_float(j & 1 ? ww[j >> 1] & 0xffff0000u : ww[j >> 1] << 16);
-                    v[i][j] = v[i][j] * rinv * (1.0f + wf);
+                    ss += v[i][j] * v[i][j];
+                    v[i][j] = v[i][j] * (1.0f + wf);
+                    um = fmaxf(um, fabsf(v[i][j]));
                 }
             }
-        } else if (op.x_mode == LB_X_F32_HEADNORM_SILU) {
+            ss = warp_sum(ss);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) um = fmaxf(um, __shfl_xor_sync(0xffffffffu, um, o));
+            if (lane == 0) { sh.scratch[warp] = ss; sh.scratch[32 + warp] = um; }
+            CH_SYNC();
+            float tot = 0.f;
+            um = 0.f;
+#pragma unroll
+            for (int w = 0; w < CH_W; ++w) { tot += sh.scratch[w]; um = fmaxf(um, sh.scratch[32 + w]); }
+            const float rinv = rsqrtf(tot / (float)op.K + op.eps);
+#pragma unroll
+            for (int i = 0; i < NI; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[i][j] *= rinv;
+            pre_max = __half2float(__float2half_rn(um * rinv)); // the largest |h| after the fp16 rounding below
+        } else if (NI <= 2 && op.x_mode == LB_X_F32_HEADNORM_SILU) { // (the host refuses this prologue for K > 8192: it would not fit the registers)
             // one head = 128 values = the 16 rows held by a 16-lane segment; h = x * rsqrt(mean_head x^2 + eps) * w * silu(z)
             const float4* wv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.aux0) + (tid & 15) * 8);
             const float4 wa = __ldg(wv), wb = __ldg(wv + 1);
@@ -235,21 +245,24 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
             }
     }
     // the scale: max|x| * 2^shift in [2^21, 2^22); all-zero or non-finite vectors use shift 0
-    float vmax = 0.f;
+    float vmax = pre_max;
+    if (pre_max < 0.f) {
+        vmax = 0.f;
 #pragma unroll
-    for (int i = 0; i < NI; ++i)
+        for (int i = 0; i < NI; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hv[i][j]));
-            vmax = fmaxf(vmax, fmaxf(fabsf(f.x), fabsf(f.y)));
-        }
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hv[i][j]));
+                vmax = fmaxf(vmax, fmaxf(fabsf(f.x), fabsf(f.y)));
+            }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
-    if (lane == 0) sh.scratch[32 + warp] = vmax;
-    __syncthreads();
-    vmax = 0.f;
+        for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+        if (lane == 0) sh.scratch[32 + warp] = vmax;
+        CH_SYNC();
+        vmax = 0.f;
 #pragma unroll
-    for (int w = 0; w < CH_W; ++w) vmax = fmaxf(vmax, sh.scratch[32 + w]);
+        for (int w = 0; w < CH_W; ++w) vmax = fmaxf(vmax, sh.scratch[32 + w]);
+    }
     int shift = 0;
     if (vmax > 0.f && vmax < 3.0e38f) shift = 21 - (int)((__float_as_uint(vmax) >> 23) & 0xffu) + 127;
     const float qscale = __uint_as_float((uint32_t)(127 + shift) << 23);
@@ -290,7 +303,7 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
                 *reinterpret_cast<uint4*>(op.x_out + r * 8) = make_uint4(hv[i][0], hv[i][1], hv[i][2], hv[i][3]);
         }
     }
-    __syncthreads();
+    CH_SYNC();
     return __uint_as_float((uint32_t)(127 - shift) << 23);
 }
 
@@ -334,6 +347,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         sh.op_pre[p.n_ops] = acc;
     }
     __syncthreads();
+
 
     // ---- this warp's stream: stages warp, warp + 16, warp + 32, ... of the CTA's list (all GEMVs of the chain).
     //      The warp writes them down once as (offset, descriptor) words; stage number m of the stream lives in ring
@@ -379,26 +393,29 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     const float lane_mul = ft == 0 ? 1.0f : (ft == 1 ? 65536.0f : 0.0f);
     pdl_wait(); // activations and barrier words belong to the stream order
     // tensor parallel: the exchange generation of this GPU, read once (every all-reduce entry of the launch shares it)
-    unsigned ar_gen0 = 0;
+    unsigned ar_gen0 = 0, n_barriers = 0; // n_barriers: grid barriers passed (thread 0 only)
     int ar_done = 0;
     const lb_tp_params* ar_tp = nullptr;
     for (int o = 0; o < p.n_ops; ++o)
-        if (p.op[o].type == LB_CHAIN_OP_ALLREDUCE) { ar_tp = reinterpret_cast<const lb_tp_params*>(p.op[o].ext); break; }
+        if (p.op[o].type == LB_CHAIN_OP_ALLREDUCE || p.op[o].type == LB_CHAIN_OP_ALLREDUCE_PUSHED) {
+            ar_tp = reinterpret_cast<const lb_tp_params*>(p.op[o].ext);
+            break;
+        }
     if (ar_tp) ar_gen0 = ar_tp->gen[0];
     for (int o = 0; o < p.n_ops; ++o) {
         const lb_chain_op& op = p.op[o];
         const int n0 = sh.op_n0[o], no = sh.op_no[o];
         unsigned long long* const tl = p.timeline ? p.timeline + ((size_t)c * LB_CHAIN_MAX_OPS + o) * 4 : nullptr;
         if (tl && tid == 0) tl[0] = globaltimer_ns();
-        if (o > 0) {
+        if (o > 0 && op.type != LB_CHAIN_OP_ALLREDUCE_PUSHED) { // (a pushed exchange reads only what this CTA's own flags cover)
             // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
-            __syncthreads();
+            CH_SYNC();
             if (tid == 0) {
                 // arrive with release (this block's results, ordered before by the barrier above, become visible to
                 // whoever observes the count), then poll with acquire; the status word of an earlier failed wait is
                 // looked at only once the wait is already long
                 asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
-                const unsigned target = (unsigned)o * (unsigned)G;
+                const unsigned target = (unsigned)(++n_barriers) * (unsigned)G;
                 bool ok = sh.bad == 0;
                 if (ok && ld_acquire_gpu(p.sync) < target) {
                     const uint64_t t0 = globaltimer_ns(), limit = lb_wait_limit_ns(p.status);
@@ -413,12 +430,52 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                 if (!ok) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_COUNTER); sh.bad = 1; }
                 sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             }
-            __syncthreads();
+            CH_SYNC();
         }
         if (tl && tid == 0) tl[1] = globaltimer_ns();
         if (o == p.trigger_op) pdl_launch_dependents();
         if (sh.snap) break; // uniform: written before the barrier above, by one thread
 
+        if (op.type == LB_CHAIN_OP_ALLREDUCE_PUSHED) {
+            // ---- tensor parallel, pushed form: the GEMV before this entry (LB_Y_TP_PUSH) stored this CTA's columns of
+            //      this rank's partial vector into every rank's buffer and raised flag [rank][c] there.  CTA c owns the
+            //      same columns on every rank (same matrix shape, same number of SMs), so it waits for the size flags of
+            //      its own columns only and adds them in rank order out of LOCAL memory. ----
+            const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
+            const unsigned gen = ar_gen0 + (unsigned)(++ar_done);
+            if (tid < tp.size) {
+                const uint64_t t0 = globaltimer_ns(), limit = lb_wait_limit_ns(p.status);
+                bool ok = sh.bad == 0;
+                if (ok) {
+                    ok = false;
+                    const unsigned* flag = tp.my_cta_flags + (size_t)tid * LB_TP_CTA_MAX + c;
+                    for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
+                        if ((int)(ld_acquire_sys(flag) - gen) >= 0) { ok = true; break; }
+                        if ((it & 63u) == 63u && (globaltimer_ns() - t0 > limit || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) break;
+                    }
+                }
+                if (!ok) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
+            }
+            CH_SYNC();
+            if (!sh.bad) {
+                const int pn0 = sh.op_n0[o - 1] * 8, pncol = sh.op_no[o - 1] * 8; // the strip of the GEMV that pushed
+                if (tid < pncol) {
+                    const int i = pn0 + tid;
+                    float part[LB_TP_MAX];
+#pragma unroll
+                    for (int r = 0; r < LB_TP_MAX; ++r) part[r] = r < tp.size ? __ldcv(tp.partials[tp.rank] + LB_TP_PARTIAL(tp, tp.slot, r) + i) : 0.f;
+                    float sum = 0.f;
+#pragma unroll
+                    for (int r = 0; r < LB_TP_MAX; ++r) sum += part[r]; // rank order
+                    tp.x[i] = __ldcg(tp.x + i) + sum;
+                }
+            }
+            if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
+            CH_SYNC();
+            if (tl && tid == 0) tl[2] = tl[3] = globaltimer_ns();
+            if (sh.snap) break;
+            continue;
+        }
         if (op.type == LB_CHAIN_OP_ALLREDUCE) {
             // ---- tensor parallel: every rank's partial vector (written by the GEMV before this entry into the rank's
             //      exchange buffer; the grid barrier above made this GPU's complete) is added into the residual stream in
@@ -443,13 +500,13 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                 }
                 if (!ok) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
             }
-            __syncthreads();
+            CH_SYNC();
             if (!sh.bad) {
                 const int per = (tp.n + G - 1) / G, i = c * per + tid;
                 if (tid < per && i < tp.n) {
                     float part[LB_TP_MAX];
 #pragma unroll
-                    for (int r = 0; r < LB_TP_MAX; ++r) part[r] = r < tp.size ? __ldcv(tp.partials[r] + (size_t)tp.slot * tp.n_max + i) : 0.f;
+                    for (int r = 0; r < LB_TP_MAX; ++r) part[r] = r < tp.size ? __ldcv(tp.partials[r] + LB_TP_PARTIAL(tp, tp.slot, r) + i) : 0.f;
                     float sum = 0.f;
 #pragma unroll
                     for (int r = 0; r < LB_TP_MAX; ++r) sum += part[r]; // rank order
@@ -457,7 +514,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                 }
             }
             if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
-            __syncthreads();
+            CH_SYNC();
             if (tl && tid == 0) tl[2] = tl[3] = globaltimer_ns();
             if (sh.snap) break;
             continue;
@@ -475,7 +532,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                 asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "n"(DN_THREADS) : "memory"); // the unit's shared memory is reused
             }
             if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
-            __syncthreads();
+            CH_SYNC();
             if (tl && tid == 0) tl[2] = tl[3] = globaltimer_ns();
             if (sh.snap) break;
             continue;
@@ -527,7 +584,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             request();    // refill this slot with the stream's next stage (maybe of a later GEMV)
         }
         flush();
-        __syncthreads();
+        CH_SYNC();
 
         // ---- column sums over the warps, in warp order; epilogue ----
         const int ncol = no * 8;
@@ -540,6 +597,14 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             v *= unit;
             if (op.y_mode == LB_Y_SWIGLU_F16) {
                 sh.vals[tid] = v;
+            } else if (op.y_mode == LB_Y_TP_PUSH) {
+                // this rank's partial sums of a row-parallel projection: straight into every rank's buffer (posted stores
+                // over NVLink; the local copy is one of them)
+                const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
+                const size_t at = LB_TP_PARTIAL(tp, tp.slot, tp.rank) + (size_t)(n0 * 8 + tid);
+#pragma unroll
+                for (int r = 0; r < LB_TP_MAX; ++r)
+                    if (r < tp.size) tp.partials[r][at] = v;
             } else {
                 const int n = n0 * 8 + tid;
                 if (op.y_mode == LB_Y_F16) reinterpret_cast<__half*>(op.y)[n] = __float2half_rn(v);
@@ -549,7 +614,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         }
         if (op.y_mode == LB_Y_SWIGLU_F16) {
             // the strip is made of (gate octet, up octet) pairs; pair P of the matrix gives y[8P .. 8P+7]
-            __syncthreads();
+            CH_SYNC();
             if (tid < ncol / 2) {
                 const int pr = tid >> 3, g = tid & 7;
                 const float gate = sh.vals[pr * 16 + g], up = sh.vals[pr * 16 + 8 + g];
@@ -558,11 +623,19 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         }
         if (tl && tid == 0) tl[3] = globaltimer_ns();
         if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
-        __syncthreads(); // red / vals are reused by the next GEMV; sh.snap is the same for everyone
+        CH_SYNC(); // red / vals are reused by the next GEMV; sh.snap is the same for everyone; the pushed columns are all issued
+        if (op.y_mode == LB_Y_TP_PUSH && !sh.snap) {
+            // tell every rank that CTA c's columns of generation (exchanges done + 1) are in its buffer
+            const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
+            if (tid < tp.size) {
+                __threadfence_system(); // the block's stores (ordered before by the barrier above) before the flag
+                st_release_sys(tp.peer_cta_flags[tid] + (size_t)tp.rank * LB_TP_CTA_MAX + c, ar_gen0 + (unsigned)ar_done + 1u);
+            }
+        }
         if (sh.snap) break;
     }
     // ---- leave: the last CTA out zeroes the barrier words for the next launch ----
-    __syncthreads();
+    CH_SYNC();
     if (tid == 0) {
         __threadfence();
         const unsigned old = atomicAdd(p.sync + 1, 1u);

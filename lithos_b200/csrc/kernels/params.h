@@ -77,7 +77,7 @@ typedef struct {
 #define LB_CHAIN_OP_ALLREDUCE 2     /* tensor parallel: x += sum over ranks of the partial vectors (comm_core.cuh); ext = lb_tp_params in device memory */
 #define LB_CHAIN_OP_ALLREDUCE_PUSHED 3 /* the same sum where the GEMV before it (y_mode LB_Y_TP_PUSH) has already stored its columns into every
                                           rank's buffer: CTA c waits for the flags of its own columns only, no grid barrier before the entry */
-#define LB_CHAIN_BLOCK (LB_CHAIN_THREADS + 32) /* threads per CTA: the consumer warps and one warp that requests weights into L2 ahead of them */
+
 #define LB_CHAIN_WARPS 16            /* consumer warps; every warp streams its own stages */
 #define LB_CHAIN_THREADS (LB_CHAIN_WARPS * 32)
 #define LB_CHAIN_RECORD 544          /* bytes per (octet, K-group) */
@@ -112,8 +112,7 @@ typedef struct {
     int32_t max_pairs;    /* pairs (incl. a trailing single) of the widest strip of the chain */
     int32_t trigger_op;   /* griddepcontrol.launch_dependents is issued when this GEMV starts */
     int32_t tab_len;      /* entries of a warp's stage list: ceil(stages of the busiest CTA / warps) */
-    int32_t prefetch_bytes; /* bytes of this CTA's weight stream the extra warp keeps requested into L2 ahead of the consumers (0 = off) */
-    int32_t pad_;
+    int32_t pad_[2];
     unsigned long long* timeline; /* optional [gridDim.x][LB_CHAIN_MAX_OPS][4] %globaltimer stamps of thread 0: reached the
                                      grid barrier, left it, activation table ready (or mixer started), entry finished */
 } lb_chain_params;

@@ -24,6 +24,8 @@ def _sigs():
     L.lb_comm_buffer.restype = C.c_uint64
     L.lb_comm_bytes.argtypes = [vp]
     L.lb_comm_bytes.restype = C.c_size_t
+    L.lb_comm_partial_offset.argtypes = [vp, i32, i32]
+    L.lb_comm_partial_offset.restype = C.c_size_t
     L.lb_comm_flags_offset.argtypes = [vp]
     L.lb_comm_flags_offset.restype = C.c_size_t
     L.lb_comm_allreduce.argtypes = [vp, C.c_uint64, i32, i32]
@@ -62,6 +64,10 @@ class Comm:
     @property
     def nbytes(self) -> int:
         return lib().lb_comm_bytes(self.h)
+
+    def partial_offset(self, slot: int, rank: int) -> int:
+        """byte offset, inside any rank's exchange buffer, of `rank`'s partial vector of exchange slot 0 / 1"""
+        return lib().lb_comm_partial_offset(self.h, slot, rank)
 
     @property
     def flags_offset(self) -> int:

@@ -32,9 +32,9 @@ def test_silent_peer_times_out_reports_and_recovers(ctx, lb):
     comm, peer, base = silent_pair(ctx, lb, n)
     x = ctx.to_device(np.ones(n, np.float32))
     mine = np.full(n, 2.0, np.float32)
-    lb.lib().lb_memcpy_h2d(ctx.h, comm.buffer, mine.ctypes.data_as(C.c_void_p), mine.nbytes)   # rank 0's partial, slot 0
+    lb.lib().lb_memcpy_h2d(ctx.h, comm.buffer + comm.partial_offset(0, 0), mine.ctypes.data_as(C.c_void_p), mine.nbytes)   # rank 0's partial, slot 0
     theirs = np.full(n, 3.0, np.float32)
-    lb.lib().lb_memcpy_h2d(ctx.h, base, theirs.ctypes.data_as(C.c_void_p), theirs.nbytes)      # "rank 1"'s partial, slot 0
+    lb.lib().lb_memcpy_h2d(ctx.h, base + comm.partial_offset(0, 1), theirs.ctypes.data_as(C.c_void_p), theirs.nbytes)      # "rank 1"'s partial, slot 0
     ctx.sync()
     ctx.set_wait_limit(LIMIT_NS)
     t0 = time.perf_counter()
