@@ -6,9 +6,9 @@
 struct lb_comm {
     lb_ctx* c;
     int rank, size, n_max;
-    size_t flags_off, cta_flags_off, bytes;
+    size_t flags_off, words_off, bytes;
     CUdeviceptr buf;              /* this rank's buffer: float [2][size][n_max] partials | float [n_max] sampling record |
-                                     unsigned pull flags [8] | unsigned gen | unsigned push flags [8][LB_TP_CTA_MAX] (params.h) */
+                                     unsigned flags [8] | unsigned gen | u64 [2][size][n_max] (value, generation) words (params.h) */
     CUdeviceptr peer[LB_TP_MAX];  /* every rank's buffer as seen from this GPU (peer[rank] == buf) */
     int opened[LB_TP_MAX];
 };
@@ -20,8 +20,8 @@ LB_API int lb_comm_create(lb_ctx* c, int rank, int size, int n_max, lb_comm** ou
     if (!m) return LB_ERR_NOMEM;
     m->c = c; m->rank = rank; m->size = size; m->n_max = n_max;
     m->flags_off = ((size_t)(2 * size + 1) * n_max * 4 + 255) & ~(size_t)255;
-    m->cta_flags_off = m->flags_off + 256;
-    m->bytes = m->cta_flags_off + (size_t)LB_TP_MAX * LB_TP_CTA_MAX * 4;
+    m->words_off = m->flags_off + 256;
+    m->bytes = m->words_off + (size_t)2 * size * n_max * 8;
     LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
     CUresult r = lb_drv.MemAlloc(&m->buf, m->bytes);
     if (r != CUDA_SUCCESS) { free(m); return lb_cu(c, r, "cuMemAlloc(exchange buffer)"); }
@@ -90,10 +90,9 @@ int lb_comm_fill(const lb_comm* m, lb_tp_params* p, int slot, int n) {
         if (!m->peer[r]) return lb_fail(m->c, LB_ERR_STATE, "exchange buffer of rank %d not opened", r);
         p->partials[r] = (float*)m->peer[r];
         p->peer_flags[r] = (unsigned*)(m->peer[r] + m->flags_off);
-        p->peer_cta_flags[r] = (unsigned*)(m->peer[r] + m->cta_flags_off);
+        p->words[r] = (unsigned long long*)(m->peer[r] + m->words_off);
     }
     p->my_flags = (unsigned*)(m->buf + m->flags_off);
-    p->my_cta_flags = (unsigned*)(m->buf + m->cta_flags_off);
     p->gen = (unsigned*)(m->buf + m->flags_off + 128);
     p->status = (unsigned*)m->c->dev_status;
     p->n = n; p->n_max = m->n_max; p->slot = slot; p->rank = m->rank; p->size = m->size;

@@ -577,35 +577,20 @@ static int q4_gemv(lb_model* m, const q4_mat* w, CUdeviceptr x, CUdeviceptr y, i
 static int row_parallel(lb_model* m, const q4_mat* w, CUdeviceptr x, int x_mode, CUdeviceptr aux0, CUdeviceptr aux1) {
     if (m->tp_size == 1) return q4_gemv(m, w, x, m->X, x_mode, LB_Y_F32_ACCUM, aux0, aux1, 0);
     if (!m->comm) return lb_fail(m->c, LB_ERR_STATE, "model: tensor-parallel shard without exchange buffers (lb_model_set_comm)");
-    const int slot = m->ar_count++ & 1;
-    if (m->use_chain && w->packed && m->tp_params[slot] && m->c->sm_count <= LB_TP_CTA_MAX) {
-        /* the exchange joins the persistent chain, pushed: the projection's epilogue stores this rank's partial columns
-         * into every rank's buffer, and the entry after it adds what the peers stored here.  The two entries must sit in
-         * one launch: what is pending goes out first when they do not fit beside it. */
+    if (m->use_chain && w->packed && m->tp_params[0]) {
+        /* the exchange happens inside the projection's epilogue (LB_Y_TP_ALLREDUCE): no entry or launch of its own */
         lb_gemv_op o;
         memset(&o, 0, sizeof o);
         o.packed = w->packed;
-        o.x = x; o.y = lb_comm_slot_ptr(m->comm, slot); o.aux0 = aux0; o.aux1 = aux1;
-        o.K = w->K; o.N = w->N; o.x_mode = x_mode; o.y_mode = LB_Y_F32; o.eps = m->cfg.eps;
-        lb_chain_op k[2];
-        LB_TRY(lb_chain_fill_gemv(m->c, &k[0], &o, m->n_pend));
-        k[0].y_mode = LB_Y_TP_PUSH;
-        k[0].ext = (const void*)m->tp_params[slot];
-        memset(&k[1], 0, sizeof k[1]);
-        k[1].type = LB_CHAIN_OP_ALLREDUCE_PUSHED;
-        k[1].ext = (const void*)m->tp_params[slot];
-        if (m->n_pend > 0) {
-            int fits = m->n_pend + 2 <= LB_CHAIN_MAX_OPS;
-            if (fits) {
-                m->pend[m->n_pend] = k[0]; m->pend[m->n_pend + 1] = k[1];
-                fits = lb_chain_fits(m->c, m->pend, m->n_pend + 2) == LB_OK;
-            }
-            if (!fits) LB_TRY(flush_chain(m));
-        }
-        m->pend[m->n_pend++] = k[0];
-        m->pend[m->n_pend++] = k[1];
-        return LB_OK;
+        o.x = x; o.y = m->X; o.aux0 = aux0; o.aux1 = aux1;
+        o.K = w->K; o.N = w->N; o.x_mode = x_mode; o.y_mode = LB_Y_F32_ACCUM; o.eps = m->cfg.eps;
+        lb_chain_op k;
+        LB_TRY(lb_chain_fill_gemv(m->c, &k, &o, m->n_pend));
+        k.y_mode = LB_Y_TP_ALLREDUCE;
+        k.ext = (const void*)m->tp_params[0];
+        return chain_push(m, &k);
     }
+    const int slot = m->ar_count++ & 1;
     LB_TRY(q4_gemv(m, w, x, (CUdeviceptr)lb_comm_slot_ptr(m->comm, slot), x_mode, LB_Y_F32, aux0, aux1, 0));
     LB_TRY(flush_chain(m));
     lb_tp_params p;

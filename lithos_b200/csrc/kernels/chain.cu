@@ -397,7 +397,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     int ar_done = 0;
     const lb_tp_params* ar_tp = nullptr;
     for (int o = 0; o < p.n_ops; ++o)
-        if (p.op[o].type == LB_CHAIN_OP_ALLREDUCE || p.op[o].type == LB_CHAIN_OP_ALLREDUCE_PUSHED) {
+        if (p.op[o].type == LB_CHAIN_OP_ALLREDUCE || (p.op[o].type == LB_CHAIN_OP_GEMV && p.op[o].y_mode == LB_Y_TP_ALLREDUCE)) {
             ar_tp = reinterpret_cast<const lb_tp_params*>(p.op[o].ext);
             break;
         }
@@ -407,7 +407,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         const int n0 = sh.op_n0[o], no = sh.op_no[o];
         unsigned long long* const tl = p.timeline ? p.timeline + ((size_t)c * LB_CHAIN_MAX_OPS + o) * 4 : nullptr;
         if (tl && tid == 0) tl[0] = globaltimer_ns();
-        if (o > 0 && op.type != LB_CHAIN_OP_ALLREDUCE_PUSHED) { // (a pushed exchange reads only what this CTA's own flags cover)
+        if (o > 0) {
             // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
             CH_SYNC();
             if (tid == 0) {
@@ -436,46 +436,6 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         if (o == p.trigger_op) pdl_launch_dependents();
         if (sh.snap) break; // uniform: written before the barrier above, by one thread
 
-        if (op.type == LB_CHAIN_OP_ALLREDUCE_PUSHED) {
-            // ---- tensor parallel, pushed form: the GEMV before this entry (LB_Y_TP_PUSH) stored this CTA's columns of
-            //      this rank's partial vector into every rank's buffer and raised flag [rank][c] there.  CTA c owns the
-            //      same columns on every rank (same matrix shape, same number of SMs), so it waits for the size flags of
-            //      its own columns only and adds them in rank order out of LOCAL memory. ----
-            const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
-            const unsigned gen = ar_gen0 + (unsigned)(++ar_done);
-            if (tid < tp.size) {
-                const uint64_t t0 = globaltimer_ns(), limit = lb_wait_limit_ns(p.status);
-                bool ok = sh.bad == 0;
-                if (ok) {
-                    ok = false;
-                    const unsigned* flag = tp.my_cta_flags + (size_t)tid * LB_TP_CTA_MAX + c;
-                    for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
-                        if ((int)(ld_acquire_sys(flag) - gen) >= 0) { ok = true; break; }
-                        if ((it & 63u) == 63u && (globaltimer_ns() - t0 > limit || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) break;
-                    }
-                }
-                if (!ok) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
-            }
-            CH_SYNC();
-            if (!sh.bad) {
-                const int pn0 = sh.op_n0[o - 1] * 8, pncol = sh.op_no[o - 1] * 8; // the strip of the GEMV that pushed
-                if (tid < pncol) {
-                    const int i = pn0 + tid;
-                    float part[LB_TP_MAX];
-#pragma unroll
-                    for (int r = 0; r < LB_TP_MAX; ++r) part[r] = r < tp.size ? __ldcv(tp.partials[tp.rank] + LB_TP_PARTIAL(tp, tp.slot, r) + i) : 0.f;
-                    float sum = 0.f;
-#pragma unroll
-                    for (int r = 0; r < LB_TP_MAX; ++r) sum += part[r]; // rank order
-                    tp.x[i] = __ldcg(tp.x + i) + sum;
-                }
-            }
-            if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
-            CH_SYNC();
-            if (tl && tid == 0) tl[2] = tl[3] = globaltimer_ns();
-            if (sh.snap) break;
-            continue;
-        }
         if (op.type == LB_CHAIN_OP_ALLREDUCE) {
             // ---- tensor parallel: every rank's partial vector (written by the GEMV before this entry into the rank's
             //      exchange buffer; the grid barrier above made this GPU's complete) is added into the residual stream in
@@ -597,14 +557,40 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             v *= unit;
             if (op.y_mode == LB_Y_SWIGLU_F16) {
                 sh.vals[tid] = v;
-            } else if (op.y_mode == LB_Y_TP_PUSH) {
-                // this rank's partial sums of a row-parallel projection: straight into every rank's buffer (posted stores
-                // over NVLink; the local copy is one of them)
+            } else if (op.y_mode == LB_Y_TP_ALLREDUCE) {
+                // This rank's partial sum of column n of a row-parallel projection.  (value, generation) goes as ONE 8-byte
+                // store into every rank's word array (posted stores over NVLink; the local copy is one of them); then this
+                // thread -- which owns column n on every rank -- polls its own rank's array until all ranks' words carry this
+                // generation, and adds them in rank order into the residual stream.  Slots alternate with the generation: a
+                // rank can only be one exchange ahead of its slowest peer, because it needs that peer's word to finish.
                 const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
-                const size_t at = LB_TP_PARTIAL(tp, tp.slot, tp.rank) + (size_t)(n0 * 8 + tid);
+                const unsigned gen = ar_gen0 + (unsigned)ar_done + 1u;
+                const int n = n0 * 8 + tid;
+                const size_t slot_at = (size_t)(gen & 1u) * tp.size * tp.n_max + (size_t)n;
+                const unsigned long long word = ((unsigned long long)gen << 32) | (unsigned long long)__float_as_uint(v);
 #pragma unroll
                 for (int r = 0; r < LB_TP_MAX; ++r)
-                    if (r < tp.size) tp.partials[r][at] = v;
+                    if (r < tp.size) st_volatile_u64(tp.words[r] + slot_at + (size_t)tp.rank * tp.n_max, word);
+                float sum = 0.f;
+                bool ok = sh.bad == 0;
+                const uint64_t t0 = globaltimer_ns(), limit = lb_wait_limit_ns(p.status);
+#pragma unroll
+                for (int r = 0; r < LB_TP_MAX; ++r) {
+                    if (r >= tp.size || !ok) continue;
+                    const unsigned long long* src = tp.words[tp.rank] + slot_at + (size_t)r * tp.n_max;
+                    unsigned long long w = ld_volatile_u64(src);
+                    if ((unsigned)(w >> 32) != gen) {
+                        ok = false;
+                        for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
+                            w = ld_volatile_u64(src);
+                            if ((unsigned)(w >> 32) == gen) { ok = true; break; }
+                            if ((it & 63u) == 63u && (globaltimer_ns() - t0 > limit || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) break;
+                        }
+                    }
+                    sum += __uint_as_float((unsigned)w); // rank order
+                }
+                if (ok) reinterpret_cast<float*>(op.y)[n] = __ldcg(reinterpret_cast<float*>(op.y) + n) + sum;
+                else { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
             } else {
                 const int n = n0 * 8 + tid;
                 if (op.y_mode == LB_Y_F16) reinterpret_cast<__half*>(op.y)[n] = __float2half_rn(v);
@@ -621,17 +607,10 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                 reinterpret_cast<__half*>(op.y)[(n0 / 2) * 8 + tid] = __float2half_rn(siluf_dev(gate) * up);
             }
         }
+        if (op.y_mode == LB_Y_TP_ALLREDUCE) ++ar_done; // one more exchange of this launch (uniform)
         if (tl && tid == 0) tl[3] = globaltimer_ns();
         if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
-        CH_SYNC(); // red / vals are reused by the next GEMV; sh.snap is the same for everyone; the pushed columns are all issued
-        if (op.y_mode == LB_Y_TP_PUSH && !sh.snap) {
-            // tell every rank that CTA c's columns of generation (exchanges done + 1) are in its buffer
-            const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
-            if (tid < tp.size) {
-                __threadfence_system(); // the block's stores (ordered before by the barrier above) before the flag
-                st_release_sys(tp.peer_cta_flags[tid] + (size_t)tp.rank * LB_TP_CTA_MAX + c, ar_gen0 + (unsigned)ar_done + 1u);
-            }
-        }
+        CH_SYNC(); // red / vals are reused by the next GEMV; sh.snap is the same for everyone
         if (sh.snap) break;
     }
     // ---- leave: the last CTA out zeroes the barrier words for the next launch ----

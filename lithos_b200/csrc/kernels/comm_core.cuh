@@ -13,6 +13,16 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
     return v;
 }
 
+// 8-byte accesses that are not cached in L1 and are delivered whole: the (value, generation) words of the pushed exchange
+__device__ __forceinline__ void st_volatile_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // returns false when a peer did not show up in time
 __device__ __forceinline__ bool tp_rendezvous(const lb_tp_params& p, unsigned g, bool* s_ok) {
     const int t = threadIdx.x;

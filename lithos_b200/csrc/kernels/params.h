@@ -29,8 +29,9 @@ enum {
     LB_Y_F32_ACCUM = 2, /* y fp32 [N] += result (residual add) */
     LB_Y_SWIGLU_F16 = 3, /* columns come in interleaved 64-wide blocks (gate block, up block, gate block, ...);
                            y fp16 [N/2] = silu(gate)*up */
-    LB_Y_TP_PUSH = 4    /* persistent chain under tensor parallelism only: the fp32 results are this rank's partial sums of a
-                           row-parallel projection and are stored straight into every rank's exchange buffer (ext = lb_tp_params) */
+    LB_Y_TP_ALLREDUCE = 4 /* persistent chain under tensor parallelism only: the fp32 results are this rank's partial sums of a
+                           row-parallel projection; y (the residual stream) += their sum over all ranks, exchanged inside the
+                           epilogue as (value, generation) words stored straight into every rank's buffer (ext = lb_tp_params) */
 };
 
 typedef struct {
@@ -75,8 +76,6 @@ typedef struct {
 #define LB_CHAIN_OP_GEMV 0
 #define LB_CHAIN_OP_DELTANET 1      /* the DeltaNet mixer of one layer (deltanet_core.cuh); ext = lb_dn_layer_params in device memory */
 #define LB_CHAIN_OP_ALLREDUCE 2     /* tensor parallel: x += sum over ranks of the partial vectors (comm_core.cuh); ext = lb_tp_params in device memory */
-#define LB_CHAIN_OP_ALLREDUCE_PUSHED 3 /* the same sum where the GEMV before it (y_mode LB_Y_TP_PUSH) has already stored its columns into every
-                                          rank's buffer: CTA c waits for the flags of its own columns only, no grid barrier before the entry */
 
 #define LB_CHAIN_WARPS 16            /* consumer warps; every warp streams its own stages */
 #define LB_CHAIN_THREADS (LB_CHAIN_WARPS * 32)
@@ -230,13 +229,15 @@ typedef struct {
 
 /* ---- tensor-parallel exchange (comm.cu) ----------------------------------------------- */
 #define LB_TP_MAX 8
-#define LB_TP_CTA_MAX 256 /* CTAs of a persistent chain that may own columns (>= SMs of the GPU) */
 /* Exchange buffer of one rank (every rank maps every peer's): float [2][size][n_max] partial vectors (slot = exchange
- * parity, then the rank that produced the vector), float [n_max] for the sampling record, then the flag words.
+ * parity, then the rank that produced the vector), float [n_max] for the sampling record, the flag words, then
+ * uint2 [2][size][n_max] (value, generation) words.
  * "Pull" exchanges (tp_allreduce_add, LB_CHAIN_OP_ALLREDUCE): rank q leaves its partial in ITS OWN buffer at (slot, q),
- * raises flag [q] in every peer's pull-flag array, readers load the vector from q's buffer.
- * "Pushed" exchanges (LB_Y_TP_PUSH + LB_CHAIN_OP_ALLREDUCE_PUSHED): CTA c of rank q stores its columns into EVERY rank's
- * buffer at (slot, q), then raises flag [q][c] in every rank's push-flag array; readers load from their own buffer. */
+ * raises flag [q] in every peer's flag array (system-scope release), readers load the vector from q's buffer.
+ * "Pushed" exchanges (LB_Y_TP_ALLREDUCE): the thread that owns column n on rank q stores the 8-byte word (partial sum,
+ * generation) into EVERY rank's word array at (slot, q, n) -- one store, delivered whole, so no fence and no flag -- and
+ * then polls its own rank's array until the words of column n from all ranks carry this generation.  The same thread owns
+ * column n on every rank (same matrix, same number of SMs), so nothing else has to be synchronised. */
 typedef struct {
     float* x;                          /* residual stream [n] on this GPU */
     float* partials[LB_TP_MAX];        /* every rank's exchange buffer (peer pointers) */
@@ -244,8 +245,7 @@ typedef struct {
     unsigned* my_flags;                /* this rank's pull-flag array (local) */
     unsigned* gen;                     /* this rank's generation counter (local, advanced by the kernel) */
     unsigned* status;
-    unsigned* peer_cta_flags[LB_TP_MAX]; /* every rank's push-flag array: unsigned [LB_TP_MAX][LB_TP_CTA_MAX] */
-    unsigned* my_cta_flags;            /* this rank's push-flag array (local) */
+    unsigned long long* words[LB_TP_MAX]; /* every rank's (value, generation) word array [2][size][n_max] (peer pointers) */
     int32_t n, n_max, slot, rank, size;
     int32_t pad_;
 } lb_tp_params;
