@@ -646,6 +646,76 @@ def bench_chain(args, local):
     return out
 
 
+def bench_timeline(args, rank, local, world, dist):
+    """--workload timeline: where the time of one persistent-chain launch goes, per kind of entry, from the %globaltimer
+    stamps of lb_set_chain_timeline (no profiler).  Three DeltaNet layers of the benchmark's widths (one chain launch of 12
+    entries: per layer input projection, mixer, out projection, gate/up, down; under tensor parallelism the out and down
+    projections carry the exchange in their epilogue) decoded at position 4096; the stamps of the last of 40 replays are
+    read on every rank, rank 0 prints medians over the SMs in microseconds."""
+    import lithos_b200 as lb
+    from lithos_b200 import model as M
+    from lithos_b200 import tp
+    cfg = M.qwen35_27b(max_ctx=CTX_PREFILL + 64, n_layers=3)
+    cfg.vocab = 8192
+    ctx = lb.Context(local)
+    comm = None
+    if world > 1:
+        def all_gather(b):
+            out_ = [None] * world
+            dist.all_gather_object(out_, b)
+            return out_
+        comm = tp.make_comm(ctx, rank, world, cfg.hidden, all_gather)
+    model = M.Model(ctx, cfg, rank, world)
+    if comm is not None:
+        tp.attach(model, comm)
+    model.fill_synthetic(args.seed)
+    model.seed_state(CTX_PREFILL, args.seed)
+    sms, MAXOPS = ctx.sm_count, 32
+    tl = ctx.alloc(sms * MAXOPS * 8 * 8).zero()
+    lb.lib().lb_set_chain_timeline(ctx.h, tl.ptr)
+    model.capture()
+    lb.lib().lb_set_chain_timeline(ctx.h, 0)
+    barrier(dist)
+    model.set_input(1, CTX_PREFILL)
+    model.replay(40)
+    ctx.sync()
+    barrier(dist)
+    t = tl.download(np.uint64, sms * MAXOPS * 8).reshape(sms, MAXOPS, 8).astype(np.int64)
+    names = ["input projection (5120 -> 16384/tp, RMSNorm prologue)", "DeltaNet mixer", "out projection (6144/tp -> 5120, head norm + gate prologue" + (", exchange" if world > 1 else "") + ")",
+             "gate/up projection (5120 -> 34816/tp, RMSNorm prologue, SwiGLU)", "down projection (17408/tp -> 5120" + (", exchange" if world > 1 else "") + ")"]
+    rows = []
+    n_ops = 15
+    t_first = t[:, 0, 0].min()
+    for o in range(n_ops):
+        e = t[:, o, :]
+        kind = o % 5
+        med = lambda a: float(np.median(a)) / 1e3
+        rec = {"entry": o, "kind": names[kind], "barrier_wait_us": round(med(e[:, 1] - e[:, 0]), 2) if o else 0.0,
+               "arrival_skew_us": round(float(e[:, 0].max() - e[:, 0].min()) / 1e3, 2),
+               "table_us": round(med(e[:, 2] - e[:, 1]), 2), "body_us": round(med(e[:, 3] - e[:, 2]), 2),
+               "epilogue_exchange_us": round(med(e[:, 4] - e[:, 3]), 2), "entry_total_us": round(med(e[:, 4] - e[:, 0]), 2)}
+        rows.append(rec)
+    total = float(t[:, n_ops - 1, 4].max() - t_first) / 1e3
+    by_kind = {}
+    for r_ in rows[5:]:      # layers 2 and 3: the first layer of the launch starts without a barrier
+        k = by_kind.setdefault(r_["kind"], {"barrier_wait_us": 0.0, "table_us": 0.0, "body_us": 0.0, "epilogue_exchange_us": 0.0, "entry_total_us": 0.0, "n": 0})
+        for f in ("barrier_wait_us", "table_us", "body_us", "epilogue_exchange_us", "entry_total_us"):
+            k[f] += r_[f]
+        k["n"] += 1
+    for k in by_kind.values():
+        n = k.pop("n")
+        for f in k:
+            k[f] = round(k[f] / n, 2)
+    out = {"metric": "persistent-chain timeline (3 DeltaNet layers, one launch)", "unit": "us", "n_gpus": world, "launch_total_us": round(total, 1),
+           "per_layer_us": round(total / 3, 1), "by_kind_mean_of_layers_2_3": by_kind, "entries": rows}
+    model.close()
+    if comm is not None:
+        barrier(dist)
+        comm.close()
+    ctx.close()
+    return out
+
+
 def bench_batched(args, local):
     """--workload batched: the batched int4 projection sweep (BASELINE config 4): the four projection shapes of the
     model at batch 1 / 4 / 16 / 64, fp16 N(0,1) activations, each launch reading a weight set that is not in L2
@@ -721,7 +791,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "chain", "batched"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "chain", "batched", "timeline"],
                     help="decode: the benchmark; gemv: config 0 alone; chain: the decode step's four GEMVs between two token "
                          "mixers as persistent gemv_chain launches alone (the small case used for ncu captures)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: number of layers (64 = the benchmark definition)")
@@ -744,6 +814,13 @@ def main():
             print(json.dumps(ref), flush=True)
         return
     dist = init_dist(world)
+    if args.workload == "timeline":
+        out = bench_timeline(args, rank, local, world, dist)
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     if args.workload in ("chain", "batched"):
         out = (bench_chain if args.workload == "chain" else bench_batched)(args, local)
         if rank == 0:

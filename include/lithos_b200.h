@@ -70,9 +70,9 @@ void lb_set_pdl(lb_ctx* ctx, int on);
  * resident at the same time (default 32 KB; 0 = the deepest weight ring) */
 void lb_set_chain_reserve(lb_ctx* ctx, int bytes);
 /* Profiling hook: while buf != 0, every persistent-chain launch made (or captured) afterwards writes, for each SM and
- * chain entry, four %globaltimer values (ns) of the SM's thread 0 -- reached the grid barrier, left it, activation
- * table ready / mixer started, entry finished -- into buf as u64 [SMs][LB_GEMV_CHAIN_MAX][4].  Launches overwrite
- * each other's stamps. */
+ * chain entry, five %globaltimer values (ns) of the SM's thread 0 -- reached the grid barrier, left it, activation
+ * table ready / mixer started, every weight stage consumed, entry finished (epilogue and, under tensor parallelism, the
+ * exchange) -- into buf as u64 [SMs][LB_GEMV_CHAIN_MAX][8].  Launches overwrite each other's stamps. */
 void lb_set_chain_timeline(lb_ctx* ctx, uint64_t buf);
 
 /* ---- generic module load + launch ----------------------------------------------

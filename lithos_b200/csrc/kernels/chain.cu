@@ -405,7 +405,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     for (int o = 0; o < p.n_ops; ++o) {
         const lb_chain_op& op = p.op[o];
         const int n0 = sh.op_n0[o], no = sh.op_no[o];
-        unsigned long long* const tl = p.timeline ? p.timeline + ((size_t)c * LB_CHAIN_MAX_OPS + o) * 4 : nullptr;
+        unsigned long long* const tl = p.timeline ? p.timeline + ((size_t)c * LB_CHAIN_MAX_OPS + o) * 8 : nullptr;
         if (tl && tid == 0) tl[0] = globaltimer_ns();
         if (o > 0) {
             // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
@@ -475,7 +475,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             }
             if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             CH_SYNC();
-            if (tl && tid == 0) tl[2] = tl[3] = globaltimer_ns();
+            if (tl && tid == 0) tl[2] = tl[3] = tl[4] = globaltimer_ns();
             if (sh.snap) break;
             continue;
         }
@@ -493,7 +493,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             }
             if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             CH_SYNC();
-            if (tl && tid == 0) tl[2] = tl[3] = globaltimer_ns();
+            if (tl && tid == 0) tl[2] = tl[3] = tl[4] = globaltimer_ns();
             if (sh.snap) break;
             continue;
         }
@@ -545,6 +545,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         }
         flush();
         CH_SYNC();
+        if (tl && tid == 0) tl[3] = globaltimer_ns(); // every stage of the strip consumed
 
         // ---- column sums over the warps, in warp order; epilogue ----
         const int ncol = no * 8;
@@ -608,7 +609,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             }
         }
         if (op.y_mode == LB_Y_TP_ALLREDUCE) ++ar_done; // one more exchange of this launch (uniform)
-        if (tl && tid == 0) tl[3] = globaltimer_ns();
+        if (tl && tid == 0) tl[4] = globaltimer_ns();
         if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
         CH_SYNC(); // red / vals are reused by the next GEMV; sh.snap is the same for everyone
         if (sh.snap) break;

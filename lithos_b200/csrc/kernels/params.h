@@ -112,8 +112,9 @@ typedef struct {
     int32_t trigger_op;   /* griddepcontrol.launch_dependents is issued when this GEMV starts */
     int32_t tab_len;      /* entries of a warp's stage list: ceil(stages of the busiest CTA / warps) */
     int32_t pad_[2];
-    unsigned long long* timeline; /* optional [gridDim.x][LB_CHAIN_MAX_OPS][4] %globaltimer stamps of thread 0: reached the
-                                     grid barrier, left it, activation table ready (or mixer started), entry finished */
+    unsigned long long* timeline; /* optional [gridDim.x][LB_CHAIN_MAX_OPS][8] %globaltimer stamps of thread 0: [0] reached the grid
+                                     barrier, [1] left it, [2] activation table ready (or mixer / exchange started), [3] every stage of
+                                     the strip consumed, [4] entry finished (epilogue and, under tensor parallelism, the exchange) */
 } lb_chain_params;
 
 /* gemv_pack_strips: reference format -> strip-packed (one thread per 32-bit word of the output) */
