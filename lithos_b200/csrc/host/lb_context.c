@@ -126,7 +126,7 @@ static int load_cubin(lb_ctx* c, const char* dir, const char* file) {
     return LB_OK;
 }
 
-static const char* const k_cubins[] = {"gemv.cubin", "chain.cubin", "batched.cubin", "batched_tc.cubin", "deltanet.cubin", "attention.cubin", "attention_mma.cubin", "small.cubin", "comm.cubin"};
+static const char* const k_cubins[] = {"gemv.cubin", "chain.cubin", "batched.cubin", "batched_tc.cubin", "deltanet.cubin", "attention.cubin", "attention_mma.cubin", "small.cubin", "comm.cubin", "prefill.cubin"};
 
 LB_API int lb_init(int device, const char* kernel_dir, lb_ctx** out) {
     if (!out) return LB_ERR_INVALID;

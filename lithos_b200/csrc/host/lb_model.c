@@ -11,64 +11,11 @@
  *                    attention + sigmoid gate]  [o projection + residual]
  *   MLP            : [RMSNorm + gate|up projection + SwiGLU]  [down projection + residual]
  */
-#include "lb_internal.h"
-#include "../kernels/params.h"
+#include "lb_model_priv.h"
 #include <math.h>
 
-enum { /* src/launcher.s:92-141 */
-    WS_DN_QKV = 0, WS_DN_Z = 3, WS_DN_OUT = 6, WS_DN_PROJ_A = 9, WS_DN_PROJ_B = 10, WS_DN_A_LOG = 11, WS_DN_DT_BIAS = 12,
-    WS_DN_CONV1D = 13, WS_DN_NORM = 14,
-    WS_FA_Q = 0, WS_FA_K = 3, WS_FA_V = 6, WS_FA_O = 9, WS_FA_Q_NORM = 12, WS_FA_K_NORM = 13,
-    WS_GATE = 15, WS_UP = 18, WS_DOWN = 21, WS_INPUT_NORM = 24, WS_POST_NORM = 25,
-    WG_EMBED = 0, WG_LM_HEAD = 1, WG_FINAL_NORM = 2
-};
-
-typedef struct {
-    CUdeviceptr qweight, scales, qzeros; /* the reference format */
-    CUdeviceptr packed;                  /* strip-packed copy for the persistent GEMV chain (0 = none) */
-    int K, N;
-} q4_mat;
-
-typedef struct {
-    int is_fa;
-    q4_mat w_in, w_out, w_gateup, w_down;
-    CUdeviceptr input_norm, post_norm;
-    /* DeltaNet */
-    CUdeviceptr proj_a, proj_b, a_log, dt_bias, conv_w, dn_norm, dn_state, conv_ring;
-    CUdeviceptr snap_state, snap_conv; /* lb_model_checkpoint copies of dn_state and conv_ring (allocated on first use) */
-    CUdeviceptr dn_params; /* lb_dn_layer_params of this layer in device memory, for the persistent chain */
-    /* attention */
-    CUdeviceptr q_norm, k_norm, k_cache, v_cache;
-    int loaded;
-} layer_t;
-
-struct lb_model {
-    lb_ctx* c;
-    lb_model_cfg cfg;
-    int tp_rank, tp_size;
-    /* per-shard sizes */
-    int HV, HK, HQ, HKV, inter_s; /* heads / intermediate columns on this shard */
-    int C_s;                      /* conv channels on this shard: 2*HK*128 + HV*128 */
-    layer_t* L;
-    CUdeviceptr embed, lm_head, final_norm;
-    int globals_loaded;
-    /* activations */
-    CUdeviceptr X, xn, in_out, mix_out, mlp_m, logits, d_token, d_pos, d_next, cand_val, cand_idx;
-    int* h_next; /* pinned */
-    int host_pos;  /* position the next step will decode, as the host knows it: set_input's value plus the steps issued since */
-    uint64_t weight_bytes;
-    lb_graph* graph;
-    int step_kernels;
-    lb_comm* comm;   /* tensor parallel: exchange buffers */
-    int vocab_s;     /* vocabulary rows on this shard */
-    int ar_count;    /* all-reduces issued so far in the step being built (slot parity) */
-    int use_chain;   /* consecutive GEMVs of the step go out as one persistent launch (lb_gemv_chain) */
-    CUdeviceptr tp_params[2]; /* tensor parallel: lb_tp_params of the two exchange slots in device memory, for the chain */
-    lb_chain_op pend[LB_CHAIN_MAX_OPS]; /* GEMVs and DeltaNet mixers collected since the last stand-alone kernel */
-    int n_pend;
-};
-
 static void dn_fill_params(const lb_model* m, const layer_t* L, lb_dn_layer_params* p);
+extern void lb_prefill_ws_free(lb_model* m);
 extern int lb_comm_fill(const lb_comm* m, lb_tp_params* p, int slot, int n);
 extern uint64_t lb_comm_slot_ptr(const lb_comm* m, int slot);
 
@@ -600,6 +547,36 @@ static int row_parallel(lb_model* m, const q4_mat* w, CUdeviceptr x, int x_mode,
     return lb_launch(m->c, LBK_tp_allreduce_add, 1, 1, 1, 1024, 0, params, 1);
 }
 
+int lb_model_is_fa(const lb_model_cfg* c, int l) { return is_fa(c, l); }
+
+int lb_model_launch_attention(lb_model* m, const layer_t* L, CUdeviceptr proj_row, CUdeviceptr out, CUdeviceptr pos_ptr, int pos, int splits_for) {
+    lb_ctx* c = m->c;
+    const lb_model_cfg* cfg = &m->cfg;
+    lb_attn_params p;
+    memset(&p, 0, sizeof p);
+    const size_t nq = (size_t)2 * m->HQ * 256, nkv = (size_t)m->HKV * 256;
+    p.q = (const void*)proj_row;                      /* per head: 256 query then 256 gate columns */
+    p.gate = (const void*)(proj_row + 256 * 4);
+    p.k_new = (const void*)(proj_row + nq * 4);
+    p.v_new = (const void*)(proj_row + (nq + nkv) * 4);
+    p.q_norm_w = (const uint16_t*)L->q_norm; p.k_norm_w = (const uint16_t*)L->k_norm;
+    p.k_cache = (uint16_t*)L->k_cache; p.v_cache = (uint16_t*)L->v_cache;
+    p.out = (float*)out; p.scratch = (float*)c->attn_scratch;
+    p.counters = (uint32_t*)(c->gemv_counters + 2048 * 4);
+    p.pos_ptr = (const int*)pos_ptr; p.pos = pos;
+    p.HQ = m->HQ; p.HKV = m->HKV;
+    p.splits = lb_attn_mma_splits(c, splits_for, m->HKV);
+    p.status = (uint32_t*)c->dev_status;
+    p.coop = m->HKV * p.splits <= c->sm_count;
+    p.max_ctx = cfg->max_ctx;
+    p.in_dtype = 1; p.gate_stride = 512; p.q_stride = 512;
+    p.rot_dims = cfg->rot_dims; p.rope_theta = cfg->rope_theta; p.eps = cfg->eps;
+    for (int i = 0; i < cfg->rot_dims / 2; i++)
+        p.rope_freq[i] = exp2(-log2((double)cfg->rope_theta) * (double)i / (double)(cfg->rot_dims / 2));
+    void* params[] = {&p};
+    return lb_launch(c, LBK_attn_decode_mma, (unsigned)m->HKV, (unsigned)p.splits, 1, 256, lb_attn_mma_smem(m->HQ / m->HKV), params, 1);
+}
+
 static int issue_step(lb_model* m) {
     lb_ctx* c = m->c;
     const lb_model_cfg* cfg = &m->cfg;
@@ -633,31 +610,8 @@ static int issue_step(lb_model* m) {
             LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32_HEADNORM_SILU, L->dn_norm, m->in_out + (size_t)C * 4));
         } else {
             LB_TRY(q4_gemv(m, &L->w_in, m->X, m->in_out, LB_X_F32_RMSNORM, LB_Y_F32, L->input_norm, 0, 0));
-            lb_attn_params p;
-            memset(&p, 0, sizeof p);
-            const size_t nq = (size_t)2 * m->HQ * 256, nkv = (size_t)m->HKV * 256;
-            p.q = (const void*)m->in_out;                      /* per head: 256 query then 256 gate columns */
-            p.gate = (const void*)(m->in_out + 256 * 4);
-            p.k_new = (const void*)(m->in_out + nq * 4);
-            p.v_new = (const void*)(m->in_out + (nq + nkv) * 4);
-            p.q_norm_w = (const uint16_t*)L->q_norm; p.k_norm_w = (const uint16_t*)L->k_norm;
-            p.k_cache = (uint16_t*)L->k_cache; p.v_cache = (uint16_t*)L->v_cache;
-            p.out = (float*)m->mix_out; p.scratch = (float*)c->attn_scratch;
-            p.counters = (uint32_t*)(c->gemv_counters + 2048 * 4);
-            p.pos_ptr = (const int*)m->d_pos; p.pos = 0;
-            p.HQ = m->HQ; p.HKV = m->HKV;
-            p.splits = lb_attn_mma_splits(c, cfg->max_ctx, m->HKV);
-            p.status = (uint32_t*)c->dev_status;
-            p.coop = m->HKV * p.splits <= c->sm_count;
-            p.max_ctx = cfg->max_ctx;
-            p.in_dtype = 1; p.gate_stride = 512; p.q_stride = 512;
-            p.rot_dims = cfg->rot_dims; p.rope_theta = cfg->rope_theta; p.eps = cfg->eps;
-            for (int i = 0; i < cfg->rot_dims / 2; i++)
-                p.rope_freq[i] = exp2(-log2((double)cfg->rope_theta) * (double)i / (double)(cfg->rot_dims / 2));
-            void* params[] = {&p};
             LB_TRY(flush_chain(m));
-            LB_TRY(lb_launch(c, LBK_attn_decode_mma, (unsigned)m->HKV, (unsigned)p.splits, 1, 256,
-                             lb_attn_mma_smem(m->HQ / m->HKV), params, 1));
+            LB_TRY(lb_model_launch_attention(m, L, m->in_out, m->mix_out, m->d_pos, 0, cfg->max_ctx));
             LB_TRY(row_parallel(m, &L->w_out, m->mix_out, LB_X_F32, 0, 0));
         }
         LB_TRY(q4_gemv(m, &L->w_gateup, m->X, m->mlp_m, LB_X_F32_RMSNORM, LB_Y_SWIGLU_F16, L->post_norm, 0, 0));
@@ -790,6 +744,7 @@ LB_API void lb_model_destroy(lb_model* m) {
                                L->snap_state, L->snap_conv};
             for (size_t i = 0; i < sizeof p / sizeof p[0]; i++) if (p[i]) lb_drv.MemFree(p[i]);
         }
+        lb_prefill_ws_free(m);
         if (m->h_next) lb_drv.MemFreeHost(m->h_next);
     }
     free(m->L);

@@ -1,0 +1,164 @@
+/* The prompt pass: lb_model_prefill runs n prompt tokens through the model in chunks of up to 128 and leaves the state a
+ * token-by-token decode of the same tokens leaves (DeltaNet states, convolution rings, KV rows), then samples the token
+ * that follows the prompt.
+ *
+ * The reference's prompt path is its dequantising tensor-core GEMM (kernels/projection_gemm.sass:390-631) in the layer
+ * order of compiler/megakernel-link.ls:281-525.  Here every projection of a chunk is one lb_gemm_int4 call (the weights
+ * are read once per chunk: tcgen05 for 33..128 tokens), the DeltaNet recurrence walks the chunk's tokens inside one
+ * launch with the state held on chip (lb_deltanet_step, n_steps = chunk), and attention runs the decode kernel once per
+ * token over the cache rows before it (causal by construction).  Single GPU only.
+ */
+#include "lb_model_priv.h"
+
+extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps,
+                           uint64_t part_val, uint64_t part_idx);
+extern int lb_dense_ctas(lb_ctx* c, int N, int K);
+
+#define PF_CHUNK 128
+
+struct lb_prefill_ws {
+    CUdeviceptr tokens, X, xn16, proj, q, k, v, g, beta, mix, mix16, y, gu, act16;
+};
+
+static int ws_alloc(lb_model* m) {
+    if (m->ws) return LB_OK;
+    lb_prefill_ws* w = (lb_prefill_ws*)calloc(1, sizeof *w);
+    if (!w) return LB_ERR_NOMEM;
+    m->ws = w;
+    const lb_model_cfg* c = &m->cfg;
+    const size_t T = PF_CHUNK, H = (size_t)c->hidden, I = (size_t)m->inter_s;
+    size_t n_in = (size_t)m->C_s + (size_t)m->HV * 128, n_fa = (size_t)(2 * m->HQ + 2 * m->HKV) * 256;
+    if (n_fa > n_in) n_in = n_fa;
+    size_t n_mix = (size_t)m->HV * 128 > (size_t)m->HQ * 256 ? (size_t)m->HV * 128 : (size_t)m->HQ * 256;
+    struct { CUdeviceptr* p; size_t bytes; } a[] = {
+        {&w->tokens, T * 4}, {&w->X, T * H * 4}, {&w->xn16, T * H * 2}, {&w->proj, T * n_in * 4},
+        {&w->q, T * (size_t)m->HK * 128 * 4}, {&w->k, T * (size_t)m->HK * 128 * 4}, {&w->v, T * (size_t)m->HV * 128 * 4},
+        {&w->g, T * (size_t)m->HV * 4}, {&w->beta, T * (size_t)m->HV * 4}, {&w->mix, T * n_mix * 4}, {&w->mix16, T * n_mix * 2},
+        {&w->y, T * H * 4}, {&w->gu, T * 2 * I * 4}, {&w->act16, T * I * 2}};
+    for (size_t i = 0; i < sizeof a / sizeof a[0]; i++) {
+        uint64_t d = 0;
+        LB_TRY(lb_malloc(m->c, a[i].bytes, &d));
+        *a[i].p = (CUdeviceptr)d;
+    }
+    return LB_OK;
+}
+
+void lb_prefill_ws_free(lb_model* m) {
+    if (!m->ws) return;
+    CUdeviceptr* p = (CUdeviceptr*)m->ws;
+    for (size_t i = 0; i < sizeof(lb_prefill_ws) / sizeof(CUdeviceptr); i++)
+        if (p[i]) lb_drv.MemFree(p[i]);
+    free(m->ws);
+    m->ws = NULL;
+}
+
+static unsigned blocks_for(long long n) {
+    long long b = (n + 255) / 256;
+    return (unsigned)(b > 4096 ? 4096 : b < 1 ? 1 : b);
+}
+
+static int gemm(lb_model* m, const q4_mat* w, CUdeviceptr x16, CUdeviceptr y32, int T) {
+    return lb_gemm_int4(m->c, w->qweight, w->scales, w->qzeros, x16, y32, w->K, w->N, T, LB_GEMV_Y_F32);
+}
+
+static int add_into_x(lb_model* m, int T) {
+    lb_prefill_ws* w = m->ws;
+    long long n = (long long)T * m->cfg.hidden;
+    void* params[] = {&w->X, &w->y, &n};
+    return lb_launch(m->c, LBK_pf_add, blocks_for(n), 1, 1, 256, 0, params, 1);
+}
+
+static int norm_f16(lb_model* m, CUdeviceptr norm_w, int T) {
+    lb_prefill_ws* w = m->ws;
+    int D = m->cfg.hidden;
+    float eps = m->cfg.eps;
+    void* params[] = {&w->X, &norm_w, &w->xn16, &D, &eps};
+    return lb_launch(m->c, LBK_pf_rmsnorm_f16, (unsigned)T, 1, 1, 256, 0, params, 1);
+}
+
+static int chunk_layer(lb_model* m, int l, int pos0, int T) {
+    lb_ctx* c = m->c;
+    lb_prefill_ws* w = m->ws;
+    const lb_model_cfg* cfg = &m->cfg;
+    layer_t* L = &m->L[l];
+    const int H = cfg->hidden;
+    if (!L->loaded) return lb_fail(c, LB_ERR_STATE, "model: layer %d has no weights", l);
+    LB_TRY(norm_f16(m, L->input_norm, T));
+    LB_TRY(gemm(m, &L->w_in, w->xn16, w->proj, T));
+    int ld = L->w_in.N;
+    if (!L->is_fa) {
+        const int C = m->C_s, HK = m->HK, HV = m->HV;
+        {
+            void* params[] = {&w->proj, &ld, &L->conv_w, &L->conv_ring, &w->q, &w->k, &w->v, (void*)&HK, (void*)&HV, &pos0, &T};
+            LB_TRY(lb_launch(c, LBK_pf_dn_frontend, (unsigned)(2 * HK + HV), 1, 1, 128, 0, params, 1));
+        }
+        {
+            void* params[] = {&w->xn16, &L->proj_a, &L->proj_b, &L->a_log, &L->dt_bias, &w->g, &w->beta, (void*)&HV, (void*)&H};
+            LB_TRY(lb_launch(c, LBK_pf_ab_gate, (unsigned)T, (unsigned)((HV + 3) / 4), 1, 128, 0, params, 1));
+        }
+        LB_TRY(lb_deltanet_step(c, L->dn_state, w->q, w->k, w->v, 0, w->g, w->beta, w->mix, HV, HK, T, 1));
+        {
+            float eps = cfg->eps;
+            int z_off = C;
+            void* params[] = {&w->mix, &w->proj, &ld, &z_off, &L->dn_norm, &w->mix16, (void*)&HV, &eps};
+            LB_TRY(lb_launch(c, LBK_pf_headnorm_gate_f16, (unsigned)T, (unsigned)((HV + 3) / 4), 1, 128, 0, params, 1));
+        }
+    } else {
+        const size_t row = (size_t)ld * 4, orow = (size_t)m->HQ * 256 * 4;
+        for (int s = 0; s < T; s++) /* causal: token s attends the cache rows [0, pos0 + s], its own appended first */
+            LB_TRY(lb_model_launch_attention(m, L, w->proj + (size_t)s * row, w->mix + (size_t)s * orow, 0, pos0 + s, pos0 + s + 1));
+        long long n = (long long)T * m->HQ * 256;
+        void* params[] = {&w->mix, &w->mix16, &n};
+        LB_TRY(lb_launch(c, LBK_pf_f32_to_f16, blocks_for(n), 1, 1, 256, 0, params, 1));
+    }
+    LB_TRY(gemm(m, &L->w_out, w->mix16, w->y, T));
+    LB_TRY(add_into_x(m, T));
+    /* MLP */
+    LB_TRY(norm_f16(m, L->post_norm, T));
+    LB_TRY(gemm(m, &L->w_gateup, w->xn16, w->gu, T));
+    {
+        int I = m->inter_s;
+        long long total = (long long)T * I;
+        void* params[] = {&w->gu, &w->act16, &I, &total};
+        LB_TRY(lb_launch(c, LBK_pf_swiglu_f16, blocks_for(total), 1, 1, 256, 0, params, 1));
+    }
+    LB_TRY(gemm(m, &L->w_down, w->act16, w->y, T));
+    return add_into_x(m, T);
+}
+
+LB_API int lb_model_prefill(lb_model* m, const int* tokens, int n, int pos0, int* next_out) {
+    if (!m || !tokens || n < 1 || pos0 < 0) return LB_ERR_INVALID;
+    lb_ctx* c = m->c;
+    const lb_model_cfg* cfg = &m->cfg;
+    if (m->tp_size != 1) return lb_fail(c, LB_ERR_STATE, "lb_model_prefill: single GPU only (this model is shard %d of %d)", m->tp_rank, m->tp_size);
+    if (pos0 + n > cfg->max_ctx) return lb_fail(c, LB_ERR_INVALID, "lb_model_prefill: %d tokens from position %d run past the context of %d rows", n, pos0, cfg->max_ctx);
+    for (int i = 0; i < n; i++)
+        if (tokens[i] < 0 || tokens[i] >= cfg->vocab) return lb_fail(c, LB_ERR_INVALID, "lb_model_prefill: token %d at %d out of range", tokens[i], i);
+    if (!m->globals_loaded) return lb_fail(c, LB_ERR_STATE, "model: globals have no weights");
+    LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
+    LB_TRY(ws_alloc(m));
+    lb_prefill_ws* w = m->ws;
+    const int H = cfg->hidden;
+    for (int c0 = 0; c0 < n; c0 += PF_CHUNK) {
+        const int T = n - c0 < PF_CHUNK ? n - c0 : PF_CHUNK;
+        LB_CU(c, lb_drv.MemcpyHtoDAsync(w->tokens, tokens + c0, (size_t)T * 4, c->stream));
+        LB_CU(c, lb_drv.StreamSynchronize(c->stream)); /* the caller's token array may be pageable */
+        {
+            void* params[] = {&m->embed, &w->tokens, &w->X, (void*)&H};
+            LB_TRY(lb_launch(c, LBK_pf_embed, (unsigned)T, 1, 1, 256, 0, params, 1));
+        }
+        for (int l = 0; l < cfg->n_layers; l++) LB_TRY(chunk_layer(m, l, pos0 + c0, T));
+        if (c0 + T == n) { /* the last prompt token's hidden state -> final norm, LM head, greedy sample */
+            LB_CU(c, lb_drv.MemcpyDtoDAsync(m->X, w->X + (size_t)(T - 1) * H * 4, (size_t)H * 4, c->stream));
+        }
+    }
+    LB_CU(c, lb_drv.MemsetD32Async(m->d_pos, (unsigned)(pos0 + n - 1), 1, c->stream)); /* the sampling kernel advances it */
+    LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, m->vocab_s, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps, m->cand_val, m->cand_idx));
+    {
+        int nc = lb_dense_ctas(c, m->vocab_s, H);
+        void* params[] = {&m->cand_val, &nc, &m->d_next, &m->d_token, &m->d_pos, &m->cand_idx};
+        LB_TRY(lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1));
+    }
+    m->host_pos = pos0 + n;
+    return next_out ? lb_model_read_next(m, next_out) : LB_OK;
+}

@@ -113,6 +113,7 @@ def _sigs():
     L.lb_model_set_input.argtypes = [vp, i32, i32]
     L.lb_model_replay.argtypes = [vp, i32]
     L.lb_model_read_next.argtypes = [vp, P(i32)]
+    L.lb_model_prefill.argtypes = [vp, P(i32), i32, i32, P(i32)]
     L.lb_model_step_kernels.argtypes = [vp]
     _sigs_done = True
 
@@ -244,6 +245,13 @@ class Model:
 
     def replay(self, n_steps: int = 1):
         self.ctx._check(lib().lb_model_replay(self.h, n_steps))
+
+    def prefill(self, tokens, pos0: int = 0) -> int:
+        """run the prompt through the model in chunks; returns the greedy token that follows it"""
+        arr = (C.c_int * len(tokens))(*[int(t) for t in tokens])
+        nxt = C.c_int(0)
+        self.ctx._check(lib().lb_model_prefill(self.h, arr, len(tokens), pos0, C.byref(nxt)))
+        return nxt.value
 
     def read_next(self) -> int:
         nxt = C.c_int(0)
