@@ -512,7 +512,21 @@ def bench_decode(args, rank, local, world, dist):
     if comm is not None:
         tp.attach(model, comm)
     model.fill_synthetic(args.seed)
-    model.seed_state(CTX_PREFILL, args.seed)     # ONE global seeded state; every rank takes its heads of it
+    prefill_rec = None
+    if args.prefill and world == 1:
+        # the state is PRODUCED by the model: a seeded random token stream of 4096 tokens through the prompt pass
+        prompt = (lb.fill_u32(CTX_PREFILL, args.seed, 500000) % cfg.vocab).astype(np.int64).tolist()
+        model.prefill(prompt[:128])                      # untimed: allocates the prompt-pass buffers, loads the kernels
+        model.reset_state()
+        ctx.sync()
+        t_p = time.perf_counter()
+        model.prefill(prompt)
+        ctx.sync()
+        t_p = time.perf_counter() - t_p
+        prefill_rec = {"tokens": CTX_PREFILL, "seconds": round(t_p, 3), "tok_s": round(CTX_PREFILL / t_p, 1),
+                       "how": "lb_model_prefill: 32 chunks of 128 tokens, batched int4 projections (tcgen05), recurrence on chip per chunk, decode attention per token"}
+    else:
+        model.seed_state(CTX_PREFILL, args.seed)     # ONE global seeded state; every rank takes its heads of it
     model.checkpoint()                           # the recurrent state is restored before every measured pass
     build_s = time.perf_counter() - t0
     if args.no_chain:
@@ -592,9 +606,11 @@ def bench_decode(args, rank, local, world, dist):
         "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int4 weights, fp16 activations (exact integer dot products), fp32 state", "data": "synthetic",
-        "config": {"workload": WORKLOAD if cfg.n_layers == 64 else WORKLOAD.replace("64-layer", f"{cfg.n_layers}-layer"),
+        "config": {"workload": (WORKLOAD if cfg.n_layers == 64 else WORKLOAD.replace("64-layer", f"{cfg.n_layers}-layer")).replace(
+                       "by seeded fill", "by the prompt pass over a seeded random token stream" if prefill_rec else "by seeded fill"),
                    "parallelism": f"tp{world}", "l2": f"every step streams {algo_step / 1e9:.2f} GB of weights/state (>> 126 MB L2)",
                    "kernels_per_step": kernels_per_step, "build_seconds": round(build_s, 1), "last_token": int(last_token)},
+        "prefill": prefill_rec,
         "parity": {"first_tokens": first_tokens, "logits_hash_after_16": lhash,
                    "what": "greedy tokens of the first 16 steps from (token 1, position 4096) on the seeded state: the same list at every N "
                            "is the tensor-parallel parity (TP=n tokens == TP=1 tokens); at N=1 the first of them are also checked against the CPU oracle"},
@@ -620,7 +636,7 @@ def bench_decode(args, rank, local, world, dist):
     if world == 1 and not args.no_small and cfg.n_layers == 64:
         out.update(bench_small_configs(ctx, lb))
     ctx.close()
-    if rank == 0 and not args.no_cpu and world == 1 and cfg.n_layers == 64:
+    if rank == 0 and not args.no_cpu and world == 1 and cfg.n_layers == 64 and not prefill_rec:
         toks, dt, cores, b_s = oracle_decode_run(args.seed, CTX_PREFILL, 1, 2)
         out["cpu_baseline"] = {"value": 1.0 / dt, "unit": "tok/s", "cores": cores, "kind": "port",
                                "sample": f"3 full decode steps (64 layers + LM head) of the same seeded model and state with the C oracle (OpenMP, {cores} "
@@ -799,6 +815,8 @@ def main():
     ap.add_argument("--batched-batches", default="1,4,16,32,64,128", help="batched workload: batch sizes")
     ap.add_argument("--seed", type=int, default=20260413)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--prefill", action="store_true", help="decode workload, 1 GPU: build the 4096-token state by running a seeded random prompt through "
+                    "lb_model_prefill instead of filling it directly; reports prompt tok/s (the CPU leg is skipped: the oracle would need 4096 steps)")
     ap.add_argument("--no-small", action="store_true", help="decode workload: skip the one-figure measurements of configs 0, 1 and 2")
     ap.add_argument("--no-chain", action="store_true", help="decode workload: one launch per projection instead of persistent chains")
     ap.add_argument("--ramp-s", type=float, default=1.5, help="seconds of untimed work before warm-up (clock ramp)")
