@@ -69,6 +69,10 @@ void lb_set_pdl(lb_ctx* ctx, int on);
 /* bytes of an SM's shared memory lb_gemv_chain leaves free so that a CTA of the kernel before/after it can be
  * resident at the same time (default 32 KB; 0 = the deepest weight ring) */
 void lb_set_chain_reserve(lb_ctx* ctx, int bytes);
+/* on (default): where a GEMV of a chain reads the result vector of the GEMV right before it, the vector is handed over
+ * as tagged 8-byte words that the consumer's loads wait on, and no grid barrier separates the two; off: a grid barrier
+ * between every pair of entries.  Same results either way (the words carry the same fp32 / fp16 values). */
+void lb_set_chain_mailbox(lb_ctx* ctx, int on);
 /* Profiling hook: while buf != 0, every persistent-chain launch made (or captured) afterwards writes, for each SM and
  * chain entry, five %globaltimer values (ns) of the SM's thread 0 -- reached the grid barrier, left it, activation
  * table ready / mixer started, every weight stage consumed, entry finished (epilogue and, under tensor parallelism, the

@@ -108,6 +108,7 @@ def lib() -> C.CDLL:
     sig("lb_gemv_pack", i32, vp, u64, u64, u64, i32, i32, i32, u64)
     sig("lb_set_chain_reserve", None, vp, i32)
     sig("lb_set_chain_timeline", None, vp, u64)
+    sig("lb_set_chain_mailbox", None, vp, i32)
     sig("lb_gemv_pack_version", i32)
     sig("lb_gptq_dequant", i32, vp, u64, u64, u64, u64, i32, i32)
     sig("lb_gemm_int4", i32, vp, u64, u64, u64, u64, u64, i32, i32, i32, i32)
@@ -296,6 +297,10 @@ class Context:
 
     def reset_launches(self):
         lib().lb_launch_count_reset(self.h)
+
+    def set_chain_mailbox(self, on: bool):
+        """hand vectors between consecutive GEMVs of a chain through tagged words (default) or through a grid barrier"""
+        lib().lb_set_chain_mailbox(self.h, 1 if on else 0)
 
     def set_pdl(self, on: bool):
         lib().lb_set_pdl(self.h, 1 if on else 0)

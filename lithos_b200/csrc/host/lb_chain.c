@@ -90,6 +90,27 @@ int lb_chain_launch(lb_ctx* c, const lb_chain_op* ops, int n_ops) {
     chain_plan pl;
     chain_plan_make(c, ops, n_ops, &pl);
     if (!pl.slots) return lb_fail(c, LB_ERR_INVALID, "chain: %d entries (longest K %d) do not fit shared memory", n_ops, pl.table_rows * 8);
+    /* GEMV fed by the GEMV right before it: hand the vector over through the producer's mailbox instead of a grid barrier */
+    for (int i = 1; i < n_ops; i++) {
+        lb_chain_op *a = &p.op[i - 1], *b = &p.op[i];
+        if (!c->chain_mailbox || a->type != LB_CHAIN_OP_GEMV || b->type != LB_CHAIN_OP_GEMV || b->x != a->y) continue;
+        /* without a barrier the consumer may read, besides the tagged vector, only what its own threads wrote before: an
+         * accumulate target must have been written by the same column owners (same N) wherever this launch wrote it */
+        int own = 1;
+        if (b->y_mode == LB_Y_F32_ACCUM || b->y_mode == LB_Y_TP_ALLREDUCE)
+            for (int j = 0; j < i; j++)
+                if (p.op[j].type == LB_CHAIN_OP_GEMV && p.op[j].y == b->y && p.op[j].N != b->N) own = 0;
+        if (!own) continue;
+        const int f32_out = a->y_mode == LB_Y_F32 || a->y_mode == LB_Y_F32_ACCUM || a->y_mode == LB_Y_TP_ALLREDUCE;
+        const int f16_out = a->y_mode == LB_Y_SWIGLU_F16;
+        const int f32_in = b->x_mode == LB_X_F32 || b->x_mode == LB_X_F32_RMSNORM, f16_in = b->x_mode == LB_X_F16;
+        if ((f32_out && f32_in && a->N == b->K && a->N <= LB_CHAIN_MAIL_WORDS) ||
+            (f16_out && f16_in && a->N / 2 == b->K && a->N / 4 <= LB_CHAIN_MAIL_WORDS)) {
+            a->mail = 1;
+            b->x_src = i; /* index of the producer + 1 */
+        }
+    }
+    p.mail = (unsigned long long*)c->chain_mail;
     p.slots = pl.slots;
     p.table_rows = pl.table_rows;
     p.max_pairs = pl.max_pairs;

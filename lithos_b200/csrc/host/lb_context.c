@@ -6,6 +6,7 @@
  */
 #define _GNU_SOURCE
 #include "lb_internal.h"
+#include "../kernels/params.h"
 #include <dlfcn.h>
 #include <stdarg.h>
 
@@ -184,6 +185,9 @@ LB_API int lb_init(int device, const char* kernel_dir, lb_ctx** out) {
     c->attn_scratch_bytes = (size_t)8 * 64 * 8 * 260 * sizeof(float) + 256;
     LB_CU(c, lb_drv.MemAlloc(&c->attn_scratch, c->attn_scratch_bytes));
     LB_CU(c, lb_drv.MemsetD8Async(c->attn_scratch, 0, c->attn_scratch_bytes, c->stream));
+    LB_CU(c, lb_drv.MemAlloc(&c->chain_mail, (size_t)LB_CHAIN_MAX_OPS * LB_CHAIN_MAIL_WORDS * 8));
+    LB_CU(c, lb_drv.MemsetD8Async(c->chain_mail, 0, (size_t)LB_CHAIN_MAX_OPS * LB_CHAIN_MAIL_WORDS * 8, c->stream));
+    c->chain_mailbox = 1;
     LB_CU(c, lb_drv.MemAlloc(&c->dev_status, 256));
     LB_CU(c, lb_drv.MemsetD8Async(c->dev_status, 0, 256, c->stream));
     c->flush_bytes = (size_t)256 << 20;
@@ -204,6 +208,7 @@ LB_API void lb_destroy(lb_ctx* c) {
         if (c->gemv_counters) lb_drv.MemFree(c->gemv_counters);
         if (c->attn_scratch) lb_drv.MemFree(c->attn_scratch);
         if (c->dev_status) lb_drv.MemFree(c->dev_status);
+        if (c->chain_mail) lb_drv.MemFree(c->chain_mail);
         if (c->flush_buf) lb_drv.MemFree(c->flush_buf);
         for (int m = 0; m < c->n_modules; m++) lb_drv.ModuleUnload(c->modules[m]);
         if (c->ev[0]) lb_drv.EventDestroy(c->ev[0]);
@@ -220,6 +225,7 @@ LB_API uint64_t lb_launch_count(const lb_ctx* c) { return c ? c->launches : 0; }
 LB_API void lb_launch_count_reset(lb_ctx* c) { if (c) c->launches = 0; }
 LB_API void lb_set_pdl(lb_ctx* c, int on) { if (c) c->pdl = on ? 1 : 0; }
 LB_API void lb_set_chain_timeline(lb_ctx* c, uint64_t buf) { if (c) c->chain_timeline = (CUdeviceptr)buf; }
+LB_API void lb_set_chain_mailbox(lb_ctx* c, int on) { if (c) c->chain_mailbox = on ? 1 : 0; }
 LB_API void lb_set_chain_reserve(lb_ctx* c, int bytes) { if (c && bytes >= 0 && bytes <= 128 * 1024) c->chain_reserve = bytes; }
 
 LB_API int lb_device_status(lb_ctx* c, uint32_t* out) {

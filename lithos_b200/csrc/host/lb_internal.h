@@ -149,6 +149,8 @@ struct lb_ctx {
     int pdl;           /* use programmatic dependent launch between kernels */
     CUdeviceptr chain_timeline; /* optional time-stamp buffer handed to every chain launch (lb_set_chain_timeline) */
     int chain_reserve; /* bytes of an SM's shared memory the GEMV chain leaves to a neighbouring kernel's CTA */
+    CUdeviceptr chain_mail; /* mailboxes of the persistent chain: LB_CHAIN_MAX_OPS x LB_CHAIN_MAIL_WORDS 8-byte (value, tag) words */
+    int chain_mailbox;      /* hand vectors from a GEMV to the next one through the mailbox (1, default) or a grid barrier (0) */
     int capturing;     /* stream capture in progress */
     uint64_t capture_launches0;
     char err[512];

@@ -27,7 +27,15 @@
 //   * Between entries the block meets the other blocks at a grid barrier (an arrival counter in
 //     global memory: release-add, acquire poll, bounded spin).  All CTAs are resident: the grid is one
 //     CTA per SM and a CTA takes more than half of an SM's shared memory.
-// Activations written inside the launch are read through L2 only (ld.global.cg).
+//   * Where a GEMV's input vector is the result of the GEMV right before it (out projection -> gate/up -> down -> next
+//     input projection), no grid barrier separates them.  The producer's threads store every result a second time as
+//     an 8-byte word (value, tag) into the entry's mailbox -- one store, delivered whole -- with tag = launch base +
+//     entry index; the consumer's activation-table loads read those words and simply repeat a row until all its tags
+//     are this launch's.  The wait for the slowest producer and the table's trip to L2 become one, and the arrive /
+//     poll / release-fence round trips of a barrier disappear.  A buffer is never overwritten while someone may still
+//     read it: a CTA reaches the epilogue of entry o+1 only after it has seen every CTA's results of entry o, which a
+//     CTA publishes after it has finished reading entry o-1's.
+// Activations written inside the launch are read through L2 only (ld.global.cg / ld.volatile).
 #include "gemv_core.cuh"
 #include "deltanet_core.cuh"
 #include "comm_core.cuh"
@@ -142,7 +150,8 @@ __device__ __forceinline__ void ch_stage_items(const unsigned char* stage, int g
 // Thread tid owns packed rows tid, tid + 512, ... (NI of them at most); all global loads are issued before the
 // first use, so the prologue costs one trip to L2, not one per row.
 template <int NI>
-__device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& sh, uint32_t* xdig, float* xsumf, int tid, bool write_x) {
+__device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& sh, uint32_t* xdig, float* xsumf, int tid, bool write_x,
+                                             const unsigned long long* mailbox, uint32_t tag, uint32_t* status) {
     const int lane = tid & 31, warp = tid >> 5;
     const int rows = op.K / 8;
     float pre_max = -1.f; // >= 0: the largest |h| is already known (no second block-wide exchange)
@@ -152,8 +161,28 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
         for (int i = 0; i < NI; ++i) {
             const int r = tid + i * LB_CHAIN_THREADS;
             uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-            if (r < rows) raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(op.x) + r * 8));
+            if (r < rows && !mailbox) raw = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(op.x) + r * 8));
             hv[i][0] = raw.x; hv[i][1] = raw.y; hv[i][2] = raw.z; hv[i][3] = raw.w;
+        }
+        if (mailbox) { // the producer's (two fp16 values, tag) words: a row of 8 values is 4 words; repeat until all are this launch's
+            const uint64_t t0 = globaltimer_ns(), limit = 2 * lb_wait_limit_ns(status); // twice: whoever the producers wait for reports first
+            for (unsigned it = 0;; ++it) {
+                bool ok = true;
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int r = tid + i * LB_CHAIN_THREADS;
+                    if (r >= rows) continue;
+                    const uint4 a = ld_volatile_v4(mailbox + (size_t)r * 4), b = ld_volatile_v4(mailbox + (size_t)r * 4 + 2);
+                    ok = ok && a.y == tag && a.w == tag && b.y == tag && b.w == tag;
+                    hv[i][0] = a.x; hv[i][1] = a.z; hv[i][2] = b.x; hv[i][3] = b.z;
+                }
+                if (ok) break;
+                if ((it & 15u) == 15u && (it >= LB_WAIT_SPINS || globaltimer_ns() - t0 > limit || *reinterpret_cast<volatile uint32_t*>(status) != 0u)) {
+                    atomicCAS(status, 0u, LB_DEV_TIMEOUT_COUNTER);
+                    sh.bad = 1;
+                    break;
+                }
+            }
         }
     } else {
         float v[NI][8];
@@ -161,13 +190,37 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
         for (int i = 0; i < NI; ++i) {
             const int r = tid + i * LB_CHAIN_THREADS;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-            if (r < rows) {
+            if (r < rows && !mailbox) {
                 const float4* xv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.x) + r * 8);
                 a = __ldcg(xv);
                 b = __ldcg(xv + 1);
             }
             v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w;
             v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+        }
+        if (mailbox) { // the producer's (fp32 value, tag) words: a row of 8 values is 8 words
+            const uint64_t t0 = globaltimer_ns(), limit = 2 * lb_wait_limit_ns(status); // twice: whoever the producers wait for reports first
+            for (unsigned it = 0;; ++it) {
+                bool ok = true;
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int r = tid + i * LB_CHAIN_THREADS;
+                    if (r >= rows) continue;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 a = ld_volatile_v4(mailbox + (size_t)r * 8 + 2 * j);
+                        ok = ok && a.y == tag && a.w == tag;
+                        v[i][2 * j] = __uint_as_float(a.x);
+                        v[i][2 * j + 1] = __uint_as_float(a.z);
+                    }
+                }
+                if (ok) break;
+                if ((it & 15u) == 15u && (it >= LB_WAIT_SPINS || globaltimer_ns() - t0 > limit || *reinterpret_cast<volatile uint32_t*>(status) != 0u)) {
+                    atomicCAS(status, 0u, LB_DEV_TIMEOUT_COUNTER);
+                    sh.bad = 1;
+                    break;
+                }
+            }
         }
         if (op.x_mode == LB_X_F32_RMSNORM) {
             // h = (x * (1 + w)) * rsqrt(mean x^2 + eps): the rows held by the block's threads are the whole vector.  The
@@ -402,12 +455,13 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             break;
         }
     if (ar_tp) ar_gen0 = ar_tp->gen[0];
+    const uint32_t tag_base = *reinterpret_cast<volatile uint32_t*>(p.sync + 2); // every CTA reads it before the last one out advances it
     for (int o = 0; o < p.n_ops; ++o) {
         const lb_chain_op& op = p.op[o];
         const int n0 = sh.op_n0[o], no = sh.op_no[o];
         unsigned long long* const tl = p.timeline ? p.timeline + ((size_t)c * LB_CHAIN_MAX_OPS + o) * 8 : nullptr;
         if (tl && tid == 0) tl[0] = globaltimer_ns();
-        if (o > 0) {
+        if (o > 0 && !(op.type == LB_CHAIN_OP_GEMV && op.x_src)) { // (a GEMV fed through a mailbox waits on the words themselves)
             // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
             CH_SYNC();
             if (tid == 0) {
@@ -500,9 +554,16 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
 
         // ---- the activation vector as exact integers: three signed base-256 digit planes ----
         for (int i = tid; i < ((no + 1) / 2) * CH_W * 16; i += LB_CHAIN_THREADS) red[i] = 0.f;
-        const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xdig, xsumf, tid, c == 0)
-                                                             : ch_prologue<5>(op, sh, xdig, xsumf, tid, c == 0);
+        const unsigned long long* in_mail = op.x_src ? p.mail + (size_t)(op.x_src - 1) * LB_CHAIN_MAIL_WORDS : nullptr;
+        const uint32_t in_tag = tag_base + (uint32_t)op.x_src;
+        const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xdig, xsumf, tid, c == 0, in_mail, in_tag, p.status)
+                                                             : ch_prologue<5>(op, sh, xdig, xsumf, tid, c == 0, in_mail, in_tag, p.status);
 
+        // the residual value this thread will add its column's result to: asked for now, so that the epilogue does not wait for it
+        // (nobody else writes the column; this thread's own earlier store is what L2 holds)
+        float y_old = 0.f;
+        if ((op.y_mode == LB_Y_F32_ACCUM || op.y_mode == LB_Y_TP_ALLREDUCE) && tid < no * 8)
+            y_old = __ldcg(reinterpret_cast<const float*>(op.y) + n0 * 8 + tid);
         if (tl && tid == 0) tl[2] = globaltimer_ns();
         // ---- this warp's stages of GEMV o.  Column sums stay in registers while consecutive stages belong to
         //      the same pair, and go to this warp's own row of `red` when the pair changes. ----
@@ -549,6 +610,8 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
 
         // ---- column sums over the warps, in warp order; epilogue ----
         const int ncol = no * 8;
+        unsigned long long* const out_mail = p.mail + (size_t)o * LB_CHAIN_MAIL_WORDS;
+        const uint32_t out_tag = tag_base + (uint32_t)o + 1u;
         if (tid < ncol) {
             const int oct = tid >> 3, g = tid & 7;
             const float* col = red + (size_t)(oct >> 1) * CH_W * 16 + (oct & 1) * 8 + g;
@@ -590,22 +653,32 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                     }
                     sum += __uint_as_float((unsigned)w); // rank order
                 }
-                if (ok) reinterpret_cast<float*>(op.y)[n] = __ldcg(reinterpret_cast<float*>(op.y) + n) + sum;
-                else { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
+                if (ok) {
+                    const float nx = y_old + sum;
+                    reinterpret_cast<float*>(op.y)[n] = nx;
+                    if (op.mail) st_volatile_u64(out_mail + n, ((unsigned long long)out_tag << 32) | __float_as_uint(nx));
+                } else { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
             } else {
                 const int n = n0 * 8 + tid;
                 if (op.y_mode == LB_Y_F16) reinterpret_cast<__half*>(op.y)[n] = __float2half_rn(v);
-                else if (op.y_mode == LB_Y_F32) reinterpret_cast<float*>(op.y)[n] = v;
-                else reinterpret_cast<float*>(op.y)[n] = __ldcg(reinterpret_cast<float*>(op.y) + n) + v;
+                else {
+                    const float nx = op.y_mode == LB_Y_F32 ? v : y_old + v;
+                    reinterpret_cast<float*>(op.y)[n] = nx;
+                    if (op.mail) st_volatile_u64(out_mail + n, ((unsigned long long)out_tag << 32) | __float_as_uint(nx));
+                }
             }
         }
         if (op.y_mode == LB_Y_SWIGLU_F16) {
             // the strip is made of (gate octet, up octet) pairs; pair P of the matrix gives y[8P .. 8P+7]
             CH_SYNC();
-            if (tid < ncol / 2) {
-                const int pr = tid >> 3, g = tid & 7;
-                const float gate = sh.vals[pr * 16 + g], up = sh.vals[pr * 16 + 8 + g];
-                reinterpret_cast<__half*>(op.y)[(n0 / 2) * 8 + tid] = __float2half_rn(siluf_dev(gate) * up);
+            if (tid < ncol / 4) { // two neighbouring results per thread: one 4-byte store, one mailbox word
+                const int i0 = 2 * tid, pr = i0 >> 3, g = i0 & 7;
+                const float a = siluf_dev(sh.vals[pr * 16 + g]) * sh.vals[pr * 16 + 8 + g];
+                const float b = siluf_dev(sh.vals[pr * 16 + g + 1]) * sh.vals[pr * 16 + 8 + g + 1];
+                const __half2 h = __floats2half2_rn(a, b);
+                const int at = (n0 / 2) * 8 + i0;
+                *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(op.y) + at) = h;
+                if (op.mail) st_volatile_u64(out_mail + (at >> 1), ((unsigned long long)out_tag << 32) | *reinterpret_cast<const uint32_t*>(&h));
             }
         }
         if (op.y_mode == LB_Y_TP_ALLREDUCE) ++ar_done; // one more exchange of this launch (uniform)
@@ -622,6 +695,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         if (old == (unsigned)G - 1u) {
             p.sync[0] = 0u;
             p.sync[1] = 0u;
+            p.sync[2] = tag_base + LB_CHAIN_MAX_OPS;
             if (ar_tp) const_cast<lb_tp_params*>(ar_tp)->gen[0] = ar_gen0 + (unsigned)ar_done; // every CTA has read the old value
         }
     }

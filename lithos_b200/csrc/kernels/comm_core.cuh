@@ -23,6 +23,13 @@ __device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned lon
     return v;
 }
 
+// two neighbouring 8-byte words in one 16-byte load (each word was stored whole, so each is seen whole)
+__device__ __forceinline__ uint4 ld_volatile_v4(const unsigned long long* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 // returns false when a peer did not show up in time
 __device__ __forceinline__ bool tp_rendezvous(const lb_tp_params& p, unsigned g, bool* s_ok) {
     const int t = threadIdx.x;

@@ -83,6 +83,7 @@ typedef struct {
 #define LB_CHAIN_GC 4                /* K-groups per stage */
 #define LB_CHAIN_STAGE_BYTES (LB_CHAIN_GC * 2 * LB_CHAIN_RECORD)
 #define LB_CHAIN_MAX_OCTETS 32       /* octets one CTA may own */
+#define LB_CHAIN_MAIL_WORDS 17408    /* 8-byte words of one entry's mailbox: fp32 results one per word, fp16 results two per word */
 
 typedef struct {
     const unsigned char* packed; /* strip-packed weights (gemv_pack_strips) */
@@ -99,12 +100,16 @@ typedef struct {
     float eps;
     int32_t type;     /* LB_CHAIN_OP_* */
     const void* ext;  /* parameters of a non-GEMV entry, in device memory */
+    int32_t x_src;    /* set by the launcher: index + 1 of the entry of this launch whose tagged results are this GEMV's x
+                         (then x is read from that entry's mailbox and NO grid barrier precedes this entry); 0 = read p.x */
+    int32_t mail;     /* set by the launcher: this GEMV also publishes its results as (value, tag) words in its mailbox */
 } lb_chain_op;
 
 typedef struct {
     lb_chain_op op[LB_CHAIN_MAX_OPS];
     uint32_t* status;
-    uint32_t* sync;       /* [0] grid-barrier arrivals, [1] CTAs that left; both zero between launches */
+    uint32_t* sync;       /* [0] grid-barrier arrivals, [1] CTAs that left; both zero between launches; [2] tag base, advanced
+                             by LB_CHAIN_MAX_OPS per launch */
     int32_t n_ops;
     int32_t slots;        /* ring slots per warp */
     int32_t table_rows;   /* packed rows (K/8) the activation table holds: the largest K of the chain */
@@ -112,6 +117,7 @@ typedef struct {
     int32_t trigger_op;   /* griddepcontrol.launch_dependents is issued when this GEMV starts */
     int32_t tab_len;      /* entries of a warp's stage list: ceil(stages of the busiest CTA / warps) */
     int32_t pad_[2];
+    unsigned long long* mail; /* mailboxes: LB_CHAIN_MAX_OPS regions of LB_CHAIN_MAIL_WORDS 8-byte words (see chain.cu) */
     unsigned long long* timeline; /* optional [gridDim.x][LB_CHAIN_MAX_OPS][8] %globaltimer stamps of thread 0: [0] reached the grid
                                      barrier, [1] left it, [2] activation table ready (or mixer / exchange started), [3] every stage of
                                      the strip consumed, [4] entry finished (epilogue and, under tensor parallelism, the exchange) */

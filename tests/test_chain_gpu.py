@@ -97,9 +97,13 @@ def test_layer_chain_vs_separate_launches_and_oracle(ctx, lb, oracle):
     one = _run_layer(ctx, lb, dev, host, chained=False)
     ch = _run_layer(ctx, lb, dev, host, chained=True)
     ch2 = _run_layer(ctx, lb, dev, host, chained=True)
+    ctx.set_chain_mailbox(False)                             # a grid barrier between every pair of entries instead of the tagged hand-over
+    ch3 = _run_layer(ctx, lb, dev, host, chained=True)
+    ctx.set_chain_mailbox(True)
     for k in one:
         assert rel_err_max(ch[k], one[k]) <= 2e-3, k        # different K partitions: same values to rounding
         assert np.array_equal(ch[k], ch2[k]), k              # run to run: bit-identical
+        assert np.array_equal(ch[k], ch3[k]), k              # the hand-over carries the same values as the buffers
     # the same four steps on the CPU
     hn = np.concatenate([oracle.rmsnorm(host["mix"][i:i + 128], host["hw"], one_plus_w=False)[0] for i in range(0, V, 128)])
     hn = hn * (host["z"] / (1 + np.exp(-host["z"])))
@@ -171,26 +175,26 @@ def test_chain_rejects_what_it_cannot_run(ctx, lb):
 
 
 def test_timeline_hook(ctx, lb):
-    """lb_set_chain_timeline: per SM and entry four device time stamps, in order, and nothing written once it is off"""
+    """lb_set_chain_timeline: per SM and entry five device time stamps, in order, and nothing written once it is off"""
     K, N = 1024, 8192
     qw, sc, qz, x = gptq_case(K, N, seed=70)
     d = _dev(ctx, qw, sc, qz, K, N)
     d_x, d_y = ctx.to_device(x), ctx.alloc(N * 4)
     n_sm = ctx.sm_count
-    tl = ctx.alloc(n_sm * 32 * 4 * 8).zero()
+    tl = ctx.alloc(n_sm * 32 * 8 * 8).zero()
     lb.lib().lb_set_chain_timeline(ctx.h, tl.ptr)
-    ctx.gemv_chain([_op(d, d_x, d_y, K, N, lb.X_F16, lb.Y_F32)] * 2)
+    ctx.gemv_chain([_op(d, d_x, d_y, K, N, lb.X_F16, lb.Y_F32)] * 2)   # the second entry does not read the first one's result: a grid barrier separates them
     ctx.sync()
     lb.lib().lb_set_chain_timeline(ctx.h, 0)
-    t = tl.download(np.uint64, n_sm * 32 * 4).reshape(n_sm, 32, 4).astype(np.int64)
+    t = tl.download(np.uint64, n_sm * 32 * 8).reshape(n_sm, 32, 8).astype(np.int64)[:, :, :5]
     assert (t[:, :2, :] > 0).all() and (t[:, 2:, :] == 0).all()
     assert (np.diff(t[:, 0, :], axis=1) >= 0).all() and (np.diff(t[:, 1, :], axis=1) >= 0).all()
-    assert (t[:, 1, 0] >= t[:, 0, 3]).all()                 # entry 1 starts after entry 0 ended on the same SM
-    assert t[:, 1, 1].min() >= t[:, 0, 3].max()             # nobody leaves the grid barrier before everybody finished entry 0
+    assert (t[:, 1, 0] >= t[:, 0, 4]).all()                 # entry 1 starts after entry 0 ended on the same SM
+    assert t[:, 1, 1].min() >= t[:, 0, 3].max()             # nobody leaves the grid barrier before everybody has consumed entry 0's weights
     tl.zero()
     ctx.gemv_chain([_op(d, d_x, d_y, K, N, lb.X_F16, lb.Y_F32)])
     ctx.sync()
-    assert not tl.download(np.uint64, n_sm * 32 * 4).any()
+    assert not tl.download(np.uint64, n_sm * 32 * 8).any()
     for b in d + [d_x, d_y, tl]:
         if b:
             b.free()
