@@ -429,6 +429,40 @@ def bench_small_configs(ctx, lb):
                                                "frac_of_measured_peak": round(algo / us / 1e3 / peak, 3)}
         for b in packed:
             b.free()
+    # the kernel to beat: the reference's own GEMV (minds/gptq_gemv_safe.ptx assembled unmodified for sm_100a) on the same matrices in
+    # its native mode (fp32 x and y, zero-point 8, result added to y), launched as src/launcher.s:1479-1535 launches it.  A baseline leg:
+    # it is timed beside the product, never inside its timed region.
+    ref_cubin = ROOT / "oracle" / "_ref" / "gptq_gemv_safe.cubin"
+    if ref_cubin.exists():
+        import ctypes as C
+        L = lb.lib()
+        L.lb_module_load.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int)]
+        L.lb_module_get_kernel.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.POINTER(C.c_uint64)]
+        L.lb_launch_kernel.argtypes = [C.c_void_p, C.c_uint64] + [C.c_uint] * 7 + [C.POINTER(C.c_void_p)]
+        mod, fn = C.c_int(), C.c_uint64()
+        ctx._check(L.lb_module_load(ctx.h, str(ref_cubin).encode(), C.byref(mod)))
+        ctx._check(L.lb_module_get_kernel(ctx.h, mod, b"gptq_gemv_safe", C.byref(fn)))
+        d_x32, d_y32 = ctx.to_device(lb.fill_normal(K, 100, 4)), ctx.alloc(N * 4).zero()
+
+        def ref_launch(w):
+            vals = [C.c_uint64(w[0].ptr), C.c_uint64(w[1].ptr), C.c_uint64(d_x32.ptr), C.c_uint64(d_y32.ptr), C.c_uint32(N), C.c_uint32(K),
+                    C.c_uint32(1), C.c_uint32(K // 8)]
+            params = (C.c_void_p * len(vals))(*[C.cast(C.pointer(v), C.c_void_p) for v in vals])
+            ctx._check(L.lb_launch_kernel(ctx.h, fn, (N + 255) // 256, 1, 1, 64, 1, 1, 4 * K, params))
+
+        for j in range(SETS):
+            ref_launch(dev[j])
+        ctx.sync()
+        ctx.timer_start()
+        for j in range(3 * SETS):
+            ref_launch(dev[j % SETS])
+        us_ref = ctx.timer_stop() * 1e3 / (3 * SETS)
+        out["gemv_config0"]["reference_kernel"] = {"kernel": "gptq_gemv_safe (the reference's PTX, assembled for sm_100a; fp32 x/y, zero-point 8)",
+                                                   "us_per_launch": round(us_ref, 2), "GBps": round(algo / us_ref / 1e3, 1),
+                                                   "frac_of_measured_peak": round(algo / us_ref / 1e3 / peak, 3),
+                                                   "ours_speedup": round(us_ref / out["gemv_config0"]["us_per_launch"], 1)}
+        d_x32.free()
+        d_y32.free()
     for w in dev:
         for b in w:
             b.free()

@@ -254,6 +254,13 @@ int lb_rmsnorm(lb_ctx* ctx, uint64_t x, uint64_t res, uint64_t w_bf16, uint64_t 
                float eps, int one_plus_w);
 int lb_argmax(lb_ctx* ctx, uint64_t x_f32, int n, uint64_t out_idx_i32);
 int lb_embed(lb_ctx* ctx, uint64_t table_bf16, uint64_t token_i32, uint64_t out_f32, int D);
+/* Temperature + top-k sampling: what the reference's `sample` kernel is specified to do (kernels/README.md:104-117: "top-k
+ * sampling ... with temperature scaling"; its shipped code only takes the arg-max, which compat/sample.cubin reproduces).
+ * Among the top_k (1..64) largest logits -- ties by smaller index -- p_i = softmax(l_i / temperature); the token is the
+ * first whose cumulative probability exceeds u, where u is element `counter` of stream 7777 of the seeded generator
+ * (lb_fill_uniform_f32(.., seed, 7777, 0, 1)).  probs_out (fp32 [top_k]) and idx_out (i32 [top_k]) may be 0. */
+int lb_sample_topk(lb_ctx* ctx, uint64_t logits_f32, int n, float temperature, int top_k, uint64_t seed, uint64_t counter,
+                   uint64_t out_idx_i32, uint64_t probs_out, uint64_t idx_out);
 
 /* ---- tensor-parallel exchange buffers (no counterpart in the reference: it is single-GPU) ---
  * One process per GPU.  Each rank creates its buffer, the launcher passes the 64-byte IPC
@@ -374,6 +381,13 @@ int lb_model_read_next(lb_model* m, int* next_out);   /* synchronises */
  * on chip for the chunk, attention runs the decode kernel once per token.  Single GPU (tp_size 1) only. */
 int lb_model_prefill(lb_model* m, const int* tokens, int n, int pos0, int* next_out);
 int lb_model_step_kernels(const lb_model* m);         /* kernels per decode step */
+/* top_k == 0 (default): greedy; else every step samples among the top_k largest logits at `temperature`, the draw being a
+ * function of (seed, position).  Takes effect at the next lb_model_decode / lb_model_capture.  Single GPU only. */
+int lb_model_set_sampling(lb_model* m, float temperature, int top_k, uint64_t seed);
+/* The launcher's decode loop (src/launcher.s:552-652, :931-1087): run the prompt (lb_model_prefill), then decode until
+ * `eos` (248044 for the reference model; negative = none), max_new tokens or a full context.  out [max_new] receives
+ * the generated tokens, *n_out their number. */
+int lb_model_generate(lb_model* m, const int* prompt, int n_prompt, int max_new, int eos, int* out, int* n_out);
 
 #ifdef __cplusplus
 }

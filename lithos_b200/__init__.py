@@ -120,6 +120,7 @@ def lib() -> C.CDLL:
     sig("lb_rmsnorm", i32, vp, u64, u64, u64, u64, u64, i32, i32, f32, i32)
     sig("lb_argmax", i32, vp, u64, i32, u64)
     sig("lb_embed", i32, vp, u64, u64, u64, i32)
+    sig("lb_sample_topk", i32, vp, u64, i32, f32, i32, u64, u64, u64, u64, u64)
     _lib = L
     return L
 
@@ -392,6 +393,10 @@ class Context:
 
     def argmax(self, x, n, out_idx):
         self._check(lib().lb_argmax(self.h, x.ptr, n, out_idx.ptr))
+
+    def sample_topk(self, x, n, temperature, top_k, seed, counter, out_idx, probs_out=None, idx_out=None):
+        self._check(lib().lb_sample_topk(self.h, x.ptr, n, temperature, top_k, seed, counter, out_idx.ptr,
+                                         probs_out.ptr if probs_out else 0, idx_out.ptr if idx_out else 0))
 
     def embed(self, table, token, out, D):
         self._check(lib().lb_embed(self.h, table.ptr, token.ptr, out.ptr, D))

@@ -102,6 +102,7 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
     X(attn_decode_mma)                \
     X(embed_bf16)                     \
     X(argmax_f32)                     \
+    X(topk_sample_f32)                \
     X(rmsnorm_f32)                    \
     X(tp_allreduce_add)               \
     X(tp_argmax_exchange)             \

@@ -577,6 +577,32 @@ int lb_model_launch_attention(lb_model* m, const layer_t* L, CUdeviceptr proj_ro
     return lb_launch(c, LBK_attn_decode_mma, (unsigned)m->HKV, (unsigned)p.splits, 1, 256, lb_attn_mma_smem(m->HQ / m->HKV), params, 1);
 }
 
+/* the kernel that turns the LM head's output into the next token (and advances the position on the device) */
+int lb_model_launch_sampler(lb_model* m) {
+    lb_ctx* c = m->c;
+    const int H = m->cfg.hidden;
+    if (m->tp_size == 1 && m->top_k > 0) { /* temperature / top-k sampling over the full logits; the draw is a function of (seed, position) */
+        uint64_t zero = 0;
+        int n = m->vocab_s;
+        void* params[] = {&m->logits, &n, &m->d_next, &m->d_token, &m->d_pos, &m->temperature, &m->top_k, &m->sample_seed, &zero, &zero, &zero};
+        LB_TRY(lb_launch(c, LBK_topk_sample_f32, 1, 1, 1, 1024, 0, params, 1));
+    } else if (m->tp_size == 1) {
+        int n = lb_dense_ctas(c, m->vocab_s, H); /* one (value, row) candidate per LM-head CTA */
+        void* params[] = {&m->cand_val, &n, &m->d_next, &m->d_token, &m->d_pos, &m->cand_idx};
+        LB_TRY(lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1));
+    } else {
+        lb_tp_argmax_params q;
+        memset(&q, 0, sizeof q);
+        LB_TRY(lb_comm_fill(m->comm, &q.tp, 2, 2));
+        q.cand_val = (const float*)m->cand_val; q.cand_idx = (const int32_t*)m->cand_idx;
+        q.n_cand = lb_dense_ctas(c, m->vocab_s, H); q.vocab_offset = m->tp_rank * m->vocab_s;
+        q.out_idx = (int32_t*)m->d_next; q.next_token = (int32_t*)m->d_token; q.pos = (int32_t*)m->d_pos;
+        void* params[] = {&q};
+        LB_TRY(lb_launch(c, LBK_tp_argmax_exchange, 1, 1, 1, 1024, 0, params, 1));
+    }
+    return LB_OK;
+}
+
 static int issue_step(lb_model* m) {
     lb_ctx* c = m->c;
     const lb_model_cfg* cfg = &m->cfg;
@@ -621,21 +647,20 @@ static int issue_step(lb_model* m) {
     LB_TRY(flush_chain(m));
     LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, m->vocab_s, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps,
                            m->cand_val, m->cand_idx));
-    if (m->tp_size == 1) {
-        int n = lb_dense_ctas(c, m->vocab_s, H); /* one (value, row) candidate per LM-head CTA */
-        void* params[] = {&m->cand_val, &n, &m->d_next, &m->d_token, &m->d_pos, &m->cand_idx};
-        LB_TRY(lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1));
-    } else {
-        lb_tp_argmax_params q;
-        memset(&q, 0, sizeof q);
-        LB_TRY(lb_comm_fill(m->comm, &q.tp, 2, 2));
-        q.cand_val = (const float*)m->cand_val; q.cand_idx = (const int32_t*)m->cand_idx;
-        q.n_cand = lb_dense_ctas(c, m->vocab_s, H); q.vocab_offset = m->tp_rank * m->vocab_s;
-        q.out_idx = (int32_t*)m->d_next; q.next_token = (int32_t*)m->d_token; q.pos = (int32_t*)m->d_pos;
-        void* params[] = {&q};
-        LB_TRY(lb_launch(c, LBK_tp_argmax_exchange, 1, 1, 1, 1024, 0, params, 1));
-    }
+    LB_TRY(lb_model_launch_sampler(m));
     m->step_kernels = (int)(c->launches - launches0);
+    return LB_OK;
+}
+
+/* top_k == 0 (default): greedy.  Otherwise the step samples among the top_k largest logits at this temperature; the
+ * uniform draw of a step is element (position) of a stream of the seeded generator, so a run can be repeated.  Takes
+ * effect at the next lb_model_decode / lb_model_capture.  Single GPU only. */
+LB_API int lb_model_set_sampling(lb_model* m, float temperature, int top_k, uint64_t seed) {
+    if (!m) return LB_ERR_INVALID;
+    if (top_k < 0 || top_k > 64 || (top_k > 0 && !(temperature > 0.f))) return lb_fail(m->c, LB_ERR_INVALID, "model: sampling needs 0 <= top_k <= 64 and temperature > 0");
+    if (top_k > 0 && m->tp_size != 1) return lb_fail(m->c, LB_ERR_STATE, "model: sampling other than greedy is single-GPU only");
+    m->temperature = temperature; m->top_k = top_k; m->sample_seed = seed;
+    if (m->graph) { lb_graph_destroy(m->c, m->graph); m->graph = NULL; } /* a captured step samples the old way */
     return LB_OK;
 }
 
@@ -716,6 +741,26 @@ LB_API int lb_model_replay(lb_model* m, int n_steps) {
     for (int i = 0; i < n_steps; i++) {
         LB_TRY(lb_graph_launch(m->c, m->graph));
         m->host_pos++;
+    }
+    return LB_OK;
+}
+
+/* The launcher's decode loop (src/launcher.s:552-652 generation loop, :931-1087 sample and print): run the prompt, then
+ * decode until `eos` (248044 for the reference model, models/families/qwen/qwen3.5/27b/config.json:12; negative = none) or
+ * max_new tokens.  out receives the generated tokens (the end-of-sequence token included when it was produced). */
+LB_API int lb_model_generate(lb_model* m, const int* prompt, int n_prompt, int max_new, int eos, int* out, int* n_out) {
+    if (!m || !prompt || n_prompt < 1 || max_new < 0 || !out || !n_out) return LB_ERR_INVALID;
+    *n_out = 0;
+    if (max_new == 0) return LB_OK;
+    int tok = 0;
+    LB_TRY(lb_model_prefill(m, prompt, n_prompt, 0, &tok));
+    out[(*n_out)++] = tok;
+    if (!m->graph) LB_TRY(lb_model_capture(m));
+    while (*n_out < max_new && tok != eos) {
+        if (m->host_pos >= m->cfg.max_ctx) break; /* the context is full */
+        LB_TRY(lb_model_replay(m, 1)); /* token and position are already on the device */
+        LB_TRY(lb_model_read_next(m, &tok));
+        out[(*n_out)++] = tok;
     }
     return LB_OK;
 }

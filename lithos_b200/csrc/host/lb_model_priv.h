@@ -55,6 +55,7 @@ struct lb_model {
     CUdeviceptr tp_params[2]; /* tensor parallel: lb_tp_params of the two exchange slots in device memory, for the chain */
     lb_chain_op pend[LB_CHAIN_MAX_OPS]; /* GEMVs and DeltaNet mixers collected since the last stand-alone kernel */
     int n_pend;
+    float temperature; int top_k; uint64_t sample_seed; /* top_k == 0: greedy (arg-max); else temperature / top-k sampling */
     struct lb_prefill_ws* ws; /* prompt-pass buffers (lb_prefill.c), NULL until the first prefill */
 };
 
@@ -63,6 +64,7 @@ struct lb_model {
 typedef struct lb_prefill_ws lb_prefill_ws;
 
 int lb_model_is_fa(const lb_model_cfg* c, int l);
+int lb_model_launch_sampler(lb_model* m);
 /* the decode-attention launch of one attention layer: inputs are the fused projection's fp32 row (per head 256 query then
  * 256 gate columns, then the key and value heads); pos_ptr != 0 reads the position from device memory (graph replay) */
 int lb_model_launch_attention(lb_model* m, const layer_t* L, CUdeviceptr proj_row, CUdeviceptr out, CUdeviceptr pos_ptr, int pos, int splits_for);

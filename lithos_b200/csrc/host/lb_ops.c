@@ -371,6 +371,14 @@ LB_API int lb_argmax(lb_ctx* c, uint64_t x, int n, uint64_t out_idx) {
     return lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1);
 }
 
+LB_API int lb_sample_topk(lb_ctx* c, uint64_t x, int n, float temperature, int top_k, uint64_t seed, uint64_t counter, uint64_t out_idx,
+                          uint64_t probs_out, uint64_t idx_out) {
+    if (!c || !x || !out_idx || n <= 0 || top_k < 1 || top_k > 64) return lb_fail(c, LB_ERR_INVALID, "lb_sample_topk: bad argument (1 <= top_k <= 64)");
+    uint64_t zero = 0;
+    void* params[] = {&x, &n, &out_idx, &zero, &zero, &temperature, &top_k, &seed, &counter, &probs_out, &idx_out};
+    return lb_launch(c, LBK_topk_sample_f32, 1, 1, 1, 1024, 0, params, 1);
+}
+
 LB_API int lb_embed(lb_ctx* c, uint64_t table, uint64_t token, uint64_t out, int D) {
     if (!c || !table || !token || !out || D <= 0) return lb_fail(c, LB_ERR_INVALID, "lb_embed: bad argument");
     void* params[] = {&table, &token, &out, &D};

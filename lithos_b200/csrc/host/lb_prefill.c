@@ -154,11 +154,7 @@ LB_API int lb_model_prefill(lb_model* m, const int* tokens, int n, int pos0, int
     }
     LB_CU(c, lb_drv.MemsetD32Async(m->d_pos, (unsigned)(pos0 + n - 1), 1, c->stream)); /* the sampling kernel advances it */
     LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, m->vocab_s, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps, m->cand_val, m->cand_idx));
-    {
-        int nc = lb_dense_ctas(c, m->vocab_s, H);
-        void* params[] = {&m->cand_val, &nc, &m->d_next, &m->d_token, &m->d_pos, &m->cand_idx};
-        LB_TRY(lb_launch(c, LBK_argmax_f32, 1, 1, 1, 1024, 0, params, 1));
-    }
+    LB_TRY(lb_model_launch_sampler(m));
     m->host_pos = pos0 + n;
     return next_out ? lb_model_read_next(m, next_out) : LB_OK;
 }

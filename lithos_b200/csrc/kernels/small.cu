@@ -64,6 +64,95 @@ extern "C" __global__ void __launch_bounds__(1024) argmax_f32(const float* __res
     }
 }
 
+// Temperature + top-k sampling (the reference's `sample` kernel is described as "top-k sampling via parallel argmax
+// reduction with temperature scaling", kernels/README.md:104-117; its shipped code only scales and takes the arg-max).
+// One CTA.  The k largest logits are found by k block-wide arg-max passes in the order (larger value, then smaller
+// index), each pass looking only at what comes after the previous winner in that order, so ties are resolved the same
+// way every time; then p_i = exp((l_i - l_0) / T) / sum over the k, and the token is the first i whose cumulative
+// probability exceeds u.  u comes from the same counter-based generator as the synthetic tensors: element `counter`
+// (the decode position when pos != 0) of stream 7777 of `seed`, so a run can be repeated.  top_k is clamped to
+// [1, 64]; temperature <= 0 means greedy.  Also writes next_token / advances *pos like argmax_f32.
+__device__ __forceinline__ unsigned long long sm_mix64(unsigned long long z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+extern "C" __global__ void __launch_bounds__(1024) topk_sample_f32(const float* __restrict__ x, int n, int* __restrict__ out_idx,
+                                                                   int* __restrict__ next_token, int* __restrict__ pos, float temperature,
+                                                                   int top_k, unsigned long long seed, unsigned long long counter,
+                                                                   float* __restrict__ probs_out, int* __restrict__ idx_out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    __shared__ float top_v[64];
+    __shared__ int top_i[64];
+    pdl_wait();
+    const int k = temperature > 0.f ? min(max(top_k, 1), 64) : 1;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    auto better = [](float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); };
+    float last_v = INFINITY;
+    int last_i = -1;
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = x[i];
+            const bool after = v < last_v || (v == last_v && i > last_i); // not taken yet
+            if (after && better(v, i, bv, bi)) { bv = v; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { sv[w] = bv; si[w] = bi; }
+        __syncthreads();
+        if (w == 0) {
+            bv = lane < nw ? sv[lane] : -INFINITY;
+            bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            }
+            if (lane == 0) { top_v[r] = bv; top_i[r] = bi; }
+        }
+        __syncthreads();
+        last_v = top_v[r];
+        last_i = top_i[r];
+    }
+    if (threadIdx.x == 0) {
+        int kk = k;
+        while (kk > 1 && top_i[kk - 1] == 0x7fffffff) --kk; // fewer than k finite candidates
+        int pick = 0;
+        if (kk > 1) {
+            const float inv_t = 1.0f / temperature;
+            float p[64], sum = 0.f;
+            for (int i = 0; i < kk; ++i) { p[i] = expf((top_v[i] - top_v[0]) * inv_t); sum += p[i]; }
+            const unsigned long long c = pos ? (unsigned long long)pos[0] : counter;
+            const unsigned long long h = sm_mix64(seed + 0x9E3779B97F4A7C15ull * (sm_mix64(7777ull ^ 0xD1342543DE82EF95ull) | 1ull));
+            const unsigned bits = (unsigned)(sm_mix64(h + 0x9E3779B97F4A7C15ull * (c + 1)) >> 32);
+            const float u = ((float)(bits >> 8) + 0.5f) * (1.0f / 16777216.0f);
+            float acc = 0.f;
+            bool found = false;
+            pick = kk - 1; // rounding may leave the total a hair below u: the last candidate takes the rest
+            for (int i = 0; i < kk; ++i) {
+                const float pi = p[i] / sum;
+                if (probs_out) probs_out[i] = pi;
+                acc += pi;
+                if (!found && u < acc) { pick = i; found = true; }
+            }
+        } else if (probs_out) probs_out[0] = 1.0f;
+        if (idx_out) for (int i = 0; i < kk; ++i) idx_out[i] = top_i[i];
+        int tok = top_i[pick];
+        if (tok == 0x7fffffff) tok = 0;
+        out_idx[0] = tok;
+        if (next_token) next_token[0] = tok;
+        if (pos) pos[0] += 1;
+    }
+}
+
 // y = (x [+ r]) * w' * rsqrt(mean((x+r)^2) + eps), w' = 1+w or w (bf16 weight);
 // inference/reduce.ls:21-147.  One CTA per row of D values.  sum_out (may be
 // NULL) receives x+r.

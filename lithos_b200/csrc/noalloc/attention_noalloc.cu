@@ -8,8 +8,13 @@
 // inside this library's device image, so loading the library is the only "allocation" there is
 // (every GPU that loads it holds NOALLOC_SCRATCH_BYTES until the process exits).
 //
-// It is the same kernel as lb_attention_decode (attn_decode_split, included below), launched with
-// at most NOALLOC_MAX_SLICES position slices per KV head.
+// It launches attn_decode_split (included below: CUDA-core dot products, split-KV with a last-arriver merge) with at
+// most NOALLOC_MAX_SLICES position slices per KV head; lb_attention_decode itself uses the tensor-core kernel
+// attn_decode_mma.  Same contract and results to rounding; tests/test_zz_no_alloc.py checks both against the CPU oracle.
+//
+// Threads: the per-device address cache below is filled by the first call on a device without a lock.  Two host
+// threads making that first call at the same moment would both store the same address (harmless), but make the
+// first call from one thread.
 #include <cuda_runtime.h>
 #include <cstdio>
 #include <cstring>

@@ -114,6 +114,8 @@ def _sigs():
     L.lb_model_replay.argtypes = [vp, i32]
     L.lb_model_read_next.argtypes = [vp, P(i32)]
     L.lb_model_prefill.argtypes = [vp, P(i32), i32, i32, P(i32)]
+    L.lb_model_set_sampling.argtypes = [vp, C.c_float, i32, u64]
+    L.lb_model_generate.argtypes = [vp, P(i32), i32, i32, i32, P(i32), P(i32)]
     L.lb_model_step_kernels.argtypes = [vp]
     _sigs_done = True
 
@@ -252,6 +254,17 @@ class Model:
         nxt = C.c_int(0)
         self.ctx._check(lib().lb_model_prefill(self.h, arr, len(tokens), pos0, C.byref(nxt)))
         return nxt.value
+
+    def set_sampling(self, temperature: float, top_k: int, seed: int = 0):
+        """top_k == 0: greedy; else temperature / top-k sampling, repeatable from (seed, position)"""
+        self.ctx._check(lib().lb_model_set_sampling(self.h, temperature, top_k, seed))
+
+    def generate(self, prompt, max_new: int, eos: int = -1):
+        """the decode loop: prompt pass, then tokens until `eos`, max_new or a full context"""
+        arr = (C.c_int * len(prompt))(*[int(t) for t in prompt])
+        out, n = (C.c_int * max(max_new, 1))(), C.c_int(0)
+        self.ctx._check(lib().lb_model_generate(self.h, arr, len(prompt), max_new, eos, out, C.byref(n)))
+        return [out[i] for i in range(n.value)]
 
     def read_next(self) -> int:
         nxt = C.c_int(0)

@@ -486,6 +486,39 @@ ORC_API int orc_argmax(const float* x, int n) {
     return best;
 }
 
+/* Temperature + top-k sampling as kernels/README.md:104-117 specifies the reference's `sample` kernel: the k largest
+ * logits (ties: smaller index first), p = softmax(l / T) over them, first index whose cumulative probability exceeds
+ * u.  Returns the token; idx_out / probs_out (k entries) may be NULL. */
+ORC_API int orc_topk_sample(const float* x, int n, float temperature, int top_k, float u, int* idx_out, float* probs_out) {
+    int idx[64];
+    float val[64];
+    int k = top_k < 1 ? 1 : top_k > 64 ? 64 : top_k, kk = 0;
+    float last_v = INFINITY;
+    int last_i = -1;
+    for (int r = 0; r < k; r++) {
+        float bv = -INFINITY;
+        int bi = -1;
+        for (int i = 0; i < n; i++) {
+            int after = x[i] < last_v || (x[i] == last_v && i > last_i);
+            if (after && (bi < 0 || x[i] > bv)) { bv = x[i]; bi = i; }
+        }
+        if (bi < 0) break;
+        idx[kk] = bi; val[kk] = bv; kk++;
+        last_v = bv; last_i = bi;
+    }
+    float p[64], sum = 0.f, acc = 0.f;
+    for (int i = 0; i < kk; i++) { p[i] = expf((val[i] - val[0]) / temperature); sum += p[i]; }
+    int pick = kk - 1, found = 0;
+    for (int i = 0; i < kk; i++) {
+        float pi = p[i] / sum;
+        if (probs_out) probs_out[i] = pi;
+        if (idx_out) idx_out[i] = idx[i];
+        acc += pi;
+        if (!found && u < acc) { pick = i; found = 1; }
+    }
+    return kk ? idx[pick] : 0;
+}
+
 /* ------------------------------------------------------------------ */
 /* A9. the whole decode step                                           */
 /* ------------------------------------------------------------------ */

@@ -309,6 +309,16 @@ def argmax(x) -> int:
     return lib().orc_argmax(_p(x), x.size)
 
 
+def topk_sample(x, temperature: float, top_k: int, u: float):
+    """returns (token, top-k indices, their probabilities)"""
+    x = _f32(x)
+    idx, probs = np.zeros(64, np.int32), np.zeros(64, np.float32)
+    lib().orc_topk_sample.restype = C.c_int
+    tok = lib().orc_topk_sample(_p(x), x.size, C.c_float(temperature), int(top_k), C.c_float(u), _p(idx), _p(probs))
+    k = max(1, min(64, int(top_k)))
+    return tok, idx[:k], probs[:k]
+
+
 # ---- whole model ------------------------------------------------------------------
 class ModelCfg(C.Structure):
     _fields_ = [(n, C.c_int) for n in (

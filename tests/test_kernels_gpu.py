@@ -203,3 +203,51 @@ def test_small_kernels(ctx, lb, oracle):
     ctx.dense_bf16_gemv(d_W, d_xv, d_o, N, D)
     want = oracle.dense_bf16_gemv(W, xv.astype(np.float32), N, D)
     assert rel_err_max(d_o.download(np.float32, N), want) <= 1e-5
+
+
+def test_topk_sampling_vs_oracle(ctx, lb, oracle):
+    """temperature + top-k sampling: the same candidates (ties by smaller index), probabilities within 1e-5, and the same
+    token for every draw u that does not sit within 1e-5 of a step of the cumulative distribution"""
+    n = 248320
+    lg = lb.fill_normal(n, 91, 1, std=3.0)
+    lg[[777, 200000]] = lg.max() + 0.5                         # a tie at the top: index 777 first
+    d_l, d_tok = ctx.to_device(lg), ctx.alloc(16)
+    d_p, d_i = ctx.alloc(64 * 4), ctx.alloc(64 * 4)
+    seed = 20260413
+    for k, T in ((1, 1.0), (8, 0.7), (50, 1.3), (64, 2.0)):
+        for counter in range(6):
+            u = float(lb.fill_uniform(counter + 1, seed, 7777, 0.0, 1.0)[counter])
+            ctx.sample_topk(d_l, n, T, k, seed, counter, d_tok, d_p, d_i)
+            tok = int(d_tok.download(np.int32, 1)[0])
+            want, idx, probs = oracle.topk_sample(lg, T, k, u)
+            assert np.array_equal(d_i.download(np.int32, 64)[:k], idx)
+            gp = d_p.download(np.float32, 64)[:k]
+            assert np.allclose(gp, probs, rtol=0, atol=1e-5)
+            cdf = np.cumsum(probs.astype(np.float64))
+            if np.min(np.abs(cdf - u)) > 1e-5:
+                assert tok == want, (k, T, counter, u)
+            assert tok in idx
+        assert idx[0] == 777 and (k == 1 or idx[1] == 200000)
+
+
+def test_generate_stops_at_eos_and_sampling_is_repeatable(ctx, lb):
+    from lithos_b200 import model as M
+    cfg = M.tiny(max_ctx=64)
+    m = M.Model(ctx, cfg)
+    m.fill_synthetic(1234)
+    prompt = [5, 17, 300, 12]
+    greedy = m.generate(prompt, 12)
+    assert len(greedy) == 12
+    m.reset_state()
+    assert m.generate(prompt, 12, eos=greedy[4]) == greedy[:greedy.index(greedy[4]) + 1]   # stops right after the first end-of-sequence token
+    # sampling: repeatable from (seed, position), different from greedy somewhere, different with another seed
+    runs = []
+    for seed in (7, 7, 8):
+        m.reset_state()
+        m.set_sampling(1.5, 40, seed)
+        runs.append(m.generate(prompt, 24))
+    assert runs[0] == runs[1] and runs[0] != runs[2] and runs[0] != greedy + [0] * 12
+    m.set_sampling(1.0, 0, 0)
+    m.reset_state()
+    assert m.generate(prompt, 12) == greedy
+    m.close()
