@@ -59,10 +59,9 @@ static void chain_plan_make(const lb_ctx* c, const lb_chain_op* ops, int n_ops, 
      * still leaves two slots) room for a small CTA of the neighbouring kernel */
     int max_pairs = (max_oct + 1) / 2;
     if (has_dn && max_pairs < 13) max_pairs = 13;
-    const size_t dig_words = (size_t)((6 * max_rows + 2 * (max_rows >> 2) + 3) & ~3);
-    const int tab_len = (int)((max_stages + LB_CHAIN_WARPS - 1) / LB_CHAIN_WARPS) + 1;
-    const size_t fixed = dig_words * 4 + (size_t)((max_rows / LB_GEMV_ROWS + 3) & ~3) * 4 + (size_t)max_pairs * LB_CHAIN_WARPS * 16 * 4 +
-                         (size_t)LB_CHAIN_WARPS * tab_len * 8;
+    const size_t table = (size_t)(max_rows / LB_GEMV_ROWS) * LB_CHAIN_GROUP_BYTES + 64;
+    const int tab_len = (int)((max_stages + LB_CHAIN_WARPS - 1) / LB_CHAIN_WARPS) + n_ops + 1; /* a warp's run of every GEMV is rounded up */
+    const size_t fixed = table + (size_t)max_pairs * LB_CHAIN_WARPS * 16 * 4 + (size_t)LB_CHAIN_WARPS * tab_len * 8;
     const size_t per_slot = (size_t)LB_CHAIN_WARPS * (LB_CHAIN_STAGE_BYTES + 8);
     const size_t limit = (size_t)c->max_smem_optin - (size_t)((c->fn_static_smem[LBK_gemv_chain] + 1023) & ~1023);
     int slots = limit > fixed + (size_t)c->chain_reserve ? (int)((limit - fixed - (size_t)c->chain_reserve) / per_slot) : 0;

@@ -10,17 +10,17 @@
 //     final: no partial sums, counters or atomics between CTAs, and the sum order is fixed.
 //   * The weights come from a strip-packed copy (gemv_pack_strips below; layout in params.h) in
 //     which a CTA's strip is one contiguous byte range, cut into stages of 4 K-groups x 16
-//     columns (4352 bytes).  Stage k of the CTA's list (all GEMVs of the launch, in order) belongs
-//     to warp k % 16: that warp requests it with a plain 1-D bulk copy into one of its own ring
+//     columns (4352 bytes).  Of every GEMV's stage list each of the 16 warps takes a contiguous run: the
+//     warp requests a stage with a plain 1-D bulk copy into one of its own ring
 //     slots, waits for it on the slot's mbarrier, consumes it alone and refills the slot with its
 //     next stage.  No producer warp, no block-wide synchronisation inside a GEMV.  Weights are
 //     constants, so a warp's requests run on into the NEXT GEMV of the chain while the block
 //     finishes the current one: the rings of all SMs keep HBM busy across entry boundaries.
-//   * A stage item is (K-group, pair of octets): two 128-bit loads per lane give the packed words,
-//     four m16n8k32 u8 x s8 tensor-core steps give the exact integer dot products of 16 columns
-//     against the three activation digit planes (gemv_core.cuh); scale and zero-point are applied
-//     in fp32 per group.  Per-column sums are added in a fixed order (stage order inside a warp,
-//     then warp order).
+//   * A stage item is (K-group, pair of octets): two 128-bit loads per lane give the packed words, which go
+//     into the tensor core as they are (a byte = two nibbles) and once more with the low nibbles masked off;
+//     four m16n8k32 u8 x s8 steps against the activation digit planes give the exact integer dot products
+//     of 16 columns (ch_item below); scale and zero-point are applied in fp32 per group.  Per-column sums
+//     are added in a fixed order (stage order inside a warp, then warp order).
 //   * A DeltaNet entry runs the mixer of a layer ((value head, 32-column slab) units, four teams of 128
 //     threads per CTA; deltanet_core.cuh); an all-reduce entry adds every rank's partial vector into the
 //     residual stream over plain peer loads (comm_core.cuh).  The weight rings stay full meanwhile.
@@ -93,54 +93,78 @@ __device__ __forceinline__ void imma_nv(int (&d)[4], uint32_t a0, uint32_t a1, u
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One stage: up to CH_GC items (K-group, pair of octets), 16 columns x 128 k each, as exact integer dot products
-// against the digit planes.  Fragment rows 0-7 are the columns of the first octet, rows 8-15 those of the second.
-// All loads first, then the tensor-core steps of the items interleaved (independent accumulator chains), then the
-// fp32 part: the latencies of one item hide behind the others.  PARTIAL = false: all CH_GC groups are there.
-template <bool PARTIAL>
-__device__ __forceinline__ void ch_stage_items(const unsigned char* stage, int g0, int gcount, bool full_pair, const uint32_t* xdig,
-                                               const float* xsumf, int lane, float lane_mul, float& acc_a, float& acc_b) {
-    const int g = lane >> 2, t = lane & 3;
-    const int recb = full_pair ? 2 * LB_CHAIN_RECORD : LB_CHAIN_RECORD;
-    // digit_row_word(16 G + t + 4 q) = 104 G + 26 q + 6 t
-    const uint32_t* xrow = xdig + 104 * g0 + 6 * t + 2 * g;
-    uint4 wa[CH_GC], wb[CH_GC];
-    uint2 xb[CH_GC][4];
-#pragma unroll
-    for (int j = 0; j < CH_GC; ++j) {
-        const bool on = !PARTIAL || j < gcount;
-        const unsigned char* rec = stage + j * recb;
-        wa[j] = on ? *reinterpret_cast<const uint4*>(rec + lane * 16) : make_uint4(0u, 0u, 0u, 0u);
-        wb[j] = on && full_pair ? *reinterpret_cast<const uint4*>(rec + LB_CHAIN_RECORD + lane * 16) : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-            xb[j][q] = on && g < 3 ? *reinterpret_cast<const uint2*>(xrow + 104 * j + 26 * q) : make_uint2(0u, 0u);
+// ---- the activation table (B operand) ------------------------------------------------------------------------------
+// One block of CH_XG bytes per K-group.  A packed weight word holds 8 consecutive k as nibbles: byte i = (k = 2i in the
+// low nibble, k = 2i + 1 in the high one).  The tensor-core step takes the word AS IT IS (byte = low + 16 high) against
+// the digits of the even k, and the word with the low nibbles masked off (byte = 16 high) against the digits of the odd
+// k and, in the neighbouring output column, of the even k again; low . even = first - third, high . odd = second / 16.
+// So the int4 -> operand conversion is ONE logic instruction per 8 weights, and the block holds
+//   [0, 192)    even-k digits: [plane 0..2][t 0..3][packed row t, t+4, t+8, t+12 of the group] as 4-byte words
+//   [192, 384)  odd-k digits, same order
+//   [384, 400)  float {16 * sum of the group's integers, 0, 0, 0}: what fragment lane t multiplies the zero-point with
+// (CH_XG = 448 keeps both the 16-byte fragment loads and the prologue's 4-byte stores free of bank conflicts).
+#define CH_XG LB_CHAIN_GROUP_BYTES
+#define CH_X_ODD 192
+#define CH_X_SUM 384
+
+// per-lane constants of the stage loop
+struct ch_lane {
+    uint32_t w_off;   // this lane's 16 bytes inside a record
+    uint32_t s_off;   // this lane's (scale, zero-point) inside a record
+    uint32_t x1, x2;  // B-operand loads inside a group block: first (even-k digits of plane g/2), second (odd-k digits for even
+                      // g, even-k digits for odd g); columns 6 and 7 of the product are never read, they repeat plane 2
+    uint32_t xs;      // this lane's word of the group-sum entry
+    float mul;        // 256^t / 16 for t < 3 (fragment lane t holds digit plane t), 0 for t = 3
+};
+__device__ __forceinline__ ch_lane ch_lane_make(int lane) {
+    const int g = lane >> 2, t = lane & 3, pl = min(g >> 1, 2);
+    ch_lane L;
+    L.w_off = (uint32_t)lane * 16u;
+    L.s_off = 512u + 4u * (uint32_t)g;
+    L.x1 = (uint32_t)(pl * 64 + t * 16);
+    L.x2 = (g & 1) ? L.x1 : CH_X_ODD + L.x1;
+    L.xs = CH_X_SUM + 4u * (uint32_t)t;
+    L.mul = t == 0 ? 0.0625f : t == 1 ? 16.0f : t == 2 ? 4096.0f : 0.0f;
+    return L;
+}
+
+// One item: K-group (record `rec`, table block `xg`) x pair of octets = 16 columns x 128 k as exact integer dot products.
+// Fragment rows 0-7 are the columns of the first octet, rows 8-15 those of the second (FULL = false: a single octet).
+// acc += scale * (16 * (w . digits of plane t) - zero * 16 * sum X [t = 0]) for this lane's column and digit plane.
+template <bool FULL>
+__device__ __forceinline__ void ch_item(const unsigned char* rec, const unsigned char* xg, const ch_lane& L, float& acc_a, float& acc_b) {
+    const uint32_t H = 0xf0f0f0f0u;
+    const uint4 wa = *reinterpret_cast<const uint4*>(rec + L.w_off);
+    const uint4 wb = FULL ? *reinterpret_cast<const uint4*>(rec + LB_CHAIN_RECORD + L.w_off) : make_uint4(0u, 0u, 0u, 0u);
+    const uint4 b1 = *reinterpret_cast<const uint4*>(xg + L.x1);
+    const uint4 b2 = *reinterpret_cast<const uint4*>(xg + L.x2);
+    int d1[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0};
+    imma_nv(d1, wa.x, wb.x, wa.y, wb.y, b1.x, b1.y);
+    imma_nv(d2, wa.x & H, wb.x & H, wa.y & H, wb.y & H, b2.x, b2.y);
+    imma_nv(d1, wa.z, wb.z, wa.w, wb.w, b1.z, b1.w);
+    imma_nv(d2, wa.z & H, wb.z & H, wa.w & H, wb.w & H, b2.z, b2.w);
+    const float xs = *reinterpret_cast<const float*>(xg + L.xs);
+    const float2 sa = __half22float2(*reinterpret_cast<const __half2*>(rec + L.s_off));
+    acc_a = fmaf(sa.x, fmaf(-sa.y, xs, (float)(16 * (d1[0] - d2[1]) + d2[0])), acc_a);
+    if (FULL) {
+        const float2 sb = __half22float2(*reinterpret_cast<const __half2*>(rec + LB_CHAIN_RECORD + L.s_off));
+        acc_b = fmaf(sb.x, fmaf(-sb.y, xs, (float)(16 * (d1[2] - d2[3]) + d2[2])), acc_b);
     }
-    int d[CH_GC][4];
+}
+
+// One stage: gcount <= CH_GC items of one pair.  The full stage is unrolled (the loads of all items are independent of
+// each other and of the accumulators, so they go first); a short one (the tail of K) is a plain loop.
+template <bool FULL>
+__device__ __forceinline__ void ch_stage_items(const unsigned char* stage, const unsigned char* xg, int gcount, const ch_lane& L,
+                                               float& acc_a, float& acc_b) {
+    constexpr int RECB = FULL ? 2 * LB_CHAIN_RECORD : LB_CHAIN_RECORD;
+    if (gcount == CH_GC) {
 #pragma unroll
-    for (int j = 0; j < CH_GC; ++j) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0;
-    const uint32_t M = 0x0f0f0f0fu;
-#pragma unroll
-    for (int q = 0; q < 4; ++q)
-#pragma unroll
-        for (int j = 0; j < CH_GC; ++j) {
-            const uint32_t a = q == 0 ? wa[j].x : q == 1 ? wa[j].y : q == 2 ? wa[j].z : wa[j].w;
-            const uint32_t b = q == 0 ? wb[j].x : q == 1 ? wb[j].y : q == 2 ? wb[j].z : wb[j].w;
-            imma_nv(d[j], a & M, b & M, (a >> 4) & M, (b >> 4) & M, xb[j][q].x, xb[j][q].y);
-        }
-#pragma unroll
-    for (int j = 0; j < CH_GC; ++j)
-        if (!PARTIAL || j < gcount) {
-            const unsigned char* rec = stage + j * recb;
-            const float xs_f = t == 0 ? xsumf[g0 + j] : 0.f;
-            // (scale, zero-point) of column g; t = 0 holds digit planes 0 and 1, t = 1 plane 2 (and the empty plane 3)
-            const float2 sa = __half22float2(*reinterpret_cast<const __half2*>(rec + 512 + 4 * g));
-            acc_a = fmaf(sa.x, fmaf(-sa.y, xs_f, (float)(d[j][0] + (d[j][1] << 8)) * lane_mul), acc_a);
-            if (full_pair) {
-                const float2 sb = __half22float2(*reinterpret_cast<const __half2*>(rec + LB_CHAIN_RECORD + 512 + 4 * g));
-                acc_b = fmaf(sb.x, fmaf(-sb.y, xs_f, (float)(d[j][2] + (d[j][3] << 8)) * lane_mul), acc_b);
-            }
-        }
+        for (int j = 0; j < CH_GC; ++j) ch_item<FULL>(stage + j * RECB, xg + j * CH_XG, L, acc_a, acc_b);
+    } else {
+#pragma unroll 1
+        for (int j = 0; j < gcount; ++j) ch_item<FULL>(stage + j * RECB, xg + j * CH_XG, L, acc_a, acc_b);
+    }
 }
 
 // The activation vector of one GEMV as exact integers, for the whole block: X_k = rint(x_k * 2^shift) with
@@ -150,7 +174,7 @@ __device__ __forceinline__ void ch_stage_items(const unsigned char* stage, int g
 // Thread tid owns packed rows tid, tid + 512, ... (NI of them at most); all global loads are issued before the
 // first use, so the prologue costs one trip to L2, not one per row.
 template <int NI>
-__device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& sh, uint32_t* xdig, float* xsumf, int tid, bool write_x,
+__device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& sh, unsigned char* xtab, int tid, bool write_x,
                                              const unsigned long long* mailbox, uint32_t tag, uint32_t* status) {
     const int lane = tid & 31, warp = tid >> 5;
     const int rows = op.K / 8;
@@ -323,35 +347,42 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
     for (int i = 0; i < NI; ++i) {
         const int r = tid + i * LB_CHAIN_THREADS;
         const bool live = r < rows;
-        // X = d0 + 256 d1 + 65536 d2 with d0, d1 in [-128,127]: d0 is the low byte of X, d1 the low byte of
-        // (X + 128) >> 8, d2 = ((X + 128 >> 8) + 128) >> 8
-        int X[8], rs = 0;
+        // X = rint(x * 2^shift) = d0 + 256 d1 + 65536 d2 with every d in [-128, 127].  Y = X + 0x808080 has the unsigned bytes
+        // d + 128, and the byte with its top bit flipped is d in two's complement.  Adding 1.5 * 2^23 in fp32 rounds x * 2^shift
+        // to the nearest integer (ties to even) and leaves it in the low mantissa bits, so Y is one FMA and one integer add.
+        uint32_t Y[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hv[i][j]));
-            X[2 * j] = __float2int_rn(f.x * qscale);
-            X[2 * j + 1] = __float2int_rn(f.y * qscale);
+            Y[2 * j] = __float_as_uint(fmaf(f.x, qscale, 12582912.0f)) + (0x00808080u - 0x4B400000u);
+            Y[2 * j + 1] = __float_as_uint(fmaf(f.y, qscale, 12582912.0f)) + (0x00808080u - 0x4B400000u);
         }
+        uint32_t rs = ((Y[0] + Y[1]) + (Y[2] + Y[3])) + ((Y[4] + Y[5]) + (Y[6] + Y[7])); // 128 values below 2^24: no overflow
+        // byte p of Y[0], Y[2], Y[4], Y[6] -> ev[p]; of Y[1], Y[3], Y[5], Y[7] -> od[p]
         uint32_t ev[3], od[3];
-#pragma unroll
-        for (int d = 0; d < 3; ++d) {
-            // bytes 0 of X[0], X[2], X[4], X[6] -> ev; of X[1], X[3], X[5], X[7] -> od
-            ev[d] = __byte_perm(__byte_perm(X[0], X[2], 0x0040), __byte_perm(X[4], X[6], 0x0040), 0x5410);
-            od[d] = __byte_perm(__byte_perm(X[1], X[3], 0x0040), __byte_perm(X[5], X[7], 0x0040), 0x5410);
-            if (d == 0) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) rs += X[j];
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) X[j] = (X[j] + 128) >> 8;
+        {
+            const uint32_t a = __byte_perm(Y[0], Y[2], 0x5140), b = __byte_perm(Y[4], Y[6], 0x5140);
+            ev[0] = __byte_perm(a, b, 0x5410);
+            ev[1] = __byte_perm(a, b, 0x7632);
+            ev[2] = __byte_perm(__byte_perm(Y[0], Y[2], 0x0062), __byte_perm(Y[4], Y[6], 0x0062), 0x5410);
+            const uint32_t c = __byte_perm(Y[1], Y[3], 0x5140), d = __byte_perm(Y[5], Y[7], 0x5140);
+            od[0] = __byte_perm(c, d, 0x5410);
+            od[1] = __byte_perm(c, d, 0x7632);
+            od[2] = __byte_perm(__byte_perm(Y[1], Y[3], 0x0062), __byte_perm(Y[5], Y[7], 0x0062), 0x5410);
         }
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o); // the group's 16 rows
         if (live) {
-            uint32_t* dst = xdig + digit_row_word(r);
+            // packed row r of group r / 16: word (r & 15) >> 2 of fragment lane t = r & 3
+            unsigned char* blk = xtab + (size_t)(r >> 4) * CH_XG + (r & 3) * 16 + ((r & 15) >> 2) * 4;
 #pragma unroll
-            for (int d = 0; d < 3; ++d) *reinterpret_cast<uint2*>(dst + 2 * d) = make_uint2(ev[d], od[d]);
-            if ((lane & 15) == 0) xsumf[r >> 4] = (float)rs;
+            for (int d = 0; d < 3; ++d) {
+                *reinterpret_cast<uint32_t*>(blk + d * 64) = ev[d] ^ 0x80808080u;
+                *reinterpret_cast<uint32_t*>(blk + CH_X_ODD + d * 64) = od[d] ^ 0x80808080u;
+            }
+            if ((lane & 15) == 0) // sum of X = sum of Y - 128 * 0x808080
+                *reinterpret_cast<float4*>(xtab + (size_t)(r >> 4) * CH_XG + CH_X_SUM) =
+                    make_float4(16.0f * (float)(int)(rs - 128u * 0x00808080u), 0.f, 0.f, 0.f);
             if (op.x_out && write_x) // every CTA holds the whole vector: one of them writes it out
                 *reinterpret_cast<uint4*>(op.x_out + r * 8) = make_uint4(hv[i][0], hv[i][1], hv[i][2], hv[i][3]);
         }
@@ -367,11 +398,9 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     const int c = blockIdx.x, G = gridDim.x;
     const int NS = p.slots; // ring slots of every warp
 
-    // shared memory: [ring: CH_W * NS stages][digit table][group sums][per (pair, warp) column sums][mbarriers][stage lists]
-    uint32_t* xdig = reinterpret_cast<uint32_t*>(smem + (size_t)CH_W * NS * LB_CHAIN_STAGE_BYTES);
-    const int dig_words = (digit_row_word(p.table_rows) + 3) & ~3;
-    float* xsumf = reinterpret_cast<float*>(xdig + dig_words);             // [table_rows / 16] sum of each K-group's integers
-    float* red = xsumf + ((p.table_rows / LB_GEMV_ROWS + 3) & ~3);        // [max_pairs][CH_W][16]
+    // shared memory: [ring: CH_W * NS stages][activation table][per (pair, warp) column sums][mbarriers][stage lists]
+    unsigned char* xtab = smem + (size_t)CH_W * NS * LB_CHAIN_STAGE_BYTES;
+    float* red = reinterpret_cast<float*>(xtab + (size_t)(p.table_rows / LB_GEMV_ROWS) * CH_XG + 64); // [max_pairs][CH_W][16]
     uint64_t* full = reinterpret_cast<uint64_t*>(red + (size_t)p.max_pairs * CH_W * 16); // [CH_W * NS]
     uint2* stage_tab = reinterpret_cast<uint2*>(full + CH_W * NS);                        // [CH_W][tab_len]
 
@@ -402,22 +431,27 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     __syncthreads();
 
 
-    // ---- this warp's stream: stages warp, warp + 16, warp + 32, ... of the CTA's list (all GEMVs of the chain).
-    //      The warp writes them down once as (offset, descriptor) words; stage number m of the stream lives in ring
-    //      slot m % NS of the warp. ----
+    // ---- this warp's stream: of every GEMV's stage list (pair-major, chunks of CH_GC K-groups) the warp takes the
+    //      contiguous run [warp * n / 16, (warp + 1) * n / 16), so that consecutive stages mostly belong to the same pair and
+    //      the column sums stay in registers.  The warp writes its stages down once as (offset, descriptor) words; stage
+    //      number m of the stream lives in ring slot m % NS of the warp. ----
     uint2* tab = stage_tab + (size_t)warp * p.tab_len;
     uint32_t n_mine = 0;
     {
-        // the lanes write the warp's entries in parallel: entry m is stage warp + 16 m of the CTA's list
-        const int total = sh.op_pre[p.n_ops];
-        if (total > warp) n_mine = min((uint32_t)((total - warp + CH_W - 1) / CH_W), (uint32_t)p.tab_len);
-        for (uint32_t m = lane; m < n_mine; m += 32) {
-            const int k = warp + CH_W * (int)m;
-            int o = 0;
-            while (k >= sh.op_pre[o + 1]) ++o; // k < total, so this stops inside the list
+        for (int o = 0; o < p.n_ops; ++o) {
+            const int n = sh.op_pre[o + 1] - sh.op_pre[o];
+            n_mine += (uint32_t)((warp + 1) * n / CH_W - warp * n / CH_W);
+        }
+        n_mine = min(n_mine, (uint32_t)p.tab_len);
+        for (uint32_t m = lane; m < n_mine; m += 32) { // the lanes write the warp's entries in parallel
+            int o = 0, li = (int)m;
+            for (;; ++o) { // m < n_mine, so this stops inside the list
+                const int n = sh.op_pre[o + 1] - sh.op_pre[o], first = warp * n / CH_W, cnt = (warp + 1) * n / CH_W - first;
+                if (li < cnt) { li += first; break; }
+                li -= cnt;
+            }
             ch_cursor cur;
             cur.o = o;
-            const int li = k - sh.op_pre[o];
             cur.pair = li / sh.op_nch[o];
             cur.chunk = li - cur.pair * sh.op_nch[o];
             const ch_stage st = ch_decode(p, sh, cur);
@@ -443,7 +477,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     for (int i = 0; i < NS; ++i) request();
 
     const int fg = lane >> 2, ft = lane & 3;
-    const float lane_mul = ft == 0 ? 1.0f : (ft == 1 ? 65536.0f : 0.0f);
+    const ch_lane L = ch_lane_make(lane);
     pdl_wait(); // activations and barrier words belong to the stream order
     // tensor parallel: the exchange generation of this GPU, read once (every all-reduce entry of the launch shares it)
     unsigned ar_gen0 = 0, n_barriers = 0; // n_barriers: grid barriers passed (thread 0 only)
@@ -556,8 +590,8 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         for (int i = tid; i < ((no + 1) / 2) * CH_W * 16; i += LB_CHAIN_THREADS) red[i] = 0.f;
         const unsigned long long* in_mail = op.x_src ? p.mail + (size_t)(op.x_src - 1) * LB_CHAIN_MAIL_WORDS : nullptr;
         const uint32_t in_tag = tag_base + (uint32_t)op.x_src;
-        const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xdig, xsumf, tid, c == 0, in_mail, in_tag, p.status)
-                                                             : ch_prologue<5>(op, sh, xdig, xsumf, tid, c == 0, in_mail, in_tag, p.status);
+        const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status)
+                                                             : ch_prologue<5>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status);
 
         // the residual value this thread will add its column's result to: asked for now, so that the epilogue does not wait for it
         // (nobody else writes the column; this thread's own earlier store is what L2 holds)
@@ -571,7 +605,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         int cur_pair = -1;
         auto flush = [&]() {
             if (cur_pair < 0) return;
-            float a = acc_a, b = acc_b;
+            float a = acc_a * L.mul, b = acc_b * L.mul; // digit plane t of the column: its power of 256
             a += __shfl_xor_sync(0xffffffffu, a, 1);
             a += __shfl_xor_sync(0xffffffffu, a, 2);
             b += __shfl_xor_sync(0xffffffffu, b, 1);
@@ -598,8 +632,8 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
                 cur_pair = pair;
             }
             const unsigned char* stage = smem + (size_t)slot * LB_CHAIN_STAGE_BYTES;
-            if (gcount == CH_GC) ch_stage_items<false>(stage, g0, gcount, full_pair, xdig, xsumf, lane, lane_mul, acc_a, acc_b);
-            else ch_stage_items<true>(stage, g0, gcount, full_pair, xdig, xsumf, lane, lane_mul, acc_a, acc_b);
+            if (full_pair) ch_stage_items<true>(stage, xtab + (size_t)g0 * CH_XG, gcount, L, acc_a, acc_b);
+            else ch_stage_items<false>(stage, xtab + (size_t)g0 * CH_XG, gcount, L, acc_a, acc_b);
             ++m_use;
             __syncwarp(); // every lane has consumed its words (the sums above depend on them): the slot can be overwritten
             request();    // refill this slot with the stream's next stage (maybe of a later GEMV)

@@ -83,6 +83,7 @@ typedef struct {
 #define LB_CHAIN_GC 4                /* K-groups per stage */
 #define LB_CHAIN_STAGE_BYTES (LB_CHAIN_GC * 2 * LB_CHAIN_RECORD)
 #define LB_CHAIN_MAX_OCTETS 32       /* octets one CTA may own */
+#define LB_CHAIN_GROUP_BYTES 448     /* shared-memory bytes of one K-group's block of the activation table (chain.cu) */
 #define LB_CHAIN_MAIL_WORDS 17408    /* 8-byte words of one entry's mailbox: fp32 results one per word, fp16 results two per word */
 
 typedef struct {
