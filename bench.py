@@ -701,7 +701,8 @@ def bench_timeline(args, rank, local, world, dist):
     stamps of lb_set_chain_timeline (no profiler).  Three DeltaNet layers of the benchmark's widths (one chain launch of 12
     entries: per layer input projection, mixer, out projection, gate/up, down; under tensor parallelism the out and down
     projections carry the exchange in their epilogue) decoded at position 4096; the stamps of the last of 40 replays are
-    read on every rank, rank 0 prints medians over the SMs in microseconds."""
+    read on every rank, rank 0 prints medians over the SMs in microseconds.  Intervals inside an entry come from the SM's
+    cycle counter; one %globaltimer stamp per entry gives the skew between the SMs and the cycle time."""
     import lithos_b200 as lb
     from lithos_b200 import model as M
     from lithos_b200 import tp
@@ -735,22 +736,32 @@ def bench_timeline(args, rank, local, world, dist):
              "gate/up projection (5120 -> 34816/tp, RMSNorm prologue, SwiGLU)", "down projection (17408/tp -> 5120" + (", exchange" if world > 1 else "") + ")"]
     rows = []
     n_ops = 15
-    t_first = t[:, 0, 0].min()
+    if not (t[:, :n_ops, 0] > 0).all() or (t[:, n_ops, 0] != 0).any():
+        raise SystemExit("timeline: the three layers did not run as one launch of %d entries" % n_ops)
+    # stamp [0] is %globaltimer (ns), [1..7] the SM's cycle counter: ns per cycle of every SM from the first and the last entry
+    ns_per_cyc = (t[:, n_ops - 1, 0] - t[:, 0, 0]) / np.maximum(t[:, n_ops - 1, 1] - t[:, 0, 1], 1)
+    us = lambda cyc: float(np.median(cyc * ns_per_cyc)) / 1e3
     for o in range(n_ops):
         e = t[:, o, :]
         kind = o % 5
-        med = lambda a: float(np.median(a)) / 1e3
-        rec = {"entry": o, "kind": names[kind], "barrier_wait_us": round(med(e[:, 1] - e[:, 0]), 2) if o else 0.0,
-               "arrival_skew_us": round(float(e[:, 0].max() - e[:, 0].min()) / 1e3, 2),
-               "table_us": round(med(e[:, 2] - e[:, 1]), 2), "body_us": round(med(e[:, 3] - e[:, 2]), 2),
-               "epilogue_exchange_us": round(med(e[:, 4] - e[:, 3]), 2), "entry_total_us": round(med(e[:, 4] - e[:, 0]), 2)}
+        rec = {"entry": o, "kind": names[kind], "arrival_skew_us": round(float(e[:, 0].max() - e[:, 0].min()) / 1e3, 2),
+               "barrier_us": round(us(e[:, 2] - e[:, 1]), 2)}
+        if kind == 1:
+            rec.update({"mixer_us": round(us(e[:, 7] - e[:, 2]), 2)})
+        else:
+            rec.update({"input_wait_us": round(us(e[:, 3] - e[:, 2]), 2), "table_us": round(us(e[:, 4] - e[:, 3]), 2),
+                        "body_us": round(us(e[:, 5] - e[:, 4]), 2), "column_sum_us": round(us(e[:, 6] - e[:, 5]), 2),
+                        "store_exchange_us": round(us(e[:, 7] - e[:, 6]), 2)})
+        rec["entry_total_us"] = round(us(e[:, 7] - e[:, 1]), 2)
         rows.append(rec)
-    total = float(t[:, n_ops - 1, 4].max() - t_first) / 1e3
+    last = t[:, n_ops - 1, :]
+    total = float((last[:, 0] + (last[:, 7] - last[:, 1]) * ns_per_cyc).max() - t[:, 0, 0].min()) / 1e3
     by_kind = {}
     for r_ in rows[5:]:      # layers 2 and 3: the first layer of the launch starts without a barrier
-        k = by_kind.setdefault(r_["kind"], {"barrier_wait_us": 0.0, "table_us": 0.0, "body_us": 0.0, "epilogue_exchange_us": 0.0, "entry_total_us": 0.0, "n": 0})
-        for f in ("barrier_wait_us", "table_us", "body_us", "epilogue_exchange_us", "entry_total_us"):
-            k[f] += r_[f]
+        k = by_kind.setdefault(r_["kind"], {"n": 0})
+        for f, v in r_.items():
+            if f.endswith("_us"):
+                k[f] = k.get(f, 0.0) + v
         k["n"] += 1
     for k in by_kind.values():
         n = k.pop("n")

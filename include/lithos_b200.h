@@ -74,9 +74,11 @@ void lb_set_chain_reserve(lb_ctx* ctx, int bytes);
  * between every pair of entries.  Same results either way (the words carry the same fp32 / fp16 values). */
 void lb_set_chain_mailbox(lb_ctx* ctx, int on);
 /* Profiling hook: while buf != 0, every persistent-chain launch made (or captured) afterwards writes, for each SM and
- * chain entry, five %globaltimer values (ns) of the SM's thread 0 -- reached the grid barrier, left it, activation
- * table ready / mixer started, every weight stage consumed, entry finished (epilogue and, under tensor parallelism, the
- * exchange) -- into buf as u64 [SMs][LB_GEMV_CHAIN_MAX][8].  Launches overwrite each other's stamps. */
+ * chain entry, eight stamps of the SM's thread 0 into buf as u64 [SMs][LB_GEMV_CHAIN_MAX][8]: [0] %globaltimer (ns) when
+ * the entry is reached, then the SM's cycle counter at [1] entry reached, [2] grid barrier left, [3] input vector arrived,
+ * [4] activation table ready, [5] every weight stage consumed, [6] column sums ready, [7] entry finished (epilogue and,
+ * under tensor parallelism, the exchange); a mixer entry stamps [3..7] when it ends.  Only [0] compares across SMs.
+ * Launches overwrite each other's stamps. */
 void lb_set_chain_timeline(lb_ctx* ctx, uint64_t buf);
 
 /* ---- generic module load + launch ----------------------------------------------

@@ -41,34 +41,34 @@ LB_API int lb_gemv_pack(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
 }
 
 /* Shared-memory plan of one chain launch: 0 ring slots = does not fit. */
-typedef struct { int slots, table_rows, max_pairs, tab_len; unsigned smem; } chain_plan;
+typedef struct { int slots, table_rows, red_slots, tab_len; unsigned smem; } chain_plan;
 
 static void chain_plan_make(const lb_ctx* c, const lb_chain_op* ops, int n_ops, chain_plan* pl) {
-    int max_rows = 16, max_oct = 2, has_dn = 0;
+    int max_rows = 16, red_slots = 1, has_dn = 0;
     long long max_stages = 0; /* stages of the busiest CTA, all GEMVs of the chain */
     for (int i = 0; i < n_ops; i++) {
         const lb_chain_op* d = &ops[i];
         if (d->type != LB_CHAIN_OP_GEMV) { has_dn = 1; continue; }
         if (d->K / 8 > max_rows) max_rows = d->K / 8;
         const int widest = (int)(((long long)d->units + c->sm_count - 1) / c->sm_count) * d->upo;
-        if (widest > max_oct) max_oct = widest;
-        max_stages += (long long)((widest + 1) / 2) * ((d->kg + LB_CHAIN_GC - 1) / LB_CHAIN_GC);
+        const int stages = ((widest + 1) / 2) * ((d->kg + LB_CHAIN_GC - 1) / LB_CHAIN_GC);
+        if (stages > red_slots) red_slots = stages;
+        max_stages += stages;
     }
-    /* the activation table of the longest K, the per-(pair, warp) column sums (the DeltaNet entries use the same
-     * bytes: four units of 3232 B), the warps' stage lists, then as many ring slots per warp as fit, minus (when that
+    /* the activation table of the longest K, one 16-float slot of column sums per stage of a GEMV (the DeltaNet entries use
+     * the same bytes: four units of 3232 B), the CTA's stage list, then as many ring slots per warp as fit, minus (when that
      * still leaves two slots) room for a small CTA of the neighbouring kernel */
-    int max_pairs = (max_oct + 1) / 2;
-    if (has_dn && max_pairs < 13) max_pairs = 13;
+    if (has_dn && red_slots < 13 * LB_CHAIN_WARPS) red_slots = 13 * LB_CHAIN_WARPS;
     const size_t table = (size_t)(max_rows / LB_GEMV_ROWS) * LB_CHAIN_GROUP_BYTES + 64;
-    const int tab_len = (int)((max_stages + LB_CHAIN_WARPS - 1) / LB_CHAIN_WARPS) + n_ops + 1; /* a warp's run of every GEMV is rounded up */
-    const size_t fixed = table + (size_t)max_pairs * LB_CHAIN_WARPS * 16 * 4 + (size_t)LB_CHAIN_WARPS * tab_len * 8;
-    const size_t per_slot = (size_t)LB_CHAIN_WARPS * (LB_CHAIN_STAGE_BYTES + 8);
+    const int tab_len = (int)max_stages;
+    const size_t fixed = table + (size_t)red_slots * 64 + (size_t)tab_len * 8 + 8;
+    const size_t per_slot = (size_t)LB_CHAIN_WARPS * (LB_CHAIN_STAGE_BYTES + 8 + 4);
     const size_t limit = (size_t)c->max_smem_optin - (size_t)((c->fn_static_smem[LBK_gemv_chain] + 1023) & ~1023);
     int slots = limit > fixed + (size_t)c->chain_reserve ? (int)((limit - fixed - (size_t)c->chain_reserve) / per_slot) : 0;
     if (slots < 2) slots = limit > fixed ? (int)((limit - fixed) / per_slot) : 0;
     if (slots > 4) slots = 4;
     if (slots < 2) slots = 0;
-    pl->slots = slots; pl->table_rows = max_rows; pl->max_pairs = max_pairs; pl->tab_len = tab_len;
+    pl->slots = slots; pl->table_rows = max_rows; pl->red_slots = red_slots; pl->tab_len = tab_len;
     pl->smem = (unsigned)(fixed + (size_t)slots * per_slot);
 }
 
@@ -112,7 +112,7 @@ int lb_chain_launch(lb_ctx* c, const lb_chain_op* ops, int n_ops) {
     p.mail = (unsigned long long*)c->chain_mail;
     p.slots = pl.slots;
     p.table_rows = pl.table_rows;
-    p.max_pairs = pl.max_pairs;
+    p.red_slots = pl.red_slots;
     p.tab_len = pl.tab_len;
     p.n_ops = n_ops;
     p.trigger_op = n_ops - 1;

@@ -10,17 +10,18 @@
 //     final: no partial sums, counters or atomics between CTAs, and the sum order is fixed.
 //   * The weights come from a strip-packed copy (gemv_pack_strips below; layout in params.h) in
 //     which a CTA's strip is one contiguous byte range, cut into stages of 4 K-groups x 16
-//     columns (4352 bytes).  Of every GEMV's stage list each of the 16 warps takes a contiguous run: the
-//     warp requests a stage with a plain 1-D bulk copy into one of its own ring
-//     slots, waits for it on the slot's mbarrier, consumes it alone and refills the slot with its
-//     next stage.  No producer warp, no block-wide synchronisation inside a GEMV.  Weights are
-//     constants, so a warp's requests run on into the NEXT GEMV of the chain while the block
-//     finishes the current one: the rings of all SMs keep HBM busy across entry boundaries.
+//     columns (4352 bytes).  Whenever one of a warp's ring slots is free the warp takes the next stage of the
+//     CTA's list that nobody has asked for (a counter in shared memory), requests it with a plain 1-D bulk
+//     copy into that slot, waits for it on the slot's mbarrier and consumes it alone.  No producer warp, no
+//     block-wide synchronisation inside a GEMV, and the 16 warps finish a GEMV together however unevenly the
+//     stages arrive.  Weights are constants, so the requests run on into the NEXT GEMV of the chain while
+//     the block finishes the current one: the rings of all SMs keep HBM busy across entry boundaries.
 //   * A stage item is (K-group, pair of octets): two 128-bit loads per lane give the packed words, which go
 //     into the tensor core as they are (a byte = two nibbles) and once more with the low nibbles masked off;
 //     four m16n8k32 u8 x s8 steps against the activation digit planes give the exact integer dot products
-//     of 16 columns (ch_item below); scale and zero-point are applied in fp32 per group.  Per-column sums
-//     are added in a fixed order (stage order inside a warp, then warp order).
+//     of 16 columns (ch_item below); scale and zero-point are applied in fp32 per group.  A stage leaves its
+//     16 column sums in the stage's own slot, and the slots of a column are added in the order of K: the
+//     result does not depend on which warp took which stage.
 //   * A DeltaNet entry runs the mixer of a layer ((value head, 32-column slab) units, four teams of 128
 //     threads per CTA; deltanet_core.cuh); an all-reduce entry adds every rank's partial vector into the
 //     residual stream over plain peer loads (comm_core.cuh).  The weight rings stay full meanwhile.
@@ -44,6 +45,17 @@
 #define CH_GC LB_CHAIN_GC
 #define CH_SYNC() __syncthreads()
 
+// timeline stamps: the "memory" clobber keeps the read where it is written (between the block barriers and memory accesses around it)
+__device__ __forceinline__ unsigned long long ch_clock() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+    return t;
+}
+__device__ __forceinline__ unsigned long long ch_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+    return t;
+}
 __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -60,8 +72,11 @@ struct __align__(16) ch_shared {
     int op_np[LB_CHAIN_MAX_OPS];     // pairs in the strip (a trailing single octet counts as one)
     int op_nch[LB_CHAIN_MAX_OPS];    // chunks of CH_GC K-groups per pair
     int op_pre[LB_CHAIN_MAX_OPS + 1]; // stages of this CTA before each GEMV (prefix sums of op_np * op_nch)
+    uint32_t next; // next stage of the CTA's list that nobody has asked for yet
     uint32_t bad;  // a bounded wait ran out (set by any thread at any time)
     uint32_t snap; // copy of bad taken by thread 0 before a block barrier: the value all threads act on together
+    unsigned long long stamp[8]; // timeline stamps of the current entry (thread 0), copied out when the entry ends: a global store
+                                 // in the middle of an entry would hold up the loads and stores behind it
 };
 
 // position in the CTA's stage list: GEMV o, pair of that GEMV's strip, chunk of CH_GC K-groups of the pair
@@ -128,14 +143,14 @@ __device__ __forceinline__ ch_lane ch_lane_make(int lane) {
     return L;
 }
 
-// One item: K-group (record `rec`, table block `xg`) x pair of octets = 16 columns x 128 k as exact integer dot products.
-// Fragment rows 0-7 are the columns of the first octet, rows 8-15 those of the second (FULL = false: a single octet).
+// One item: K-group (packed words wa, wb and (scale, zero-point) words sa, sb of this lane; table block `xg`) x pair of
+// octets = 16 columns x 128 k as exact integer dot products.  Fragment rows 0-7 are the columns of the first octet, rows
+// 8-15 those of the second (FULL = false: a single octet, wb = sb = 0).
 // acc += scale * (16 * (w . digits of plane t) - zero * 16 * sum X [t = 0]) for this lane's column and digit plane.
 template <bool FULL>
-__device__ __forceinline__ void ch_item(const unsigned char* rec, const unsigned char* xg, const ch_lane& L, float& acc_a, float& acc_b) {
+__device__ __forceinline__ void ch_item(const uint4& wa, const uint4& wb, uint32_t sa_bits, uint32_t sb_bits, const unsigned char* xg,
+                                        const ch_lane& L, float& acc_a, float& acc_b) {
     const uint32_t H = 0xf0f0f0f0u;
-    const uint4 wa = *reinterpret_cast<const uint4*>(rec + L.w_off);
-    const uint4 wb = FULL ? *reinterpret_cast<const uint4*>(rec + LB_CHAIN_RECORD + L.w_off) : make_uint4(0u, 0u, 0u, 0u);
     const uint4 b1 = *reinterpret_cast<const uint4*>(xg + L.x1);
     const uint4 b2 = *reinterpret_cast<const uint4*>(xg + L.x2);
     int d1[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0};
@@ -144,26 +159,50 @@ __device__ __forceinline__ void ch_item(const unsigned char* rec, const unsigned
     imma_nv(d1, wa.z, wb.z, wa.w, wb.w, b1.z, b1.w);
     imma_nv(d2, wa.z & H, wb.z & H, wa.w & H, wb.w & H, b2.z, b2.w);
     const float xs = *reinterpret_cast<const float*>(xg + L.xs);
-    const float2 sa = __half22float2(*reinterpret_cast<const __half2*>(rec + L.s_off));
+    const float2 sa = __half22float2(*reinterpret_cast<const __half2*>(&sa_bits));
     acc_a = fmaf(sa.x, fmaf(-sa.y, xs, (float)(16 * (d1[0] - d2[1]) + d2[0])), acc_a);
     if (FULL) {
-        const float2 sb = __half22float2(*reinterpret_cast<const __half2*>(rec + LB_CHAIN_RECORD + L.s_off));
+        const float2 sb = __half22float2(*reinterpret_cast<const __half2*>(&sb_bits));
         acc_b = fmaf(sb.x, fmaf(-sb.y, xs, (float)(16 * (d1[2] - d2[3]) + d2[2])), acc_b);
     }
 }
 
-// One stage: gcount <= CH_GC items of one pair.  The full stage is unrolled (the loads of all items are independent of
-// each other and of the accumulators, so they go first); a short one (the tail of K) is a plain loop.
+// A whole stage (CH_GC items) in registers: the ring slot is read in one go, handed back to the copy engine, and the
+// tensor-core work runs from registers and the activation table while the slot's next stage is already on its way.
 template <bool FULL>
-__device__ __forceinline__ void ch_stage_items(const unsigned char* stage, const unsigned char* xg, int gcount, const ch_lane& L,
-                                               float& acc_a, float& acc_b) {
-    constexpr int RECB = FULL ? 2 * LB_CHAIN_RECORD : LB_CHAIN_RECORD;
-    if (gcount == CH_GC) {
+struct ch_stage_regs {
+    uint4 wa[CH_GC], wb[CH_GC];
+    uint32_t sa[CH_GC], sb[CH_GC];
+    __device__ __forceinline__ void load(const unsigned char* stage, const ch_lane& L) {
+        constexpr int RECB = FULL ? 2 * LB_CHAIN_RECORD : LB_CHAIN_RECORD;
 #pragma unroll
-        for (int j = 0; j < CH_GC; ++j) ch_item<FULL>(stage + j * RECB, xg + j * CH_XG, L, acc_a, acc_b);
-    } else {
+        for (int j = 0; j < CH_GC; ++j) {
+            const unsigned char* rec = stage + j * RECB;
+            wa[j] = *reinterpret_cast<const uint4*>(rec + L.w_off);
+            sa[j] = *reinterpret_cast<const uint32_t*>(rec + L.s_off);
+            wb[j] = FULL ? *reinterpret_cast<const uint4*>(rec + LB_CHAIN_RECORD + L.w_off) : make_uint4(0u, 0u, 0u, 0u);
+            sb[j] = FULL ? *reinterpret_cast<const uint32_t*>(rec + LB_CHAIN_RECORD + L.s_off) : 0u;
+        }
+    }
+    __device__ __forceinline__ void compute(const unsigned char* xg, const ch_lane& L, float& acc_a, float& acc_b) const {
+#pragma unroll
+        for (int j = 0; j < CH_GC; ++j) ch_item<FULL>(wa[j], wb[j], sa[j], sb[j], xg + j * CH_XG, L, acc_a, acc_b);
+    }
+};
+
+// A short stage (the tail of K: fewer than CH_GC items), straight from the ring slot.
+template <bool FULL>
+__device__ __forceinline__ void ch_stage_tail(const unsigned char* stage, const unsigned char* xg, int gcount, const ch_lane& L,
+                                              float& acc_a, float& acc_b) {
+    constexpr int RECB = FULL ? 2 * LB_CHAIN_RECORD : LB_CHAIN_RECORD;
 #pragma unroll 1
-        for (int j = 0; j < gcount; ++j) ch_item<FULL>(stage + j * RECB, xg + j * CH_XG, L, acc_a, acc_b);
+    for (int j = 0; j < gcount; ++j) {
+        const unsigned char* rec = stage + j * RECB;
+        const uint4 wa = *reinterpret_cast<const uint4*>(rec + L.w_off);
+        const uint4 wb = FULL ? *reinterpret_cast<const uint4*>(rec + LB_CHAIN_RECORD + L.w_off) : make_uint4(0u, 0u, 0u, 0u);
+        const uint32_t sa = *reinterpret_cast<const uint32_t*>(rec + L.s_off);
+        const uint32_t sb = FULL ? *reinterpret_cast<const uint32_t*>(rec + LB_CHAIN_RECORD + L.s_off) : 0u;
+        ch_item<FULL>(wa, wb, sa, sb, xg + j * CH_XG, L, acc_a, acc_b);
     }
 }
 
@@ -175,7 +214,7 @@ __device__ __forceinline__ void ch_stage_items(const unsigned char* stage, const
 // first use, so the prologue costs one trip to L2, not one per row.
 template <int NI>
 __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& sh, unsigned char* xtab, int tid, bool write_x,
-                                             const unsigned long long* mailbox, uint32_t tag, uint32_t* status) {
+                                             const unsigned long long* mailbox, uint32_t tag, uint32_t* status, unsigned long long* tl) {
     const int lane = tid & 31, warp = tid >> 5;
     const int rows = op.K / 8;
     float pre_max = -1.f; // >= 0: the largest |h| is already known (no second block-wide exchange)
@@ -208,7 +247,17 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
                 }
             }
         }
+        if (tl && tid == 0) sh.stamp[3] = ch_clock(); // this thread's part of the input vector has arrived (mailbox) or been asked for
     } else {
+        // the norm weights do not depend on the input vector: asked for before the wait for it
+        uint4 wr[NI];
+        if (op.x_mode == LB_X_F32_RMSNORM) {
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const int r = tid + i * LB_CHAIN_THREADS;
+                wr[i] = r < rows ? __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op.aux0) + r * 8)) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
         float v[NI][8];
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
@@ -246,16 +295,11 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
                 }
             }
         }
+        if (tl && tid == 0) sh.stamp[3] = ch_clock();
         if (op.x_mode == LB_X_F32_RMSNORM) {
             // h = (x * (1 + w)) * rsqrt(mean x^2 + eps): the rows held by the block's threads are the whole vector.  The
             // product with (1 + w) comes first, so that the sum of squares and the largest |x (1 + w)| go through ONE
             // block-wide exchange: rounding is monotonic, so the largest |h| is the largest |x (1 + w)| times the factor.
-            uint4 wr[NI];
-#pragma unroll
-            for (int i = 0; i < NI; ++i) {
-                const int r = tid + i * LB_CHAIN_THREADS;
-                wr[i] = r < rows ? __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(op.aux0) + r * 8)) : make_uint4(0u, 0u, 0u, 0u);
-            }
             float ss = 0.f, um = 0.f;
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
@@ -398,11 +442,12 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     const int c = blockIdx.x, G = gridDim.x;
     const int NS = p.slots; // ring slots of every warp
 
-    // shared memory: [ring: CH_W * NS stages][activation table][per (pair, warp) column sums][mbarriers][stage lists]
+    // shared memory: [ring: CH_W * NS stages][activation table][per-stage column sums][mbarriers][slot descriptors][stage list]
     unsigned char* xtab = smem + (size_t)CH_W * NS * LB_CHAIN_STAGE_BYTES;
-    float* red = reinterpret_cast<float*>(xtab + (size_t)(p.table_rows / LB_GEMV_ROWS) * CH_XG + 64); // [max_pairs][CH_W][16]
-    uint64_t* full = reinterpret_cast<uint64_t*>(red + (size_t)p.max_pairs * CH_W * 16); // [CH_W * NS]
-    uint2* stage_tab = reinterpret_cast<uint2*>(full + CH_W * NS);                        // [CH_W][tab_len]
+    float* red = reinterpret_cast<float*>(xtab + (size_t)(p.table_rows / LB_GEMV_ROWS) * CH_XG + 64); // [red_slots][16]
+    uint64_t* full = reinterpret_cast<uint64_t*>(red + (size_t)p.red_slots * 16);          // [CH_W * NS]
+    uint32_t* slot_desc = reinterpret_cast<uint32_t*>(full + CH_W * NS);                   // [CH_W * NS]
+    uint2* tab = reinterpret_cast<uint2*>(slot_desc + ((CH_W * NS + 1) & ~1));             // [tab_len]
 
     if (tid < CH_W * NS) mbar_init(&full[tid], 1);
     if (tid < p.n_ops) {
@@ -417,6 +462,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     if (tid == 0) {
         sh.bad = 0;
         sh.snap = 0;
+        sh.next = 0;
     }
     mbar_fence_init();
     __syncthreads();
@@ -431,50 +477,51 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     __syncthreads();
 
 
-    // ---- this warp's stream: of every GEMV's stage list (pair-major, chunks of CH_GC K-groups) the warp takes the
-    //      contiguous run [warp * n / 16, (warp + 1) * n / 16), so that consecutive stages mostly belong to the same pair and
-    //      the column sums stay in registers.  The warp writes its stages down once as (offset, descriptor) words; stage
-    //      number m of the stream lives in ring slot m % NS of the warp. ----
-    uint2* tab = stage_tab + (size_t)warp * p.tab_len;
-    uint32_t n_mine = 0;
-    {
-        for (int o = 0; o < p.n_ops; ++o) {
-            const int n = sh.op_pre[o + 1] - sh.op_pre[o];
-            n_mine += (uint32_t)((warp + 1) * n / CH_W - warp * n / CH_W);
-        }
-        n_mine = min(n_mine, (uint32_t)p.tab_len);
-        for (uint32_t m = lane; m < n_mine; m += 32) { // the lanes write the warp's entries in parallel
-            int o = 0, li = (int)m;
-            for (;; ++o) { // m < n_mine, so this stops inside the list
-                const int n = sh.op_pre[o + 1] - sh.op_pre[o], first = warp * n / CH_W, cnt = (warp + 1) * n / CH_W - first;
-                if (li < cnt) { li += first; break; }
-                li -= cnt;
-            }
-            ch_cursor cur;
-            cur.o = o;
-            cur.pair = li / sh.op_nch[o];
-            cur.chunk = li - cur.pair * sh.op_nch[o];
-            const ch_stage st = ch_decode(p, sh, cur);
-            const uint32_t full_pair = st.recb == 2 * LB_CHAIN_RECORD;
-            tab[m] = make_uint2((uint32_t)((st.src - p.op[o].packed) >> 4),
-                                (uint32_t)o | ((uint32_t)cur.pair << 5) | ((uint32_t)st.g0 << 10) | ((uint32_t)st.gcount << 22) | (full_pair << 25));
-        }
+    // ---- the CTA's stage list: all GEMVs of the chain in order, each pair-major in chunks of CH_GC K-groups, written down
+    //      once as (offset, descriptor) words.  A warp takes the next stage nobody has asked for whenever one of its ring
+    //      slots is free (a counter in shared memory), so the warps of a block finish a GEMV together however unevenly the
+    //      stages arrive; what a stage adds to the column sums goes to the stage's own slot, so the result does not depend
+    //      on who took what. ----
+    const uint32_t total = min((uint32_t)sh.op_pre[p.n_ops], (uint32_t)p.tab_len);
+    for (uint32_t k = tid; k < total; k += LB_CHAIN_THREADS) {
+        int o = 0;
+        while ((int)k >= sh.op_pre[o + 1]) ++o; // k < total, so this stops inside the list
+        ch_cursor cur;
+        cur.o = o;
+        const int li = (int)k - sh.op_pre[o];
+        cur.pair = li / sh.op_nch[o];
+        cur.chunk = li - cur.pair * sh.op_nch[o];
+        const ch_stage st = ch_decode(p, sh, cur);
+        const uint32_t full_pair = st.recb == 2 * LB_CHAIN_RECORD;
+        tab[k] = make_uint2((uint32_t)((st.src - p.op[o].packed) >> 4),
+                            (uint32_t)o | ((uint32_t)cur.pair << 5) | ((uint32_t)st.g0 << 10) | ((uint32_t)st.gcount << 22) | (full_pair << 25));
     }
-    __syncwarp();
+    __syncthreads();
     const uint64_t pol = l2_policy_evict_first();
-    uint32_t m_req = 0, m_use = 0;
+    uint32_t pending = 0;                             // stages asked for and not yet consumed (at most NS)
+    uint32_t req_slot = 0, use_slot = 0, use_par = 0; // the warp's ring: next slot to fill, next to consume and its mbarrier phase
+    bool exhausted = false;                           // the list has no stage left
+    unsigned char* const ring = smem + (size_t)warp * NS * LB_CHAIN_STAGE_BYTES;
+    uint64_t* const wfull = full + warp * NS;
+    uint32_t* const wdesc = slot_desc + warp * NS;
     auto request = [&]() { // weights never change: requests may run ahead of everything, the first ones start before griddepcontrol.wait
-        if (m_req >= n_mine) return;
+        if (exhausted) return;
+        uint32_t k = 0;
+        if (lane == 0) k = atomicAdd(&sh.next, 1u);
+        k = __shfl_sync(0xffffffffu, k, 0);
+        if (k >= total) { exhausted = true; return; }
         if (lane == 0) {
-            const uint2 e = tab[m_req];
-            const uint32_t slot = warp * NS + m_req % NS;
+            const uint2 e = tab[k];
             const uint32_t bytes = ((e.y >> 22) & 7u) * ((e.y >> 25) & 1u ? 2u * LB_CHAIN_RECORD : (uint32_t)LB_CHAIN_RECORD);
-            mbar_arrive_expect_tx(&full[slot], bytes);
-            bulk_g2s(smem + (size_t)slot * LB_CHAIN_STAGE_BYTES, p.op[e.y & 31u].packed + ((size_t)e.x << 4), bytes, &full[slot], pol);
+            wdesc[req_slot] = e.y;
+            mbar_arrive_expect_tx(&wfull[req_slot], bytes);
+            bulk_g2s(ring + (size_t)req_slot * LB_CHAIN_STAGE_BYTES, p.op[e.y & 31u].packed + ((size_t)e.x << 4), bytes, &wfull[req_slot], pol);
         }
-        ++m_req;
+        ++pending;
+        req_slot = req_slot + 1 == (uint32_t)NS ? 0u : req_slot + 1;
     };
     for (int i = 0; i < NS; ++i) request();
+    __syncwarp();
 
     const int fg = lane >> 2, ft = lane & 3;
     const ch_lane L = ch_lane_make(lane);
@@ -494,7 +541,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         const lb_chain_op& op = p.op[o];
         const int n0 = sh.op_n0[o], no = sh.op_no[o];
         unsigned long long* const tl = p.timeline ? p.timeline + ((size_t)c * LB_CHAIN_MAX_OPS + o) * 8 : nullptr;
-        if (tl && tid == 0) tl[0] = globaltimer_ns();
+        if (tl && tid == 0) { sh.stamp[0] = ch_globaltimer(); sh.stamp[1] = ch_clock(); }
         if (o > 0 && !(op.type == LB_CHAIN_OP_GEMV && op.x_src)) { // (a GEMV fed through a mailbox waits on the words themselves)
             // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
             CH_SYNC();
@@ -520,7 +567,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             }
             CH_SYNC();
         }
-        if (tl && tid == 0) tl[1] = globaltimer_ns();
+        if (tl && tid == 0) sh.stamp[2] = ch_clock();
         if (o == p.trigger_op) pdl_launch_dependents();
         if (sh.snap) break; // uniform: written before the barrier above, by one thread
 
@@ -563,7 +610,11 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             }
             if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             CH_SYNC();
-            if (tl && tid == 0) tl[2] = tl[3] = tl[4] = globaltimer_ns();
+            if (tl && tid == 0) {
+                const unsigned long long now = ch_clock();
+                tl[0] = sh.stamp[0]; tl[1] = sh.stamp[1]; tl[2] = sh.stamp[2];
+                tl[3] = tl[4] = tl[5] = tl[6] = tl[7] = now;
+            }
             if (sh.snap) break;
             continue;
         }
@@ -581,66 +632,83 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             }
             if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             CH_SYNC();
-            if (tl && tid == 0) tl[2] = tl[3] = tl[4] = globaltimer_ns();
+            if (tl && tid == 0) {
+                const unsigned long long now = ch_clock();
+                tl[0] = sh.stamp[0]; tl[1] = sh.stamp[1]; tl[2] = sh.stamp[2];
+                tl[3] = tl[4] = tl[5] = tl[6] = tl[7] = now;
+            }
             if (sh.snap) break;
             continue;
         }
 
         // ---- the activation vector as exact integers: three signed base-256 digit planes ----
-        for (int i = tid; i < ((no + 1) / 2) * CH_W * 16; i += LB_CHAIN_THREADS) red[i] = 0.f;
         const unsigned long long* in_mail = op.x_src ? p.mail + (size_t)(op.x_src - 1) * LB_CHAIN_MAIL_WORDS : nullptr;
         const uint32_t in_tag = tag_base + (uint32_t)op.x_src;
-        const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status)
-                                                             : ch_prologue<5>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status);
+        const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status, tl)
+                                                             : ch_prologue<5>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status, tl);
 
         // the residual value this thread will add its column's result to: asked for now, so that the epilogue does not wait for it
         // (nobody else writes the column; this thread's own earlier store is what L2 holds)
         float y_old = 0.f;
         if ((op.y_mode == LB_Y_F32_ACCUM || op.y_mode == LB_Y_TP_ALLREDUCE) && tid < no * 8)
             y_old = __ldcg(reinterpret_cast<const float*>(op.y) + n0 * 8 + tid);
-        if (tl && tid == 0) tl[2] = globaltimer_ns();
-        // ---- this warp's stages of GEMV o.  Column sums stay in registers while consecutive stages belong to
-        //      the same pair, and go to this warp's own row of `red` when the pair changes. ----
-        float acc_a = 0.f, acc_b = 0.f;
-        int cur_pair = -1;
-        auto flush = [&]() {
-            if (cur_pair < 0) return;
-            float a = acc_a * L.mul, b = acc_b * L.mul; // digit plane t of the column: its power of 256
-            a += __shfl_xor_sync(0xffffffffu, a, 1);
-            a += __shfl_xor_sync(0xffffffffu, a, 2);
-            b += __shfl_xor_sync(0xffffffffu, b, 1);
-            b += __shfl_xor_sync(0xffffffffu, b, 2);
-            if (ft == 0) { // only this warp touches row (cur_pair, warp): plain read-modify-write, fixed order
-                float* row = red + ((size_t)cur_pair * CH_W + warp) * 16;
-                row[fg] += a;
-                row[8 + fg] += b;
-            }
-            acc_a = acc_b = 0.f;
-        };
-        while (m_use < n_mine) {
-            const uint2 e = tab[m_use];
-            if ((int)(e.y & 31u) != o) break; // the stream has reached the next GEMV
-            const uint32_t slot = warp * NS + m_use % NS;
-            if (!__all_sync(0xffffffffu, mbar_wait(&full[slot], (m_use / NS) & 1))) { // the same answer in every lane
+        if (tl && tid == 0) sh.stamp[4] = ch_clock();
+        // ---- the stages of GEMV o that this warp took.  Every stage leaves its 16 column sums in its own slot of `red`. ----
+        const int nch = sh.op_nch[o];
+        while (pending) {
+            const uint32_t desc = *reinterpret_cast<volatile uint32_t*>(&wdesc[use_slot]);
+            if ((int)(desc & 31u) != o) break; // the warp's next stage belongs to a later GEMV
+            if (!__all_sync(0xffffffffu, mbar_wait(&wfull[use_slot], use_par))) { // the same answer in every lane
                 if (lane == 0) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_FULL); sh.bad = 1; }
                 break;
             }
-            const int pair = (int)((e.y >> 5) & 31u), g0 = (int)((e.y >> 10) & 4095u), gcount = (int)((e.y >> 22) & 7u);
-            const bool full_pair = (e.y >> 25) & 1u;
-            if (pair != cur_pair) {
-                flush();
-                cur_pair = pair;
+            const int pair = (int)((desc >> 5) & 31u), g0 = (int)((desc >> 10) & 4095u), gcount = (int)((desc >> 22) & 7u);
+            const unsigned char* stage = ring + (size_t)use_slot * LB_CHAIN_STAGE_BYTES;
+            const unsigned char* xg = xtab + (size_t)g0 * CH_XG;
+            const bool full_pair = (desc >> 25) & 1u;
+            float acc_a = 0.f, acc_b = 0.f;
+            // the slot goes back to the copy engine as soon as every lane has its words: refilled with the next stage nobody
+            // has asked for (maybe of a later GEMV); its descriptor, written by lane 0, is read after the __syncwarp below.
+            // (The lanes' loads from the slot are ahead of the request in the same in-order pipe: the shared-memory atomic
+            // that picks the next stage returns after them, and the copy it leads to lands a memory latency later.)
+            auto hand_back = [&]() {
+                --pending;
+                if (++use_slot == (uint32_t)NS) { use_slot = 0; use_par ^= 1u; }
+                __syncwarp();
+                request();
+            };
+            if (gcount == CH_GC) {
+                if (full_pair) {
+                    ch_stage_regs<true> R;
+                    R.load(stage, L);
+                    hand_back();
+                    R.compute(xg, L, acc_a, acc_b);
+                } else {
+                    ch_stage_regs<false> R;
+                    R.load(stage, L);
+                    hand_back();
+                    R.compute(xg, L, acc_a, acc_b);
+                }
+            } else {
+                if (full_pair) ch_stage_tail<true>(stage, xg, gcount, L, acc_a, acc_b);
+                else ch_stage_tail<false>(stage, xg, gcount, L, acc_a, acc_b);
+                hand_back();
             }
-            const unsigned char* stage = smem + (size_t)slot * LB_CHAIN_STAGE_BYTES;
-            if (full_pair) ch_stage_items<true>(stage, xtab + (size_t)g0 * CH_XG, gcount, L, acc_a, acc_b);
-            else ch_stage_items<false>(stage, xtab + (size_t)g0 * CH_XG, gcount, L, acc_a, acc_b);
-            ++m_use;
-            __syncwarp(); // every lane has consumed its words (the sums above depend on them): the slot can be overwritten
-            request();    // refill this slot with the stream's next stage (maybe of a later GEMV)
+            acc_a *= L.mul; // digit plane t of the column: its power of 256
+            acc_b *= L.mul;
+            acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
+            acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
+            acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 2);
+            acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 2);
+            if (ft == 0) {
+                float* row = red + (size_t)(pair * nch + g0 / CH_GC) * 16;
+                row[fg] = acc_a;
+                row[8 + fg] = acc_b;
+            }
+            __syncwarp();
         }
-        flush();
         CH_SYNC();
-        if (tl && tid == 0) tl[3] = globaltimer_ns(); // every stage of the strip consumed
+        if (tl && tid == 0) sh.stamp[5] = ch_clock(); // every stage of the strip consumed
 
         // ---- column sums over the warps, in warp order; epilogue ----
         const int ncol = no * 8;
@@ -648,11 +716,12 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         const uint32_t out_tag = tag_base + (uint32_t)o + 1u;
         if (tid < ncol) {
             const int oct = tid >> 3, g = tid & 7;
-            const float* col = red + (size_t)(oct >> 1) * CH_W * 16 + (oct & 1) * 8 + g;
+            const float* col = red + (size_t)(oct >> 1) * nch * 16 + (oct & 1) * 8 + g;
             float v = 0.f;
-#pragma unroll
-            for (int w = 0; w < CH_W; ++w) v += col[w * 16];
+#pragma unroll 4
+            for (int ch = 0; ch < nch; ++ch) v += col[ch * 16]; // in the order of K
             v *= unit;
+            if (tl && tid == 0) sh.stamp[6] = ch_clock() + (v == 1.2345e-30f ? 1 : 0); // the column sum is there
             if (op.y_mode == LB_Y_SWIGLU_F16) {
                 sh.vals[tid] = v;
             } else if (op.y_mode == LB_Y_TP_ALLREDUCE) {
@@ -716,7 +785,11 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             }
         }
         if (op.y_mode == LB_Y_TP_ALLREDUCE) ++ar_done; // one more exchange of this launch (uniform)
-        if (tl && tid == 0) tl[4] = globaltimer_ns();
+        if (tl && tid == 0) {
+            sh.stamp[7] = ch_clock();
+#pragma unroll
+            for (int k = 0; k < 8; ++k) tl[k] = sh.stamp[k];
+        }
         if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
         CH_SYNC(); // red / vals are reused by the next GEMV; sh.snap is the same for everyone
         if (sh.snap) break;
@@ -735,7 +808,10 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     }
     // no copy may still be in flight into this CTA's shared memory when it exits (only after a failed wait can
     // requested stages be left unconsumed)
-    for (; m_use < m_req; ++m_use) mbar_wait(&full[warp * NS + m_use % NS], (m_use / NS) & 1);
+    for (; pending; --pending) {
+        mbar_wait(&wfull[use_slot], use_par);
+        if (++use_slot == (uint32_t)NS) { use_slot = 0; use_par ^= 1u; }
+    }
 }
 
 // ---------------------------------------------------------------------------

@@ -114,14 +114,16 @@ typedef struct {
     int32_t n_ops;
     int32_t slots;        /* ring slots per warp */
     int32_t table_rows;   /* packed rows (K/8) the activation table holds: the largest K of the chain */
-    int32_t max_pairs;    /* pairs (incl. a trailing single) of the widest strip of the chain */
+    int32_t red_slots;    /* 16-float slots for per-stage column sums: the most stages any CTA has in one GEMV of the chain */
     int32_t trigger_op;   /* griddepcontrol.launch_dependents is issued when this GEMV starts */
-    int32_t tab_len;      /* entries of a warp's stage list: ceil(stages of the busiest CTA / warps) */
+    int32_t tab_len;      /* entries of a CTA's stage list: the stages of the busiest CTA, all GEMVs of the chain */
     int32_t pad_[2];
     unsigned long long* mail; /* mailboxes: LB_CHAIN_MAX_OPS regions of LB_CHAIN_MAIL_WORDS 8-byte words (see chain.cu) */
-    unsigned long long* timeline; /* optional [gridDim.x][LB_CHAIN_MAX_OPS][8] %globaltimer stamps of thread 0: [0] reached the grid
-                                     barrier, [1] left it, [2] activation table ready (or mixer / exchange started), [3] every stage of
-                                     the strip consumed, [4] entry finished (epilogue and, under tensor parallelism, the exchange) */
+    unsigned long long* timeline; /* optional [gridDim.x][LB_CHAIN_MAX_OPS][8] stamps of thread 0.  [0] %globaltimer (ns) when the entry
+                                     is reached (the one stamp that compares across SMs); the rest are the SM's cycle counter:
+                                     [1] entry reached, [2] grid barrier left, [3] input vector arrived, [4] activation table ready,
+                                     [5] every stage of the strip consumed, [6] column sums ready, [7] entry finished (epilogue and,
+                                     under tensor parallelism, the exchange); a mixer or all-reduce entry stamps [3..7] when it ends */
 } lb_chain_params;
 
 /* gemv_pack_strips: reference format -> strip-packed (one thread per 32-bit word of the output) */

@@ -175,7 +175,8 @@ def test_chain_rejects_what_it_cannot_run(ctx, lb):
 
 
 def test_timeline_hook(ctx, lb):
-    """lb_set_chain_timeline: per SM and entry five device time stamps, in order, and nothing written once it is off"""
+    """lb_set_chain_timeline: per SM and entry one %globaltimer stamp and seven cycle-counter stamps, in order, and nothing
+    written once it is off"""
     K, N = 1024, 8192
     qw, sc, qz, x = gptq_case(K, N, seed=70)
     d = _dev(ctx, qw, sc, qz, K, N)
@@ -186,11 +187,13 @@ def test_timeline_hook(ctx, lb):
     ctx.gemv_chain([_op(d, d_x, d_y, K, N, lb.X_F16, lb.Y_F32)] * 2)   # the second entry does not read the first one's result: a grid barrier separates them
     ctx.sync()
     lb.lib().lb_set_chain_timeline(ctx.h, 0)
-    t = tl.download(np.uint64, n_sm * 32 * 8).reshape(n_sm, 32, 8).astype(np.int64)[:, :, :5]
+    t = tl.download(np.uint64, n_sm * 32 * 8).reshape(n_sm, 32, 8).astype(np.int64)
     assert (t[:, :2, :] > 0).all() and (t[:, 2:, :] == 0).all()
-    assert (np.diff(t[:, 0, :], axis=1) >= 0).all() and (np.diff(t[:, 1, :], axis=1) >= 0).all()
-    assert (t[:, 1, 0] >= t[:, 0, 4]).all()                 # entry 1 starts after entry 0 ended on the same SM
-    assert t[:, 1, 1].min() >= t[:, 0, 3].max()             # nobody leaves the grid barrier before everybody has consumed entry 0's weights
+    cyc = t[:, :, 1:]                                        # the SM's cycle counter: ordered inside an entry and from entry 0 to entry 1
+    assert (np.diff(cyc[:, 0, :], axis=1) >= 0).all() and (np.diff(cyc[:, 1, :], axis=1) >= 0).all()
+    assert (cyc[:, 1, 0] >= cyc[:, 0, 6]).all()
+    assert (t[:, 1, 0] >= t[:, 0, 0]).all()                  # %globaltimer: the one stamp that compares across SMs
+    assert (cyc[:, 1, 1] > cyc[:, 1, 0]).all()               # entry 1 passed a grid barrier
     tl.zero()
     ctx.gemv_chain([_op(d, d_x, d_y, K, N, lb.X_F16, lb.Y_F32)])
     ctx.sync()
