@@ -217,6 +217,8 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
                                              const unsigned long long* mailbox, uint32_t tag, uint32_t* status, unsigned long long* tl) {
     const int lane = tid & 31, warp = tid >> 5;
     const int rows = op.K / 8;
+    // a warp's rows of round i are 32 consecutive ones: when none of them exists the whole warp skips the round's arithmetic
+#define CH_WARP_ROWS(i) ((tid & ~31) + (i) * LB_CHAIN_THREADS < rows)
     float pre_max = -1.f; // >= 0: the largest |h| is already known (no second block-wide exchange)
     uint32_t hv[NI][4]; // the row as 8 fp16 values
     if (op.x_mode == LB_X_F16) {
@@ -303,6 +305,7 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
             float ss = 0.f, um = 0.f;
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
+                if (!CH_WARP_ROWS(i)) continue;
                 const uint32_t ww[4] = {wr[i].x, wr[i].y, wr[i].z, wr[i].w};
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -389,6 +392,7 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
     const float qscale = __uint_as_float((uint32_t)(127 + shift) << 23);
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
+        if (!CH_WARP_ROWS(i)) continue;
         const int r = tid + i * LB_CHAIN_THREADS;
         const bool live = r < rows;
         // X = rint(x * 2^shift) = d0 + 256 d1 + 65536 d2 with every d in [-128, 127].  Y = X + 0x808080 has the unsigned bytes
@@ -433,6 +437,7 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
     }
     CH_SYNC();
     return __uint_as_float((uint32_t)(127 - shift) << 23);
+#undef CH_WARP_ROWS
 }
 
 extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(const __grid_constant__ lb_chain_params p) {
