@@ -140,7 +140,10 @@ void lb_convert_bf16_to_f32(const uint16_t* src, float* dst, size_t n);
  *   (0 = zero-point 8 as in every reference kernel).  K % 128 == 0, N % 32 == 0.
  * flags select the activation / result types (primary contract: fp16 x, fp16 y).
  * The result OVERWRITES y unless LB_GEMV_Y_ACCUM is set (the reference kernel
- * always accumulates into a caller-zeroed y). */
+ * always accumulates into a caller-zeroed y).
+ * Once lb_gemv_pack (below) has made a strip-packed copy of a matrix, lb_gemv_int4 on the same qweight pointer
+ * (same K, N and SwiGLU flag) reads the copy and runs as a persistent chain of one: one CTA per SM owning whole
+ * columns, no split-K and no cluster reduction.  Freeing either buffer with lb_free ends that. */
 enum {
     LB_GEMV_X_F32 = 1 << 0,   /* x is fp32 (rounded to fp16 inside) instead of fp16 */
     LB_GEMV_Y_F32 = 1 << 1,   /* y is fp32 instead of fp16 */
@@ -179,6 +182,8 @@ typedef struct {
 size_t lb_gemv_packed_bytes(int K, int N);
 int lb_gemv_pack_version(void); /* version of the strip-packed byte layout (recorded beside measured DRAM traffic) */
 int lb_gemv_pack(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, int K, int N, int swiglu, uint64_t packed_out);
+/* the strip-packed copy lb_gemv_int4 would read for this matrix (made by lb_gemv_pack, neither buffer freed since), or 0 */
+uint64_t lb_gemv_packed_copy(const lb_ctx* ctx, uint64_t qweight, int K, int N, int swiglu);
 int lb_gemv_chain(lb_ctx* ctx, const lb_gemv_op* ops, int n_ops);
 /* LB_OK when lb_gemv_pack / lb_gemv_chain accept this shape on this GPU (no launch) */
 int lb_gemv_chain_supports(lb_ctx* ctx, int K, int N, int swiglu);

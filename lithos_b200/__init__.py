@@ -109,6 +109,7 @@ def lib() -> C.CDLL:
     sig("lb_set_chain_reserve", None, vp, i32)
     sig("lb_set_chain_timeline", None, vp, u64)
     sig("lb_set_chain_mailbox", None, vp, i32)
+    sig("lb_gemv_packed_copy", u64, vp, u64, i32, i32, i32)
     sig("lb_gemv_pack_version", i32)
     sig("lb_gptq_dequant", i32, vp, u64, u64, u64, u64, i32, i32)
     sig("lb_gemm_int4", i32, vp, u64, u64, u64, u64, u64, i32, i32, i32, i32)
@@ -341,6 +342,10 @@ class Context:
         out = self.alloc(lib().lb_gemv_packed_bytes(K, N))
         self._check(lib().lb_gemv_pack(self.h, qweight.ptr, scales.ptr, qzeros.ptr if qzeros else 0, K, N, 1 if swiglu else 0, out.ptr))
         return out
+
+    def gemv_packed_copy(self, qweight, K, N, swiglu=False) -> int:
+        """device address of the strip-packed copy gemv_int4 reads for this matrix, or 0"""
+        return lib().lb_gemv_packed_copy(self.h, qweight.ptr, K, N, 1 if swiglu else 0)
 
     def gemv_chain(self, ops):
         """ops: dicts (packed, x, y, K, N, x_mode, y_mode, aux0, aux1, x_out, eps); all of them run as ONE persistent launch"""

@@ -37,7 +37,36 @@ LB_API int lb_gemv_pack(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
     p.out = (uint32_t*)packed_out;
     p.K = K; p.N = N; p.swiglu = swiglu ? 1 : 0; p.G = c->sm_count;
     void* params[] = {&p};
-    return lb_launch(c, LBK_gemv_pack_strips, (unsigned)c->sm_count * 8, 1, 1, 256, 0, params, 0);
+    LB_TRY(lb_launch(c, LBK_gemv_pack_strips, (unsigned)c->sm_count * 8, 1, 1, 256, 0, params, 0));
+    /* remember the copy: lb_gemv_int4 on this qweight runs the strip-packed kernel from now on (until either buffer is freed) */
+    int at = c->n_packed_reg;
+    for (int i = 0; i < c->n_packed_reg; i++)
+        if (c->packed_reg[i].qweight == qweight) at = i;
+    if (at < LB_PACKED_REG_MAX) {
+        c->packed_reg[at].qweight = qweight; c->packed_reg[at].packed = packed_out;
+        c->packed_reg[at].K = K; c->packed_reg[at].N = N; c->packed_reg[at].swiglu = swiglu ? 1 : 0;
+        if (at == c->n_packed_reg) c->n_packed_reg++;
+    }
+    return LB_OK;
+}
+
+/* internal: the packed copy of this matrix, or 0 */
+uint64_t lb_packed_lookup(const lb_ctx* c, uint64_t qweight, int K, int N, int swiglu) {
+    for (int i = 0; i < c->n_packed_reg; i++)
+        if (c->packed_reg[i].qweight == qweight && c->packed_reg[i].K == K && c->packed_reg[i].N == N && c->packed_reg[i].swiglu == swiglu)
+            return c->packed_reg[i].packed;
+    return 0;
+}
+
+LB_API uint64_t lb_gemv_packed_copy(const lb_ctx* c, uint64_t qweight, int K, int N, int swiglu) {
+    return c ? lb_packed_lookup(c, qweight, K, N, swiglu ? 1 : 0) : 0;
+}
+
+/* internal: a device buffer is going away */
+void lb_packed_forget(lb_ctx* c, uint64_t ptr) {
+    for (int i = 0; i < c->n_packed_reg;)
+        if (c->packed_reg[i].qweight == ptr || c->packed_reg[i].packed == ptr) c->packed_reg[i] = c->packed_reg[--c->n_packed_reg];
+        else i++;
 }
 
 /* Shared-memory plan of one chain launch: 0 ring slots = does not fit. */

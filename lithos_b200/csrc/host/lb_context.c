@@ -271,6 +271,7 @@ LB_API int lb_malloc(lb_ctx* c, size_t bytes, uint64_t* out) {
 LB_API int lb_free(lb_ctx* c, uint64_t p) {
     if (!c) return LB_ERR_INVALID;
     if (!p) return LB_OK;
+    lb_packed_forget(c, p);
     LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
     LB_CU(c, lb_drv.MemFree((CUdeviceptr)p));
     return LB_OK;

@@ -126,6 +126,7 @@ enum {
 #define LB_MAX_MODULES 64
 #define LB_MAX_PEERS 8
 
+#define LB_PACKED_REG_MAX 1024
 struct lb_ctx {
     int device;
     CUdevice cu_dev;
@@ -151,6 +152,9 @@ struct lb_ctx {
     CUdeviceptr chain_timeline; /* optional time-stamp buffer handed to every chain launch (lb_set_chain_timeline) */
     int chain_reserve; /* bytes of an SM's shared memory the GEMV chain leaves to a neighbouring kernel's CTA */
     CUdeviceptr chain_mail; /* mailboxes of the persistent chain: LB_CHAIN_MAX_OPS x LB_CHAIN_MAIL_WORDS 8-byte (value, tag) words */
+    /* strip-packed copies made by lb_gemv_pack and still alive: lb_gemv_int4 runs the strip-packed kernel for these matrices */
+    struct { uint64_t qweight, packed; int K, N, swiglu; } packed_reg[LB_PACKED_REG_MAX];
+    int n_packed_reg;
     int chain_mailbox;      /* hand vectors from a GEMV to the next one through the mailbox (1, default) or a grid barrier (0) */
     int capturing;     /* stream capture in progress */
     uint64_t capture_launches0;
@@ -181,6 +185,8 @@ int lb_launch_cluster(lb_ctx* c, int kernel, unsigned gx, unsigned gy, unsigned 
 
 /* rng helpers used by the synthetic model builder */
 uint64_t lb_rng_u64(uint64_t seed, uint64_t stream, uint64_t i);
+uint64_t lb_packed_lookup(const lb_ctx* c, uint64_t qweight, int K, int N, int swiglu); /* lb_chain.c: strip-packed copy of a matrix, or 0 */
+void lb_packed_forget(lb_ctx* c, uint64_t ptr);                                         /* a device buffer is going away */
 uint32_t lb_rng_word(uint64_t seed, uint64_t stream, uint64_t i);
 uint16_t lb_rng_scale_f16(uint64_t seed, uint64_t stream, uint64_t i);
 uint16_t lb_f32_to_f16(float f);

@@ -135,6 +135,15 @@ LB_API int lb_gemv_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
                  : (flags & LB_GEMV_Y_ACCUM) ? LB_Y_F32_ACCUM
                  : (flags & LB_GEMV_Y_F32)   ? LB_Y_F32
                                              : LB_Y_F16;
+    /* a strip-packed copy of this matrix exists (lb_gemv_pack): one CTA per SM streams whole columns, no split-K, no cluster */
+    const uint64_t packed = lb_packed_lookup(c, qweight, K, N, y_mode == LB_Y_SWIGLU_F16);
+    if (packed) {
+        lb_gemv_op o;
+        memset(&o, 0, sizeof o);
+        o.packed = packed;
+        o.x = x; o.y = y; o.K = K; o.N = N; o.x_mode = x_mode; o.y_mode = y_mode; o.eps = 1e-6f;
+        return lb_gemv_chain(c, &o, 1);
+    }
     return lb_gemv_int4_fused(c, qweight, scales, qzeros, x, y, K, N, x_mode, y_mode, 0, 0, 0, 1e-6f);
 }
 

@@ -201,3 +201,30 @@ def test_timeline_hook(ctx, lb):
     for b in d + [d_x, d_y, tl]:
         if b:
             b.free()
+
+
+def test_gemv_int4_reads_the_packed_copy_once_there_is_one(ctx, lb, oracle):
+    """lb_gemv_int4 on a matrix that lb_gemv_pack has packed runs as a chain of one (bit-identical to lb_gemv_chain), and goes
+    back to the reference-format kernel when the copy is freed"""
+    K, N = 5120, 17408
+    qw, sc, qz, x = gptq_case(K, N, seed=77)
+    want, _ = oracle.gptq_gemv(qw, sc, qz, x, K, N)
+    d = [ctx.to_device(qw), ctx.to_device(sc), ctx.to_device(qz)]
+    d_x, y0, y1, y2, y3 = ctx.to_device(x), ctx.alloc(N * 4), ctx.alloc(N * 4), ctx.alloc(N * 4), ctx.alloc(N * 4)
+    assert ctx.gemv_packed_copy(d[0], K, N) == 0
+    ctx.gemv_int4(d[0], d[1], d[2], d_x, y0, K, N, lb.GEMV_Y_F32)
+    packed = ctx.gemv_pack(d[0], d[1], d[2], K, N)
+    assert ctx.gemv_packed_copy(d[0], K, N) == packed.ptr and ctx.gemv_packed_copy(d[0], K, N, swiglu=True) == 0
+    ctx.gemv_int4(d[0], d[1], d[2], d_x, y1, K, N, lb.GEMV_Y_F32)
+    ctx.gemv_chain([dict(packed=packed, x=d_x, y=y2, K=K, N=N, x_mode=lb.X_F16, y_mode=lb.Y_F32)])
+    packed.free()
+    assert ctx.gemv_packed_copy(d[0], K, N) == 0
+    ctx.gemv_int4(d[0], d[1], d[2], d_x, y3, K, N, lb.GEMV_Y_F32)
+    g = [b.download(np.float32, N) for b in (y0, y1, y2, y3)]
+    assert ctx.device_status() == 0
+    assert np.array_equal(g[1], g[2]) and np.array_equal(g[0], g[3])
+    for got in g:
+        assert rel_err_max(got, want) <= TOL
+    for b in d + [d_x, y0, y1, y2, y3]:
+        b.free()
+
