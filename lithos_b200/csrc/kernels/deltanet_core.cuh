@@ -12,17 +12,33 @@
 
 struct __align__(16) dn_unit_smem {
     float part[16][DN_COLS];
-    float ks[DN_D], qs[DN_D], vs[DN_COLS], red[8];
+    float ks[DN_D], qs[DN_D], vs[DN_COLS], red[16];
 };
 
 // sum over the team's 128 threads (4 warps, fixed order); every thread gets the total
 template <class Sync>
-__device__ __forceinline__ float dn_unit_sum(float v, float (&red)[8], int t, Sync sync) {
+__device__ __forceinline__ float dn_unit_sum(float v, float (&red)[16], int t, Sync sync) {
     v = warp_sum(v);
     sync(); // earlier readers of red are done
     if ((t & 31) == 0) red[t >> 5] = v;
     sync();
     return (red[0] + red[1]) + (red[2] + red[3]);
+}
+
+// four sums at once (each added in the same order as dn_unit_sum would): one exchange through shared memory instead of four
+template <class Sync>
+__device__ __forceinline__ void dn_unit_sum4(float& a, float& b, float& c, float& d, float (&red)[16], int t, Sync sync) {
+    a = warp_sum(a); b = warp_sum(b); c = warp_sum(c); d = warp_sum(d);
+    sync(); // earlier readers of red are done
+    if ((t & 31) == 0) {
+        const int w = t >> 5;
+        red[w] = a; red[4 + w] = b; red[8 + w] = c; red[12 + w] = d;
+    }
+    sync();
+    a = (red[0] + red[1]) + (red[2] + red[3]);
+    b = (red[4] + red[5]) + (red[6] + red[7]);
+    c = (red[8] + red[9]) + (red[10] + red[11]);
+    d = (red[12] + red[13]) + (red[14] + red[15]);
 }
 
 // in_proj_a/b, conv1d x3, activate, l2norm x2, decay_gate, gate_sigmoid and the recurrence of one layer
@@ -36,7 +52,7 @@ __device__ __forceinline__ float dn_unit_sum(float v, float (&red)[8], int t, Sy
 // three previous slots while one of them writes the current one.
 template <bool STANDALONE, class Sync>
 __device__ __forceinline__ void deltanet_layer_unit(const lb_dn_layer_params& p, int h, int jb, int t, dn_unit_smem& sm, Sync sync) {
-    float (&ks)[DN_D] = sm.ks, (&qs)[DN_D] = sm.qs, (&vs)[DN_COLS] = sm.vs, (&red)[8] = sm.red;
+    float (&ks)[DN_D] = sm.ks, (&qs)[DN_D] = sm.qs, (&vs)[DN_COLS] = sm.vs, (&red)[16] = sm.red;
     float (&part)[16][DN_COLS] = sm.part;
     const int gqa = p.HV / p.HK, kh = h / gqa;
     const int tj = t & 7, ti = t >> 3;
@@ -51,6 +67,26 @@ __device__ __forceinline__ void deltanet_layer_unit(const lb_dn_layer_params& p,
 
     if (STANDALONE) pdl_wait();
     const int pos = p.pos[0];
+    // (the convolution's operands and the decay / beta dot products below share one trip to L2: no block barrier lies
+    // between their loads)
+    // causal depthwise conv (ring history) + SiLU on this head's q, k channels and this slab's v channels
+    auto conv = [&](int c) {
+        const float x = __ldcg(p.qkvz + c);
+        float y = bf16_bits_to_f32(p.conv_w[c]) * x;
+        y = fmaf(bf16_bits_to_f32(p.conv_w[C + c]), p.conv_ring[(size_t)((pos + 3) & 3) * C + c], y);
+        y = fmaf(bf16_bits_to_f32(p.conv_w[2 * C + c]), p.conv_ring[(size_t)((pos + 2) & 3) * C + c], y);
+        y = fmaf(bf16_bits_to_f32(p.conv_w[3 * C + c]), p.conv_ring[(size_t)((pos + 1) & 3) * C + c], y);
+        return siluf_dev(y);
+    };
+    const int cq = kh * DN_D + t, ck = QK + kh * DN_D + t, cv = 2 * QK + h * DN_D + jb * DN_COLS + t;
+    float qv = conv(cq), kv = conv(ck);
+    if (t < DN_COLS) vs[t] = conv(cv);
+    // one CTA per key head (and every CTA for its own v channels) records the current token
+    if (h % gqa == 0 && jb == 0) {
+        p.conv_ring[(size_t)(pos & 3) * C + cq] = __ldcg(p.qkvz + cq);
+        p.conv_ring[(size_t)(pos & 3) * C + ck] = __ldcg(p.qkvz + ck);
+    }
+    if (t < DN_COLS) p.conv_ring[(size_t)(pos & 3) * C + cv] = __ldcg(p.qkvz + cv);
     // decay / beta projections: two 5120-long dot products per value head
     float a = 0.f, b = 0.f;
     {
@@ -84,33 +120,14 @@ __device__ __forceinline__ void deltanet_layer_unit(const lb_dn_layer_params& p,
                 }
             }
         }
-        a = dn_unit_sum(a, red, t, sync);
-        b = dn_unit_sum(b, red, t, sync);
     }
+    float qn = qv * qv, kn = kv * kv;
+    dn_unit_sum4(a, b, qn, kn, red, t, sync);
     const float tt = a + bf16_bits_to_f32(p.dt_bias[h]);
     const float sp = tt > 20.f ? tt : log1pf(expf(tt));
     const float g = expf(-expf(p.a_log[h]) * sp);
     const float beta = 1.0f / (1.0f + expf(-b));
 
-    // causal depthwise conv (ring history) + SiLU on this head's q, k channels and this slab's v channels
-    auto conv = [&](int c) {
-        const float x = __ldcg(p.qkvz + c);
-        float y = bf16_bits_to_f32(p.conv_w[c]) * x;
-        y = fmaf(bf16_bits_to_f32(p.conv_w[C + c]), p.conv_ring[(size_t)((pos + 3) & 3) * C + c], y);
-        y = fmaf(bf16_bits_to_f32(p.conv_w[2 * C + c]), p.conv_ring[(size_t)((pos + 2) & 3) * C + c], y);
-        y = fmaf(bf16_bits_to_f32(p.conv_w[3 * C + c]), p.conv_ring[(size_t)((pos + 1) & 3) * C + c], y);
-        return siluf_dev(y);
-    };
-    const int cq = kh * DN_D + t, ck = QK + kh * DN_D + t, cv = 2 * QK + h * DN_D + jb * DN_COLS + t;
-    float qv = conv(cq), kv = conv(ck);
-    if (t < DN_COLS) vs[t] = conv(cv);
-    // one CTA per key head (and every CTA for its own v channels) records the current token
-    if (h % gqa == 0 && jb == 0) {
-        p.conv_ring[(size_t)(pos & 3) * C + cq] = __ldcg(p.qkvz + cq);
-        p.conv_ring[(size_t)(pos & 3) * C + ck] = __ldcg(p.qkvz + ck);
-    }
-    if (t < DN_COLS) p.conv_ring[(size_t)(pos & 3) * C + cv] = __ldcg(p.qkvz + cv);
-    const float qn = dn_unit_sum(qv * qv, red, t, sync), kn = dn_unit_sum(kv * kv, red, t, sync);
     qs[t] = qv * rsqrtf(qn) * 0.08838834764831845f; // l2norm then 1/sqrt(128)
     ks[t] = kv * rsqrtf(kn);
     sync();
