@@ -75,6 +75,7 @@ struct __align__(16) ch_shared {
     uint32_t next; // next stage of the CTA's list that nobody has asked for yet
     uint32_t bad;  // a bounded wait ran out (set by any thread at any time)
     uint32_t snap; // copy of bad taken by thread 0 before a block barrier: the value all threads act on together
+    float dn_ab[2][2]; // DeltaNet entry: the gate dot products (a, b) of the units of teams 0 and 1, from teams 2 and 3
     unsigned long long stamp[8]; // timeline stamps of the current entry (thread 0), copied out when the entry ends: a global store
                                  // in the middle of an entry would hold up the loads and stores behind it
 };
@@ -547,6 +548,9 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         const int n0 = sh.op_n0[o], no = sh.op_no[o];
         unsigned long long* const tl = p.timeline ? p.timeline + ((size_t)c * LB_CHAIN_MAX_OPS + o) * 8 : nullptr;
         if (tl && tid == 0) { sh.stamp[0] = ch_globaltimer(); sh.stamp[1] = ch_clock(); }
+        // a mixer entry reads its parameter block and the token position (neither written by this launch) before it waits
+        int dn_pos = 0;
+        if (op.type == LB_CHAIN_OP_DELTANET) dn_pos = reinterpret_cast<const lb_dn_layer_params*>(op.ext)->pos[0];
         if (o > 0 && !(op.type == LB_CHAIN_OP_GEMV && op.x_src)) { // (a GEMV fed through a mailbox waits on the words themselves)
             // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
             CH_SYNC();
@@ -627,13 +631,38 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             // ---- the DeltaNet mixer of a layer: (value head, 32-column slab) units, one per team of 128 threads.
             //      The warps' weight rings stay full meanwhile (their next stages belong to the following GEMV). ----
             const lb_dn_layer_params& dn = *reinterpret_cast<const lb_dn_layer_params*>(op.ext);
-            const int team = tid >> 7;
+            const int team = tid >> 7, tt = tid & (DN_THREADS - 1), NU = dn.HV * (DN_D / DN_COLS);
             dn_unit_smem& sm = reinterpret_cast<dn_unit_smem*>(red)[team];
-            for (int u = c + G * team; u < dn.HV * (DN_D / DN_COLS); u += G * (LB_CHAIN_THREADS / DN_THREADS)) {
-                deltanet_layer_unit<false>(dn, u / (DN_D / DN_COLS), u % (DN_D / DN_COLS), tid & (DN_THREADS - 1), sm, [team] {
-                    asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "n"(DN_THREADS) : "memory");
-                });
-                asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "n"(DN_THREADS) : "memory"); // the unit's shared memory is reused
+            auto team_sync = [team] { asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "n"(DN_THREADS) : "memory"); };
+            const int pos = dn_pos;
+            if (NU <= 2 * G) {
+                // At most one unit for each of teams 0 and 1.  Teams 2 and 3 have none: they compute the two 5120-long gate
+                // dot products of those units' heads (in_proj_a: team 2, in_proj_b: team 3) while teams 0 and 1 are busy with
+                // the convolution and the state, and hand them over through shared memory (named barriers 5 and 6: the
+                // consumer waits, the two helper teams only arrive).
+                if (team < 2) {
+                    const int u = c + G * team;
+                    if (u < NU)
+                        deltanet_layer_unit<false, true>(dn, u / (DN_D / DN_COLS), u % (DN_D / DN_COLS), tt, sm, team_sync, pos, sh.dn_ab[team], [team] {
+                            asm volatile("bar.sync %0, %1;" ::"r"(5 + team), "n"(3 * DN_THREADS) : "memory");
+                        });
+                } else {
+                    for (int k = 0; k < 2; ++k) {
+                        const int u = c + G * k;
+                        if (u >= NU) break;
+                        const int h = u / (DN_D / DN_COLS);
+                        float v, unused;
+                        dn_gate_dot<1>(dn, (team == 2 ? dn.proj_a : dn.proj_b) + (size_t)h * dn.hidden, nullptr, tt, v, unused);
+                        v = dn_unit_sum(v, sm.red, tt, team_sync);
+                        if (tt == 0) sh.dn_ab[k][team - 2] = v;
+                        asm volatile("bar.arrive %0, %1;" ::"r"(5 + k), "n"(3 * DN_THREADS) : "memory");
+                    }
+                }
+            } else {
+                for (int u = c + G * team; u < NU; u += G * (LB_CHAIN_THREADS / DN_THREADS)) {
+                    deltanet_layer_unit<false, false>(dn, u / (DN_D / DN_COLS), u % (DN_D / DN_COLS), tt, sm, team_sync, pos, nullptr, [] {});
+                    team_sync(); // the unit's shared memory is reused
+                }
             }
             if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
             CH_SYNC();

@@ -145,5 +145,5 @@ extern "C" __global__ void decay_gate_beta(const __grid_constant__ lb_decay_para
 // ---------------------------------------------------------------------------
 extern "C" __global__ void __launch_bounds__(DN_THREADS) deltanet_layer_fused(const __grid_constant__ lb_dn_layer_params p) {
     __shared__ dn_unit_smem sm;
-    deltanet_layer_unit<true>(p, blockIdx.x, blockIdx.y, threadIdx.x, sm, [] { __syncthreads(); });
+    deltanet_layer_unit<true, false>(p, blockIdx.x, blockIdx.y, threadIdx.x, sm, [] { __syncthreads(); }, 0, nullptr, [] {});
 }

@@ -41,6 +41,46 @@ __device__ __forceinline__ void dn_unit_sum4(float& a, float& b, float& c, float
     d = (red[12] + red[13]) + (red[14] + red[15]);
 }
 
+// in_proj_a / in_proj_b of one value head: the partial dot products of thread t of a team with the normalised layer input
+// (bf16 rows, fp16 input, fp32 accumulate; ROWS = 2: both rows, ROWS = 1: the row `row0`).  All loads are issued before the
+// first use, so the dot products cost one trip to L2, not one per piece (hidden 5120 = exactly one pass of five
+// 8-element pieces per thread).
+template <int ROWS>
+__device__ __forceinline__ void dn_gate_dot(const lb_dn_layer_params& p, const uint16_t* row0, const uint16_t* row1, int t, float& a, float& b) {
+    const uint4* ra = reinterpret_cast<const uint4*>(row0);
+    const uint4* rb = reinterpret_cast<const uint4*>(row1);
+    const uint4* xv = reinterpret_cast<const uint4*>(p.xn);
+    const int n8 = p.hidden / 8;
+    a = b = 0.f;
+    for (int base = 0; base < n8; base += 5 * DN_THREADS) {
+        uint4 wa[5], wb[5], xx[5];
+#pragma unroll
+        for (int j = 0; j < 5; ++j) {
+            const int i = base + j * DN_THREADS + t;
+            const bool on = i < n8;
+            wa[j] = on ? __ldg(ra + i) : make_uint4(0u, 0u, 0u, 0u);
+            if (ROWS == 2) wb[j] = on ? __ldg(rb + i) : make_uint4(0u, 0u, 0u, 0u);
+            xx[j] = on ? __ldcg(xv + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 5; ++j) {
+            const uint32_t aw[4] = {wa[j].x, wa[j].y, wa[j].z, wa[j].w};
+            const uint32_t xw[4] = {xx[j].x, xx[j].y, xx[j].z, xx[j].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xw[q]));
+                a = fmaf(__uint_as_float(aw[q] << 16), xf.x, a);
+                a = fmaf(__uint_as_float(aw[q] & 0xffff0000u), xf.y, a);
+                if (ROWS == 2) {
+                    const uint32_t bw = q == 0 ? wb[j].x : q == 1 ? wb[j].y : q == 2 ? wb[j].z : wb[j].w;
+                    b = fmaf(__uint_as_float(bw << 16), xf.x, b);
+                    b = fmaf(__uint_as_float(bw & 0xffff0000u), xf.y, b);
+                }
+            }
+        }
+    }
+}
+
 // in_proj_a/b, conv1d x3, activate, l2norm x2, decay_gate, gate_sigmoid and the recurrence of one layer
 // (src/launcher.s:832-844; models/.../deltanet/kernels.ls:4-14):
 //   a,b   = in_proj_a/b . xn                       (bf16 rows, fp32 accumulate)
@@ -50,8 +90,11 @@ __device__ __forceinline__ void dn_unit_sum4(float& a, float& b, float& c, float
 //   r_j = sum_i k_i S_ij;  d_j = beta (v_j - r_j);  S_ij <- g S_ij + k_i d_j;  o_j = sum_i S_ij(new) q_i
 // The conv history is a ring of 4 slots indexed by position, so the units that share a key head can all read the
 // three previous slots while one of them writes the current one.
-template <bool STANDALONE, class Sync>
-__device__ __forceinline__ void deltanet_layer_unit(const lb_dn_layer_params& p, int h, int jb, int t, dn_unit_smem& sm, Sync sync) {
+// EXT_AB: the two gate dot products come from elsewhere (other teams of the block computed them meanwhile): wait_ab() then
+// ab[0], ab[1]; pos = the token position (read once by the caller).
+template <bool STANDALONE, bool EXT_AB, class Sync, class WaitAB>
+__device__ __forceinline__ void deltanet_layer_unit(const lb_dn_layer_params& p, int h, int jb, int t, dn_unit_smem& sm, Sync sync, int pos_in,
+                                                    const volatile float* ab, WaitAB wait_ab) {
     float (&ks)[DN_D] = sm.ks, (&qs)[DN_D] = sm.qs, (&vs)[DN_COLS] = sm.vs, (&red)[16] = sm.red;
     float (&part)[16][DN_COLS] = sm.part;
     const int gqa = p.HV / p.HK, kh = h / gqa;
@@ -66,7 +109,7 @@ __device__ __forceinline__ void deltanet_layer_unit(const lb_dn_layer_params& p,
     for (int rr = 0; rr < 8; ++rr) s[rr] = *reinterpret_cast<const float4*>(S + (size_t)(ti + 16 * rr) * DN_D + j0);
 
     if (STANDALONE) pdl_wait();
-    const int pos = p.pos[0];
+    const int pos = STANDALONE ? p.pos[0] : pos_in;
     // (the convolution's operands and the decay / beta dot products below share one trip to L2: no block barrier lies
     // between their loads)
     // causal depthwise conv (ring history) + SiLU on this head's q, k channels and this slab's v channels
@@ -89,40 +132,14 @@ __device__ __forceinline__ void deltanet_layer_unit(const lb_dn_layer_params& p,
     if (t < DN_COLS) p.conv_ring[(size_t)(pos & 3) * C + cv] = __ldcg(p.qkvz + cv);
     // decay / beta projections: two 5120-long dot products per value head
     float a = 0.f, b = 0.f;
-    {
-        const uint4* ra = reinterpret_cast<const uint4*>(p.proj_a + (size_t)h * p.hidden);
-        const uint4* rb = reinterpret_cast<const uint4*>(p.proj_b + (size_t)h * p.hidden);
-        const uint4* xv = reinterpret_cast<const uint4*>(p.xn);
-        // five 8-element pieces per thread and pass (hidden 5120 = exactly one pass): all fifteen loads are issued
-        // before the first use, so the two dot products cost one trip to L2, not one per piece
-        const int n8 = p.hidden / 8;
-        for (int base = 0; base < n8; base += 5 * DN_THREADS) {
-            uint4 wa[5], wb[5], xx[5];
-#pragma unroll
-            for (int j = 0; j < 5; ++j) {
-                const int i = base + j * DN_THREADS + t;
-                const bool on = i < n8;
-                wa[j] = on ? __ldg(ra + i) : make_uint4(0u, 0u, 0u, 0u);
-                wb[j] = on ? __ldg(rb + i) : make_uint4(0u, 0u, 0u, 0u);
-                xx[j] = on ? __ldcg(xv + i) : make_uint4(0u, 0u, 0u, 0u);
-            }
-#pragma unroll
-            for (int j = 0; j < 5; ++j) {
-                const uint32_t aw[4] = {wa[j].x, wa[j].y, wa[j].z, wa[j].w}, bw[4] = {wb[j].x, wb[j].y, wb[j].z, wb[j].w};
-                const uint32_t xw[4] = {xx[j].x, xx[j].y, xx[j].z, xx[j].w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xw[q]));
-                    a = fmaf(__uint_as_float(aw[q] << 16), xf.x, a);
-                    a = fmaf(__uint_as_float(aw[q] & 0xffff0000u), xf.y, a);
-                    b = fmaf(__uint_as_float(bw[q] << 16), xf.x, b);
-                    b = fmaf(__uint_as_float(bw[q] & 0xffff0000u), xf.y, b);
-                }
-            }
-        }
-    }
+    if (!EXT_AB) dn_gate_dot<2>(p, p.proj_a + (size_t)h * p.hidden, p.proj_b + (size_t)h * p.hidden, t, a, b);
     float qn = qv * qv, kn = kv * kv;
     dn_unit_sum4(a, b, qn, kn, red, t, sync);
+    if (EXT_AB) {
+        wait_ab();
+        a = ab[0];
+        b = ab[1];
+    }
     const float tt = a + bf16_bits_to_f32(p.dt_bias[h]);
     const float sp = tt > 20.f ? tt : log1pf(expf(tt));
     const float g = expf(-expf(p.a_log[h]) * sp);
