@@ -138,6 +138,14 @@ int lb_chain_launch(lb_ctx* c, const lb_chain_op* ops, int n_ops) {
             b->x_src = i; /* index of the producer + 1 */
         }
     }
+    /* per-head norm + gate prologue: the gate vector may be read (and its silu taken) before the entry's grid barrier when the
+     * entry right before does not write it -- everything earlier in the launch is complete by then */
+    for (int i = 0; i < n_ops; i++) {
+        lb_chain_op* b = &p.op[i];
+        if (b->type != LB_CHAIN_OP_GEMV || b->x_mode != LB_X_F32_HEADNORM_SILU) continue;
+        const lb_chain_op* a = i ? &p.op[i - 1] : NULL;
+        b->early_gate = !a || a->type == LB_CHAIN_OP_DELTANET || (a->type == LB_CHAIN_OP_GEMV && a->y != b->aux1 && (const void*)a->x_out != b->aux1);
+    }
     p.mail = (unsigned long long*)c->chain_mail;
     p.slots = pl.slots;
     p.table_rows = pl.table_rows;

@@ -207,6 +207,18 @@ __device__ __forceinline__ void ch_stage_tail(const unsigned char* stage, const 
     }
 }
 
+// silu of the 8 gate values of packed row r (zeros past the end of the vector)
+__device__ __forceinline__ void ch_gate_rows(const lb_chain_op& op, int r, int rows, float (&g)[8]) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    if (r < rows) {
+        const float4* zv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.aux1) + r * 8);
+        a = __ldcg(zv);
+        b = __ldcg(zv + 1);
+    }
+    g[0] = siluf_dev(a.x); g[1] = siluf_dev(a.y); g[2] = siluf_dev(a.z); g[3] = siluf_dev(a.w);
+    g[4] = siluf_dev(b.x); g[5] = siluf_dev(b.y); g[6] = siluf_dev(b.z); g[7] = siluf_dev(b.w);
+}
+
 // The activation vector of one GEMV as exact integers, for the whole block: X_k = rint(x_k * 2^shift) with
 // |X| < 2^22, split into three signed base-256 digits that become the B operand of the integer MMA (digit table
 // layout: digit_row_word).  x_k is the fp16 activation (after the optional norm prologue), so X_k is EXACT for every
@@ -215,7 +227,8 @@ __device__ __forceinline__ void ch_stage_tail(const unsigned char* stage, const 
 // first use, so the prologue costs one trip to L2, not one per row.
 template <int NI>
 __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& sh, unsigned char* xtab, int tid, bool write_x,
-                                             const unsigned long long* mailbox, uint32_t tag, uint32_t* status, unsigned long long* tl) {
+                                             const unsigned long long* mailbox, uint32_t tag, uint32_t* status, unsigned long long* tl,
+                                             const float (&gz)[2][8]) {
     const int lane = tid & 31, warp = tid >> 5;
     const int rows = op.K / 8;
     // a warp's rows of round i are 32 consecutive ones: when none of them exists the whole warp skips the round's arithmetic
@@ -336,18 +349,14 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
             const float4* wv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.aux0) + (tid & 15) * 8);
             const float4 wa = __ldg(wv), wb = __ldg(wv + 1);
             const float hw[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+            // silu(z) of this thread's rows: taken by the caller before the entry's barrier (op.early_gate), else here
             float z[NI][8];
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
-                const int r = tid + i * LB_CHAIN_THREADS;
-                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-                if (r < rows) {
-                    const float4* zv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.aux1) + r * 8);
-                    a = __ldcg(zv);
-                    b = __ldcg(zv + 1);
-                }
-                z[i][0] = a.x; z[i][1] = a.y; z[i][2] = a.z; z[i][3] = a.w;
-                z[i][4] = b.x; z[i][5] = b.y; z[i][6] = b.z; z[i][7] = b.w;
+                if (op.early_gate) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) z[i][j] = gz[i][j];
+                } else ch_gate_rows(op, tid + i * LB_CHAIN_THREADS, rows, z[i]);
             }
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
@@ -358,7 +367,7 @@ __device__ __forceinline__ float ch_prologue(const lb_chain_op& op, ch_shared& s
                 for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
                 const float hr = rsqrtf(ss * (1.0f / 128.0f) + op.eps);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * hr * hw[j] * siluf_dev(z[i][j]);
+                for (int j = 0; j < 8; ++j) v[i][j] = v[i][j] * hr * hw[j] * z[i][j];
             }
         }
 #pragma unroll
@@ -548,17 +557,27 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         const int n0 = sh.op_n0[o], no = sh.op_no[o];
         unsigned long long* const tl = p.timeline ? p.timeline + ((size_t)c * LB_CHAIN_MAX_OPS + o) * 8 : nullptr;
         if (tl && tid == 0) { sh.stamp[0] = ch_globaltimer(); sh.stamp[1] = ch_clock(); }
-        // a mixer entry reads its parameter block and the token position (neither written by this launch) before it waits
+        // ---- grid barrier: every result of entry o-1 is in memory before it is read (a GEMV fed through a mailbox waits on
+        //      the words themselves instead).  The block arrives first, then does what it may do before the others have
+        //      arrived, then waits. ----
+        const bool barrier = o > 0 && !(op.type == LB_CHAIN_OP_GEMV && op.x_src);
+        if (barrier) {
+            CH_SYNC();
+            // arrive with release: this block's results, ordered before by the block barrier, become visible to whoever observes the count
+            if (tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
+        }
+        // a mixer entry reads its parameter block and the token position (neither written by this launch) ...
         int dn_pos = 0;
         if (op.type == LB_CHAIN_OP_DELTANET) dn_pos = reinterpret_cast<const lb_dn_layer_params*>(op.ext)->pos[0];
-        if (o > 0 && !(op.type == LB_CHAIN_OP_GEMV && op.x_src)) { // (a GEMV fed through a mailbox waits on the words themselves)
-            // ---- grid barrier: every result of GEMV o-1 is in memory before it is read ----
-            CH_SYNC();
+        // ... and a GEMV whose input goes through the per-head norm takes the silu of its gate vector, where it may
+        float gz[2][8];
+        if (op.type == LB_CHAIN_OP_GEMV && op.x_mode == LB_X_F32_HEADNORM_SILU && op.early_gate) {
+            ch_gate_rows(op, tid, op.K / 8, gz[0]);
+            ch_gate_rows(op, tid + LB_CHAIN_THREADS, op.K / 8, gz[1]);
+        }
+        if (barrier) {
             if (tid == 0) {
-                // arrive with release (this block's results, ordered before by the barrier above, become visible to
-                // whoever observes the count), then poll with acquire; the status word of an earlier failed wait is
-                // looked at only once the wait is already long
-                asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
+                // poll with acquire; the status word of an earlier failed wait is looked at only once the wait is already long
                 const unsigned target = (unsigned)(++n_barriers) * (unsigned)G;
                 bool ok = sh.bad == 0;
                 if (ok && ld_acquire_gpu(p.sync) < target) {
@@ -678,8 +697,8 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         // ---- the activation vector as exact integers: three signed base-256 digit planes ----
         const unsigned long long* in_mail = op.x_src ? p.mail + (size_t)(op.x_src - 1) * LB_CHAIN_MAIL_WORDS : nullptr;
         const uint32_t in_tag = tag_base + (uint32_t)op.x_src;
-        const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status, tl)
-                                                             : ch_prologue<5>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status, tl);
+        const float unit = op.K <= 8 * LB_CHAIN_THREADS * 2 ? ch_prologue<2>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status, tl, gz)
+                                                             : ch_prologue<5>(op, sh, xtab, tid, c == 0, in_mail, in_tag, p.status, tl, gz);
 
         // the residual value this thread will add its column's result to: asked for now, so that the epilogue does not wait for it
         // (nobody else writes the column; this thread's own earlier store is what L2 holds)

@@ -100,6 +100,8 @@ typedef struct {
     int32_t x_mode, y_mode;
     float eps;
     int32_t type;     /* LB_CHAIN_OP_* */
+    int32_t early_gate; /* set by the launcher (LB_X_F32_HEADNORM_SILU): the entry right before this one does not write the gate
+                           vector aux1, so its silu is taken before this entry's grid barrier */
     const void* ext;  /* parameters of a non-GEMV entry, in device memory */
     int32_t x_src;    /* set by the launcher: index + 1 of the entry of this launch whose tagged results are this GEMV's x
                          (then x is read from that entry's mailbox and NO grid barrier precedes this entry); 0 = read p.x */
