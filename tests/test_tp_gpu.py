@@ -17,7 +17,9 @@ ROOT = Path(__file__).resolve().parent.parent
 def _gpu_count():
     try:
         out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
-        return sum(1 for l in out.splitlines() if l.startswith("GPU "))
+        n = sum(1 for l in out.splitlines() if l.startswith("GPU "))
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")          # a restricted process sees fewer than the box has
+        return min(n, len([v for v in vis.split(",") if v.strip()])) if vis is not None else n
     except Exception:  # noqa: BLE001
         return 0
 
