@@ -44,6 +44,7 @@
 #define CH_W LB_CHAIN_WARPS
 #define CH_GC LB_CHAIN_GC
 #define CH_SYNC() __syncthreads()
+#define CH_NO_STAGE 0xffffffffu // slot descriptor: nothing was asked for (the list is exhausted)
 
 // timeline stamps: the "memory" clobber keeps the read where it is written (between the block barriers and memory accesses around it)
 __device__ __forceinline__ unsigned long long ch_clock() {
@@ -72,6 +73,7 @@ struct __align__(16) ch_shared {
     int op_np[LB_CHAIN_MAX_OPS];     // pairs in the strip (a trailing single octet counts as one)
     int op_nch[LB_CHAIN_MAX_OPS];    // chunks of CH_GC K-groups per pair
     int op_pre[LB_CHAIN_MAX_OPS + 1]; // stages of this CTA before each GEMV (prefix sums of op_np * op_nch)
+    const unsigned char* op_packed[LB_CHAIN_MAX_OPS]; // the GEMV's strip-packed weights (a copy of the parameter, for indexed reads)
     uint32_t next; // next stage of the CTA's list that nobody has asked for yet
     uint32_t bad;  // a bounded wait ran out (set by any thread at any time)
     uint32_t snap; // copy of bad taken by thread 0 before a block barrier: the value all threads act on together
@@ -473,6 +475,7 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         sh.op_no[tid] = no;
         sh.op_np[tid] = (no + 1) / 2;
         sh.op_nch[tid] = (op.kg + CH_GC - 1) / CH_GC;
+        sh.op_packed[tid] = op.packed;
     }
     if (tid == 0) {
         sh.bad = 0;
@@ -513,26 +516,28 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     }
     __syncthreads();
     const uint64_t pol = l2_policy_evict_first();
-    uint32_t pending = 0;                             // stages asked for and not yet consumed (at most NS)
     uint32_t req_slot = 0, use_slot = 0, use_par = 0; // the warp's ring: next slot to fill, next to consume and its mbarrier phase
-    bool exhausted = false;                           // the list has no stage left
     unsigned char* const ring = smem + (size_t)warp * NS * LB_CHAIN_STAGE_BYTES;
     uint64_t* const wfull = full + warp * NS;
-    uint32_t* const wdesc = slot_desc + warp * NS;
+    uint32_t* const wdesc = slot_desc + warp * NS; // per slot: the descriptor of the stage asked for, CH_NO_STAGE when none
+    // Asking for a stage is lane 0's business alone (the other lanes learn about it from the slot's descriptor after the
+    // next __syncwarp).  The index of the stage to ask for next is taken one request ahead: the shared-memory atomic has
+    // long returned when the slot it is for becomes free.
+    uint32_t next_k = 0;
+    if (lane == 0) next_k = atomicAdd(&sh.next, 1u);
     auto request = [&]() { // weights never change: requests may run ahead of everything, the first ones start before griddepcontrol.wait
-        if (exhausted) return;
-        uint32_t k = 0;
-        if (lane == 0) k = atomicAdd(&sh.next, 1u);
-        k = __shfl_sync(0xffffffffu, k, 0);
-        if (k >= total) { exhausted = true; return; }
         if (lane == 0) {
-            const uint2 e = tab[k];
-            const uint32_t bytes = ((e.y >> 22) & 7u) * ((e.y >> 25) & 1u ? 2u * LB_CHAIN_RECORD : (uint32_t)LB_CHAIN_RECORD);
-            wdesc[req_slot] = e.y;
-            mbar_arrive_expect_tx(&wfull[req_slot], bytes);
-            bulk_g2s(ring + (size_t)req_slot * LB_CHAIN_STAGE_BYTES, p.op[e.y & 31u].packed + ((size_t)e.x << 4), bytes, &wfull[req_slot], pol);
+            uint32_t d = CH_NO_STAGE;
+            if (next_k < total) {
+                const uint2 e = tab[next_k];
+                const uint32_t bytes = ((e.y >> 22) & 7u) * ((e.y >> 25) & 1u ? 2u * LB_CHAIN_RECORD : (uint32_t)LB_CHAIN_RECORD);
+                d = e.y;
+                mbar_arrive_expect_tx(&wfull[req_slot], bytes);
+                bulk_g2s(ring + (size_t)req_slot * LB_CHAIN_STAGE_BYTES, sh.op_packed[e.y & 31u] + ((size_t)e.x << 4), bytes, &wfull[req_slot], pol);
+                next_k = atomicAdd(&sh.next, 1u);
+            }
+            wdesc[req_slot] = d;
         }
-        ++pending;
         req_slot = req_slot + 1 == (uint32_t)NS ? 0u : req_slot + 1;
     };
     for (int i = 0; i < NS; ++i) request();
@@ -708,9 +713,9 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         if (tl && tid == 0) sh.stamp[4] = ch_clock();
         // ---- the stages of GEMV o that this warp took.  Every stage leaves its 16 column sums in its own slot of `red`. ----
         const int nch = sh.op_nch[o];
-        while (pending) {
+        for (;;) {
             const uint32_t desc = *reinterpret_cast<volatile uint32_t*>(&wdesc[use_slot]);
-            if ((int)(desc & 31u) != o) break; // the warp's next stage belongs to a later GEMV
+            if (desc == CH_NO_STAGE || (int)(desc & 31u) != o) break; // nothing left, or the warp's next stage belongs to a later GEMV
             if (!__all_sync(0xffffffffu, mbar_wait(&wfull[use_slot], use_par))) { // the same answer in every lane
                 if (lane == 0) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_FULL); sh.bad = 1; }
                 break;
@@ -725,7 +730,6 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
             // (The lanes' loads from the slot are ahead of the request in the same in-order pipe: the shared-memory atomic
             // that picks the next stage returns after them, and the copy it leads to lands a memory latency later.)
             auto hand_back = [&]() {
-                --pending;
                 if (++use_slot == (uint32_t)NS) { use_slot = 0; use_par ^= 1u; }
                 __syncwarp();
                 request();
@@ -861,8 +865,9 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     }
     // no copy may still be in flight into this CTA's shared memory when it exits (only after a failed wait can
     // requested stages be left unconsumed)
-    for (; pending; --pending) {
-        mbar_wait(&wfull[use_slot], use_par);
+    __syncwarp();
+    for (int i = 0; i < NS; ++i) {
+        if (*reinterpret_cast<volatile uint32_t*>(&wdesc[use_slot]) != CH_NO_STAGE) mbar_wait(&wfull[use_slot], use_par);
         if (++use_slot == (uint32_t)NS) { use_slot = 0; use_par ^= 1u; }
     }
 }
