@@ -23,8 +23,10 @@
 //     16 column sums in the stage's own slot, and the slots of a column are added in the order of K: the
 //     result does not depend on which warp took which stage.
 //   * A DeltaNet entry runs the mixer of a layer ((value head, 32-column slab) units, four teams of 128
-//     threads per CTA; deltanet_core.cuh); an all-reduce entry adds every rank's partial vector into the
-//     residual stream over plain peer loads (comm_core.cuh).  The weight rings stay full meanwhile.
+//     threads per CTA of which two compute the gate dot products for the other two; deltanet_core.cuh).
+//     Under tensor parallelism a row-parallel GEMV exchanges its partial sums with the other GPUs in its own
+//     epilogue (8-byte (value, generation) words stored into every rank's buffer; comm_core.cuh).  The weight
+//     rings stay full meanwhile.
 //   * Between entries the block meets the other blocks at a grid barrier (an arrival counter in
 //     global memory: release-add, acquire poll, bounded spin).  All CTAs are resident: the grid is one
 //     CTA per SM and a CTA takes more than half of an SM's shared memory.
@@ -210,7 +212,7 @@ __device__ __forceinline__ void ch_stage_tail(const unsigned char* stage, const 
 }
 
 // silu of the 8 gate values of packed row r (zeros past the end of the vector)
-__device__ __forceinline__ void ch_gate_rows(const lb_chain_op& op, int r, int rows, float (&g)[8]) {
+__device__ __noinline__ void ch_gate_rows(const lb_chain_op& op, int r, int rows, float (&g)[8]) {
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
     if (r < rows) {
         const float4* zv = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.aux1) + r * 8);
@@ -546,12 +548,12 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
     const int fg = lane >> 2, ft = lane & 3;
     const ch_lane L = ch_lane_make(lane);
     pdl_wait(); // activations and barrier words belong to the stream order
-    // tensor parallel: the exchange generation of this GPU, read once (every all-reduce entry of the launch shares it)
+    // tensor parallel: the exchange generation of this GPU, read once (every exchange of the launch counts up from it)
     unsigned ar_gen0 = 0, n_barriers = 0; // n_barriers: grid barriers passed (thread 0 only)
     int ar_done = 0;
     const lb_tp_params* ar_tp = nullptr;
     for (int o = 0; o < p.n_ops; ++o)
-        if (p.op[o].type == LB_CHAIN_OP_ALLREDUCE || (p.op[o].type == LB_CHAIN_OP_GEMV && p.op[o].y_mode == LB_Y_TP_ALLREDUCE)) {
+        if (p.op[o].type == LB_CHAIN_OP_GEMV && p.op[o].y_mode == LB_Y_TP_ALLREDUCE) {
             ar_tp = reinterpret_cast<const lb_tp_params*>(p.op[o].ext);
             break;
         }
@@ -604,53 +606,6 @@ extern "C" __global__ void __launch_bounds__(LB_CHAIN_THREADS, 1) gemv_chain(con
         if (o == p.trigger_op) pdl_launch_dependents();
         if (sh.snap) break; // uniform: written before the barrier above, by one thread
 
-        if (op.type == LB_CHAIN_OP_ALLREDUCE) {
-            // ---- tensor parallel: every rank's partial vector (written by the GEMV before this entry into the rank's
-            //      exchange buffer; the grid barrier above made this GPU's complete) is added into the residual stream in
-            //      rank order.  CTA 0 tells the peers, every CTA waits on this GPU's own flag array and sums its own
-            //      columns with plain peer loads (no multicast). ----
-            const lb_tp_params& tp = *reinterpret_cast<const lb_tp_params*>(op.ext);
-            const unsigned gen = ar_gen0 + (unsigned)(++ar_done);
-            if (c == 0 && tid < tp.size) {
-                __threadfence_system(); // this GPU's partial (observed complete through the grid barrier) before the flag
-                st_release_sys(tp.peer_flags[tid] + tp.rank, gen);
-            }
-            if (tid < tp.size) {
-                const uint64_t t0 = globaltimer_ns(), limit = lb_wait_limit_ns(p.status);
-                bool ok = sh.bad == 0;
-                if (ok) {
-                    ok = false;
-                    for (unsigned it = 0; it < LB_WAIT_SPINS; ++it) {
-                        // generations only grow; the (int) difference keeps the test valid across wrap-around
-                        if ((int)(ld_acquire_sys(tp.my_flags + tid) - gen) >= 0) { ok = true; break; }
-                        if ((it & 63u) == 63u && (globaltimer_ns() - t0 > limit || *reinterpret_cast<volatile uint32_t*>(p.status) != 0u)) break;
-                    }
-                }
-                if (!ok) { atomicCAS(p.status, 0u, LB_DEV_TIMEOUT_PEER); sh.bad = 1; }
-            }
-            CH_SYNC();
-            if (!sh.bad) {
-                const int per = (tp.n + G - 1) / G, i = c * per + tid;
-                if (tid < per && i < tp.n) {
-                    float part[LB_TP_MAX];
-#pragma unroll
-                    for (int r = 0; r < LB_TP_MAX; ++r) part[r] = r < tp.size ? __ldcv(tp.partials[r] + LB_TP_PARTIAL(tp, tp.slot, r) + i) : 0.f;
-                    float sum = 0.f;
-#pragma unroll
-                    for (int r = 0; r < LB_TP_MAX; ++r) sum += part[r]; // rank order
-                    tp.x[i] = __ldcg(tp.x + i) + sum;
-                }
-            }
-            if (tid == 0) sh.snap = *reinterpret_cast<volatile uint32_t*>(&sh.bad);
-            CH_SYNC();
-            if (tl && tid == 0) {
-                const unsigned long long now = ch_clock();
-                tl[0] = sh.stamp[0]; tl[1] = sh.stamp[1]; tl[2] = sh.stamp[2];
-                tl[3] = tl[4] = tl[5] = tl[6] = tl[7] = now;
-            }
-            if (sh.snap) break;
-            continue;
-        }
         if (op.type == LB_CHAIN_OP_DELTANET) {
             // ---- the DeltaNet mixer of a layer: (value head, 32-column slab) units, one per team of 128 threads.
             //      The warps' weight rings stay full meanwhile (their next stages belong to the following GEMV). ----

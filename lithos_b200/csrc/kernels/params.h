@@ -75,7 +75,6 @@ typedef struct {
 #define LB_CHAIN_PACK_VERSION 1      /* bumped whenever the strip-packed byte layout changes */
 #define LB_CHAIN_OP_GEMV 0
 #define LB_CHAIN_OP_DELTANET 1      /* the DeltaNet mixer of one layer (deltanet_core.cuh); ext = lb_dn_layer_params in device memory */
-#define LB_CHAIN_OP_ALLREDUCE 2     /* tensor parallel: x += sum over ranks of the partial vectors (comm_core.cuh); ext = lb_tp_params in device memory */
 
 #define LB_CHAIN_WARPS 16            /* consumer warps; every warp streams its own stages */
 #define LB_CHAIN_THREADS (LB_CHAIN_WARPS * 32)
@@ -244,7 +243,7 @@ typedef struct {
 /* Exchange buffer of one rank (every rank maps every peer's): float [2][size][n_max] partial vectors (slot = exchange
  * parity, then the rank that produced the vector), float [n_max] for the sampling record, the flag words, then
  * uint2 [2][size][n_max] (value, generation) words.
- * "Pull" exchanges (tp_allreduce_add, LB_CHAIN_OP_ALLREDUCE): rank q leaves its partial in ITS OWN buffer at (slot, q),
+ * "Pull" exchanges (tp_allreduce_add): rank q leaves its partial in ITS OWN buffer at (slot, q),
  * raises flag [q] in every peer's flag array (system-scope release), readers load the vector from q's buffer.
  * "Pushed" exchanges (LB_Y_TP_ALLREDUCE): the thread that owns column n on rank q stores the 8-byte word (partial sum,
  * generation) into EVERY rank's word array at (slot, q, n) -- one store, delivered whole, so no fence and no flag -- and
