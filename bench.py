@@ -858,9 +858,10 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "chain", "batched", "timeline"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "chain", "batched", "timeline", "small"],
                     help="decode: the benchmark; gemv: config 0 alone; chain: the decode step's four GEMVs between two token "
-                         "mixers as persistent gemv_chain launches alone (the small case used for ncu captures)")
+                         "mixers as persistent gemv_chain launches alone (the small case used for ncu captures); small: the "
+                         "one-figure measurements of configs 0, 1 and 2 alone (the ncu target for the DeltaNet and attention kernels)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: number of layers (64 = the benchmark definition)")
     ap.add_argument("--batched-shapes", default="", help="batched workload: comma-separated substrings of the shape names to run (default all)")
     ap.add_argument("--batched-batches", default="1,4,16,32,64,128", help="batched workload: batch sizes")
@@ -889,6 +890,14 @@ def main():
             print(json.dumps(out), flush=True)
         if dist is not None:
             dist.destroy_process_group()
+        return
+    if args.workload == "small":
+        import lithos_b200 as lb
+        ctx = lb.Context(local)
+        out = bench_small_configs(ctx, lb)
+        ctx.close()
+        if rank == 0:
+            print(json.dumps(out), flush=True)
         return
     if args.workload in ("chain", "batched"):
         out = (bench_chain if args.workload == "chain" else bench_batched)(args, local)
