@@ -346,6 +346,14 @@ size_t lb_model_global_bytes(const lb_model_cfg* cfg, int which);
 int lb_save_weights(const char* model_dir, const lb_model_cfg* cfg, const void* const* layer_slots, const void* const* globals,
                     char* err, size_t errlen);
 int lb_load_weights(lb_ctx* ctx, const char* model_dir, lb_model* m);
+/* Writes <model_dir>/weight_index.bin for a safetensors checkpoint lying in model_dir: every *.safetensors file becomes a
+ * shard (name order), every slot the (shard, file offset, size) of the tensor the reference resolves it from
+ * (model.layers.<n>.<suffix> with the suffixes of src/launcher.s:92-141, compiler/megakernel-link.ls:220-269; globals
+ * model.embed_tokens.weight, lm_head.weight, model.norm.weight, :825-827), so that lb_load_weights -- or the reference's
+ * launcher -- reads the checkpoint in place.  Host only.  A tensor that is missing is LB_ERR_INVALID, one whose byte size is
+ * not what the model shape implies, or a malformed header, LB_ERR_IO.  The tensors are taken as stored: AutoGPTQ's
+ * "zero-point minus one" convention, where a checkpoint uses it, is the exporter's to undo. */
+int lb_weight_index_from_safetensors(const char* model_dir, const lb_model_cfg* cfg, char* err, size_t errlen);
 /* Host-only view of the same re-layout (no GPU needed): device matrix `which` (0 fused input
  * projections, 1 out/o projection, 2 gate|up interleaved, 3 down) of tensor-parallel shard
  * tp_rank/tp_size for `layer`.  Call with NULL outputs for the sizes, then with buffers of

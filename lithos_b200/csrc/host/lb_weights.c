@@ -294,3 +294,181 @@ LB_API int lb_load_weights(lb_ctx* c, const char* model_dir, lb_model* m) {
     lb_weight_index_close(w); /* every tensor has been re-laid and uploaded: the mappings are no longer needed */
     return st;
 }
+
+/* ---- safetensors -> weight_index.bin --------------------------------------------------------------------------------
+ * The reference resolves its slots from a safetensors checkpoint by tensor name (compiler/megakernel-link.ls:220-269 for the
+ * layers, :825-827 for the globals; slot names in src/launcher.s:92-141) and its launcher then reads weight_index.bin, whose
+ * generator is not in the tree.  This is that generator: every *.safetensors file of the directory becomes a shard, every slot
+ * the (shard, file offset, size) of the tensor `model.layers.<n>.<suffix>`.
+ * A safetensors file is: u64 LE header length, a JSON object {"<name>": {"dtype": .., "shape": [..], "data_offsets": [b, e]},
+ * ..., "__metadata__": {..}}, then the data; offsets are relative to the end of the header. */
+static const char* const k_dn_suffix[LB_WS_SLOTS] = {
+    "linear_attn.in_proj_qkv.qweight", "linear_attn.in_proj_qkv.scales", "linear_attn.in_proj_qkv.qzeros",
+    "linear_attn.in_proj_z.qweight", "linear_attn.in_proj_z.scales", "linear_attn.in_proj_z.qzeros",
+    "linear_attn.out_proj.qweight", "linear_attn.out_proj.scales", "linear_attn.out_proj.qzeros",
+    "linear_attn.in_proj_a.weight", "linear_attn.in_proj_b.weight", "linear_attn.A_log", "linear_attn.dt_bias",
+    "linear_attn.conv1d.weight", "linear_attn.norm.weight",
+    "mlp.gate_proj.qweight", "mlp.gate_proj.scales", "mlp.gate_proj.qzeros", "mlp.up_proj.qweight", "mlp.up_proj.scales", "mlp.up_proj.qzeros",
+    "mlp.down_proj.qweight", "mlp.down_proj.scales", "mlp.down_proj.qzeros", "input_layernorm.weight", "post_attention_layernorm.weight"};
+static const char* const k_fa_suffix[15] = {
+    "self_attn.q_proj.qweight", "self_attn.q_proj.scales", "self_attn.q_proj.qzeros", "self_attn.k_proj.qweight", "self_attn.k_proj.scales",
+    "self_attn.k_proj.qzeros", "self_attn.v_proj.qweight", "self_attn.v_proj.scales", "self_attn.v_proj.qzeros", "self_attn.o_proj.qweight",
+    "self_attn.o_proj.scales", "self_attn.o_proj.qzeros", "self_attn.q_norm.weight", "self_attn.k_norm.weight", NULL};
+static const char* const k_global_name[LB_WG_SLOTS] = {"model.embed_tokens.weight", "lm_head.weight", "model.norm.weight"};
+
+typedef struct { char* name; uint32_t shard; uint64_t off, size; } st_tensor;
+
+/* p at an opening quote: returns the position after the closing quote, *s / *n the text between (escapes are skipped, not decoded) */
+static const char* st_string(const char* p, const char* end, const char** s, size_t* n) {
+    if (p >= end || *p != '"') return NULL;
+    const char* q = ++p;
+    while (q < end && *q != '"') q += (*q == '\\' && q + 1 < end) ? 2 : 1;
+    if (q >= end) return NULL;
+    *s = p; *n = (size_t)(q - p);
+    return q + 1;
+}
+static const char* st_ws(const char* p, const char* end) { while (p < end && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) p++; return p; }
+/* p at the first character of a JSON value: returns the position after it (strings, nesting and escapes respected) */
+static const char* st_skip_value(const char* p, const char* end) {
+    int depth = 0;
+    while (p < end) {
+        if (*p == '"') { const char* s; size_t n; p = st_string(p, end, &s, &n); if (!p) return NULL; if (!depth) return p; continue; }
+        if (*p == '{' || *p == '[') depth++;
+        else if (*p == '}' || *p == ']') { if (--depth == 0) return p + 1; if (depth < 0) return NULL; }
+        else if (!depth && (*p == ',')) return p;
+        p++;
+    }
+    return depth ? NULL : p;
+}
+
+/* the tensors of one header; data_base = file offset of the data section */
+static int st_parse_header(const char* js, size_t len, uint32_t shard, uint64_t data_base, uint64_t file_bytes, st_tensor** tab, size_t* n_tab,
+                           size_t* cap, char* err, size_t errlen, const char* file) {
+    const char *p = st_ws(js, js + len), *end = js + len;
+    if (p >= end || *p != '{') return wfail(err, errlen, LB_ERR_IO, "%s: the header is not a JSON object", file);
+    p = st_ws(p + 1, end);
+    while (p < end && *p != '}') {
+        const char* key; size_t klen;
+        p = st_string(p, end, &key, &klen);
+        if (!p) return wfail(err, errlen, LB_ERR_IO, "%s: malformed header (tensor name)", file);
+        p = st_ws(p, end);
+        if (p >= end || *p != ':') return wfail(err, errlen, LB_ERR_IO, "%s: malformed header (':' after a name)", file);
+        p = st_ws(p + 1, end);
+        const char* v0 = p;
+        const char* v1 = st_skip_value(p, end);
+        if (!v1) return wfail(err, errlen, LB_ERR_IO, "%s: malformed header (value of %.*s)", file, (int)klen, key);
+        if (!(klen == 12 && !memcmp(key, "__metadata__", 12))) {
+            /* "data_offsets": [begin, end] inside the value */
+            const char* d = NULL;
+            for (const char* q = v0; q + 14 <= v1; q++)
+                if (!memcmp(q, "\"data_offsets\"", 14)) { d = q + 14; break; }
+            unsigned long long b = 0, e = 0;
+            if (!d || sscanf(d, " : [ %llu , %llu ]", &b, &e) != 2 || e < b || data_base + e > file_bytes)
+                return wfail(err, errlen, LB_ERR_IO, "%s: tensor %.*s has no valid data_offsets", file, (int)klen, key);
+            if (*n_tab == *cap) {
+                *cap = *cap ? *cap * 2 : 1024;
+                st_tensor* t = (st_tensor*)realloc(*tab, *cap * sizeof **tab);
+                if (!t) return wfail(err, errlen, LB_ERR_NOMEM, "weight index: out of memory");
+                *tab = t;
+            }
+            st_tensor* t = &(*tab)[(*n_tab)++];
+            t->name = (char*)malloc(klen + 1);
+            if (!t->name) return wfail(err, errlen, LB_ERR_NOMEM, "weight index: out of memory");
+            memcpy(t->name, key, klen); t->name[klen] = 0;
+            t->shard = shard; t->off = data_base + b; t->size = e - b;
+        }
+        p = st_ws(v1, end);
+        if (p < end && *p == ',') p = st_ws(p + 1, end);
+    }
+    return LB_OK;
+}
+
+static int st_cmp_name(const void* a, const void* b) { return strcmp(((const st_tensor*)a)->name, ((const st_tensor*)b)->name); }
+static int st_cmp_str(const void* a, const void* b) { return strcmp(*(const char* const*)a, *(const char* const*)b); }
+
+#include <dirent.h>
+
+LB_API int lb_weight_index_from_safetensors(const char* model_dir, const lb_model_cfg* c, char* err, size_t errlen) {
+    if (!model_dir || !c) return wfail(err, errlen, LB_ERR_INVALID, "lb_weight_index_from_safetensors: NULL argument");
+    /* the shard files, in name order */
+    char* files[WIDX_MAX_SHARDS];
+    int n_files = 0, st = LB_OK;
+    DIR* d = opendir(model_dir);
+    if (!d) return wfail(err, errlen, LB_ERR_IO, "cannot open %s (%s)", model_dir, strerror(errno));
+    for (struct dirent* e; (e = readdir(d)) != NULL;) {
+        const size_t n = strlen(e->d_name);
+        if (n < 13 || n > 255 || strcmp(e->d_name + n - 12, ".safetensors")) continue;
+        if (n_files == WIDX_MAX_SHARDS) { st = wfail(err, errlen, LB_ERR_IO, "%s holds more than %d safetensors files", model_dir, WIDX_MAX_SHARDS); break; }
+        files[n_files++] = strdup(e->d_name);
+    }
+    closedir(d);
+    if (st == LB_OK && !n_files) st = wfail(err, errlen, LB_ERR_IO, "%s holds no *.safetensors file", model_dir);
+    qsort(files, (size_t)n_files, sizeof files[0], st_cmp_str);
+    st_tensor* tab = NULL;
+    size_t n_tab = 0, cap = 0;
+    uint64_t shard_bytes[WIDX_MAX_SHARDS] = {0};
+    for (int i = 0; i < n_files && st == LB_OK; i++) {
+        char path[1536];
+        snprintf(path, sizeof path, "%s/%s", model_dir, files[i]);
+        size_t bytes = 0;
+        unsigned char* m = map_file(path, &bytes);
+        if (!m) { st = wfail(err, errlen, LB_ERR_IO, "cannot map %s (%s)", path, strerror(errno)); break; }
+        shard_bytes[i] = bytes;
+        uint64_t hlen = bytes >= 8 ? rd64(m) : 0;
+        if (bytes < 8 || hlen > bytes - 8) st = wfail(err, errlen, LB_ERR_IO, "%s: header length %llu does not fit the file", path, (unsigned long long)hlen);
+        else st = st_parse_header((const char*)m + 8, (size_t)hlen, (uint32_t)i, 8 + hlen, bytes, &tab, &n_tab, &cap, err, errlen, files[i]);
+        munmap(m, bytes);
+    }
+    const size_t n_entries = (size_t)LB_WG_SLOTS + (size_t)c->n_layers * LB_WS_SLOTS;
+    unsigned char* out = st == LB_OK ? (unsigned char*)calloc(n_entries, WIDX_ENTRY) : NULL;
+    if (st == LB_OK && !out) st = wfail(err, errlen, LB_ERR_NOMEM, "weight index: out of memory");
+    if (st == LB_OK) {
+        qsort(tab, n_tab, sizeof *tab, st_cmp_name);
+        for (size_t i = 0; i < n_entries && st == LB_OK; i++) {
+            char name[320];
+            size_t want;
+            if (i < LB_WG_SLOTS) {
+                snprintf(name, sizeof name, "%s", k_global_name[i]);
+                want = lb_model_global_bytes(c, (int)i);
+            } else {
+                const int l = (int)((i - LB_WG_SLOTS) / LB_WS_SLOTS), s = (int)((i - LB_WG_SLOTS) % LB_WS_SLOTS);
+                const char* suffix = (s < 15 && layer_is_fa(c, l)) ? k_fa_suffix[s] : k_dn_suffix[s];
+                want = lb_model_slot_bytes(c, l, s);
+                if (!suffix || !want) continue; /* slot unused in this kind of layer */
+                snprintf(name, sizeof name, "model.layers.%d.%s", l, suffix);
+            }
+            st_tensor key;
+            key.name = name;
+            const st_tensor* t = (const st_tensor*)bsearch(&key, tab, n_tab, sizeof *tab, st_cmp_name);
+            if (!t) { st = wfail(err, errlen, LB_ERR_INVALID, "tensor %s is not in the checkpoint", name); break; }
+            if (t->size != want) { st = wfail(err, errlen, LB_ERR_IO, "tensor %s holds %llu bytes, the model shape needs %zu", name, (unsigned long long)t->size, want); break; }
+            unsigned char* e = out + i * WIDX_ENTRY;
+            memcpy(e, &t->shard, 4); memcpy(e + 8, &t->off, 8); memcpy(e + 16, &t->size, 8);
+        }
+    }
+    if (st == LB_OK) {
+        char path[1536];
+        snprintf(path, sizeof path, "%s/weight_index.bin", model_dir);
+        FILE* f = fopen(path, "wb");
+        if (!f) st = wfail(err, errlen, LB_ERR_IO, "cannot create %s (%s)", path, strerror(errno));
+        else {
+            uint32_t hdr[8] = {WIDX_MAGIC, WIDX_VERSION, (uint32_t)n_files, (uint32_t)c->n_layers, LB_WS_SLOTS, LB_WG_SLOTS, 0, 0};
+            int bad = put(f, hdr, 32);
+            for (int i = 0; i < n_files; i++) {
+                unsigned char se[WIDX_SHARD_ENTRY];
+                memset(se, 0, sizeof se);
+                memcpy(se, files[i], strlen(files[i]));
+                memcpy(se + 256, &shard_bytes[i], 8);
+                bad |= put(f, se, sizeof se);
+            }
+            bad |= put(f, out, n_entries * WIDX_ENTRY);
+            bad |= fclose(f) != 0;
+            if (bad) st = wfail(err, errlen, LB_ERR_IO, "writing %s failed", path);
+        }
+    }
+    for (size_t i = 0; i < n_tab; i++) free(tab[i].name);
+    free(tab);
+    free(out);
+    for (int i = 0; i < n_files; i++) free(files[i]);
+    return st;
+}

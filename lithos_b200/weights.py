@@ -31,6 +31,7 @@ def _sigs():
     L.lb_model_global_bytes.restype = sz
     L.lb_save_weights.argtypes = [C.c_char_p, P(ModelCfg), P(vp), P(vp), C.c_char_p, sz]
     L.lb_load_weights.argtypes = [vp, C.c_char_p, vp]
+    L.lb_weight_index_from_safetensors.argtypes = [C.c_char_p, P(ModelCfg), C.c_char_p, sz]
     _done = True
 
 
@@ -58,6 +59,16 @@ def save_weights(model_dir: str, cfg: ModelCfg, layer_slots, globals_) -> None:
     g = (C.c_void_p * WG_SLOTS)(*[a.ctypes.data for a in globals_])
     err = C.create_string_buffer(512)
     st = lib().lb_save_weights(str(model_dir).encode(), C.byref(cfg), arr, g, err, 512)
+    if st != LB_OK:
+        raise LithosError(st, err.value.decode())
+
+
+def index_from_safetensors(model_dir: str, cfg: ModelCfg) -> None:
+    """lb_weight_index_from_safetensors: writes model_dir/weight_index.bin over the *.safetensors files lying there, every
+    slot found by the tensor name the reference resolves it from (src/launcher.s:92-141)"""
+    _sigs()
+    err = C.create_string_buffer(512)
+    st = lib().lb_weight_index_from_safetensors(str(model_dir).encode(), C.byref(cfg), err, 512)
     if st != LB_OK:
         raise LithosError(st, err.value.decode())
 
