@@ -564,7 +564,7 @@ def bench_decode(args, rank, local, world, dist):
         ctx.sync()
         t_p = time.perf_counter() - t_p
         prefill_rec = {"tokens": CTX_PREFILL, "seconds": round(t_p, 3), "tok_s": round(CTX_PREFILL / t_p, 1),
-                       "how": "lb_model_prefill: 32 chunks of 128 tokens, batched int4 projections (tcgen05), recurrence on chip per chunk, decode attention per token"}
+                       "how": "lb_model_prefill: 32 chunks of 128 tokens, batched int4 projections (tcgen05), recurrence on chip per chunk, causal tensor-core attention per chunk"}
     else:
         model.seed_state(CTX_PREFILL, args.seed)     # ONE global seeded state; every rank takes its heads of it
     model.checkpoint()                           # the recurrent state is restored before every measured pass

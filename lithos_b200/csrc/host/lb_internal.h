@@ -109,11 +109,13 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
     X(pf_embed)                       \
     X(pf_rmsnorm_f16)                 \
     X(pf_dn_frontend)                 \
+    X(pf_dn_ring)                     \
     X(pf_ab_gate)                     \
     X(pf_headnorm_gate_f16)           \
     X(pf_swiglu_f16)                  \
     X(pf_add)                         \
-    X(pf_f32_to_f16)                  \
+    X(pf_attn_prepare)                \
+    X(pf_attn_chunk)                  \
     X(l2_flush)
 
 enum {

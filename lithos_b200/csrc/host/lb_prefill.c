@@ -5,10 +5,12 @@
  * The reference's prompt path is its dequantising tensor-core GEMM (kernels/projection_gemm.sass:390-631) in the layer
  * order of compiler/megakernel-link.ls:281-525.  Here every projection of a chunk is one lb_gemm_int4 call (the weights
  * are read once per chunk: tcgen05 for 33..128 tokens), the DeltaNet recurrence walks the chunk's tokens inside one
- * launch with the state held on chip (lb_deltanet_step, n_steps = chunk), and attention runs the decode kernel once per
- * token over the cache rows before it (causal by construction).  Single GPU only.
+ * launch with the state held on chip (lb_deltanet_step, n_steps = chunk), and attention is two launches per chunk: the
+ * per-token part (norm, RoPE, KV append) with the decode kernel's own routine, then one causal tensor-core kernel over
+ * all the chunk's tokens (pf_attn_prepare, pf_attn_chunk).  Single GPU only.
  */
 #include "lb_model_priv.h"
+#include <math.h>
 
 extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N, int K, int x_mode, uint64_t norm_w, float eps,
                            uint64_t part_val, uint64_t part_idx);
@@ -63,16 +65,18 @@ static int gemm(lb_model* m, const q4_mat* w, CUdeviceptr x16, CUdeviceptr y32, 
 
 static int add_into_x(lb_model* m, int T) {
     lb_prefill_ws* w = m->ws;
-    long long n = (long long)T * m->cfg.hidden;
-    void* params[] = {&w->X, &w->y, &n};
-    return lb_launch(m->c, LBK_pf_add, blocks_for(n), 1, 1, 256, 0, params, 1);
+    int n4 = T * m->cfg.hidden / 4;
+    void* params[] = {&w->X, &w->y, &n4};
+    return lb_launch(m->c, LBK_pf_add, blocks_for(n4), 1, 1, 256, 0, params, 1);
 }
 
-static int norm_f16(lb_model* m, CUdeviceptr norm_w, int T) {
+/* xn16 = fp16(rmsnorm(X)); with add_y the projection result in y is added into X first (the residual add in the same pass) */
+static int norm_f16(lb_model* m, CUdeviceptr norm_w, int T, int add_y) {
     lb_prefill_ws* w = m->ws;
     int D = m->cfg.hidden;
     float eps = m->cfg.eps;
-    void* params[] = {&w->X, &norm_w, &w->xn16, &D, &eps};
+    CUdeviceptr add = add_y ? w->y : 0;
+    void* params[] = {&w->X, &add, &norm_w, &w->xn16, &D, &eps};
     return lb_launch(m->c, LBK_pf_rmsnorm_f16, (unsigned)T, 1, 1, 256, 0, params, 1);
 }
 
@@ -83,18 +87,23 @@ static int chunk_layer(lb_model* m, int l, int pos0, int T) {
     layer_t* L = &m->L[l];
     const int H = cfg->hidden;
     if (!L->loaded) return lb_fail(c, LB_ERR_STATE, "model: layer %d has no weights", l);
-    LB_TRY(norm_f16(m, L->input_norm, T));
+    LB_TRY(norm_f16(m, L->input_norm, T, 0));
     LB_TRY(gemm(m, &L->w_in, w->xn16, w->proj, T));
     int ld = L->w_in.N;
     if (!L->is_fa) {
         const int C = m->C_s, HK = m->HK, HV = m->HV;
         {
             void* params[] = {&w->proj, &ld, &L->conv_w, &L->conv_ring, &w->q, &w->k, &w->v, (void*)&HK, (void*)&HV, &pos0, &T};
-            LB_TRY(lb_launch(c, LBK_pf_dn_frontend, (unsigned)(2 * HK + HV), 1, 1, 128, 0, params, 1));
+            LB_TRY(lb_launch(c, LBK_pf_dn_frontend, (unsigned)T, (unsigned)(2 * HK + HV), 1, 128, 0, params, 1));
         }
         {
-            void* params[] = {&w->xn16, &L->proj_a, &L->proj_b, &L->a_log, &L->dt_bias, &w->g, &w->beta, (void*)&HV, (void*)&H};
-            LB_TRY(lb_launch(c, LBK_pf_ab_gate, (unsigned)T, (unsigned)((HV + 3) / 4), 1, 128, 0, params, 1));
+            int Cq = 2 * HK * 128 + HV * 128;
+            void* params[] = {&w->proj, &ld, &L->conv_ring, &Cq, &pos0, &T};
+            LB_TRY(lb_launch(c, LBK_pf_dn_ring, (unsigned)((Cq + 255) / 256), 1, 1, 256, 0, params, 1));
+        }
+        {
+            void* params[] = {&w->xn16, &L->proj_a, &L->proj_b, &L->a_log, &L->dt_bias, &w->g, &w->beta, (void*)&HV, (void*)&H, &T};
+            LB_TRY(lb_launch(c, LBK_pf_ab_gate, (unsigned)((T + 7) / 8), (unsigned)HV, 1, 128, 0, params, 1));
         }
         LB_TRY(lb_deltanet_step(c, L->dn_state, w->q, w->k, w->v, 0, w->g, w->beta, w->mix, HV, HK, T, 1));
         {
@@ -104,23 +113,33 @@ static int chunk_layer(lb_model* m, int l, int pos0, int T) {
             LB_TRY(lb_launch(c, LBK_pf_headnorm_gate_f16, (unsigned)T, (unsigned)((HV + 3) / 4), 1, 128, 0, params, 1));
         }
     } else {
-        const size_t row = (size_t)ld * 4, orow = (size_t)m->HQ * 256 * 4;
-        for (int s = 0; s < T; s++) /* causal: token s attends the cache rows [0, pos0 + s], its own appended first */
-            LB_TRY(lb_model_launch_attention(m, L, w->proj + (size_t)s * row, w->mix + (size_t)s * orow, 0, pos0 + s, pos0 + s + 1));
-        long long n = (long long)T * m->HQ * 256;
-        void* params[] = {&w->mix, &w->mix16, &n};
-        LB_TRY(lb_launch(c, LBK_pf_f32_to_f16, blocks_for(n), 1, 1, 256, 0, params, 1));
+        /* per token: norm, RoPE, the chunk's KV rows into the cache, queries as two bf16 terms (in the fp32 mixer buffer);
+         * then every token of the chunk at once, token s over the cache rows [0, pos0 + s] */
+        lb_pf_attn_params p;
+        memset(&p, 0, sizeof p);
+        p.proj = (const float*)w->proj;
+        p.q_norm_w = (const uint16_t*)L->q_norm; p.k_norm_w = (const uint16_t*)L->k_norm;
+        p.k_cache = (uint16_t*)L->k_cache; p.v_cache = (uint16_t*)L->v_cache;
+        p.qh = (uint16_t*)w->mix; p.ql = (uint16_t*)(w->mix + (size_t)PF_CHUNK * m->HQ * 256 * 2);
+        p.out = (uint16_t*)w->mix16;
+        p.ld = ld; p.HQ = m->HQ; p.HKV = m->HKV; p.pos0 = pos0; p.T = T; p.rot_dims = cfg->rot_dims; p.eps = cfg->eps;
+        for (int i = 0; i < cfg->rot_dims / 2; i++)
+            p.rope_freq[i] = exp2(-log2((double)cfg->rope_theta) * (double)i / (double)(cfg->rot_dims / 2));
+        void* params[] = {&p};
+        LB_TRY(lb_launch(c, LBK_pf_attn_prepare, (unsigned)T, 1, 1, 256, 0, params, 1));
+        const int rows = T * (m->HQ / m->HKV);
+        LB_TRY(lb_launch(c, LBK_pf_attn_chunk, (unsigned)((rows + LB_PF_ATTN_ROWS - 1) / LB_PF_ATTN_ROWS), (unsigned)m->HKV, 1,
+                         LB_PF_ATTN_THREADS, LB_PF_ATTN_SMEM, params, 1));
     }
     LB_TRY(gemm(m, &L->w_out, w->mix16, w->y, T));
-    LB_TRY(add_into_x(m, T));
     /* MLP */
-    LB_TRY(norm_f16(m, L->post_norm, T));
+    LB_TRY(norm_f16(m, L->post_norm, T, 1));
     LB_TRY(gemm(m, &L->w_gateup, w->xn16, w->gu, T));
     {
         int I = m->inter_s;
-        long long total = (long long)T * I;
-        void* params[] = {&w->gu, &w->act16, &I, &total};
-        LB_TRY(lb_launch(c, LBK_pf_swiglu_f16, blocks_for(total), 1, 1, 256, 0, params, 1));
+        int total4 = T * (I / 4);
+        void* params[] = {&w->gu, &w->act16, &I, &total4};
+        LB_TRY(lb_launch(c, LBK_pf_swiglu_f16, blocks_for(total4), 1, 1, 256, 0, params, 1));
     }
     LB_TRY(gemm(m, &L->w_down, w->act16, w->y, T));
     return add_into_x(m, T);

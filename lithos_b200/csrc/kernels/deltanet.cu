@@ -15,98 +15,124 @@
 // n_steps > 1 it stays on chip for the whole run of steps.
 #include "deltanet_core.cuh"
 
-template <typename T> __device__ __forceinline__ float ld_as_f32(const T* p, size_t i);
-template <> __device__ __forceinline__ float ld_as_f32<float>(const float* p, size_t i) { return p[i]; }
-template <> __device__ __forceinline__ float ld_as_f32<__nv_bfloat16>(const __nv_bfloat16* p, size_t i) {
-    return __bfloat162float(p[i]);
+// Thread (column jl of the slab, row quarter q4 = t & 3) holds rows 32*q4 .. 32*q4+31 of its column: the sums over rows
+// are 32 local terms and two shuffles between the four neighbouring lanes of a column, no shared-memory reduction.  With
+// the state on chip a step is a chain of latencies (one warp per scheduler) shorter than a trip to L2, so the operands of
+// a step (k, q, the slab's 32 values of v, g, beta) are copied DN_AHEAD - 1 steps ahead into a ring in shared memory by
+// cp.async -- loads into registers that far ahead still stalled every step, because a warp waits on a scoreboard counter,
+// not on one load -- and a step costs one block barrier.
+#define DN_AHEAD 4
+template <typename T> struct dn_in; // element type of q, k, v: how four consecutive values read as fp32
+template <> struct dn_in<float> {
+    static __device__ __forceinline__ float4 ld4(const unsigned char* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ float ld1(const unsigned char* p) { return *reinterpret_cast<const float*>(p); }
+};
+template <> struct dn_in<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 ld4(const unsigned char* p) {
+        const uint2 u = *reinterpret_cast<const uint2*>(p);
+        return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+    }
+    static __device__ __forceinline__ float ld1(const unsigned char* p) { return __uint_as_float((uint32_t)*reinterpret_cast<const uint16_t*>(p) << 16); }
+};
+__device__ __forceinline__ void dn_cp16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void dn_cp4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 
 // n_steps consecutive tokens: q,k are [n_steps][HK][128], v (z, out) are
 // [n_steps][HV][128], g and beta are [n_steps][HV].
 template <typename T>
 __device__ __forceinline__ void deltanet_body(const lb_deltanet_params& p, int n_steps) {
-    __shared__ float ks[DN_D], qs[DN_D];
-    __shared__ __align__(16) float part[16][DN_COLS];
+    constexpr int E = (int)sizeof(T);
+    constexpr int QS = 32 * E + 16;        // bytes per row quarter of k / q in a stage (+16: the four quarters on different banks)
+    constexpr int CQ = 2 * E;              // 16-byte pieces per row quarter
+    constexpr int OFF_Q = 4 * QS, OFF_V = 8 * QS, OFF_G = OFF_V + 32 * E, STAGE = OFF_G + 16;
+    __shared__ __align__(16) unsigned char ring[DN_AHEAD][STAGE];
     const int h = blockIdx.x, jb = blockIdx.y;
     const int kh = h / (p.HV / p.HK);
-    const int t = threadIdx.x, tj = t & 7, ti = t >> 3;
-    const int j0 = jb * DN_COLS + tj * 4;
-    float* S = p.state + (size_t)h * DN_D * DN_D;
+    const int t = threadIdx.x, q4 = t & 3, jl = t >> 2;
+    const int j = jb * DN_COLS + jl;
+    float* S = p.state + (size_t)h * DN_D * DN_D + (size_t)(32 * q4) * DN_D + j;
 
     pdl_wait();
-    float4 s[8];
+    // every thread brings at most one piece of a step's operands: 4 CQ pieces of k, 4 CQ of q, 2 E of v, g, beta
+    auto fetch = [&](int step) {
+        unsigned char* st = ring[step % DN_AHEAD];
+        if (t < 8 * CQ) {
+            const int which = t / (4 * CQ), i = t % (4 * CQ); // k or q, piece i of its 128 values
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(which ? p.q : p.k) + ((size_t)step * p.HK + kh) * DN_D * E;
+            dn_cp16(st + which * OFF_Q + (i / CQ) * QS + (i % CQ) * 16, src + i * 16);
+        } else if (t < 8 * CQ + 2 * E) {
+            const int i = t - 8 * CQ;
+            dn_cp16(st + OFF_V + i * 16, reinterpret_cast<const unsigned char*>(p.v) + (((size_t)step * p.HV + h) * DN_D + jb * DN_COLS) * E + i * 16);
+        } else if (t == 8 * CQ + 2 * E) {
+            dn_cp4(st + OFF_G, p.g + (size_t)step * p.HV + h);
+        } else if (t == 8 * CQ + 2 * E + 1) {
+            dn_cp4(st + OFF_G + 4, p.beta + (size_t)step * p.HV + h);
+        }
+    };
 #pragma unroll
-    for (int rr = 0; rr < 8; ++rr) s[rr] = *reinterpret_cast<const float4*>(S + (size_t)(ti + 16 * rr) * DN_D + j0);
+    for (int u = 0; u < DN_AHEAD - 1; ++u) {
+        if (u < n_steps) fetch(u);
+        asm volatile("cp.async.commit_group;" ::: "memory"); // one group per step, empty or not: the wait below counts groups
+    }
+    float s[32];
+#pragma unroll
+    for (int rr = 0; rr < 32; ++rr) s[rr] = S[(size_t)rr * DN_D];
 
     for (int step = 0; step < n_steps; ++step) {
-        const T* q = reinterpret_cast<const T*>(p.q) + ((size_t)step * p.HK + kh) * DN_D;
-        const T* k = reinterpret_cast<const T*>(p.k) + ((size_t)step * p.HK + kh) * DN_D;
-        const T* v = reinterpret_cast<const T*>(p.v) + ((size_t)step * p.HV + h) * DN_D;
-        __syncthreads(); // previous step's readers of ks/qs/part are done
-        ks[t] = ld_as_f32<T>(k, t);
-        qs[t] = ld_as_f32<T>(q, t);
-        __syncthreads();
-        const float g = p.g[(size_t)step * p.HV + h], beta = p.beta[(size_t)step * p.HV + h];
+        asm volatile("cp.async.wait_group %0;" ::"n"(DN_AHEAD - 2) : "memory"); // this thread's piece of this step has landed
+        __syncthreads(); // everybody's pieces are visible, and everybody is done with the previous step's stage ...
+        if (step + DN_AHEAD - 1 < n_steps) fetch(step + DN_AHEAD - 1); // ... which the step DN_AHEAD - 1 ahead now takes
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const unsigned char* st = ring[step % DN_AHEAD];
+        const unsigned char* kq = st + q4 * QS;
+        const float g = *reinterpret_cast<const float*>(st + OFF_G), beta = *reinterpret_cast<const float*>(st + OFF_G + 4);
+        const float v = dn_in<T>::ld1(st + OFF_V + jl * E);
 
-        // r = S^T k over this thread's 8 rows, then across the 16 row phases
-        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+        // r_j = sum_i k_i S_ij (pre-update state): four running sums per thread, then the column's four lanes
+        float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-        for (int rr = 0; rr < 8; ++rr) {
-            const float kk = ks[ti + 16 * rr];
-            r.x = fmaf(kk, s[rr].x, r.x);
-            r.y = fmaf(kk, s[rr].y, r.y);
-            r.z = fmaf(kk, s[rr].z, r.z);
-            r.w = fmaf(kk, s[rr].w, r.w);
+        for (int c = 0; c < 8; ++c) {
+            const float4 kk = dn_in<T>::ld4(kq + c * 4 * E);
+            r0 = fmaf(kk.x, s[4 * c + 0], r0);
+            r1 = fmaf(kk.y, s[4 * c + 1], r1);
+            r2 = fmaf(kk.z, s[4 * c + 2], r2);
+            r3 = fmaf(kk.w, s[4 * c + 3], r3);
         }
-        *reinterpret_cast<float4*>(&part[ti][tj * 4]) = r;
-        __syncthreads();
-        r = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float4 a = *reinterpret_cast<const float4*>(&part[i][tj * 4]);
-            r.x += a.x; r.y += a.y; r.z += a.z; r.w += a.w;
-        }
-        float4 d;
-        d.x = beta * (ld_as_f32<T>(v, j0 + 0) - r.x);
-        d.y = beta * (ld_as_f32<T>(v, j0 + 1) - r.y);
-        d.z = beta * (ld_as_f32<T>(v, j0 + 2) - r.z);
-        d.w = beta * (ld_as_f32<T>(v, j0 + 3) - r.w);
+        float r = (r0 + r1) + (r2 + r3);
+        r += __shfl_xor_sync(0xffffffffu, r, 1);
+        r += __shfl_xor_sync(0xffffffffu, r, 2);
+        const float d = beta * (v - r);
 
-        // update + read-out from the new state
-        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        // S_ij <- g S_ij + k_i d_j, o_j = sum_i S_ij(new) q_i
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-        for (int rr = 0; rr < 8; ++rr) {
-            const float kk = ks[ti + 16 * rr], qq = qs[ti + 16 * rr];
-            s[rr].x = fmaf(kk, d.x, g * s[rr].x);
-            s[rr].y = fmaf(kk, d.y, g * s[rr].y);
-            s[rr].z = fmaf(kk, d.z, g * s[rr].z);
-            s[rr].w = fmaf(kk, d.w, g * s[rr].w);
-            o.x = fmaf(s[rr].x, qq, o.x);
-            o.y = fmaf(s[rr].y, qq, o.y);
-            o.z = fmaf(s[rr].z, qq, o.z);
-            o.w = fmaf(s[rr].w, qq, o.w);
+        for (int c = 0; c < 8; ++c) {
+            const float4 kk = dn_in<T>::ld4(kq + c * 4 * E), qq = dn_in<T>::ld4(kq + OFF_Q + c * 4 * E);
+            s[4 * c + 0] = fmaf(kk.x, d, g * s[4 * c + 0]);
+            s[4 * c + 1] = fmaf(kk.y, d, g * s[4 * c + 1]);
+            s[4 * c + 2] = fmaf(kk.z, d, g * s[4 * c + 2]);
+            s[4 * c + 3] = fmaf(kk.w, d, g * s[4 * c + 3]);
+            o0 = fmaf(s[4 * c + 0], qq.x, o0);
+            o1 = fmaf(s[4 * c + 1], qq.y, o1);
+            o2 = fmaf(s[4 * c + 2], qq.z, o2);
+            o3 = fmaf(s[4 * c + 3], qq.w, o3);
         }
-        __syncthreads(); // everyone has consumed part[] from the r reduction
-        *reinterpret_cast<float4*>(&part[ti][tj * 4]) = o;
-        __syncthreads();
-        if (ti == 0) {
-            o = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float4 a = *reinterpret_cast<const float4*>(&part[i][tj * 4]);
-                o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
-            }
-            const size_t oi = ((size_t)step * p.HV + h) * DN_D + j0;
-            if (p.z) {
-                const float4 z = *reinterpret_cast<const float4*>(p.z + oi);
-                o.x *= siluf_dev(z.x); o.y *= siluf_dev(z.y); o.z *= siluf_dev(z.z); o.w *= siluf_dev(z.w);
-            }
-            *reinterpret_cast<float4*>(p.out + oi) = o;
+        float o = (o0 + o1) + (o2 + o3);
+        o += __shfl_xor_sync(0xffffffffu, o, 1);
+        o += __shfl_xor_sync(0xffffffffu, o, 2);
+        if (q4 == 0) {
+            const size_t oi = ((size_t)step * p.HV + h) * DN_D + j;
+            if (p.z) o *= siluf_dev(p.z[oi]);
+            p.out[oi] = o;
         }
     }
     pdl_launch_dependents();
 #pragma unroll
-    for (int rr = 0; rr < 8; ++rr) *reinterpret_cast<float4*>(S + (size_t)(ti + 16 * rr) * DN_D + j0) = s[rr];
+    for (int rr = 0; rr < 32; ++rr) S[(size_t)rr * DN_D] = s[rr];
 }
 
 extern "C" __global__ void __launch_bounds__(DN_THREADS) deltanet_step_bf16(const __grid_constant__ lb_deltanet_params p,

@@ -207,6 +207,26 @@ typedef struct {
     int32_t h0;              /* first global value head of this shard (tensor parallel), for nothing but clarity */
 } lb_dn_layer_params;
 
+/* ---- causal attention of a prompt chunk (pf_attn_prepare, pf_attn_chunk) --- */
+typedef struct {
+    const float* proj;        /* fp32 [T, ld]: per token, per head 256 query then 256 gate columns | k [HKV,256] | v [HKV,256] */
+    const uint16_t* q_norm_w; /* bf16 [256] */
+    const uint16_t* k_norm_w; /* bf16 [256] */
+    uint16_t* k_cache;        /* bf16 [ctx,HKV,256]: rows pos0 .. pos0+T-1 are written by pf_attn_prepare */
+    uint16_t* v_cache;
+    uint16_t* qh;             /* bf16 [T,HQ,256]: the normalised, rotated, pre-scaled queries, leading term */
+    uint16_t* ql;             /* bf16 [T,HQ,256]: what the rounding of qh left over */
+    uint16_t* out;            /* fp16 [T,HQ,256]: attention output x sigmoid(gate), the o projection's input */
+    int32_t ld, HQ, HKV, pos0, T, rot_dims;
+    float eps;
+    double rope_freq[64];     /* theta^(-i/(rot_dims/2)), computed on the host in double */
+} lb_pf_attn_params;
+/* pf_attn_chunk: query rows per CTA (16 per warp), threads, dynamic shared memory (two query tiles of ROWS x 528 B, two
+ * stages of 32 K rows + 32 V rows x 528 B) */
+#define LB_PF_ATTN_ROWS 32
+#define LB_PF_ATTN_THREADS 64
+#define LB_PF_ATTN_SMEM (2 * LB_PF_ATTN_ROWS * 528 + 2 * 2 * 32 * 528)
+
 /* ---- GQA decode attention ------------------------------------------------- */
 typedef struct {
     const void* q;        /* [HQ,256] bf16 or fp32 (raw, before norm) */

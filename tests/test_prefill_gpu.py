@@ -1,7 +1,7 @@
 """GPU: the prompt pass (lb_model_prefill) against the CPU oracle decoding the same tokens one by one.
 
 A prompt of seeded random tokens goes through the model in chunks (batched int4 projections, the recurrence walking
-the chunk inside one launch, attention once per token); then 8 greedy decode steps follow.  The oracle decodes all
+the chunk inside one launch, causal attention once per chunk); then 8 greedy decode steps follow.  The oracle decodes all
 tokens one at a time.  Checked: the token sampled after the prompt and the 8 decoded tokens are the oracle's, logits
 within 2e-3 of max|logit| (4 layers), DeltaNet states within 2e-3 (Frobenius per head), appended KV rows within a
 bf16 ulp of the row maximum, the convolution ring bit-identical to a token-by-token GPU decode."""
@@ -62,6 +62,13 @@ def test_prefill_two_chunks_and_ragged_tail(ctx, lb, oracle):
     """150 tokens = one full chunk of 128 + a tail of 22 (a different projection kernel), attention across the boundary"""
     from lithos_b200 import model as M
     run_case(ctx, lb, oracle, M.tiny(max_ctx=176), 150, 77)
+
+
+def test_prefill_three_chunks_long_context(ctx, lb, oracle):
+    """300 tokens = 128 + 128 + 44: the chunk attention reads cache rows written by two earlier chunks, its last chunk has
+    query tiles that end inside a tile, and the cache-row loop ends inside a staged block"""
+    from lithos_b200 import model as M
+    run_case(ctx, lb, oracle, M.tiny(max_ctx=320), 300, 4321)
 
 
 def test_prefill_single_token_and_continuation(ctx, lb, oracle):
