@@ -835,7 +835,7 @@ def bench_batched(args, local):
     ctx.close()
     return {"metric": "batched int4 projection sweep (config 4)", "unit": "us per launch", "n_gpus": 1, "data": "synthetic",
             "higher_is_better": False, "dtype": "int4 weights, fp16 activations, fp32 accumulation", "peak": peak, "peak_source": which,
-            "kernels": "gemm_int4_tc (tcgen05.mma 128 x NT x 16, TMEM accumulator), gemm_int4_mma_b8/b16/b32/b64 (mma.sync m16n8k16)", "l2": "weight sets of a shape rotate, together > L2", "sweep": sweep}
+            "kernels": "gemm_int4_tc_ta (tcgen05.mma 128 x NT x 16, accumulator and dequantised weights in TMEM), gemm_int4_mma_b8/b16/b32/b64 (mma.sync m16n8k16)", "l2": "weight sets of a shape rotate, together > L2", "sweep": sweep}
 
 
 def reference_decode(args, rank):
