@@ -556,7 +556,7 @@ def bench_decode(args, rank, local, world, dist):
     if args.prefill and world == 1:
         # the state is PRODUCED by the model: a seeded random token stream of 4096 tokens through the prompt pass
         prompt = (lb.fill_u32(CTX_PREFILL, args.seed, 500000) % cfg.vocab).astype(np.int64).tolist()
-        model.prefill(prompt[:128])                      # untimed: allocates the prompt-pass buffers, loads the kernels
+        model.prefill(prompt[:256])                      # untimed: allocates the prompt-pass buffers, loads the kernels
         model.reset_state()
         ctx.sync()
         t_p = time.perf_counter()
@@ -564,7 +564,7 @@ def bench_decode(args, rank, local, world, dist):
         ctx.sync()
         t_p = time.perf_counter() - t_p
         prefill_rec = {"tokens": CTX_PREFILL, "seconds": round(t_p, 3), "tok_s": round(CTX_PREFILL / t_p, 1),
-                       "how": "lb_model_prefill: 32 chunks of 128 tokens, batched int4 projections (tcgen05), recurrence on chip per chunk, causal tensor-core attention per chunk"}
+                       "how": "lb_model_prefill: 16 chunks of 256 tokens, batched int4 projections (tcgen05, 128 columns x 256 tokens per product), recurrence on chip per chunk, causal tensor-core attention per chunk"}
     else:
         model.seed_state(CTX_PREFILL, args.seed)     # ONE global seeded state; every rank takes its heads of it
     model.checkpoint()                           # the recurrent state is restored before every measured pass
@@ -687,7 +687,7 @@ def bench_decode(args, rank, local, world, dist):
 
 
 def bench_prompt_chunks(args, local):
-    """--workload prompt: two chunks of 128 prompt tokens at positions 3840..4095 through 8 layers of the benchmark's widths
+    """--workload prompt: two chunks of 256 prompt tokens at positions 3584..4095 through 8 layers of the benchmark's widths
     (6 DeltaNet + 2 attention, vocabulary 4096; 1.6 GB on the device): the small case the prompt pass is profiled on.  The
     caches below the chunk hold zeros (the time of a chunk does not depend on their values)."""
     import lithos_b200 as lb
@@ -697,21 +697,21 @@ def bench_prompt_chunks(args, local):
     ctx = lb.Context(local)
     m = M.Model(ctx, cfg)
     m.fill_synthetic(3)
-    toks = [int(t) for t in lb.fill_u32(256, 3, 999) % cfg.vocab]
-    m.prefill(toks[:128], pos0=0)          # untimed: allocates the prompt-pass buffers, loads the kernels
+    toks = [int(t) for t in lb.fill_u32(512, 3, 999) % cfg.vocab]
+    m.prefill(toks[:256], pos0=0)          # untimed: allocates the prompt-pass buffers, loads the kernels
     best = None
     for _ in range(max(1, min(args.steps, 10))):
         ctx.sync()
         t0 = time.perf_counter()
-        m.prefill(toks, pos0=3840)
+        m.prefill(toks, pos0=3584)
         ctx.sync()
         dt = time.perf_counter() - t0
         best = dt if best is None or dt < best else best
     m.close()
     ctx.close()
-    return {"metric": "prompt pass, 256 tokens at a 4k context through 8 layers", "value": round(best * 1e3, 3), "unit": "ms", "n_gpus": 1,
+    return {"metric": "prompt pass, 512 tokens at a 4k context through 8 layers", "value": round(best * 1e3, 3), "unit": "ms", "n_gpus": 1,
             "higher_is_better": False, "data": "synthetic", "timing": "host clock around lb_model_prefill + synchronize, best of the repeats",
-            "config": {"workload": "2 chunks x 128 tokens, positions 3840..4095, 6 DeltaNet + 2 attention layers of the 27B widths, vocabulary 4096"}}
+            "config": {"workload": "2 chunks x 256 tokens, positions 3584..4095, 6 DeltaNet + 2 attention layers of the 27B widths, vocabulary 4096"}}
 
 
 def bench_chain(args, local):
@@ -833,8 +833,8 @@ def bench_batched(args, local):
             dev.append([ctx.to_device(lb.fill_u32(K // 8 * N, 300 + s_, 1)), ctx.to_device(lb.fill_scales_f16(K // 128 * N, 300 + s_, 2)),
                         ctx.to_device(lb.fill_u32(K // 128 * (N // 8), 300 + s_, 3))])
         wbytes = K // 8 * N * 4 + K // 128 * N * 2 + K // 128 * (N // 8) * 4
-        d_x = ctx.to_device(lb.fill_normal(128 * K, 300, 4, dtype="f16"))
-        d_y = ctx.alloc(128 * N * 4)
+        d_x = ctx.to_device(lb.fill_normal(max(batches + [128]) * K, 300, 4, dtype="f16"))
+        d_y = ctx.alloc(max(batches + [128]) * N * 4)
         for B, flag in [(B, f) for B in batches for f in ((lb.GEMM_TCGEN05,) if B > 64 else (lb.GEMM_TCGEN05, lb.GEMM_MMA_SYNC) if B > 8 else (0, lb.GEMM_MMA_SYNC) if B == 1 else (0,))]:
             ctx.begin_capture()
             for j in range(reps):
@@ -892,7 +892,7 @@ def main():
                          "one-figure measurements of configs 0, 1 and 2 alone (the ncu target for the DeltaNet and attention kernels)")
     ap.add_argument("--layers", type=int, default=64, help="decode workload: number of layers (64 = the benchmark definition)")
     ap.add_argument("--batched-shapes", default="", help="batched workload: comma-separated substrings of the shape names to run (default all)")
-    ap.add_argument("--batched-batches", default="1,4,16,32,64,128", help="batched workload: batch sizes")
+    ap.add_argument("--batched-batches", default="1,4,16,32,64,128,256", help="batched workload: batch sizes")
     ap.add_argument("--seed", type=int, default=20260413)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--prefill", action="store_true", help="decode workload, 1 GPU: build the 4096-token state by running a seeded random prompt through "

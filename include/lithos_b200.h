@@ -193,16 +193,17 @@ int lb_gemv_chain_supports(lb_ctx* ctx, int K, int N, int swiglu);
  * The reference's batched path is its prefill projection (kernels/projection_gemm.sass:390-631:
  * int4 -> fp16 dequantisation into shared memory, eight 16x8x16 tensor-core products per k-step);
  * One token is handed to the GEMV kernel of lb_gemv_int4.
- * 33..128 tokens run on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory):
- * the weights are dequantised to fp16 - (q - z) * s, q - z exact, one fp16 rounding for the scale - into
- * shared memory, as the reference kernel does.  Up to 32 tokens use mma.sync (faster there, measured):
+ * 33..256 tokens run on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory):
+ * the weights are dequantised to fp16 - (q - z) * s, q - z exact, one fp16 rounding for the scale - as the
+ * reference kernel does, and handed to the tensor cores through tensor memory (129..256 tokens: one
+ * product of 128 columns x 256 tokens per k step, the weights converted once for all of them).  Up to 32 tokens use mma.sync (faster there, measured):
  * q - z stays exact and the group scale multiplies the group's fp32 sum, so row b of Y equals
  * lb_gemv_int4 on row b of X to fp32 rounding.  LB_GEMM_TCGEN05 forces the tensor-memory kernel for
  * 9 tokens or more, LB_GEMM_MMA_SYNC the mma.sync kernels for every size up to 64 tokens (cross-checks).
  * Overwrites y.  x and y must not overlap. */
 #define LB_GEMM_MMA_SYNC (1 << 4) /* flags: use the mma.sync kernels for every batch size */
 #define LB_GEMM_TCGEN05 (1 << 5)  /* flags: use the tcgen05 kernel (B >= 9) */
-#define LB_GEMM_MAX_BATCH 128
+#define LB_GEMM_MAX_BATCH 256
 int lb_gemm_int4(lb_ctx* ctx, uint64_t qweight, uint64_t scales, uint64_t qzeros, uint64_t x_f16, uint64_t y, int K,
                  int N, int B, int flags);
 /* bit-exact targets: W(k,n) = fma(float(q), s, -z*s) as fp32 [K,N]; q as u8 [K,N] */

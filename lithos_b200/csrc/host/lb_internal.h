@@ -91,6 +91,7 @@ int lb_driver_load(char* err, size_t errlen); /* LB_OK or LB_ERR_NO_DRIVER */
     X(gemm_int4_tc)                   \
     X(gemm_int4_tc_g1)                \
     X(gemm_int4_tc_ta)                \
+    X(gemm_int4_tc_ta_g1)             \
     X(gptq_dequant_f32)               \
     X(gptq_unpack_u8)                 \
     X(dense_bf16_gemv)                \

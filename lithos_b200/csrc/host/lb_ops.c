@@ -230,9 +230,9 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
     const int blocks = (N + 127) / 128, groups = K / 128;
     void* params[] = {&p};
     if ((B > 32 && !(flags & LB_GEMM_MMA_SYNC)) || (flags & LB_GEMM_TCGEN05)) {
-        const int nt = B > 64 ? 128 : B > 32 ? 64 : B > 16 ? 32 : 16;
-        const int ta = getenv("LB_GEMM_SMEM_A") == NULL; /* weights through tensor memory (default), or the shared-memory operand tiles for comparison */
-        const unsigned smem = ta ? (unsigned)((nt > 64 ? 6 : nt > 32 ? 12 : 16) * nt * 256) /* 6..16 activation stages */
+        const int nt = B > 128 ? 256 : B > 64 ? 128 : B > 32 ? 64 : B > 16 ? 32 : 16;
+        const int ta = nt > 128 || getenv("LB_GEMM_SMEM_A") == NULL; /* weights through tensor memory (default), or the shared-memory operand tiles for comparison (up to 128 tokens) */
+        const unsigned smem = ta ? (unsigned)((nt > 128 ? 3 : nt > 64 ? 6 : nt > 32 ? 12 : 16) * nt * 256) /* 3..16 activation stages */
                                  : (unsigned)(4 * 32768 + (nt > 64 ? 3 : nt > 32 ? 5 : nt > 16 ? 10 : 16) * nt * 256); /* four weight stages + 3..16 activation stages */
         if (x & 15) return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: x must be 16-byte aligned");
         CUtensorMap tm; /* X [B, K] fp16, box = 64 k (128 bytes) x NT tokens, laid down with the 128-byte swizzle */
@@ -248,7 +248,7 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
         if (ksplit > 8) ksplit = 8;
         while (ksplit > 1 && groups / ksplit < 4) ksplit--;
         if (ksplit < 1) ksplit = 1;
-        return lb_launch_cluster(c, ta ? LBK_gemm_int4_tc_ta : nt > 64 ? LBK_gemm_int4_tc_g1 : LBK_gemm_int4_tc, (unsigned)blocks, (unsigned)ksplit, 1, 576, smem, params, 1, (unsigned)ksplit);
+        return lb_launch_cluster(c, ta ? (nt > 128 ? LBK_gemm_int4_tc_ta_g1 : LBK_gemm_int4_tc_ta) : nt > 64 ? LBK_gemm_int4_tc_g1 : LBK_gemm_int4_tc, (unsigned)blocks, (unsigned)ksplit, 1, 576, smem, params, 1, (unsigned)ksplit);
     }
     const int rows = B > 32 ? 64 : B > 16 ? 32 : B > 8 ? 16 : 8; /* token rows the CTA stages */
     const int kernel = B > 32 ? LBK_gemm_int4_mma_b64 : B > 16 ? LBK_gemm_int4_mma_b32 : B > 8 ? LBK_gemm_int4_mma_b16 : LBK_gemm_int4_mma_b8;

@@ -1,10 +1,10 @@
-/* The prompt pass: lb_model_prefill runs n prompt tokens through the model in chunks of up to 128 and leaves the state a
+/* The prompt pass: lb_model_prefill runs n prompt tokens through the model in chunks of up to 256 and leaves the state a
  * token-by-token decode of the same tokens leaves (DeltaNet states, convolution rings, KV rows), then samples the token
  * that follows the prompt.
  *
  * The reference's prompt path is its dequantising tensor-core GEMM (kernels/projection_gemm.sass:390-631) in the layer
  * order of compiler/megakernel-link.ls:281-525.  Here every projection of a chunk is one lb_gemm_int4 call (the weights
- * are read once per chunk: tcgen05 for 33..128 tokens), the DeltaNet recurrence walks the chunk's tokens inside one
+ * are read once per chunk: tcgen05 for 33..256 tokens), the DeltaNet recurrence walks the chunk's tokens inside one
  * launch with the state held on chip (lb_deltanet_step, n_steps = chunk), and attention is two launches per chunk: the
  * per-token part (norm, RoPE, KV append) with the decode kernel's own routine, then one causal tensor-core kernel over
  * all the chunk's tokens (pf_attn_prepare, pf_attn_chunk).  Single GPU only.
@@ -16,7 +16,7 @@ extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N,
                            uint64_t part_val, uint64_t part_idx);
 extern int lb_dense_ctas(lb_ctx* c, int N, int K);
 
-#define PF_CHUNK 128
+#define PF_CHUNK 256
 
 struct lb_prefill_ws {
     CUdeviceptr tokens, X, xn16, proj, q, k, v, g, beta, mix, mix16, y, gu, act16;

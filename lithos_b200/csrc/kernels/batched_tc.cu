@@ -37,8 +37,8 @@
 #define TC_RING 4 // K-groups of packed words a thread keeps in registers ahead of its conversion (a multiple of TC_STAGES)
 #define TC_PSTRIDE 132                 // floats per row of the partial tile
 #define TC_TMEM_COLS 128
-#define TC_TA_COLS 512    // weights in tensor memory: accumulator in columns 0..127, weight stage s in columns 128 + 64 s .. + 63
-#define TC_TA_A0 128
+#define TC_TA_COLS 512    // weights in tensor memory: accumulator in columns 0..255 (one per token), weight stage s in columns
+#define TC_TA_A0 256      // 256 + 64 s .. + 63
 
 __device__ __forceinline__ uint32_t tc_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ void tc_cluster_sync() {
@@ -170,8 +170,8 @@ __device__ __forceinline__ void gemm_int4_tc_body(const lb_bgemm_params& p, unsi
     __shared__ __align__(8) uint64_t bar_done;
     __shared__ uint32_t tmem_base_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int NT = p.B > 64 ? 128 : p.B > 32 ? 64 : p.B > 16 ? 32 : 16; // tokens the product carries (rows past B are zero)
-    const int xstages = TA ? (NT > 64 ? 6 : NT > 32 ? 12 : TC_X_STAGES)
+    const int NT = p.B > 128 ? 256 : p.B > 64 ? 128 : p.B > 32 ? 64 : p.B > 16 ? 32 : 16; // tokens the product carries (rows past B are zero)
+    const int xstages = TA ? (NT > 128 ? 3 : NT > 64 ? 6 : NT > 32 ? 12 : TC_X_STAGES)
                            : (NT > 64 ? 3 : NT > 32 ? 5 : NT > 16 ? 10 : TC_X_STAGES); // activation stages that fit (beside the weight stages)
     const uint32_t x_stage_bytes = (uint32_t)NT * 256u, x_half = (uint32_t)NT * 128u; // a 64-k half: NT rows of 128 bytes
     unsigned char* a_smem = tc_smem;                          // [TC_STAGES][TC_A_STAGE]
@@ -395,4 +395,10 @@ extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc_g1(cons
 extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc_ta(const __grid_constant__ lb_bgemm_params p) { // weights through tensor memory
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     gemm_int4_tc_body<2, true>(p, tc_smem);
+}
+// 129..256 tokens: one product of 128 x 256 x 16 per k step (the weights of a K-group are converted once for twice the tokens);
+// three activation stages of 64 KB fit, so K-groups are handed over one at a time
+extern "C" __global__ void __launch_bounds__(TC_THREADS, 1) gemm_int4_tc_ta_g1(const __grid_constant__ lb_bgemm_params p) {
+    extern __shared__ __align__(1024) unsigned char tc_smem[];
+    gemm_int4_tc_body<1, true>(p, tc_smem);
 }

@@ -163,7 +163,7 @@ extern "C" __global__ void __launch_bounds__(128) pf_headnorm_gate_f16(const flo
 }
 
 // SwiGLU of a chunk: gu [T, 2I] in interleaved 64-wide (gate, up) blocks -> y16 [T, I] = silu(gate) * up    (kernels.ls:61-66)
-// four outputs per thread; total4 = T * I / 4 (fits 32 bits: a chunk has at most 128 tokens)
+// four outputs per thread; total4 = T * I / 4 (fits 32 bits: a chunk has at most 256 tokens)
 extern "C" __global__ void pf_swiglu_f16(const float* __restrict__ gu, __half* __restrict__ y, int I, int total4) {
     pdl_wait(); // launched with programmatic stream serialization: nothing of the previous kernel is read before this
     const int I4 = I / 4;

@@ -48,15 +48,18 @@ def test_rows_match_oracle(ctx, lb, K, N, zeros, path):
     qw, sc, qz, _ = gptq_case(K, N, seed=K + N, zeros=zeros)
     d_qw, d_sc = ctx.to_device(qw), ctx.to_device(sc)
     d_qz = ctx.to_device(qz) if zeros else None
-    X = batch_x(K, 128, seed=N)
+    X = batch_x(K, 256, seed=N)
     ref = np.stack([orc.gptq_gemv(qw, sc, qz, X[b], K, N)[0] for b in range(8)])
-    for B in (1, 3, 4, 8, 16, 17, 33, 64) + ((100, 128) if path == "tcgen05" else ()):  # more than 64 tokens: tcgen05 only
+    for B in (1, 3, 4, 8, 16, 17, 33, 64) + ((100, 128, 129, 200, 256) if path == "tcgen05" else ()):  # more than 64 tokens: tcgen05 only
         extra = force if B > 8 else 0  # up to 8 tokens there is only the mma.sync kernel
         y = run_gemm(ctx, lb, d_qw, d_sc, d_qz, X[:B], K, N, extra=extra)
         assert np.isfinite(y).all()
         nb = min(B, 8)
         for b in range(nb):
             assert rel_err_max(y[b], ref[b]) <= TOL, (B, b)
+        if B > 64:  # the last row and one in the upper half of the batch (other columns of tensor memory)
+            for b in (B - 1, B // 2 + 3):
+                assert rel_err_max(y[b], orc.gptq_gemv(qw, sc, qz, X[b], K, N)[0]) <= TOL, (B, b)
     y16 = run_gemm(ctx, lb, d_qw, d_sc, d_qz, X[:12], K, N, f32=False, extra=force)
     for b in range(5):
         assert rel_err_max(y16[b], ref[b].astype(np.float16)) <= 2e-3  # + one fp16 rounding of the result
@@ -130,7 +133,7 @@ def test_runs_inside_a_graph(ctx, lb):
 
 def test_bad_arguments_are_rejected(ctx, lb):
     d = ctx.alloc(1 << 16)
-    for K, N, B in ((100, 128, 4), (128, 24, 4), (128, 128, 0), (128, 128, 129)):
+    for K, N, B in ((100, 128, 4), (128, 24, 4), (128, 128, 0), (128, 128, 257)):
         with pytest.raises(lb_mod.LithosError):
             ctx.gemm_int4(d, d, None, d, d, K, N, B, lb.GEMV_Y_F32)
     with pytest.raises(lb_mod.LithosError):
