@@ -51,6 +51,7 @@
     X(EventCreate, cuEventCreate, (CUevent*, unsigned int))                                                     \
     X(EventDestroy, cuEventDestroy, (CUevent))                                                                  \
     X(EventRecord, cuEventRecord, (CUevent, CUstream))                                                          \
+    X(StreamWaitEvent, cuStreamWaitEvent, (CUstream, CUevent, unsigned int))                                    \
     X(EventSynchronize, cuEventSynchronize, (CUevent))                                                          \
     X(EventElapsedTime, cuEventElapsedTime, (float*, CUevent, CUevent))                                         \
     X(StreamBeginCapture, cuStreamBeginCapture, (CUstream, CUstreamCaptureMode))                                \

@@ -8,6 +8,12 @@
  * launch with the state held on chip (lb_deltanet_step, n_steps = chunk), and attention is two launches per chunk: the
  * per-token part (norm, RoPE, KV append) with the decode kernel's own routine, then one causal tensor-core kernel over
  * all the chunk's tokens (pf_attn_prepare, pf_attn_chunk).  Single GPU only.
+ *
+ * PF_STREAMS chunks are in flight at a time, each on its own stream with its own buffer set: chunk c+1 follows chunk c one layer behind
+ * (layer l of chunk c+1 waits for the event recorded after layer l of chunk c: the DeltaNet state, the convolution ring and
+ * the cache rows of a layer pass from chunk to chunk in order).  About half of a chunk-layer's time is kernels that
+ * cannot fill the GPU (the recurrence: 192 small CTAs walking 256 dependent steps; chunk attention; the element-wise
+ * kernels): they now run beside the other chunk's projections instead of alone.
  */
 #include "lb_model_priv.h"
 #include <math.h>
@@ -17,40 +23,76 @@ extern int lb_dense_launch(lb_ctx* c, uint64_t w, uint64_t x, uint64_t y, int N,
 extern int lb_dense_ctas(lb_ctx* c, int N, int K);
 
 #define PF_CHUNK 256
+#define PF_STREAMS 4 /* chunks in flight */
+
+typedef struct { /* the activations of one chunk */
+    CUdeviceptr X, xn16, proj, q, k, v, g, beta, mix, mix16, y, gu, act16;
+} pf_set;
+#define PF_SET_PTRS (sizeof(pf_set) / sizeof(CUdeviceptr))
 
 struct lb_prefill_ws {
-    CUdeviceptr tokens, X, xn16, proj, q, k, v, g, beta, mix, mix16, y, gu, act16;
+    pf_set set[PF_STREAMS]; /* one per stream */
+    pf_set* cur;            /* the set of the chunk being enqueued */
+    CUdeviceptr tokens;     /* the whole prompt's token ids [max_ctx] */
+    CUstream stream[PF_STREAMS];
+    CUevent* layer_done[PF_STREAMS]; /* [n_layers] per stream: recorded after a chunk's layer l */
+    CUevent fork, join[PF_STREAMS];
 };
 
 static int ws_alloc(lb_model* m) {
     if (m->ws) return LB_OK;
-    lb_prefill_ws* w = (lb_prefill_ws*)calloc(1, sizeof *w);
-    if (!w) return LB_ERR_NOMEM;
-    m->ws = w;
+    lb_prefill_ws* ws = (lb_prefill_ws*)calloc(1, sizeof *ws);
+    if (!ws) return LB_ERR_NOMEM;
+    m->ws = ws; /* lb_prefill_ws_free releases whatever a failure below leaves behind */
+    lb_ctx* ctx = m->c;
     const lb_model_cfg* c = &m->cfg;
     const size_t T = PF_CHUNK, H = (size_t)c->hidden, I = (size_t)m->inter_s;
     size_t n_in = (size_t)m->C_s + (size_t)m->HV * 128, n_fa = (size_t)(2 * m->HQ + 2 * m->HKV) * 256;
     if (n_fa > n_in) n_in = n_fa;
     size_t n_mix = (size_t)m->HV * 128 > (size_t)m->HQ * 256 ? (size_t)m->HV * 128 : (size_t)m->HQ * 256;
-    struct { CUdeviceptr* p; size_t bytes; } a[] = {
-        {&w->tokens, T * 4}, {&w->X, T * H * 4}, {&w->xn16, T * H * 2}, {&w->proj, T * n_in * 4},
-        {&w->q, T * (size_t)m->HK * 128 * 4}, {&w->k, T * (size_t)m->HK * 128 * 4}, {&w->v, T * (size_t)m->HV * 128 * 4},
-        {&w->g, T * (size_t)m->HV * 4}, {&w->beta, T * (size_t)m->HV * 4}, {&w->mix, T * n_mix * 4}, {&w->mix16, T * n_mix * 2},
-        {&w->y, T * H * 4}, {&w->gu, T * 2 * I * 4}, {&w->act16, T * I * 2}};
-    for (size_t i = 0; i < sizeof a / sizeof a[0]; i++) {
-        uint64_t d = 0;
-        LB_TRY(lb_malloc(m->c, a[i].bytes, &d));
-        *a[i].p = (CUdeviceptr)d;
+    uint64_t d = 0;
+    LB_TRY(lb_malloc(ctx, (size_t)c->max_ctx * 4, &d));
+    ws->tokens = (CUdeviceptr)d;
+    for (int s = 0; s < PF_STREAMS; s++) {
+        pf_set* w = &ws->set[s];
+        struct { CUdeviceptr* p; size_t bytes; } a[] = {
+            {&w->X, T * H * 4}, {&w->xn16, T * H * 2}, {&w->proj, T * n_in * 4},
+            {&w->q, T * (size_t)m->HK * 128 * 4}, {&w->k, T * (size_t)m->HK * 128 * 4}, {&w->v, T * (size_t)m->HV * 128 * 4},
+            {&w->g, T * (size_t)m->HV * 4}, {&w->beta, T * (size_t)m->HV * 4}, {&w->mix, T * n_mix * 4}, {&w->mix16, T * n_mix * 2},
+            {&w->y, T * H * 4}, {&w->gu, T * 2 * I * 4}, {&w->act16, T * I * 2}};
+        for (size_t i = 0; i < sizeof a / sizeof a[0]; i++) {
+            LB_TRY(lb_malloc(ctx, a[i].bytes, &d));
+            *a[i].p = (CUdeviceptr)d;
+        }
+        LB_CU(ctx, lb_drv.StreamCreate(&ws->stream[s], CU_STREAM_NON_BLOCKING));
+        ws->layer_done[s] = (CUevent*)calloc((size_t)c->n_layers, sizeof(CUevent));
+        if (!ws->layer_done[s]) return LB_ERR_NOMEM;
+        for (int l = 0; l < c->n_layers; l++) LB_CU(ctx, lb_drv.EventCreate(&ws->layer_done[s][l], CU_EVENT_DISABLE_TIMING));
+        LB_CU(ctx, lb_drv.EventCreate(&ws->join[s], CU_EVENT_DISABLE_TIMING));
     }
+    LB_CU(ctx, lb_drv.EventCreate(&ws->fork, CU_EVENT_DISABLE_TIMING));
     return LB_OK;
 }
 
 void lb_prefill_ws_free(lb_model* m) {
-    if (!m->ws) return;
-    CUdeviceptr* p = (CUdeviceptr*)m->ws;
-    for (size_t i = 0; i < sizeof(lb_prefill_ws) / sizeof(CUdeviceptr); i++)
-        if (p[i]) lb_drv.MemFree(p[i]);
-    free(m->ws);
+    lb_prefill_ws* ws = m->ws;
+    if (!ws) return;
+    for (int s = 0; s < PF_STREAMS; s++) {
+        if (ws->stream[s]) lb_drv.StreamSynchronize(ws->stream[s]);
+        CUdeviceptr* p = (CUdeviceptr*)&ws->set[s];
+        for (size_t i = 0; i < PF_SET_PTRS; i++)
+            if (p[i]) lb_drv.MemFree(p[i]);
+        if (ws->layer_done[s]) {
+            for (int l = 0; l < m->cfg.n_layers; l++)
+                if (ws->layer_done[s][l]) lb_drv.EventDestroy(ws->layer_done[s][l]);
+            free(ws->layer_done[s]);
+        }
+        if (ws->join[s]) lb_drv.EventDestroy(ws->join[s]);
+        if (ws->stream[s]) lb_drv.StreamDestroy(ws->stream[s]);
+    }
+    if (ws->fork) lb_drv.EventDestroy(ws->fork);
+    if (ws->tokens) lb_drv.MemFree(ws->tokens);
+    free(ws);
     m->ws = NULL;
 }
 
@@ -64,7 +106,7 @@ static int gemm(lb_model* m, const q4_mat* w, CUdeviceptr x16, CUdeviceptr y32, 
 }
 
 static int add_into_x(lb_model* m, int T) {
-    lb_prefill_ws* w = m->ws;
+    pf_set* w = m->ws->cur;
     int n4 = T * m->cfg.hidden / 4;
     void* params[] = {&w->X, &w->y, &n4};
     return lb_launch(m->c, LBK_pf_add, blocks_for(n4), 1, 1, 256, 0, params, 1);
@@ -72,7 +114,7 @@ static int add_into_x(lb_model* m, int T) {
 
 /* xn16 = fp16(rmsnorm(X)); with add_y the projection result in y is added into X first (the residual add in the same pass) */
 static int norm_f16(lb_model* m, CUdeviceptr norm_w, int T, int add_y) {
-    lb_prefill_ws* w = m->ws;
+    pf_set* w = m->ws->cur;
     int D = m->cfg.hidden;
     float eps = m->cfg.eps;
     CUdeviceptr add = add_y ? w->y : 0;
@@ -82,7 +124,7 @@ static int norm_f16(lb_model* m, CUdeviceptr norm_w, int T, int add_y) {
 
 static int chunk_layer(lb_model* m, int l, int pos0, int T) {
     lb_ctx* c = m->c;
-    lb_prefill_ws* w = m->ws;
+    pf_set* w = m->ws->cur;
     const lb_model_cfg* cfg = &m->cfg;
     layer_t* L = &m->L[l];
     const int H = cfg->hidden;
@@ -156,21 +198,40 @@ LB_API int lb_model_prefill(lb_model* m, const int* tokens, int n, int pos0, int
     if (!m->globals_loaded) return lb_fail(c, LB_ERR_STATE, "model: globals have no weights");
     LB_CU(c, lb_drv.CtxSetCurrent(c->cu_ctx));
     LB_TRY(ws_alloc(m));
-    lb_prefill_ws* w = m->ws;
+    lb_prefill_ws* ws = m->ws;
     const int H = cfg->hidden;
-    for (int c0 = 0; c0 < n; c0 += PF_CHUNK) {
-        const int T = n - c0 < PF_CHUNK ? n - c0 : PF_CHUNK;
-        LB_CU(c, lb_drv.MemcpyHtoDAsync(w->tokens, tokens + c0, (size_t)T * 4, c->stream));
-        LB_CU(c, lb_drv.StreamSynchronize(c->stream)); /* the caller's token array may be pageable */
-        {
-            void* params[] = {&m->embed, &w->tokens, &w->X, (void*)&H};
-            LB_TRY(lb_launch(c, LBK_pf_embed, (unsigned)T, 1, 1, 256, 0, params, 1));
+    CUstream main_stream = c->stream;
+    LB_CU(c, lb_drv.MemcpyHtoDAsync(ws->tokens, tokens, (size_t)n * 4, main_stream));
+    LB_CU(c, lb_drv.StreamSynchronize(main_stream)); /* the caller's token array may be pageable */
+    /* both chunk streams start behind what the caller's stream holds so far (an earlier decode step, the token copy) */
+    LB_CU(c, lb_drv.EventRecord(ws->fork, main_stream));
+    for (int s = 0; s < PF_STREAMS; s++) LB_CU(c, lb_drv.StreamWaitEvent(ws->stream[s], ws->fork, 0));
+    int st = LB_OK, chunk = 0;
+    for (int c0 = 0; c0 < n && st == LB_OK; c0 += PF_CHUNK, chunk++) {
+        const int T = n - c0 < PF_CHUNK ? n - c0 : PF_CHUNK, s = chunk % PF_STREAMS, prev = (chunk + PF_STREAMS - 1) % PF_STREAMS;
+        ws->cur = &ws->set[s];
+        c->stream = ws->stream[s]; /* every launch below goes to this chunk's stream */
+        CUdeviceptr toks = ws->tokens + (size_t)c0 * 4;
+        void* params[] = {&m->embed, &toks, &ws->cur->X, (void*)&H};
+        st = lb_launch(c, LBK_pf_embed, (unsigned)T, 1, 1, 256, 0, params, 1);
+        for (int l = 0; l < cfg->n_layers && st == LB_OK; l++) {
+            /* layer l's state, ring and cache rows come from the previous chunk's layer l (on the stream before this one) */
+            if (chunk > 0 && lb_drv.StreamWaitEvent(c->stream, ws->layer_done[prev][l], 0) != CUDA_SUCCESS) st = LB_ERR_CUDA;
+            if (st == LB_OK) st = chunk_layer(m, l, pos0 + c0, T);
+            if (st == LB_OK && lb_drv.EventRecord(ws->layer_done[s][l], c->stream) != CUDA_SUCCESS) st = LB_ERR_CUDA;
         }
-        for (int l = 0; l < cfg->n_layers; l++) LB_TRY(chunk_layer(m, l, pos0 + c0, T));
-        if (c0 + T == n) { /* the last prompt token's hidden state -> final norm, LM head, greedy sample */
-            LB_CU(c, lb_drv.MemcpyDtoDAsync(m->X, w->X + (size_t)(T - 1) * H * 4, (size_t)H * 4, c->stream));
+        if (st == LB_OK && c0 + T == n) { /* the last prompt token's hidden state -> final norm, LM head, greedy sample */
+            if (lb_drv.MemcpyDtoDAsync(m->X, ws->cur->X + (size_t)(T - 1) * H * 4, (size_t)H * 4, c->stream) != CUDA_SUCCESS) st = LB_ERR_CUDA;
         }
     }
+    c->stream = main_stream;
+    /* the caller's stream continues behind both chunk streams (also after a failed launch: nothing may still be running
+     * on buffers the caller is about to reuse) */
+    for (int s = 0; s < PF_STREAMS; s++) {
+        LB_CU(c, lb_drv.EventRecord(ws->join[s], ws->stream[s]));
+        LB_CU(c, lb_drv.StreamWaitEvent(main_stream, ws->join[s], 0));
+    }
+    if (st != LB_OK) return st == LB_ERR_CUDA ? lb_fail(c, LB_ERR_CUDA, "lb_model_prefill: a stream operation failed") : st;
     LB_CU(c, lb_drv.MemsetD32Async(m->d_pos, (unsigned)(pos0 + n - 1), 1, c->stream)); /* the sampling kernel advances it */
     LB_TRY(lb_dense_launch(c, m->lm_head, m->X, m->logits, m->vocab_s, H, LB_X_F32_RMSNORM, m->final_norm, cfg->eps, m->cand_val, m->cand_idx));
     LB_TRY(lb_model_launch_sampler(m));

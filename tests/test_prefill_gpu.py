@@ -58,17 +58,25 @@ def test_prefill_64_tokens_tiny_model(ctx, lb, oracle):
     run_case(ctx, lb, oracle, M.tiny(max_ctx=96), 64, 1234)
 
 
-def test_prefill_two_chunks_and_ragged_tail(ctx, lb, oracle):
-    """150 tokens = one full chunk of 128 + a tail of 22 (a different projection kernel), attention across the boundary"""
+def test_prefill_150_tokens_one_padded_chunk(ctx, lb, oracle):
+    """150 tokens: one chunk on the 256-token projection kernel (its upper tokens are padding)"""
     from lithos_b200 import model as M
     run_case(ctx, lb, oracle, M.tiny(max_ctx=176), 150, 77)
 
 
-def test_prefill_three_chunks_long_context(ctx, lb, oracle):
-    """300 tokens = 128 + 128 + 44: the chunk attention reads cache rows written by two earlier chunks, its last chunk has
-    query tiles that end inside a tile, and the cache-row loop ends inside a staged block"""
+def test_prefill_two_chunks_ragged_tiles(ctx, lb, oracle):
+    """300 tokens = 256 + 44: the chunk attention reads cache rows written by the earlier chunk, its last chunk has query
+    tiles that end inside a tile, and the cache-row loop ends inside a staged block"""
     from lithos_b200 import model as M
     run_case(ctx, lb, oracle, M.tiny(max_ctx=320), 300, 4321)
+
+
+def test_prefill_six_chunks_four_in_flight(ctx, lb, oracle):
+    """1400 tokens = 5 x 256 + 120: the chunks go round four streams (the fifth and sixth reuse the first two streams'
+    buffers and events), each layer waiting for the same layer of the chunk before it; state, convolution ring and cache
+    rows must pass from chunk to chunk in order"""
+    from lithos_b200 import model as M
+    run_case(ctx, lb, oracle, M.tiny(max_ctx=1440), 1400, 99)
 
 
 def test_prefill_single_token_and_continuation(ctx, lb, oracle):
