@@ -388,13 +388,16 @@ int lb_model_set_input(lb_model* m, int token, int pos); /* stream-ordered, by v
  * the host tracks the position from lb_model_set_input / lb_model_decode plus the steps issued since. */
 int lb_model_replay(lb_model* m, int n_steps);
 int lb_model_read_next(lb_model* m, int* next_out);   /* synchronises */
-/* The prompt pass.  Runs tokens[0..n) at positions pos0 .. pos0+n-1 through the model in chunks of up to 128 and leaves
+/* The prompt pass.  Runs tokens[0..n) at positions pos0 .. pos0+n-1 through the model in chunks of up to 256 and leaves
  * the state a token-by-token lb_model_decode of the same tokens leaves (DeltaNet states, convolution rings, KV rows);
  * *next_out (may be NULL) receives the greedy token that follows the prompt, the logits of the last prompt token are
  * in lb_model_logits_ptr, and lb_model_replay / lb_model_decode continue from position pos0+n.  Every projection of a
  * chunk is one lb_gemm_int4 call (the reference's prompt path is its dequantising tensor-core GEMM,
  * kernels/projection_gemm.sass:390-631; layer order compiler/megakernel-link.ls:281-525), the recurrence keeps the state
- * on chip for the chunk, attention runs the decode kernel once per token.  Single GPU (tp_size 1) only. */
+ * on chip for the chunk, attention is one causal tensor-core kernel per chunk.  Up to four chunks are in flight on
+ * streams of the library's own (a layer of a chunk waits for the same layer of the chunk before it); they start behind
+ * what the context's stream holds when the call is made and the context's stream continues behind them.  The first call
+ * allocates the chunks' buffers (about 90 MB each at the 27B widths).  Single GPU (tp_size 1) only. */
 int lb_model_prefill(lb_model* m, const int* tokens, int n, int pos0, int* next_out);
 int lb_model_step_kernels(const lb_model* m);         /* kernels per decode step */
 /* top_k == 0 (default): greedy; else every step samples among the top_k largest logits at `temperature`, the draw being a
