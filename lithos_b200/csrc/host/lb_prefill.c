@@ -39,11 +39,12 @@ struct lb_prefill_ws {
     CUevent fork, join[PF_STREAMS];
 };
 
-static int ws_alloc(lb_model* m) {
-    if (m->ws) return LB_OK;
+void lb_prefill_ws_free(lb_model* m);
+
+static int ws_fill(lb_model* m) {
     lb_prefill_ws* ws = (lb_prefill_ws*)calloc(1, sizeof *ws);
     if (!ws) return LB_ERR_NOMEM;
-    m->ws = ws; /* lb_prefill_ws_free releases whatever a failure below leaves behind */
+    m->ws = ws; /* ws_alloc releases whatever a failure below leaves behind */
     lb_ctx* ctx = m->c;
     const lb_model_cfg* c = &m->cfg;
     const size_t T = PF_CHUNK, H = (size_t)c->hidden, I = (size_t)m->inter_s;
@@ -72,6 +73,13 @@ static int ws_alloc(lb_model* m) {
     }
     LB_CU(ctx, lb_drv.EventCreate(&ws->fork, CU_EVENT_DISABLE_TIMING));
     return LB_OK;
+}
+
+static int ws_alloc(lb_model* m) {
+    if (m->ws) return LB_OK;
+    const int st = ws_fill(m);
+    if (st != LB_OK) lb_prefill_ws_free(m); /* never leave half a workspace behind for the next call */
+    return st;
 }
 
 void lb_prefill_ws_free(lb_model* m) {

@@ -363,7 +363,12 @@ static int st_parse_header(const char* js, size_t len, uint32_t shard, uint64_t 
             for (const char* q = v0; q + 14 <= v1; q++)
                 if (!memcmp(q, "\"data_offsets\"", 14)) { d = q + 14; break; }
             unsigned long long b = 0, e = 0;
-            if (!d || sscanf(d, " : [ %llu , %llu ]", &b, &e) != 2 || e < b || data_base + e > file_bytes)
+            char num[96]; /* a bounded, terminated copy: the header is a slice of a mapped file */
+            size_t nn = d ? (size_t)(v1 - d) : 0;
+            if (nn > sizeof num - 1) nn = sizeof num - 1;
+            if (d) memcpy(num, d, nn);
+            num[nn] = 0;
+            if (!d || sscanf(num, " : [ %llu , %llu ]", &b, &e) != 2 || e < b || data_base + e > file_bytes)
                 return wfail(err, errlen, LB_ERR_IO, "%s: tensor %.*s has no valid data_offsets", file, (int)klen, key);
             if (*n_tab == *cap) {
                 *cap = *cap ? *cap * 2 : 1024;
