@@ -76,3 +76,45 @@ def test_noalloc_rejects_what_does_not_fit(ctx, lb):
     st = L_.lb_attention_decode_noalloc(None, d.ptr, d.ptr, d.ptr, 0, 0, 0, d.ptr, d.ptr, d.ptr, 0, 8, 1, 0, 64, 1e7, 1e-6, err, 256)
     assert st == lb.LB_ERR_INVALID
     d.free()
+
+
+def test_noalloc_attention_inside_a_stream_capture(ctx, lb):
+    """What the entry point is for: the caller captures its own CUDA graph (driver API here) with the call inside, then
+    replays it.  The call must add only capturable work (a memset of its counters and the kernel) to the caller's stream,
+    and every replay must leave the bits of the uncaptured call (same position, so the appended row is rewritten in place)."""
+    L_ = lb.lib()
+    u64, i32 = C.c_uint64, C.c_int
+    L_.lb_attention_decode_noalloc.restype = i32
+    L_.lb_attention_decode_noalloc.argtypes = [C.c_void_p] + [u64] * 9 + [i32] * 5 + [C.c_float, C.c_float, C.c_char_p, C.c_size_t]
+    cuda = C.CDLL("libcuda.so.1")
+    HQ, HKV, L = 24, 4, 1500
+    c = attention_case(901, L, HQ, HKV)
+    d = {n: ctx.to_device(c[n]) for n in ("q", "k_new", "v_new", "gate", "q_norm_w", "k_norm_w")}
+    d_kc, d_vc = ctx.to_device(c["kc"]), ctx.to_device(c["vc"])
+    d_out = ctx.alloc(HQ * 256 * 4).zero()
+    ctx.sync()
+    err = C.create_string_buffer(256)
+
+    def call(stream):
+        st = L_.lb_attention_decode_noalloc(stream, d["q"].ptr, d["k_new"].ptr, d["v_new"].ptr, d["gate"].ptr, d["q_norm_w"].ptr,
+                                            d["k_norm_w"].ptr, d_kc.ptr, d_vc.ptr, d_out.ptr, L - 1, HQ, HKV, 0, 64, 1e7, 1e-6, err, 256)
+        assert st == lb.LB_OK, err.value.decode()
+
+    call(None)                                       # uncaptured (also the call that looks the scratch array up)
+    _device_sync()
+    want = d_out.download(np.float32, HQ * 256)
+    stream, graph, gexec = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    assert cuda.cuStreamCreate(C.byref(stream), 1) == 0                      # CU_STREAM_NON_BLOCKING
+    assert cuda.cuStreamBeginCapture_v2(stream, 0) == 0                      # CU_STREAM_CAPTURE_MODE_GLOBAL
+    call(stream)
+    assert cuda.cuStreamEndCapture(stream, C.byref(graph)) == 0 and graph.value
+    assert cuda.cuGraphInstantiateWithFlags(C.byref(gexec), graph, C.c_ulonglong(0)) == 0
+    for _ in range(2):
+        d_out.zero()
+        ctx.sync()
+        assert cuda.cuGraphLaunch(gexec, stream) == 0
+        assert cuda.cuStreamSynchronize(stream) == 0
+        assert np.array_equal(d_out.download(np.float32, HQ * 256), want)
+    assert cuda.cuGraphExecDestroy(gexec) == 0 and cuda.cuGraphDestroy(graph) == 0 and cuda.cuStreamDestroy_v2(stream) == 0
+    for b in list(d.values()) + [d_kc, d_vc, d_out]:
+        b.free()
