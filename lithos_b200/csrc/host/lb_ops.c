@@ -232,8 +232,9 @@ LB_API int lb_gemm_int4(lb_ctx* c, uint64_t qweight, uint64_t scales, uint64_t q
     if ((B > 32 && !(flags & LB_GEMM_MMA_SYNC)) || (flags & LB_GEMM_TCGEN05)) {
         const int nt = B > 128 ? 256 : B > 64 ? 128 : B > 32 ? 64 : B > 16 ? 32 : 16;
         const int ta = nt > 128 || getenv("LB_GEMM_SMEM_A") == NULL; /* weights through tensor memory (default), or the shared-memory operand tiles for comparison (up to 128 tokens) */
-        const unsigned smem = ta ? (unsigned)((nt > 128 ? 3 : nt > 64 ? 6 : nt > 32 ? 12 : 16) * nt * 256) /* 3..16 activation stages */
-                                 : (unsigned)(4 * 32768 + (nt > 64 ? 3 : nt > 32 ? 5 : nt > 16 ? 10 : 16) * nt * 256); /* four weight stages + 3..16 activation stages */
+        unsigned smem = ta ? (unsigned)((nt > 128 ? 3 : nt > 64 ? 6 : nt > 32 ? 12 : 16) * nt * 256) /* 3..16 activation stages */
+                           : (unsigned)(4 * 32768 + (nt > 64 ? 3 : nt > 32 ? 5 : nt > 16 ? 10 : 16) * nt * 256); /* four weight stages + 3..16 activation stages */
+        if (smem < (unsigned)nt * 132u * 4u) smem = (unsigned)nt * 132u * 4u; /* the epilogue's partial tile [nt][132] fp32 lies over the stages */
         if (x & 15) return lb_fail(c, LB_ERR_INVALID, "lb_gemm_int4: x must be 16-byte aligned");
         CUtensorMap tm; /* X [B, K] fp16, box = 64 k (128 bytes) x NT tokens, laid down with the 128-byte swizzle */
         cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)B};
