@@ -211,7 +211,7 @@ LB_API int lb_model_prefill(lb_model* m, const int* tokens, int n, int pos0, int
     CUstream main_stream = c->stream;
     LB_CU(c, lb_drv.MemcpyHtoDAsync(ws->tokens, tokens, (size_t)n * 4, main_stream));
     LB_CU(c, lb_drv.StreamSynchronize(main_stream)); /* the caller's token array may be pageable */
-    /* both chunk streams start behind what the caller's stream holds so far (an earlier decode step, the token copy) */
+    /* the chunk streams start behind what the caller's stream holds so far (an earlier decode step, the token copy) */
     LB_CU(c, lb_drv.EventRecord(ws->fork, main_stream));
     for (int s = 0; s < PF_STREAMS; s++) LB_CU(c, lb_drv.StreamWaitEvent(ws->stream[s], ws->fork, 0));
     int st = LB_OK, chunk = 0;
@@ -233,7 +233,7 @@ LB_API int lb_model_prefill(lb_model* m, const int* tokens, int n, int pos0, int
         }
     }
     c->stream = main_stream;
-    /* the caller's stream continues behind both chunk streams (also after a failed launch: nothing may still be running
+    /* the caller's stream continues behind all chunk streams (also after a failed launch: nothing may still be running
      * on buffers the caller is about to reuse) */
     for (int s = 0; s < PF_STREAMS; s++) {
         LB_CU(c, lb_drv.EventRecord(ws->join[s], ws->stream[s]));
